@@ -1,0 +1,371 @@
+#!/usr/bin/env python
+"""Benchmark of the GGUF quantized-linear decode path (Q4_K / Q4_0 GEMV sweep) on B200.
+
+One "step" is one pass over the whole decode sweep: batch 1, 4 and 16 activation rows, Q4_0 and Q4_K weights,
+shapes (K->N) 3840->3840, 3840->15360, 15360->3840, 5120->17408, 17408->5120, fp32 in / fp32 out.  The step
+streams 350 MB of distinct packed weights per batch size (larger than L2), in an order that puts 350 MB of
+other traffic between two uses of the same matrix, so no launch finds its weights in L2.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line.  `value` is algorithmic bytes per second over the timed steps with inputs resident in
+HBM; `e2e` is the same sweep through the host-buffer C-ABI call (activations copied in, results copied out,
+every call); `roofline` covers the Q4_K decode kernel at batch 1 and 4; `cpu_baseline` times the CPU oracle
+(a port of the reference's CPU path) on the host cores.  With N > 1 every matrix is tensor-parallel: up-projections
+are split by output rows, down-projections by 256-aligned input columns with an NCCL all-reduce of the partials.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SHAPES = [(3840, 3840), (3840, 15360), (15360, 3840), (5120, 17408), (17408, 5120)]  # (K, N)
+BATCHES = [1, 4, 16]
+Q4_0, Q4_K = 2, 12
+FORMATS = [(Q4_K, "q4_k"), (Q4_0, "q4_0")]
+METRIC = "Q4_K/Q4_0 decode GEMV sweep, algorithmic HBM GB/s"
+BPW = 0.5625
+
+
+def algorithmic_bytes(k: int, n: int, m: int) -> int:
+    """Packed weight bytes (original GGUF packing) + fp32 activations in + fp32 results out."""
+    return int(n * k * BPW) + m * k * 4 + m * n * 4
+
+
+def read_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return float(p["hbm_gbs"]), float(p.get("bf16_tflops", 1590.0)), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = "clocks.sm,clocks.max.sm,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 7:
+                continue
+            try:
+                sm.append(float(r[0]))
+                smax.append(float(r[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(smax) if smax else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def shard_plan(k: int, n: int, world: int, rank: int, block: int = 256):
+    """Tensor-parallel shard of W[n, k]: up-projections (n >= k) by output rows, down-projections (n < k) by
+    256-aligned input columns (K-quant super-blocks cannot be cut, src/backend/rocm/expert.rs:182-207)."""
+    if world == 1:
+        return "none", (0, n), (0, k)
+    if n >= k:
+        per = -(-n // world)
+        per = -(-per // 128) * 128
+        lo, hi = min(n, rank * per), min(n, (rank + 1) * per)
+        return "column", (lo, hi), (0, k)
+    units = k // block
+    base, extra = divmod(units, world)
+    lo = rank * base + min(rank, extra)
+    hi = lo + base + (1 if rank < extra else 0)
+    return "row", (0, n), (lo * block, hi * block)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from zllm_b200.backend import B200Context
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    ctx = B200Context(local_rank)
+    device = torch.device("cuda", local_rank)
+    hbm_peak, _, peak_kind = read_peaks()
+
+    # ---- synthetic inputs: N(0, 0.02) weights quantised on the device, N(0, 1) activations, seed 0
+    gen = torch.Generator(device=device)
+    cases = []  # (fmt_name, fmt, k, n, mode, weight, k_local, n_local)
+    for fmt, name in FORMATS:
+        for si, (k, n) in enumerate(SHAPES):
+            gen.manual_seed(1000 * fmt + si)
+            full = torch.randn((n, k), generator=gen, device=device, dtype=torch.float32) * 0.02
+            mode, (r0, r1), (c0, c1) = shard_plan(k, n, world, rank)
+            local = full[r0:r1, c0:c1].contiguous()
+            del full
+            packed = ctx.quantize(fmt, local)
+            w = ctx.prepare_weight(fmt, packed, r1 - r0, c1 - c0)
+            del local, packed
+            cases.append((name, fmt, k, n, mode, w, (c0, c1), (r0, r1)))
+    xs = {}
+    for k in sorted({k for k, _ in SHAPES}):
+        gen.manual_seed(77 + k)
+        xs[k] = torch.randn((max(BATCHES), k), generator=gen, device=device, dtype=torch.float32)
+    ctx.sync()
+    torch.cuda.synchronize()
+
+    # step order: batch-major, then format, then shape => 350 MB of other weights between two uses of a matrix
+    plan = []
+    for m in BATCHES:
+        for fmt, name in FORMATS:
+            for case in cases:
+                if case[1] == fmt:
+                    plan.append((m, case))
+    outs = {}
+    for m, case in plan:
+        name, fmt, k, n, mode, w, (c0, c1), (r0, r1) = case
+        outs[(m, name, k, n)] = torch.empty((m, r1 - r0), device=device, dtype=torch.float32)
+    x_local = {}
+    for m, case in plan:
+        name, fmt, k, n, mode, w, (c0, c1), (r0, r1) = case
+        x_local[(m, k, c0, c1)] = xs[k][:m, c0:c1].contiguous()
+
+    import ctypes as C
+
+    from zllm_b200 import ffi
+
+    def launch(m, case):
+        name, fmt, k, n, mode, w, (c0, c1), (r0, r1) = case
+        x = x_local[(m, k, c0, c1)]
+        y = outs[(m, name, k, n)]
+        ffi.call("zq_linear", ctx.handle, w.handle, C.c_void_p(x.data_ptr()), ffi.F32, m, C.c_void_p(y.data_ptr()), ffi.F32, None)
+        if mode == "row":
+            dist.all_reduce(y)
+
+    # events bracket the Q4_K batch-1 and batch-4 blocks (the headline kernel) inside the timed region
+    def step(events=None):
+        for bi, m in enumerate(BATCHES):
+            for fmt, name in FORMATS:
+                mark = events is not None and fmt == Q4_K and m <= 4
+                if mark:
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                for mm, case in plan:
+                    if mm == m and case[1] == fmt:
+                        launch(m, case)
+                if mark:
+                    e1.record()
+                    events.append((e0, e1))
+
+    step_bytes = sum(algorithmic_bytes(case[2], case[3], m) for m, case in plan)
+    q4k_kernel_bytes = sum(algorithmic_bytes(case[2], case[3], m) for m, case in plan if case[1] == Q4_K and m <= 4)
+    q4k_kernel_launches = sum(1 for m, case in plan if case[1] == Q4_K and m <= 4)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches_before = ctx.launch_count
+    events = []
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t0.record()
+    for _ in range(args.steps):
+        step(events)
+    t1.record()
+    barrier()
+    ctx.sync()
+    elapsed_ms = t0.elapsed_time(t1)
+    kernel_ms = sum(a.elapsed_time(b) for a, b in events)
+    launches = ctx.launch_count - launches_before
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([elapsed_ms, kernel_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms, kernel_ms = float(t[0]), float(t[1])
+        lt = torch.tensor([launches], device=device, dtype=torch.int64)
+        dist.all_reduce(lt)
+        launches = int(lt[0])
+    ms_per_step = elapsed_ms / args.steps
+    value = step_bytes / (ms_per_step * 1e-3) / 1e9
+    achieved = q4k_kernel_bytes * args.steps / (kernel_ms * 1e-3) / 1e9 / max(world, 1)
+
+    # ---- end to end through the host-buffer entry point (activations H2D, results D2H, every call)
+    e2e = None
+    if world == 1:
+        import numpy as np
+
+        hx = {k: xs[k].cpu().numpy() for k in xs}
+        hy = {key: np.zeros(tuple(v.shape), dtype=np.float32) for key, v in outs.items()}
+
+        def host_step():
+            for m, case in plan:
+                name, fmt, k, n, mode, w, _, _ = case
+                ctx.linear_host(hx[k][:m], w, hy[(m, name, k, n)])
+
+        host_step()
+        e2e_steps = max(1, min(args.steps, 5))
+        torch.cuda.synchronize()
+        h0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            host_step()
+        torch.cuda.synchronize()
+        h1 = time.perf_counter()
+        e2e = {
+            "value": round(step_bytes * e2e_steps / (h1 - h0) / 1e9, 2), "unit": "GB/s",
+            "h2d_bytes_per_step": sum(m * case[2] * 4 for m, case in plan), "d2h_bytes_per_step": sum(m * case[3] * 4 for m, case in plan),
+            "ms_per_step": round((h1 - h0) / e2e_steps * 1e3, 3), "api": "zq_linear_host",
+        }
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    cpu = cpu_baseline_sample() if world == 1 and not args.no_cpu else None
+    line = {
+        "metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u4*f16->f32", "data": "synthetic",
+        "config": {"workload": "configs[1]: decode GEMV sweep, batch 1/4/16, Q4_0+Q4_K, 5 shapes, fp32 in/out", "l2": "inputs larger than L2: 350 MB of distinct weights between reuses",
+                   "parallelism": f"tp{world}" if world > 1 else "single", "bytes_per_step": step_bytes, "launches_per_step": launches // max(args.steps, 1) // max(world, 1)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": hbm_peak, "unit": "GB/s", "frac": round(achieved / hbm_peak, 4), "traffic": None,
+                     "kernel": "zq::gemv_kernel<Q4_K, 1 column tile> (batch 1 and 4)", "peak_kind": peak_kind, "launches": q4k_kernel_launches * args.steps,
+                     "bytes_per_launch_avg": q4k_kernel_bytes // q4k_kernel_launches},
+        "gpu_launches": launches, "clocks": clocks, "e2e": e2e, "cpu_baseline": cpu,
+    }
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def _cpu_sweep(batches, repeat_seed=0):
+    """The decode sweep on the CPU oracle (ggml_quant::matvec for one row, ::matmul for several)."""
+    import numpy as np
+
+    from oracle import oracle as orc
+
+    rng = np.random.default_rng(repeat_seed)
+    work = []
+    for fmt, name in FORMATS:
+        for k, n in SHAPES:
+            e, b = orc.BLOCK[fmt]
+            # random packed bytes with small finite scales: CPU time does not depend on the values
+            data = rng.integers(0, 256, size=(n * k // e, b), dtype=np.uint8)
+            data[:, 0:2] = np.frombuffer(np.float16(0.01).tobytes(), dtype=np.uint8)
+            if fmt == Q4_K:
+                data[:, 2:4] = np.frombuffer(np.float16(0.01).tobytes(), dtype=np.uint8)
+            work.append((fmt, k, n, data.reshape(-1)))
+    xs = {k: rng.standard_normal((max(batches), k)).astype(np.float32) for k, _ in SHAPES}
+    return orc, work, xs
+
+
+def cpu_baseline_sample():
+    """Times the CPU oracle on a bounded sample of the same sweep (batch 1 and 4 of every matrix)."""
+    batches = [1, 4]
+    orc, work, xs = _cpu_sweep(batches)
+    orc.set_threads(0)
+    cores = orc.threads()
+    t0 = time.perf_counter()
+    total = 0
+    for m in batches:
+        for fmt, k, n, data in work:
+            orc.linear(fmt, data, n, k, xs[k][:m])
+            total += algorithmic_bytes(k, n, m)
+    dt = time.perf_counter() - t0
+    return {"value": round(total / dt / 1e9, 3), "unit": "GB/s", "cores": cores, "kind": "port", "sample": "batch 1 and 4 of all 10 matrices, one pass", "seconds": round(dt, 2)}
+
+
+def run_reference(args):
+    """Reference arm: the reference's own CPU algorithm for this path (C port in oracle/; the Rust original cannot
+    be built here), all host threads, same sweep and metric.  Rank 0 only."""
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if rank != 0:
+        return
+    orc, work, xs = _cpu_sweep(BATCHES)
+    orc.set_threads(0)
+    cores = orc.threads()
+
+    def step():
+        for m in BATCHES:
+            for fmt, k, n, data in work:
+                orc.linear(fmt, data, n, k, xs[k][:m])
+
+    step_bytes = sum(algorithmic_bytes(k, n, m) for m in BATCHES for _, k, n, _ in work)
+    warm = min(args.warmup, 1)
+    for _ in range(warm):
+        step()
+    steps = max(1, min(args.steps, 3))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = time.perf_counter() - t0
+    value = round(step_bytes * steps / dt / 1e9, 3)
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": steps, "warmup": warm, "ms_per_step": round(dt / steps * 1e3, 2),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "configs[1]: decode GEMV sweep, batch 1/4/16, Q4_0+Q4_K, 5 shapes, fp32 in/out", "bytes_per_step": step_bytes},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port", "sample": f"{steps} full sweep step(s) on the host cores"},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

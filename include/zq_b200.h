@@ -1,0 +1,107 @@
+/*
+ * zq_b200 — C ABI of the B200 (sm_100a) GGUF block-quantized linear layer.
+ *
+ * This is the boundary a zLLM CUDA backend binds instead of its NVRTC kernel layer.  Every entry point names
+ * the reference interface it replaces (paths relative to the reference project root).  Conventions:
+ *   - weights W[rows = out features, cols = in features], GGUF packed rows (src/kernel/cpu/ggml_quant.rs:193-197);
+ *     activations X[m, cols] row-major; outputs Y[m, rows] row-major, Y[token*rows + row]
+ *     (src/kernel/cpu/ggml_quant.rs:309-313);
+ *   - GGUF type ids: Q4_0 = 2, Q8_0 = 8, Q4_K = 12, IQ4_NL = 20 (src/weight/container/gguf.rs:112-151);
+ *   - every call returns 0 on success; on failure it returns a non-zero code and, when `err` is not NULL, fills
+ *     err->message.  Shape and byte-count mismatches are errors, never undefined behaviour
+ *     (src/kernel/cuda/linear.rs:1441-1444).  The layout of zq_error follows the reference's own native-FFI
+ *     convention, NativeError{ message: [c_char; 512] } (src/backend/qnn/mod.rs:64-133);
+ *   - all work is enqueued on the context's stream and is asynchronous unless the name says `_host`;
+ *   - device pointers are plain `void*`/`float*`; no framework types cross this boundary.
+ */
+#ifndef ZQ_B200_H
+#define ZQ_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct zq_ctx zq_ctx;
+typedef struct zq_weight zq_weight;
+typedef struct zq_moe_experts zq_moe_experts;
+
+typedef struct zq_error { char message[512]; } zq_error;
+
+enum { ZQ_Q4_0 = 2, ZQ_Q8_0 = 8, ZQ_Q4_K = 12, ZQ_IQ4_NL = 20 };
+enum { ZQ_F32 = 0, ZQ_F16 = 1, ZQ_BF16 = 2 };
+enum { ZQ_OK = 0, ZQ_ERR_SHAPE = 1, ZQ_ERR_UNSUPPORTED = 2, ZQ_ERR_CUDA = 3, ZQ_ERR_ARG = 4, ZQ_ERR_DEVICE_STATUS = 5, ZQ_ERR_DIST = 6 };
+
+/* ---- context: CudaContext::new (src/backend/cuda/context.rs:248-276): one device, one compute stream. ---- */
+int zq_ctx_create(int device, zq_ctx **out, zq_error *err);
+void zq_ctx_destroy(zq_ctx *ctx);
+/* Run on a caller-owned cudaStream_t instead of the context's own stream (NULL restores the own stream). */
+int zq_ctx_set_stream(zq_ctx *ctx, void *cuda_stream, zq_error *err);
+/* Waits for the stream and reports any status word a kernel left behind (bounded waits that ran out). */
+int zq_ctx_sync(zq_ctx *ctx, zq_error *err);
+int zq_ctx_sm_count(const zq_ctx *ctx);
+/* Number of kernels this library has launched on the context since creation (bench accounting). */
+uint64_t zq_ctx_launch_count(const zq_ctx *ctx);
+
+/* ---- weights: Backend::prepare_weight(LinearWeight::gguf) (src/backend/mod.rs:333; src/backend/cuda/mod.rs:61-72)
+ * and CudaGgufPacked (src/backend/cuda/resident.rs:82-107).  `nbytes` must equal rows*cols/block*block_bytes
+ * (src/kernel/cuda/linear.rs:1441-1444).  The library owns the resident copy. ---- */
+int zq_weight_prepare(zq_ctx *ctx, uint32_t ggml_type, const void *host_bytes, size_t nbytes, size_t rows, size_t cols, zq_weight **out, zq_error *err);
+/* Same, from GGUF-layout bytes already on the device (expert tensors sliced on device, synthetic inputs). */
+int zq_weight_prepare_device(zq_ctx *ctx, uint32_t ggml_type, const void *dev_bytes, size_t nbytes, size_t rows, size_t cols, zq_weight **out, zq_error *err);
+void zq_weight_release(zq_weight *w);
+size_t zq_weight_rows(const zq_weight *w);
+size_t zq_weight_cols(const zq_weight *w);
+uint32_t zq_weight_type(const zq_weight *w);
+/* Bytes of the original GGUF packing (the figure roofline accounting uses). */
+size_t zq_weight_gguf_bytes(const zq_weight *w);
+
+/* ---- codec: codec::ggml::dequantize (src/weight/codec/ggml.rs:146-160), bit-exact f32 [rows, cols]. ---- */
+int zq_dequantize_f32(zq_ctx *ctx, const zq_weight *w, float *dev_out, zq_error *err);
+/* gguf_rows_f16 (src/kernel/cuda/linear.rs:1420-1437): dequantise the listed rows (embedding gather).
+ * dev_row_ids may be NULL for rows 0..n_rows-1.  out dtype ZQ_F32 / ZQ_F16 / ZQ_BF16. */
+int zq_gather_rows(zq_ctx *ctx, const zq_weight *w, const uint32_t *dev_row_ids, size_t n_rows, void *dev_out, int out_dtype, zq_error *err);
+/* requantize_q4_k / encode_q4_k (src/weight/codec/ggml.rs:163-227) on the device: f32 [rows, cols] -> GGUF bytes.
+ * Q4_K follows the reference encoder bit for bit; Q4_0, Q8_0 and IQ4_NL (no encoder in the reference) use
+ * round-to-nearest encoders meant for generating synthetic inputs. */
+int zq_quantize(zq_ctx *ctx, uint32_t ggml_type, const float *dev_values, size_t rows, size_t cols, void *dev_gguf_bytes, size_t nbytes, zq_error *err);
+
+/* ---- linear: gguf_kq_matmul_f16 (src/kernel/cuda/linear.rs:1440-1584) behind Backend::linear / linear_add
+ * (src/backend/mod.rs:389, 417).  m <= 16 runs the decode GEMV, larger m the prefill GEMM.  `dev_residual`
+ * (same shape and dtype as y) may be NULL; when given, y = W x + residual (matvec_residual,
+ * src/kernel/cpu/ggml_quant.rs:224-233). ---- */
+int zq_linear(zq_ctx *ctx, const zq_weight *w, const void *dev_x, int x_dtype, size_t m, void *dev_y, int y_dtype, const void *dev_residual, zq_error *err);
+/* Backend::dual_linear / triple_linear (src/backend/mod.rs:444-451): up to 3 weights share one input. */
+int zq_linear_multi(zq_ctx *ctx, const zq_weight *const *w, size_t n_weights, const void *dev_x, int x_dtype, size_t m, void *const *dev_y, int y_dtype, zq_error *err);
+/* gated_linear_q4_k_silu_f16 / gated_linear_q4_0_silu_f16 (src/kernel/cuda/linear.rs:1683, 1916) behind
+ * Backend::gated_linear (src/backend/mod.rs:467): y = silu(gate x) * (up x). */
+int zq_gated_silu(zq_ctx *ctx, const zq_weight *gate, const zq_weight *up, const void *dev_x, int x_dtype, size_t m, void *dev_y, int y_dtype, zq_error *err);
+/* Backend::gated_mlp / gated_mlp_add_residual (src/backend/mod.rs:474, 483): down(silu(gate x) * up x) (+ residual). */
+int zq_gated_mlp(zq_ctx *ctx, const zq_weight *gate, const zq_weight *up, const zq_weight *down, const void *dev_x, int x_dtype, size_t m, void *dev_y, int y_dtype, const void *dev_residual, zq_error *err);
+
+/* Host-buffer form of zq_linear: copies x from host memory, runs, copies y back and waits.  This is what a
+ * backend that keeps activations on the host between operators calls (CpuTensor in, CpuTensor out). */
+int zq_linear_host(zq_ctx *ctx, const zq_weight *w, const void *host_x, int x_dtype, size_t m, void *host_y, int y_dtype, zq_error *err);
+
+/* ---- MoE: kernel::cuda::routing (src/kernel/cuda/routing.rs:167-210) and the expert entry points
+ * (src/kernel/cuda/linear.rs:1735-1819; src/backend/cuda/expert.rs:572-918). ---- */
+/* moe_route_softmax_topk_device_f32: logits = x router^T (+ bias), softmax top-k with ties to the lower expert id.
+ * router_f32 [num_experts, hidden] on the device; bias may be NULL.  Writes ids [m, top_k] and weights [m, top_k]. */
+int zq_moe_route_softmax_topk(zq_ctx *ctx, const void *dev_x, int x_dtype, size_t m, size_t hidden, const float *dev_router_f32, const float *dev_bias_f32, size_t num_experts, size_t top_k, float scaling_factor, int normalize_selected, uint32_t *dev_ids, float *dev_weights, zq_error *err);
+/* The resident expert table that replaces CudaMoeState's LRU/arena cache (src/backend/cuda/expert.rs:284-570)
+ * when every expert fits in HBM.  gate/up: [intermediate, hidden]; down: [hidden, intermediate].  The table
+ * borrows the weights; release them after zq_moe_experts_destroy. */
+int zq_moe_experts_create(zq_ctx *ctx, const zq_weight *const *gate, const zq_weight *const *up, const zq_weight *const *down, size_t num_experts, zq_moe_experts **out, zq_error *err);
+void zq_moe_experts_destroy(zq_moe_experts *experts);
+/* Routed experts (+ optional shared expert and residual): prefill_resident_routed_experts(_add) /
+ * decode_routed_experts (src/backend/mod.rs:1921-1960, 2012-2024).
+ * y[m, hidden] = residual + shared(x) + sum_k w_k * expert_k(x), contributions added in ascending expert id per
+ * token (src/backend/cpu/moe.rs:107-141).  shared_* may be NULL. */
+int zq_moe_forward(zq_ctx *ctx, const zq_moe_experts *experts, const zq_weight *shared_gate, const zq_weight *shared_up, const zq_weight *shared_down, const void *dev_x, int x_dtype, size_t m, const uint32_t *dev_ids, const float *dev_weights, size_t top_k, void *dev_y, int y_dtype, const void *dev_residual, zq_error *err);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ZQ_B200_H */

@@ -1,0 +1,158 @@
+"""GPU parity of the codec: dequantised values bit-exact against the CPU oracle (through the C ABI)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as orc
+from tests import helpers as H
+from tests.gpu_util import ctx, dev, host
+
+pytestmark = pytest.mark.gpu
+TYPES = [H.Q4_0, H.Q8_0, H.Q4_K, H.IQ4_NL]
+
+
+def _bits(a):
+    return np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+
+
+@pytest.mark.parametrize("tensor_type", TYPES)
+@pytest.mark.parametrize("rows,cols", [(3, 256), (37, 1024), (130, 512), (5, 4096)])
+def test_dequantize_is_bit_exact_on_random_bytes(tensor_type, rows, cols):
+    data = H.random_bytes_weight(tensor_type, rows, cols, seed=rows * 7 + cols)
+    w = ctx().prepare_weight(tensor_type, data, rows, cols)
+    got = host(ctx().dequantize(w))
+    want = orc.dequantize(tensor_type, data, rows * cols).reshape(rows, cols)
+    assert np.array_equal(_bits(got), _bits(want))
+
+
+@pytest.mark.parametrize("tensor_type", [H.Q4_0, H.Q8_0, H.IQ4_NL])
+@pytest.mark.parametrize("cols", [32, 1056, 2560])
+def test_dequantize_handles_rows_that_are_not_whole_units(tensor_type, cols):
+    """Column counts of the reference's Q8_0 test (src/kernel/cuda/linear.rs:2209-2230): 32-aligned, not 256-aligned."""
+    rows = 9
+    data = H.random_bytes_weight(tensor_type, rows, cols, seed=cols)
+    w = ctx().prepare_weight(tensor_type, data, rows, cols)
+    got = host(ctx().dequantize(w))
+    want = orc.dequantize(tensor_type, data, rows * cols).reshape(rows, cols)
+    assert np.array_equal(_bits(got), _bits(want))
+
+
+def test_q4_k_every_finite_f16_scale_pattern_decodes_bit_exactly():
+    """All 63 488 finite f16 patterns as d and dmin, crossed with every 6-bit code and nibble through random payloads."""
+    finite = np.array([b for b in range(65536) if (b & 0x7C00) != 0x7C00], dtype=np.uint16)
+    rng = np.random.default_rng(1)
+    blocks = finite.size
+    data = rng.integers(0, 256, size=(blocks, 144), dtype=np.uint8)
+    data[:, 0:2] = finite.view(np.uint8).reshape(-1, 2)
+    data[:, 2:4] = rng.permutation(finite).view(np.uint8).reshape(-1, 2)
+    rows, cols = blocks // 8, 2048
+    data = data[: rows * 8].reshape(-1)
+    w = ctx().prepare_weight(H.Q4_K, data, rows, cols)
+    got = host(ctx().dequantize(w))
+    want = orc.dequantize(H.Q4_K, data, rows * cols).reshape(rows, cols)
+    assert np.array_equal(_bits(got), _bits(want))
+
+
+@pytest.mark.parametrize("tensor_type", TYPES)
+def test_f16_edge_scales(tensor_type):
+    """Zero, smallest subnormal, subnormal edge, non-powers of two and a negative scale (src/kernel/rocm/hip/linear/gguf.rs:869)."""
+    e, b = orc.BLOCK[tensor_type]
+    rng = np.random.default_rng(2)
+    n = len(H.F16_EDGE_SCALES)
+    per_row = 256 // e
+    data = rng.integers(0, 256, size=(n * per_row, b), dtype=np.uint8)
+    for i, bits in enumerate(H.F16_EDGE_SCALES):
+        for j in range(per_row):
+            data[i * per_row + j, 0:2] = np.frombuffer(np.uint16(bits).tobytes(), dtype=np.uint8)
+            if tensor_type == H.Q4_K:
+                data[i * per_row + j, 2:4] = np.frombuffer(np.uint16(H.F16_EDGE_SCALES[(i + 3) % n]).tobytes(), dtype=np.uint8)
+    data = data.reshape(-1)
+    w = ctx().prepare_weight(tensor_type, data, n, 256)
+    got = host(ctx().dequantize(w))
+    want = orc.dequantize(tensor_type, data, n * 256).reshape(n, 256)
+    assert np.array_equal(_bits(got), _bits(want))
+
+
+def test_reference_known_answers_through_the_device_path():
+    """src/weight/codec/ggml.rs:513-537, 593-597 decoded by the CUDA kernels."""
+    block = np.zeros((8, 18), dtype=np.uint8)
+    block[:, :2] = np.frombuffer(H.f16_bytes(0.5), dtype=np.uint8)
+    block[0, 2] = 0x0F
+    block[0, 3] = 0x98
+    out = host(ctx().dequantize(ctx().prepare_weight(H.IQ4_NL, block.reshape(-1), 1, 256)))[0]
+    assert out[0] == 0.5 * 113.0 and out[16] == 0.5 * -127.0 and out[1] == 0.5 and out[17] == 0.5 * 13.0
+    q8 = np.zeros((8, 34), dtype=np.uint8)
+    q8[0, :2] = [0x00, 0x40]
+    q8[0, 2] = np.int8(-3).view(np.uint8)
+    q8[0, 3] = 4
+    out = host(ctx().dequantize(ctx().prepare_weight(H.Q8_0, q8.reshape(-1), 1, 256)))[0]
+    assert list(out[:2]) == [-6.0, 8.0]
+    q4 = np.zeros(144, dtype=np.uint8)
+    q4[:2] = [0x00, 0x3C]
+    q4[4] = 1
+    q4[16] = 2
+    out = host(ctx().dequantize(ctx().prepare_weight(H.Q4_K, q4, 1, 256)))[0]
+    assert out[0] == 2.0
+
+
+@pytest.mark.parametrize("tensor_type", [H.Q8_0, H.IQ4_NL, H.Q4_K])
+def test_gather_rows_equals_f16_of_dequant(tensor_type):
+    """src/kernel/cuda/linear.rs:2156-2173: gathered rows == f16(dequant) exactly."""
+    rows, cols = 50, 512
+    data = H.random_weight(tensor_type, rows, cols, seed=5)
+    w = ctx().prepare_weight(tensor_type, data, rows, cols)
+    ids = np.array([49, 0, 7, 7, 23], dtype=np.int32)
+    got = ctx().gather_rows(w, torch.from_numpy(ids), dtype=torch.float16)
+    ctx().sync()
+    want = orc.dequantize(tensor_type, data, rows * cols).reshape(rows, cols)[ids].astype(np.float16)
+    assert np.array_equal(got.cpu().numpy().view(np.uint16), want.view(np.uint16))
+
+
+def test_gather_rows_reports_bad_row_ids_without_faulting():
+    from zllm_b200 import ffi
+
+    rows, cols = 4, 256
+    w = ctx().prepare_weight(H.Q8_0, H.random_weight(H.Q8_0, rows, cols, seed=6), rows, cols)
+    ctx().gather_rows(w, torch.tensor([1, 99], dtype=torch.int32), dtype=torch.float32)
+    with pytest.raises(ffi.ZqFailure):
+        ctx().sync()
+    ctx().sync()  # the status word is cleared once reported
+
+
+def test_quantize_q4_k_matches_reference_encoder_bit_for_bit():
+    """encode_q4_k (src/weight/codec/ggml.rs:188-227) on the device against the oracle restatement."""
+    rng = np.random.default_rng(7)
+    v = (rng.standard_normal((24, 1024)) * 0.02).astype(np.float32)
+    v[0, :256] = 0.0            # all-zero block: d == dmin == 0 branch
+    v[1, :32] = np.abs(v[1, :32])  # all-positive group: min clamps to 0
+    got = ctx().quantize(H.Q4_K, dev(v))
+    ctx().sync()
+    want = orc.encode_q4_k(v)
+    assert np.array_equal(got.cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("tensor_type", [H.Q8_0, H.Q4_0, H.IQ4_NL])
+def test_block32_encoders_match_the_test_generators(tensor_type):
+    rng = np.random.default_rng(8)
+    v = (rng.standard_normal((16, 512)) * 0.02).astype(np.float32)
+    got = ctx().quantize(tensor_type, dev(v))
+    ctx().sync()
+    got = got.cpu().numpy()
+    want = H.quantize(tensor_type, v)
+    back_got = orc.dequantize(tensor_type, got, v.size)
+    back_want = orc.dequantize(tensor_type, want, v.size)
+    # same algorithm; allow rare ties to resolve differently, but the reconstruction must be as good
+    assert np.mean(got != want) < 1e-3
+    assert abs(np.abs(back_got - v.ravel()).max() - np.abs(back_want - v.ravel()).max()) < 1e-4
+
+
+def test_prepare_weight_rejects_wrong_sizes():
+    """Byte-count and alignment mismatches are errors (src/kernel/cuda/linear.rs:1441-1444)."""
+    from zllm_b200 import ffi
+
+    with pytest.raises(ffi.ZqFailure):
+        ctx().prepare_weight(H.Q4_K, np.zeros(143, dtype=np.uint8), 1, 256)
+    with pytest.raises(ffi.ZqFailure):
+        ctx().prepare_weight(H.Q4_K, np.zeros(144, dtype=np.uint8), 1, 255)
+    with pytest.raises(ffi.ZqFailure):
+        ctx().prepare_weight(13, np.zeros(176, dtype=np.uint8), 1, 256)

@@ -1,0 +1,208 @@
+"""Host-side mirror of the reference's operator surface for the GGUF linear path, over the C ABI.
+
+Names and argument meaning follow the ``Backend`` trait family of the reference (src/backend/mod.rs):
+``prepare_weight`` (:333), ``linear`` (:389), ``linear_add`` (:417), ``dual_linear`` / ``triple_linear``
+(:444-451), ``gated_linear`` (:467), ``gated_mlp`` / ``gated_mlp_add_residual`` (:474, :483), and the MoE
+entry points (:1627-2025).  torch is used only for device memory and streams; every operator is a call into
+``libzq_b200.so``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence
+
+import torch
+
+from . import ffi
+
+_DTYPES = {torch.float32: ffi.F32, torch.float16: ffi.F16, torch.bfloat16: ffi.BF16}
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise TypeError(f"unsupported activation dtype {t.dtype}") from None
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return C.c_void_p(t.data_ptr()) if t is not None else None
+
+
+class Weight:
+    """Resident packed weight (``CudaWeight`` / ``CudaGgufPacked``, src/backend/cuda/resident.rs:82-107)."""
+
+    def __init__(self, ctx: "B200Context", handle: C.c_void_p):
+        self.ctx = ctx
+        self.handle = handle
+
+    @property
+    def rows(self) -> int:
+        return ffi.load().zq_weight_rows(self.handle)
+
+    @property
+    def cols(self) -> int:
+        return ffi.load().zq_weight_cols(self.handle)
+
+    @property
+    def tensor_type(self) -> int:
+        return ffi.load().zq_weight_type(self.handle)
+
+    @property
+    def gguf_bytes(self) -> int:
+        return ffi.load().zq_weight_gguf_bytes(self.handle)
+
+    def release(self):
+        if self.handle:
+            ffi.load().zq_weight_release(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.release()
+        except Exception:
+            pass
+
+
+class B200Context:
+    """One device, one stream (``CudaContext``, src/backend/cuda/context.rs:248-276)."""
+
+    def __init__(self, device: int = 0, use_torch_stream: bool = True):
+        self.lib = ffi.load()
+        handle = C.c_void_p()
+        ffi.call("zq_ctx_create", device, C.byref(handle))
+        self.handle = handle
+        self.device = torch.device("cuda", device)
+        if use_torch_stream:
+            self.set_stream(torch.cuda.current_stream(self.device).cuda_stream)
+
+    # ---- context
+    def set_stream(self, cuda_stream: int):
+        ffi.call("zq_ctx_set_stream", self.handle, C.c_void_p(cuda_stream))
+
+    def sync(self):
+        ffi.call("zq_ctx_sync", self.handle)
+
+    @property
+    def sm_count(self) -> int:
+        return self.lib.zq_ctx_sm_count(self.handle)
+
+    @property
+    def launch_count(self) -> int:
+        return int(self.lib.zq_ctx_launch_count(self.handle))
+
+    def close(self):
+        if self.handle:
+            self.lib.zq_ctx_destroy(self.handle)
+            self.handle = None
+
+    # ---- weights
+    def prepare_weight(self, tensor_type: int, data, rows: int, cols: int) -> Weight:
+        """``prepare_weight(LinearWeight::gguf)``: ``data`` is GGUF-layout bytes (bytes, numpy uint8 or a uint8 tensor)."""
+        out = C.c_void_p()
+        if isinstance(data, torch.Tensor) and data.is_cuda:
+            data = data.contiguous()
+            ffi.call("zq_weight_prepare_device", self.handle, tensor_type, _ptr(data), data.numel(), rows, cols, C.byref(out))
+            self.sync()
+        else:
+            if isinstance(data, torch.Tensor):
+                data = data.contiguous().numpy()
+            buf = memoryview(data).cast("B")
+            arr = (C.c_uint8 * len(buf)).from_buffer_copy(buf) if buf.readonly else (C.c_uint8 * len(buf)).from_buffer(buf)
+            ffi.call("zq_weight_prepare", self.handle, tensor_type, arr, len(buf), rows, cols, C.byref(out))
+        return Weight(self, out)
+
+    def quantize(self, tensor_type: int, values: torch.Tensor) -> torch.Tensor:
+        """f32 ``[rows, cols]`` on the device -> GGUF-layout bytes (uint8 tensor)."""
+        values = values.contiguous().float()
+        rows, cols = values.shape
+        e, b = ffi.BLOCK[tensor_type]
+        if cols % e:
+            raise ffi.ZqFailure(1, f"columns {cols} not aligned to block {e}")
+        out = torch.empty(rows * (cols // e) * b, dtype=torch.uint8, device=values.device)
+        ffi.call("zq_quantize", self.handle, tensor_type, _ptr(values), rows, cols, _ptr(out), out.numel())
+        return out
+
+    def dequantize(self, w: Weight) -> torch.Tensor:
+        out = torch.empty((w.rows, w.cols), dtype=torch.float32, device=self.device)
+        ffi.call("zq_dequantize_f32", self.handle, w.handle, _ptr(out))
+        return out
+
+    def gather_rows(self, w: Weight, row_ids: Optional[torch.Tensor], n_rows: Optional[int] = None, dtype=torch.float16) -> torch.Tensor:
+        n = int(row_ids.numel()) if row_ids is not None else int(n_rows)
+        if row_ids is not None:
+            row_ids = row_ids.to(device=self.device, dtype=torch.int32).contiguous()
+        out = torch.empty((n, w.cols), dtype=dtype, device=self.device)
+        ffi.call("zq_gather_rows", self.handle, w.handle, _ptr(row_ids), n, _ptr(out), _DTYPES[dtype])
+        return out
+
+    # ---- linear family
+    def _rows(self, x: torch.Tensor, cols: int) -> int:
+        if x.dim() == 1:
+            x = x.unsqueeze(0)
+        if x.shape[-1] != cols:
+            raise ffi.ZqFailure(1, f"linear input cols={x.shape[-1]}, weight cols={cols}")
+        return x.numel() // cols
+
+    def linear(self, x: torch.Tensor, w: Weight, out_dtype=None, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        x = x.contiguous()
+        m = self._rows(x, w.cols)
+        out_dtype = out_dtype or x.dtype
+        y = torch.empty((m, w.rows), dtype=out_dtype, device=x.device)
+        if residual is not None:
+            residual = residual.contiguous()
+            if residual.numel() != y.numel() or residual.dtype != out_dtype:
+                raise ffi.ZqFailure(1, f"residual shape/dtype mismatch: {tuple(residual.shape)} {residual.dtype} vs {tuple(y.shape)} {out_dtype}")
+        ffi.call("zq_linear", self.handle, w.handle, _ptr(x), _dt(x), m, _ptr(y), _DTYPES[out_dtype], _ptr(residual))
+        return y
+
+    def linear_add(self, x: torch.Tensor, w: Weight, residual: torch.Tensor, out_dtype=None) -> torch.Tensor:
+        return self.linear(x, w, out_dtype=out_dtype or residual.dtype, residual=residual)
+
+    def linear_multi(self, x: torch.Tensor, weights: Sequence[Weight], out_dtype=None):
+        x = x.contiguous()
+        m = self._rows(x, weights[0].cols)
+        out_dtype = out_dtype or x.dtype
+        ys = [torch.empty((m, w.rows), dtype=out_dtype, device=x.device) for w in weights]
+        wa = (C.c_void_p * len(weights))(*[w.handle for w in weights])
+        ya = (C.c_void_p * len(weights))(*[y.data_ptr() for y in ys])
+        ffi.call("zq_linear_multi", self.handle, wa, len(weights), _ptr(x), _dt(x), m, ya, _DTYPES[out_dtype])
+        return ys
+
+    def dual_linear(self, x, first: Weight, second: Weight, out_dtype=None):
+        a, b = self.linear_multi(x, [first, second], out_dtype)
+        return a, b
+
+    def triple_linear(self, x, first: Weight, second: Weight, third: Weight, out_dtype=None):
+        a, b, c = self.linear_multi(x, [first, second, third], out_dtype)
+        return a, b, c
+
+    def gated_linear(self, x: torch.Tensor, gate: Weight, up: Weight, out_dtype=None) -> torch.Tensor:
+        x = x.contiguous()
+        m = self._rows(x, gate.cols)
+        out_dtype = out_dtype or x.dtype
+        y = torch.empty((m, gate.rows), dtype=out_dtype, device=x.device)
+        ffi.call("zq_gated_silu", self.handle, gate.handle, up.handle, _ptr(x), _dt(x), m, _ptr(y), _DTYPES[out_dtype])
+        return y
+
+    def gated_mlp(self, x: torch.Tensor, gate: Weight, up: Weight, down: Weight, out_dtype=None, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        x = x.contiguous()
+        m = self._rows(x, gate.cols)
+        out_dtype = out_dtype or x.dtype
+        y = torch.empty((m, down.rows), dtype=out_dtype, device=x.device)
+        if residual is not None:
+            residual = residual.contiguous()
+        ffi.call("zq_gated_mlp", self.handle, gate.handle, up.handle, down.handle, _ptr(x), _dt(x), m, _ptr(y), _DTYPES[out_dtype], _ptr(residual))
+        return y
+
+    def gated_mlp_add_residual(self, x, gate, up, down, residual, out_dtype=None):
+        return self.gated_mlp(x, gate, up, down, out_dtype=out_dtype or residual.dtype, residual=residual)
+
+    def linear_host(self, x_host, w: Weight, y_host):
+        """Host-buffer linear: numpy arrays in and out, copies inside the call."""
+        import numpy as np
+
+        dt = {np.dtype(np.float32): ffi.F32, np.dtype(np.float16): ffi.F16}
+        m = x_host.size // w.cols
+        ffi.call("zq_linear_host", self.handle, w.handle, C.c_void_p(x_host.ctypes.data), dt[x_host.dtype], m, C.c_void_p(y_host.ctypes.data), dt[y_host.dtype])
+        return y_host

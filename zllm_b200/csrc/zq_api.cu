@@ -1,0 +1,343 @@
+// C-ABI entry points, context and resident-weight management of the zq_b200 library.
+#include "zq_common.cuh"
+
+namespace zq {
+
+int set_error(zq_error *err, int code, const char *fmt, ...) {
+    if (err) {
+        va_list args;
+        va_start(args, fmt);
+        vsnprintf(err->message, sizeof(err->message), fmt, args);
+        va_end(args);
+    }
+    return code;
+}
+
+// cuTensorMapEncodeTiled is fetched through the runtime so that the library does not link libcuda and can be
+// loaded (symbols inspected, argument checks exercised) on a machine without a driver.
+EncodeTiledFn get_encode_tiled(zq_error *err) {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess) fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    });
+    if (!fn) set_error(err, ZQ_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the CUDA driver");
+    return fn;
+}
+
+// Tensor map over the resident bytes of a weight seen as u32 [rows, row_pitch/4]; OOB reads give zeros.
+int make_weight_map(const zq_weight *w, int box_words, int box_rows, CUtensorMap *out, zq_error *err) {
+    EncodeTiledFn encode = get_encode_tiled(err);
+    if (!encode) return ZQ_ERR_CUDA;
+    cuuint64_t dims[2] = {(cuuint64_t)(w->row_pitch / 4), (cuuint64_t)w->rows};
+    cuuint64_t strides[1] = {(cuuint64_t)w->row_pitch};
+    cuuint32_t box[2] = {(cuuint32_t)box_words, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, w->data, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(err, ZQ_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d (rows=%zu pitch=%zu box=%dx%d)", (int)r, w->rows, w->row_pitch, box_words, box_rows);
+    return ZQ_OK;
+}
+
+int ensure_workspace(zq_ctx *ctx, size_t bytes, zq_error *err) {
+    if (bytes <= ctx->workspace_bytes) return ZQ_OK;
+    // growing is rare (first call at a new size); wait for queued work that may still read the old buffer
+    ZQ_CUDA_CHECK(cudaStreamSynchronize(ctx->stream), err);
+    if (ctx->workspace) cudaFree(ctx->workspace);
+    ctx->workspace = nullptr;
+    ctx->workspace_bytes = 0;
+    size_t rounded = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+    ZQ_CUDA_CHECK(cudaMalloc(&ctx->workspace, rounded), err);
+    ctx->workspace_bytes = rounded;
+    return ZQ_OK;
+}
+
+int ensure_scratch_mid(zq_ctx *ctx, size_t bytes, zq_error *err) {
+    if (bytes <= ctx->mid_bytes) return ZQ_OK;
+    ZQ_CUDA_CHECK(cudaStreamSynchronize(ctx->stream), err);
+    if (ctx->mid) cudaFree(ctx->mid);
+    ctx->mid = nullptr;
+    ctx->mid_bytes = 0;
+    size_t rounded = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+    ZQ_CUDA_CHECK(cudaMalloc(&ctx->mid, rounded), err);
+    ctx->mid_bytes = rounded;
+    return ZQ_OK;
+}
+
+static int check_dtype(int dtype, const char *what, zq_error *err) {
+    if (dtype != ZQ_F32 && dtype != ZQ_F16 && dtype != ZQ_BF16) return set_error(err, ZQ_ERR_ARG, "%s: unknown dtype %d", what, dtype);
+    return ZQ_OK;
+}
+
+static int prepare_common(zq_ctx *ctx, uint32_t type, size_t nbytes, size_t rows, size_t cols, zq_weight **out, zq_error *err) {
+    if (!ctx || !out) return set_error(err, ZQ_ERR_ARG, "weight prepare: null context or output");
+    FormatInfo f = format_info(type);
+    if (!f.ggml_type) return set_error(err, ZQ_ERR_UNSUPPORTED, "GGUF tensor type %u is not supported (supported: 2, 8, 12, 20)", type);
+    if (rows == 0 || cols == 0 || cols % f.block_elems) return set_error(err, ZQ_ERR_SHAPE, "GGUF type %u weight [%zu, %zu]: columns must be a positive multiple of %d", type, rows, cols, f.block_elems);
+    size_t expected = rows * (cols / f.block_elems) * f.block_bytes;
+    if (nbytes != expected) return set_error(err, ZQ_ERR_SHAPE, "GGUF type %u weight [%zu, %zu]: %zu bytes given, %zu expected", type, rows, cols, nbytes, expected);
+    if (rows > (size_t)INT32_MAX || cols > (size_t)INT32_MAX) return set_error(err, ZQ_ERR_SHAPE, "weight [%zu, %zu] is too large", rows, cols);
+    zq_weight *w = new zq_weight();
+    w->ctx = ctx;
+    w->type = type;
+    w->rows = rows;
+    w->cols = cols;
+    w->units_per_row = (cols + kUnitWeights - 1) / kUnitWeights;
+    w->row_pitch = w->units_per_row * f.unit_bytes;
+    w->gguf_bytes = nbytes;
+    *out = w;
+    return ZQ_OK;
+}
+
+static int finish_prepare(zq_ctx *ctx, zq_weight *w, zq_error *err) {
+    FormatInfo f = format_info(w->type);
+    int rc = make_weight_map(w, 2 * f.unit_bytes / 4, 128, &w->gemv_map, err);
+    if (!rc) rc = make_weight_map(w, 2 * f.unit_bytes / 4, 64, &w->gemv_map_half, err);
+    (void)ctx;
+    return rc;
+}
+
+}  // namespace zq
+
+using namespace zq;
+
+extern "C" {
+
+int zq_ctx_create(int device, zq_ctx **out, zq_error *err) {
+    if (!out) return set_error(err, ZQ_ERR_ARG, "zq_ctx_create: null output");
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) return set_error(err, ZQ_ERR_CUDA, "no CUDA device is available (%s); this library has no CPU fallback", cudaGetErrorString(e));
+    if (device < 0 || device >= count) return set_error(err, ZQ_ERR_ARG, "device %d out of range (0..%d)", device, count - 1);
+    ZQ_CUDA_CHECK(cudaSetDevice(device), err);
+    cudaDeviceProp prop;
+    ZQ_CUDA_CHECK(cudaGetDeviceProperties(&prop, device), err);
+    if (prop.major != 10) return set_error(err, ZQ_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major, prop.minor);
+    zq_ctx *ctx = new zq_ctx();
+    ctx->device = device;
+    ctx->sm_count = prop.multiProcessorCount;
+    ZQ_CUDA_CHECK(cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking), err);
+    ctx->stream = ctx->own_stream;
+    ctx->gemv_partials_floats = (size_t)ctx->sm_count * 2 * 128 * 8;
+    ZQ_CUDA_CHECK(cudaMalloc(&ctx->gemv_partials, ctx->gemv_partials_floats * sizeof(float)), err);
+    ctx->gemv_counters_n = 1 << 16;
+    ZQ_CUDA_CHECK(cudaMalloc(&ctx->gemv_counters, ctx->gemv_counters_n * sizeof(uint32_t)), err);
+    ZQ_CUDA_CHECK(cudaMemset(ctx->gemv_counters, 0, ctx->gemv_counters_n * sizeof(uint32_t)), err);
+    ZQ_CUDA_CHECK(cudaHostAlloc(reinterpret_cast<void **>(&ctx->status_host), sizeof(uint32_t), cudaHostAllocMapped), err);
+    *ctx->status_host = 0;
+    ZQ_CUDA_CHECK(cudaHostGetDevicePointer(reinterpret_cast<void **>(&ctx->status_dev), ctx->status_host, 0), err);
+    ZQ_CUDA_CHECK(cudaDeviceSynchronize(), err);
+    *out = ctx;
+    return ZQ_OK;
+}
+
+void zq_ctx_destroy(zq_ctx *ctx) {
+    if (!ctx) return;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    if (ctx->gemv_partials) cudaFree(ctx->gemv_partials);
+    if (ctx->gemv_counters) cudaFree(ctx->gemv_counters);
+    if (ctx->workspace) cudaFree(ctx->workspace);
+    if (ctx->mid) cudaFree(ctx->mid);
+    if (ctx->status_host) cudaFreeHost(ctx->status_host);
+    if (ctx->pinned) cudaFreeHost(ctx->pinned);
+    if (ctx->host_io_dev) cudaFree(ctx->host_io_dev);
+    if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
+    delete ctx;
+}
+
+int zq_ctx_set_stream(zq_ctx *ctx, void *cuda_stream, zq_error *err) {
+    if (!ctx) return set_error(err, ZQ_ERR_ARG, "zq_ctx_set_stream: null context");
+    ctx->stream = cuda_stream ? reinterpret_cast<cudaStream_t>(cuda_stream) : ctx->own_stream;
+    return ZQ_OK;
+}
+
+int zq_ctx_sync(zq_ctx *ctx, zq_error *err) {
+    if (!ctx) return set_error(err, ZQ_ERR_ARG, "zq_ctx_sync: null context");
+    ZQ_CUDA_CHECK(cudaStreamSynchronize(ctx->stream), err);
+    uint32_t status = *reinterpret_cast<volatile uint32_t *>(ctx->status_host);
+    if (status != kStatusOk) {
+        *ctx->status_host = 0;
+        const char *what = status == kStatusTmaTimeout ? "a TMA copy did not complete within its wait limit"
+                         : status == kStatusMmaTimeout ? "a tensor-core pipeline wait ran out"
+                         : status == kStatusTmemAlloc ? "tensor memory could not be allocated"
+                         : status == kStatusBadIndex ? "an index argument was out of range (the access was skipped)" : "unknown device status";
+        return set_error(err, ZQ_ERR_DEVICE_STATUS, "device status %u: %s", status, what);
+    }
+    return ZQ_OK;
+}
+
+int zq_ctx_sm_count(const zq_ctx *ctx) { return ctx ? ctx->sm_count : 0; }
+uint64_t zq_ctx_launch_count(const zq_ctx *ctx) { return ctx ? ctx->launches.load() : 0; }
+
+int zq_weight_prepare_device(zq_ctx *ctx, uint32_t ggml_type, const void *dev_bytes, size_t nbytes, size_t rows, size_t cols, zq_weight **out, zq_error *err) {
+    if (!dev_bytes) return set_error(err, ZQ_ERR_ARG, "weight prepare: null bytes");
+    zq_weight *w = nullptr;
+    int rc = prepare_common(ctx, ggml_type, nbytes, rows, cols, &w, err);
+    if (rc) return rc;
+    size_t resident = w->rows * w->row_pitch;
+    cudaError_t e = cudaMalloc(reinterpret_cast<void **>(&w->data), resident);
+    if (e != cudaSuccess) {
+        delete w;
+        return set_error(err, ZQ_ERR_CUDA, "cudaMalloc of %zu resident bytes failed: %s", resident, cudaGetErrorString(e));
+    }
+    if (ggml_type == ZQ_Q4_K) {
+        e = cudaMemcpyAsync(w->data, dev_bytes, nbytes, cudaMemcpyDeviceToDevice, ctx->stream);
+        if (e != cudaSuccess) rc = set_error(err, ZQ_ERR_CUDA, "copy of packed weight failed: %s", cudaGetErrorString(e));
+    } else {
+        rc = launch_repack(ctx, ggml_type, reinterpret_cast<const uint8_t *>(dev_bytes), w->data, rows, cols, err);
+    }
+    if (!rc) rc = finish_prepare(ctx, w, err);
+    if (rc) {
+        cudaFree(w->data);
+        delete w;
+        return rc;
+    }
+    *out = w;
+    return ZQ_OK;
+}
+
+int zq_weight_prepare(zq_ctx *ctx, uint32_t ggml_type, const void *host_bytes, size_t nbytes, size_t rows, size_t cols, zq_weight **out, zq_error *err) {
+    if (!host_bytes) return set_error(err, ZQ_ERR_ARG, "weight prepare: null bytes");
+    zq_weight *probe = nullptr;
+    int rc = prepare_common(ctx, ggml_type, nbytes, rows, cols, &probe, err);  // validates before any allocation
+    if (rc) return rc;
+    delete probe;
+    void *staging = nullptr;
+    ZQ_CUDA_CHECK(cudaSetDevice(ctx->device), err);
+    ZQ_CUDA_CHECK(cudaMalloc(&staging, nbytes), err);
+    cudaError_t e = cudaMemcpyAsync(staging, host_bytes, nbytes, cudaMemcpyHostToDevice, ctx->stream);
+    if (e != cudaSuccess) {
+        cudaFree(staging);
+        return set_error(err, ZQ_ERR_CUDA, "upload of packed weight failed: %s", cudaGetErrorString(e));
+    }
+    rc = zq_weight_prepare_device(ctx, ggml_type, staging, nbytes, rows, cols, out, err);
+    cudaStreamSynchronize(ctx->stream);  // host bytes are only borrowed for the duration of this call
+    cudaFree(staging);
+    return rc;
+}
+
+void zq_weight_release(zq_weight *w) {
+    if (!w) return;
+    if (w->ctx) {
+        cudaSetDevice(w->ctx->device);
+        cudaStreamSynchronize(w->ctx->stream);
+    }
+    if (w->owns_data && w->data) cudaFree(w->data);
+    delete w;
+}
+
+size_t zq_weight_rows(const zq_weight *w) { return w ? w->rows : 0; }
+size_t zq_weight_cols(const zq_weight *w) { return w ? w->cols : 0; }
+uint32_t zq_weight_type(const zq_weight *w) { return w ? w->type : 0; }
+size_t zq_weight_gguf_bytes(const zq_weight *w) { return w ? w->gguf_bytes : 0; }
+
+int zq_dequantize_f32(zq_ctx *ctx, const zq_weight *w, float *dev_out, zq_error *err) {
+    if (!ctx || !w || !dev_out) return set_error(err, ZQ_ERR_ARG, "zq_dequantize_f32: null argument");
+    return launch_dequantize(ctx, w, nullptr, w->rows, dev_out, ZQ_F32, err);
+}
+
+int zq_gather_rows(zq_ctx *ctx, const zq_weight *w, const uint32_t *dev_row_ids, size_t n_rows, void *dev_out, int out_dtype, zq_error *err) {
+    if (!ctx || !w || !dev_out) return set_error(err, ZQ_ERR_ARG, "zq_gather_rows: null argument");
+    int rc = check_dtype(out_dtype, "zq_gather_rows", err);
+    if (rc) return rc;
+    if (!dev_row_ids && n_rows > w->rows) return set_error(err, ZQ_ERR_SHAPE, "zq_gather_rows: %zu rows requested from a weight with %zu rows", n_rows, w->rows);
+    return launch_dequantize(ctx, w, dev_row_ids, n_rows, dev_out, out_dtype, err);
+}
+
+int zq_quantize(zq_ctx *ctx, uint32_t ggml_type, const float *dev_values, size_t rows, size_t cols, void *dev_gguf_bytes, size_t nbytes, zq_error *err) {
+    if (!ctx || !dev_values || !dev_gguf_bytes) return set_error(err, ZQ_ERR_ARG, "zq_quantize: null argument");
+    FormatInfo f = format_info(ggml_type);
+    if (!f.ggml_type) return set_error(err, ZQ_ERR_UNSUPPORTED, "zq_quantize: GGUF tensor type %u is not supported", ggml_type);
+    if (cols % f.block_elems) return set_error(err, ZQ_ERR_SHAPE, "zq_quantize: columns %zu not aligned to block %d", cols, f.block_elems);
+    size_t expected = rows * (cols / f.block_elems) * f.block_bytes;
+    if (nbytes != expected) return set_error(err, ZQ_ERR_SHAPE, "zq_quantize: output holds %zu bytes, %zu expected", nbytes, expected);
+    return launch_quantize(ctx, ggml_type, dev_values, rows, cols, dev_gguf_bytes, err);
+}
+
+static int check_linear(zq_ctx *ctx, const zq_weight *w, const void *x, int x_dtype, size_t m, void *y, int y_dtype, zq_error *err) {
+    if (!ctx || !w || !x || !y) return set_error(err, ZQ_ERR_ARG, "linear: null argument");
+    if (w->ctx != ctx) return set_error(err, ZQ_ERR_ARG, "linear: weight belongs to another context");
+    int rc = check_dtype(x_dtype, "linear input", err);
+    if (!rc) rc = check_dtype(y_dtype, "linear output", err);
+    if (rc) return rc;
+    if (m == 0) return set_error(err, ZQ_ERR_SHAPE, "linear: input has no rows");
+    if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(y) & 15)) return set_error(err, ZQ_ERR_ARG, "linear: device buffers must be 16-byte aligned");
+    return ZQ_OK;
+}
+
+int zq_linear(zq_ctx *ctx, const zq_weight *w, const void *dev_x, int x_dtype, size_t m, void *dev_y, int y_dtype, const void *dev_residual, zq_error *err) {
+    int rc = check_linear(ctx, w, dev_x, x_dtype, m, dev_y, y_dtype, err);
+    if (rc) return rc;
+    if (m <= 16) return launch_gemv(ctx, w, nullptr, dev_x, x_dtype, m, dev_y, y_dtype, dev_residual, err);
+    return launch_gemm(ctx, w, nullptr, dev_x, x_dtype, m, dev_y, y_dtype, dev_residual, err);
+}
+
+int zq_linear_multi(zq_ctx *ctx, const zq_weight *const *w, size_t n_weights, const void *dev_x, int x_dtype, size_t m, void *const *dev_y, int y_dtype, zq_error *err) {
+    if (!w || !dev_y || n_weights == 0 || n_weights > 3) return set_error(err, ZQ_ERR_ARG, "zq_linear_multi: 1 to 3 weights expected");
+    for (size_t i = 0; i < n_weights; ++i) {
+        if (!w[i] || w[i]->cols != w[0]->cols) return set_error(err, ZQ_ERR_SHAPE, "zq_linear_multi: weights must share the input width");
+    }
+    for (size_t i = 0; i < n_weights; ++i) {
+        int rc = zq_linear(ctx, w[i], dev_x, x_dtype, m, dev_y[i], y_dtype, nullptr, err);
+        if (rc) return rc;
+    }
+    return ZQ_OK;
+}
+
+int zq_gated_silu(zq_ctx *ctx, const zq_weight *gate, const zq_weight *up, const void *dev_x, int x_dtype, size_t m, void *dev_y, int y_dtype, zq_error *err) {
+    int rc = check_linear(ctx, gate, dev_x, x_dtype, m, dev_y, y_dtype, err);
+    if (rc) return rc;
+    if (!up || up->ctx != ctx) return set_error(err, ZQ_ERR_ARG, "gated linear: bad up weight");
+    if (gate->rows != up->rows || gate->cols != up->cols || gate->type != up->type) return set_error(err, ZQ_ERR_SHAPE, "gated linear: gate [%zu, %zu] type %u and up [%zu, %zu] type %u differ", gate->rows, gate->cols, gate->type, up->rows, up->cols, up->type);
+    if (m <= 16) return launch_gemv(ctx, gate, up, dev_x, x_dtype, m, dev_y, y_dtype, nullptr, err);
+    return launch_gemm(ctx, gate, up, dev_x, x_dtype, m, dev_y, y_dtype, nullptr, err);
+}
+
+int zq_gated_mlp(zq_ctx *ctx, const zq_weight *gate, const zq_weight *up, const zq_weight *down, const void *dev_x, int x_dtype, size_t m, void *dev_y, int y_dtype, const void *dev_residual, zq_error *err) {
+    if (!down || !gate) return set_error(err, ZQ_ERR_ARG, "gated mlp: null weight");
+    if (down->cols != gate->rows) return set_error(err, ZQ_ERR_SHAPE, "gated mlp: down expects %zu inputs, gate produces %zu", down->cols, gate->rows);
+    // the activated intermediate [m, I] lives in the context workspace as f32 (decode) or in the input dtype (prefill)
+    int mid_dtype = m <= 16 ? ZQ_F32 : (x_dtype == ZQ_F32 ? ZQ_F32 : x_dtype);
+    size_t mid_bytes = m * gate->rows * dtype_size(mid_dtype);
+    int rc = ensure_scratch_mid(ctx, mid_bytes, err);
+    if (rc) return rc;
+    rc = zq_gated_silu(ctx, gate, up, dev_x, x_dtype, m, ctx->mid, mid_dtype, err);
+    if (rc) return rc;
+    return zq_linear(ctx, down, ctx->mid, mid_dtype, m, dev_y, y_dtype, dev_residual, err);
+}
+
+int zq_linear_host(zq_ctx *ctx, const zq_weight *w, const void *host_x, int x_dtype, size_t m, void *host_y, int y_dtype, zq_error *err) {
+    if (!ctx || !w || !host_x || !host_y) return set_error(err, ZQ_ERR_ARG, "zq_linear_host: null argument");
+    int rc = check_dtype(x_dtype, "linear input", err);
+    if (!rc) rc = check_dtype(y_dtype, "linear output", err);
+    if (rc) return rc;
+    size_t xb = m * w->cols * dtype_size(x_dtype), yb = m * w->rows * dtype_size(y_dtype);
+    size_t xb_al = (xb + 255) & ~size_t(255);
+    if (ctx->host_io_bytes < xb_al + yb) {
+        ZQ_CUDA_CHECK(cudaStreamSynchronize(ctx->stream), err);
+        if (ctx->host_io_dev) cudaFree(ctx->host_io_dev);
+        if (ctx->pinned) cudaFreeHost(ctx->pinned);
+        ctx->host_io_dev = nullptr;
+        ctx->pinned = nullptr;
+        ctx->host_io_bytes = 0;
+        ZQ_CUDA_CHECK(cudaMalloc(&ctx->host_io_dev, xb_al + yb), err);
+        ZQ_CUDA_CHECK(cudaHostAlloc(&ctx->pinned, xb_al + yb, cudaHostAllocDefault), err);
+        ctx->host_io_bytes = xb_al + yb;
+    }
+    uint8_t *dx = reinterpret_cast<uint8_t *>(ctx->host_io_dev), *dy = dx + xb_al;
+    uint8_t *px = reinterpret_cast<uint8_t *>(ctx->pinned), *py = px + xb_al;
+    memcpy(px, host_x, xb);
+    ZQ_CUDA_CHECK(cudaMemcpyAsync(dx, px, xb, cudaMemcpyHostToDevice, ctx->stream), err);
+    rc = zq_linear(ctx, w, dx, x_dtype, m, dy, y_dtype, nullptr, err);
+    if (rc) return rc;
+    ZQ_CUDA_CHECK(cudaMemcpyAsync(py, dy, yb, cudaMemcpyDeviceToHost, ctx->stream), err);
+    rc = zq_ctx_sync(ctx, err);
+    if (rc) return rc;
+    memcpy(host_y, py, yb);
+    return ZQ_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,246 @@
+// Codec kernels: GGUF -> resident re-layout, bit-exact dequantisation (all rows or gathered rows), and the
+// device-side encoders.
+//
+// Reference behaviour restated here:
+//   decode formulas         src/weight/codec/ggml.rs:102-109 (Q4_0), 229-234 (Q8_0), 237-244 (IQ4_NL), 408-423 (Q4_K)
+//   dequantize              src/weight/codec/ggml.rs:146-160
+//   gathered rows to f16    src/kernel/cuda/linear.rs:1420-1437 (gguf_rows_f16)
+//   encode_q4_k             src/weight/codec/ggml.rs:188-227
+#include "zq_common.cuh"
+
+namespace zq {
+
+// One thread per resident byte: find the GGUF byte it comes from.  Padding blocks (beyond the row's last
+// GGUF block) are zero.
+__global__ void repack_kernel(uint32_t type, const uint8_t *__restrict__ gguf, uint8_t *__restrict__ resident, size_t rows, size_t blocks_per_row, size_t units_per_row, int unit_bytes, int block_bytes) {
+    size_t row_pitch = units_per_row * (size_t)unit_bytes;
+    size_t total = rows * row_pitch;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        size_t row = idx / row_pitch;
+        size_t in_row = idx % row_pitch;
+        size_t unit = in_row / unit_bytes;
+        int o = (int)(in_row % unit_bytes);
+        int block, src;
+        if (o < 16) {
+            block = o >> 1;
+            src = o & 1;
+        } else {
+            int u = (o - 16) >> 4, w = ((o - 16) & 15) >> 2, by = o & 3;
+            int t = u & 3, h = u >> 2;
+            if (type == ZQ_Q8_0) {
+                block = 2 * h + (w >> 1);
+                src = 2 + 4 * (4 * (w & 1) + t) + by;
+            } else {
+                block = 4 * h + w;
+                src = 2 + 4 * t + by;
+            }
+        }
+        size_t gblock = unit * 8 + block;
+        uint8_t v = 0;
+        if (gblock < blocks_per_row) v = gguf[(row * blocks_per_row + gblock) * block_bytes + src];
+        resident[idx] = v;
+    }
+}
+
+int launch_repack(zq_ctx *ctx, uint32_t type, const uint8_t *gguf, uint8_t *resident, size_t rows, size_t cols, zq_error *err) {
+    FormatInfo f = format_info(type);
+    size_t blocks_per_row = cols / f.block_elems;
+    size_t units_per_row = (cols + kUnitWeights - 1) / kUnitWeights;
+    size_t total = rows * units_per_row * f.unit_bytes;
+    if (total == 0) return ZQ_OK;
+    int threads = 256;
+    size_t blocks = (total + threads - 1) / threads;
+    if (blocks > 65535u * 16u) blocks = 65535u * 16u;
+    repack_kernel<<<(unsigned)blocks, threads, 0, ctx->stream>>>(type, gguf, resident, rows, blocks_per_row, units_per_row, f.unit_bytes, f.block_bytes);
+    ctx->launches++;
+    ZQ_CUDA_CHECK(cudaGetLastError(), err);
+    return ZQ_OK;
+}
+
+// Decode element `i` (0..255) of a resident unit.  Every product below is exactly representable in f32, so the
+// only rounding is the reference's final subtraction; __fmul_rn/__fsub_rn keep the compiler from contracting.
+__device__ __forceinline__ float decode_unit_element(uint32_t type, const uint8_t *unit, int i) {
+    uint8_t q = unit[unit_quant_offset(type, i)];
+    if (type == ZQ_Q4_K) {
+        const __half *hd = reinterpret_cast<const __half *>(unit);
+        float d = __half2float(hd[0]), dmin = __half2float(hd[1]);
+        const uint8_t *scales = unit + 4;
+        int g = i >> 5;
+        int sc, mn;
+        if (g < 4) {
+            sc = scales[g] & 0x3f;
+            mn = scales[g + 4] & 0x3f;
+        } else {
+            sc = (scales[g + 4] & 0x0f) | ((scales[g - 4] >> 6) << 4);
+            mn = (scales[g + 4] >> 4) | ((scales[g] >> 6) << 4);
+        }
+        int quant = (g & 1) ? (q >> 4) : (q & 0x0f);
+        return __fsub_rn(__fmul_rn(__fmul_rn(d, (float)sc), (float)quant), __fmul_rn(dmin, (float)mn));
+    }
+    int blk = i >> 5, e = i & 31;
+    float d = __half2float(reinterpret_cast<const __half *>(unit)[blk]);
+    if (type == ZQ_Q8_0) return __fmul_rn(d, (float)(int8_t)q);
+    int nib = (e >> 4) ? (q >> 4) : (q & 0x0f);
+    if (type == ZQ_Q4_0) return __fmul_rn((float)(nib - 8), d);
+    return __fmul_rn(d, (float)kIq4nlValues[nib]);
+}
+
+// One thread per 4 consecutive output elements.
+__global__ void dequantize_kernel(uint32_t type, const uint8_t *__restrict__ resident, size_t row_pitch, int unit_bytes, size_t total_rows, size_t cols, const uint32_t *__restrict__ row_ids, size_t n_rows,
+                                  void *__restrict__ out, int out_dtype, uint32_t *status) {
+    size_t quads_per_row = cols / 4;
+    size_t total = n_rows * quads_per_row;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        size_t orow = idx / quads_per_row;
+        size_t k0 = (idx % quads_per_row) * 4;
+        size_t srow = row_ids ? row_ids[orow] : orow;
+        if (srow >= total_rows) {  // bad row id: record and skip, never read out of bounds
+            atomicMax(status, (uint32_t)kStatusBadIndex);
+            continue;
+        }
+        const uint8_t *unit = resident + srow * row_pitch + (k0 / kUnitWeights) * unit_bytes;
+        int i0 = (int)(k0 % kUnitWeights);
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = decode_unit_element(type, unit, i0 + j);
+        size_t o = orow * cols + k0;
+        if (out_dtype == ZQ_F32) {
+            *reinterpret_cast<float4 *>(reinterpret_cast<float *>(out) + o) = make_float4(v[0], v[1], v[2], v[3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) store_from_f32(out, out_dtype, o + j, v[j]);
+        }
+    }
+}
+
+int launch_dequantize(zq_ctx *ctx, const zq_weight *w, const uint32_t *row_ids, size_t n_rows, void *out, int out_dtype, zq_error *err) {
+    size_t total = n_rows * (w->cols / 4);
+    if (total == 0) return ZQ_OK;
+    int threads = 256;
+    size_t blocks = (total + threads - 1) / threads;
+    if (blocks > (size_t)ctx->sm_count * 64) blocks = (size_t)ctx->sm_count * 64;
+    FormatInfo f = format_info(w->type);
+    dequantize_kernel<<<(unsigned)blocks, threads, 0, ctx->stream>>>(w->type, w->data, w->row_pitch, f.unit_bytes, w->rows, w->cols, row_ids, n_rows, out, out_dtype, ctx->status_dev);
+    ctx->launches++;
+    ZQ_CUDA_CHECK(cudaGetLastError(), err);
+    return ZQ_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Encoders (GGUF layout out).
+// ---------------------------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ float f16_round(float v) { return __half2float(__float2half_rn(v)); }
+__device__ __forceinline__ float clampf(float v, float lo, float hi) { return v < lo ? lo : (v > hi ? hi : v); }
+
+// encode_q4_k, one thread per super-block, same operation order as the reference (f32 throughout, f16 rounding
+// of d and dmin, round-half-away-from-zero codes).
+__global__ void quantize_q4_k_kernel(const float *__restrict__ values, uint8_t *__restrict__ out, size_t blocks) {
+    size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= blocks) return;
+    const float *v = values + b * 256;
+    uint8_t *block = out + b * 144;
+    float scales[8], minimums[8];
+    for (int g = 0; g < 8; ++g) {
+        float minimum = INFINITY, maximum = -INFINITY;
+        for (int i = 0; i < 32; ++i) {
+            float x = v[g * 32 + i];
+            minimum = fminf(minimum, x);
+            maximum = fmaxf(maximum, x);
+        }
+        minimums[g] = fmaxf(-minimum, 0.0f);
+        scales[g] = __fdiv_rn(fmaxf(__fadd_rn(maximum, minimums[g]), 0.0f), 15.0f);
+    }
+    float max_scale = 0.0f, max_min = 0.0f;
+    for (int g = 0; g < 8; ++g) {
+        max_scale = fmaxf(max_scale, scales[g]);
+        max_min = fmaxf(max_min, minimums[g]);
+    }
+    float d = f16_round(__fdiv_rn(max_scale, 63.0f));
+    float dmin = f16_round(__fdiv_rn(max_min, 63.0f));
+    for (int i = 0; i < 144; ++i) block[i] = 0;
+    __half dh = __float2half_rn(d), dmh = __float2half_rn(dmin);
+    uint16_t db = *reinterpret_cast<uint16_t *>(&dh), dmb = *reinterpret_cast<uint16_t *>(&dmh);
+    block[0] = (uint8_t)db; block[1] = (uint8_t)(db >> 8);
+    block[2] = (uint8_t)dmb; block[3] = (uint8_t)(dmb >> 8);
+    uint8_t sc[8], mc[8];
+    for (int g = 0; g < 8; ++g) {
+        sc[g] = d == 0.0f ? 0 : (uint8_t)clampf(roundf(__fdiv_rn(scales[g], d)), 0.0f, 63.0f);
+        mc[g] = dmin == 0.0f ? 0 : (uint8_t)clampf(roundf(__fdiv_rn(minimums[g], dmin)), 0.0f, 63.0f);
+    }
+    for (int g = 0; g < 4; ++g) {
+        block[4 + g] = (uint8_t)((sc[g] & 0x3f) | ((sc[g + 4] >> 4) << 6));
+        block[8 + g] = (uint8_t)((mc[g] & 0x3f) | ((mc[g + 4] >> 4) << 6));
+        block[12 + g] = (uint8_t)((sc[g + 4] & 0x0f) | ((mc[g + 4] & 0x0f) << 4));
+    }
+    for (int g = 0; g < 8; ++g) {
+        float scale = __fmul_rn(d, (float)sc[g]);
+        float minimum = __fmul_rn(dmin, (float)mc[g]);
+        for (int i = 0; i < 32; ++i) {
+            uint8_t quant = 0;
+            if (scale != 0.0f) quant = (uint8_t)clampf(roundf(__fdiv_rn(__fadd_rn(v[g * 32 + i], minimum), scale)), 0.0f, 15.0f);
+            int target = 16 + (g / 2) * 32 + i;
+            if ((g & 1) == 0) block[target] = quant;
+            else block[target] |= (uint8_t)(quant << 4);
+        }
+    }
+}
+
+// Round-to-nearest encoders for the 32-weight block types (synthetic-input generators; the reference has none).
+//   Q8_0:   d = f16(max|v| / 127), q = rint(v / d)
+//   Q4_0:   d = f16(v_at_max_abs / -8), code = nearest of -8..7 to v / d
+//   IQ4_NL: d = f16(v_at_max_abs / -127), code = nearest codebook entry to v / d
+__global__ void quantize_block32_kernel(uint32_t type, const float *__restrict__ values, uint8_t *__restrict__ out, size_t blocks) {
+    size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= blocks) return;
+    const float *v = values + b * 32;
+    float amax = 0.0f, smax = 0.0f;
+    for (int i = 0; i < 32; ++i) {
+        float a = fabsf(v[i]);
+        if (a > amax) { amax = a; smax = v[i]; }
+    }
+    if (type == ZQ_Q8_0) {
+        uint8_t *block = out + b * 34;
+        float d = f16_round(__fdiv_rn(amax, 127.0f));
+        float inv = d > 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+        __half dh = __float2half_rn(d);
+        uint16_t db = *reinterpret_cast<uint16_t *>(&dh);
+        block[0] = (uint8_t)db; block[1] = (uint8_t)(db >> 8);
+        for (int i = 0; i < 32; ++i) block[2 + i] = (uint8_t)(int8_t)clampf(rintf(__fmul_rn(v[i], inv)), -127.0f, 127.0f);
+        return;
+    }
+    uint8_t *block = out + b * 18;
+    float d = f16_round(__fdiv_rn(smax, type == ZQ_Q4_0 ? -8.0f : -127.0f));
+    float inv = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+    __half dh = __float2half_rn(d);
+    uint16_t db = *reinterpret_cast<uint16_t *>(&dh);
+    block[0] = (uint8_t)db; block[1] = (uint8_t)(db >> 8);
+    uint8_t codes[32];
+    for (int i = 0; i < 32; ++i) {
+        float s = __fmul_rn(v[i], inv);
+        int best = 0;
+        float best_err = INFINITY;
+        for (int c = 0; c < 16; ++c) {
+            float target = type == ZQ_Q4_0 ? (float)(c - 8) : (float)kIq4nlValues[c];
+            float e = fabsf(__fsub_rn(s, target));
+            if (e < best_err) { best_err = e; best = c; }
+        }
+        codes[i] = (uint8_t)best;
+    }
+    for (int i = 0; i < 16; ++i) block[2 + i] = (uint8_t)(codes[i] | (codes[i + 16] << 4));
+}
+
+int launch_quantize(zq_ctx *ctx, uint32_t type, const float *values, size_t rows, size_t cols, void *out, zq_error *err) {
+    FormatInfo f = format_info(type);
+    size_t blocks = rows * cols / f.block_elems;
+    if (blocks == 0) return ZQ_OK;
+    int threads = 128;
+    unsigned grid = (unsigned)((blocks + threads - 1) / threads);
+    if (type == ZQ_Q4_K) quantize_q4_k_kernel<<<grid, threads, 0, ctx->stream>>>(values, reinterpret_cast<uint8_t *>(out), blocks);
+    else quantize_block32_kernel<<<grid, threads, 0, ctx->stream>>>(type, values, reinterpret_cast<uint8_t *>(out), blocks);
+    ctx->launches++;
+    ZQ_CUDA_CHECK(cudaGetLastError(), err);
+    return ZQ_OK;
+}
+
+}  // namespace zq

@@ -1,0 +1,243 @@
+// Shared definitions for the zq_b200 CUDA library: resident weight layouts, PTX wrappers (mbarrier, TMA bulk
+// tensor copies, warp MMA), host-side context and error plumbing.  sm_100a only.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/zq_b200.h"
+
+namespace zq {
+
+// ---------------------------------------------------------------------------------------------------------------
+// Resident layouts.
+//
+// Q4_K keeps the GGUF layout: 144-byte super-blocks of 256 weights (d:f16, dmin:f16, scales[12], qs[128]).
+//
+// The 32-weight block formats (Q4_0, IQ4_NL: 18 B; Q8_0: 34 B) are only 2-byte aligned in GGUF.  They are
+// re-laid at prepare time, without adding bytes, into "units" of 8 blocks = 256 weights whose pieces are 16-byte
+// aligned, so that one unit has the same geometry as a Q4_K super-block:
+//   Q4_0 / IQ4_NL unit (144 B): d[8]:f16 | 8 pieces of 16 B.  Piece u = t + 4h (t = u%4, h = u/4) holds, for
+//       bb = 0..3, 32-bit word t of the 16 quant bytes of block 4h+bb.
+//   Q8_0 unit (272 B): d[8]:f16 | 16 pieces of 16 B.  Piece u = t + 4h (h = 0..3) holds, for j = 0..3, 32-bit
+//       word 4*(j%2)+t of the 32 quant bytes of block 2h + j/2.
+// Rows whose block count is not a multiple of 8 are padded with zero blocks (d = 0).  The interleave puts, in
+// each thread's 16-byte piece, exactly the words its warp-MMA fragment consumes (see zq_gemv.cu).
+// ---------------------------------------------------------------------------------------------------------------
+
+constexpr int kUnitWeights = 256;
+
+struct FormatInfo {
+    uint32_t ggml_type;
+    int block_elems;   // GGUF block size in weights
+    int block_bytes;   // GGUF block size in bytes
+    int unit_bytes;    // resident bytes per 256 weights
+};
+
+__host__ __device__ inline FormatInfo format_info(uint32_t t) {
+    switch (t) {
+    case ZQ_Q4_0: return {ZQ_Q4_0, 32, 18, 144};
+    case ZQ_IQ4_NL: return {ZQ_IQ4_NL, 32, 18, 144};
+    case ZQ_Q8_0: return {ZQ_Q8_0, 32, 34, 272};
+    case ZQ_Q4_K: return {ZQ_Q4_K, 256, 144, 144};
+    default: return {0, 0, 0, 0};
+    }
+}
+
+// Byte offset, inside a resident unit, of the quant byte that holds element `i` (0..255) of the unit.
+__host__ __device__ inline int unit_quant_offset(uint32_t type, int i) {
+    if (type == ZQ_Q4_K) {
+        int g = i >> 5, j = i & 31;
+        return 16 + (g >> 1) * 32 + j;
+    }
+    int blk = i >> 5, e = i & 31;
+    if (type == ZQ_Q8_0) {
+        int wv = e >> 2, eh = wv >> 2, t = wv & 3, s = 2 * blk + eh, h = s >> 2, j = s & 3;
+        return 16 + 16 * (t + 4 * h) + 4 * j + (e & 3);
+    }
+    int idx = e & 15, t = idx >> 2, h = blk >> 2, bb = blk & 3;  // Q4_0 / IQ4_NL: nibble = e >> 4
+    return 16 + 16 * (t + 4 * h) + 4 * bb + (idx & 3);
+}
+
+__device__ __constant__ const int8_t kIq4nlValues[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+
+// ---------------------------------------------------------------------------------------------------------------
+// Device status word: kernels never trap or spin forever.  A bounded wait that runs out records a code here
+// and the kernel returns; zq_ctx_sync reports it.
+// ---------------------------------------------------------------------------------------------------------------
+enum DeviceStatus : uint32_t { kStatusOk = 0, kStatusTmaTimeout = 1, kStatusMmaTimeout = 2, kStatusTmemAlloc = 3, kStatusBadIndex = 4 };
+
+// ---------------------------------------------------------------------------------------------------------------
+// PTX wrappers.
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: returns false when the barrier did not complete within `limit` polls (each poll may itself
+// block for a hardware-defined short time).  Callers record a status and leave.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, uint32_t limit = (1u << 22)) {
+    for (uint32_t i = 0; i < limit; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap *map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+// 2-D tiled bulk tensor load, global -> this CTA's shared memory, completion on an mbarrier.  No multicast.
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, uint64_t *bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(dst)),
+                 "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, uint64_t *bar, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(smem_u32(dst)),
+                 "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+                 : "memory");
+}
+
+// Warp-level MMA m16n8k16, f16 inputs, f32 accumulate: D = A*B + C.
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 v) { return *reinterpret_cast<uint32_t *>(&v); }
+__device__ __forceinline__ __half2 u32_as_h2(uint32_t v) { return *reinterpret_cast<__half2 *>(&v); }
+__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t mask, uint32_t orv) {
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(mask), "r"(orv));  // (a & mask) | orv
+    return r;
+}
+__device__ __forceinline__ uint32_t hfma2_u32(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t r;
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+    return r;
+}
+__device__ __forceinline__ uint32_t hsub2_u32(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+
+__device__ __forceinline__ float load_as_f32(const void *base, int dtype, size_t index) {
+    if (dtype == ZQ_F32) return reinterpret_cast<const float *>(base)[index];
+    if (dtype == ZQ_F16) return __half2float(reinterpret_cast<const __half *>(base)[index]);
+    return __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(base)[index]);
+}
+__device__ __forceinline__ void store_from_f32(void *base, int dtype, size_t index, float v) {
+    if (dtype == ZQ_F32) reinterpret_cast<float *>(base)[index] = v;
+    else if (dtype == ZQ_F16) reinterpret_cast<__half *>(base)[index] = __float2half_rn(v);
+    else reinterpret_cast<__nv_bfloat16 *>(base)[index] = __float2bfloat16_rn(v);
+}
+__host__ __device__ inline size_t dtype_size(int dtype) { return dtype == ZQ_F32 ? 4 : 2; }
+
+// ---------------------------------------------------------------------------------------------------------------
+// Host side.
+// ---------------------------------------------------------------------------------------------------------------
+int set_error(zq_error *err, int code, const char *fmt, ...);
+
+#define ZQ_CUDA_CHECK(expr, err)                                                                                            \
+    do {                                                                                                                    \
+        cudaError_t _e = (expr);                                                                                            \
+        if (_e != cudaSuccess) return zq::set_error((err), ZQ_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), __FILE__, __LINE__); \
+    } while (0)
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn get_encode_tiled(zq_error *err);
+
+}  // namespace zq
+
+struct zq_ctx {
+    int device = 0;
+    int sm_count = 0;
+    cudaStream_t own_stream = nullptr;
+    cudaStream_t stream = nullptr;
+    // Split-K fix-up scratch of the decode GEMV: partial tiles and per-tile arrival counters (zeroed once;
+    // the finishing CTA of every tile resets its counter).
+    float *gemv_partials = nullptr;
+    uint32_t *gemv_counters = nullptr;
+    size_t gemv_partials_floats = 0;
+    size_t gemv_counters_n = 0;
+    // General workspace (grows on demand, never shrinks): dequantised operands of the prefill GEMM, MoE buffers.
+    void *workspace = nullptr;
+    size_t workspace_bytes = 0;
+    // Activated intermediate [m, I] of gated_mlp (grows on demand).
+    void *mid = nullptr;
+    size_t mid_bytes = 0;
+    // Device status word (mapped pinned host memory so the host can read it without a copy).
+    uint32_t *status_host = nullptr;
+    uint32_t *status_dev = nullptr;
+    // Pinned staging for the *_host entry points.
+    void *pinned = nullptr;
+    size_t pinned_bytes = 0;
+    void *host_io_dev = nullptr;
+    size_t host_io_bytes = 0;
+    std::atomic<uint64_t> launches{0};
+    std::mutex mutex;
+};
+
+struct zq_weight {
+    zq_ctx *ctx = nullptr;
+    uint32_t type = 0;
+    size_t rows = 0, cols = 0;
+    size_t units_per_row = 0;    // ceil(cols / 256)
+    size_t row_pitch = 0;        // resident bytes per row = units_per_row * unit_bytes
+    size_t gguf_bytes = 0;       // bytes of the original packing
+    uint8_t *data = nullptr;     // resident layout, device
+    bool owns_data = true;
+    CUtensorMap gemv_map;        // u32 tensor [rows, row_pitch/4], box = (chunk words, 128 rows): decode GEMV
+    CUtensorMap gemv_map_half;   // same tensor, box of 64 rows: gated GEMV (gate and up halves of one stage)
+};
+
+namespace zq {
+int ensure_workspace(zq_ctx *ctx, size_t bytes, zq_error *err);
+int ensure_scratch_mid(zq_ctx *ctx, size_t bytes, zq_error *err);
+int make_weight_map(const zq_weight *w, int box_words, int box_rows, CUtensorMap *out, zq_error *err);
+
+// Launchers implemented in the .cu files.
+int launch_repack(zq_ctx *ctx, uint32_t type, const uint8_t *gguf, uint8_t *resident, size_t rows, size_t cols, zq_error *err);
+int launch_dequantize(zq_ctx *ctx, const zq_weight *w, const uint32_t *row_ids, size_t n_rows, void *out, int out_dtype, zq_error *err);
+int launch_quantize(zq_ctx *ctx, uint32_t type, const float *values, size_t rows, size_t cols, void *out, zq_error *err);
+int launch_gemv(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const void *x, int x_dtype, size_t m, void *y, int y_dtype, const void *residual, zq_error *err);
+int launch_gemm(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const void *x, int x_dtype, size_t m, void *y, int y_dtype, const void *residual, zq_error *err);
+}  // namespace zq

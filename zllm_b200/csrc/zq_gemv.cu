@@ -1,0 +1,591 @@
+// Decode GEMV for GGUF block-quantised weights (1..8 activation rows per launch), sm_100a.
+//
+// Replaces, behind the same operator surface, the reference's decode kernels gguf_kq_gemv_f16,
+// gguf_block32_gemv_f16, linear_q4_0_gemv_f16 and gated_linear_q4_k_silu_f16
+// (src/kernel/cuda/linear.rs:139-204, 267-294, 799-852); the arithmetic contract is the CPU path
+// ggml_quant::matvec / matvec_residual / gated_silu_matvec (src/kernel/cpu/ggml_quant.rs:189-277).
+//
+// Design (HBM-bound: 0.5625 B per weight, so only ~3 issue slots per weight exist at full bandwidth):
+//   * Work item = (tile of 128 weight rows) x (chunk of 2 units = 512 input columns).  All items are laid out
+//     in one line (tile-major) and cut into gridDim.x equal contiguous ranges, one persistent CTA per SM, so every
+//     SM streams the same number of bytes whatever the matrix shape.  A tile whose chunks are split between CTAs
+//     is finished by whichever CTA arrives last, which adds the partial tiles in CTA order (deterministic).
+//   * Packed rows are staged by TMA (cp.async.bulk.tensor.2d, one box of 128 rows x 288/544 bytes per item)
+//     through a ring of shared-memory stages with mbarrier completion; rows past the matrix and units past the
+//     row are zero-filled by the TMA unit, so edge tiles need no special code.
+//   * The dot products run on the tensor cores as m16n8k16 f16 MMAs with f32 accumulation.  The A operand is
+//     built in registers from the packed quants with exact integer-in-f16 tricks: Q4_K feeds scale*quant
+//     (<= 63*15, exact in f16) and handles the min term with one extra MMA against per-group activation sums;
+//     Q4_0 feeds nibble-8, Q8_0 the int8 value and IQ4_NL the codebook entry, each scaled per block in f32.
+//     The B operand is the activation row split into two f16 limbs (hi + lo, ~22 bits) so that the result
+//     carries f32-level accuracy; limbs of up to 4 rows fill the 8 MMA columns.
+//   * Which four weights a thread feeds into MMA step s is free (a dot product does not care about the order
+//     of k), so it is chosen to make every shared-memory read a conflict-free 16-byte load of bytes the thread
+//     needs anyway; the activation staging applies the same permutation.
+#include "zq_common.cuh"
+
+namespace zq {
+
+constexpr int kTileRows = 128;
+constexpr int kChunkUnits = 2;
+constexpr int kChunkCols = kChunkUnits * kUnitWeights;  // 512
+constexpr int kGemvThreads = 512;                       // 16 warps: 8 row sub-tiles x 2 units
+constexpr int kMaxGemvRows = 8;
+constexpr int kSlotFloats = kTileRows * kMaxGemvRows;   // one partial tile in the fix-up scratch
+
+template <uint32_t TYPE> struct Fmt;
+template <> struct Fmt<ZQ_Q4_K> { static constexpr int unit_bytes = 144; static constexpr int stages = 4; static constexpr bool lut = false; };
+template <> struct Fmt<ZQ_Q4_0> { static constexpr int unit_bytes = 144; static constexpr int stages = 4; static constexpr bool lut = false; };
+template <> struct Fmt<ZQ_IQ4_NL> { static constexpr int unit_bytes = 144; static constexpr int stages = 3; static constexpr bool lut = true; };
+template <> struct Fmt<ZQ_Q8_0> { static constexpr int unit_bytes = 272; static constexpr int stages = 2; static constexpr bool lut = false; };
+
+template <uint32_t TYPE, int NT> struct GemvSmem {
+    static constexpr int pitch = kChunkUnits * Fmt<TYPE>::unit_bytes;
+    static constexpr int stage_w = kTileRows * pitch;
+    static constexpr int stage_x = NT * kChunkUnits * 16 * 32 * 8;
+    static constexpr int stage_sx = NT * kChunkUnits * 32 * 4;
+    static constexpr int off_w = 0;
+    static constexpr int off_x = off_w + Fmt<TYPE>::stages * stage_w;
+    static constexpr int off_sx = off_x + Fmt<TYPE>::stages * stage_x;
+    static constexpr int off_red = off_sx + Fmt<TYPE>::stages * stage_sx;
+    static constexpr int red_bytes = 2 * kTileRows * NT * 4 * 4;
+    static constexpr int off_lut = off_red + red_bytes;
+    static constexpr int lut_bytes = Fmt<TYPE>::lut ? 256 * 32 * 4 : 0;
+    static constexpr int off_bar = off_lut + lut_bytes;
+    static constexpr int total = off_bar + 64 + 128;  // barriers + slack for 128-byte alignment of the base
+};
+
+struct GemvParams {
+    const void *x;        // [m, cols]
+    void *y;              // [m, n_out]
+    const void *residual; // [m, n_out] or null
+    float *partials;      // fix-up scratch
+    uint32_t *counters;
+    uint32_t *status;
+    int x_dtype, y_dtype;
+    int m;                // 1..8
+    int cols;             // logical K
+    int n_out;            // output features (rows of W; for gated: rows of gate == rows of up)
+    int tiles;            // ceil(n_out / rows_per_tile)
+    int chunks;           // ceil(units_per_row / kChunkUnits)
+    int chunk_words;      // kChunkUnits * unit_bytes / 4
+};
+
+// Fragment row g (0..7) -> row inside the warp's 16-row sub-tile.  Swapping the two low bits puts the two rows a
+// quarter-warp reads 2 apart, which makes the 16-byte fragment loads bank-conflict free for row pitches that
+// are 32 mod 128 bytes (288 and 544).
+__device__ __forceinline__ int frag_row(int g) { return (g & 4) | ((g & 1) << 1) | ((g >> 1) & 1); }
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+
+// Where the activation quad starting at unit element i (a multiple of 4) lands in the B-fragment staging:
+// MMA step and lane-t for the whole-quad formats.
+template <uint32_t TYPE> __device__ __forceinline__ void quad_slot(int i, int &step, int &t) {
+    if (TYPE == ZQ_Q4_K) {
+        int G = i >> 5, e = (i >> 4) & 1, ii = (i >> 2) & 3;
+        int piece = 2 * (G >> 1) + e;
+        t = piece & 3;
+        step = 8 * (piece >> 2) + 2 * ii + (G & 1);
+    } else if (TYPE == ZQ_Q8_0) {
+        int blk = i >> 5, e = (i >> 4) & 1;
+        t = (i >> 2) & 3;
+        step = 2 * blk + e;
+    } else {  // Q4_0
+        int blk = i >> 5, nib = (i >> 4) & 1;
+        t = (i >> 2) & 3;
+        step = 8 * (blk >> 2) + 2 * (blk & 3) + nib;
+    }
+}
+
+template <uint32_t TYPE, int NT, bool GATED>
+__global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemvParams p) {
+    using S = GemvSmem<TYPE, NT>;
+    constexpr int STAGES = Fmt<TYPE>::stages;
+    constexpr int UB = Fmt<TYPE>::unit_bytes;
+    constexpr int XQ = NT;  // activation quads converted per thread per item: m*128 quads over 512 threads
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+    uint8_t *ws = smem + S::off_w;
+    uint2 *xs = reinterpret_cast<uint2 *>(smem + S::off_x);
+    uint32_t *sxs = reinterpret_cast<uint32_t *>(smem + S::off_sx);
+    float *red = reinterpret_cast<float *>(smem + S::off_red);
+    uint32_t *lut = reinterpret_cast<uint32_t *>(smem + S::off_lut);
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + S::off_bar);
+    __shared__ int s_flag;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int rs = warp & 7, ul = warp >> 3;
+    const int rows_per_tile = GATED ? kTileRows / 2 : kTileRows;
+
+    // ---- this CTA's contiguous range of work items
+    const long long T = (long long)p.tiles * p.chunks;
+    const long long G = gridDim.x;
+    const long long begin = (long long)blockIdx.x * T / G;
+    const long long end = (long long)(blockIdx.x + 1) * T / G;
+    const int n_items = (int)(end - begin);
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) mbar_init(&full[s], 1);
+        fence_mbar_init();
+        tma_prefetch_desc(&map_a);
+        if (GATED) tma_prefetch_desc(&map_b);
+    }
+    // zero the activation staging once: lanes of unused MMA columns must read zeros
+    for (int i = tid; i < (STAGES * (S::stage_x + S::stage_sx)) / 4; i += kGemvThreads) reinterpret_cast<uint32_t *>(smem + S::off_x)[i] = 0;
+    if constexpr (Fmt<TYPE>::lut) {
+        // codebook pairs, one private copy per lane (entry*32 + lane) so that the random lookups never conflict
+        for (int i = tid; i < 256 * 32; i += kGemvThreads) {
+            int b = i >> 5;
+            __half2 v = __halves2half2(__int2half_rn(kIq4nlValues[b & 15]), __int2half_rn(kIq4nlValues[b >> 4]));
+            lut[i] = h2_as_u32(v);
+        }
+    }
+    __syncthreads();
+
+    auto issue_tma = [&](int local, int stage) {
+        long long item = begin + local;
+        int tile = (int)(item / p.chunks), chunk = (int)(item % p.chunks);
+        uint8_t *dst = ws + (size_t)stage * S::stage_w;
+        mbar_expect_tx(&full[stage], S::stage_w);
+        if (GATED) {
+            tma_load_2d(dst, &map_a, &full[stage], chunk * p.chunk_words, tile * rows_per_tile);
+            tma_load_2d(dst + S::stage_w / 2, &map_b, &full[stage], chunk * p.chunk_words, tile * rows_per_tile);
+        } else {
+            tma_load_2d(dst, &map_a, &full[stage], chunk * p.chunk_words, tile * rows_per_tile);
+        }
+    };
+
+    // activation quads of one item: register staging (load early, convert after the MMAs)
+    float4 xr[XQ];
+    auto load_x = [&](int local) {
+        long long item = begin + local;
+        int chunk = (int)(item % p.chunks);
+#pragma unroll
+        for (int r = 0; r < XQ; ++r) {
+            int q = tid + r * kGemvThreads;
+            int m = q >> 7, quad = q & 127;
+            int k0 = chunk * kChunkCols + quad * 4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (m < p.m && k0 < p.cols) {
+                size_t o = (size_t)m * p.cols + k0;
+                if (p.x_dtype == ZQ_F32) v = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p.x) + o);
+                else v = make_float4(load_as_f32(p.x, p.x_dtype, o), load_as_f32(p.x, p.x_dtype, o + 1), load_as_f32(p.x, p.x_dtype, o + 2), load_as_f32(p.x, p.x_dtype, o + 3));
+            }
+            xr[r] = v;
+        }
+    };
+    auto store_x = [&](int stage) {
+        uint2 *xst = xs + (size_t)stage * (S::stage_x / 8);
+        uint32_t *sxst = sxs + (size_t)stage * (S::stage_sx / 4);
+#pragma unroll
+        for (int r = 0; r < XQ; ++r) {
+            int q = tid + r * kGemvThreads;
+            int m = q >> 7, quad = q & 127;
+            if (m >= p.m) continue;  // whole warps: 128 quads per row
+            float v[4] = {xr[r].x, xr[r].y, xr[r].z, xr[r].w};
+            __half hi[4], lo[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                hi[j] = __float2half_rn(v[j]);
+                lo[j] = __float2half_rn(v[j] - __half2float(hi[j]));
+            }
+            int unit = quad >> 6, i = (quad & 63) * 4;
+            int nt = m >> 2, col = 2 * (m & 3);
+            if constexpr (TYPE == ZQ_IQ4_NL) {
+                // element i+by of the quad pairs with the other nibble of the same byte: MMA step 8h+2bb+(by>>1),
+                // register by&1, half index = nibble (see the A-fragment construction below)
+                int blk = i >> 5, nib = (i >> 4) & 1, tt = (i >> 2) & 3;
+                int step0 = 8 * (blk >> 2) + 2 * (blk & 3);
+#pragma unroll
+                for (int by = 0; by < 4; ++by) {
+                    int step = step0 + (by >> 1);
+                    __half *dst_hi = reinterpret_cast<__half *>(&xst[((nt * kChunkUnits + unit) * 16 + step) * 32 + (col * 4 + tt)]);
+                    __half *dst_lo = reinterpret_cast<__half *>(&xst[((nt * kChunkUnits + unit) * 16 + step) * 32 + ((col + 1) * 4 + tt)]);
+                    dst_hi[(by & 1) * 2 + nib] = hi[by];
+                    dst_lo[(by & 1) * 2 + nib] = lo[by];
+                }
+            } else {
+                int step, tt;
+                quad_slot<TYPE>(i, step, tt);
+                uint2 *base = &xst[((nt * kChunkUnits + unit) * 16 + step) * 32];
+                base[col * 4 + tt] = make_uint2(h2_as_u32(__halves2half2(hi[0], hi[2])), h2_as_u32(__halves2half2(hi[1], hi[3])));
+                base[(col + 1) * 4 + tt] = make_uint2(h2_as_u32(__halves2half2(lo[0], lo[2])), h2_as_u32(__halves2half2(lo[1], lo[3])));
+            }
+            if constexpr (TYPE == ZQ_Q4_K) {
+                // per-group activation sums (32 columns = 8 consecutive quads = 8 consecutive lanes)
+                float sum = (v[0] + v[1]) + (v[2] + v[3]);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+                if ((lane & 7) == 0) {
+                    int G8 = (i >> 5);  // group inside the unit
+                    __half shi = __float2half_rn(sum);
+                    __half slo = __float2half_rn(sum - __half2float(shi));
+                    __half *dst = reinterpret_cast<__half *>(&sxst[(nt * kChunkUnits + unit) * 32]);
+                    dst[(col * 4 + (G8 >> 1)) * 2 + (G8 & 1)] = shi;
+                    dst[((col + 1) * 4 + (G8 >> 1)) * 2 + (G8 & 1)] = slo;
+                }
+            }
+        }
+    };
+
+    // ---- prologue: fill the ring
+    const int pre = n_items < STAGES - 1 ? n_items : STAGES - 1;
+    for (int s = 0; s < pre; ++s) {
+        if (tid == 0) issue_tma(s, s);
+        load_x(s);
+        store_x(s);
+    }
+    __syncthreads();
+
+    float yacc[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) yacc[nt][0] = yacc[nt][1] = 0.f;
+
+    const int r0 = 16 * rs + frag_row(g);  // tile row of fragment row g; the g+8 row is r0 + 8
+    bool failed = false;
+
+    for (int it = 0; it < n_items; ++it) {
+        const int stage = it % STAGES;
+        const int nxt = it + STAGES - 1;
+        const int nstage = nxt % STAGES;
+        if (nxt < n_items) {
+            if (tid == 0) issue_tma(nxt, nstage);
+            load_x(nxt);
+        }
+        if (!mbar_wait_bounded(&full[stage], (it / STAGES) & 1)) {
+            failed = true;
+        }
+        if (__syncthreads_or(failed ? 1 : 0)) {  // a TMA that never landed: record and leave together
+            if (tid == 0) atomicMax(p.status, (uint32_t)kStatusTmaTimeout);
+            return;
+        }
+
+        // ---------------- MMAs of this item: this warp's 16 rows x one unit
+        {
+            const uint8_t *w0 = ws + (size_t)stage * S::stage_w + (size_t)r0 * S::pitch + ul * UB;
+            const uint8_t *w1 = w0 + 8 * S::pitch;
+            const uint2 *xb = xs + (size_t)stage * (S::stage_x / 8) + (size_t)ul * 16 * 32 + lane;
+            const uint4 hdr0 = *reinterpret_cast<const uint4 *>(w0);
+            const uint4 hdr1 = *reinterpret_cast<const uint4 *>(w1);
+
+            if constexpr (TYPE == ZQ_Q4_K) {
+                float d1[NT][4], d2[NT][4];
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) d1[nt][j] = d2[nt][j] = 0.f;
+                const uint32_t k1024 = 0x64006400u, k64x4 = 0x64646464u, kNeg1024 = 0xE400E400u, kNeg64 = 0xD400D400u;
+                // 6-bit codes of the 8 groups, four per word
+                uint32_t sc_lo0 = hdr0.y & 0x3F3F3F3Fu, sc_hi0 = (hdr0.w & 0x0F0F0F0Fu) | ((hdr0.y >> 2) & 0x30303030u);
+                uint32_t sc_lo1 = hdr1.y & 0x3F3F3F3Fu, sc_hi1 = (hdr1.w & 0x0F0F0F0Fu) | ((hdr1.y >> 2) & 0x30303030u);
+                uint32_t mn_lo0 = hdr0.z & 0x3F3F3F3Fu, mn_hi0 = ((hdr0.w >> 4) & 0x0F0F0F0Fu) | ((hdr0.z >> 2) & 0x30303030u);
+                uint32_t mn_lo1 = hdr1.z & 0x3F3F3F3Fu, mn_hi1 = ((hdr1.w >> 4) & 0x0F0F0F0Fu) | ((hdr1.z >> 2) & 0x30303030u);
+                const uint32_t bidx = 2 * (t >> 1);
+                const uint32_t sel_a = 0x4040u | (bidx * 0x0101u);        // [code, 0x64, code, 0x64] of group bidx
+                const uint32_t sel_b = 0x4040u | ((bidx + 1) * 0x0101u);  // ... of group bidx+1
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint4 pc0 = *reinterpret_cast<const uint4 *>(w0 + 16 + 16 * (t + 4 * h));
+                    const uint4 pc1 = *reinterpret_cast<const uint4 *>(w1 + 16 + 16 * (t + 4 * h));
+                    const uint32_t sc0 = h ? sc_hi0 : sc_lo0, sc1 = h ? sc_hi1 : sc_lo1;
+                    // scale as f16 pair, and the offset that removes the 1024 / 64 bias of the nibble trick
+                    const uint32_t sa0 = hsub2_u32(prmt(sc0, k64x4, sel_a), k1024), sb0 = hsub2_u32(prmt(sc0, k64x4, sel_b), k1024);
+                    const uint32_t sa1 = hsub2_u32(prmt(sc1, k64x4, sel_a), k1024), sb1 = hsub2_u32(prmt(sc1, k64x4, sel_b), k1024);
+                    const uint32_t oa0 = hmul2_u32(sa0, kNeg1024), ob0 = hmul2_u32(sb0, kNeg64);
+                    const uint32_t oa1 = hmul2_u32(sa1, kNeg1024), ob1 = hmul2_u32(sb1, kNeg64);
+                    const uint32_t q0[4] = {pc0.x, pc0.y, pc0.z, pc0.w};
+                    const uint32_t q1[4] = {pc1.x, pc1.y, pc1.z, pc1.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const uint32_t x0 = q0[i], x0s = q0[i] >> 8, x1 = q1[i], x1s = q1[i] >> 8;
+                        // low nibbles -> group 2p (bias 1024), high nibbles -> group 2p+1 (bias 64)
+                        uint32_t a0 = hfma2_u32(lop3_and_or(x0, 0x000F000Fu, 0x64006400u), sa0, oa0);
+                        uint32_t a2 = hfma2_u32(lop3_and_or(x0s, 0x000F000Fu, 0x64006400u), sa0, oa0);
+                        uint32_t a1 = hfma2_u32(lop3_and_or(x1, 0x000F000Fu, 0x64006400u), sa1, oa1);
+                        uint32_t a3 = hfma2_u32(lop3_and_or(x1s, 0x000F000Fu, 0x64006400u), sa1, oa1);
+                        const int step = 8 * h + 2 * i;
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt) {
+                            uint2 b = xb[((size_t)nt * kChunkUnits * 16 + step) * 32];
+                            mma_16816(d1[nt], a0, a1, a2, a3, b.x, b.y);
+                        }
+                        a0 = hfma2_u32(lop3_and_or(x0, 0x00F000F0u, 0x54005400u), sb0, ob0);
+                        a2 = hfma2_u32(lop3_and_or(x0s, 0x00F000F0u, 0x54005400u), sb0, ob0);
+                        a1 = hfma2_u32(lop3_and_or(x1, 0x00F000F0u, 0x54005400u), sb1, ob1);
+                        a3 = hfma2_u32(lop3_and_or(x1s, 0x00F000F0u, 0x54005400u), sb1, ob1);
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt) {
+                            uint2 b = xb[((size_t)nt * kChunkUnits * 16 + step + 1) * 32];
+                            mma_16816(d1[nt], a0, a1, a2, a3, b.x, b.y);
+                        }
+                    }
+                }
+                // min term: one MMA of the 8 min codes against the 8 per-group activation sums
+                {
+                    const uint32_t mb = 2 * (t & 1);
+                    const uint32_t sel_m = 0x4040u | ((mb + 1) << 8) | mb;  // [m_2t, 0x64, m_2t+1, 0x64]
+                    const uint32_t ma0 = hsub2_u32(prmt(t < 2 ? mn_lo0 : mn_hi0, k64x4, sel_m), k1024);
+                    const uint32_t ma1 = hsub2_u32(prmt(t < 2 ? mn_lo1 : mn_hi1, k64x4, sel_m), k1024);
+                    const uint32_t *sxb = sxs + (size_t)stage * (S::stage_sx / 4) + (size_t)ul * 32 + lane;
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) mma_16816(d2[nt], ma0, ma1, 0u, 0u, sxb[(size_t)nt * kChunkUnits * 32], 0u);
+                }
+                const __half2 dd0 = u32_as_h2(hdr0.x), dd1 = u32_as_h2(hdr1.x);
+                const float d_0 = __low2float(dd0), dm_0 = __high2float(dd0), d_1 = __low2float(dd1), dm_1 = __high2float(dd1);
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    yacc[nt][0] += d_0 * (d1[nt][0] + d1[nt][1]) - dm_0 * (d2[nt][0] + d2[nt][1]);
+                    yacc[nt][1] += d_1 * (d1[nt][2] + d1[nt][3]) - dm_1 * (d2[nt][2] + d2[nt][3]);
+                }
+            } else if constexpr (TYPE == ZQ_Q8_0) {
+                const uint32_t hd0[4] = {hdr0.x, hdr0.y, hdr0.z, hdr0.w}, hd1[4] = {hdr1.x, hdr1.y, hdr1.z, hdr1.w};
+#pragma unroll
+                for (int h = 0; h < 4; ++h) {
+                    const uint4 pc0 = *reinterpret_cast<const uint4 *>(w0 + 16 + 16 * (t + 4 * h));
+                    const uint4 pc1 = *reinterpret_cast<const uint4 *>(w1 + 16 + 16 * (t + 4 * h));
+                    const uint32_t q0[4] = {pc0.x, pc0.y, pc0.z, pc0.w};
+                    const uint32_t q1[4] = {pc1.x, pc1.y, pc1.z, pc1.w};
+                    const __half2 s0 = u32_as_h2(hd0[h]), s1 = u32_as_h2(hd1[h]);  // scales of blocks 2h, 2h+1
+#pragma unroll
+                    for (int bb = 0; bb < 2; ++bb) {
+                        float acc[NT][4];
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) acc[nt][j] = 0.f;
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            const int j = 2 * bb + e;
+                            // int8 -> exact f16: flip the sign bit (value + 128), splice under exponent 0x64, subtract 1152
+                            const uint32_t u0 = q0[j] ^ 0x80808080u, u1 = q1[j] ^ 0x80808080u;
+                            const uint32_t a0 = hsub2_u32(prmt(u0, 0x64646464u, 0x4240u), 0x64806480u);
+                            const uint32_t a2 = hsub2_u32(prmt(u0, 0x64646464u, 0x4341u), 0x64806480u);
+                            const uint32_t a1 = hsub2_u32(prmt(u1, 0x64646464u, 0x4240u), 0x64806480u);
+                            const uint32_t a3 = hsub2_u32(prmt(u1, 0x64646464u, 0x4341u), 0x64806480u);
+                            const int step = 4 * h + j;
+#pragma unroll
+                            for (int nt = 0; nt < NT; ++nt) {
+                                uint2 b = xb[((size_t)nt * kChunkUnits * 16 + step) * 32];
+                                mma_16816(acc[nt], a0, a1, a2, a3, b.x, b.y);
+                            }
+                        }
+                        const float sc0 = bb ? __high2float(s0) : __low2float(s0), sc1 = bb ? __high2float(s1) : __low2float(s1);
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt) {
+                            yacc[nt][0] += sc0 * (acc[nt][0] + acc[nt][1]);
+                            yacc[nt][1] += sc1 * (acc[nt][2] + acc[nt][3]);
+                        }
+                    }
+                }
+            } else {  // Q4_0, IQ4_NL
+                const uint32_t hd0[4] = {hdr0.x, hdr0.y, hdr0.z, hdr0.w}, hd1[4] = {hdr1.x, hdr1.y, hdr1.z, hdr1.w};
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint4 pc0 = *reinterpret_cast<const uint4 *>(w0 + 16 + 16 * (t + 4 * h));
+                    const uint4 pc1 = *reinterpret_cast<const uint4 *>(w1 + 16 + 16 * (t + 4 * h));
+                    const uint32_t q0[4] = {pc0.x, pc0.y, pc0.z, pc0.w};
+                    const uint32_t q1[4] = {pc1.x, pc1.y, pc1.z, pc1.w};
+#pragma unroll
+                    for (int bb = 0; bb < 4; ++bb) {  // block 4h+bb, word t of its quants
+                        float acc[NT][4];
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) acc[nt][j] = 0.f;
+                        const uint32_t x0 = q0[bb], x1 = q1[bb];
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            uint32_t a0, a1, a2, a3;
+                            if constexpr (TYPE == ZQ_Q4_0) {
+                                // e = 0: low nibbles (elements 4t..4t+3), e = 1: high nibbles (16+4t..); value = nibble - 8
+                                const uint32_t mask = e ? 0x00F000F0u : 0x000F000Fu, bias = e ? 0x54005400u : 0x64006400u;
+                                const uint32_t off = e ? 0x54805480u : 0x64086408u;  // 64+8 = 72, 1024+8 = 1032
+                                a0 = hsub2_u32(lop3_and_or(x0, mask, bias), off);
+                                a2 = hsub2_u32(lop3_and_or(x0 >> 8, mask, bias), off);
+                                a1 = hsub2_u32(lop3_and_or(x1, mask, bias), off);
+                                a3 = hsub2_u32(lop3_and_or(x1 >> 8, mask, bias), off);
+                            } else {
+                                // codebook pair of one byte = (element 4t+by, element 16+4t+by); step e takes bytes 2e, 2e+1
+                                const uint32_t *l = lut + lane;
+                                a0 = l[((x0 >> (16 * e)) & 0xFFu) * 32];
+                                a2 = l[((x0 >> (16 * e + 8)) & 0xFFu) * 32];
+                                a1 = l[((x1 >> (16 * e)) & 0xFFu) * 32];
+                                a3 = l[((x1 >> (16 * e + 8)) & 0xFFu) * 32];
+                            }
+                            const int step = 8 * h + 2 * bb + e;
+#pragma unroll
+                            for (int nt = 0; nt < NT; ++nt) {
+                                uint2 b = xb[((size_t)nt * kChunkUnits * 16 + step) * 32];
+                                mma_16816(acc[nt], a0, a1, a2, a3, b.x, b.y);
+                            }
+                        }
+                        const int blk = 4 * h + bb;
+                        const __half2 s0 = u32_as_h2(hd0[blk >> 1]), s1 = u32_as_h2(hd1[blk >> 1]);
+                        const float sc0 = (blk & 1) ? __high2float(s0) : __low2float(s0), sc1 = (blk & 1) ? __high2float(s1) : __low2float(s1);
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt) {
+                            yacc[nt][0] += sc0 * (acc[nt][0] + acc[nt][1]);
+                            yacc[nt][1] += sc1 * (acc[nt][2] + acc[nt][3]);
+                        }
+                    }
+                }
+            }
+        }
+
+        if (nxt < n_items) store_x(nstage);
+
+        // ---------------- end of a tile (or of this CTA's range): reduce, then store or hand over
+        const long long item = begin + it;
+        const int tile = (int)(item / p.chunks);
+        const bool tile_ends = (it == n_items - 1) || ((int)((item + 1) / p.chunks) != tile);
+        if (tile_ends) {
+            // the two warps that share a row sub-tile add up through shared memory: red[ul][row][token]
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                red[(ul * kTileRows + r0) * (NT * 4) + nt * 4 + t] = yacc[nt][0];
+                red[(ul * kTileRows + r0 + 8) * (NT * 4) + nt * 4 + t] = yacc[nt][1];
+                yacc[nt][0] = yacc[nt][1] = 0.f;
+            }
+            __syncthreads();
+            const long long tile_first = (long long)tile * p.chunks, tile_last = tile_first + p.chunks - 1;
+            const bool whole = begin <= tile_first && tile_last < end;
+            const int c_first = (int)(((tile_first + 1) * G - 1) / T), c_last = (int)(((tile_last + 1) * G - 1) / T);
+            bool finish = whole;
+            if (!whole) {
+                const int which = (tile == (int)(begin / p.chunks)) ? 0 : 1;
+                float *slot = p.partials + ((size_t)blockIdx.x * 2 + which) * kSlotFloats;
+                for (int i = tid; i < kTileRows * p.m; i += kGemvThreads) {
+                    int row = i & (kTileRows - 1), tok = i >> 7;
+                    slot[tok * kTileRows + row] = red[row * (NT * 4) + tok] + red[(kTileRows + row) * (NT * 4) + tok];
+                }
+                __threadfence();
+                __syncthreads();
+                if (tid == 0) {
+                    unsigned old = atomicAdd(&p.counters[tile], 1u);
+                    s_flag = (old == (unsigned)(c_last - c_first)) ? 1 : 0;
+                }
+                __syncthreads();
+                finish = s_flag != 0;
+                if (finish) __threadfence();
+            }
+            if (finish) {
+                // final value of every (row, token) of the tile, staged in red[0] as fin[token][row]
+                float vals[(kTileRows * kMaxGemvRows + kGemvThreads - 1) / kGemvThreads];
+                int cnt = 0;
+                for (int i = tid; i < kTileRows * p.m; i += kGemvThreads, ++cnt) {
+                    int row = i & (kTileRows - 1), tok = i >> 7;
+                    float v;
+                    if (whole) {
+                        v = red[row * (NT * 4) + tok] + red[(kTileRows + row) * (NT * 4) + tok];
+                    } else {
+                        v = 0.f;
+                        for (int c = c_first; c <= c_last; ++c) {  // fixed order: deterministic
+                            long long cb = (long long)c * T / G;
+                            int which = (tile == (int)(cb / p.chunks)) ? 0 : 1;
+                            v += __ldcg(p.partials + ((size_t)c * 2 + which) * kSlotFloats + tok * kTileRows + row);
+                        }
+                    }
+                    vals[cnt] = v;
+                }
+                __syncthreads();
+                cnt = 0;
+                for (int i = tid; i < kTileRows * p.m; i += kGemvThreads, ++cnt) red[i] = vals[cnt];  // fin[tok*128 + row]
+                __syncthreads();
+                const int out_rows = rows_per_tile;
+                for (int i = tid; i < out_rows * p.m; i += kGemvThreads) {
+                    int row = i % out_rows, tok = i / out_rows;
+                    int n = tile * out_rows + row;
+                    if (n >= p.n_out) continue;
+                    float v;
+                    if (GATED) {
+                        float gate = red[tok * kTileRows + row], up = red[tok * kTileRows + out_rows + row];
+                        v = (gate / (1.0f + expf(-gate))) * up;  // src/kernel/cpu/ggml_quant.rs:274
+                    } else {
+                        v = red[tok * kTileRows + row];
+                    }
+                    size_t o = (size_t)tok * p.n_out + n;
+                    if (p.residual) v += load_as_f32(p.residual, p.y_dtype, o);
+                    store_from_f32(p.y, p.y_dtype, o, v);
+                }
+                if (!whole && tid == 0) p.counters[tile] = 0;  // leave the counter ready for the next launch
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Host launcher.
+// ---------------------------------------------------------------------------------------------------------------
+
+template <uint32_t TYPE, int NT, bool GATED>
+static int launch_one(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const GemvParams &p, int grid, zq_error *err) {
+    using S = GemvSmem<TYPE, NT>;
+    static bool configured[64] = {};
+    auto kernel = gemv_kernel<TYPE, NT, GATED>;
+    if (!configured[ctx->device & 63]) {
+        ZQ_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::total), err);
+        configured[ctx->device & 63] = true;
+    }
+    const CUtensorMap &ma = GATED ? w->gemv_map_half : w->gemv_map;
+    const CUtensorMap &mb = GATED ? w_up->gemv_map_half : w->gemv_map;
+    kernel<<<grid, kGemvThreads, S::total, ctx->stream>>>(ma, mb, p);
+    ctx->launches++;
+    ZQ_CUDA_CHECK(cudaGetLastError(), err);
+    return ZQ_OK;
+}
+
+template <uint32_t TYPE>
+static int launch_type(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const GemvParams &p, int grid, zq_error *err) {
+    const bool gated = w_up != nullptr;
+    if (p.m <= 4) return gated ? launch_one<TYPE, 1, true>(ctx, w, w_up, p, grid, err) : launch_one<TYPE, 1, false>(ctx, w, w_up, p, grid, err);
+    return gated ? launch_one<TYPE, 2, true>(ctx, w, w_up, p, grid, err) : launch_one<TYPE, 2, false>(ctx, w, w_up, p, grid, err);
+}
+
+// y[m, n] = x[m, k] W^T (+ residual), or silu(x gate^T) * (x up^T) when w_up is given.  m may exceed 8: the rows
+// are then processed in groups of 8 (each group streams the weights once).
+int launch_gemv(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const void *x, int x_dtype, size_t m, void *y, int y_dtype, const void *residual, zq_error *err) {
+    const FormatInfo f = format_info(w->type);
+    const bool gated = w_up != nullptr;
+    const int rows_per_tile = gated ? kTileRows / 2 : kTileRows;
+    GemvParams p;
+    p.partials = ctx->gemv_partials;
+    p.counters = ctx->gemv_counters;
+    p.status = ctx->status_dev;
+    p.x_dtype = x_dtype;
+    p.y_dtype = y_dtype;
+    p.cols = (int)w->cols;
+    p.n_out = (int)w->rows;
+    p.tiles = (int)((w->rows + rows_per_tile - 1) / rows_per_tile);
+    p.chunks = (int)((w->units_per_row + kChunkUnits - 1) / kChunkUnits);
+    p.chunk_words = kChunkUnits * f.unit_bytes / 4;
+    if ((size_t)p.tiles > ctx->gemv_counters_n) return set_error(err, ZQ_ERR_UNSUPPORTED, "GEMV needs %d tile counters, context has %zu", p.tiles, ctx->gemv_counters_n);
+    long long total = (long long)p.tiles * p.chunks;
+    int grid = (int)(total < ctx->sm_count ? total : ctx->sm_count);
+    if (grid <= 0) return ZQ_OK;
+    for (size_t m0 = 0; m0 < m; m0 += kMaxGemvRows) {
+        size_t mm = m - m0 < (size_t)kMaxGemvRows ? m - m0 : (size_t)kMaxGemvRows;
+        p.m = (int)mm;
+        p.x = reinterpret_cast<const uint8_t *>(x) + m0 * w->cols * dtype_size(x_dtype);
+        p.y = reinterpret_cast<uint8_t *>(y) + m0 * w->rows * dtype_size(y_dtype);
+        p.residual = residual ? reinterpret_cast<const uint8_t *>(residual) + m0 * w->rows * dtype_size(y_dtype) : nullptr;
+        int rc;
+        switch (w->type) {
+        case ZQ_Q4_K: rc = launch_type<ZQ_Q4_K>(ctx, w, w_up, p, grid, err); break;
+        case ZQ_Q4_0: rc = launch_type<ZQ_Q4_0>(ctx, w, w_up, p, grid, err); break;
+        case ZQ_IQ4_NL: rc = launch_type<ZQ_IQ4_NL>(ctx, w, w_up, p, grid, err); break;
+        case ZQ_Q8_0: rc = launch_type<ZQ_Q8_0>(ctx, w, w_up, p, grid, err); break;
+        default: return set_error(err, ZQ_ERR_UNSUPPORTED, "GEMV: unsupported GGUF type %u", w->type);
+        }
+        if (rc) return rc;
+    }
+    return ZQ_OK;
+}
+
+}  // namespace zq

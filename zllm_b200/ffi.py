@@ -1,0 +1,85 @@
+"""ctypes binding of ``libzq_b200.so`` (the C ABI declared in ``include/zq_b200.h``).
+
+The CUDA library is the product; this module only loads it and gives the entry points their prototypes.
+There is no fallback of any kind: if the library is missing or fails to load, importing raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libzq_b200.so")
+
+Q4_0, Q8_0, Q4_K, IQ4_NL = 2, 8, 12, 20
+F32, F16, BF16 = 0, 1, 2
+BLOCK = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), IQ4_NL: (32, 18)}
+
+
+class ZqError(C.Structure):
+    _fields_ = [("message", C.c_char * 512)]
+
+
+class ZqFailure(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"zq_b200 error {code}: {message}")
+        self.code = code
+        self.message = message
+
+
+_vp, _sz, _u32, _i, _f = C.c_void_p, C.c_size_t, C.c_uint32, C.c_int, C.c_float
+_err = C.POINTER(ZqError)
+
+PROTOTYPES = {
+    "zq_ctx_create": (_i, [_i, C.POINTER(_vp), _err]),
+    "zq_ctx_destroy": (None, [_vp]),
+    "zq_ctx_set_stream": (_i, [_vp, _vp, _err]),
+    "zq_ctx_sync": (_i, [_vp, _err]),
+    "zq_ctx_sm_count": (_i, [_vp]),
+    "zq_ctx_launch_count": (C.c_uint64, [_vp]),
+    "zq_weight_prepare": (_i, [_vp, _u32, _vp, _sz, _sz, _sz, C.POINTER(_vp), _err]),
+    "zq_weight_prepare_device": (_i, [_vp, _u32, _vp, _sz, _sz, _sz, C.POINTER(_vp), _err]),
+    "zq_weight_release": (None, [_vp]),
+    "zq_weight_rows": (_sz, [_vp]),
+    "zq_weight_cols": (_sz, [_vp]),
+    "zq_weight_type": (_u32, [_vp]),
+    "zq_weight_gguf_bytes": (_sz, [_vp]),
+    "zq_dequantize_f32": (_i, [_vp, _vp, _vp, _err]),
+    "zq_gather_rows": (_i, [_vp, _vp, _vp, _sz, _vp, _i, _err]),
+    "zq_quantize": (_i, [_vp, _u32, _vp, _sz, _sz, _vp, _sz, _err]),
+    "zq_linear": (_i, [_vp, _vp, _vp, _i, _sz, _vp, _i, _vp, _err]),
+    "zq_linear_multi": (_i, [_vp, C.POINTER(_vp), _sz, _vp, _i, _sz, C.POINTER(_vp), _i, _err]),
+    "zq_gated_silu": (_i, [_vp, _vp, _vp, _vp, _i, _sz, _vp, _i, _err]),
+    "zq_gated_mlp": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _sz, _vp, _i, _vp, _err]),
+    "zq_linear_host": (_i, [_vp, _vp, _vp, _i, _sz, _vp, _i, _err]),
+    "zq_moe_route_softmax_topk": (_i, [_vp, _vp, _i, _sz, _sz, _vp, _vp, _sz, _sz, _f, _i, _vp, _vp, _err]),
+    "zq_moe_experts_create": (_i, [_vp, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), _sz, C.POINTER(_vp), _err]),
+    "zq_moe_experts_destroy": (None, [_vp]),
+    "zq_moe_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _sz, _vp, _vp, _sz, _vp, _i, _vp, _err]),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Load the CUDA library (built in-tree by ``zllm_b200.build``)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(f"{LIB_PATH} is missing: build it with `python -m zllm_b200.build` (there is no fallback path)")
+        lib = C.CDLL(LIB_PATH)
+        for name, (res, args) in PROTOTYPES.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+def call(name: str, *args):
+    """Call an entry point that returns a status code and takes a trailing ``zq_error*``."""
+    err = ZqError()
+    rc = getattr(load(), name)(*args, C.byref(err))
+    if rc != 0:
+        raise ZqFailure(rc, err.message.decode("utf-8", "replace"))
+    return rc
