@@ -160,9 +160,9 @@ __global__ void quantize_q4_k_kernel(const float *__restrict__ values, uint8_t *
     float dmin = f16_round(__fdiv_rn(max_min, 63.0f));
     for (int i = 0; i < 144; ++i) block[i] = 0;
     __half dh = __float2half_rn(d), dmh = __float2half_rn(dmin);
-    uint16_t db = *reinterpret_cast<uint16_t *>(&dh), dmb = *reinterpret_cast<uint16_t *>(&dmh);
-    block[0] = (uint8_t)db; block[1] = (uint8_t)(db >> 8);
-    block[2] = (uint8_t)dmb; block[3] = (uint8_t)(dmb >> 8);
+    // blocks start on even addresses: the two f16 fields go out as 16-bit stores
+    reinterpret_cast<uint16_t *>(block)[0] = __half_as_ushort(dh);
+    reinterpret_cast<uint16_t *>(block)[1] = __half_as_ushort(dmh);
     uint8_t sc[8], mc[8];
     for (int g = 0; g < 8; ++g) {
         sc[g] = d == 0.0f ? 0 : (uint8_t)clampf(roundf(__fdiv_rn(scales[g], d)), 0.0f, 63.0f);
@@ -204,8 +204,7 @@ __global__ void quantize_block32_kernel(uint32_t type, const float *__restrict__
         float d = f16_round(__fdiv_rn(amax, 127.0f));
         float inv = d > 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
         __half dh = __float2half_rn(d);
-        uint16_t db = *reinterpret_cast<uint16_t *>(&dh);
-        block[0] = (uint8_t)db; block[1] = (uint8_t)(db >> 8);
+        reinterpret_cast<uint16_t *>(block)[0] = __half_as_ushort(dh);
         for (int i = 0; i < 32; ++i) block[2 + i] = (uint8_t)(int8_t)clampf(rintf(__fmul_rn(v[i], inv)), -127.0f, 127.0f);
         return;
     }
@@ -213,8 +212,7 @@ __global__ void quantize_block32_kernel(uint32_t type, const float *__restrict__
     float d = f16_round(__fdiv_rn(smax, type == ZQ_Q4_0 ? -8.0f : -127.0f));
     float inv = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
     __half dh = __float2half_rn(d);
-    uint16_t db = *reinterpret_cast<uint16_t *>(&dh);
-    block[0] = (uint8_t)db; block[1] = (uint8_t)(db >> 8);
+    reinterpret_cast<uint16_t *>(block)[0] = __half_as_ushort(dh);
     uint8_t codes[32];
     for (int i = 0; i < 32; ++i) {
         float s = __fmul_rn(v[i], inv);
