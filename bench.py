@@ -158,6 +158,12 @@ def run_ours(args):
             for case in cases:
                 if case[1] == fmt:
                     plan.append((m, case))
+    if args.only:
+        oname, oshape, om = args.only.split(":")
+        ok, on = (int(v) for v in oshape.split("x"))
+        plan = [(m, c) for m, c in plan if c[0] == oname and c[2] == ok and c[3] == on and m == int(om)]
+        if not plan:
+            raise SystemExit(f"--only {args.only}: no such case")
     outs = {}
     for m, case in plan:
         name, fmt, k, n, mode, w, (c0, c1), (r0, r1) = case
@@ -179,20 +185,45 @@ def run_ours(args):
         if mode == "row":
             dist.all_reduce(y)
 
-    # events bracket the Q4_K batch-1 and batch-4 blocks (the headline kernel) inside the timed region
+    # One CUDA graph per (batch, format) block of launches: replaying graphs keeps the host out of the timed
+    # region (a Python/ctypes launch costs more than a 5 us kernel).  Events between graph launches bracket the
+    # Q4_K batch-1 and batch-4 blocks (the headline kernel) inside the timed region.
+    blocks = []
+    for m in BATCHES:
+        for fmt, name in FORMATS:
+            members = [(mm, case) for mm, case in plan if mm == m and case[1] == fmt]
+            if members:
+                blocks.append((m, fmt, members))
+    for m, fmt, members in blocks:  # eager pass: sizes every internal buffer before capture
+        for mm, case in members:
+            launch(mm, case)
+    torch.cuda.synchronize()
+    graphs = []
+    if not args.no_graph:
+        side = torch.cuda.Stream(device=device)
+        for m, fmt, members in blocks:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                ctx.set_stream(torch.cuda.current_stream(device).cuda_stream)
+                for mm, case in members:
+                    launch(mm, case)
+            graphs.append(g)
+        ctx.set_stream(torch.cuda.current_stream(device).cuda_stream)
+
     def step(events=None):
-        for bi, m in enumerate(BATCHES):
-            for fmt, name in FORMATS:
-                mark = events is not None and fmt == Q4_K and m <= 4
-                if mark:
-                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    e0.record()
-                for mm, case in plan:
-                    if mm == m and case[1] == fmt:
-                        launch(m, case)
-                if mark:
-                    e1.record()
-                    events.append((e0, e1))
+        for bi, (m, fmt, members) in enumerate(blocks):
+            mark = events is not None and fmt == Q4_K and m <= 4
+            if mark:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+            if graphs:
+                graphs[bi].replay()
+            else:
+                for mm, case in members:
+                    launch(mm, case)
+            if mark:
+                e1.record()
+                events.append((e0, e1))
 
     step_bytes = sum(algorithmic_bytes(case[2], case[3], m) for m, case in plan)
     q4k_kernel_bytes = sum(algorithmic_bytes(case[2], case[3], m) for m, case in plan if case[1] == Q4_K and m <= 4)
@@ -207,7 +238,7 @@ def run_ours(args):
         step()
     barrier()
     sampler = ClockSampler(local_rank)
-    if rank == 0:
+    if rank == 0 and not args.no_clocks:
         sampler.start()
     launches_before = ctx.launch_count
     events = []
@@ -222,7 +253,7 @@ def run_ours(args):
     elapsed_ms = t0.elapsed_time(t1)
     kernel_ms = sum(a.elapsed_time(b) for a, b in events)
     launches = ctx.launch_count - launches_before
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop() if rank == 0 and not args.no_clocks else None
     if world > 1:
         t = torch.tensor([elapsed_ms, kernel_ms], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -232,11 +263,11 @@ def run_ours(args):
         launches = int(lt[0])
     ms_per_step = elapsed_ms / args.steps
     value = step_bytes / (ms_per_step * 1e-3) / 1e9
-    achieved = q4k_kernel_bytes * args.steps / (kernel_ms * 1e-3) / 1e9 / max(world, 1)
+    achieved = q4k_kernel_bytes * args.steps / (kernel_ms * 1e-3) / 1e9 / max(world, 1) if kernel_ms > 0 else 0.0
 
     # ---- end to end through the host-buffer entry point (activations H2D, results D2H, every call)
     e2e = None
-    if world == 1:
+    if world == 1 and not args.no_e2e:
         import numpy as np
 
         hx = {k: xs[k].cpu().numpy() for k in xs}
@@ -273,7 +304,7 @@ def run_ours(args):
                    "parallelism": f"tp{world}" if world > 1 else "single", "bytes_per_step": step_bytes, "launches_per_step": launches // max(args.steps, 1) // max(world, 1)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": hbm_peak, "unit": "GB/s", "frac": round(achieved / hbm_peak, 4), "traffic": None,
                      "kernel": "zq::gemv_kernel<Q4_K, 1 column tile> (batch 1 and 4)", "peak_kind": peak_kind, "launches": q4k_kernel_launches * args.steps,
-                     "bytes_per_launch_avg": q4k_kernel_bytes // q4k_kernel_launches},
+                     "bytes_per_launch_avg": q4k_kernel_bytes // max(q4k_kernel_launches, 1)},
         "gpu_launches": launches, "clocks": clocks, "e2e": e2e, "cpu_baseline": cpu,
     }
     print(json.dumps(line))
@@ -356,10 +387,14 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying CUDA graphs")
+    ap.add_argument("--no-clocks", action="store_true", help="do not sample clocks with nvidia-smi")
+    ap.add_argument("--only", default=None, help="restrict the sweep to one case, e.g. q4_k:5120x17408:1 (format:KxN:batch); for profiling")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -37,8 +37,10 @@ enum { ZQ_OK = 0, ZQ_ERR_SHAPE = 1, ZQ_ERR_UNSUPPORTED = 2, ZQ_ERR_CUDA = 3, ZQ_
 /* ---- context: CudaContext::new (src/backend/cuda/context.rs:248-276): one device, one compute stream. ---- */
 int zq_ctx_create(int device, zq_ctx **out, zq_error *err);
 void zq_ctx_destroy(zq_ctx *ctx);
-/* Run on a caller-owned cudaStream_t instead of the context's own stream (NULL restores the own stream). */
+/* Run on a caller-owned cudaStream_t instead of the context's own stream.  NULL is a valid handle: it is the
+ * legacy default stream.  zq_ctx_use_own_stream goes back to the stream the context created. */
 int zq_ctx_set_stream(zq_ctx *ctx, void *cuda_stream, zq_error *err);
+int zq_ctx_use_own_stream(zq_ctx *ctx, zq_error *err);
 /* Waits for the stream and reports any status word a kernel left behind (bounded waits that ran out). */
 int zq_ctx_sync(zq_ctx *ctx, zq_error *err);
 int zq_ctx_sm_count(const zq_ctx *ctx);

@@ -150,7 +150,13 @@ void zq_ctx_destroy(zq_ctx *ctx) {
 
 int zq_ctx_set_stream(zq_ctx *ctx, void *cuda_stream, zq_error *err) {
     if (!ctx) return set_error(err, ZQ_ERR_ARG, "zq_ctx_set_stream: null context");
-    ctx->stream = cuda_stream ? reinterpret_cast<cudaStream_t>(cuda_stream) : ctx->own_stream;
+    ctx->stream = reinterpret_cast<cudaStream_t>(cuda_stream);
+    return ZQ_OK;
+}
+
+int zq_ctx_use_own_stream(zq_ctx *ctx, zq_error *err) {
+    if (!ctx) return set_error(err, ZQ_ERR_ARG, "zq_ctx_use_own_stream: null context");
+    ctx->stream = ctx->own_stream;
     return ZQ_OK;
 }
 

@@ -34,6 +34,7 @@ PROTOTYPES = {
     "zq_ctx_create": (_i, [_i, C.POINTER(_vp), _err]),
     "zq_ctx_destroy": (None, [_vp]),
     "zq_ctx_set_stream": (_i, [_vp, _vp, _err]),
+    "zq_ctx_use_own_stream": (_i, [_vp, _err]),
     "zq_ctx_sync": (_i, [_vp, _err]),
     "zq_ctx_sm_count": (_i, [_vp]),
     "zq_ctx_launch_count": (C.c_uint64, [_vp]),
