@@ -12,6 +12,17 @@ from tests import helpers as H
 from tests.gpu_util import ctx, dev, host
 
 pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True, params=["resident", "staged"])
+def gemv_variant(request):
+    """Every case runs on both decode kernels: activations resident in shared memory (the default whenever
+    they fit) and per-item activation staging (the variant for large batch x K)."""
+    ctx().set_option("force_staged_gemv", 1 if request.param == "staged" else 0)
+    yield request.param
+    ctx().set_option("force_staged_gemv", 0)
+
+
 TYPES = [H.Q4_0, H.Q8_0, H.Q4_K, H.IQ4_NL]
 BOUND = 2e-3
 TIGHT = 2e-5

@@ -83,6 +83,9 @@ class B200Context:
     def sync(self):
         ffi.call("zq_ctx_sync", self.handle)
 
+    def set_option(self, key: str, value: int):
+        ffi.call("zq_ctx_set_option", self.handle, key.encode(), int(value))
+
     @property
     def sm_count(self) -> int:
         return self.lib.zq_ctx_sm_count(self.handle)

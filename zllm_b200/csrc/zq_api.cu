@@ -175,6 +175,15 @@ int zq_ctx_sync(zq_ctx *ctx, zq_error *err) {
     return ZQ_OK;
 }
 
+int zq_ctx_set_option(zq_ctx *ctx, const char *key, int value, zq_error *err) {
+    if (!ctx || !key) return set_error(err, ZQ_ERR_ARG, "zq_ctx_set_option: null argument");
+    if (!strcmp(key, "force_staged_gemv")) {
+        ctx->force_staged_gemv = value;
+        return ZQ_OK;
+    }
+    return set_error(err, ZQ_ERR_ARG, "zq_ctx_set_option: unknown option '%s'", key);
+}
+
 int zq_ctx_sm_count(const zq_ctx *ctx) { return ctx ? ctx->sm_count : 0; }
 uint64_t zq_ctx_launch_count(const zq_ctx *ctx) { return ctx ? ctx->launches.load() : 0; }
 

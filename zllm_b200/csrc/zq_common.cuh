@@ -212,6 +212,9 @@ struct zq_ctx {
     size_t pinned_bytes = 0;
     void *host_io_dev = nullptr;
     size_t host_io_bytes = 0;
+    // Diagnostics: 1 = always use the per-item activation staging GEMV (the variant for activations too large to
+    // stay resident in shared memory), so that tests can cover it at small sizes.
+    int force_staged_gemv = 0;
     std::atomic<uint64_t> launches{0};
     std::mutex mutex;
 };

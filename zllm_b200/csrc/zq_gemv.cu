@@ -22,84 +22,9 @@
 //   * Which four weights a thread feeds into MMA step s is free (a dot product does not care about the order
 //     of k), so it is chosen to make every shared-memory read a conflict-free 16-byte load of bytes the thread
 //     needs anyway; the activation staging applies the same permutation.
-#include "zq_common.cuh"
+#include "zq_gemv_frag.cuh"
 
 namespace zq {
-
-constexpr int kTileRows = 128;
-constexpr int kChunkUnits = 2;
-constexpr int kChunkCols = kChunkUnits * kUnitWeights;  // 512
-constexpr int kGemvThreads = 512;                       // 16 warps: 8 row sub-tiles x 2 units
-constexpr int kMaxGemvRows = 8;
-constexpr int kSlotFloats = kTileRows * kMaxGemvRows;   // one partial tile in the fix-up scratch
-
-template <uint32_t TYPE> struct Fmt;
-template <> struct Fmt<ZQ_Q4_K> { static constexpr int unit_bytes = 144; static constexpr int stages = 4; static constexpr bool lut = false; };
-template <> struct Fmt<ZQ_Q4_0> { static constexpr int unit_bytes = 144; static constexpr int stages = 4; static constexpr bool lut = false; };
-template <> struct Fmt<ZQ_IQ4_NL> { static constexpr int unit_bytes = 144; static constexpr int stages = 3; static constexpr bool lut = true; };
-template <> struct Fmt<ZQ_Q8_0> { static constexpr int unit_bytes = 272; static constexpr int stages = 2; static constexpr bool lut = false; };
-
-template <uint32_t TYPE, int NT> struct GemvSmem {
-    static constexpr int pitch = kChunkUnits * Fmt<TYPE>::unit_bytes;
-    static constexpr int stage_w = kTileRows * pitch;
-    static constexpr int stage_x = NT * kChunkUnits * 16 * 32 * 8;
-    static constexpr int stage_sx = NT * kChunkUnits * 32 * 4;
-    static constexpr int off_w = 0;
-    static constexpr int off_x = off_w + Fmt<TYPE>::stages * stage_w;
-    static constexpr int off_sx = off_x + Fmt<TYPE>::stages * stage_x;
-    static constexpr int off_red = off_sx + Fmt<TYPE>::stages * stage_sx;
-    static constexpr int red_bytes = 2 * kTileRows * NT * 4 * 4;
-    static constexpr int off_lut = off_red + red_bytes;
-    static constexpr int lut_bytes = Fmt<TYPE>::lut ? 256 * 32 * 4 : 0;
-    static constexpr int off_bar = off_lut + lut_bytes;
-    static constexpr int total = off_bar + 64 + 128;  // barriers + slack for 128-byte alignment of the base
-};
-
-struct GemvParams {
-    const void *x;        // [m, cols]
-    void *y;              // [m, n_out]
-    const void *residual; // [m, n_out] or null
-    float *partials;      // fix-up scratch
-    uint32_t *counters;
-    uint32_t *status;
-    int x_dtype, y_dtype;
-    int m;                // 1..8
-    int cols;             // logical K
-    int n_out;            // output features (rows of W; for gated: rows of gate == rows of up)
-    int tiles;            // ceil(n_out / rows_per_tile)
-    int chunks;           // ceil(units_per_row / kChunkUnits)
-    int chunk_words;      // kChunkUnits * unit_bytes / 4
-};
-
-// Fragment row g (0..7) -> row inside the warp's 16-row sub-tile.  Swapping the two low bits puts the two rows a
-// quarter-warp reads 2 apart, which makes the 16-byte fragment loads bank-conflict free for row pitches that
-// are 32 mod 128 bytes (288 and 544).
-__device__ __forceinline__ int frag_row(int g) { return (g & 4) | ((g & 1) << 1) | ((g >> 1) & 1); }
-
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
-    uint32_t r;
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
-    return r;
-}
-
-// Where the activation quad starting at unit element i (a multiple of 4) lands in the B-fragment staging:
-// MMA step and lane-t for the whole-quad formats.
-template <uint32_t TYPE> __device__ __forceinline__ void quad_slot(int i, int &step, int &t) {
-    if (TYPE == ZQ_Q4_K) {
-        int G = i >> 5, e = (i >> 4) & 1, ii = (i >> 2) & 3;
-        int piece = 2 * (G >> 1) + e;
-        t = piece & 3;
-        step = 8 * (piece >> 2) + 2 * ii + (G & 1);
-    } else if (TYPE == ZQ_Q8_0) {
-        int blk = i >> 5, e = (i >> 4) & 1;
-        t = (i >> 2) & 3;
-        step = 2 * blk + e;
-    } else {  // Q4_0
-        int blk = i >> 5, nib = (i >> 4) & 1;
-        t = (i >> 2) & 3;
-        step = 8 * (blk >> 2) + 2 * (blk & 3) + nib;
-    }
-}
 
 template <uint32_t TYPE, int NT, bool GATED>
 __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemvParams p) {
@@ -576,6 +501,12 @@ int launch_gemv(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const vo
         p.y = reinterpret_cast<uint8_t *>(y) + m0 * w->rows * dtype_size(y_dtype);
         p.residual = residual ? reinterpret_cast<const uint8_t *>(residual) + m0 * w->rows * dtype_size(y_dtype) : nullptr;
         int rc;
+        if (!ctx->force_staged_gemv) {
+            bool taken = false;
+            rc = launch_gemv_resident(ctx, w, w_up, p, grid, taken, err);
+            if (rc) return rc;
+            if (taken) continue;
+        }
         switch (w->type) {
         case ZQ_Q4_K: rc = launch_type<ZQ_Q4_K>(ctx, w, w_up, p, grid, err); break;
         case ZQ_Q4_0: rc = launch_type<ZQ_Q4_0>(ctx, w, w_up, p, grid, err); break;

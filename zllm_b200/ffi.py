@@ -36,6 +36,7 @@ PROTOTYPES = {
     "zq_ctx_set_stream": (_i, [_vp, _vp, _err]),
     "zq_ctx_use_own_stream": (_i, [_vp, _err]),
     "zq_ctx_sync": (_i, [_vp, _err]),
+    "zq_ctx_set_option": (_i, [_vp, C.c_char_p, _i, _err]),
     "zq_ctx_sm_count": (_i, [_vp]),
     "zq_ctx_launch_count": (C.c_uint64, [_vp]),
     "zq_weight_prepare": (_i, [_vp, _u32, _vp, _sz, _sz, _sz, C.POINTER(_vp), _err]),
