@@ -86,6 +86,18 @@ int zq_gated_silu(zq_ctx *ctx, const zq_weight *gate, const zq_weight *up, const
 /* Backend::gated_mlp / gated_mlp_add_residual (src/backend/mod.rs:474, 483): down(silu(gate x) * up x) (+ residual). */
 int zq_gated_mlp(zq_ctx *ctx, const zq_weight *gate, const zq_weight *up, const zq_weight *down, const void *dev_x, int x_dtype, size_t m, void *dev_y, int y_dtype, const void *dev_residual, zq_error *err);
 
+/* Decode linear (1..8 activation rows, y = W x) that allocates nothing.  It has no counterpart in the reference:
+ * it exists for callers that cannot allocate device memory where they run a layer (a host application that owns
+ * the allocator, a fixed-budget real-time loop, a region in which allocator calls are forbidden).  The kernel's
+ * scratch (partial tiles and arrival counters of the split-tile fix-up) lives in a fixed device array inside the
+ * library, about 1.3 MB per GPU, held from library load until process exit.  Limits: at most 8 activation rows per
+ * call, weights of at most 524 288 rows, devices of at most 160 SMs; anything beyond is rejected with an error.
+ * The first call on a device looks up the array's device address (no allocation) and should be made before any
+ * stream capture.  All calls on a device share the array: calls that overlap on the GPU (two streams, two contexts)
+ * race; calls ordered on one stream do not.  Inputs, outputs and the prepared weight are the caller's, as for
+ * zq_linear. */
+int zq_linear_noalloc(zq_ctx *ctx, const zq_weight *w, const void *dev_x, int x_dtype, size_t m, void *dev_y, int y_dtype, zq_error *err);
+
 /* Host-buffer form of zq_linear: copies x from host memory, runs, copies y back and waits.  This is what a
  * backend that keeps activations on the host between operators calls (CpuTensor in, CpuTensor out). */
 int zq_linear_host(zq_ctx *ctx, const zq_weight *w, const void *host_x, int x_dtype, size_t m, void *host_y, int y_dtype, zq_error *err);

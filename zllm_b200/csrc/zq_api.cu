@@ -324,6 +324,12 @@ int zq_gated_mlp(zq_ctx *ctx, const zq_weight *gate, const zq_weight *up, const 
     return zq_linear(ctx, down, ctx->mid, mid_dtype, m, dev_y, y_dtype, dev_residual, err);
 }
 
+int zq_linear_noalloc(zq_ctx *ctx, const zq_weight *w, const void *dev_x, int x_dtype, size_t m, void *dev_y, int y_dtype, zq_error *err) {
+    int rc = check_linear(ctx, w, dev_x, x_dtype, m, dev_y, y_dtype, err);
+    if (rc) return rc;
+    return launch_gemv_noalloc(ctx, w, dev_x, x_dtype, m, dev_y, y_dtype, err);
+}
+
 int zq_linear_host(zq_ctx *ctx, const zq_weight *w, const void *host_x, int x_dtype, size_t m, void *host_y, int y_dtype, zq_error *err) {
     if (!ctx || !w || !host_x || !host_y) return set_error(err, ZQ_ERR_ARG, "zq_linear_host: null argument");
     int rc = check_dtype(x_dtype, "linear input", err);

@@ -519,4 +519,94 @@ int launch_gemv(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const vo
     return ZQ_OK;
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------
+// Allocation-free decode entry (zq_linear_noalloc).
+//
+// Some hosts may not allocate device memory at the point where they run a layer: code running inside a
+// stream-ordered region that forbids allocator calls, a real-time loop with a fixed memory budget, or a plugin
+// whose host application owns the allocator.  For them the split-tile fix-up scratch of the decode GEMV (partial
+// tiles + per-tile arrival counters) lives in the two file-scope device arrays below instead of in memory the
+// context allocated.  Every GPU that loads the library holds these ~1.3 MB until the process exits.
+//
+// In host code the array names are host-side stand-ins, not device addresses; the device addresses are looked
+// up once per device with cudaGetSymbolAddress (with that device current) and passed to the kernel.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int kStaticMaxSms = 160;       // partial-tile slots: two per persistent CTA
+constexpr int kStaticMaxTiles = 4096;    // arrival counters: one per 128-row tile (weights up to 524 288 rows)
+static __device__ __align__(256) float g_static_partials[(size_t)kStaticMaxSms * 2 * kSlotFloats];
+static __device__ __align__(256) uint32_t g_static_counters[kStaticMaxTiles];
+
+struct StaticScratch {
+    float *partials = nullptr;
+    uint32_t *counters = nullptr;
+    bool ready = false;
+};
+static StaticScratch g_static_scratch[64];
+static std::mutex g_static_mutex;
+
+// First call on a device resolves the device addresses of the static arrays (no allocation involved).
+static int static_scratch_for(zq_ctx *ctx, StaticScratch **out, zq_error *err) {
+    if (ctx->device < 0 || ctx->device >= 64) return set_error(err, ZQ_ERR_ARG, "zq_linear_noalloc: device index %d is outside the supported 0..63", ctx->device);
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    StaticScratch &s = g_static_scratch[ctx->device];
+    if (!s.ready) {
+        int current = -1;
+        ZQ_CUDA_CHECK(cudaGetDevice(&current), err);
+        if (current != ctx->device) ZQ_CUDA_CHECK(cudaSetDevice(ctx->device), err);
+        void *pp = nullptr, *pc = nullptr;
+        cudaError_t e1 = cudaGetSymbolAddress(&pp, g_static_partials);
+        cudaError_t e2 = cudaGetSymbolAddress(&pc, g_static_counters);
+        if (current != ctx->device && current >= 0) cudaSetDevice(current);
+        if (e1 != cudaSuccess) return set_error(err, ZQ_ERR_CUDA, "cudaGetSymbolAddress(partials) failed: %s", cudaGetErrorString(e1));
+        if (e2 != cudaSuccess) return set_error(err, ZQ_ERR_CUDA, "cudaGetSymbolAddress(counters) failed: %s", cudaGetErrorString(e2));
+        s.partials = reinterpret_cast<float *>(pp);
+        s.counters = reinterpret_cast<uint32_t *>(pc);
+        s.ready = true;
+    }
+    *out = &s;
+    return ZQ_OK;
+}
+
+// y[m, n] = x[m, k] W^T for 1..8 activation rows, one launch, scratch in the static device arrays.
+int launch_gemv_noalloc(zq_ctx *ctx, const zq_weight *w, const void *x, int x_dtype, size_t m, void *y, int y_dtype, zq_error *err) {
+    if (m == 0 || m > (size_t)kMaxGemvRows) return set_error(err, ZQ_ERR_SHAPE, "zq_linear_noalloc handles 1..%d activation rows per call, got %zu", kMaxGemvRows, m);
+    if (ctx->sm_count > kStaticMaxSms) return set_error(err, ZQ_ERR_UNSUPPORTED, "zq_linear_noalloc: device has %d SMs, the static scratch is sized for %d", ctx->sm_count, kStaticMaxSms);
+    const FormatInfo f = format_info(w->type);
+    GemvParams p;
+    p.x = x;
+    p.y = y;
+    p.residual = nullptr;
+    p.status = ctx->status_dev;
+    p.x_dtype = x_dtype;
+    p.y_dtype = y_dtype;
+    p.m = (int)m;
+    p.cols = (int)w->cols;
+    p.n_out = (int)w->rows;
+    p.tiles = (int)((w->rows + kTileRows - 1) / kTileRows);
+    p.chunks = (int)((w->units_per_row + kChunkUnits - 1) / kChunkUnits);
+    p.chunk_words = kChunkUnits * f.unit_bytes / 4;
+    if (p.tiles > kStaticMaxTiles) return set_error(err, ZQ_ERR_UNSUPPORTED, "zq_linear_noalloc: weight has %zu rows; the static scratch covers at most %d rows", w->rows, kStaticMaxTiles * kTileRows);
+    StaticScratch *scratch = nullptr;
+    int rc = static_scratch_for(ctx, &scratch, err);
+    if (rc) return rc;
+    p.partials = scratch->partials;
+    p.counters = scratch->counters;
+    // the array keeps whatever the previous call (or an interrupted one) left: arrival counters must start at zero
+    ZQ_CUDA_CHECK(cudaMemsetAsync(scratch->counters, 0, (size_t)p.tiles * sizeof(uint32_t), ctx->stream), err);
+    long long total = (long long)p.tiles * p.chunks;
+    int grid = (int)(total < ctx->sm_count ? total : ctx->sm_count);
+    if (grid <= 0) return ZQ_OK;
+    bool taken = false;
+    rc = launch_gemv_resident(ctx, w, nullptr, p, grid, taken, err);
+    if (rc || taken) return rc;
+    switch (w->type) {
+    case ZQ_Q4_K: return launch_type<ZQ_Q4_K>(ctx, w, nullptr, p, grid, err);
+    case ZQ_Q4_0: return launch_type<ZQ_Q4_0>(ctx, w, nullptr, p, grid, err);
+    case ZQ_IQ4_NL: return launch_type<ZQ_IQ4_NL>(ctx, w, nullptr, p, grid, err);
+    case ZQ_Q8_0: return launch_type<ZQ_Q8_0>(ctx, w, nullptr, p, grid, err);
+    default: return set_error(err, ZQ_ERR_UNSUPPORTED, "zq_linear_noalloc: unsupported GGUF type %u", w->type);
+    }
+}
+
 }  // namespace zq
