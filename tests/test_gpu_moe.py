@@ -1,0 +1,95 @@
+"""GPU parity of the MoE layer (router, grouping, routed experts, shared expert, combine) against the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as orc
+from tests import helpers as H
+from tests.gpu_util import ctx, dev, host
+
+pytestmark = pytest.mark.gpu
+BOUND = 2e-3
+
+
+def _experts(tensor_type, n, hidden, inter, seed):
+    gates = [H.random_weight(tensor_type, inter, hidden, seed=seed + 3 * e) for e in range(n)]
+    ups = [H.random_weight(tensor_type, inter, hidden, seed=seed + 3 * e + 1) for e in range(n)]
+    downs = [H.random_weight(tensor_type, hidden, inter, seed=seed + 3 * e + 2, std=0.05) for e in range(n)]
+    return gates, ups, downs
+
+
+@pytest.mark.parametrize("m,experts,top_k,hidden", [(1, 8, 2, 512), (5, 16, 4, 256), (64, 256, 8, 512), (33, 12, 3, 1024)])
+@pytest.mark.parametrize("normalize", [True, False])
+def test_router_matches_cpu_softmax_topk(m, experts, top_k, hidden, normalize):
+    """src/moe/routing.rs:25-39 through the device router (src/kernel/cuda/routing.rs:15-62)."""
+    from zllm_b200.backend import moe_route
+
+    rng = np.random.default_rng(m + experts)
+    x = rng.standard_normal((m, hidden)).astype(np.float32)
+    router = (rng.standard_normal((experts, hidden)) / np.sqrt(hidden)).astype(np.float32)
+    ids, w = moe_route(ctx(), dev(x), dev(router), top_k, 1.5, normalize)
+    ctx().sync()
+    want_ids, want_w = orc.moe_route_softmax(x, router, top_k, 1.5, normalize)
+    got_ids = ids.cpu().numpy().astype(np.uint32)
+    assert np.array_equal(got_ids, want_ids)
+    np.testing.assert_allclose(w.cpu().numpy(), want_w, rtol=2e-5, atol=1e-7)
+
+
+def test_router_breaks_ties_by_lower_expert_id():
+    from zllm_b200.backend import moe_route
+
+    hidden, experts = 64, 6
+    x = np.ones((1, hidden), dtype=np.float32)
+    router = np.zeros((experts, hidden), dtype=np.float32)
+    router[1] = router[3] = router[4] = 0.5   # three equal logits
+    router[0] = 0.25
+    ids, _ = moe_route(ctx(), dev(x), dev(router), 2, 1.0, True)
+    ctx().sync()
+    assert list(ids.cpu().numpy()[0]) == [1, 3]
+
+
+@pytest.mark.parametrize("tensor_type", [H.Q4_K, H.Q8_0])
+@pytest.mark.parametrize("m", [1, 6, 48])
+@pytest.mark.parametrize("with_shared", [False, True])
+def test_moe_forward_matches_cpu_path(tensor_type, m, with_shared):
+    """Routed + shared experts + residual against the oracle's moe_forward (decode and prefill orchestration:
+    experts with few routed tokens run the decode kernel, experts with more than 16 the tensor-core GEMM)."""
+    from zllm_b200.backend import MoeExperts, moe_forward, moe_route
+
+    n_exp, top_k, hidden, inter = 8, 2, 512, 256
+    gates, ups, downs = _experts(tensor_type, n_exp, hidden, inter, seed=100)
+    rng = np.random.default_rng(7 + m)
+    x = rng.standard_normal((m, hidden)).astype(np.float32)
+    router = (rng.standard_normal((n_exp, hidden)) / np.sqrt(hidden)).astype(np.float32)
+    residual = rng.standard_normal((m, hidden)).astype(np.float32)
+    c = ctx()
+    wg = [c.prepare_weight(tensor_type, g, inter, hidden) for g in gates]
+    wu = [c.prepare_weight(tensor_type, u, inter, hidden) for u in ups]
+    wd = [c.prepare_weight(tensor_type, d, hidden, inter) for d in downs]
+    table = MoeExperts(c, wg, wu, wd)
+    shared_np = shared_dev = None
+    if with_shared:
+        sg, su = H.random_weight(tensor_type, inter, hidden, seed=900), H.random_weight(tensor_type, inter, hidden, seed=901)
+        sd = H.random_weight(tensor_type, hidden, inter, seed=902, std=0.05)
+        shared_np = [(tensor_type, sg, inter, hidden), (tensor_type, su, inter, hidden), (tensor_type, sd, hidden, inter)]
+        shared_dev = (c.prepare_weight(tensor_type, sg, inter, hidden), c.prepare_weight(tensor_type, su, inter, hidden), c.prepare_weight(tensor_type, sd, hidden, inter))
+    xd = dev(x)
+    ids, w = moe_route(c, xd, dev(router), top_k, 1.0, True)
+    got = host(moe_forward(c, table, xd, ids, w, shared=shared_dev, residual=dev(residual)))
+    ids_np, w_np = ids.cpu().numpy().astype(np.uint32), w.cpu().numpy()
+    want = orc.moe_forward([(tensor_type, g, inter, hidden) for g in gates], [(tensor_type, u, inter, hidden) for u in ups], [(tensor_type, d, hidden, inter) for d in downs], x, ids_np, w_np,
+                           shared=shared_np, residual=residual)
+    assert H.max_rel_error(got, want) <= BOUND
+
+
+def test_moe_forward_rejects_bad_expert_ids():
+    from zllm_b200 import ffi
+    from zllm_b200.backend import MoeExperts, moe_forward
+
+    n_exp, hidden, inter = 2, 256, 256
+    gates, ups, downs = _experts(H.Q4_K, n_exp, hidden, inter, seed=300)
+    c = ctx()
+    table = MoeExperts(c, [c.prepare_weight(H.Q4_K, g, inter, hidden) for g in gates], [c.prepare_weight(H.Q4_K, u, inter, hidden) for u in ups], [c.prepare_weight(H.Q4_K, d, hidden, inter) for d in downs])
+    x = dev(np.zeros((1, hidden), dtype=np.float32))
+    with pytest.raises(ffi.ZqFailure):
+        moe_forward(c, table, x, torch.tensor([[0, 5]], dtype=torch.int32, device="cuda"), torch.tensor([[0.5, 0.5]], device="cuda"))

@@ -209,3 +209,55 @@ class B200Context:
         m = x_host.size // w.cols
         ffi.call("zq_linear_host", self.handle, w.handle, C.c_void_p(x_host.ctypes.data), dt[x_host.dtype], m, C.c_void_p(y_host.ctypes.data), dt[y_host.dtype])
         return y_host
+
+
+class MoeExperts:
+    """Resident expert table (replaces ``CudaMoeState``'s cache when every expert fits in HBM,
+    src/backend/cuda/expert.rs:284-570).  Keeps the weights alive for as long as the table."""
+
+    def __init__(self, ctx: B200Context, gate: Sequence[Weight], up: Sequence[Weight], down: Sequence[Weight]):
+        self.ctx, self.gate, self.up, self.down = ctx, list(gate), list(up), list(down)
+        n = len(self.gate)
+        ga = (C.c_void_p * n)(*[w.handle for w in self.gate])
+        ua = (C.c_void_p * n)(*[w.handle for w in self.up])
+        da = (C.c_void_p * n)(*[w.handle for w in self.down])
+        out = C.c_void_p()
+        ffi.call("zq_moe_experts_create", ctx.handle, ga, ua, da, n, C.byref(out))
+        self.handle = out
+
+    def __del__(self):
+        try:
+            if self.handle:
+                ffi.load().zq_moe_experts_destroy(self.handle)
+                self.handle = None
+        except Exception:
+            pass
+
+
+def moe_route(ctx: B200Context, x: torch.Tensor, router: torch.Tensor, top_k: int, scaling_factor: float = 1.0, normalize_selected: bool = True, bias: Optional[torch.Tensor] = None):
+    """``moe_route_softmax_topk_device_f32`` (src/kernel/cuda/routing.rs:167): returns ``(ids [m, k] int32, weights [m, k] f32)`` on the device."""
+    x = x.contiguous()
+    router = router.contiguous().float()
+    m, hidden = x.shape
+    experts = router.shape[0]
+    ids = torch.empty((m, top_k), dtype=torch.int32, device=x.device)
+    w = torch.empty((m, top_k), dtype=torch.float32, device=x.device)
+    ffi.call("zq_moe_route_softmax_topk", ctx.handle, _ptr(x), _dt(x), m, hidden, _ptr(router), _ptr(bias), experts, top_k, float(scaling_factor), int(normalize_selected), _ptr(ids), _ptr(w))
+    return ids, w
+
+
+def moe_forward(ctx: B200Context, experts: MoeExperts, x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, shared=None, residual: Optional[torch.Tensor] = None, out_dtype=None) -> torch.Tensor:
+    """Routed experts (+ shared expert, + residual): ``prefill_resident_routed_experts_add`` / ``decode_routed_experts``
+    (src/backend/mod.rs:1921-1960, 2012-2024).  ``shared`` is ``(gate, up, down)`` or None."""
+    x = x.contiguous()
+    m, hidden = x.shape
+    out_dtype = out_dtype or x.dtype
+    y = torch.empty((m, hidden), dtype=out_dtype, device=x.device)
+    ids = ids.contiguous()
+    weights = weights.contiguous().float()
+    top_k = ids.numel() // m
+    sg, su, sd = (w.handle for w in shared) if shared is not None else (None, None, None)
+    if residual is not None:
+        residual = residual.contiguous()
+    ffi.call("zq_moe_forward", ctx.handle, experts.handle, sg, su, sd, _ptr(x), _dt(x), m, _ptr(ids), _ptr(weights), top_k, _ptr(y), _DTYPES[out_dtype], _ptr(residual))
+    return y

@@ -141,6 +141,7 @@ void zq_ctx_destroy(zq_ctx *ctx) {
     if (ctx->gemv_counters) cudaFree(ctx->gemv_counters);
     if (ctx->workspace) cudaFree(ctx->workspace);
     if (ctx->mid) cudaFree(ctx->mid);
+    if (ctx->moe_ws) cudaFree(ctx->moe_ws);
     if (ctx->status_host) cudaFreeHost(ctx->status_host);
     if (ctx->pinned) cudaFreeHost(ctx->pinned);
     if (ctx->host_io_dev) cudaFree(ctx->host_io_dev);

@@ -201,6 +201,9 @@ struct zq_ctx {
     // General workspace (grows on demand, never shrinks): dequantised operands of the prefill GEMM, MoE buffers.
     void *workspace = nullptr;
     size_t workspace_bytes = 0;
+    // MoE buffers: routing tables, gathered rows, per-route activations and outputs (grows on demand).
+    void *moe_ws = nullptr;
+    size_t moe_ws_bytes = 0;
     // Activated intermediate [m, I] of gated_mlp (grows on demand).
     void *mid = nullptr;
     size_t mid_bytes = 0;

@@ -1,23 +1,296 @@
-// MoE entry points (router, resident expert table, routed forward).
+// MoE entry points: router (logits + softmax top-k), resident expert table, routed forward.
+//
+// Reference behaviour restated here:
+//   router logits + softmax top-k      src/kernel/cuda/routing.rs:15-62, 167-210; src/moe/routing.rs:25-39
+//                                      (ordering: logit descending, ties to the lower expert id)
+//   token-major stable grouping        src/moe/routing.rs:136-156
+//   expert = gate/up + SiLU, then down src/kernel/cpu/moe.rs:122-138
+//   weighted combine, per token in     src/backend/cpu/moe.rs:107-141 (no atomics; fixed order)
+//     ascending expert order
+//   shared expert added to the sum     src/moe/topk_moe.rs:84-104
+//
+// This version keeps the reference CUDA backend's orchestration (router ids come back to the host,
+// src/kernel/cuda/routing.rs:208; the host groups routes and issues the expert kernels,
+// src/backend/cuda/expert.rs:787-917): routing and combine run on the device, the per-expert projections are
+// calls into the decode GEMV / prefill GEMM of this library over gathered token rows.
+#include <algorithm>
+
 #include "zq_common.cuh"
 
 using namespace zq;
 
 struct zq_moe_experts {
     zq_ctx *ctx = nullptr;
-    size_t num_experts = 0;
+    size_t num_experts = 0, hidden = 0, inter = 0;
     std::vector<const zq_weight *> gate, up, down;
 };
 
+namespace zq {
+
+constexpr int kRouterTokens = 4;     // tokens per CTA
+constexpr int kRouterThreads = 256;
+
+// logits[t, e] = x[t] . router[e] (+ bias[e]) in f32, then softmax top-k per token.
+// One CTA per 4 tokens; each warp owns experts e = warp, warp + 8, ...; lanes stride the hidden dimension.
+__global__ void __launch_bounds__(kRouterThreads) router_topk_kernel(const void *__restrict__ x, int x_dtype, int m, int hidden, const float *__restrict__ router, const float *__restrict__ bias, int num_experts, int top_k,
+                                                                      float scaling, int normalize_selected, uint32_t *__restrict__ ids, float *__restrict__ weights) {
+    extern __shared__ float rsm[];
+    float *xs = rsm;                                 // [kRouterTokens][hidden]
+    float *logits = rsm + (size_t)kRouterTokens * hidden;  // [kRouterTokens][num_experts]
+    const int tok0 = blockIdx.x * kRouterTokens;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int i = threadIdx.x; i < kRouterTokens * hidden; i += kRouterThreads) {
+        int t = i / hidden, c = i - t * hidden;
+        xs[i] = (tok0 + t < m) ? load_as_f32(x, x_dtype, (size_t)(tok0 + t) * hidden + c) : 0.f;
+    }
+    __syncthreads();
+    for (int e = warp; e < num_experts; e += kRouterThreads / 32) {
+        const float *w = router + (size_t)e * hidden;
+        float acc[kRouterTokens];
+#pragma unroll
+        for (int t = 0; t < kRouterTokens; ++t) acc[t] = 0.f;
+        for (int c = lane; c < hidden; c += 32) {
+            const float wv = w[c];
+#pragma unroll
+            for (int t = 0; t < kRouterTokens; ++t) acc[t] = fmaf(xs[t * hidden + c], wv, acc[t]);
+        }
+#pragma unroll
+        for (int t = 0; t < kRouterTokens; ++t) {
+            float v = acc[t];
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0) logits[t * num_experts + e] = v + (bias ? bias[e] : 0.f);
+        }
+    }
+    __syncthreads();
+    // top-k: warp t handles token t; repeated arg-max with ties to the lower expert id
+    if (warp < kRouterTokens && tok0 + warp < m) {
+        float *l = logits + warp * num_experts;
+        float maximum = -INFINITY;
+        for (int e = lane; e < num_experts; e += 32) maximum = fmaxf(maximum, l[e]);
+        for (int o = 16; o > 0; o >>= 1) maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, o));
+        float denom_all = 0.f;
+        if (!normalize_selected) {
+            for (int e = lane; e < num_experts; e += 32) denom_all += expf(l[e] - maximum);
+            for (int o = 16; o > 0; o >>= 1) denom_all += __shfl_xor_sync(0xffffffffu, denom_all, o);
+        }
+        float sel_logit = 0.f, denom_sel = 0.f;  // lane j keeps the j-th selected logit (top_k <= 32)
+        uint32_t sel_id = 0;
+        for (int slot = 0; slot < top_k; ++slot) {
+            float best = -INFINITY;
+            int best_e = 0x7fffffff;
+            for (int e = lane; e < num_experts; e += 32) {
+                float v = l[e];
+                if (v > best || (v == best && e < best_e)) { best = v; best_e = e; }
+            }
+            for (int o = 16; o > 0; o >>= 1) {
+                float ov = __shfl_xor_sync(0xffffffffu, best, o);
+                int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+                if (ov > best || (ov == best && oe < best_e)) { best = ov; best_e = oe; }
+            }
+            if (lane == slot) { sel_logit = best; sel_id = (uint32_t)best_e; }
+            if (lane == 0) l[best_e] = -INFINITY;
+            __syncwarp();
+            denom_sel += expf(best - maximum);
+        }
+        const float denom = normalize_selected ? denom_sel : denom_all;
+        if (lane < top_k) {
+            const size_t o = (size_t)(tok0 + warp) * top_k + lane;
+            ids[o] = sel_id;
+            weights[o] = expf(sel_logit - maximum) / denom * scaling;
+        }
+    }
+}
+
+__global__ void gather_rows_kernel(const void *__restrict__ x, int dtype, const uint32_t *__restrict__ tokens, size_t n_rows, int hidden, void *__restrict__ out) {
+    const size_t esz = dtype_size(dtype);
+    const size_t row_bytes = (size_t)hidden * esz;  // multiple of 16: hidden is a multiple of 32
+    const size_t vec_per_row = row_bytes / 16;
+    const size_t total = n_rows * vec_per_row;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        size_t r = i / vec_per_row, v = i - r * vec_per_row;
+        reinterpret_cast<uint4 *>(out)[i] = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint8_t *>(x) + (size_t)tokens[r] * row_bytes)[v];
+    }
+}
+
+// y[t] = ((sum_j w[t,j] * out[slot[t,j]]) + shared[t]) + residual[t]; slots of a token are in ascending expert order.
+__global__ void combine_kernel(const float *__restrict__ routed, const uint32_t *__restrict__ slots, const float *__restrict__ w, int top_k, const float *__restrict__ shared, const void *__restrict__ residual, void *__restrict__ y,
+                               int y_dtype, size_t m, int hidden) {
+    const size_t total = m * (size_t)hidden;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        size_t t = i / hidden;
+        int c = (int)(i - t * hidden);
+        float acc = 0.f;
+        for (int j = 0; j < top_k; ++j) acc = __fadd_rn(acc, __fmul_rn(routed[(size_t)slots[t * top_k + j] * hidden + c], w[t * top_k + j]));
+        if (shared) acc = __fadd_rn(acc, shared[i]);
+        if (residual) acc = __fadd_rn(acc, load_as_f32(residual, y_dtype, i));
+        store_from_f32(y, y_dtype, i, acc);
+    }
+}
+
+static unsigned grid_for(zq_ctx *ctx, size_t total, int threads) {
+    size_t blocks = (total + threads - 1) / threads;
+    size_t cap = (size_t)ctx->sm_count * 32;
+    if (blocks > cap) blocks = cap;
+    if (blocks == 0) blocks = 1;
+    return (unsigned)blocks;
+}
+
+static int ensure_moe_ws(zq_ctx *ctx, size_t bytes, zq_error *err) {
+    if (bytes <= ctx->moe_ws_bytes) return ZQ_OK;
+    ZQ_CUDA_CHECK(cudaStreamSynchronize(ctx->stream), err);
+    if (ctx->moe_ws) cudaFree(ctx->moe_ws);
+    ctx->moe_ws = nullptr;
+    ctx->moe_ws_bytes = 0;
+    size_t rounded = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+    ZQ_CUDA_CHECK(cudaMalloc(&ctx->moe_ws, rounded), err);
+    ctx->moe_ws_bytes = rounded;
+    return ZQ_OK;
+}
+
+}  // namespace zq
+
 extern "C" {
-int zq_moe_route_softmax_topk(zq_ctx *, const void *, int, size_t, size_t, const float *, const float *, size_t, size_t, float, int, uint32_t *, float *, zq_error *err) {
-    return set_error(err, ZQ_ERR_UNSUPPORTED, "zq_moe_route_softmax_topk: not built yet");
+
+int zq_moe_route_softmax_topk(zq_ctx *ctx, const void *dev_x, int x_dtype, size_t m, size_t hidden, const float *dev_router_f32, const float *dev_bias_f32, size_t num_experts, size_t top_k, float scaling_factor, int normalize_selected,
+                              uint32_t *dev_ids, float *dev_weights, zq_error *err) {
+    if (!ctx || !dev_x || !dev_router_f32 || !dev_ids || !dev_weights) return set_error(err, ZQ_ERR_ARG, "zq_moe_route_softmax_topk: null argument");
+    // same limits as the reference's device router (src/kernel/cuda/routing.rs:177): experts <= 1024, 0 < top_k <= experts
+    if (num_experts == 0 || num_experts > 1024 || top_k == 0 || top_k > num_experts || top_k > 32) return set_error(err, ZQ_ERR_SHAPE, "softmax router: experts=%zu top_k=%zu outside the supported range (experts <= 1024, top_k <= 32)", num_experts, top_k);
+    if (!(scaling_factor == scaling_factor) || scaling_factor > 3.0e38f || scaling_factor < -3.0e38f) return set_error(err, ZQ_ERR_ARG, "softmax router: scaling factor is not finite");
+    if (m == 0 || hidden == 0) return set_error(err, ZQ_ERR_SHAPE, "softmax router: empty input");
+    size_t smem = ((size_t)kRouterTokens * hidden + (size_t)kRouterTokens * num_experts) * sizeof(float);
+    if (smem > 200 * 1024) return set_error(err, ZQ_ERR_UNSUPPORTED, "softmax router: hidden=%zu does not fit the router kernel's shared memory", hidden);
+    static bool configured[64] = {};
+    if (!configured[ctx->device & 63]) {
+        ZQ_CUDA_CHECK(cudaFuncSetAttribute(router_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), err);
+        configured[ctx->device & 63] = true;
+    }
+    unsigned grid = (unsigned)((m + kRouterTokens - 1) / kRouterTokens);
+    router_topk_kernel<<<grid, kRouterThreads, smem, ctx->stream>>>(dev_x, x_dtype, (int)m, (int)hidden, dev_router_f32, dev_bias_f32, (int)num_experts, (int)top_k, scaling_factor, normalize_selected, dev_ids, dev_weights);
+    ctx->launches++;
+    ZQ_CUDA_CHECK(cudaGetLastError(), err);
+    return ZQ_OK;
 }
-int zq_moe_experts_create(zq_ctx *, const zq_weight *const *, const zq_weight *const *, const zq_weight *const *, size_t, zq_moe_experts **, zq_error *err) {
-    return set_error(err, ZQ_ERR_UNSUPPORTED, "zq_moe_experts_create: not built yet");
+
+int zq_moe_experts_create(zq_ctx *ctx, const zq_weight *const *gate, const zq_weight *const *up, const zq_weight *const *down, size_t num_experts, zq_moe_experts **out, zq_error *err) {
+    if (!ctx || !gate || !up || !down || !out || num_experts == 0) return set_error(err, ZQ_ERR_ARG, "zq_moe_experts_create: null or empty argument");
+    zq_moe_experts *t = new zq_moe_experts();
+    t->ctx = ctx;
+    t->num_experts = num_experts;
+    for (size_t e = 0; e < num_experts; ++e) {
+        const zq_weight *g = gate[e], *u = up[e], *d = down[e];
+        if (!g || !u || !d || g->ctx != ctx || u->ctx != ctx || d->ctx != ctx) {
+            delete t;
+            return set_error(err, ZQ_ERR_ARG, "expert %zu: missing weight or weight from another context", e);
+        }
+        if (e == 0) {
+            t->hidden = g->cols;
+            t->inter = g->rows;
+        }
+        if (g->cols != t->hidden || g->rows != t->inter || u->cols != t->hidden || u->rows != t->inter || d->cols != t->inter || d->rows != t->hidden || g->type != u->type) {
+            delete t;
+            return set_error(err, ZQ_ERR_SHAPE, "expert %zu: gate [%zu,%zu] up [%zu,%zu] down [%zu,%zu] do not form hidden=%zu intermediate=%zu", e, g->rows, g->cols, u->rows, u->cols, d->rows, d->cols, t->hidden, t->inter);
+        }
+        t->gate.push_back(g);
+        t->up.push_back(u);
+        t->down.push_back(d);
+    }
+    *out = t;
+    return ZQ_OK;
 }
+
 void zq_moe_experts_destroy(zq_moe_experts *experts) { delete experts; }
-int zq_moe_forward(zq_ctx *, const zq_moe_experts *, const zq_weight *, const zq_weight *, const zq_weight *, const void *, int, size_t, const uint32_t *, const float *, size_t, void *, int, const void *, zq_error *err) {
-    return set_error(err, ZQ_ERR_UNSUPPORTED, "zq_moe_forward: not built yet");
+
+int zq_moe_forward(zq_ctx *ctx, const zq_moe_experts *experts, const zq_weight *shared_gate, const zq_weight *shared_up, const zq_weight *shared_down, const void *dev_x, int x_dtype, size_t m, const uint32_t *dev_ids,
+                   const float *dev_weights, size_t top_k, void *dev_y, int y_dtype, const void *dev_residual, zq_error *err) {
+    if (!ctx || !experts || !dev_x || !dev_ids || !dev_weights || !dev_y) return set_error(err, ZQ_ERR_ARG, "zq_moe_forward: null argument");
+    if (experts->ctx != ctx) return set_error(err, ZQ_ERR_ARG, "zq_moe_forward: expert table belongs to another context");
+    if (m == 0 || top_k == 0) return set_error(err, ZQ_ERR_SHAPE, "zq_moe_forward: empty routing (rows=%zu top_k=%zu)", m, top_k);
+    const bool has_shared = shared_gate || shared_up || shared_down;
+    if (has_shared && !(shared_gate && shared_up && shared_down)) return set_error(err, ZQ_ERR_ARG, "zq_moe_forward: shared expert needs gate, up and down");
+    const size_t E = experts->num_experts, H = experts->hidden, I = experts->inter, routes = m * top_k;
+    if (has_shared && (shared_gate->cols != H || shared_down->rows != H || shared_down->cols != shared_gate->rows)) return set_error(err, ZQ_ERR_SHAPE, "zq_moe_forward: shared expert shapes do not match hidden=%zu", H);
+
+    // ---- routing back to the host, token-major stable grouping (src/moe/routing.rs:136-156)
+    std::vector<uint32_t> ids(routes);
+    std::vector<float> wts(routes);
+    ZQ_CUDA_CHECK(cudaMemcpyAsync(ids.data(), dev_ids, routes * sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream), err);
+    ZQ_CUDA_CHECK(cudaMemcpyAsync(wts.data(), dev_weights, routes * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream), err);
+    ZQ_CUDA_CHECK(cudaStreamSynchronize(ctx->stream), err);
+    std::vector<uint32_t> offsets(E + 1, 0);
+    for (size_t r = 0; r < routes; ++r) {
+        if (ids[r] >= E) return set_error(err, ZQ_ERR_SHAPE, "router returned expert %u, table holds %zu", ids[r], E);
+        offsets[ids[r] + 1]++;
+    }
+    for (size_t e = 0; e < E; ++e) offsets[e + 1] += offsets[e];
+    std::vector<uint32_t> cursor(offsets.begin(), offsets.end() - 1);
+    std::vector<uint32_t> slot_token(routes), token_slots(routes);
+    std::vector<float> token_w(routes);
+    std::vector<uint32_t> fill(m, 0);
+    // visiting routes token-major and experts ascending keeps, per token, its slots in ascending expert order
+    std::vector<std::pair<uint32_t, uint32_t>> order(top_k);
+    for (size_t t = 0; t < m; ++t) {
+        for (size_t j = 0; j < top_k; ++j) {
+            uint32_t e = ids[t * top_k + j];
+            uint32_t slot = cursor[e]++;
+            slot_token[slot] = (uint32_t)t;
+            order[j] = {e, (uint32_t)j};
+            token_slots[t * top_k + j] = slot;
+        }
+        // per-token combine order: ascending expert id (src/backend/cpu/moe.rs:107-141); stable for repeated ids
+        std::stable_sort(order.begin(), order.end(), [](const std::pair<uint32_t, uint32_t> &a, const std::pair<uint32_t, uint32_t> &b) { return a.first < b.first; });
+        uint32_t tmp_s[64];
+        float tmp_w[64];
+        if (top_k > 64) return set_error(err, ZQ_ERR_SHAPE, "zq_moe_forward: top_k=%zu above 64", top_k);
+        for (size_t j = 0; j < top_k; ++j) {
+            tmp_s[j] = token_slots[t * top_k + order[j].second];
+            tmp_w[j] = wts[t * top_k + order[j].second];
+        }
+        for (size_t j = 0; j < top_k; ++j) {
+            token_slots[t * top_k + j] = tmp_s[j];
+            token_w[t * top_k + j] = tmp_w[j];
+        }
+    }
+
+    // ---- workspace: [slot_token | token_slots | token_w | gathered x | activated | routed out | shared out]
+    const size_t esz = dtype_size(x_dtype);
+    auto al = [](size_t v) { return (v + 255) & ~size_t(255); };
+    const size_t o_slot_token = 0, o_token_slots = o_slot_token + al(routes * 4), o_token_w = o_token_slots + al(routes * 4);
+    const size_t o_xs = o_token_w + al(routes * 4), o_act = o_xs + al(routes * H * esz), o_out = o_act + al(routes * I * 4);
+    const size_t o_shared = o_out + al(routes * H * 4), total = o_shared + (has_shared ? al(m * H * 4) : 0);
+    int rc = ensure_moe_ws(ctx, total, err);
+    if (rc) return rc;
+    uint8_t *ws = reinterpret_cast<uint8_t *>(ctx->moe_ws);
+    uint32_t *d_slot_token = reinterpret_cast<uint32_t *>(ws + o_slot_token), *d_token_slots = reinterpret_cast<uint32_t *>(ws + o_token_slots);
+    float *d_token_w = reinterpret_cast<float *>(ws + o_token_w);
+    uint8_t *d_xs = ws + o_xs;
+    float *d_act = reinterpret_cast<float *>(ws + o_act), *d_out = reinterpret_cast<float *>(ws + o_out), *d_shared = has_shared ? reinterpret_cast<float *>(ws + o_shared) : nullptr;
+    ZQ_CUDA_CHECK(cudaMemcpyAsync(d_slot_token, slot_token.data(), routes * 4, cudaMemcpyHostToDevice, ctx->stream), err);
+    ZQ_CUDA_CHECK(cudaMemcpyAsync(d_token_slots, token_slots.data(), routes * 4, cudaMemcpyHostToDevice, ctx->stream), err);
+    ZQ_CUDA_CHECK(cudaMemcpyAsync(d_token_w, token_w.data(), routes * 4, cudaMemcpyHostToDevice, ctx->stream), err);
+    ZQ_CUDA_CHECK(cudaStreamSynchronize(ctx->stream), err);  // the host vectors go out of scope at return
+
+    gather_rows_kernel<<<grid_for(ctx, routes * (H * esz / 16), 256), 256, 0, ctx->stream>>>(dev_x, x_dtype, d_slot_token, routes, (int)H, d_xs);
+    ctx->launches++;
+    ZQ_CUDA_CHECK(cudaGetLastError(), err);
+
+    // ---- experts, ascending id (src/moe/routing.rs:180-213: gather rows, expert batch, weighted scatter)
+    for (size_t e = 0; e < E; ++e) {
+        const size_t first = offsets[e], count = offsets[e + 1] - offsets[e];
+        if (!count) continue;
+        rc = zq_gated_silu(ctx, experts->gate[e], experts->up[e], d_xs + first * H * esz, x_dtype, count, d_act + first * I, ZQ_F32, err);
+        if (rc) return rc;
+        rc = zq_linear(ctx, experts->down[e], d_act + first * I, ZQ_F32, count, d_out + first * H, ZQ_F32, nullptr, err);
+        if (rc) return rc;
+    }
+    if (has_shared) {
+        rc = zq_gated_mlp(ctx, shared_gate, shared_up, shared_down, dev_x, x_dtype, m, d_shared, ZQ_F32, nullptr, err);
+        if (rc) return rc;
+    }
+    combine_kernel<<<grid_for(ctx, m * H, 256), 256, 0, ctx->stream>>>(d_out, d_token_slots, d_token_w, (int)top_k, d_shared, dev_residual, dev_y, y_dtype, m, (int)H);
+    ctx->launches++;
+    ZQ_CUDA_CHECK(cudaGetLastError(), err);
+    return ZQ_OK;
 }
-}
+
+}  // extern "C"
