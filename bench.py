@@ -97,28 +97,12 @@ class ClockSampler:
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(smax) if smax else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def shard_plan(k: int, n: int, world: int, rank: int, block: int = 256):
-    """Tensor-parallel shard of W[n, k]: up-projections (n >= k) by output rows, down-projections (n < k) by
-    256-aligned input columns (K-quant super-blocks cannot be cut, src/backend/rocm/expert.rs:182-207)."""
-    if world == 1:
-        return "none", (0, n), (0, k)
-    if n >= k:
-        per = -(-n // world)
-        per = -(-per // 128) * 128
-        lo, hi = min(n, rank * per), min(n, (rank + 1) * per)
-        return "column", (lo, hi), (0, k)
-    units = k // block
-    base, extra = divmod(units, world)
-    lo = rank * base + min(rank, extra)
-    hi = lo + base + (1 if rank < extra else 0)
-    return "row", (0, n), (lo * block, hi * block)
-
-
 def run_ours(args):
     import torch
     import torch.distributed as dist
 
     from zllm_b200.backend import B200Context
+    from zllm_b200.dist import shard_plan
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -201,13 +185,17 @@ def run_ours(args):
     graphs = []
     if not args.no_graph:
         side = torch.cuda.Stream(device=device)
-        for m, fmt, members in blocks:
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=side):
-                ctx.set_stream(torch.cuda.current_stream(device).cuda_stream)
-                for mm, case in members:
-                    launch(mm, case)
-            graphs.append(g)
+        try:
+            for m, fmt, members in blocks:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    ctx.set_stream(torch.cuda.current_stream(device).cuda_stream)
+                    for mm, case in members:
+                        launch(mm, case)
+                graphs.append(g)
+        except Exception as exc:  # e.g. a collective that cannot be captured: fall back to host launches
+            graphs = []
+            sys.stderr.write(f"bench: graph capture failed ({exc}); launching from the host\n")
         ctx.set_stream(torch.cuda.current_stream(device).cuda_stream)
 
     def step(events=None):
@@ -292,6 +280,14 @@ def run_ours(args):
             "ms_per_step": round((h1 - h0) / e2e_steps * 1e3, 3), "api": "zq_linear_host",
         }
 
+    # free the sweep's weights before the larger side measurements
+    extras = {}
+    if not args.no_extras:
+        del graphs, cases, plan, blocks
+        torch.cuda.empty_cache()
+        if world == 1:
+            extras["prefill_gemm"] = bench_prefill(ctx, device, args)
+        extras["moe"] = bench_moe(ctx, device, args, world, rank)
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -307,9 +303,143 @@ def run_ours(args):
                      "bytes_per_launch_avg": q4k_kernel_bytes // max(q4k_kernel_launches, 1)},
         "gpu_launches": launches, "clocks": clocks, "e2e": e2e, "cpu_baseline": cpu,
     }
+    line.update(extras)
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def _time_ms(fn, reps):
+    import torch
+
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+def bench_prefill(ctx, device, args):
+    """configs[2]: Q4_K 5120->17408 and 17408->5120, bf16 activations and outputs, f32 accumulate, a stack of
+    64 distinct (up, down) pairs (6.4 GB packed) timed end to end.  Every layer takes fixed N(0,1) inputs (chaining
+    un-normalised outputs would overflow), so the stack is 128 independent GEMMs over 128 distinct weights."""
+    import ctypes as C
+
+    import torch
+
+    from zllm_b200 import ffi
+
+    layers = args.stack_layers
+    k, n = 5120, 17408
+    gen = torch.Generator(device=device)
+    ups, downs = [], []
+    for l in range(layers):
+        for lst, (rows, cols) in ((ups, (n, k)), (downs, (k, n))):
+            gen.manual_seed(5000 + 2 * l + (lst is downs))
+            full = torch.randn((rows, cols), generator=gen, device=device, dtype=torch.float32) * 0.02
+            lst.append(ctx.prepare_weight(Q4_K, ctx.quantize(Q4_K, full), rows, cols))
+            del full
+    _, tensor_peak, kind = read_peaks()
+    sustained = tensor_peak
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        sustained = float(json.load(open(path)).get("bf16_tflops_sustained", tensor_peak))
+    out = {"unit": "TFLOP/s", "stack_layers": layers, "weights": "Q4_K 5120x17408 + 17408x5120 per layer", "activations": "bf16 in, bf16 out, f32 accumulate", "operands": "f16"}
+    launches0 = ctx.launch_count
+    for m in (512, 4096, 16384):
+        gen.manual_seed(31 + m)
+        x = torch.randn((m, k), generator=gen, device=device, dtype=torch.float32).to(torch.bfloat16)
+        h0 = torch.randn((m, n), generator=gen, device=device, dtype=torch.float32).to(torch.bfloat16)
+        h = torch.empty((m, n), device=device, dtype=torch.bfloat16)
+        y = torch.empty((m, k), device=device, dtype=torch.bfloat16)
+
+        def stack():
+            for l in range(layers):
+                ffi.call("zq_linear", ctx.handle, ups[l].handle, C.c_void_p(x.data_ptr()), ffi.BF16, m, C.c_void_p(h.data_ptr()), ffi.BF16, None)
+                ffi.call("zq_linear", ctx.handle, downs[l].handle, C.c_void_p(h0.data_ptr()), ffi.BF16, m, C.c_void_p(y.data_ptr()), ffi.BF16, None)
+
+        stack()
+        ms = _time_ms(stack, 2 if m >= 4096 else 4)
+        flops = layers * 2 * 2.0 * m * k * n
+        out[f"m{m}"] = {"ms_per_stack": round(ms, 3), "tflops": round(flops / ms / 1e9, 1)}
+        del x, h0, h, y
+    best = out["m16384"]["tflops"]
+    out["roofline"] = {"bound": "tensor", "achieved": best, "peak": sustained, "unit": "TFLOP/s", "frac": round(best / sustained, 4), "peak_kind": kind + " (sustained bf16)", "kernel": "zq::gemm_kernel (tcgen05, M=16384, incl. operand dequantisation)"}
+    out["gpu_launches"] = ctx.launch_count - launches0
+    for w in ups + downs:
+        w.release()
+    torch.cuda.empty_cache()
+    return out
+
+
+def bench_moe(ctx, device, args, world, rank):
+    """configs[4]: 256 experts, top-8, hidden 7168, expert FFN 2048 (Q4_K), one shared expert, softmax top-k router,
+    bf16 activations; 64 tokens (decode) and 8192 tokens (prefill).  With N ranks the experts are expert-parallel
+    (256/N per rank), tokens data-parallel (total fixed), routed rows cross ranks with one all-to-all each way."""
+    import torch
+    import torch.distributed as dist
+
+    from zllm_b200.backend import MoeExperts, moe_forward, moe_route
+    from zllm_b200.dist import expert_parallel_forward, expert_range
+
+    E, K, H, I = 256, 8, 7168, 2048
+    lo, hi = expert_range(E, world, rank)
+    gen = torch.Generator(device=device)
+
+    def make(rows, cols, seed):
+        gen.manual_seed(seed)
+        full = torch.randn((rows, cols), generator=gen, device=device, dtype=torch.float32) * 0.02
+        w = ctx.prepare_weight(Q4_K, ctx.quantize(Q4_K, full), rows, cols)
+        del full
+        return w
+
+    gates = [make(I, H, 9000 + 3 * e) for e in range(lo, hi)]
+    ups = [make(I, H, 9001 + 3 * e) for e in range(lo, hi)]
+    downs = [make(H, I, 9002 + 3 * e) for e in range(lo, hi)]
+    table = MoeExperts(ctx, gates, ups, downs)
+    shared = (make(I, H, 8000), make(I, H, 8001), make(H, I, 8002))
+    gen.manual_seed(8100)
+    router = torch.randn((E, H), generator=gen, device=device, dtype=torch.float32) / (H ** 0.5)
+    expert_bytes = 3 * int(I * H * BPW)
+    out = {"experts": E, "top_k": K, "hidden": H, "intermediate": I, "weights": "Q4_K", "parallelism": f"ep{world}" if world > 1 else "single", "router": "softmax top-k, renormalised over the selected experts"}
+    for name, m_total in (("decode_m64", 64), ("prefill_m8192", 8192)):
+        m = m_total // world
+        gen.manual_seed(8200 + m_total)
+        x_all = torch.randn((m_total, H), generator=gen, device=device, dtype=torch.float32).to(torch.bfloat16)
+        x = x_all[rank * m:(rank + 1) * m].contiguous()
+
+        def run_local(rows, local_ids, route_w):
+            n = rows.shape[0]
+            return moe_forward(ctx, table, rows, local_ids.view(n, 1).contiguous(), route_w.view(n, 1).contiguous(), out_dtype=torch.float32)
+
+        def forward():
+            ids, w = moe_route(ctx, x, router, K, 1.0, True)
+            if world == 1:
+                return moe_forward(ctx, table, x, ids, w, shared=shared, out_dtype=torch.bfloat16), ids
+            routed = expert_parallel_forward(x, ids, w, E, run_local)
+            sh = ctx.gated_mlp(x, *shared, out_dtype=torch.float32)
+            return (routed + sh).to(torch.bfloat16), ids
+
+        y, ids = forward()
+        distinct = int(torch.unique(ids).numel())
+        if world > 1:
+            dist.barrier()
+        ms = _time_ms(lambda: forward(), 3)
+        if world > 1:
+            t = torch.tensor([ms], device=device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t[0])
+        flops = (m_total * K + m_total) * 3 * 2.0 * H * I
+        entry = {"tokens": m_total, "ms": round(ms, 3), "tflops": round(flops / ms / 1e9, 2)}
+        if m_total == 64:
+            entry["distinct_experts_hit_rank0"] = distinct
+            entry["weight_gbs_rank0"] = round((distinct + 1) * expert_bytes / ms / 1e6, 1)
+        out[name] = entry
+        del x_all, x, y
+    return out
 
 
 def _cpu_sweep(batches, repeat_seed=0):
@@ -392,8 +522,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--no-extras", action="store_true", help="skip the prefill-GEMM and MoE side measurements")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying CUDA graphs")
     ap.add_argument("--no-clocks", action="store_true", help="do not sample clocks with nvidia-smi")
+    ap.add_argument("--stack-layers", type=int, default=64, help="layers of the prefill GEMM stack (configs[2] names 64)")
     ap.add_argument("--only", default=None, help="restrict the sweep to one case, e.g. q4_k:5120x17408:1 (format:KxN:batch); for profiling")
     args = ap.parse_args()
     if args.impl == "reference":
