@@ -109,7 +109,12 @@ def run_ours(args):
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        import datetime
+        import faulthandler
+
+        # a collective that never completes must end the run with a traceback, not sit on the GPUs
+        faulthandler.dump_traceback_later(args.watchdog, exit=True)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), timeout=datetime.timedelta(seconds=120))
     ctx = B200Context(local_rank)
     device = torch.device("cuda", local_rank)
     hbm_peak, _, peak_kind = read_peaks()
@@ -183,7 +188,7 @@ def run_ours(args):
             launch(mm, case)
     torch.cuda.synchronize()
     graphs = []
-    if not args.no_graph:
+    if not args.no_graph and world == 1:  # collectives are launched from the host, never captured
         side = torch.cuda.Stream(device=device)
         try:
             for m, fmt, members in blocks:
@@ -522,6 +527,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--watchdog", type=int, default=480, help="multi-GPU runs: seconds after which a stuck run dumps tracebacks and exits")
     ap.add_argument("--no-extras", action="store_true", help="skip the prefill-GEMM and MoE side measurements")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying CUDA graphs")
     ap.add_argument("--no-clocks", action="store_true", help="do not sample clocks with nvidia-smi")
