@@ -118,6 +118,17 @@ def run_ours(args):
     ctx = B200Context(local_rank)
     device = torch.device("cuda", local_rank)
     hbm_peak, _, peak_kind = read_peaks()
+    if args.only_prefill:
+        m, k, n = args.only_prefill, 5120, 17408
+        full = torch.randn((n, k), device=device, dtype=torch.float32) * 0.02
+        w = ctx.prepare_weight(Q4_K, ctx.quantize(Q4_K, full), n, k)
+        del full
+        x = torch.randn((m, k), device=device, dtype=torch.float32).to(torch.bfloat16)
+        for _ in range(max(args.steps, 1)):
+            y = ctx.linear(x, w)
+        ctx.sync()
+        print(json.dumps({"only_prefill": m, "launches": ctx.launch_count}))
+        return
 
     # ---- synthetic inputs: N(0, 0.02) weights quantised on the device, N(0, 1) activations, seed 0
     gen = torch.Generator(device=device)
@@ -290,9 +301,10 @@ def run_ours(args):
     if not args.no_extras:
         del graphs, cases, plan, blocks
         torch.cuda.empty_cache()
-        if world == 1:
+        if world == 1 and args.extras in ("all", "prefill"):
             extras["prefill_gemm"] = bench_prefill(ctx, device, args)
-        extras["moe"] = bench_moe(ctx, device, args, world, rank)
+        if args.extras in ("all", "moe"):
+            extras["moe"] = bench_moe(ctx, device, args, world, rank)
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -529,9 +541,11 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--watchdog", type=int, default=480, help="multi-GPU runs: seconds after which a stuck run dumps tracebacks and exits")
     ap.add_argument("--no-extras", action="store_true", help="skip the prefill-GEMM and MoE side measurements")
+    ap.add_argument("--extras", default="all", choices=["all", "prefill", "moe"], help="which side measurements to run")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying CUDA graphs")
     ap.add_argument("--no-clocks", action="store_true", help="do not sample clocks with nvidia-smi")
     ap.add_argument("--stack-layers", type=int, default=64, help="layers of the prefill GEMM stack (configs[2] names 64)")
+    ap.add_argument("--only-prefill", type=int, default=0, help="profiling aid: run only a few prefill GEMMs (Q4_K 5120->17408) at this token count and exit")
     ap.add_argument("--only", default=None, help="restrict the sweep to one case, e.g. q4_k:5120x17408:1 (format:KxN:batch); for profiling")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -14,13 +14,15 @@ from tests.gpu_util import ctx, dev, host
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(autouse=True, params=["resident", "staged"])
+@pytest.fixture(autouse=True, params=["tcgen05", "resident", "staged"])
 def gemv_variant(request):
-    """Every case runs on both decode kernels: activations resident in shared memory (the default whenever
-    they fit) and per-item activation staging (the variant for large batch x K)."""
+    """Every case runs on all decode kernels: the tcgen05 kernel (Q4_K, opt-in), the warp-MMA kernel with
+    activations resident in shared memory, and the warp-MMA kernel with per-item activation staging."""
+    ctx().set_option("enable_tcgen05_gemv", 1 if request.param == "tcgen05" else 0)
     ctx().set_option("force_staged_gemv", 1 if request.param == "staged" else 0)
     yield request.param
     ctx().set_option("force_staged_gemv", 0)
+    ctx().set_option("enable_tcgen05_gemv", 0)
 
 
 TYPES = [H.Q4_0, H.Q8_0, H.Q4_K, H.IQ4_NL]
@@ -112,7 +114,7 @@ def test_gated_is_silu_gate_times_up_of_the_plain_projections():
     g = host(ctx().linear(dev(x), w)).astype(np.float32)
     got = host(ctx().gated_linear(dev(x), w, w))
     want = (g / (np.float32(1) + np.exp(-g))) * g
-    np.testing.assert_allclose(got, want, rtol=1e-6)
+    np.testing.assert_allclose(got, want, rtol=2e-5)  # the plain projection may run on a different kernel than the gated one
 
 
 @pytest.mark.parametrize("m", [1, 4])

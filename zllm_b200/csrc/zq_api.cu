@@ -95,6 +95,7 @@ static int finish_prepare(zq_ctx *ctx, zq_weight *w, zq_error *err) {
     FormatInfo f = format_info(w->type);
     int rc = make_weight_map(w, 2 * f.unit_bytes / 4, 128, &w->gemv_map, err);
     if (!rc) rc = make_weight_map(w, 2 * f.unit_bytes / 4, 64, &w->gemv_map_half, err);
+    if (!rc) rc = make_weight_map(w, f.unit_bytes / 4, 128, &w->qmv_map, err);
     (void)ctx;
     return rc;
 }
@@ -180,6 +181,10 @@ int zq_ctx_set_option(zq_ctx *ctx, const char *key, int value, zq_error *err) {
     if (!ctx || !key) return set_error(err, ZQ_ERR_ARG, "zq_ctx_set_option: null argument");
     if (!strcmp(key, "force_staged_gemv")) {
         ctx->force_staged_gemv = value;
+        return ZQ_OK;
+    }
+    if (!strcmp(key, "enable_tcgen05_gemv")) {
+        ctx->enable_tcgen05_gemv = value;
         return ZQ_OK;
     }
     return set_error(err, ZQ_ERR_ARG, "zq_ctx_set_option: unknown option '%s'", key);

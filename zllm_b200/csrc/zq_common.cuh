@@ -92,14 +92,16 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One poll of an mbarrier phase.  The suspend-time hint lets the hardware park the thread (up to ~10 us) until the
+// phase completes instead of spinning, so waiting warps do not eat issue slots of the warps that have work.
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(10000u)
         : "memory");
     return ok != 0;
 }
@@ -218,6 +220,9 @@ struct zq_ctx {
     // Diagnostics: 1 = always use the per-item activation staging GEMV (the variant for activations too large to
     // stay resident in shared memory), so that tests can cover it at small sizes.
     int force_staged_gemv = 0;
+    // 1 = run Q4_K decode on the tcgen05 kernel (zq_qmv.cu) instead of the warp-MMA kernels.  Off by default: it is
+    // parity-clean but, as measured, not yet faster than the warp-MMA path.
+    int enable_tcgen05_gemv = 0;
     std::atomic<uint64_t> launches{0};
     std::mutex mutex;
 };
@@ -232,6 +237,7 @@ struct zq_weight {
     uint8_t *data = nullptr;     // resident layout, device
     bool owns_data = true;
     CUtensorMap gemv_map;        // u32 tensor [rows, row_pitch/4], box = (chunk words, 128 rows): decode GEMV
+    CUtensorMap qmv_map;         // same tensor, box of one unit x 128 rows: tcgen05 decode kernel
     CUtensorMap gemv_map_half;   // same tensor, box of 64 rows: gated GEMV (gate and up halves of one stage)
 };
 

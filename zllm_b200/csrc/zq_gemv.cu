@@ -389,9 +389,9 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const __grid_cons
                     int row = i & (kTileRows - 1), tok = i >> 7;
                     slot[tok * kTileRows + row] = red[row * (NT * 4) + tok] + red[(kTileRows + row) * (NT * 4) + tok];
                 }
-                __threadfence();
                 __syncthreads();
                 if (tid == 0) {
+                    __threadfence();  // the barrier orders the CTA's stores before this thread; one fence publishes them
                     unsigned old = atomicAdd(&p.counters[tile], 1u);
                     s_flag = (old == (unsigned)(c_last - c_first)) ? 1 : 0;
                 }
@@ -493,6 +493,9 @@ int launch_gemv(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const vo
     if ((size_t)p.tiles > ctx->gemv_counters_n) return set_error(err, ZQ_ERR_UNSUPPORTED, "GEMV needs %d tile counters, context has %zu", p.tiles, ctx->gemv_counters_n);
     long long total = (long long)p.tiles * p.chunks;
     int grid = (int)(total < ctx->sm_count ? total : ctx->sm_count);
+    // When the tiles alone nearly fill the machine, give every CTA one whole tile: a few SMs idle, but no tile is
+    // split, so the partial-tile hand-over (several microseconds of fences and atomics per launch) disappears.
+    if (p.tiles <= ctx->sm_count && p.tiles * 100 >= ctx->sm_count * 85) grid = p.tiles;
     if (grid <= 0) return ZQ_OK;
     for (size_t m0 = 0; m0 < m; m0 += kMaxGemvRows) {
         size_t mm = m - m0 < (size_t)kMaxGemvRows ? m - m0 : (size_t)kMaxGemvRows;
@@ -501,6 +504,12 @@ int launch_gemv(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const vo
         p.y = reinterpret_cast<uint8_t *>(y) + m0 * w->rows * dtype_size(y_dtype);
         p.residual = residual ? reinterpret_cast<const uint8_t *>(residual) + m0 * w->rows * dtype_size(y_dtype) : nullptr;
         int rc;
+        if (ctx->enable_tcgen05_gemv && !ctx->force_staged_gemv && !gated) {
+            bool taken = false;
+            rc = launch_qmv(ctx, w, p, taken, err);
+            if (rc) return rc;
+            if (taken) continue;
+        }
         if (!ctx->force_staged_gemv) {
             bool taken = false;
             rc = launch_gemv_resident(ctx, w, w_up, p, grid, taken, err);
@@ -598,8 +607,14 @@ int launch_gemv_noalloc(zq_ctx *ctx, const zq_weight *w, const void *x, int x_dt
     int grid = (int)(total < ctx->sm_count ? total : ctx->sm_count);
     if (grid <= 0) return ZQ_OK;
     bool taken = false;
-    rc = launch_gemv_resident(ctx, w, nullptr, p, grid, taken, err);
-    if (rc || taken) return rc;
+    if (ctx->enable_tcgen05_gemv && !ctx->force_staged_gemv) {  // same kernel choice as zq_linear, so results agree bit for bit
+        rc = launch_qmv(ctx, w, p, taken, err);
+        if (rc || taken) return rc;
+    }
+    if (!ctx->force_staged_gemv) {
+        rc = launch_gemv_resident(ctx, w, nullptr, p, grid, taken, err);
+        if (rc || taken) return rc;
+    }
     switch (w->type) {
     case ZQ_Q4_K: return launch_type<ZQ_Q4_K>(ctx, w, nullptr, p, grid, err);
     case ZQ_Q4_0: return launch_type<ZQ_Q4_0>(ctx, w, nullptr, p, grid, err);

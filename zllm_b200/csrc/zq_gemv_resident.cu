@@ -6,9 +6,12 @@
 //     arrival per warp);
 //   * the refill of a released stage (wait for `empty`, re-arm `full`, issue the TMA box of the item STAGES-1
 //     ahead) is done by one lane of a different warp each iteration, so no warp is the permanent straggler.
-// Only the end of a 128-row tile (every `chunks` items) synchronises the warps.
-// Work partition, split-tile fix-up, arithmetic and operator contract are those of zq_gemv.cu; this variant is
-// chosen whenever the staged activations fit beside at least two ring stages.
+// Work partition: one CTA per (128-row tile, K slice).  When the tiles alone do not fill the machine, each tile is
+// split over a thread-block cluster of 2, 4 or 8 CTAs (one K slice each); the slices' partial sums meet in
+// distributed shared memory: every CTA leaves its partial tile in its own shared memory, the cluster synchronises,
+// and rank 0 adds the partials in rank order (deterministic) and stores the tile.  No global scratch, no atomics.
+// Arithmetic and operator contract are those of zq_gemv.cu; this variant is chosen whenever the staged activations
+// of a K slice fit beside at least two ring stages.
 #include "zq_gemv_frag.cuh"
 
 namespace zq {
@@ -17,12 +20,25 @@ constexpr int kConsumerThreads = 512;
 constexpr int kResidentThreads = kConsumerThreads;
 
 struct ResidentArgs {
-    int stages;       // 2..4 ring stages
+    int stages;       // 2..5 ring stages
+    int split;        // CTAs per tile (cluster size): 1, 2, 4 or 8
+    int slice_units;  // units of activations staged per CTA (upper bound over the K slices)
     int units_total;  // resident units per row (ceil(K / 256))
     int off_x, off_sx, off_red, off_lut, off_bar;  // byte offsets from the 128-byte aligned base (weights at 0)
 };
 
 __device__ __forceinline__ void consumer_bar() { __syncthreads(); }
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// f32 at the same shared-memory offset in the CTA of rank `rank` of this cluster
+__device__ __forceinline__ float ld_cluster_f32(const float *local, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
 
 // Bounded wait that never strands the CTA: when the barrier does not complete (or another warp already gave up)
 // the abort flag is raised and every later wait in the CTA falls through, so all warps still walk the same
@@ -48,18 +64,20 @@ __global__ void __launch_bounds__(kResidentThreads, 1) gemv_resident_kernel(cons
     float *red = reinterpret_cast<float *>(smem + ra.off_red);
     uint32_t *lut = reinterpret_cast<uint32_t *>(smem + ra.off_lut);
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + ra.off_bar);
-    uint64_t *empty = full + 4;
+    uint64_t *empty = full + 8;
     __shared__ int s_flag;
     __shared__ int s_abort;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int STAGES = ra.stages;
     const int rows_per_tile = GATED ? kTileRows / 2 : kTileRows;
-    const long long T = (long long)p.tiles * p.chunks;
-    const long long G = gridDim.x;
-    const long long begin = (long long)blockIdx.x * T / G;
-    const long long end = (long long)(blockIdx.x + 1) * T / G;
-    const int n_items = (int)(end - begin);
+    // this CTA: tile blockIdx.x / split, K slice (cluster rank) blockIdx.x % split
+    const int split = ra.split;
+    const int my_tile = blockIdx.x / split, my_rank = blockIdx.x % split;
+    const int chunk_begin = (int)((long long)my_rank * p.chunks / split), chunk_end = (int)((long long)(my_rank + 1) * p.chunks / split);
+    const long long begin = (long long)my_tile * p.chunks + chunk_begin;
+    const int n_items = chunk_end - chunk_begin;
+    const int unit0 = chunk_begin * kChunkUnits;  // first unit of the staged activation slice
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -103,14 +121,18 @@ __global__ void __launch_bounds__(kResidentThreads, 1) gemv_resident_kernel(cons
     }
     {
         // stage every activation quad: B-fragment slot (unit, step, column, t); Q4_K also gets per-group sums
-        const int quads_per_row = ra.units_total * (kUnitWeights / 4);
+        int slice_units = chunk_end * kChunkUnits;
+        if (slice_units > ra.units_total) slice_units = ra.units_total;
+        slice_units -= unit0;
+        if (slice_units < 0) slice_units = 0;
+        const int quads_per_row = slice_units * (kUnitWeights / 4);
         const int total_quads = p.m * quads_per_row;
         for (int q = tid; q < total_quads; q += kConsumerThreads) {  // whole warps stay together (multiples of 64)
             const int m = q / quads_per_row, quad = q - m * quads_per_row;
-            const int k0 = quad * 4;
+            const int k0 = quad * 4;  // column inside the slice
             float v[4] = {0.f, 0.f, 0.f, 0.f};
-            if (k0 < p.cols) {
-                const size_t o = (size_t)m * p.cols + k0;
+            if (unit0 * kUnitWeights + k0 < p.cols) {
+                const size_t o = (size_t)m * p.cols + (size_t)unit0 * kUnitWeights + k0;
                 if (p.x_dtype == ZQ_F32) {
                     const float4 f = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p.x) + o);
                     v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
@@ -184,8 +206,8 @@ __global__ void __launch_bounds__(kResidentThreads, 1) gemv_resident_kernel(cons
         }
         wait_or_abort(&full[stage], (it / STAGES) & 1, &s_abort, p.status);
 
-        const int unit = chunk * kChunkUnits + ul;
-        if (unit < ra.units_total) {
+        const int unit = chunk * kChunkUnits + ul - unit0;  // unit inside the staged slice
+        if (unit + unit0 < ra.units_total) {
             const uint8_t *w0 = ws + (size_t)stage * S::stage_w + (size_t)r0 * S::pitch + ul * UB;
             const uint8_t *w1 = w0 + 8 * S::pitch;
             const uint2 *xu = xs + (size_t)unit * 16 * cols2 * 4 + t;
@@ -203,120 +225,124 @@ __global__ void __launch_bounds__(kResidentThreads, 1) gemv_resident_kernel(cons
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[stage]);
 
-        const bool tile_ends = (it == n_items - 1) || ((int)((item + 1) / p.chunks) != tile);
-        if (tile_ends) {
+    }
+
+    // ---------------------------------------------------- end of the K slice: combine and store
+    {
+        const int tile = my_tile;
+        // the two warps that share a row sub-tile add up through shared memory: red[ul][row][token]
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-                red[(ul * kTileRows + r0) * (NT * 4) + nt * 4 + t] = yacc[nt][0];
-                red[(ul * kTileRows + r0 + 8) * (NT * 4) + nt * 4 + t] = yacc[nt][1];
-                yacc[nt][0] = yacc[nt][1] = 0.f;
-            }
-            consumer_bar();
-            const long long tile_first = (long long)tile * p.chunks, tile_last = tile_first + p.chunks - 1;
-            const bool whole = begin <= tile_first && tile_last < end;
-            const int c_first = (int)(((tile_first + 1) * G - 1) / T), c_last = (int)(((tile_last + 1) * G - 1) / T);
-            bool finish = whole;
-            if (!whole) {
-                const int which = (tile == (int)(begin / p.chunks)) ? 0 : 1;
-                float *slot = p.partials + ((size_t)blockIdx.x * 2 + which) * kSlotFloats;
-                for (int i = tid; i < kTileRows * p.m; i += kConsumerThreads) {
-                    int row = i & (kTileRows - 1), tok = i >> 7;
-                    slot[tok * kTileRows + row] = red[row * (NT * 4) + tok] + red[(kTileRows + row) * (NT * 4) + tok];
-                }
-                __threadfence();
-                consumer_bar();
-                if (tid == 0) {
-                    unsigned old = atomicAdd(&p.counters[tile], 1u);
-                    s_flag = (old == (unsigned)(c_last - c_first)) ? 1 : 0;
-                }
-                consumer_bar();
-                finish = s_flag != 0;
-                if (finish) __threadfence();
-            }
-            if (finish) {
-                float vals[(kTileRows * kMaxGemvRows + kConsumerThreads - 1) / kConsumerThreads];
-                int cnt = 0;
+        for (int nt = 0; nt < NT; ++nt) {
+            red[(ul * kTileRows + r0) * (NT * 4) + nt * 4 + t] = yacc[nt][0];
+            red[(ul * kTileRows + r0 + 8) * (NT * 4) + nt * 4 + t] = yacc[nt][1];
+        }
+        consumer_bar();
+        float vals[(kTileRows * kMaxGemvRows + kConsumerThreads - 1) / kConsumerThreads];
+        int cnt = 0;
+        for (int i = tid; i < kTileRows * p.m; i += kConsumerThreads, ++cnt) {
+            int row = i & (kTileRows - 1), tok = i >> 7;
+            vals[cnt] = red[row * (NT * 4) + tok] + red[(kTileRows + row) * (NT * 4) + tok];
+        }
+        consumer_bar();
+        cnt = 0;
+        for (int i = tid; i < kTileRows * p.m; i += kConsumerThreads, ++cnt) red[i] = vals[cnt];  // part[tok * 128 + row]
+        if (split > 1) {
+            cluster_sync_all();  // every slice's partial tile is in its CTA's shared memory
+            if (my_rank == 0) {
+                cnt = 0;
                 for (int i = tid; i < kTileRows * p.m; i += kConsumerThreads, ++cnt) {
-                    int row = i & (kTileRows - 1), tok = i >> 7;
-                    float v;
-                    if (whole) {
-                        v = red[row * (NT * 4) + tok] + red[(kTileRows + row) * (NT * 4) + tok];
-                    } else {
-                        v = 0.f;
-                        for (int c = c_first; c <= c_last; ++c) {
-                            long long cb = (long long)c * T / G;
-                            int which = (tile == (int)(cb / p.chunks)) ? 0 : 1;
-                            v += __ldcg(p.partials + ((size_t)c * 2 + which) * kSlotFloats + tok * kTileRows + row);
-                        }
-                    }
+                    float v = vals[cnt];
+                    for (int r = 1; r < split; ++r) v += ld_cluster_f32(&red[i], (uint32_t)r);  // rank order: deterministic
                     vals[cnt] = v;
                 }
                 consumer_bar();
                 cnt = 0;
                 for (int i = tid; i < kTileRows * p.m; i += kConsumerThreads, ++cnt) red[i] = vals[cnt];
-                consumer_bar();
-                const int out_rows = rows_per_tile;
-                for (int i = tid; i < out_rows * p.m; i += kConsumerThreads) {
-                    int row = i % out_rows, tok = i / out_rows;
-                    int n = tile * out_rows + row;
-                    if (n >= p.n_out) continue;
-                    float v;
-                    if (GATED) {
-                        float gate = red[tok * kTileRows + row], up = red[tok * kTileRows + out_rows + row];
-                        v = (gate / (1.0f + expf(-gate))) * up;
-                    } else {
-                        v = red[tok * kTileRows + row];
-                    }
-                    size_t o = (size_t)tok * p.n_out + n;
-                    if (p.residual) v += load_as_f32(p.residual, p.y_dtype, o);
-                    store_from_f32(p.y, p.y_dtype, o, v);
-                }
-                if (!whole && tid == 0) p.counters[tile] = 0;
             }
-            consumer_bar();  // red is free again before the next tile's sums land in it
         }
+        consumer_bar();
+        if (my_rank == 0) {
+            const int out_rows = rows_per_tile;
+            for (int i = tid; i < out_rows * p.m; i += kConsumerThreads) {
+                int row = i % out_rows, tok = i / out_rows;
+                int n = tile * out_rows + row;
+                if (n >= p.n_out) continue;
+                float v;
+                if (GATED) {
+                    float gate = red[tok * kTileRows + row], up = red[tok * kTileRows + out_rows + row];
+                    v = (gate / (1.0f + expf(-gate))) * up;
+                } else {
+                    v = red[tok * kTileRows + row];
+                }
+                size_t o = (size_t)tok * p.n_out + n;
+                if (p.residual) v += load_as_f32(p.residual, p.y_dtype, o);
+                store_from_f32(p.y, p.y_dtype, o, v);
+            }
+        }
+        if (split > 1) cluster_sync_all();  // nobody leaves while rank 0 may still read its shared memory
     }
 }
 
-// Shared-memory plan of the resident variant; returns false when fewer than two ring stages would fit.
+// Plan of the resident variant: CTAs per tile (cluster size) and shared-memory layout; returns false when fewer
+// than two ring stages would fit beside the staged activation slice.
 template <uint32_t TYPE, int NT>
-static bool plan_resident(int m, int units_total, ResidentArgs &ra, int &total_bytes) {
+static bool plan_resident(int m, int units_total, int tiles, int chunks, int sm_count, ResidentArgs &ra, int &total_bytes) {
     using S = GemvSmem<TYPE, NT>;
+    int split = 1;
+    while (split < 8 && tiles * split * 2 <= sm_count && split * 2 <= chunks) split *= 2;
+    const int slice_chunks = (chunks + split - 1) / split;
+    int slice_units = slice_chunks * kChunkUnits;
+    if (slice_units > units_total) slice_units = units_total;
     const int max_smem = 232448 - 256;  // 227 KB opt-in limit minus static shared and alignment slack
-    const int x_bytes = units_total * 16 * (2 * m) * 4 * 8;
-    const int sx_bytes = TYPE == ZQ_Q4_K ? units_total * (2 * m) * 4 * 4 : 0;
-    const int fixed = x_bytes + sx_bytes + S::red_bytes + S::lut_bytes + 64 + 128;
+    const int x_bytes = slice_units * 16 * (2 * m) * 4 * 8;
+    const int sx_bytes = TYPE == ZQ_Q4_K ? slice_units * (2 * m) * 4 * 4 : 0;
+    const int fixed = x_bytes + sx_bytes + S::red_bytes + S::lut_bytes + 128 + 128;
     int stages = (max_smem - fixed) / S::stage_w;
-    if (stages > 4) stages = 4;
+    if (stages > 5) stages = 5;
     if (stages < 2) return false;
     ra.stages = stages;
+    ra.split = split;
+    ra.slice_units = slice_units;
     ra.units_total = units_total;
     ra.off_x = stages * S::stage_w;
     ra.off_sx = ra.off_x + x_bytes;
     ra.off_red = ra.off_sx + sx_bytes;
     ra.off_lut = ra.off_red + S::red_bytes;
     ra.off_bar = ra.off_lut + S::lut_bytes;
-    total_bytes = ra.off_bar + 64 + 128;
+    total_bytes = ra.off_bar + 128 + 128;
     return true;
 }
 
 template <uint32_t TYPE, int NT, bool GATED>
 static int launch_resident_one(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const GemvParams &p, int grid, bool &taken, zq_error *err) {
+    (void)grid;
     ResidentArgs ra;
     int total = 0;
-    taken = plan_resident<TYPE, NT>(p.m, (int)w->units_per_row, ra, total);
+    taken = plan_resident<TYPE, NT>(p.m, (int)w->units_per_row, p.tiles, p.chunks, ctx->sm_count, ra, total);
     if (!taken) return ZQ_OK;
     auto kernel = gemv_resident_kernel<TYPE, NT, GATED>;
     static bool configured[64] = {};
     if (!configured[ctx->device & 63]) {
         ZQ_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 256), err);
+        ZQ_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 0), err);
         configured[ctx->device & 63] = true;
     }
     const CUtensorMap &ma = GATED ? w->gemv_map_half : w->gemv_map;
     const CUtensorMap &mb = GATED ? w_up->gemv_map_half : w->gemv_map;
-    kernel<<<grid, kResidentThreads, total, ctx->stream>>>(ma, mb, p, ra);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(p.tiles * ra.split));
+    cfg.blockDim = dim3(kResidentThreads);
+    cfg.dynamicSmemBytes = (size_t)total;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)ra.split;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    ZQ_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, ma, mb, p, ra), err);
     ctx->launches++;
-    ZQ_CUDA_CHECK(cudaGetLastError(), err);
     return ZQ_OK;
 }
 
