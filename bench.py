@@ -199,16 +199,19 @@ def run_ours(args):
             launch(mm, case)
     torch.cuda.synchronize()
     graphs = []
+    launches_per_graph = []
     if not args.no_graph and world == 1:  # collectives are launched from the host, never captured
         side = torch.cuda.Stream(device=device)
         try:
             for m, fmt, members in blocks:
                 g = torch.cuda.CUDAGraph()
+                n0 = ctx.launch_count
                 with torch.cuda.graph(g, stream=side):
                     ctx.set_stream(torch.cuda.current_stream(device).cuda_stream)
                     for mm, case in members:
                         launch(mm, case)
                 graphs.append(g)
+                launches_per_graph.append(ctx.launch_count - n0)
         except Exception as exc:  # e.g. a collective that cannot be captured: fall back to host launches
             graphs = []
             sys.stderr.write(f"bench: graph capture failed ({exc}); launching from the host\n")
@@ -257,6 +260,8 @@ def run_ours(args):
     elapsed_ms = t0.elapsed_time(t1)
     kernel_ms = sum(a.elapsed_time(b) for a, b in events)
     launches = ctx.launch_count - launches_before
+    if graphs:  # replayed launches do not pass through the library's counter: count what each graph captured
+        launches = sum(launches_per_graph) * args.steps
     clocks = sampler.stop() if rank == 0 and not args.no_clocks else None
     if world > 1:
         t = torch.tensor([elapsed_ms, kernel_ms], device=device, dtype=torch.float64)

@@ -90,7 +90,7 @@ int zq_gated_mlp(zq_ctx *ctx, const zq_weight *gate, const zq_weight *up, const 
  * it exists for callers that cannot allocate device memory where they run a layer (a host application that owns
  * the allocator, a fixed-budget real-time loop, a region in which allocator calls are forbidden).  The kernel's
  * scratch (partial tiles and arrival counters of the split-tile fix-up) lives in a fixed device array inside the
- * library, about 1.3 MB per GPU, held from library load until process exit.  Limits: at most 8 activation rows per
+ * library, about 2.6 MB per GPU, held from library load until process exit.  Limits: at most 8 activation rows per
  * call, weights of at most 524 288 rows, devices of at most 160 SMs; anything beyond is rejected with an error.
  * The first call on a device looks up the array's device address (no allocation) and should be made before any
  * stream capture.  All calls on a device share the array: calls that overlap on the GPU (two streams, two contexts)

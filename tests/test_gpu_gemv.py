@@ -44,7 +44,8 @@ def test_linear_matches_cpu_path(tensor_type, m):
     x = np.random.default_rng(m).standard_normal((m, cols)).astype(np.float32)
     w = ctx().prepare_weight(tensor_type, data, rows, cols)
     got = host(ctx().linear(dev(x), w))
-    _check(got, orc.linear(tensor_type, data, rows, cols, x))
+    # 9..16 rows run as single f16 limbs (activation rounding 2^-12), up to 8 rows keep f32-level accuracy
+    _check(got, orc.linear(tensor_type, data, rows, cols, x), tight=TIGHT if m <= 8 else 1e-3)
 
 
 @pytest.mark.parametrize("tensor_type,rows,cols", [
@@ -92,7 +93,7 @@ def test_reference_generator_cases(tensor_type, m):
 
 
 @pytest.mark.parametrize("tensor_type", [H.Q4_K, H.Q4_0, H.IQ4_NL, H.Q8_0])
-@pytest.mark.parametrize("m,rows,cols", [(1, 3840, 1536), (1, 100, 512), (4, 192, 1024), (8, 64, 768)])
+@pytest.mark.parametrize("m,rows,cols", [(1, 3840, 1536), (1, 100, 512), (4, 192, 1024), (8, 64, 768), (12, 200, 1024)])
 def test_gated_silu_matches_cpu_path(tensor_type, m, rows, cols):
     if tensor_type == H.Q4_K and cols % 256:
         pytest.skip("Q4_K needs 256-aligned columns")
@@ -101,7 +102,7 @@ def test_gated_silu_matches_cpu_path(tensor_type, m, rows, cols):
     x = np.random.default_rng(23).standard_normal((m, cols)).astype(np.float32)
     wg, wu = ctx().prepare_weight(tensor_type, gate, rows, cols), ctx().prepare_weight(tensor_type, up, rows, cols)
     got = host(ctx().gated_linear(dev(x), wg, wu))
-    _check(got, orc.gated_linear(tensor_type, gate, up, rows, cols, x), tight=5e-5)
+    _check(got, orc.gated_linear(tensor_type, gate, up, rows, cols, x), tight=5e-5 if m <= 8 else BOUND)
 
 
 def test_gated_is_silu_gate_times_up_of_the_plain_projections():

@@ -121,7 +121,7 @@ int zq_ctx_create(int device, zq_ctx **out, zq_error *err) {
     ctx->sm_count = prop.multiProcessorCount;
     ZQ_CUDA_CHECK(cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking), err);
     ctx->stream = ctx->own_stream;
-    ctx->gemv_partials_floats = (size_t)ctx->sm_count * 2 * 128 * 8;
+    ctx->gemv_partials_floats = (size_t)ctx->sm_count * 2 * 128 * 16;  // two partial-tile slots (128 rows x 16 activation rows) per CTA
     ZQ_CUDA_CHECK(cudaMalloc(&ctx->gemv_partials, ctx->gemv_partials_floats * sizeof(float)), err);
     ctx->gemv_counters_n = 1 << 16;
     ZQ_CUDA_CHECK(cudaMalloc(&ctx->gemv_counters, ctx->gemv_counters_n * sizeof(uint32_t)), err);

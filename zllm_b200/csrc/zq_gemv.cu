@@ -29,14 +29,14 @@ namespace zq {
 template <uint32_t TYPE, int NT, bool GATED>
 __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemvParams p) {
     using S = GemvSmem<TYPE, NT>;
-    constexpr int STAGES = Fmt<TYPE>::stages;
+    constexpr int STAGES = S::stages;
     constexpr int UB = Fmt<TYPE>::unit_bytes;
-    constexpr int XQ = NT;  // activation quads converted per thread per item: m*128 quads over 512 threads
+    constexpr int XQ = NT == 1 ? 1 : 4;  // activation quads per thread per item: up to 16 rows x 128 quads over 512 threads
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
     uint8_t *ws = smem + S::off_w;
     uint2 *xs = reinterpret_cast<uint2 *>(smem + S::off_x);
-    uint32_t *sxs = reinterpret_cast<uint32_t *>(smem + S::off_sx);
+    uint2 *sxs = reinterpret_cast<uint2 *>(smem + S::off_sx);
     float *red = reinterpret_cast<float *>(smem + S::off_red);
     uint32_t *lut = reinterpret_cast<uint32_t *>(smem + S::off_lut);
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + S::off_bar);
@@ -106,7 +106,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const __grid_cons
     };
     auto store_x = [&](int stage) {
         uint2 *xst = xs + (size_t)stage * (S::stage_x / 8);
-        uint32_t *sxst = sxs + (size_t)stage * (S::stage_sx / 4);
+        uint2 *sxst = sxs + (size_t)stage * (S::stage_sx / 8);
 #pragma unroll
         for (int r = 0; r < XQ; ++r) {
             int q = tid + r * kGemvThreads;
@@ -120,7 +120,9 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const __grid_cons
                 lo[j] = __float2half_rn(v[j] - __half2float(hi[j]));
             }
             int unit = quad >> 6, i = (quad & 63) * 4;
-            int nt = m >> 2, col = 2 * (m & 3);
+            // two limbs: row m owns columns 2(m%4), 2(m%4)+1 of tile m/4; one limb: column m%8 of tile m/8
+            const bool two = p.limbs == 2;
+            int nt = two ? (m >> 2) : (m >> 3), col = two ? 2 * (m & 3) : (m & 7);
             if constexpr (TYPE == ZQ_IQ4_NL) {
                 // element i+by of the quad pairs with the other nibble of the same byte: MMA step 8h+2bb+(by>>1),
                 // register by&1, half index = nibble (see the A-fragment construction below)
@@ -132,18 +134,22 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const __grid_cons
                     __half *dst_hi = reinterpret_cast<__half *>(&xst[((nt * kChunkUnits + unit) * 16 + step) * 32 + (col * 4 + tt)]);
                     __half *dst_lo = reinterpret_cast<__half *>(&xst[((nt * kChunkUnits + unit) * 16 + step) * 32 + ((col + 1) * 4 + tt)]);
                     dst_hi[(by & 1) * 2 + nib] = hi[by];
-                    dst_lo[(by & 1) * 2 + nib] = lo[by];
+                    if (two) dst_lo[(by & 1) * 2 + nib] = lo[by];
                 }
             } else {
                 int step, tt;
                 quad_slot<TYPE>(i, step, tt);
                 uint2 *base = &xst[((nt * kChunkUnits + unit) * 16 + step) * 32];
                 base[col * 4 + tt] = make_uint2(h2_as_u32(__halves2half2(hi[0], hi[2])), h2_as_u32(__halves2half2(hi[1], hi[3])));
-                base[(col + 1) * 4 + tt] = make_uint2(h2_as_u32(__halves2half2(lo[0], lo[2])), h2_as_u32(__halves2half2(lo[1], lo[3])));
+                if (two) base[(col + 1) * 4 + tt] = make_uint2(h2_as_u32(__halves2half2(lo[0], lo[2])), h2_as_u32(__halves2half2(lo[1], lo[3])));
             }
             if constexpr (TYPE == ZQ_Q4_K) {
                 // per-group activation sums (32 columns = 8 consecutive quads = 8 consecutive lanes)
-                float sum = (v[0] + v[1]) + (v[2] + v[3]);
+                // sums of the values the MMAs really see (the staged limbs), so that the scale and min terms cancel
+                // exactly as in the reference's per-element form
+                float sum = 0.f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) sum += __half2float(hi[j]) + (two ? __half2float(lo[j]) : 0.f);
                 sum += __shfl_xor_sync(0xffffffffu, sum, 1);
                 sum += __shfl_xor_sync(0xffffffffu, sum, 2);
                 sum += __shfl_xor_sync(0xffffffffu, sum, 4);
@@ -151,9 +157,11 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const __grid_cons
                     int G8 = (i >> 5);  // group inside the unit
                     __half shi = __float2half_rn(sum);
                     __half slo = __float2half_rn(sum - __half2float(shi));
-                    __half *dst = reinterpret_cast<__half *>(&sxst[(nt * kChunkUnits + unit) * 32]);
-                    dst[(col * 4 + (G8 >> 1)) * 2 + (G8 & 1)] = shi;
-                    dst[((col + 1) * 4 + (G8 >> 1)) * 2 + (G8 & 1)] = slo;
+                    // lane (column, t') of the min-term fragment: .x = hi limbs of sums 2t', 2t'+1, .y = their lo limbs;
+                    // the sums ride in the row's first column (its second, lo-limb column keeps zeros)
+                    __half *dst = reinterpret_cast<__half *>(&sxst[(nt * kChunkUnits + unit) * 32 + col * 4 + (G8 >> 1)]);
+                    dst[G8 & 1] = shi;
+                    dst[2 + (G8 & 1)] = slo;
                 }
             }
         }
@@ -168,9 +176,9 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const __grid_cons
     }
     __syncthreads();
 
-    float yacc[NT][2];
+    float yacc[NT][2][2];
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) yacc[nt][0] = yacc[nt][1] = 0.f;
+    for (int nt = 0; nt < NT; ++nt) yacc[nt][0][0] = yacc[nt][0][1] = yacc[nt][1][0] = yacc[nt][1][1] = 0.f;
 
     const int r0 = 16 * rs + frag_row(g);  // tile row of fragment row g; the g+8 row is r0 + 8
     bool failed = false;
@@ -196,171 +204,10 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const __grid_cons
             const uint8_t *w0 = ws + (size_t)stage * S::stage_w + (size_t)r0 * S::pitch + ul * UB;
             const uint8_t *w1 = w0 + 8 * S::pitch;
             const uint2 *xb = xs + (size_t)stage * (S::stage_x / 8) + (size_t)ul * 16 * 32 + lane;
-            const uint4 hdr0 = *reinterpret_cast<const uint4 *>(w0);
-            const uint4 hdr1 = *reinterpret_cast<const uint4 *>(w1);
-
-            if constexpr (TYPE == ZQ_Q4_K) {
-                float d1[NT][4], d2[NT][4];
-#pragma unroll
-                for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) d1[nt][j] = d2[nt][j] = 0.f;
-                const uint32_t k1024 = 0x64006400u, k64x4 = 0x64646464u, kNeg1024 = 0xE400E400u, kNeg64 = 0xD400D400u;
-                // 6-bit codes of the 8 groups, four per word
-                uint32_t sc_lo0 = hdr0.y & 0x3F3F3F3Fu, sc_hi0 = (hdr0.w & 0x0F0F0F0Fu) | ((hdr0.y >> 2) & 0x30303030u);
-                uint32_t sc_lo1 = hdr1.y & 0x3F3F3F3Fu, sc_hi1 = (hdr1.w & 0x0F0F0F0Fu) | ((hdr1.y >> 2) & 0x30303030u);
-                uint32_t mn_lo0 = hdr0.z & 0x3F3F3F3Fu, mn_hi0 = ((hdr0.w >> 4) & 0x0F0F0F0Fu) | ((hdr0.z >> 2) & 0x30303030u);
-                uint32_t mn_lo1 = hdr1.z & 0x3F3F3F3Fu, mn_hi1 = ((hdr1.w >> 4) & 0x0F0F0F0Fu) | ((hdr1.z >> 2) & 0x30303030u);
-                const uint32_t bidx = 2 * (t >> 1);
-                const uint32_t sel_a = 0x4040u | (bidx * 0x0101u);        // [code, 0x64, code, 0x64] of group bidx
-                const uint32_t sel_b = 0x4040u | ((bidx + 1) * 0x0101u);  // ... of group bidx+1
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const uint4 pc0 = *reinterpret_cast<const uint4 *>(w0 + 16 + 16 * (t + 4 * h));
-                    const uint4 pc1 = *reinterpret_cast<const uint4 *>(w1 + 16 + 16 * (t + 4 * h));
-                    const uint32_t sc0 = h ? sc_hi0 : sc_lo0, sc1 = h ? sc_hi1 : sc_lo1;
-                    // scale as f16 pair, and the offset that removes the 1024 / 64 bias of the nibble trick
-                    const uint32_t sa0 = hsub2_u32(prmt(sc0, k64x4, sel_a), k1024), sb0 = hsub2_u32(prmt(sc0, k64x4, sel_b), k1024);
-                    const uint32_t sa1 = hsub2_u32(prmt(sc1, k64x4, sel_a), k1024), sb1 = hsub2_u32(prmt(sc1, k64x4, sel_b), k1024);
-                    const uint32_t oa0 = hmul2_u32(sa0, kNeg1024), ob0 = hmul2_u32(sb0, kNeg64);
-                    const uint32_t oa1 = hmul2_u32(sa1, kNeg1024), ob1 = hmul2_u32(sb1, kNeg64);
-                    const uint32_t q0[4] = {pc0.x, pc0.y, pc0.z, pc0.w};
-                    const uint32_t q1[4] = {pc1.x, pc1.y, pc1.z, pc1.w};
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const uint32_t x0 = q0[i], x0s = q0[i] >> 8, x1 = q1[i], x1s = q1[i] >> 8;
-                        // low nibbles -> group 2p (bias 1024), high nibbles -> group 2p+1 (bias 64)
-                        uint32_t a0 = hfma2_u32(lop3_and_or(x0, 0x000F000Fu, 0x64006400u), sa0, oa0);
-                        uint32_t a2 = hfma2_u32(lop3_and_or(x0s, 0x000F000Fu, 0x64006400u), sa0, oa0);
-                        uint32_t a1 = hfma2_u32(lop3_and_or(x1, 0x000F000Fu, 0x64006400u), sa1, oa1);
-                        uint32_t a3 = hfma2_u32(lop3_and_or(x1s, 0x000F000Fu, 0x64006400u), sa1, oa1);
-                        const int step = 8 * h + 2 * i;
-#pragma unroll
-                        for (int nt = 0; nt < NT; ++nt) {
-                            uint2 b = xb[((size_t)nt * kChunkUnits * 16 + step) * 32];
-                            mma_16816(d1[nt], a0, a1, a2, a3, b.x, b.y);
-                        }
-                        a0 = hfma2_u32(lop3_and_or(x0, 0x00F000F0u, 0x54005400u), sb0, ob0);
-                        a2 = hfma2_u32(lop3_and_or(x0s, 0x00F000F0u, 0x54005400u), sb0, ob0);
-                        a1 = hfma2_u32(lop3_and_or(x1, 0x00F000F0u, 0x54005400u), sb1, ob1);
-                        a3 = hfma2_u32(lop3_and_or(x1s, 0x00F000F0u, 0x54005400u), sb1, ob1);
-#pragma unroll
-                        for (int nt = 0; nt < NT; ++nt) {
-                            uint2 b = xb[((size_t)nt * kChunkUnits * 16 + step + 1) * 32];
-                            mma_16816(d1[nt], a0, a1, a2, a3, b.x, b.y);
-                        }
-                    }
-                }
-                // min term: one MMA of the 8 min codes against the 8 per-group activation sums
-                {
-                    const uint32_t mb = 2 * (t & 1);
-                    const uint32_t sel_m = 0x4040u | ((mb + 1) << 8) | mb;  // [m_2t, 0x64, m_2t+1, 0x64]
-                    const uint32_t ma0 = hsub2_u32(prmt(t < 2 ? mn_lo0 : mn_hi0, k64x4, sel_m), k1024);
-                    const uint32_t ma1 = hsub2_u32(prmt(t < 2 ? mn_lo1 : mn_hi1, k64x4, sel_m), k1024);
-                    const uint32_t *sxb = sxs + (size_t)stage * (S::stage_sx / 4) + (size_t)ul * 32 + lane;
-#pragma unroll
-                    for (int nt = 0; nt < NT; ++nt) mma_16816(d2[nt], ma0, ma1, 0u, 0u, sxb[(size_t)nt * kChunkUnits * 32], 0u);
-                }
-                const __half2 dd0 = u32_as_h2(hdr0.x), dd1 = u32_as_h2(hdr1.x);
-                const float d_0 = __low2float(dd0), dm_0 = __high2float(dd0), d_1 = __low2float(dd1), dm_1 = __high2float(dd1);
-#pragma unroll
-                for (int nt = 0; nt < NT; ++nt) {
-                    yacc[nt][0] += d_0 * (d1[nt][0] + d1[nt][1]) - dm_0 * (d2[nt][0] + d2[nt][1]);
-                    yacc[nt][1] += d_1 * (d1[nt][2] + d1[nt][3]) - dm_1 * (d2[nt][2] + d2[nt][3]);
-                }
-            } else if constexpr (TYPE == ZQ_Q8_0) {
-                const uint32_t hd0[4] = {hdr0.x, hdr0.y, hdr0.z, hdr0.w}, hd1[4] = {hdr1.x, hdr1.y, hdr1.z, hdr1.w};
-#pragma unroll
-                for (int h = 0; h < 4; ++h) {
-                    const uint4 pc0 = *reinterpret_cast<const uint4 *>(w0 + 16 + 16 * (t + 4 * h));
-                    const uint4 pc1 = *reinterpret_cast<const uint4 *>(w1 + 16 + 16 * (t + 4 * h));
-                    const uint32_t q0[4] = {pc0.x, pc0.y, pc0.z, pc0.w};
-                    const uint32_t q1[4] = {pc1.x, pc1.y, pc1.z, pc1.w};
-                    const __half2 s0 = u32_as_h2(hd0[h]), s1 = u32_as_h2(hd1[h]);  // scales of blocks 2h, 2h+1
-#pragma unroll
-                    for (int bb = 0; bb < 2; ++bb) {
-                        float acc[NT][4];
-#pragma unroll
-                        for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) acc[nt][j] = 0.f;
-#pragma unroll
-                        for (int e = 0; e < 2; ++e) {
-                            const int j = 2 * bb + e;
-                            // int8 -> exact f16: flip the sign bit (value + 128), splice under exponent 0x64, subtract 1152
-                            const uint32_t u0 = q0[j] ^ 0x80808080u, u1 = q1[j] ^ 0x80808080u;
-                            const uint32_t a0 = hsub2_u32(prmt(u0, 0x64646464u, 0x4240u), 0x64806480u);
-                            const uint32_t a2 = hsub2_u32(prmt(u0, 0x64646464u, 0x4341u), 0x64806480u);
-                            const uint32_t a1 = hsub2_u32(prmt(u1, 0x64646464u, 0x4240u), 0x64806480u);
-                            const uint32_t a3 = hsub2_u32(prmt(u1, 0x64646464u, 0x4341u), 0x64806480u);
-                            const int step = 4 * h + j;
-#pragma unroll
-                            for (int nt = 0; nt < NT; ++nt) {
-                                uint2 b = xb[((size_t)nt * kChunkUnits * 16 + step) * 32];
-                                mma_16816(acc[nt], a0, a1, a2, a3, b.x, b.y);
-                            }
-                        }
-                        const float sc0 = bb ? __high2float(s0) : __low2float(s0), sc1 = bb ? __high2float(s1) : __low2float(s1);
-#pragma unroll
-                        for (int nt = 0; nt < NT; ++nt) {
-                            yacc[nt][0] += sc0 * (acc[nt][0] + acc[nt][1]);
-                            yacc[nt][1] += sc1 * (acc[nt][2] + acc[nt][3]);
-                        }
-                    }
-                }
-            } else {  // Q4_0, IQ4_NL
-                const uint32_t hd0[4] = {hdr0.x, hdr0.y, hdr0.z, hdr0.w}, hd1[4] = {hdr1.x, hdr1.y, hdr1.z, hdr1.w};
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const uint4 pc0 = *reinterpret_cast<const uint4 *>(w0 + 16 + 16 * (t + 4 * h));
-                    const uint4 pc1 = *reinterpret_cast<const uint4 *>(w1 + 16 + 16 * (t + 4 * h));
-                    const uint32_t q0[4] = {pc0.x, pc0.y, pc0.z, pc0.w};
-                    const uint32_t q1[4] = {pc1.x, pc1.y, pc1.z, pc1.w};
-#pragma unroll
-                    for (int bb = 0; bb < 4; ++bb) {  // block 4h+bb, word t of its quants
-                        float acc[NT][4];
-#pragma unroll
-                        for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) acc[nt][j] = 0.f;
-                        const uint32_t x0 = q0[bb], x1 = q1[bb];
-#pragma unroll
-                        for (int e = 0; e < 2; ++e) {
-                            uint32_t a0, a1, a2, a3;
-                            if constexpr (TYPE == ZQ_Q4_0) {
-                                // e = 0: low nibbles (elements 4t..4t+3), e = 1: high nibbles (16+4t..); value = nibble - 8
-                                const uint32_t mask = e ? 0x00F000F0u : 0x000F000Fu, bias = e ? 0x54005400u : 0x64006400u;
-                                const uint32_t off = e ? 0x54805480u : 0x64086408u;  // 64+8 = 72, 1024+8 = 1032
-                                a0 = hsub2_u32(lop3_and_or(x0, mask, bias), off);
-                                a2 = hsub2_u32(lop3_and_or(x0 >> 8, mask, bias), off);
-                                a1 = hsub2_u32(lop3_and_or(x1, mask, bias), off);
-                                a3 = hsub2_u32(lop3_and_or(x1 >> 8, mask, bias), off);
-                            } else {
-                                // codebook pair of one byte = (element 4t+by, element 16+4t+by); step e takes bytes 2e, 2e+1
-                                const uint32_t *l = lut + lane;
-                                a0 = l[((x0 >> (16 * e)) & 0xFFu) * 32];
-                                a2 = l[((x0 >> (16 * e + 8)) & 0xFFu) * 32];
-                                a1 = l[((x1 >> (16 * e)) & 0xFFu) * 32];
-                                a3 = l[((x1 >> (16 * e + 8)) & 0xFFu) * 32];
-                            }
-                            const int step = 8 * h + 2 * bb + e;
-#pragma unroll
-                            for (int nt = 0; nt < NT; ++nt) {
-                                uint2 b = xb[((size_t)nt * kChunkUnits * 16 + step) * 32];
-                                mma_16816(acc[nt], a0, a1, a2, a3, b.x, b.y);
-                            }
-                        }
-                        const int blk = 4 * h + bb;
-                        const __half2 s0 = u32_as_h2(hd0[blk >> 1]), s1 = u32_as_h2(hd1[blk >> 1]);
-                        const float sc0 = (blk & 1) ? __high2float(s0) : __low2float(s0), sc1 = (blk & 1) ? __high2float(s1) : __low2float(s1);
-#pragma unroll
-                        for (int nt = 0; nt < NT; ++nt) {
-                            yacc[nt][0] += sc0 * (acc[nt][0] + acc[nt][1]);
-                            yacc[nt][1] += sc1 * (acc[nt][2] + acc[nt][3]);
-                        }
-                    }
-                }
-            }
+            const uint2 *sxb = sxs + (size_t)stage * (S::stage_sx / 8) + (size_t)ul * 32 + lane;
+            auto getb = [&](int nt, int step) -> uint2 { return xb[((size_t)nt * kChunkUnits * 16 + step) * 32]; };
+            auto getsx = [&](int nt) -> uint2 { return sxb[(size_t)nt * kChunkUnits * 32]; };
+            consume_unit<TYPE, NT>(w0, w1, t, lut + lane, getb, getsx, yacc);
         }
 
         if (nxt < n_items) store_x(nstage);
@@ -373,9 +220,17 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const __grid_cons
             // the two warps that share a row sub-tile add up through shared memory: red[ul][row][token]
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-                red[(ul * kTileRows + r0) * (NT * 4) + nt * 4 + t] = yacc[nt][0];
-                red[(ul * kTileRows + r0 + 8) * (NT * 4) + nt * 4 + t] = yacc[nt][1];
-                yacc[nt][0] = yacc[nt][1] = 0.f;
+                float *ra_ = red + (ul * kTileRows + r0) * (NT * 8), *rb_ = red + (ul * kTileRows + r0 + 8) * (NT * 8);
+                if (p.limbs == 2) {  // the thread's two columns are the limbs of activation row 4nt + t
+                    ra_[nt * 4 + t] = yacc[nt][0][0] + yacc[nt][0][1];
+                    rb_[nt * 4 + t] = yacc[nt][1][0] + yacc[nt][1][1];
+                } else {             // two activation rows: 8nt + 2t and 8nt + 2t + 1
+                    ra_[nt * 8 + 2 * t] = yacc[nt][0][0];
+                    ra_[nt * 8 + 2 * t + 1] = yacc[nt][0][1];
+                    rb_[nt * 8 + 2 * t] = yacc[nt][1][0];
+                    rb_[nt * 8 + 2 * t + 1] = yacc[nt][1][1];
+                }
+                yacc[nt][0][0] = yacc[nt][0][1] = yacc[nt][1][0] = yacc[nt][1][1] = 0.f;
             }
             __syncthreads();
             const long long tile_first = (long long)tile * p.chunks, tile_last = tile_first + p.chunks - 1;
@@ -387,7 +242,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const __grid_cons
                 float *slot = p.partials + ((size_t)blockIdx.x * 2 + which) * kSlotFloats;
                 for (int i = tid; i < kTileRows * p.m; i += kGemvThreads) {
                     int row = i & (kTileRows - 1), tok = i >> 7;
-                    slot[tok * kTileRows + row] = red[row * (NT * 4) + tok] + red[(kTileRows + row) * (NT * 4) + tok];
+                    slot[tok * kTileRows + row] = red[row * (NT * 8) + tok] + red[(kTileRows + row) * (NT * 8) + tok];
                 }
                 __syncthreads();
                 if (tid == 0) {
@@ -407,7 +262,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_kernel(const __grid_cons
                     int row = i & (kTileRows - 1), tok = i >> 7;
                     float v;
                     if (whole) {
-                        v = red[row * (NT * 4) + tok] + red[(kTileRows + row) * (NT * 4) + tok];
+                        v = red[row * (NT * 8) + tok] + red[(kTileRows + row) * (NT * 8) + tok];
                     } else {
                         v = 0.f;
                         for (int c = c_first; c <= c_last; ++c) {  // fixed order: deterministic
@@ -469,7 +324,7 @@ static int launch_one(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, co
 template <uint32_t TYPE>
 static int launch_type(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const GemvParams &p, int grid, zq_error *err) {
     const bool gated = w_up != nullptr;
-    if (p.m <= 4) return gated ? launch_one<TYPE, 1, true>(ctx, w, w_up, p, grid, err) : launch_one<TYPE, 1, false>(ctx, w, w_up, p, grid, err);
+    if (p.m * p.limbs <= 8) return gated ? launch_one<TYPE, 1, true>(ctx, w, w_up, p, grid, err) : launch_one<TYPE, 1, false>(ctx, w, w_up, p, grid, err);
     return gated ? launch_one<TYPE, 2, true>(ctx, w, w_up, p, grid, err) : launch_one<TYPE, 2, false>(ctx, w, w_up, p, grid, err);
 }
 
@@ -497,9 +352,13 @@ int launch_gemv(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const vo
     // split, so the partial-tile hand-over (several microseconds of fences and atomics per launch) disappears.
     if (p.tiles <= ctx->sm_count && p.tiles * 100 >= ctx->sm_count * 85) grid = p.tiles;
     if (grid <= 0) return ZQ_OK;
-    for (size_t m0 = 0; m0 < m; m0 += kMaxGemvRows) {
-        size_t mm = m - m0 < (size_t)kMaxGemvRows ? m - m0 : (size_t)kMaxGemvRows;
+    // up to 8 rows per pass as two f16 limbs each (f32-level accuracy); 9..16 rows go in one pass as single f16
+    // limbs (the reference's CUDA path takes f16 activations throughout, src/kernel/cuda/linear.rs:1440)
+    const size_t per_pass = m > 8 ? 16 : 8;
+    for (size_t m0 = 0; m0 < m; m0 += per_pass) {
+        size_t mm = m - m0 < per_pass ? m - m0 : per_pass;
         p.m = (int)mm;
+        p.limbs = mm > 8 ? 1 : 2;
         p.x = reinterpret_cast<const uint8_t *>(x) + m0 * w->cols * dtype_size(x_dtype);
         p.y = reinterpret_cast<uint8_t *>(y) + m0 * w->rows * dtype_size(y_dtype);
         p.residual = residual ? reinterpret_cast<const uint8_t *>(residual) + m0 * w->rows * dtype_size(y_dtype) : nullptr;
@@ -536,7 +395,7 @@ int launch_gemv(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const vo
 // stream-ordered region that forbids allocator calls, a real-time loop with a fixed memory budget, or a plugin
 // whose host application owns the allocator.  For them the split-tile fix-up scratch of the decode GEMV (partial
 // tiles + per-tile arrival counters) lives in the two file-scope device arrays below instead of in memory the
-// context allocated.  Every GPU that loads the library holds these ~1.3 MB until the process exits.
+// context allocated.  Every GPU that loads the library holds these ~2.6 MB until the process exits.
 //
 // In host code the array names are host-side stand-ins, not device addresses; the device addresses are looked
 // up once per device with cudaGetSymbolAddress (with that device current) and passed to the kernel.
@@ -579,7 +438,7 @@ static int static_scratch_for(zq_ctx *ctx, StaticScratch **out, zq_error *err) {
 
 // y[m, n] = x[m, k] W^T for 1..8 activation rows, one launch, scratch in the static device arrays.
 int launch_gemv_noalloc(zq_ctx *ctx, const zq_weight *w, const void *x, int x_dtype, size_t m, void *y, int y_dtype, zq_error *err) {
-    if (m == 0 || m > (size_t)kMaxGemvRows) return set_error(err, ZQ_ERR_SHAPE, "zq_linear_noalloc handles 1..%d activation rows per call, got %zu", kMaxGemvRows, m);
+    if (m == 0 || m > 8) return set_error(err, ZQ_ERR_SHAPE, "zq_linear_noalloc handles 1..8 activation rows per call, got %zu", m);
     if (ctx->sm_count > kStaticMaxSms) return set_error(err, ZQ_ERR_UNSUPPORTED, "zq_linear_noalloc: device has %d SMs, the static scratch is sized for %d", ctx->sm_count, kStaticMaxSms);
     const FormatInfo f = format_info(w->type);
     GemvParams p;
@@ -590,6 +449,7 @@ int launch_gemv_noalloc(zq_ctx *ctx, const zq_weight *w, const void *x, int x_dt
     p.x_dtype = x_dtype;
     p.y_dtype = y_dtype;
     p.m = (int)m;
+    p.limbs = 2;
     p.cols = (int)w->cols;
     p.n_out = (int)w->rows;
     p.tiles = (int)((w->rows + kTileRows - 1) / kTileRows);

@@ -10,7 +10,7 @@ constexpr int kTileRows = 128;
 constexpr int kChunkUnits = 2;
 constexpr int kChunkCols = kChunkUnits * kUnitWeights;  // 512
 constexpr int kGemvThreads = 512;                       // 16 warps: 8 row sub-tiles x 2 units
-constexpr int kMaxGemvRows = 8;
+constexpr int kMaxGemvRows = 16;                        // 8 rows with two f16 limbs each, or 16 rows with one limb
 constexpr int kSlotFloats = kTileRows * kMaxGemvRows;   // one partial tile in the fix-up scratch
 
 template <uint32_t TYPE> struct Fmt;
@@ -20,15 +20,16 @@ template <> struct Fmt<ZQ_IQ4_NL> { static constexpr int unit_bytes = 144; stati
 template <> struct Fmt<ZQ_Q8_0> { static constexpr int unit_bytes = 272; static constexpr int stages = 2; static constexpr bool lut = false; };
 
 template <uint32_t TYPE, int NT> struct GemvSmem {
+    static constexpr int stages = (NT == 2 && Fmt<TYPE>::stages > 3) ? 3 : Fmt<TYPE>::stages;  // two column tiles need room
     static constexpr int pitch = kChunkUnits * Fmt<TYPE>::unit_bytes;
     static constexpr int stage_w = kTileRows * pitch;
     static constexpr int stage_x = NT * kChunkUnits * 16 * 32 * 8;
-    static constexpr int stage_sx = NT * kChunkUnits * 32 * 4;
+    static constexpr int stage_sx = NT * kChunkUnits * 32 * 8;  // per lane: (hi limbs, lo limbs) of two group sums
     static constexpr int off_w = 0;
-    static constexpr int off_x = off_w + Fmt<TYPE>::stages * stage_w;
-    static constexpr int off_sx = off_x + Fmt<TYPE>::stages * stage_x;
-    static constexpr int off_red = off_sx + Fmt<TYPE>::stages * stage_sx;
-    static constexpr int red_bytes = 2 * kTileRows * NT * 4 * 4;
+    static constexpr int off_x = off_w + stages * stage_w;
+    static constexpr int off_sx = off_x + stages * stage_x;
+    static constexpr int off_red = off_sx + stages * stage_sx;
+    static constexpr int red_bytes = 2 * kTileRows * NT * 8 * 4;  // [unit half][row][up to 8 columns per tile] f32
     static constexpr int off_lut = off_red + red_bytes;
     static constexpr int lut_bytes = Fmt<TYPE>::lut ? 256 * 32 * 4 : 0;
     static constexpr int off_bar = off_lut + lut_bytes;
@@ -43,7 +44,8 @@ struct GemvParams {
     uint32_t *counters;
     uint32_t *status;
     int x_dtype, y_dtype;
-    int m;                // 1..8
+    int m;                // 1..8 rows as two f16 limbs each, or 9..16 rows as one limb each
+    int limbs;            // 2 or 1
     int cols;             // logical K
     int n_out;            // output features (rows of W; for gated: rows of gate == rows of up)
     int tiles;            // ceil(n_out / rows_per_tile)
@@ -92,12 +94,14 @@ __device__ __forceinline__ void mma_16816_zero(float (&d)[4], uint32_t a0, uint3
 // One unit (256 weights) of the two fragment rows a thread owns -> MMAs.
 //   w0 / w1   shared-memory address of the unit in fragment rows g and g+8
 //   getb      (nt, step) -> the thread's B fragment {b0, b1} of MMA step `step` for column tile nt
-//   getsx     (nt) -> the thread's B fragment of the per-group activation sums (Q4_K only)
-//   yacc      running sums [nt][row g / row g+8]; the thread's column pair (2t, 2t+1) holds the two limbs of one
-//             activation row, so limb sums are added here.
+//   getsx     (nt) -> the thread's B fragment {hi limbs, lo limbs} of the per-group activation sums (Q4_K only);
+//             the min-term MMA pairs the 8 min codes with the hi limbs (K slots 0..7) and again with the lo limbs
+//             (K slots 8..15), so the sums keep two limbs whatever the activations use
+//   yacc      running sums [nt][row g / row g+8][column 2t / 2t+1]; the two columns are the two limbs of one
+//             activation row, or two activation rows when each row is staged as a single limb.
 // Q4_K spreads its 32 dependent MMAs over CH independent accumulator chains.
 template <uint32_t TYPE, int NT, class GetB, class GetSx>
-__device__ __forceinline__ void consume_unit(const uint8_t *w0, const uint8_t *w1, int t, const uint32_t *lut_lane, GetB getb, GetSx getsx, float (&yacc)[NT][2]) {
+__device__ __forceinline__ void consume_unit(const uint8_t *w0, const uint8_t *w1, int t, const uint32_t *lut_lane, GetB getb, GetSx getsx, float (&yacc)[NT][2][2]) {
     const uint4 hdr0 = *reinterpret_cast<const uint4 *>(w0);
     const uint4 hdr1 = *reinterpret_cast<const uint4 *>(w1);
     if constexpr (TYPE == ZQ_Q4_K) {
@@ -161,20 +165,27 @@ __device__ __forceinline__ void consume_unit(const uint8_t *w0, const uint8_t *w
             const uint32_t ma0 = hsub2_u32(prmt(t < 2 ? mn_lo0 : mn_hi0, k64x4, sel_m), k1024);
             const uint32_t ma1 = hsub2_u32(prmt(t < 2 ? mn_lo1 : mn_hi1, k64x4, sel_m), k1024);
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) mma_16816(d2[nt], ma0, ma1, 0u, 0u, getsx(nt), 0u);
+            for (int nt = 0; nt < NT; ++nt) {
+                const uint2 sx = getsx(nt);
+                mma_16816(d2[nt], ma0, ma1, ma0, ma1, sx.x, sx.y);
+            }
         }
         const __half2 dd0 = u32_as_h2(hdr0.x), dd1 = u32_as_h2(hdr1.x);
         const float d_0 = __low2float(dd0), dm_0 = __high2float(dd0), d_1 = __low2float(dd1), dm_1 = __high2float(dd1);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-            float s0 = 0.f, s1 = 0.f;
+            float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
 #pragma unroll
             for (int c = 0; c < CH; ++c) {
-                s0 += d1[nt][c][0] + d1[nt][c][1];
-                s1 += d1[nt][c][2] + d1[nt][c][3];
+                a0 += d1[nt][c][0];
+                a1 += d1[nt][c][1];
+                b0 += d1[nt][c][2];
+                b1 += d1[nt][c][3];
             }
-            yacc[nt][0] += d_0 * s0 - dm_0 * (d2[nt][0] + d2[nt][1]);
-            yacc[nt][1] += d_1 * s1 - dm_1 * (d2[nt][2] + d2[nt][3]);
+            yacc[nt][0][0] += d_0 * a0 - dm_0 * d2[nt][0];
+            yacc[nt][0][1] += d_0 * a1 - dm_0 * d2[nt][1];
+            yacc[nt][1][0] += d_1 * b0 - dm_1 * d2[nt][2];
+            yacc[nt][1][1] += d_1 * b1 - dm_1 * d2[nt][3];
         }
     } else if constexpr (TYPE == ZQ_Q8_0) {
         const uint32_t hd0[4] = {hdr0.x, hdr0.y, hdr0.z, hdr0.w}, hd1[4] = {hdr1.x, hdr1.y, hdr1.z, hdr1.w};
@@ -207,8 +218,10 @@ __device__ __forceinline__ void consume_unit(const uint8_t *w0, const uint8_t *w
                 const float sc0 = bb ? __high2float(s0) : __low2float(s0), sc1 = bb ? __high2float(s1) : __low2float(s1);
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
-                    yacc[nt][0] += sc0 * (acc[nt][0] + acc[nt][1]);
-                    yacc[nt][1] += sc1 * (acc[nt][2] + acc[nt][3]);
+                    yacc[nt][0][0] += sc0 * acc[nt][0];
+                    yacc[nt][0][1] += sc0 * acc[nt][1];
+                    yacc[nt][1][0] += sc1 * acc[nt][2];
+                    yacc[nt][1][1] += sc1 * acc[nt][3];
                 }
             }
         }
@@ -253,8 +266,10 @@ __device__ __forceinline__ void consume_unit(const uint8_t *w0, const uint8_t *w
                 const float sc0 = (blk & 1) ? __high2float(s0) : __low2float(s0), sc1 = (blk & 1) ? __high2float(s1) : __low2float(s1);
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
-                    yacc[nt][0] += sc0 * (acc[nt][0] + acc[nt][1]);
-                    yacc[nt][1] += sc1 * (acc[nt][2] + acc[nt][3]);
+                    yacc[nt][0][0] += sc0 * acc[nt][0];
+                    yacc[nt][0][1] += sc0 * acc[nt][1];
+                    yacc[nt][1][0] += sc1 * acc[nt][2];
+                    yacc[nt][1][1] += sc1 * acc[nt][3];
                 }
             }
         }

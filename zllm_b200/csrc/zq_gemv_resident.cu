@@ -60,7 +60,7 @@ __global__ void __launch_bounds__(kResidentThreads, 1) gemv_resident_kernel(cons
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
     uint8_t *ws = smem;
     uint2 *xs = reinterpret_cast<uint2 *>(smem + ra.off_x);
-    __half *sxs = reinterpret_cast<__half *>(smem + ra.off_sx);
+    uint2 *sxs = reinterpret_cast<uint2 *>(smem + ra.off_sx);
     float *red = reinterpret_cast<float *>(smem + ra.off_red);
     uint32_t *lut = reinterpret_cast<uint32_t *>(smem + ra.off_lut);
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + ra.off_bar);
@@ -111,13 +111,18 @@ __global__ void __launch_bounds__(kResidentThreads, 1) gemv_resident_kernel(cons
     // ---------------------------------------------------- consumers
     const int g = lane >> 2, t = lane & 3;
     const int rs = warp & 7, ul = warp >> 3;
-    const int cols2 = 2 * p.m;  // staged MMA columns: (hi, lo) limb per activation row
+    const int limbs = p.limbs;
+    const int cols2 = limbs * p.m;  // staged MMA columns: (hi, lo) limb per activation row, or one column per row
 
     if constexpr (Fmt<TYPE>::lut) {
         for (int i = tid; i < 256 * 32; i += kConsumerThreads) {
             int b = i >> 5;
             lut[i] = h2_as_u32(__halves2half2(__int2half_rn(kIq4nlValues[b & 15]), __int2half_rn(kIq4nlValues[b >> 4])));
         }
+    }
+    if constexpr (TYPE == ZQ_Q4_K) {
+        for (int i = tid; i < (ra.off_red - ra.off_sx) / 8; i += kConsumerThreads) sxs[i] = make_uint2(0u, 0u);
+        __syncthreads();
     }
     {
         // stage every activation quad: B-fragment slot (unit, step, column, t); Q4_K also gets per-group sums
@@ -148,7 +153,8 @@ __global__ void __launch_bounds__(kResidentThreads, 1) gemv_resident_kernel(cons
                 lo[j] = __float2half_rn(v[j] - __half2float(hi[j]));
             }
             const int unit = k0 >> 8, i = k0 & 255;
-            const int col = 2 * m;
+            const int col = limbs * m;
+            const bool two = limbs == 2;
             if constexpr (TYPE == ZQ_IQ4_NL) {
                 const int blk = i >> 5, nib = (i >> 4) & 1, tt = (i >> 2) & 3;
                 const int step0 = 8 * (blk >> 2) + 2 * (blk & 3);
@@ -156,19 +162,23 @@ __global__ void __launch_bounds__(kResidentThreads, 1) gemv_resident_kernel(cons
                 for (int by = 0; by < 4; ++by) {
                     const int step = step0 + (by >> 1);
                     __half *dh = reinterpret_cast<__half *>(&xs[((size_t)(unit * 16 + step) * cols2 + col) * 4 + tt]);
-                    __half *dl = reinterpret_cast<__half *>(&xs[((size_t)(unit * 16 + step) * cols2 + col + 1) * 4 + tt]);
+                    __half *dl = reinterpret_cast<__half *>(&xs[((size_t)(unit * 16 + step) * cols2 + col + (two ? 1 : 0)) * 4 + tt]);
                     dh[(by & 1) * 2 + nib] = hi[by];
-                    dl[(by & 1) * 2 + nib] = lo[by];
+                    if (two) dl[(by & 1) * 2 + nib] = lo[by];
                 }
             } else {
                 int step, tt;
                 quad_slot<TYPE>(i, step, tt);
                 uint2 *base = &xs[(size_t)(unit * 16 + step) * cols2 * 4];
                 base[col * 4 + tt] = make_uint2(h2_as_u32(__halves2half2(hi[0], hi[2])), h2_as_u32(__halves2half2(hi[1], hi[3])));
-                base[(col + 1) * 4 + tt] = make_uint2(h2_as_u32(__halves2half2(lo[0], lo[2])), h2_as_u32(__halves2half2(lo[1], lo[3])));
+                if (two) base[(col + 1) * 4 + tt] = make_uint2(h2_as_u32(__halves2half2(lo[0], lo[2])), h2_as_u32(__halves2half2(lo[1], lo[3])));
             }
             if constexpr (TYPE == ZQ_Q4_K) {
-                float sum = (v[0] + v[1]) + (v[2] + v[3]);
+                // sums of the values the MMAs really see (the staged limbs), so that the scale and min terms cancel
+                // exactly as in the reference's per-element form
+                float sum = 0.f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) sum += __half2float(hi[j]) + (two ? __half2float(lo[j]) : 0.f);
                 sum += __shfl_xor_sync(0xffffffffu, sum, 1);
                 sum += __shfl_xor_sync(0xffffffffu, sum, 2);
                 sum += __shfl_xor_sync(0xffffffffu, sum, 4);
@@ -176,18 +186,20 @@ __global__ void __launch_bounds__(kResidentThreads, 1) gemv_resident_kernel(cons
                     const int G8 = i >> 5;
                     const __half shi = __float2half_rn(sum);
                     const __half slo = __float2half_rn(sum - __half2float(shi));
-                    // fragment of the min-term MMA: lane (column, t') holds (sum of group 2t', sum of group 2t'+1)
-                    sxs[(((size_t)unit * cols2 + col) * 4 + (G8 >> 1)) * 2 + (G8 & 1)] = shi;
-                    sxs[(((size_t)unit * cols2 + col + 1) * 4 + (G8 >> 1)) * 2 + (G8 & 1)] = slo;
+                    // fragment of the min-term MMA: lane (column, t') holds .x = hi limbs of sums 2t', 2t'+1 and .y = their
+                    // lo limbs; the sums ride in the row's first column (a lo-limb column keeps zeros)
+                    __half *dst = reinterpret_cast<__half *>(&sxs[((size_t)unit * cols2 + col) * 4 + (G8 >> 1)]);
+                    dst[G8 & 1] = shi;
+                    dst[2 + (G8 & 1)] = slo;
                 }
             }
         }
     }
     consumer_bar();
 
-    float yacc[NT][2];
+    float yacc[NT][2][2];
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) yacc[nt][0] = yacc[nt][1] = 0.f;
+    for (int nt = 0; nt < NT; ++nt) yacc[nt][0][0] = yacc[nt][0][1] = yacc[nt][1][0] = yacc[nt][1][1] = 0.f;
     const int r0 = 16 * rs + frag_row(g);
 
     for (int it = 0; it < n_items; ++it) {
@@ -211,14 +223,14 @@ __global__ void __launch_bounds__(kResidentThreads, 1) gemv_resident_kernel(cons
             const uint8_t *w0 = ws + (size_t)stage * S::stage_w + (size_t)r0 * S::pitch + ul * UB;
             const uint8_t *w1 = w0 + 8 * S::pitch;
             const uint2 *xu = xs + (size_t)unit * 16 * cols2 * 4 + t;
-            const uint32_t *sxu = reinterpret_cast<const uint32_t *>(sxs) + (size_t)unit * cols2 * 4 + t;
+            const uint2 *sxu = sxs + (size_t)unit * cols2 * 4 + t;
             auto getb = [&](int nt, int step) -> uint2 {
                 const int col = 8 * nt + g;
                 return col < cols2 ? xu[(step * cols2 + col) * 4] : make_uint2(0u, 0u);
             };
-            auto getsx = [&](int nt) -> uint32_t {
+            auto getsx = [&](int nt) -> uint2 {
                 const int col = 8 * nt + g;
-                return col < cols2 ? sxu[col * 4] : 0u;
+                return col < cols2 ? sxu[col * 4] : make_uint2(0u, 0u);
             };
             consume_unit<TYPE, NT>(w0, w1, t, lut + lane, getb, getsx, yacc);
         }
@@ -233,15 +245,23 @@ __global__ void __launch_bounds__(kResidentThreads, 1) gemv_resident_kernel(cons
         // the two warps that share a row sub-tile add up through shared memory: red[ul][row][token]
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-            red[(ul * kTileRows + r0) * (NT * 4) + nt * 4 + t] = yacc[nt][0];
-            red[(ul * kTileRows + r0 + 8) * (NT * 4) + nt * 4 + t] = yacc[nt][1];
+            float *ra_ = red + (ul * kTileRows + r0) * (NT * 8), *rb_ = red + (ul * kTileRows + r0 + 8) * (NT * 8);
+            if (limbs == 2) {  // the thread's two columns are the limbs of activation row 4nt + t
+                ra_[nt * 4 + t] = yacc[nt][0][0] + yacc[nt][0][1];
+                rb_[nt * 4 + t] = yacc[nt][1][0] + yacc[nt][1][1];
+            } else {           // two activation rows: 8nt + 2t and 8nt + 2t + 1
+                ra_[nt * 8 + 2 * t] = yacc[nt][0][0];
+                ra_[nt * 8 + 2 * t + 1] = yacc[nt][0][1];
+                rb_[nt * 8 + 2 * t] = yacc[nt][1][0];
+                rb_[nt * 8 + 2 * t + 1] = yacc[nt][1][1];
+            }
         }
         consumer_bar();
         float vals[(kTileRows * kMaxGemvRows + kConsumerThreads - 1) / kConsumerThreads];
         int cnt = 0;
         for (int i = tid; i < kTileRows * p.m; i += kConsumerThreads, ++cnt) {
             int row = i & (kTileRows - 1), tok = i >> 7;
-            vals[cnt] = red[row * (NT * 4) + tok] + red[(kTileRows + row) * (NT * 4) + tok];
+            vals[cnt] = red[row * (NT * 8) + tok] + red[(kTileRows + row) * (NT * 8) + tok];
         }
         consumer_bar();
         cnt = 0;
@@ -286,7 +306,7 @@ __global__ void __launch_bounds__(kResidentThreads, 1) gemv_resident_kernel(cons
 // Plan of the resident variant: CTAs per tile (cluster size) and shared-memory layout; returns false when fewer
 // than two ring stages would fit beside the staged activation slice.
 template <uint32_t TYPE, int NT>
-static bool plan_resident(int m, int units_total, int tiles, int chunks, int sm_count, ResidentArgs &ra, int &total_bytes) {
+static bool plan_resident(int cols2, int units_total, int tiles, int chunks, int sm_count, ResidentArgs &ra, int &total_bytes) {
     using S = GemvSmem<TYPE, NT>;
     int split = 1;
     while (split < 8 && tiles * split * 2 <= sm_count && split * 2 <= chunks) split *= 2;
@@ -294,8 +314,8 @@ static bool plan_resident(int m, int units_total, int tiles, int chunks, int sm_
     int slice_units = slice_chunks * kChunkUnits;
     if (slice_units > units_total) slice_units = units_total;
     const int max_smem = 232448 - 256;  // 227 KB opt-in limit minus static shared and alignment slack
-    const int x_bytes = slice_units * 16 * (2 * m) * 4 * 8;
-    const int sx_bytes = TYPE == ZQ_Q4_K ? slice_units * (2 * m) * 4 * 4 : 0;
+    const int x_bytes = slice_units * 16 * cols2 * 4 * 8;
+    const int sx_bytes = TYPE == ZQ_Q4_K ? slice_units * cols2 * 4 * 8 : 0;
     const int fixed = x_bytes + sx_bytes + S::red_bytes + S::lut_bytes + 128 + 128;
     int stages = (max_smem - fixed) / S::stage_w;
     if (stages > 5) stages = 5;
@@ -318,7 +338,7 @@ static int launch_resident_one(zq_ctx *ctx, const zq_weight *w, const zq_weight 
     (void)grid;
     ResidentArgs ra;
     int total = 0;
-    taken = plan_resident<TYPE, NT>(p.m, (int)w->units_per_row, p.tiles, p.chunks, ctx->sm_count, ra, total);
+    taken = plan_resident<TYPE, NT>(p.m * p.limbs, (int)w->units_per_row, p.tiles, p.chunks, ctx->sm_count, ra, total);
     if (!taken) return ZQ_OK;
     auto kernel = gemv_resident_kernel<TYPE, NT, GATED>;
     static bool configured[64] = {};
@@ -349,7 +369,7 @@ static int launch_resident_one(zq_ctx *ctx, const zq_weight *w, const zq_weight 
 template <uint32_t TYPE>
 static int launch_resident_type(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const GemvParams &p, int grid, bool &taken, zq_error *err) {
     const bool gated = w_up != nullptr;
-    if (p.m <= 4) return gated ? launch_resident_one<TYPE, 1, true>(ctx, w, w_up, p, grid, taken, err) : launch_resident_one<TYPE, 1, false>(ctx, w, w_up, p, grid, taken, err);
+    if (p.m * p.limbs <= 8) return gated ? launch_resident_one<TYPE, 1, true>(ctx, w, w_up, p, grid, taken, err) : launch_resident_one<TYPE, 1, false>(ctx, w, w_up, p, grid, taken, err);
     return gated ? launch_resident_one<TYPE, 2, true>(ctx, w, w_up, p, grid, taken, err) : launch_resident_one<TYPE, 2, false>(ctx, w, w_up, p, grid, taken, err);
 }
 

@@ -34,6 +34,7 @@
 namespace zq {
 
 constexpr int kQmvThreads = 13 * 32;
+constexpr int kQmvRows = 8;  // activation rows per launch (two f16 limbs each fill the 16 MMA columns)
 constexpr int kQmvWStages = 10;  // ~170 KB of packed rows in flight per SM: HBM latency x bandwidth needs that much
 constexpr int kQmvXStages = 3;
 constexpr int kQmvXWarps = 3;
@@ -41,7 +42,7 @@ constexpr int kQmvB1Bytes = 16 * 256 * 2;   // 16 operand rows (8 activation row
 constexpr int kQmvB2Bytes = 16 * 16 * 2;    // 16 operand rows x 16 (8 group sums + 8 zero)
 constexpr int kQmvXStageBytes = kQmvB1Bytes + kQmvB2Bytes;
 constexpr int kQmvWStageBytes = kTileRows * 144;
-constexpr int kQmvRedFloats = 2 * 2 * kMaxGemvRows * kTileRows;  // [tile parity][group][row of x][weight row]
+constexpr int kQmvRedFloats = 2 * 2 * kQmvRows * kTileRows;  // [tile parity][group][row of x][weight row]
 constexpr int kQmvOffX = kQmvWStages * kQmvWStageBytes;
 constexpr int kQmvOffRed = kQmvOffX + kQmvXStages * kQmvXStageBytes;
 constexpr int kQmvOffBar = kQmvOffRed + kQmvRedFloats * 4;
@@ -195,13 +196,13 @@ __global__ void __launch_bounds__(kQmvThreads, 1) qmv_q4k_kernel(const __grid_co
         const int xw = warp - 2;
         const int a = lane;  // 8-column chunk of the unit: columns 8a .. 8a+7 (group a/4, words 2(a%4), 2(a%4)+1)
         const int g = a >> 2, i0 = 2 * (a & 3);
-        float v[kMaxGemvRows][8];
+        float v[kQmvRows][8];
         auto fetch = [&](int it) {
             const long long item = begin + it;
             const int unit = (int)(item % units);
             const size_t k0 = (size_t)unit * 256 + 8 * a;
 #pragma unroll
-            for (int m = 0; m < kMaxGemvRows; ++m) {
+            for (int m = 0; m < kQmvRows; ++m) {
                 if (m < p.m) {
                     const size_t o = (size_t)m * p.cols + k0;
                     if (p.x_dtype == ZQ_F32) {
@@ -221,7 +222,7 @@ __global__ void __launch_bounds__(kQmvThreads, 1) qmv_q4k_kernel(const __grid_co
             uint8_t *stage = xs + (size_t)xsidx * kQmvXStageBytes;
             if (it >= kQmvXStages) qmv_wait(&x_empty[xsidx], ((it / kQmvXStages) - 1) & 1, abort_flag, p.status, kStatusMmaTimeout);
 #pragma unroll
-            for (int m = 0; m < kMaxGemvRows; ++m) {
+            for (int m = 0; m < kQmvRows; ++m) {
                 if (m < p.m) {
                     __half hi[8], lo[8];
                     float sum = 0.f;
@@ -353,22 +354,22 @@ __global__ void __launch_bounds__(kQmvThreads, 1) qmv_q4k_kernel(const __grid_co
             const bool tile_ends = (it == n_items - 1) || ((int)((item + 1) / units) != tile);
             if (tile_ends) {
                 collect();
-                float *rb = red + (size_t)tile_parity * (2 * kMaxGemvRows * kTileRows) + (size_t)wg * (kMaxGemvRows * kTileRows);
+                float *rb = red + (size_t)tile_parity * (2 * kQmvRows * kTileRows) + (size_t)wg * (kQmvRows * kTileRows);
 #pragma unroll
-                for (int m = 0; m < kMaxGemvRows; ++m) {
+                for (int m = 0; m < kQmvRows; ++m) {
                     rb[m * kTileRows + row_in_tile] = yacc[2 * m] + yacc[2 * m + 1];
                     yacc[2 * m] = yacc[2 * m + 1] = 0.f;
                 }
                 named_bar(1, 256);
                 if (wg == 0) {
-                    const float *r0p = red + (size_t)tile_parity * (2 * kMaxGemvRows * kTileRows);
-                    const float *r1p = r0p + kMaxGemvRows * kTileRows;
+                    const float *r0p = red + (size_t)tile_parity * (2 * kQmvRows * kTileRows);
+                    const float *r1p = r0p + kQmvRows * kTileRows;
                     const long long tile_first = (long long)tile * units, tile_last = tile_first + units - 1;
                     const bool whole = begin <= tile_first && tile_last < end;
                     const int c_first = (int)(((tile_first + 1) * G - 1) / T), c_last = (int)(((tile_last + 1) * G - 1) / T);
-                    float vals[kMaxGemvRows];
+                    float vals[kQmvRows];
 #pragma unroll
-                    for (int m = 0; m < kMaxGemvRows; ++m) vals[m] = r0p[m * kTileRows + row_in_tile] + r1p[m * kTileRows + row_in_tile];
+                    for (int m = 0; m < kQmvRows; ++m) vals[m] = r0p[m * kTileRows + row_in_tile] + r1p[m * kTileRows + row_in_tile];
                     bool finish = whole;
                     if (!whole) {
                         const int which = (tile == (int)(begin / units)) ? 0 : 1;
@@ -421,7 +422,7 @@ __global__ void __launch_bounds__(kQmvThreads, 1) qmv_q4k_kernel(const __grid_co
 // One launch for up to 8 activation rows of a Q4_K weight; `taken` is false when the shape is not eligible.
 int launch_qmv(zq_ctx *ctx, const zq_weight *w, const GemvParams &p_in, bool &taken, zq_error *err) {
     taken = false;
-    if (w->type != ZQ_Q4_K) return ZQ_OK;
+    if (w->type != ZQ_Q4_K || p_in.m > kQmvRows || p_in.limbs != 2) return ZQ_OK;
     GemvParams p = p_in;
     p.chunks = (int)w->units_per_row;
     p.tiles = (int)((w->rows + kTileRows - 1) / kTileRows);
