@@ -113,6 +113,67 @@ __global__ void dequantize_kernel(uint32_t type, const uint8_t *__restrict__ res
     }
 }
 
+// All rows -> f16 [rows, cols], one thread per 8 consecutive elements (one 16-byte store): the operand pass of the
+// prefill GEMM.  Each value is the reference's f32 value (same operation order as decode_unit_element) rounded once.
+__global__ void dequantize_f16_kernel(uint32_t type, const uint8_t *__restrict__ resident, size_t row_pitch, int unit_bytes, size_t rows, size_t cols, __half *__restrict__ out) {
+    const size_t oct_per_row = cols / 8;
+    const size_t total = rows * oct_per_row;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t row = idx / oct_per_row;
+        const size_t k0 = (idx - row * oct_per_row) * 8;
+        const uint8_t *unit = resident + row * row_pitch + (k0 / kUnitWeights) * unit_bytes;
+        const int i0 = (int)(k0 % kUnitWeights);
+        float v[8];
+        if (type == ZQ_Q4_K) {
+            const uint4 hdr = *reinterpret_cast<const uint4 *>(unit);
+            const __half2 dd = *reinterpret_cast<const __half2 *>(&hdr.x);
+            const float d = __low2float(dd), dmin = __high2float(dd);
+            const uint8_t *scales = reinterpret_cast<const uint8_t *>(&hdr.y);
+            const int g = i0 >> 5, j0 = i0 & 31;
+            int sc, mn;
+            if (g < 4) {
+                sc = scales[g] & 0x3f;
+                mn = scales[g + 4] & 0x3f;
+            } else {
+                sc = (scales[g + 4] & 0x0f) | ((scales[g - 4] >> 6) << 4);
+                mn = (scales[g + 4] >> 4) | ((scales[g] >> 6) << 4);
+            }
+            const float dsc = __fmul_rn(d, (float)sc), dm = __fmul_rn(dmin, (float)mn);
+            const uint2 qw = *reinterpret_cast<const uint2 *>(unit + 16 + (g >> 1) * 32 + j0);
+            const int shift = (g & 1) * 4;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const uint32_t word = j < 4 ? qw.x : qw.y;
+                const int q = (word >> (8 * (j & 3) + shift)) & 0x0f;
+                v[j] = __fsub_rn(__fmul_rn(dsc, (float)q), dm);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = decode_unit_element(type, unit, i0 + j);
+        }
+        uint4 packed;
+        packed.x = h2_as_u32(__floats2half2_rn(v[0], v[1]));
+        packed.y = h2_as_u32(__floats2half2_rn(v[2], v[3]));
+        packed.z = h2_as_u32(__floats2half2_rn(v[4], v[5]));
+        packed.w = h2_as_u32(__floats2half2_rn(v[6], v[7]));
+        *reinterpret_cast<uint4 *>(out + row * cols + k0) = packed;
+    }
+}
+
+int launch_dequantize_f16(zq_ctx *ctx, const zq_weight *w, __half *out, zq_error *err) {
+    if (w->cols % 8) return set_error(err, ZQ_ERR_SHAPE, "f16 operand pass needs columns aligned to 8, got %zu", w->cols);
+    const size_t total = w->rows * (w->cols / 8);
+    if (total == 0) return ZQ_OK;
+    const int threads = 256;
+    size_t blocks = (total + threads - 1) / threads;
+    if (blocks > (size_t)ctx->sm_count * 32) blocks = (size_t)ctx->sm_count * 32;
+    const FormatInfo f = format_info(w->type);
+    dequantize_f16_kernel<<<(unsigned)blocks, threads, 0, ctx->stream>>>(w->type, w->data, w->row_pitch, f.unit_bytes, w->rows, w->cols, out);
+    ctx->launches++;
+    ZQ_CUDA_CHECK(cudaGetLastError(), err);
+    return ZQ_OK;
+}
+
 int launch_dequantize(zq_ctx *ctx, const zq_weight *w, const uint32_t *row_ids, size_t n_rows, void *out, int out_dtype, zq_error *err) {
     size_t total = n_rows * (w->cols / 4);
     if (total == 0) return ZQ_OK;

@@ -249,6 +249,7 @@ int make_weight_map(const zq_weight *w, int box_words, int box_rows, CUtensorMap
 // Launchers implemented in the .cu files.
 int launch_repack(zq_ctx *ctx, uint32_t type, const uint8_t *gguf, uint8_t *resident, size_t rows, size_t cols, zq_error *err);
 int launch_dequantize(zq_ctx *ctx, const zq_weight *w, const uint32_t *row_ids, size_t n_rows, void *out, int out_dtype, zq_error *err);
+int launch_dequantize_f16(zq_ctx *ctx, const zq_weight *w, __half *out, zq_error *err);
 int launch_quantize(zq_ctx *ctx, uint32_t type, const float *values, size_t rows, size_t cols, void *out, zq_error *err);
 int launch_gemv(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const void *x, int x_dtype, size_t m, void *y, int y_dtype, const void *residual, zq_error *err);
 int launch_gemv_noalloc(zq_ctx *ctx, const zq_weight *w, const void *x, int x_dtype, size_t m, void *y, int y_dtype, zq_error *err);

@@ -9,12 +9,13 @@
 //   1. dequantise the resident packed weight once into an f16 [rows, K] operand in the context workspace
 //      (f32 value rounded once to f16: 2^-12 relative, which keeps layer outputs inside the 2e-3 bound; bf16
 //      operands would not), and convert the activations to f16 (exact for bf16/f16 inputs in f16 range);
-//   2. one CTA per 128 weight rows x 256 tokens: a TMA warp streams 64-column K blocks of both operands
-//      (128-byte swizzle) through a 4-stage mbarrier ring; one thread issues tcgen05.mma (M=128, N=256, K=16,
-//      kind::f16, f32 accumulator in 256 TMEM columns); tcgen05.commit releases ring stages and finally
-//      signals the epilogue warps, which read the accumulator with tcgen05.ld and store Y (+ residual) in the
-//      requested dtype.  For the gated form two accumulators (gate and up, 512 TMEM columns) share the
-//      activation tile and the epilogue applies silu(gate) * up.
+//   2. persistent CTAs (one per SM) walk output tiles of 128 weight rows x 256 tokens: a TMA warp streams
+//      64-column K blocks of both operands (128-byte swizzle) through a 4-stage mbarrier ring; one thread issues
+//      tcgen05.mma (M=128, N=256, K=16, kind::f16, f32 accumulator in 256 TMEM columns); tcgen05.commit releases
+//      ring stages and signals the epilogue warps, which read the accumulator with tcgen05.ld and store
+//      Y (+ residual) in the requested dtype while the MMAs of the next tile fill the second accumulator.  For the
+//      gated form two accumulators (gate and up, all 512 TMEM columns) share the activation tile and the epilogue
+//      applies silu(gate) * up.
 // Every wait is bounded; a wait that runs out raises the CTA's abort flag, all roles fall through to the end,
 // TMEM is released and the context status word reports it.
 #include "zq_common.cuh"
@@ -90,6 +91,7 @@ __device__ __forceinline__ bool wait_flag(uint64_t *bar, uint32_t parity, volati
 
 template <bool GATED> struct GemmSmem {
     static constexpr int stages = GATED ? 3 : 4;
+    static constexpr int acc_bufs = GATED ? 1 : 2;  // 256-column accumulators that fit the 512 TMEM columns
     static constexpr int a_bytes = kBM * kBK * 2;  // 16 KB
     static constexpr int b_bytes = kBN * kBK * 2;  // 32 KB
     static constexpr int stage_bytes = (GATED ? 2 : 1) * a_bytes + b_bytes;
@@ -97,30 +99,49 @@ template <bool GATED> struct GemmSmem {
     static constexpr int total = off_bar + 256 + 1024;  // barriers, tmem slot, slack for 1024-byte alignment
 };
 
+constexpr int kTokGroup = 8;  // token tiles per raster group: a weight tile is reused by 8 token tiles while it is hot in L2
+
+// Persistent CTA (one per SM) over output tiles of 128 weight rows x 256 tokens.  Tiles are rastered in groups of
+// 8 token tiles x all row tiles (token tile fastest), so that the CTAs in flight share weight tiles and the group's
+// activation tiles stay in L2.  The plain form double-buffers the accumulator in tensor memory: the epilogue of tile
+// i runs while the MMAs of tile i+1 fill the other buffer, and the TMA ring never drains between tiles.
 template <bool GATED>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2, const __grid_constant__ CUtensorMap map_x, const GemmParams p) {
     using S = GemmSmem<GATED>;
     constexpr int STAGES = S::stages;
-    constexpr uint32_t TMEM_COLS = GATED ? 512 : 256;
+    constexpr int ACC = S::acc_bufs;
+    constexpr uint32_t ACC_COLS = GATED ? 512 : 256;
+    constexpr uint32_t TMEM_COLS = 512;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + S::off_bar);
     uint64_t *empty = full + STAGES;
-    uint64_t *acc_ready = empty + STAGES;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_ready + 1);
+    uint64_t *acc_full = empty + STAGES;
+    uint64_t *acc_empty = acc_full + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
     __shared__ int s_abort;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row0 = blockIdx.x * kBM;   // first weight row of the tile
-    const int tok0 = blockIdx.y * kBN;   // first token of the tile
     const int k_blocks = (p.k + kBK - 1) / kBK;
+    const int n_row_tiles = (p.n_out + kBM - 1) / kBM, n_tok_tiles = (p.m + kBN - 1) / kBN;
+    const int total_tiles = n_row_tiles * n_tok_tiles;
+    auto tile_coords = [&](int tile, int &row0, int &tok0) {
+        const int per_group = kTokGroup * n_row_tiles;
+        const int group = tile / per_group, in_group = tile - group * per_group;
+        const int group_toks = (n_tok_tiles - group * kTokGroup) < kTokGroup ? (n_tok_tiles - group * kTokGroup) : kTokGroup;
+        row0 = (in_group / group_toks) * kBM;
+        tok0 = (group * kTokGroup + in_group % group_toks) * kBN;
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
-        mbar_init(acc_ready, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 4);
+        }
         fence_mbar_init();
         s_abort = 0;
         tma_prefetch_desc(&map_w);
@@ -139,14 +160,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
     if (warp == 0) {
         // ------------------------------------------------ TMA producer
         if (lane == 0) {
-            for (int kb = 0; kb < k_blocks; ++kb) {
-                const int s = kb % STAGES;
-                if (kb >= STAGES && !wait_flag(&empty[s], ((kb / STAGES) - 1) & 1, &s_abort, p.status, kStatusMmaTimeout)) break;
-                uint8_t *st = smem + (size_t)s * S::stage_bytes;
-                mbar_expect_tx(&full[s], S::stage_bytes);
-                tma_load_2d(st, &map_w, &full[s], kb * kBK, row0);
-                if (GATED) tma_load_2d(st + S::a_bytes, &map_w2, &full[s], kb * kBK, row0);
-                tma_load_2d(st + (GATED ? 2 : 1) * S::a_bytes, &map_x, &full[s], kb * kBK, tok0);
+            long long kg = 0;  // k-block counter over all tiles of this CTA: ring position
+            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+                int row0, tok0;
+                tile_coords(tile, row0, tok0);
+                for (int kb = 0; kb < k_blocks; ++kb, ++kg) {
+                    const int s = (int)(kg % STAGES);
+                    if (kg >= STAGES && !wait_flag(&empty[s], (uint32_t)((kg / STAGES) - 1) & 1, &s_abort, p.status, kStatusMmaTimeout)) break;
+                    uint8_t *st = smem + (size_t)s * S::stage_bytes;
+                    mbar_expect_tx(&full[s], S::stage_bytes);
+                    tma_load_2d(st, &map_w, &full[s], kb * kBK, row0);
+                    if (GATED) tma_load_2d(st + S::a_bytes, &map_w2, &full[s], kb * kBK, row0);
+                    tma_load_2d(st + (GATED ? 2 : 1) * S::a_bytes, &map_x, &full[s], kb * kBK, tok0);
+                }
+                if (*(volatile int *)&s_abort) break;
             }
         }
     } else if (warp == 1) {
@@ -154,58 +181,76 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
         if (lane == 0) {
             // instruction descriptor: f32 accumulator, f16 A and B, both K-major, N = 256, M = 128
             const uint32_t idesc = (1u << 4) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+            long long kg = 0;
+            int iter = 0;
             bool ok = true;
-            for (int kb = 0; kb < k_blocks && ok; ++kb) {
-                const int s = kb % STAGES;
-                ok = wait_flag(&full[s], (kb / STAGES) & 1, &s_abort, p.status, kStatusTmaTimeout);
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++iter) {
+                const int b = iter % ACC;
+                if (iter >= ACC) ok = wait_flag(&acc_empty[b], (uint32_t)((iter / ACC) - 1) & 1, &s_abort, p.status, kStatusMmaTimeout);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t st = smem_u32(smem + (size_t)s * S::stage_bytes);
-                const uint64_t da = make_sw128_desc(st);
-                const uint64_t da2 = make_sw128_desc(st + S::a_bytes);
-                const uint64_t db = make_sw128_desc(st + (GATED ? 2 : 1) * S::a_bytes);
+                const uint32_t acc_addr = tmem_base + (uint32_t)b * ACC_COLS;
+                for (int kb = 0; kb < k_blocks && ok; ++kb, ++kg) {
+                    const int s = (int)(kg % STAGES);
+                    ok = wait_flag(&full[s], (uint32_t)(kg / STAGES) & 1, &s_abort, p.status, kStatusTmaTimeout);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t st = smem_u32(smem + (size_t)s * S::stage_bytes);
+                    const uint64_t da = make_sw128_desc(st);
+                    const uint64_t da2 = make_sw128_desc(st + S::a_bytes);
+                    const uint64_t db = make_sw128_desc(st + (GATED ? 2 : 1) * S::a_bytes);
 #pragma unroll
-                for (int k = 0; k < kBK / 16; ++k) {
-                    const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
-                    // 16 K elements = 32 bytes = 2 descriptor units along the swizzled row
-                    umma_f16_ss(tmem_base, da + 2 * k, db + 2 * k, idesc, acc);
-                    if (GATED) umma_f16_ss(tmem_base + kBN, da2 + 2 * k, db + 2 * k, idesc, acc);
+                    for (int k = 0; k < kBK / 16; ++k) {
+                        const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
+                        // 16 K elements = 32 bytes = 2 descriptor units along the swizzled row
+                        umma_f16_ss(acc_addr, da + 2 * k, db + 2 * k, idesc, acc);
+                        if (GATED) umma_f16_ss(acc_addr + kBN, da2 + 2 * k, db + 2 * k, idesc, acc);
+                    }
+                    tc_commit(&empty[s]);  // arrives once the MMAs above have read the stage
                 }
-                tc_commit(&empty[s]);  // arrives once the MMAs above have read the stage
+                tc_commit(&acc_full[b]);   // arrives when every MMA of the tile has completed
             }
-            tc_commit(acc_ready);      // arrives when every MMA of the tile has completed
         }
     } else {
         // ------------------------------------------------ epilogue: warp q of 4 owns TMEM lanes 32q..32q+31
         const int q = warp & 3;
-        const int row = row0 + q * 32 + lane;
-        const bool ok = wait_flag(acc_ready, 0, &s_abort, p.status, kStatusMmaTimeout);
-        tc_fence_after();
-        if (ok) {
-            const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
-            for (int c0 = 0; c0 < kBN; c0 += 16) {
-                if (tok0 + c0 >= p.m) break;  // warp-uniform
-                uint32_t v[16], u[16];
-                tmem_ld16(lane_base + c0, v);
-                if (GATED) tmem_ld16(lane_base + kBN + c0, u);
-                tmem_ld_wait();
-                if (row < p.n_out) {
+        int iter = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++iter) {
+            int row0, tok0;
+            tile_coords(tile, row0, tok0);
+            const int b = iter % ACC;
+            const int row = row0 + q * 32 + lane;
+            const bool ok = wait_flag(&acc_full[b], (uint32_t)(iter / ACC) & 1, &s_abort, p.status, kStatusMmaTimeout);
+            tc_fence_after();
+            if (ok) {
+                const uint32_t lane_base = tmem_base + (uint32_t)b * ACC_COLS + ((uint32_t)(q * 32) << 16);
+                for (int c0 = 0; c0 < kBN; c0 += 16) {
+                    if (tok0 + c0 >= p.m) break;  // warp-uniform
+                    uint32_t v[16], u[16];
+                    tmem_ld16(lane_base + c0, v);
+                    if (GATED) tmem_ld16(lane_base + kBN + c0, u);
+                    tmem_ld_wait();
+                    if (row < p.n_out) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int tok = tok0 + c0 + j;
-                        if (tok < p.m) {
-                            float val = __uint_as_float(v[j]);
-                            if (GATED) {
-                                const float up = __uint_as_float(u[j]);
-                                val = (val / (1.0f + expf(-val))) * up;  // src/kernel/cpu/ggml_quant.rs:352
+                        for (int j = 0; j < 16; ++j) {
+                            const int tok = tok0 + c0 + j;
+                            if (tok < p.m) {
+                                float val = __uint_as_float(v[j]);
+                                if (GATED) {
+                                    const float up = __uint_as_float(u[j]);
+                                    val = (val / (1.0f + expf(-val))) * up;  // src/kernel/cpu/ggml_quant.rs:352
+                                }
+                                const size_t o = (size_t)tok * p.n_out + row;
+                                if (p.residual) val += load_as_f32(p.residual, p.y_dtype, o);
+                                store_from_f32(p.y, p.y_dtype, o, val);
                             }
-                            const size_t o = (size_t)tok * p.n_out + row;
-                            if (p.residual) val += load_as_f32(p.residual, p.y_dtype, o);
-                            store_from_f32(p.y, p.y_dtype, o, val);
                         }
                     }
                 }
             }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[b]);  // this warp's quarter of the accumulator may be overwritten
         }
     }
     tc_fence_before();
@@ -248,8 +293,8 @@ int launch_gemm(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const vo
     __half *w16 = reinterpret_cast<__half *>(ws);
     __half *w16b = reinterpret_cast<__half *>(ws + w_bytes);
     __half *x16 = reinterpret_cast<__half *>(ws + (gated ? 2 : 1) * w_bytes);
-    rc = launch_dequantize(ctx, w, nullptr, n, w16, ZQ_F16, err);
-    if (!rc && gated) rc = launch_dequantize(ctx, w_up, nullptr, n, w16b, ZQ_F16, err);
+    rc = launch_dequantize_f16(ctx, w, w16, err);
+    if (!rc && gated) rc = launch_dequantize_f16(ctx, w_up, w16b, err);
     if (rc) return rc;
     const __half *xin = reinterpret_cast<const __half *>(x);
     if (x_dtype != ZQ_F16) {
@@ -275,7 +320,8 @@ int launch_gemm(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const vo
     p.m = (int)m;
     p.n_out = (int)n;
     p.k = (int)k;
-    dim3 grid((unsigned)((n + kBM - 1) / kBM), (unsigned)((m + kBN - 1) / kBN));
+    const size_t total_tiles = ((n + kBM - 1) / kBM) * ((m + kBN - 1) / kBN);
+    dim3 grid((unsigned)(total_tiles < (size_t)ctx->sm_count ? total_tiles : (size_t)ctx->sm_count));
     static bool configured[2][64] = {};
     if (gated) {
         if (!configured[1][ctx->device & 63]) {
