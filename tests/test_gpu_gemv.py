@@ -1,7 +1,8 @@
 """GPU parity of the decode GEMV family against the CPU oracle, through the C ABI.
 
-Tolerance: the contract is max_i |a_i - e_i| / max(|e_i|, rms(e)) <= 2e-3 (fp32 accumulation).  The decode path
-keeps activations at ~22 bits and integer-exact weights, so the tests also hold it to 2e-5.
+Tolerance: the contract is max_i |a_i - e_i| / max(|e_i|, rms(e)) <= 2e-3 (fp32 accumulation).  The f16 decode
+kernels keep activations at ~22 bits and integer-exact weights, so the tests also hold them to 2e-5; the integer-MMA
+kernel carries activations as 16-bit integers per 256-column slice and is held to 3e-4.
 """
 import numpy as np
 import pytest
@@ -14,15 +15,23 @@ from tests.gpu_util import ctx, dev, host
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(autouse=True, params=["tcgen05", "resident", "staged"])
+_VARIANT = {"name": "i8"}
+
+
+@pytest.fixture(autouse=True, params=["i8", "tcgen05", "resident", "staged"])
 def gemv_variant(request):
-    """Every case runs on all decode kernels: the tcgen05 kernel (Q4_K, opt-in), the warp-MMA kernel with
-    activations resident in shared memory, and the warp-MMA kernel with per-item activation staging."""
+    """Every case runs on all decode kernels: the integer-MMA kernel (the default; 16-bit integer activations), the
+    tcgen05 kernel (Q4_K, opt-in), the f16 warp-MMA kernel with activations resident in shared memory, and the f16
+    warp-MMA kernel with per-item activation staging."""
     ctx().set_option("enable_tcgen05_gemv", 1 if request.param == "tcgen05" else 0)
     ctx().set_option("force_staged_gemv", 1 if request.param == "staged" else 0)
+    ctx().set_option("force_f16_gemv", 1 if request.param in ("resident", "tcgen05") else 0)
+    _VARIANT["name"] = request.param
     yield request.param
     ctx().set_option("force_staged_gemv", 0)
     ctx().set_option("enable_tcgen05_gemv", 0)
+    ctx().set_option("force_f16_gemv", 0)
+    _VARIANT["name"] = "i8"
 
 
 TYPES = [H.Q4_0, H.Q8_0, H.Q4_K, H.IQ4_NL]
@@ -31,6 +40,8 @@ TIGHT = 2e-5
 
 
 def _check(got, want, tight=TIGHT):
+    if _VARIANT["name"] == "i8":
+        tight = max(tight, 3e-4)  # activations as 16-bit integers per 256-column slice: 2^-16 of the slice maximum
     err = H.max_rel_error(got, want)
     assert err <= BOUND, f"max relative error {err} above the 2e-3 contract"
     assert err <= tight, f"max relative error {err} above the decode path's own {tight}"
@@ -115,7 +126,7 @@ def test_gated_is_silu_gate_times_up_of_the_plain_projections():
     g = host(ctx().linear(dev(x), w)).astype(np.float32)
     got = host(ctx().gated_linear(dev(x), w, w))
     want = (g / (np.float32(1) + np.exp(-g))) * g
-    np.testing.assert_allclose(got, want, rtol=2e-5)  # the plain projection may run on a different kernel than the gated one
+    np.testing.assert_allclose(got, want, rtol=2e-5, atol=1e-6)  # the plain projection may run on a different kernel than the gated one
 
 
 @pytest.mark.parametrize("m", [1, 4])
@@ -168,7 +179,8 @@ def test_half_precision_activations(x_dtype, y_dtype):
     got = host(ctx().linear(x, w, out_dtype=y_dtype))
     want = orc.linear(H.Q4_K, data, rows, cols, x.float().cpu().numpy())
     err = H.max_rel_error(got, want)
-    assert err <= (TIGHT if y_dtype == torch.float32 else (5e-4 if y_dtype == torch.float16 else 4e-3))
+    tight = 3e-4 if _VARIANT["name"] == "i8" else TIGHT
+    assert err <= (tight if y_dtype == torch.float32 else (5e-4 if y_dtype == torch.float16 else 4e-3))
 
 
 def test_results_are_deterministic_across_launches():

@@ -223,6 +223,7 @@ struct zq_ctx {
     // 1 = run Q4_K decode on the tcgen05 kernel (zq_qmv.cu) instead of the warp-MMA kernels.  Off by default: it is
     // parity-clean but, as measured, not yet faster than the warp-MMA path.
     int enable_tcgen05_gemv = 0;
+    int force_f16_gemv = 0;  // skip the integer-MMA decode kernel (tests of the f16 kernels)
     std::atomic<uint64_t> launches{0};
     std::mutex mutex;
 };

@@ -369,6 +369,12 @@ int launch_gemv(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const vo
             if (rc) return rc;
             if (taken) continue;
         }
+        if (!ctx->force_staged_gemv && !ctx->force_f16_gemv) {
+            bool taken = false;
+            rc = launch_gemv_i8(ctx, w, w_up, p, taken, err);
+            if (rc) return rc;
+            if (taken) continue;
+        }
         if (!ctx->force_staged_gemv) {
             bool taken = false;
             rc = launch_gemv_resident(ctx, w, w_up, p, grid, taken, err);
@@ -469,6 +475,10 @@ int launch_gemv_noalloc(zq_ctx *ctx, const zq_weight *w, const void *x, int x_dt
     bool taken = false;
     if (ctx->enable_tcgen05_gemv && !ctx->force_staged_gemv) {  // same kernel choice as zq_linear, so results agree bit for bit
         rc = launch_qmv(ctx, w, p, taken, err);
+        if (rc || taken) return rc;
+    }
+    if (!ctx->force_staged_gemv && !ctx->force_f16_gemv) {
+        rc = launch_gemv_i8(ctx, w, nullptr, p, taken, err);
         if (rc || taken) return rc;
     }
     if (!ctx->force_staged_gemv) {

@@ -277,6 +277,7 @@ __device__ __forceinline__ void consume_unit(const uint8_t *w0, const uint8_t *w
 }
 
 int launch_qmv(zq_ctx *ctx, const zq_weight *w, const GemvParams &p, bool &taken, zq_error *err);
+int launch_gemv_i8(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const GemvParams &p, bool &taken, zq_error *err);
 int launch_gemv_resident(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const GemvParams &p, int grid, bool &taken, zq_error *err);
 
 }  // namespace zq
