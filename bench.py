@@ -116,6 +116,10 @@ def run_ours(args):
         faulthandler.dump_traceback_later(args.watchdog, exit=True)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), timeout=datetime.timedelta(seconds=120))
     ctx = B200Context(local_rank)
+    if args.no_pdl:
+        ctx.set_option("disable_pdl", 1)
+    if args.f16_gemv:
+        ctx.set_option("force_f16_gemv", 1)
     device = torch.device("cuda", local_rank)
     hbm_peak, _, peak_kind = read_peaks()
     if args.only_prefill:
@@ -549,6 +553,8 @@ def main():
     ap.add_argument("--extras", default="all", choices=["all", "prefill", "moe"], help="which side measurements to run")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying CUDA graphs")
     ap.add_argument("--no-clocks", action="store_true", help="do not sample clocks with nvidia-smi")
+    ap.add_argument("--no-pdl", action="store_true", help="launch decode kernels without programmatic dependent launch (A/B aid)")
+    ap.add_argument("--f16-gemv", action="store_true", help="decode on the f16 warp-MMA kernels instead of the integer-MMA kernel (A/B aid)")
     ap.add_argument("--stack-layers", type=int, default=64, help="layers of the prefill GEMM stack (configs[2] names 64)")
     ap.add_argument("--only-prefill", type=int, default=0, help="profiling aid: run only a few prefill GEMMs (Q4_K 5120->17408) at this token count and exit")
     ap.add_argument("--only", default=None, help="restrict the sweep to one case, e.g. q4_k:5120x17408:1 (format:KxN:batch); for profiling")

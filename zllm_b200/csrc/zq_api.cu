@@ -183,6 +183,10 @@ int zq_ctx_set_option(zq_ctx *ctx, const char *key, int value, zq_error *err) {
         ctx->force_staged_gemv = value;
         return ZQ_OK;
     }
+    if (!strcmp(key, "disable_pdl")) {
+        ctx->disable_pdl = value;
+        return ZQ_OK;
+    }
     if (!strcmp(key, "force_f16_gemv")) {
         ctx->force_f16_gemv = value;
         return ZQ_OK;

@@ -81,6 +81,13 @@ enum DeviceStatus : uint32_t { kStatusOk = 0, kStatusTmaTimeout = 1, kStatusMmaT
 // ---------------------------------------------------------------------------------------------------------------
 // PTX wrappers.
 // ---------------------------------------------------------------------------------------------------------------
+// Programmatic dependent launch.  A decode kernel launched with the stream-serialization attribute may start while
+// the previous kernel of the stream is still draining: it sets up its barriers and starts streaming its (constant)
+// weights, and only then waits for the previous kernel to complete before it touches activations or outputs.
+// Both instructions do nothing in a kernel launched without the attribute.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
+__device__ __forceinline__ void pdl_wait_prior_grid() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
 __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
@@ -223,7 +230,8 @@ struct zq_ctx {
     // 1 = run Q4_K decode on the tcgen05 kernel (zq_qmv.cu) instead of the warp-MMA kernels.  Off by default: it is
     // parity-clean but, as measured, not yet faster than the warp-MMA path.
     int enable_tcgen05_gemv = 0;
-    int force_f16_gemv = 0;  // skip the integer-MMA decode kernel (tests of the f16 kernels)
+    int force_f16_gemv = 0;
+    int disable_pdl = 0;     // launch decode kernels without programmatic dependent launch  // skip the integer-MMA decode kernel (tests of the f16 kernels)
     std::atomic<uint64_t> launches{0};
     std::mutex mutex;
 };

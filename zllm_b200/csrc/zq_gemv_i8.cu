@@ -325,7 +325,9 @@ __global__ void __launch_bounds__(kI8Threads, 1) gemv_i8_kernel(const __grid_con
         const int n16 = (ia.off_red - ia.off_x) / 16;
         for (int i = tid; i < n16; i += kI8Threads) z[i] = make_uint4(0u, 0u, 0u, 0u);
     }
+    pdl_launch_dependents();
     __syncthreads();
+    pdl_wait_prior_grid();  // activations (and, later, outputs) belong to the previous kernel until it completes
     {
         // Quantise the activation slice: one warp per (row, 256-column slice), 8 consecutive columns per lane.
         int m = 0, unit = warp;
@@ -568,13 +570,15 @@ static int launch_i8_one(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up,
     cfg.blockDim = dim3(kI8Threads);
     cfg.dynamicSmemBytes = (size_t)total;
     cfg.stream = ctx->stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = (unsigned)ia.split;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = ctx->disable_pdl ? 1 : 2;
     ZQ_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, ma, mb, p, ia), err);
     ctx->launches++;
     return ZQ_OK;

@@ -124,6 +124,8 @@ __global__ void __launch_bounds__(kResidentThreads, 1) gemv_resident_kernel(cons
         for (int i = tid; i < (ra.off_red - ra.off_sx) / 8; i += kConsumerThreads) sxs[i] = make_uint2(0u, 0u);
         __syncthreads();
     }
+    pdl_launch_dependents();
+    pdl_wait_prior_grid();  // activations (and, later, outputs) belong to the previous kernel until it completes
     {
         // stage every activation quad: B-fragment slot (unit, step, column, t); Q4_K also gets per-group sums
         int slice_units = chunk_end * kChunkUnits;
@@ -354,13 +356,15 @@ static int launch_resident_one(zq_ctx *ctx, const zq_weight *w, const zq_weight 
     cfg.blockDim = dim3(kResidentThreads);
     cfg.dynamicSmemBytes = (size_t)total;
     cfg.stream = ctx->stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = (unsigned)ra.split;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = ctx->disable_pdl ? 1 : 2;
     ZQ_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, ma, mb, p, ra), err);
     ctx->launches++;
     return ZQ_OK;
