@@ -319,90 +319,96 @@ __global__ void __launch_bounds__(kI8Threads, 1) gemv_i8_kernel(const __grid_con
     if (slice_units > ia.units_total) slice_units = ia.units_total;
     slice_units -= unit0;
     if (slice_units < 0) slice_units = 0;
-    {
-        // columns, sums and scales nobody writes below must read as zero
-        uint4 *z = reinterpret_cast<uint4 *>(smem + ia.off_x);
-        const int n16 = (ia.off_red - ia.off_x) / 16;
-        for (int i = tid; i < n16; i += kI8Threads) z[i] = make_uint4(0u, 0u, 0u, 0u);
-    }
     pdl_launch_dependents();
-    __syncthreads();
     pdl_wait_prior_grid();  // activations (and, later, outputs) belong to the previous kernel until it completes
     {
-        // Quantise the activation slice: one warp per (row, 256-column slice), 8 consecutive columns per lane.
-        int m = 0, unit = warp;
-        while (unit >= slice_units && m < M) { unit -= slice_units; ++m; }
-        while (m < M) {
-            const int k0 = (unit0 + unit) * kUnitWeights + 8 * lane;
-            float v[8];
+        // Quantise the activation slice: one warp per (row, 256-column slice), 8 consecutive columns per lane.  A warp
+        // takes its slices four at a time, all loads first, so that their latencies overlap.  Columns past 2 m, and
+        // sums and scales of rows past m, are never written: whatever they hold only reaches accumulator columns
+        // that no one reads (integer MMAs cannot produce NaNs for the columns that are read).
+        constexpr int kBatch = 4, kWarps = kI8Threads / 32;
+        const int total = M * slice_units;
+        for (int base = warp; base < total; base += kBatch * kWarps) {
+            float v[kBatch][8];
+            int tm[kBatch], tu[kBatch];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = 0.f;
-            if (k0 < p.cols) {  // K is a multiple of 32, so a lane's 8 columns are all inside or all outside
-                const size_t o = (size_t)m * p.cols + k0;
-                if (p.x_dtype == ZQ_F32) {
-                    const float4 f0 = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p.x) + o);
-                    const float4 f1 = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p.x) + o + 4);
-                    v[0] = f0.x; v[1] = f0.y; v[2] = f0.z; v[3] = f0.w; v[4] = f1.x; v[5] = f1.y; v[6] = f1.z; v[7] = f1.w;
-                } else {
-                    const uint4 raw = *reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(p.x) + o);
-                    const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
+            for (int b = 0; b < kBatch; ++b) {
+                const int task = base + b * kWarps;
+                tm[b] = task < total ? task / slice_units : -1;
+                tu[b] = task < total ? task - tm[b] * slice_units : 0;
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        if (p.x_dtype == ZQ_F16) {
-                            const float2 f = __half22float2(u32_as_h2(rw[j]));
-                            v[2 * j] = f.x; v[2 * j + 1] = f.y;
-                        } else {  // bf16: the upper half of an f32
-                            v[2 * j] = __uint_as_float(rw[j] << 16);
-                            v[2 * j + 1] = __uint_as_float(rw[j] & 0xFFFF0000u);
+                for (int j = 0; j < 8; ++j) v[b][j] = 0.f;
+                const int k0 = (unit0 + tu[b]) * kUnitWeights + 8 * lane;
+                if (tm[b] >= 0 && k0 < p.cols) {  // K is a multiple of 32, so a lane's 8 columns are all inside or all outside
+                    const size_t o = (size_t)tm[b] * p.cols + k0;
+                    if (p.x_dtype == ZQ_F32) {
+                        const float4 f0 = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p.x) + o);
+                        const float4 f1 = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p.x) + o + 4);
+                        v[b][0] = f0.x; v[b][1] = f0.y; v[b][2] = f0.z; v[b][3] = f0.w; v[b][4] = f1.x; v[b][5] = f1.y; v[b][6] = f1.z; v[b][7] = f1.w;
+                    } else {
+                        const uint4 raw = *reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(p.x) + o);
+                        const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            if (p.x_dtype == ZQ_F16) {
+                                const float2 f = __half22float2(u32_as_h2(rw[j]));
+                                v[b][2 * j] = f.x; v[b][2 * j + 1] = f.y;
+                            } else {  // bf16: the upper half of an f32
+                                v[b][2 * j] = __uint_as_float(rw[j] << 16);
+                                v[b][2 * j + 1] = __uint_as_float(rw[j] & 0xFFFF0000u);
+                            }
                         }
                     }
                 }
             }
-            float amax = 0.f;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+            for (int b = 0; b < kBatch; ++b) {
+                if (tm[b] < 0) continue;  // warp-uniform
+                const int m = tm[b], unit = tu[b];
+                float amax = 0.f;
 #pragma unroll
-            for (int s = 16; s >= 1; s >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, s));
-            const bool live = amax > 0.f && amax < 3.0e38f;
-            const float inv = live ? __fdividef(kActMax, amax) : 0.f;
-            int hi[8], lo[8], sum = 0;
+                for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[b][j]));
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                int xq = __float2int_rn(v[j] * inv);
-                xq = xq > 32512 ? 32512 : (xq < -32512 ? -32512 : xq);
-                hi[j] = (xq + 128) >> 8;
-                lo[j] = xq - (hi[j] << 8);
-                sum += xq;
-            }
-            const int i0 = 8 * lane;  // first of the lane's elements inside the unit
+                for (int s = 16; s >= 1; s >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, s));
+                const bool live = amax > 0.f && amax < 3.0e38f;
+                const float inv = live ? __fdividef(kActMax, amax) : 0.f;
+                int hi[8], lo[8], sum = 0;
 #pragma unroll
-            for (int qd = 0; qd < 2; ++qd) {
-                int G, tt, reg;
-                i8_slot<TYPE>(i0 + 4 * qd, G, tt, reg);
-                const uint32_t ph = (uint32_t)(hi[4 * qd] & 0xFF) | ((uint32_t)(hi[4 * qd + 1] & 0xFF) << 8) | ((uint32_t)(hi[4 * qd + 2] & 0xFF) << 16) | ((uint32_t)(hi[4 * qd + 3] & 0xFF) << 24);
-                const uint32_t pl = (uint32_t)(lo[4 * qd] & 0xFF) | ((uint32_t)(lo[4 * qd + 1] & 0xFF) << 8) | ((uint32_t)(lo[4 * qd + 2] & 0xFF) << 16) | ((uint32_t)(lo[4 * qd + 3] & 0xFF) << 24);
-                const int slot = (((unit * 8 + G) * CP + 2 * m) * 4 + tt) * 2 + reg;
-                xw[slot] = ph;
-                xw[slot + 8] = pl;  // next column: the lo limb
-            }
-            // the scale actually applied: x ~ x_q / inv
-            if (lane == 0) sact[unit * (4 * NT) + m] = live ? __fdividef(1.f, inv) : 0.f;
-            if constexpr (TYPE == ZQ_Q4_K) {
-                // exact integer sum of each 32-column group, as two f16 limbs for the min-term MMA
-                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-                if ((lane & 3) == 0) {
-                    const int G8 = lane >> 2;
-                    // |sum| can reach 32 * 32512, beyond f16: sum = 1024 a + r with |a| <= 1016, |r| <= 512, both exact
-                    // in f16; the factor 1024 rides on the min codes of the hi-limb K slots
-                    const int a = (sum + 512) >> 10, r = sum - (a << 10);
-                    __half *dst = reinterpret_cast<__half *>(&sxs[(unit * CP + 2 * m) * 4 + (G8 >> 1)]);
-                    dst[G8 & 1] = __int2half_rn(a);
-                    dst[2 + (G8 & 1)] = __int2half_rn(r);
+                for (int j = 0; j < 8; ++j) {
+                    int xq = __float2int_rn(v[b][j] * inv);
+                    xq = xq > 32512 ? 32512 : (xq < -32512 ? -32512 : xq);
+                    hi[j] = (xq + 128) >> 8;
+                    lo[j] = xq - (hi[j] << 8);
+                    sum += xq;
+                }
+                const int i0 = 8 * lane;  // first of the lane's elements inside the unit
+#pragma unroll
+                for (int qd = 0; qd < 2; ++qd) {
+                    int G, tt, reg;
+                    i8_slot<TYPE>(i0 + 4 * qd, G, tt, reg);
+                    const uint32_t ph = (uint32_t)(hi[4 * qd] & 0xFF) | ((uint32_t)(hi[4 * qd + 1] & 0xFF) << 8) | ((uint32_t)(hi[4 * qd + 2] & 0xFF) << 16) | ((uint32_t)(hi[4 * qd + 3] & 0xFF) << 24);
+                    const uint32_t pl = (uint32_t)(lo[4 * qd] & 0xFF) | ((uint32_t)(lo[4 * qd + 1] & 0xFF) << 8) | ((uint32_t)(lo[4 * qd + 2] & 0xFF) << 16) | ((uint32_t)(lo[4 * qd + 3] & 0xFF) << 24);
+                    const int slot = (((unit * 8 + G) * CP + 2 * m) * 4 + tt) * 2 + reg;
+                    xw[slot] = ph;
+                    xw[slot + 8] = pl;  // next column: the lo limb
+                }
+                // the scale actually applied: x ~ x_q / inv
+                if (lane == 0) sact[unit * (4 * NT) + m] = live ? __fdividef(1.f, inv) : 0.f;
+                if constexpr (TYPE == ZQ_Q4_K) {
+                    // exact integer sum of each 32-column group, as two f16 limbs for the min-term MMA
+                    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                    if ((lane & 3) == 0) {
+                        const int G8 = lane >> 2;
+                        // |sum| can reach 32 * 32512, beyond f16: sum = 1024 a + r with |a| <= 1016, |r| <= 512, both exact
+                        // in f16; the factor 1024 rides on the min codes of the hi-limb K slots
+                        const int a = (sum + 512) >> 10, r = sum - (a << 10);
+                        __half *dst = reinterpret_cast<__half *>(&sxs[(unit * CP + 2 * m) * 4 + (G8 >> 1)]);
+                        dst[G8 & 1] = __int2half_rn(a);
+                        dst[2 + (G8 & 1)] = __int2half_rn(r);
+                    }
                 }
             }
-            unit += kI8Threads / 32;
-            while (unit >= slice_units && m < M) { unit -= slice_units; ++m; }
         }
     }
     __syncthreads();
@@ -452,62 +458,35 @@ __global__ void __launch_bounds__(kI8Threads, 1) gemv_i8_kernel(const __grid_con
 
     // ---------------------------------------------------- end of the K slice: combine and store
     {
+        // Every CTA leaves its partial tile (one copy per unit half) in its own shared memory; after one barrier
+        // (cluster-wide when the tile is split) the threads of rank 0 add up, for their output element, the halves
+        // of every rank in rank order (deterministic), apply the epilogue and store.
         constexpr int RS = NT * 4;  // activation rows a tile row can hold
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-            red[(ul * kTileRows + r0) * RS + nt * 4 + t] = yacc[nt][0];
-            red[(ul * kTileRows + r0 + 8) * RS + nt * 4 + t] = yacc[nt][1];
+            red[(ul * RS + nt * 4 + t) * kTileRows + r0] = yacc[nt][0];  // [unit half][activation row][tile row]
+            red[(ul * RS + nt * 4 + t) * kTileRows + r0 + 8] = yacc[nt][1];
         }
-        __syncthreads();
-        float vals[(kTileRows * kMaxGemvRows + kI8Threads - 1) / kI8Threads];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            const int i = tid + c * kI8Threads;
-            if (i < kTileRows * M) {
-                const int row = i & (kTileRows - 1), tok = i >> 7;
-                vals[c] = red[row * RS + tok] + red[(kTileRows + row) * RS + tok];
-            }
-        }
-        __syncthreads();
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            const int i = tid + c * kI8Threads;
-            if (i < kTileRows * M) red[i] = vals[c];  // part[tok * 128 + row]
-        }
-        if (split > 1) {
-            i8_cluster_sync();  // every slice's partial tile is in its CTA's shared memory
-            if (my_rank == 0) {
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const int i = tid + c * kI8Threads;
-                    if (i < kTileRows * M) {
-                        float v = vals[c];
-                        for (int r = 1; r < split; ++r) v += i8_ld_cluster_f32(&red[i], (uint32_t)r);  // rank order: deterministic
-                        vals[c] = v;
-                    }
-                }
-                __syncthreads();
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const int i = tid + c * kI8Threads;
-                    if (i < kTileRows * M) red[i] = vals[c];
-                }
-            }
-        }
-        __syncthreads();
+        if (split > 1) i8_cluster_sync();
+        else __syncthreads();
         if (my_rank == 0) {
-            // thread -> (activation row, tile row): consecutive threads store consecutive output features
-            const int out_rows = rows_per_tile;  // 128 or 64: a power of two
+            constexpr int out_rows = GATED ? kTileRows / 2 : kTileRows;
+            auto total_of = [&](int rr, int tok) -> float {
+                const float *a = &red[tok * kTileRows + rr], *b = &red[(RS + tok) * kTileRows + rr];
+                float v = *a + *b;
+                for (int r = 1; r < split; ++r) v += i8_ld_cluster_f32(a, (uint32_t)r) + i8_ld_cluster_f32(b, (uint32_t)r);
+                return v;
+            };
             for (int i = tid; i < out_rows * M; i += kI8Threads) {
                 const int row = i & (out_rows - 1), tok = i / out_rows;
                 const int n = my_tile * out_rows + row;
                 if (n >= p.n_out) continue;
                 float v;
                 if (GATED) {
-                    const float gate = red[tok * kTileRows + row], up = red[tok * kTileRows + out_rows + row];
+                    const float gate = total_of(row, tok), up = total_of(out_rows + row, tok);
                     v = (gate / (1.0f + expf(-gate))) * up;
                 } else {
-                    v = red[tok * kTileRows + row];
+                    v = total_of(row, tok);
                 }
                 const size_t o = (size_t)tok * p.n_out + n;
                 if (p.residual) v += load_as_f32(p.residual, p.y_dtype, o);
@@ -523,22 +502,31 @@ __global__ void __launch_bounds__(kI8Threads, 1) gemv_i8_kernel(const __grid_con
 template <uint32_t TYPE, int NT>
 static bool plan_i8(int m, int units_total, int tiles, int chunks, int sm_count, I8Args &ia, int &total_bytes) {
     constexpr int STAGE_W = kTileRows * kChunkUnits * Fmt<TYPE>::unit_bytes;
-    int split = 1;
-    while (split < 8 && tiles * split * 2 <= sm_count && split * 2 <= chunks) split *= 2;
-    const int slice_chunks = (chunks + split - 1) / split;
-    int slice_units = slice_chunks * kChunkUnits;
-    if (slice_units > units_total) slice_units = units_total;
-    const int max_smem = 232448 - 256;  // 227 KB opt-in limit minus static shared and alignment slack
     constexpr int CP = 8 * NT;  // MMA columns, padded to whole column tiles
-    const int x_bytes = slice_units * 8 * CP * 32;
-    const int sx_bytes = TYPE == ZQ_Q4_K ? slice_units * CP * 32 : 0;
-    const int sa_bytes = (slice_units * 4 * NT * 4 + 127) & ~127;
-    int red_bytes = 2 * kTileRows * NT * 4 * 4;
-    if (red_bytes < kTileRows * m * 4) red_bytes = kTileRows * m * 4;
-    const int fixed = x_bytes + sx_bytes + sa_bytes + red_bytes + 128 + 128;
-    int stages = (max_smem - fixed) / STAGE_W;
-    if (stages > 5) stages = 5;
-    if (stages < 2) return false;
+    const int max_smem = 232448 - 256;  // 227 KB opt-in limit minus static shared and alignment slack
+    const int red_bytes = 2 * kTileRows * NT * 4 * 4;
+    // CTAs per tile: as many K slices as fill the SMs (any cluster size up to 8, not only powers of two); more than
+    // that, i.e. more CTAs than SMs, only when the activation slice would otherwise leave no room for the ring
+    int split = sm_count / (tiles > 0 ? tiles : 1);
+    if (split > 8) split = 8;
+    if (split > chunks) split = chunks;
+    if (split < 1) split = 1;
+    int room = 0, slice_chunks = 0, x_bytes = 0, sx_bytes = 0, sa_bytes = 0;  // room: ring stages that fit
+    for (;; ++split) {
+        slice_chunks = (chunks + split - 1) / split;
+        int slice_units = slice_chunks * kChunkUnits;
+        if (slice_units > units_total) slice_units = units_total;
+        x_bytes = slice_units * 8 * CP * 32;
+        sx_bytes = TYPE == ZQ_Q4_K ? slice_units * CP * 32 : 0;
+        sa_bytes = (slice_units * 4 * NT * 4 + 127) & ~127;
+        room = (max_smem - (x_bytes + sx_bytes + sa_bytes + red_bytes + 128 + 128)) / STAGE_W;
+        if (room >= 3 || split >= 8 || split >= chunks) break;
+    }
+    if (room < 2) return false;
+    int stages = room > 5 ? 5 : room;
+    if (stages > slice_chunks + 1) stages = slice_chunks + 1;  // no point in more ring than work
+    if (stages < 2) stages = 2;
+    (void)m;
     ia.stages = stages;
     ia.split = split;
     ia.units_total = units_total;
