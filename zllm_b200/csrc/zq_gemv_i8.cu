@@ -4,7 +4,7 @@
 // one AND per four weights here (the low nibbles as they are, the high nibbles left in place as 16 q), against an
 // AND-OR plus a scaled half-precision FMA per two weights on the f16 path, and one MMA covers a whole 32-weight
 // scale group, so the group's scale is applied once to the s32 accumulator instead of to every operand pair.
-// That cuts the instruction count per weight to under a third, which is what bounds these kernels.
+// That cuts the instruction count per weight to under a half, which is what bounds these kernels.
 //
 // Activations: each row is cut into 256-column slices; a slice is scaled by its own absolute maximum to a signed
 // 16-bit integer x_q in [-32512, 32512] and split into two s8 limbs, x_q = 256 hi + lo with lo in [-128, 127].
@@ -18,31 +18,64 @@
 // Everything up to the final scale is exact integer arithmetic; the result differs from the f32 reference only by
 // the 2^-16 activation resolution and f32 rounding of the per-unit terms.
 //
-// Structure (ring of TMA stages, one CTA per 128-row tile and K slice, cluster reduction through distributed
-// shared memory, bounded waits) is that of zq_gemv_resident.cu; up to 16 activation rows go in one pass.
+// Work partition: one CTA per (128-row tile, K slice); the CTAs of a thread-block cluster are `tshare`
+// neighbouring tiles times `split` K slices.
+//   * The K slices of one tile meet at the end in distributed shared memory: every CTA leaves its partial tile in
+//     its own shared memory, the cluster synchronises, and the CTA of slice 0 adds the partials in slice order
+//     (deterministic) and stores the tile.  No global scratch, no atomics.
+//   * The tiles of a cluster need the same quantised activations.  Quantising them is the expensive part of the
+//     prologue (it grows with the number of activation rows), so the CTAs that share a K slice divide it: each
+//     quantises every tshare-th 256-column record and stores it into the shared memory of all of them.
+// The weights stream through a ring of TMA stages (128 rows x 2 units each); every wait is bounded and a wait that
+// runs out raises a CTA-wide abort flag plus the device status word, so the kernel always returns.
+#include <map>
+#include <mutex>
+#include <tuple>
+
 #include "zq_gemv_frag.cuh"
 
 namespace zq {
 
 constexpr int kI8Threads = 512;
 constexpr float kActMax = 32512.f;  // 127 * 256
+// One record per (256-column unit, activation row): 32 B-fragment slots of 16 bytes (hi-limb pair | lo-limb pair),
+// 32 bytes of group sums (min-term fragment), the slice scale.
+constexpr int kRec = 576, kRecSums = 512, kRecScale = 544;
 
 struct I8Args {
     int stages;       // 2..5 ring stages
-    int split;        // CTAs per tile (cluster size): 1, 2, 4 or 8
+    int split;        // K slices per tile
+    int tshare;       // neighbouring tiles per cluster that share the activation staging (cluster = tshare * split CTAs)
     int units_total;  // resident units per row (ceil(K / 256))
-    int off_x, off_sx, off_sa, off_red, off_bar;  // byte offsets from the 128-byte aligned base (weights at 0)
+    int off_x, off_red, off_bar;  // byte offsets from the 128-byte aligned base (weights at 0)
 };
 
-__device__ __forceinline__ void i8_cluster_sync() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+__device__ __forceinline__ void i8_cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void i8_cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+__device__ __forceinline__ uint32_t i8_cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
 }
-__device__ __forceinline__ float i8_ld_cluster_f32(const float *local, uint32_t rank) {
+// shared address of `local` (a shared address of this CTA) in the CTA of cluster rank `rank`
+__device__ __forceinline__ uint32_t i8_mapa(uint32_t local, uint32_t rank) {
     uint32_t remote;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+    return remote;
+}
+__device__ __forceinline__ float i8_ld_cluster_f32(uint32_t addr) {
     float v;
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
     return v;
+}
+__device__ __forceinline__ void i8_st_cluster_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared::cluster.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ void i8_st_cluster_v2(uint32_t addr, uint32_t a, uint32_t b) {
+    asm volatile("st.shared::cluster.v2.u32 [%0], {%1,%2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
+}
+__device__ __forceinline__ void i8_st_cluster_u32(uint32_t addr, uint32_t a) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr), "r"(a) : "memory");
 }
 // Bounded wait: when the barrier does not complete (or another warp already gave up) the abort flag is raised and
 // every later wait in the CTA falls through, so all warps still reach every barrier and return.
@@ -72,7 +105,7 @@ __device__ __forceinline__ float lds_f32(uint32_t addr) {
     asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
     return v;
 }
-// zero-extended byte j of a word
+// zero-extended byte J of a word
 template <int J> __device__ __forceinline__ int byte_of(uint32_t w) {
     uint32_t r;
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(w), "r"(0u), "n"(0x4440 + J));
@@ -83,12 +116,12 @@ template <bool A_SIGNED>
 __device__ __forceinline__ void imma_16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     if constexpr (A_SIGNED) {
         asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-                     : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
-                     : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+            : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
     } else {
         asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-                     : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
-                     : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+            : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
     }
 }
 // (a & b) ^ c in one LOP3
@@ -97,34 +130,22 @@ __device__ __forceinline__ uint32_t lop3_and_xor(uint32_t a, uint32_t b, uint32_
     asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
     return r;
 }
-
-// Where the activation quad that starts at unit element i (a multiple of 4) sits in the B fragments:
-// scale group G (one MMA each), lane-in-quad t, fragment register reg.
-template <uint32_t TYPE> __device__ __forceinline__ void i8_slot(int i, int &G, int &t, int &reg) {
-    G = i >> 5;
-    if (TYPE == ZQ_Q4_K) {
-        const int j = i & 31;  // byte of the 32-byte nibble pair; lane t reads words 2t and 2t+1
-        t = j >> 3;
-        reg = (j >> 2) & 1;
-    } else {  // block-32 units: lane t reads the word with elements 4t..4t+3 (first half) and 16+4t.. (second half)
-        const int e = i & 31;
-        t = (e & 15) >> 2;
-        reg = e >> 4;
-    }
+__device__ __forceinline__ uint32_t pack_s8x4(int a, int b, int c, int d) {
+    return (uint32_t)(a & 0xFF) | ((uint32_t)(b & 0xFF) << 8) | ((uint32_t)(c & 0xFF) << 16) | ((uint32_t)(d & 0xFF) << 24);
 }
 
-// Shared-memory layout of the quantised activations, CP = 8 NT MMA columns (columns past 2 m hold zeros):
-//   x   [unit][group G][column][lane-in-quad t][register]  u32   -> one 8-byte B fragment per (G, column, t)
-//   sx  [unit][column][t]                                  2 x half2 (hi limbs | lo limbs of two group sums)
-//   sa  [unit][activation row 0 .. 4 NT - 1]               f32 slice scale
-// All addresses below are 32-bit shared addresses.
+// Reader side of a record: the B fragment (k 4t..4t+3 | k 16+4t..) of scale group G, limb l, for lane-in-quad t
+// sits at byte (4 G + t) * 16 + 8 l.  Which activation columns those k stand for is the format's business:
+//   Q4_K        k-th byte of the 32-byte nibble pair  ->  slot t holds columns 8t..8t+7 of the group
+//   Q4_0/Q8_0   slot t holds columns 4t..4t+3 and 16+4t..16+4t+3 of the block
+// (any bijection works as long as the weights use the same one; these match the resident layouts).
 
 // One Q4_K unit (256 weights) of the thread's two fragment rows.
-//   wq0 / wq1  unit base of fragment rows g and g+8      xa  this lane's B fragment of group 0, column tile 0
-//   sxa        this lane's group-sum fragment             saa this lane's slice scale (row t of column tile 0)
+//   wq0 / wq1  unit base of fragment rows g and g+8 (shared addresses)
+//   rec[nt]    record of the activation row this lane's B column of tile nt belongs to (row g / 2);  xoff = 16 t + 8 limb
+//   srec[nt]   record of the activation row this lane's accumulator columns belong to (row t): its slice scale
 template <int NT>
-__device__ __forceinline__ void consume_q4k_i8(uint32_t wq0, uint32_t wq1, int t, uint32_t xa, uint32_t sxa, uint32_t saa, float (&yacc)[NT][2]) {
-    constexpr int CP = 8 * NT;
+__device__ __forceinline__ void consume_q4k_i8(uint32_t wq0, uint32_t wq1, int t, const uint32_t (&rec)[NT], const uint32_t (&srec)[NT], uint32_t xoff, float (&yacc)[NT][2]) {
     const uint4 hdr0 = lds128(wq0), hdr1 = lds128(wq1);
     uint2 q0[4], q1[4];
 #pragma unroll
@@ -144,8 +165,8 @@ __device__ __forceinline__ void consume_q4k_i8(uint32_t wq0, uint32_t wq1, int t
         uint2 bl[NT], bh[NT];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-            bl[nt] = lds64(xa + (2 * pr) * 32 * CP + nt * 256);
-            bh[nt] = lds64(xa + (2 * pr + 1) * 32 * CP + nt * 256);
+            bl[nt] = lds64(rec[nt] + xoff + (2 * pr) * 64);
+            bh[nt] = lds64(rec[nt] + xoff + (2 * pr + 1) * 64);
         }
         const uint32_t s0w = pr < 2 ? sc_lo0 : sc_hi0, s1w = pr < 2 ? sc_lo1 : sc_hi1;
         {
@@ -187,7 +208,8 @@ __device__ __forceinline__ void consume_q4k_i8(uint32_t wq0, uint32_t wq1, int t
         const uint32_t ma0k = hmul2_u32(ma0, 0x64006400u), ma1k = hmul2_u32(ma1, 0x64006400u);  // x 1024 (<= 64512, exact)
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-            const uint2 sx = lds64(sxa + nt * 256);
+            // both limb columns of a row read the row's sums; only the hi-limb column's result is used
+            const uint2 sx = lds64(rec[nt] + kRecSums + 8 * t);
             mma_16816_zero(d2[nt], ma0k, ma1k, ma0, ma1, sx.x, sx.y);
         }
     }
@@ -196,7 +218,7 @@ __device__ __forceinline__ void consume_q4k_i8(uint32_t wq0, uint32_t wq1, int t
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
         // columns 2t / 2t+1 of the tile are the hi / lo limb of one activation row
-        const float sa = lds_f32(saa + nt * 16);
+        const float sa = lds_f32(srec[nt] + kRecScale);
         const float f0 = (float)((tl[nt][0] << 4) + th[nt][0]) * 256.f + (float)((tl[nt][1] << 4) + th[nt][1]);
         const float f1 = (float)((tl[nt][2] << 4) + th[nt][2]) * 256.f + (float)((tl[nt][3] << 4) + th[nt][3]);
         yacc[nt][0] += sa * (d_0 * f0 - dm_0 * d2[nt][0]);
@@ -206,8 +228,7 @@ __device__ __forceinline__ void consume_q4k_i8(uint32_t wq0, uint32_t wq1, int t
 
 // One block-32 unit (8 blocks of 32 weights) of the thread's two fragment rows: Q4_0 or Q8_0.
 template <uint32_t TYPE, int NT>
-__device__ __forceinline__ void consume_b32_i8(uint32_t wq0, uint32_t wq1, int t, uint32_t xa, uint32_t saa, float (&yacc)[NT][2]) {
-    constexpr int CP = 8 * NT;
+__device__ __forceinline__ void consume_b32_i8(uint32_t wq0, uint32_t wq1, int t, const uint32_t (&rec)[NT], const uint32_t (&srec)[NT], uint32_t xoff, float (&yacc)[NT][2]) {
     constexpr int H = TYPE == ZQ_Q8_0 ? 4 : 2;     // 16-byte pieces per lane
     constexpr int BPP = TYPE == ZQ_Q8_0 ? 2 : 4;   // blocks per piece
     constexpr float kPre = TYPE == ZQ_Q8_0 ? 1.f : 0.0625f;
@@ -221,7 +242,7 @@ __device__ __forceinline__ void consume_b32_i8(uint32_t wq0, uint32_t wq1, int t
     const uint32_t hd0[4] = {hdr0.x, hdr0.y, hdr0.z, hdr0.w}, hd1[4] = {hdr1.x, hdr1.y, hdr1.z, hdr1.w};
     float sap[NT];
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) sap[nt] = lds_f32(saa + nt * 16) * kPre;
+    for (int nt = 0; nt < NT; ++nt) sap[nt] = lds_f32(srec[nt] + kRecScale) * kPre;
 #pragma unroll
     for (int h = 0; h < H; ++h) {
         const uint32_t q0[4] = {pc0[h].x, pc0[h].y, pc0[h].z, pc0[h].w};
@@ -230,7 +251,7 @@ __device__ __forceinline__ void consume_b32_i8(uint32_t wq0, uint32_t wq1, int t
 #pragma unroll
         for (int bb = 0; bb < BPP; ++bb)
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) b[bb][nt] = lds64(xa + (BPP * h + bb) * 32 * CP + nt * 256);
+            for (int nt = 0; nt < NT; ++nt) b[bb][nt] = lds64(rec[nt] + xoff + (BPP * h + bb) * 64);
 #pragma unroll
         for (int bb = 0; bb < BPP; ++bb) {
             const int blk = BPP * h + bb;
@@ -261,14 +282,9 @@ __global__ void __launch_bounds__(kI8Threads, 1) gemv_i8_kernel(const __grid_con
     constexpr int UB = Fmt<TYPE>::unit_bytes;
     constexpr int PITCH = kChunkUnits * UB;
     constexpr int STAGE_W = kTileRows * PITCH;
-    constexpr int CP = 8 * NT;
-    constexpr int X_UNIT = 8 * CP * 32, SX_UNIT = CP * 32, SA_UNIT = 4 * NT * 4;  // bytes per staged unit
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
     uint8_t *ws = smem;
-    uint32_t *xw = reinterpret_cast<uint32_t *>(smem + ia.off_x);
-    uint2 *sxs = reinterpret_cast<uint2 *>(smem + ia.off_sx);
-    float *sact = reinterpret_cast<float *>(smem + ia.off_sa);
     float *red = reinterpret_cast<float *>(smem + ia.off_red);
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + ia.off_bar);
     uint64_t *empty = full + 8;
@@ -277,12 +293,16 @@ __global__ void __launch_bounds__(kI8Threads, 1) gemv_i8_kernel(const __grid_con
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int STAGES = ia.stages;
     const int rows_per_tile = GATED ? kTileRows / 2 : kTileRows;
-    const int split = ia.split;
+    const int split = ia.split, tshare = ia.tshare;
+    const bool clustered = split * tshare > 1;
     const int my_tile = blockIdx.x / split, my_rank = blockIdx.x % split;
+    const uint32_t crank = clustered ? i8_cluster_rank() : 0u;
+    const int tile_local = (int)crank / split;  // which of the cluster's tiles
     const int chunk_begin = (int)((long long)my_rank * p.chunks / split), chunk_end = (int)((long long)(my_rank + 1) * p.chunks / split);
     const int n_items = chunk_end - chunk_begin;
     const int unit0 = chunk_begin * kChunkUnits;
 
+    if (tshare > 1) i8_cluster_arrive();  // "this CTA runs": peers wait for it before they store into this CTA
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&full[s], 1);
@@ -310,6 +330,7 @@ __global__ void __launch_bounds__(kI8Threads, 1) gemv_i8_kernel(const __grid_con
         const int pre = n_items < STAGES - 1 ? n_items : STAGES - 1;
         for (int s = 0; s < pre; ++s) issue_tma(s, s);
     }
+    pdl_launch_dependents();
 
     const int g = lane >> 2, t = lane & 3;
     const int rs = warp & 7, ul = warp >> 3;
@@ -319,28 +340,36 @@ __global__ void __launch_bounds__(kI8Threads, 1) gemv_i8_kernel(const __grid_con
     if (slice_units > ia.units_total) slice_units = ia.units_total;
     slice_units -= unit0;
     if (slice_units < 0) slice_units = 0;
-    pdl_launch_dependents();
+    const uint32_t x_base = smem_u32(smem + ia.off_x);
+
     pdl_wait_prior_grid();  // activations (and, later, outputs) belong to the previous kernel until it completes
+    if (tshare > 1) i8_cluster_wait();  // every CTA of the cluster is running: its shared memory may be written
     {
-        // Quantise the activation slice: one warp per (row, 256-column slice), 8 consecutive columns per lane.  A warp
-        // takes its slices four at a time, all loads first, so that their latencies overlap.  Columns past 2 m, and
-        // sums and scales of rows past m, are never written: whatever they hold only reaches accumulator columns
-        // that no one reads (integer MMAs cannot produce NaNs for the columns that are read).
+        // Quantise this CTA's share of the activation slice (every tshare-th record), one warp per record, 8
+        // consecutive columns per lane, four records at a time with all loads first so that their latencies overlap;
+        // each record goes to all CTAs of the cluster that work on this K slice.  Records of activation rows past m
+        // do not exist: lanes whose MMA column has no row read some existing record instead, and whatever they
+        // compute only reaches accumulator columns no one reads.
         constexpr int kBatch = 4, kWarps = kI8Threads / 32;
+        uint32_t peer_x[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) peer_x[q] = (clustered && q < tshare) ? i8_mapa(x_base, (uint32_t)(q * split + my_rank)) : x_base;
         const int total = M * slice_units;
-        for (int base = warp; base < total; base += kBatch * kWarps) {
+        const int n_mine = total > tile_local ? (total - tile_local + tshare - 1) / tshare : 0;
+        for (int base = warp; base < n_mine; base += kBatch * kWarps) {
             float v[kBatch][8];
-            int tm[kBatch], tu[kBatch];
+            int trec[kBatch];
 #pragma unroll
             for (int b = 0; b < kBatch; ++b) {
-                const int task = base + b * kWarps;
-                tm[b] = task < total ? task / slice_units : -1;
-                tu[b] = task < total ? task - tm[b] * slice_units : 0;
+                const int k = base + b * kWarps;
+                const int task = tile_local + tshare * k;  // record index: unit-major, then activation row
+                trec[b] = k < n_mine ? task : -1;
+                const int unit = task / M, m = task - unit * M;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) v[b][j] = 0.f;
-                const int k0 = (unit0 + tu[b]) * kUnitWeights + 8 * lane;
-                if (tm[b] >= 0 && k0 < p.cols) {  // K is a multiple of 32, so a lane's 8 columns are all inside or all outside
-                    const size_t o = (size_t)tm[b] * p.cols + k0;
+                const int k0 = (unit0 + unit) * kUnitWeights + 8 * lane;
+                if (trec[b] >= 0 && k0 < p.cols) {  // K is a multiple of 32, so a lane's 8 columns are all inside or all outside
+                    const size_t o = (size_t)m * p.cols + k0;
                     if (p.x_dtype == ZQ_F32) {
                         const float4 f0 = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p.x) + o);
                         const float4 f1 = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p.x) + o + 4);
@@ -363,8 +392,7 @@ __global__ void __launch_bounds__(kI8Threads, 1) gemv_i8_kernel(const __grid_con
             }
 #pragma unroll
             for (int b = 0; b < kBatch; ++b) {
-                if (tm[b] < 0) continue;  // warp-uniform
-                const int m = tm[b], unit = tu[b];
+                if (trec[b] < 0) continue;  // warp-uniform
                 float amax = 0.f;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[b][j]));
@@ -381,37 +409,62 @@ __global__ void __launch_bounds__(kI8Threads, 1) gemv_i8_kernel(const __grid_con
                     lo[j] = xq - (hi[j] << 8);
                     sum += xq;
                 }
-                const int i0 = 8 * lane;  // first of the lane's elements inside the unit
-#pragma unroll
-                for (int qd = 0; qd < 2; ++qd) {
-                    int G, tt, reg;
-                    i8_slot<TYPE>(i0 + 4 * qd, G, tt, reg);
-                    const uint32_t ph = (uint32_t)(hi[4 * qd] & 0xFF) | ((uint32_t)(hi[4 * qd + 1] & 0xFF) << 8) | ((uint32_t)(hi[4 * qd + 2] & 0xFF) << 16) | ((uint32_t)(hi[4 * qd + 3] & 0xFF) << 24);
-                    const uint32_t pl = (uint32_t)(lo[4 * qd] & 0xFF) | ((uint32_t)(lo[4 * qd + 1] & 0xFF) << 8) | ((uint32_t)(lo[4 * qd + 2] & 0xFF) << 16) | ((uint32_t)(lo[4 * qd + 3] & 0xFF) << 24);
-                    const int slot = (((unit * 8 + G) * CP + 2 * m) * 4 + tt) * 2 + reg;
-                    xw[slot] = ph;
-                    xw[slot + 8] = pl;  // next column: the lo limb
-                }
-                // the scale actually applied: x ~ x_q / inv
-                if (lane == 0) sact[unit * (4 * NT) + m] = live ? __fdividef(1.f, inv) : 0.f;
+                // the lane's two quads (columns 8 lane .. +3 and +4 .. +7) as packed limbs
+                uint32_t ph0 = pack_s8x4(hi[0], hi[1], hi[2], hi[3]), ph1 = pack_s8x4(hi[4], hi[5], hi[6], hi[7]);
+                uint32_t pl0 = pack_s8x4(lo[0], lo[1], lo[2], lo[3]), pl1 = pack_s8x4(lo[4], lo[5], lo[6], lo[7]);
+                uint32_t slot;
                 if constexpr (TYPE == ZQ_Q4_K) {
-                    // exact integer sum of each 32-column group, as two f16 limbs for the min-term MMA
+                    slot = (uint32_t)lane * 16;  // group lane / 4, slot t = lane % 4: both quads are this lane's
+                } else {
+                    // block lane / 4; the quads are (slot 2 (lane & 1) + qd, register r) with r = (lane >> 1) & 1: trade the
+                    // quad of the other slot for the partner's quad of this slot
+                    const int r = (lane >> 1) & 1;
+                    const uint32_t got_h = __shfl_xor_sync(0xffffffffu, r ? ph0 : ph1, 2), got_l = __shfl_xor_sync(0xffffffffu, r ? pl0 : pl1, 2);
+                    const uint32_t keep_h = r ? ph1 : ph0, keep_l = r ? pl1 : pl0;
+                    ph0 = r ? got_h : keep_h; ph1 = r ? keep_h : got_h;
+                    pl0 = r ? got_l : keep_l; pl1 = r ? keep_l : got_l;
+                    slot = (uint32_t)(4 * (lane >> 2) + 2 * (lane & 1) + r) * 16;
+                }
+                const uint32_t rec_off = (uint32_t)trec[b] * kRec;
+                // the scale actually applied: x ~ x_q / inv
+                const float scale = live ? __fdividef(1.f, inv) : 0.f;
+                uint32_t sw0 = 0, sw1 = 0;
+                if constexpr (TYPE == ZQ_Q4_K) {
+                    // exact integer sum of each 32-column group: |sum| can reach 32 * 32512, beyond f16, so
+                    // sum = 1024 a + r with |a| <= 1016, |r| <= 512, both exact in f16; the factor 1024 rides on the min
+                    // codes of the hi-limb K slots.  Fragment entry t' = {half2(a_2t', a_2t'+1), half2(r_2t', r_2t'+1)}.
                     sum += __shfl_xor_sync(0xffffffffu, sum, 1);
                     sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-                    if ((lane & 3) == 0) {
-                        const int G8 = lane >> 2;
-                        // |sum| can reach 32 * 32512, beyond f16: sum = 1024 a + r with |a| <= 1016, |r| <= 512, both exact
-                        // in f16; the factor 1024 rides on the min codes of the hi-limb K slots
-                        const int a = (sum + 512) >> 10, r = sum - (a << 10);
-                        __half *dst = reinterpret_cast<__half *>(&sxs[(unit * CP + 2 * m) * 4 + (G8 >> 1)]);
-                        dst[G8 & 1] = __int2half_rn(a);
-                        dst[2 + (G8 & 1)] = __int2half_rn(r);
+                    const int a = (sum + 512) >> 10, r = sum - (a << 10);
+                    const int oa = __shfl_xor_sync(0xffffffffu, a, 4), orr = __shfl_xor_sync(0xffffffffu, r, 4);
+                    sw0 = h2_as_u32(__halves2half2(__int2half_rn(a), __int2half_rn(oa)));
+                    sw1 = h2_as_u32(__halves2half2(__int2half_rn(r), __int2half_rn(orr)));
+                }
+                if (tshare == 1) {  // plain shared-memory stores
+                    uint8_t *dst = smem + ia.off_x + rec_off;
+                    *reinterpret_cast<uint4 *>(dst + slot) = make_uint4(ph0, ph1, pl0, pl1);
+                    if (TYPE == ZQ_Q4_K && (lane & 7) == 0) *reinterpret_cast<uint2 *>(dst + kRecSums + (lane >> 3) * 8) = make_uint2(sw0, sw1);
+                    if (lane == 0) *reinterpret_cast<float *>(dst + kRecScale) = scale;
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        if (q < tshare) {
+                            const uint32_t dst = peer_x[q] + rec_off;
+                            i8_st_cluster_v4(dst + slot, ph0, ph1, pl0, pl1);
+                            if (TYPE == ZQ_Q4_K && (lane & 7) == 0) i8_st_cluster_v2(dst + kRecSums + (lane >> 3) * 8, sw0, sw1);
+                            if (lane == 0) i8_st_cluster_u32(dst + kRecScale, __float_as_uint(scale));
+                        }
                     }
                 }
             }
         }
     }
-    __syncthreads();
+    if (tshare > 1) {
+        i8_cluster_arrive();
+        i8_cluster_wait();
+    } else {
+        __syncthreads();
+    }
 
     float yacc[NT][2];
 #pragma unroll
@@ -420,9 +473,20 @@ __global__ void __launch_bounds__(kI8Threads, 1) gemv_i8_kernel(const __grid_con
 
     {
         const uint32_t w_first = smem_u32(ws) + (uint32_t)(r0 * PITCH + ul * UB);
-        uint32_t xa = smem_u32(smem + ia.off_x) + (uint32_t)(ul * X_UNIT + lane * 8);
-        uint32_t sxa = smem_u32(smem + ia.off_sx) + (uint32_t)(ul * SX_UNIT + lane * 8);
-        uint32_t saa = smem_u32(smem + ia.off_sa) + (uint32_t)(ul * SA_UNIT + t * 4);
+        const uint32_t xoff = (uint32_t)(16 * t + 8 * (g & 1));
+        // records of the activation rows this lane touches (clamped to an existing row): its B column of tile nt is
+        // row 4 nt + g / 2, its accumulator columns are row 4 nt + t
+        uint32_t moff[NT], soff[NT];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            int m = 4 * nt + (g >> 1), ms = 4 * nt + t;
+            if (m > M - 1) m = M - 1;
+            if (ms > M - 1) ms = M - 1;
+            moff[nt] = (uint32_t)(m * kRec);
+            soff[nt] = (uint32_t)(ms * kRec);
+        }
+        const uint32_t unit_stride = (uint32_t)(M * kRec);
+        uint32_t recu = x_base + (uint32_t)ul * unit_stride;
         int stage = 0;
         uint32_t phase = 0;
         int unit_abs = unit0 + ul;
@@ -440,8 +504,14 @@ __global__ void __launch_bounds__(kI8Threads, 1) gemv_i8_kernel(const __grid_con
             i8_wait_or_abort(&full[stage], phase, &s_abort, p.status);
             if (unit_abs < ia.units_total) {
                 const uint32_t wq0 = w_first + (uint32_t)(stage * STAGE_W), wq1 = wq0 + 8 * PITCH;
-                if constexpr (TYPE == ZQ_Q4_K) consume_q4k_i8<NT>(wq0, wq1, t, xa, sxa, saa, yacc);
-                else consume_b32_i8<TYPE, NT>(wq0, wq1, t, xa, saa, yacc);
+                uint32_t rec[NT], srec[NT];
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    rec[nt] = recu + moff[nt];
+                    srec[nt] = recu + soff[nt];
+                }
+                if constexpr (TYPE == ZQ_Q4_K) consume_q4k_i8<NT>(wq0, wq1, t, rec, srec, xoff, yacc);
+                else consume_b32_i8<TYPE, NT>(wq0, wq1, t, rec, srec, xoff, yacc);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[stage]);
@@ -450,31 +520,36 @@ __global__ void __launch_bounds__(kI8Threads, 1) gemv_i8_kernel(const __grid_con
                 phase ^= 1u;
             }
             unit_abs += kChunkUnits;
-            xa += kChunkUnits * X_UNIT;
-            sxa += kChunkUnits * SX_UNIT;
-            saa += kChunkUnits * SA_UNIT;
+            recu += kChunkUnits * unit_stride;
         }
     }
 
     // ---------------------------------------------------- end of the K slice: combine and store
     {
         // Every CTA leaves its partial tile (one copy per unit half) in its own shared memory; after one barrier
-        // (cluster-wide when the tile is split) the threads of rank 0 add up, for their output element, the halves
-        // of every rank in rank order (deterministic), apply the epilogue and store.
+        // (cluster-wide when the tile is split) the threads of slice 0 add up, for their output element, the halves
+        // of every slice in slice order (deterministic), apply the epilogue and store.
         constexpr int RS = NT * 4;  // activation rows a tile row can hold
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
             red[(ul * RS + nt * 4 + t) * kTileRows + r0] = yacc[nt][0];  // [unit half][activation row][tile row]
             red[(ul * RS + nt * 4 + t) * kTileRows + r0 + 8] = yacc[nt][1];
         }
-        if (split > 1) i8_cluster_sync();
-        else __syncthreads();
+        if (split > 1) {
+            i8_cluster_arrive();
+            i8_cluster_wait();
+        } else {
+            __syncthreads();
+        }
         if (my_rank == 0) {
             constexpr int out_rows = GATED ? kTileRows / 2 : kTileRows;
             auto total_of = [&](int rr, int tok) -> float {
                 const float *a = &red[tok * kTileRows + rr], *b = &red[(RS + tok) * kTileRows + rr];
                 float v = *a + *b;
-                for (int r = 1; r < split; ++r) v += i8_ld_cluster_f32(a, (uint32_t)r) + i8_ld_cluster_f32(b, (uint32_t)r);
+                for (int r = 1; r < split; ++r) {
+                    const uint32_t peer = (uint32_t)(tile_local * split + r);
+                    v += i8_ld_cluster_f32(i8_mapa(smem_u32(a), peer)) + i8_ld_cluster_f32(i8_mapa(smem_u32(b), peer));
+                }
                 return v;
             };
             for (int i = tid; i < out_rows * M; i += kI8Threads) {
@@ -493,47 +568,74 @@ __global__ void __launch_bounds__(kI8Threads, 1) gemv_i8_kernel(const __grid_con
                 store_from_f32(p.y, p.y_dtype, o, v);
             }
         }
-        if (split > 1) i8_cluster_sync();  // nobody leaves while rank 0 may still read its shared memory
+        if (split > 1) {  // nobody leaves while slice 0 may still read its shared memory
+            i8_cluster_arrive();
+            i8_cluster_wait();
+        }
     }
 }
 
-// Shared-memory plan: CTAs per tile (cluster size), ring depth and offsets; false when fewer than two ring stages
-// fit beside the quantised activation slice.
+// How many clusters of a configuration can be resident at once (cached: the query is a host-side driver call).
+template <class Kernel>
+static int max_active_clusters(Kernel kernel, int device, int cluster, int smem_bytes, int grid) {
+    static std::mutex mu;
+    static std::map<std::tuple<const void *, int, int, int>, int> cache;
+    const auto key = std::make_tuple((const void *)kernel, device, cluster, smem_bytes);
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) return it->second;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(grid - grid % cluster));
+    cfg.blockDim = dim3(kI8Threads);
+    cfg.dynamicSmemBytes = (size_t)smem_bytes;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)cluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        n = 0;
+    }
+    cache[key] = n;
+    return n;
+}
+
+// Shared-memory plan: K slices per tile, ring depth and offsets; false when fewer than two ring stages fit beside
+// the quantised activation slice.
 template <uint32_t TYPE, int NT>
 static bool plan_i8(int m, int units_total, int tiles, int chunks, int sm_count, I8Args &ia, int &total_bytes) {
     constexpr int STAGE_W = kTileRows * kChunkUnits * Fmt<TYPE>::unit_bytes;
-    constexpr int CP = 8 * NT;  // MMA columns, padded to whole column tiles
     const int max_smem = 232448 - 256;  // 227 KB opt-in limit minus static shared and alignment slack
     const int red_bytes = 2 * kTileRows * NT * 4 * 4;
-    // CTAs per tile: as many K slices as fill the SMs (any cluster size up to 8, not only powers of two); more than
-    // that, i.e. more CTAs than SMs, only when the activation slice would otherwise leave no room for the ring
+    // K slices per tile: as many as fill the SMs (any count up to 8, not only powers of two); more than that, i.e.
+    // more CTAs than SMs, only when the activation slice would otherwise leave no room for the ring
     int split = sm_count / (tiles > 0 ? tiles : 1);
     if (split > 8) split = 8;
     if (split > chunks) split = chunks;
     if (split < 1) split = 1;
-    int room = 0, slice_chunks = 0, x_bytes = 0, sx_bytes = 0, sa_bytes = 0;  // room: ring stages that fit
+    int room = 0, slice_chunks = 0, x_bytes = 0;  // room: ring stages that fit
     for (;; ++split) {
         slice_chunks = (chunks + split - 1) / split;
         int slice_units = slice_chunks * kChunkUnits;
         if (slice_units > units_total) slice_units = units_total;
-        x_bytes = slice_units * 8 * CP * 32;
-        sx_bytes = TYPE == ZQ_Q4_K ? slice_units * CP * 32 : 0;
-        sa_bytes = (slice_units * 4 * NT * 4 + 127) & ~127;
-        room = (max_smem - (x_bytes + sx_bytes + sa_bytes + red_bytes + 128 + 128)) / STAGE_W;
+        x_bytes = (slice_units * m * kRec + 127) & ~127;
+        room = (max_smem - (x_bytes + red_bytes + 128 + 128)) / STAGE_W;
         if (room >= 3 || split >= 8 || split >= chunks) break;
     }
     if (room < 2) return false;
     int stages = room > 5 ? 5 : room;
     if (stages > slice_chunks + 1) stages = slice_chunks + 1;  // no point in more ring than work
     if (stages < 2) stages = 2;
-    (void)m;
     ia.stages = stages;
     ia.split = split;
+    ia.tshare = 1;
     ia.units_total = units_total;
     ia.off_x = stages * STAGE_W;
-    ia.off_sx = ia.off_x + x_bytes;
-    ia.off_sa = ia.off_sx + sx_bytes;
-    ia.off_red = ia.off_sa + sa_bytes;
+    ia.off_red = ia.off_x + x_bytes;
     ia.off_bar = ia.off_red + red_bytes;
     total_bytes = ia.off_bar + 128 + 128;
     return true;
@@ -551,16 +653,31 @@ static int launch_i8_one(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up,
         ZQ_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 256), err);
         configured[ctx->device & 63] = true;
     }
+    // Tiles per cluster that share the activation staging: the largest divisor of the tile count that keeps the
+    // cluster within 8 CTAs and still lets as many CTAs run at once as unshared clusters would.
+    const int grid = p.tiles * ia.split;
+    if (p.m * (int)w->units_per_row >= 32) {  // a handful of records is quicker done by every CTA for itself
+        const int base_active = max_active_clusters(kernel, ctx->device, ia.split, total, grid) * ia.split;
+        const int want = grid < base_active ? grid : base_active;
+        for (int ts = 8 / ia.split; ts > 1; --ts) {
+            if (p.tiles % ts) continue;
+            const int c = ia.split * ts;
+            if (max_active_clusters(kernel, ctx->device, c, total, grid) * c >= want) {
+                ia.tshare = ts;
+                break;
+            }
+        }
+    }
     const CUtensorMap &ma = GATED ? w->gemv_map_half : w->gemv_map;
     const CUtensorMap &mb = GATED ? w_up->gemv_map_half : w->gemv_map;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(p.tiles * ia.split));
+    cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3(kI8Threads);
     cfg.dynamicSmemBytes = (size_t)total;
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = (unsigned)ia.split;
+    attr[0].val.clusterDim.x = (unsigned)(ia.split * ia.tshare);
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
