@@ -54,10 +54,23 @@ int ensure_workspace(zq_ctx *ctx, size_t bytes, zq_error *err) {
     return ZQ_OK;
 }
 
+int ensure_xq(zq_ctx *ctx, size_t bytes, zq_error *err) {
+    if (bytes <= ctx->xq_bytes) return ZQ_OK;
+    ZQ_CUDA_CHECK(cudaStreamSynchronize(ctx->stream), err);
+    if (ctx->xq) cudaFree(ctx->xq);
+    ctx->xq = nullptr;
+    ctx->xq_bytes = 0;
+    size_t rounded = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+    ZQ_CUDA_CHECK(cudaMalloc(&ctx->xq, rounded), err);
+    ctx->xq_bytes = rounded;
+    return ZQ_OK;
+}
+
 int ensure_scratch_mid(zq_ctx *ctx, size_t bytes, zq_error *err) {
     if (bytes <= ctx->mid_bytes) return ZQ_OK;
     ZQ_CUDA_CHECK(cudaStreamSynchronize(ctx->stream), err);
     if (ctx->mid) cudaFree(ctx->mid);
+    if (ctx->xq) cudaFree(ctx->xq);
     ctx->mid = nullptr;
     ctx->mid_bytes = 0;
     size_t rounded = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);

@@ -131,6 +131,13 @@ __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, u
                  "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
                  : "memory");
 }
+// 1-D bulk copy, global -> this CTA's shared memory, completion on an mbarrier.  Both addresses 16-byte aligned, size a
+// multiple of 16 bytes.  No multicast.
+__device__ __forceinline__ void bulk_load_1d(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes),
+                 "r"(smem_u32(bar))
+                 : "memory");
+}
 __device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, uint64_t *bar, int x, int y, int z) {
     asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(smem_u32(dst)),
                  "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
@@ -213,6 +220,9 @@ struct zq_ctx {
     // MoE buffers: routing tables, gathered rows, per-route activations and outputs (grows on demand).
     void *moe_ws = nullptr;
     size_t moe_ws_bytes = 0;
+    // Quantised activations of the integer-MMA decode kernel for more than 4 rows (grows on demand).
+    void *xq = nullptr;
+    size_t xq_bytes = 0;
     // Activated intermediate [m, I] of gated_mlp (grows on demand).
     void *mid = nullptr;
     size_t mid_bytes = 0;
@@ -230,8 +240,8 @@ struct zq_ctx {
     // 1 = run Q4_K decode on the tcgen05 kernel (zq_qmv.cu) instead of the warp-MMA kernels.  Off by default: it is
     // parity-clean but, as measured, not yet faster than the warp-MMA path.
     int enable_tcgen05_gemv = 0;
-    int force_f16_gemv = 0;
-    int disable_pdl = 0;     // launch decode kernels without programmatic dependent launch  // skip the integer-MMA decode kernel (tests of the f16 kernels)
+    int force_f16_gemv = 0;  // skip the integer-MMA decode kernel (tests of the f16 kernels)
+    int disable_pdl = 0;     // launch decode kernels without programmatic dependent launch
     std::atomic<uint64_t> launches{0};
     std::mutex mutex;
 };
@@ -252,6 +262,7 @@ struct zq_weight {
 
 namespace zq {
 int ensure_workspace(zq_ctx *ctx, size_t bytes, zq_error *err);
+int ensure_xq(zq_ctx *ctx, size_t bytes, zq_error *err);
 int ensure_scratch_mid(zq_ctx *ctx, size_t bytes, zq_error *err);
 int make_weight_map(const zq_weight *w, int box_words, int box_rows, CUtensorMap *out, zq_error *err);
 

@@ -477,7 +477,7 @@ int launch_gemv_noalloc(zq_ctx *ctx, const zq_weight *w, const void *x, int x_dt
         rc = launch_qmv(ctx, w, p, taken, err);
         if (rc || taken) return rc;
     }
-    if (!ctx->force_staged_gemv && !ctx->force_f16_gemv) {
+    if (!ctx->force_staged_gemv && !ctx->force_f16_gemv && m <= 4) {  // beyond 4 rows that kernel wants a device buffer it may have to allocate
         rc = launch_gemv_i8(ctx, w, nullptr, p, taken, err);
         if (rc || taken) return rc;
     }

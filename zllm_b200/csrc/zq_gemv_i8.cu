@@ -48,6 +48,8 @@ struct I8Args {
     int tshare;       // neighbouring tiles per cluster that share the activation staging (cluster = tshare * split CTAs)
     int units_total;  // resident units per row (ceil(K / 256))
     int off_x, off_red, off_bar;  // byte offsets from the 128-byte aligned base (weights at 0)
+    int stage_stride;       // bytes from one ring stage to the next (weights, plus the chunk's records when streamed)
+    const uint8_t *xq;      // streamed variant: all records of the activation block in global memory
 };
 
 __device__ __forceinline__ void i8_cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
@@ -277,11 +279,120 @@ __device__ __forceinline__ void consume_b32_i8(uint32_t wq0, uint32_t wq1, int t
     }
 }
 
+
+// Eight consecutive activation columns starting at element offset o, as f32 (zeros when !valid).
+__device__ __forceinline__ void load_act8(const void *x, int x_dtype, size_t o, bool valid, float (&v)[8]) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = 0.f;
+    if (!valid) return;
+    if (x_dtype == ZQ_F32) {
+        const float4 f0 = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(x) + o);
+        const float4 f1 = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(x) + o + 4);
+        v[0] = f0.x; v[1] = f0.y; v[2] = f0.z; v[3] = f0.w; v[4] = f1.x; v[5] = f1.y; v[6] = f1.z; v[7] = f1.w;
+    } else {
+        const uint4 raw = *reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(x) + o);
+        const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (x_dtype == ZQ_F16) {
+                const float2 f = __half22float2(u32_as_h2(rw[j]));
+                v[2 * j] = f.x; v[2 * j + 1] = f.y;
+            } else {  // bf16: the upper half of an f32
+                v[2 * j] = __uint_as_float(rw[j] << 16);
+                v[2 * j + 1] = __uint_as_float(rw[j] & 0xFFFF0000u);
+            }
+        }
+    }
+}
+
+// What one lane contributes to a record: its 16-byte fragment slot, and (some lanes) group sums and the scale.
+struct RecLane {
+    uint32_t ph0, ph1, pl0, pl1;  // hi-limb pair, lo-limb pair
+    uint32_t slot;                // byte offset of the 16-byte slot inside the record
+    uint32_t sw0, sw1;            // Q4_K, lanes with lane % 8 == 0: min-term fragment entry lane / 8
+    float scale;                  // lane 0: slice scale
+};
+
+// Quantises one record (256 columns of one activation row; the lane holds columns 8 lane .. 8 lane + 7).  All 32
+// lanes of the warp must call it together.
+template <uint32_t TYPE> __device__ __forceinline__ RecLane quantize_record(const float (&v)[8], int lane) {
+    RecLane o;
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+#pragma unroll
+    for (int s = 16; s >= 1; s >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, s));
+    const bool live = amax > 0.f && amax < 3.0e38f;
+    const float inv = live ? __fdividef(kActMax, amax) : 0.f;
+    o.scale = live ? __fdividef(1.f, inv) : 0.f;  // the scale actually applied: x ~ x_q / inv
+    int hi[8], lo[8], sum = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        int xq = __float2int_rn(v[j] * inv);
+        xq = xq > 32512 ? 32512 : (xq < -32512 ? -32512 : xq);
+        hi[j] = (xq + 128) >> 8;
+        lo[j] = xq - (hi[j] << 8);
+        sum += xq;
+    }
+    // the lane's two quads (columns 8 lane .. +3 and +4 .. +7) as packed limbs
+    o.ph0 = pack_s8x4(hi[0], hi[1], hi[2], hi[3]); o.ph1 = pack_s8x4(hi[4], hi[5], hi[6], hi[7]);
+    o.pl0 = pack_s8x4(lo[0], lo[1], lo[2], lo[3]); o.pl1 = pack_s8x4(lo[4], lo[5], lo[6], lo[7]);
+    if constexpr (TYPE == ZQ_Q4_K) {
+        o.slot = (uint32_t)lane * 16;  // group lane / 4, slot t = lane % 4: both quads are this lane's
+    } else {
+        // block lane / 4; the quads are (slot 2 (lane & 1) + qd, register r) with r = (lane >> 1) & 1: trade the quad of
+        // the other slot for the partner's quad of this slot
+        const int r = (lane >> 1) & 1;
+        const uint32_t got_h = __shfl_xor_sync(0xffffffffu, r ? o.ph0 : o.ph1, 2), got_l = __shfl_xor_sync(0xffffffffu, r ? o.pl0 : o.pl1, 2);
+        const uint32_t keep_h = r ? o.ph1 : o.ph0, keep_l = r ? o.pl1 : o.pl0;
+        o.ph0 = r ? got_h : keep_h; o.ph1 = r ? keep_h : got_h;
+        o.pl0 = r ? got_l : keep_l; o.pl1 = r ? keep_l : got_l;
+        o.slot = (uint32_t)(4 * (lane >> 2) + 2 * (lane & 1) + r) * 16;
+    }
+    o.sw0 = o.sw1 = 0;
+    if constexpr (TYPE == ZQ_Q4_K) {
+        // exact integer sum of each 32-column group: |sum| can reach 32 * 32512, beyond f16, so sum = 1024 a + r with
+        // |a| <= 1016, |r| <= 512, both exact in f16; the factor 1024 rides on the min codes of the hi-limb K slots.
+        // Fragment entry t' = {half2(a_2t', a_2t'+1), half2(r_2t', r_2t'+1)}.
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        const int a = (sum + 512) >> 10, r = sum - (a << 10);
+        const int oa = __shfl_xor_sync(0xffffffffu, a, 4), orr = __shfl_xor_sync(0xffffffffu, r, 4);
+        o.sw0 = h2_as_u32(__halves2half2(__int2half_rn(a), __int2half_rn(oa)));
+        o.sw1 = h2_as_u32(__halves2half2(__int2half_rn(r), __int2half_rn(orr)));
+    }
+    return o;
+}
+
+// Quantises all records of an activation block [m, K] into global memory (record index = unit * m + row), for
+// the kernel variant that streams the records through its ring instead of keeping them resident.
+template <uint32_t TYPE>
+__global__ void __launch_bounds__(256) quantize_acts_kernel(const void *x, int x_dtype, int M, int cols, int units_total, uint8_t *out) {
+    pdl_launch_dependents();
+    pdl_wait_prior_grid();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int rec = blockIdx.x * 8 + warp;
+    if (rec >= M * units_total) return;  // warp-uniform
+    const int unit = rec / M, m = rec - unit * M;
+    const int k0 = unit * kUnitWeights + 8 * lane;
+    float v[8];
+    load_act8(x, x_dtype, (size_t)m * cols + k0, k0 < cols, v);
+    const RecLane o = quantize_record<TYPE>(v, lane);
+    uint8_t *dst = out + (size_t)rec * kRec;
+    *reinterpret_cast<uint4 *>(dst + o.slot) = make_uint4(o.ph0, o.ph1, o.pl0, o.pl1);
+    if (TYPE == ZQ_Q4_K && (lane & 7) == 0) *reinterpret_cast<uint2 *>(dst + kRecSums + (lane >> 3) * 8) = make_uint2(o.sw0, o.sw1);
+    if (lane == 0) *reinterpret_cast<float *>(dst + kRecScale) = o.scale;
+}
+
 template <uint32_t TYPE, int NT, bool GATED>
 __global__ void __launch_bounds__(kI8Threads, 1) gemv_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemvParams p, const I8Args ia) {
     constexpr int UB = Fmt<TYPE>::unit_bytes;
     constexpr int PITCH = kChunkUnits * UB;
     constexpr int STAGE_W = kTileRows * PITCH;
+    // More than 4 activation rows: the records would crowd the ring out of shared memory, and quantising them in every
+    // CTA would cost more than the matrix; a small kernel quantises them once into global memory and every ring stage
+    // brings the records of its two units along with the weights.
+    constexpr bool XS = NT > 1;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
     uint8_t *ws = smem;
@@ -315,10 +426,19 @@ __global__ void __launch_bounds__(kI8Threads, 1) gemv_i8_kernel(const __grid_con
     }
     __syncthreads();
 
-    auto issue_tma = [&](int local, int stage) {
+    const int M = p.m;
+    const int stage_stride = ia.stage_stride;
+    // weights of ring item `local` (and the byte count the stage's barrier has to see)
+    auto issue_w = [&](int local, int stage) {
         const int chunk = chunk_begin + local;
-        uint8_t *dst = ws + (size_t)stage * STAGE_W;
-        mbar_expect_tx(&full[stage], STAGE_W);
+        uint8_t *dst = ws + (size_t)stage * stage_stride;
+        uint32_t bytes = STAGE_W;
+        if (XS) {
+            int nu = ia.units_total - chunk * kChunkUnits;
+            if (nu > kChunkUnits) nu = kChunkUnits;
+            bytes += (uint32_t)(nu * M * kRec);
+        }
+        mbar_expect_tx(&full[stage], bytes);
         if (GATED) {
             tma_load_2d(dst, &map_a, &full[stage], chunk * p.chunk_words, my_tile * rows_per_tile);
             tma_load_2d(dst + STAGE_W / 2, &map_b, &full[stage], chunk * p.chunk_words, my_tile * rows_per_tile);
@@ -326,15 +446,22 @@ __global__ void __launch_bounds__(kI8Threads, 1) gemv_i8_kernel(const __grid_con
             tma_load_2d(dst, &map_a, &full[stage], chunk * p.chunk_words, my_tile * rows_per_tile);
         }
     };
+    // streamed variant: the records of the item's units, right behind the weights of the stage
+    auto issue_x = [&](int local, int stage) {
+        if (!XS) return;
+        const int chunk = chunk_begin + local;
+        int nu = ia.units_total - chunk * kChunkUnits;
+        if (nu > kChunkUnits) nu = kChunkUnits;
+        bulk_load_1d(ws + (size_t)stage * stage_stride + STAGE_W, ia.xq + (size_t)chunk * kChunkUnits * M * kRec, (uint32_t)(nu * M * kRec), &full[stage]);
+    };
+    const int pre = n_items < STAGES - 1 ? n_items : STAGES - 1;
     if (tid == 0) {
-        const int pre = n_items < STAGES - 1 ? n_items : STAGES - 1;
-        for (int s = 0; s < pre; ++s) issue_tma(s, s);
+        for (int s = 0; s < pre; ++s) issue_w(s, s);
     }
     pdl_launch_dependents();
 
     const int g = lane >> 2, t = lane & 3;
     const int rs = warp & 7, ul = warp >> 3;
-    const int M = p.m;
 
     int slice_units = chunk_end * kChunkUnits;
     if (slice_units > ia.units_total) slice_units = ia.units_total;
@@ -343,6 +470,11 @@ __global__ void __launch_bounds__(kI8Threads, 1) gemv_i8_kernel(const __grid_con
     const uint32_t x_base = smem_u32(smem + ia.off_x);
 
     pdl_wait_prior_grid();  // activations (and, later, outputs) belong to the previous kernel until it completes
+    if (XS) {
+        if (tid == 0) {
+            for (int s = 0; s < pre; ++s) issue_x(s, s);
+        }
+    } else {
     if (tshare > 1) i8_cluster_wait();  // every CTA of the cluster is running: its shared memory may be written
     {
         // Quantise this CTA's share of the activation slice (every tshare-th record), one warp per record, 8
@@ -362,97 +494,31 @@ __global__ void __launch_bounds__(kI8Threads, 1) gemv_i8_kernel(const __grid_con
 #pragma unroll
             for (int b = 0; b < kBatch; ++b) {
                 const int k = base + b * kWarps;
-                const int task = tile_local + tshare * k;  // record index: unit-major, then activation row
+                const int task = tile_local + tshare * k;  // record index inside the slice: unit-major, then activation row
                 trec[b] = k < n_mine ? task : -1;
                 const int unit = task / M, m = task - unit * M;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) v[b][j] = 0.f;
                 const int k0 = (unit0 + unit) * kUnitWeights + 8 * lane;
-                if (trec[b] >= 0 && k0 < p.cols) {  // K is a multiple of 32, so a lane's 8 columns are all inside or all outside
-                    const size_t o = (size_t)m * p.cols + k0;
-                    if (p.x_dtype == ZQ_F32) {
-                        const float4 f0 = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p.x) + o);
-                        const float4 f1 = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p.x) + o + 4);
-                        v[b][0] = f0.x; v[b][1] = f0.y; v[b][2] = f0.z; v[b][3] = f0.w; v[b][4] = f1.x; v[b][5] = f1.y; v[b][6] = f1.z; v[b][7] = f1.w;
-                    } else {
-                        const uint4 raw = *reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(p.x) + o);
-                        const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            if (p.x_dtype == ZQ_F16) {
-                                const float2 f = __half22float2(u32_as_h2(rw[j]));
-                                v[b][2 * j] = f.x; v[b][2 * j + 1] = f.y;
-                            } else {  // bf16: the upper half of an f32
-                                v[b][2 * j] = __uint_as_float(rw[j] << 16);
-                                v[b][2 * j + 1] = __uint_as_float(rw[j] & 0xFFFF0000u);
-                            }
-                        }
-                    }
-                }
+                // K is a multiple of 32, so a lane's 8 columns are all inside or all outside
+                load_act8(p.x, p.x_dtype, (size_t)m * p.cols + k0, trec[b] >= 0 && k0 < p.cols, v[b]);
             }
 #pragma unroll
             for (int b = 0; b < kBatch; ++b) {
                 if (trec[b] < 0) continue;  // warp-uniform
-                float amax = 0.f;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[b][j]));
-#pragma unroll
-                for (int s = 16; s >= 1; s >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, s));
-                const bool live = amax > 0.f && amax < 3.0e38f;
-                const float inv = live ? __fdividef(kActMax, amax) : 0.f;
-                int hi[8], lo[8], sum = 0;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    int xq = __float2int_rn(v[b][j] * inv);
-                    xq = xq > 32512 ? 32512 : (xq < -32512 ? -32512 : xq);
-                    hi[j] = (xq + 128) >> 8;
-                    lo[j] = xq - (hi[j] << 8);
-                    sum += xq;
-                }
-                // the lane's two quads (columns 8 lane .. +3 and +4 .. +7) as packed limbs
-                uint32_t ph0 = pack_s8x4(hi[0], hi[1], hi[2], hi[3]), ph1 = pack_s8x4(hi[4], hi[5], hi[6], hi[7]);
-                uint32_t pl0 = pack_s8x4(lo[0], lo[1], lo[2], lo[3]), pl1 = pack_s8x4(lo[4], lo[5], lo[6], lo[7]);
-                uint32_t slot;
-                if constexpr (TYPE == ZQ_Q4_K) {
-                    slot = (uint32_t)lane * 16;  // group lane / 4, slot t = lane % 4: both quads are this lane's
-                } else {
-                    // block lane / 4; the quads are (slot 2 (lane & 1) + qd, register r) with r = (lane >> 1) & 1: trade the
-                    // quad of the other slot for the partner's quad of this slot
-                    const int r = (lane >> 1) & 1;
-                    const uint32_t got_h = __shfl_xor_sync(0xffffffffu, r ? ph0 : ph1, 2), got_l = __shfl_xor_sync(0xffffffffu, r ? pl0 : pl1, 2);
-                    const uint32_t keep_h = r ? ph1 : ph0, keep_l = r ? pl1 : pl0;
-                    ph0 = r ? got_h : keep_h; ph1 = r ? keep_h : got_h;
-                    pl0 = r ? got_l : keep_l; pl1 = r ? keep_l : got_l;
-                    slot = (uint32_t)(4 * (lane >> 2) + 2 * (lane & 1) + r) * 16;
-                }
+                const RecLane o = quantize_record<TYPE>(v[b], lane);
                 const uint32_t rec_off = (uint32_t)trec[b] * kRec;
-                // the scale actually applied: x ~ x_q / inv
-                const float scale = live ? __fdividef(1.f, inv) : 0.f;
-                uint32_t sw0 = 0, sw1 = 0;
-                if constexpr (TYPE == ZQ_Q4_K) {
-                    // exact integer sum of each 32-column group: |sum| can reach 32 * 32512, beyond f16, so
-                    // sum = 1024 a + r with |a| <= 1016, |r| <= 512, both exact in f16; the factor 1024 rides on the min
-                    // codes of the hi-limb K slots.  Fragment entry t' = {half2(a_2t', a_2t'+1), half2(r_2t', r_2t'+1)}.
-                    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-                    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-                    const int a = (sum + 512) >> 10, r = sum - (a << 10);
-                    const int oa = __shfl_xor_sync(0xffffffffu, a, 4), orr = __shfl_xor_sync(0xffffffffu, r, 4);
-                    sw0 = h2_as_u32(__halves2half2(__int2half_rn(a), __int2half_rn(oa)));
-                    sw1 = h2_as_u32(__halves2half2(__int2half_rn(r), __int2half_rn(orr)));
-                }
                 if (tshare == 1) {  // plain shared-memory stores
                     uint8_t *dst = smem + ia.off_x + rec_off;
-                    *reinterpret_cast<uint4 *>(dst + slot) = make_uint4(ph0, ph1, pl0, pl1);
-                    if (TYPE == ZQ_Q4_K && (lane & 7) == 0) *reinterpret_cast<uint2 *>(dst + kRecSums + (lane >> 3) * 8) = make_uint2(sw0, sw1);
-                    if (lane == 0) *reinterpret_cast<float *>(dst + kRecScale) = scale;
+                    *reinterpret_cast<uint4 *>(dst + o.slot) = make_uint4(o.ph0, o.ph1, o.pl0, o.pl1);
+                    if (TYPE == ZQ_Q4_K && (lane & 7) == 0) *reinterpret_cast<uint2 *>(dst + kRecSums + (lane >> 3) * 8) = make_uint2(o.sw0, o.sw1);
+                    if (lane == 0) *reinterpret_cast<float *>(dst + kRecScale) = o.scale;
                 } else {
 #pragma unroll
                     for (int q = 0; q < 8; ++q) {
                         if (q < tshare) {
                             const uint32_t dst = peer_x[q] + rec_off;
-                            i8_st_cluster_v4(dst + slot, ph0, ph1, pl0, pl1);
-                            if (TYPE == ZQ_Q4_K && (lane & 7) == 0) i8_st_cluster_v2(dst + kRecSums + (lane >> 3) * 8, sw0, sw1);
-                            if (lane == 0) i8_st_cluster_u32(dst + kRecScale, __float_as_uint(scale));
+                            i8_st_cluster_v4(dst + o.slot, o.ph0, o.ph1, o.pl0, o.pl1);
+                            if (TYPE == ZQ_Q4_K && (lane & 7) == 0) i8_st_cluster_v2(dst + kRecSums + (lane >> 3) * 8, o.sw0, o.sw1);
+                            if (lane == 0) i8_st_cluster_u32(dst + kRecScale, __float_as_uint(o.scale));
                         }
                     }
                 }
@@ -465,6 +531,7 @@ __global__ void __launch_bounds__(kI8Threads, 1) gemv_i8_kernel(const __grid_con
     } else {
         __syncthreads();
     }
+    }  // !XS
 
     float yacc[NT][2];
 #pragma unroll
@@ -486,7 +553,8 @@ __global__ void __launch_bounds__(kI8Threads, 1) gemv_i8_kernel(const __grid_con
             soff[nt] = (uint32_t)(ms * kRec);
         }
         const uint32_t unit_stride = (uint32_t)(M * kRec);
-        uint32_t recu = x_base + (uint32_t)ul * unit_stride;
+        // resident: walks the slice's records; streamed: the stage's own two units
+        uint32_t recu = (XS ? smem_u32(ws) + STAGE_W : x_base) + (uint32_t)ul * unit_stride;
         int stage = 0;
         uint32_t phase = 0;
         int unit_abs = unit0 + ul;
@@ -497,18 +565,23 @@ __global__ void __launch_bounds__(kI8Threads, 1) gemv_i8_kernel(const __grid_con
                 if (nxt < n_items && warp == (it & 15) && lane == 0) {
                     const int nstage = stage == 0 ? STAGES - 1 : stage - 1;
                     if (it >= 1) i8_wait_or_abort(&empty[nstage], stage == 0 ? phase ^ 1u : phase, &s_abort, p.status);
-                    if (!*(volatile int *)&s_abort) issue_tma(nxt, nstage);  // never start a copy nobody will wait for
+                    if (!*(volatile int *)&s_abort) {  // never start a copy nobody will wait for
+                        issue_w(nxt, nstage);
+                        issue_x(nxt, nstage);
+                    }
                 }
                 __syncwarp();
             }
             i8_wait_or_abort(&full[stage], phase, &s_abort, p.status);
             if (unit_abs < ia.units_total) {
-                const uint32_t wq0 = w_first + (uint32_t)(stage * STAGE_W), wq1 = wq0 + 8 * PITCH;
+                const uint32_t soffs = (uint32_t)(stage * stage_stride);
+                const uint32_t wq0 = w_first + soffs, wq1 = wq0 + 8 * PITCH;
+                const uint32_t rb = XS ? recu + soffs : recu;
                 uint32_t rec[NT], srec[NT];
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
-                    rec[nt] = recu + moff[nt];
-                    srec[nt] = recu + soff[nt];
+                    rec[nt] = rb + moff[nt];
+                    srec[nt] = rb + soff[nt];
                 }
                 if constexpr (TYPE == ZQ_Q4_K) consume_q4k_i8<NT>(wq0, wq1, t, rec, srec, xoff, yacc);
                 else consume_b32_i8<TYPE, NT>(wq0, wq1, t, rec, srec, xoff, yacc);
@@ -520,7 +593,7 @@ __global__ void __launch_bounds__(kI8Threads, 1) gemv_i8_kernel(const __grid_con
                 phase ^= 1u;
             }
             unit_abs += kChunkUnits;
-            recu += kChunkUnits * unit_stride;
+            if (!XS) recu += kChunkUnits * unit_stride;
         }
     }
 
@@ -618,23 +691,32 @@ static bool plan_i8(int m, int units_total, int tiles, int chunks, int sm_count,
     if (split > chunks) split = chunks;
     if (split < 1) split = 1;
     int room = 0, slice_chunks = 0, x_bytes = 0;  // room: ring stages that fit
-    for (;; ++split) {
+    int stage_stride = STAGE_W;
+    if (NT > 1) {  // records stream through the ring: nothing resident, no reason to split beyond the SM count
+        stage_stride = STAGE_W + kChunkUnits * m * kRec;
         slice_chunks = (chunks + split - 1) / split;
-        int slice_units = slice_chunks * kChunkUnits;
-        if (slice_units > units_total) slice_units = units_total;
-        x_bytes = (slice_units * m * kRec + 127) & ~127;
-        room = (max_smem - (x_bytes + red_bytes + 128 + 128)) / STAGE_W;
-        if (room >= 3 || split >= 8 || split >= chunks) break;
+        room = (max_smem - (red_bytes + 128 + 128)) / stage_stride;
+    } else {
+        for (;; ++split) {
+            slice_chunks = (chunks + split - 1) / split;
+            int slice_units = slice_chunks * kChunkUnits;
+            if (slice_units > units_total) slice_units = units_total;
+            x_bytes = (slice_units * m * kRec + 127) & ~127;
+            room = (max_smem - (x_bytes + red_bytes + 128 + 128)) / STAGE_W;
+            if (room >= 3 || split >= 8 || split >= chunks) break;
+        }
     }
     if (room < 2) return false;
     int stages = room > 5 ? 5 : room;
     if (stages > slice_chunks + 1) stages = slice_chunks + 1;  // no point in more ring than work
     if (stages < 2) stages = 2;
+    ia.stage_stride = stage_stride;
+    ia.xq = nullptr;
     ia.stages = stages;
     ia.split = split;
     ia.tshare = 1;
     ia.units_total = units_total;
-    ia.off_x = stages * STAGE_W;
+    ia.off_x = stages * stage_stride;
     ia.off_red = ia.off_x + x_bytes;
     ia.off_bar = ia.off_red + red_bytes;
     total_bytes = ia.off_bar + 128 + 128;
@@ -653,10 +735,28 @@ static int launch_i8_one(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up,
         ZQ_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 256), err);
         configured[ctx->device & 63] = true;
     }
+    if (NT > 1) {
+        // quantise the activation block once; the main kernel's ring picks the records up
+        const int records = p.m * (int)w->units_per_row;
+        int rc = ensure_xq(ctx, (size_t)records * kRec, err);
+        if (rc) return rc;
+        ia.xq = reinterpret_cast<const uint8_t *>(ctx->xq);
+        cudaLaunchConfig_t qcfg = {};
+        qcfg.gridDim = dim3((unsigned)((records + 7) / 8));
+        qcfg.blockDim = dim3(256);
+        qcfg.stream = ctx->stream;
+        cudaLaunchAttribute qattr[1];
+        qattr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        qattr[0].val.programmaticStreamSerializationAllowed = 1;
+        qcfg.attrs = qattr;
+        qcfg.numAttrs = ctx->disable_pdl ? 0 : 1;
+        ZQ_CUDA_CHECK(cudaLaunchKernelEx(&qcfg, quantize_acts_kernel<TYPE>, p.x, p.x_dtype, p.m, p.cols, (int)w->units_per_row, reinterpret_cast<uint8_t *>(ctx->xq)), err);
+        ctx->launches++;
+    }
     // Tiles per cluster that share the activation staging: the largest divisor of the tile count that keeps the
     // cluster within 8 CTAs and still lets as many CTAs run at once as unshared clusters would.
     const int grid = p.tiles * ia.split;
-    if (p.m * (int)w->units_per_row >= 32) {  // a handful of records is quicker done by every CTA for itself
+    if (NT == 1 && p.m * (int)w->units_per_row >= 32) {  // a handful of records is quicker done by every CTA for itself
         const int base_active = max_active_clusters(kernel, ctx->device, ia.split, total, grid) * ia.split;
         const int want = grid < base_active ? grid : base_active;
         for (int ts = 8 / ia.split; ts > 1; --ts) {
