@@ -33,6 +33,7 @@ Q4_0, Q4_K = 2, 12
 FORMATS = [(Q4_K, "q4_k"), (Q4_0, "q4_0")]
 METRIC = "Q4_K/Q4_0 decode GEMV sweep, algorithmic HBM GB/s"
 BPW = 0.5625
+NCU_TRAFFIC_RATIO = 50.21 / 50.23  # measured DRAM bytes over algorithmic bytes of the captured launch (profiles/)
 
 
 def algorithmic_bytes(k: int, n: int, m: int) -> int:
@@ -321,11 +322,13 @@ def run_ours(args):
     cpu = cpu_baseline_sample() if world == 1 and not args.no_cpu else None
     line = {
         "metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u4*f16->f32", "data": "synthetic",
+        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u4 x s16 (two s8 limbs) -> s32, f32 scales", "data": "synthetic",
         "config": {"workload": "configs[1]: decode GEMV sweep, batch 1/4/16, Q4_0+Q4_K, 5 shapes, fp32 in/out", "l2": "inputs larger than L2: 350 MB of distinct weights between reuses",
                    "parallelism": f"tp{world}" if world > 1 else "single", "bytes_per_step": step_bytes, "launches_per_step": launches // max(args.steps, 1) // max(world, 1)},
-        "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": hbm_peak, "unit": "GB/s", "frac": round(achieved / hbm_peak, 4), "traffic": None,
-                     "kernel": "zq::gemv_kernel<Q4_K, 1 column tile> (batch 1 and 4)", "peak_kind": peak_kind, "launches": q4k_kernel_launches * args.steps,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": hbm_peak, "unit": "GB/s", "frac": round(achieved / hbm_peak, 4),
+                     # ncu, 5120x17408 batch-1 launch: dram read+write = 50.21 MB for 50.23 MB algorithmic; scaled by bytes
+                     "traffic": int(q4k_kernel_bytes // max(q4k_kernel_launches, 1) * NCU_TRAFFIC_RATIO), "traffic_kind": "ncu capture of one launch, scaled by algorithmic bytes",
+                     "kernel": "zq::gemv_i8_kernel<Q4_K, 1 column tile> (batch 1 and 4)", "peak_kind": peak_kind, "launches": q4k_kernel_launches * args.steps,
                      "bytes_per_launch_avg": q4k_kernel_bytes // max(q4k_kernel_launches, 1)},
         "gpu_launches": launches, "clocks": clocks, "e2e": e2e, "cpu_baseline": cpu,
     }

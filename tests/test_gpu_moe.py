@@ -48,10 +48,19 @@ def test_router_breaks_ties_by_lower_expert_id():
     assert list(ids.cpu().numpy()[0]) == [1, 3]
 
 
-@pytest.mark.parametrize("tensor_type", [H.Q4_K, H.Q8_0])
+@pytest.fixture(params=["grouped", "per_expert"])
+def moe_path(request):
+    """Both orchestrations: everything on the device in grouped launches (decode-sized batches), or host-grouped
+    routes with one pair of calls per expert (what larger batches use)."""
+    ctx().set_option("force_moe_per_expert", 1 if request.param == "per_expert" else 0)
+    yield request.param
+    ctx().set_option("force_moe_per_expert", 0)
+
+
+@pytest.mark.parametrize("tensor_type", [H.Q4_K, H.Q8_0, H.Q4_0])
 @pytest.mark.parametrize("m", [1, 6, 48])
 @pytest.mark.parametrize("with_shared", [False, True])
-def test_moe_forward_matches_cpu_path(tensor_type, m, with_shared):
+def test_moe_forward_matches_cpu_path(tensor_type, m, with_shared, moe_path):
     """Routed + shared experts + residual against the oracle's moe_forward (decode and prefill orchestration:
     experts with few routed tokens run the decode kernel, experts with more than 16 the tensor-core GEMM)."""
     from zllm_b200.backend import MoeExperts, moe_forward, moe_route
@@ -91,5 +100,17 @@ def test_moe_forward_rejects_bad_expert_ids():
     c = ctx()
     table = MoeExperts(c, [c.prepare_weight(H.Q4_K, g, inter, hidden) for g in gates], [c.prepare_weight(H.Q4_K, u, inter, hidden) for u in ups], [c.prepare_weight(H.Q4_K, d, hidden, inter) for d in downs])
     x = dev(np.zeros((1, hidden), dtype=np.float32))
+    bad_ids, w = torch.tensor([[0, 5]], dtype=torch.int32, device="cuda"), torch.tensor([[0.5, 0.5]], device="cuda")
+    # host-grouped path: the ids are read on the host, the call itself fails
+    c.set_option("force_moe_per_expert", 1)
+    try:
+        with pytest.raises(ffi.ZqFailure):
+            moe_forward(c, table, x, bad_ids, w)
+    finally:
+        c.set_option("force_moe_per_expert", 0)
+    # device-grouped path: nothing comes back to the host; the kernel skips the bad index (no out-of-range access),
+    # records it in the status word, and the next sync reports it
+    moe_forward(c, table, x, bad_ids, w)
     with pytest.raises(ffi.ZqFailure):
-        moe_forward(c, table, x, torch.tensor([[0, 5]], dtype=torch.int32, device="cuda"), torch.tensor([[0.5, 0.5]], device="cuda"))
+        c.sync()
+    c.sync()  # reported once, then clear

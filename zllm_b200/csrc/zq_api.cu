@@ -70,7 +70,6 @@ int ensure_scratch_mid(zq_ctx *ctx, size_t bytes, zq_error *err) {
     if (bytes <= ctx->mid_bytes) return ZQ_OK;
     ZQ_CUDA_CHECK(cudaStreamSynchronize(ctx->stream), err);
     if (ctx->mid) cudaFree(ctx->mid);
-    if (ctx->xq) cudaFree(ctx->xq);
     ctx->mid = nullptr;
     ctx->mid_bytes = 0;
     size_t rounded = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
@@ -155,6 +154,7 @@ void zq_ctx_destroy(zq_ctx *ctx) {
     if (ctx->gemv_counters) cudaFree(ctx->gemv_counters);
     if (ctx->workspace) cudaFree(ctx->workspace);
     if (ctx->mid) cudaFree(ctx->mid);
+    if (ctx->xq) cudaFree(ctx->xq);
     if (ctx->moe_ws) cudaFree(ctx->moe_ws);
     if (ctx->status_host) cudaFreeHost(ctx->status_host);
     if (ctx->pinned) cudaFreeHost(ctx->pinned);
@@ -194,6 +194,10 @@ int zq_ctx_set_option(zq_ctx *ctx, const char *key, int value, zq_error *err) {
     if (!ctx || !key) return set_error(err, ZQ_ERR_ARG, "zq_ctx_set_option: null argument");
     if (!strcmp(key, "force_staged_gemv")) {
         ctx->force_staged_gemv = value;
+        return ZQ_OK;
+    }
+    if (!strcmp(key, "force_moe_per_expert")) {
+        ctx->force_moe_per_expert = value;
         return ZQ_OK;
     }
     if (!strcmp(key, "disable_pdl")) {

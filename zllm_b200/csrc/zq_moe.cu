@@ -9,21 +9,17 @@
 //     ascending expert order
 //   shared expert added to the sum     src/moe/topk_moe.rs:84-104
 //
-// This version keeps the reference CUDA backend's orchestration (router ids come back to the host,
+// Two orchestrations.  Decode-sized batches (a few rows per expert) stay on the device: grouping, both projections of
+// all routed experts and the combine are seven launches with no host round trip (zq_moe_grouped.cu).  Larger
+// batches keep the reference CUDA backend's orchestration (router ids come back to the host,
 // src/kernel/cuda/routing.rs:208; the host groups routes and issues the expert kernels,
-// src/backend/cuda/expert.rs:787-917): routing and combine run on the device, the per-expert projections are
-// calls into the decode GEMV / prefill GEMM of this library over gathered token rows.
+// src/backend/cuda/expert.rs:787-917): the per-expert projections are calls into the prefill GEMM of this library
+// over gathered token rows.
 #include <algorithm>
 
-#include "zq_common.cuh"
+#include "zq_moe.cuh"
 
 using namespace zq;
-
-struct zq_moe_experts {
-    zq_ctx *ctx = nullptr;
-    size_t num_experts = 0, hidden = 0, inter = 0;
-    std::vector<const zq_weight *> gate, up, down;
-};
 
 namespace zq {
 
@@ -195,21 +191,73 @@ int zq_moe_experts_create(zq_ctx *ctx, const zq_weight *const *gate, const zq_we
         t->up.push_back(u);
         t->down.push_back(d);
     }
+    // grouped decode path: needs one gate/up type and one down type across the table
+    bool uniform = true;
+    t->gate_type = gate[0]->type;
+    t->down_type = down[0]->type;
+    for (size_t e = 0; e < num_experts; ++e) uniform = uniform && gate[e]->type == t->gate_type && down[e]->type == t->down_type;
+    if (uniform) {
+        std::vector<CUtensorMap> hg(num_experts), hu(num_experts), hd(num_experts);
+        for (size_t e = 0; e < num_experts; ++e) {
+            hg[e] = gate[e]->gemv_map_half;
+            hu[e] = up[e]->gemv_map_half;
+            hd[e] = down[e]->gemv_map;
+        }
+        const size_t bytes = num_experts * sizeof(CUtensorMap);
+        cudaError_t ce = cudaMalloc(&t->d_gate_maps, bytes);
+        if (ce == cudaSuccess) ce = cudaMalloc(&t->d_up_maps, bytes);
+        if (ce == cudaSuccess) ce = cudaMalloc(&t->d_down_maps, bytes);
+        if (ce == cudaSuccess) ce = cudaMemcpy(t->d_gate_maps, hg.data(), bytes, cudaMemcpyHostToDevice);
+        if (ce == cudaSuccess) ce = cudaMemcpy(t->d_up_maps, hu.data(), bytes, cudaMemcpyHostToDevice);
+        if (ce == cudaSuccess) ce = cudaMemcpy(t->d_down_maps, hd.data(), bytes, cudaMemcpyHostToDevice);
+        if (ce != cudaSuccess) {
+            zq_moe_experts_destroy(t);
+            return set_error(err, ZQ_ERR_CUDA, "zq_moe_experts_create: tensor-map table: %s", cudaGetErrorString(ce));
+        }
+    }
     *out = t;
     return ZQ_OK;
 }
 
-void zq_moe_experts_destroy(zq_moe_experts *experts) { delete experts; }
+void zq_moe_experts_destroy(zq_moe_experts *experts) {
+    if (!experts) return;
+    if (experts->d_gate_maps) cudaFree(experts->d_gate_maps);
+    if (experts->d_up_maps) cudaFree(experts->d_up_maps);
+    if (experts->d_down_maps) cudaFree(experts->d_down_maps);
+    delete experts;
+}
 
 int zq_moe_forward(zq_ctx *ctx, const zq_moe_experts *experts, const zq_weight *shared_gate, const zq_weight *shared_up, const zq_weight *shared_down, const void *dev_x, int x_dtype, size_t m, const uint32_t *dev_ids,
                    const float *dev_weights, size_t top_k, void *dev_y, int y_dtype, const void *dev_residual, zq_error *err) {
     if (!ctx || !experts || !dev_x || !dev_ids || !dev_weights || !dev_y) return set_error(err, ZQ_ERR_ARG, "zq_moe_forward: null argument");
     if (experts->ctx != ctx) return set_error(err, ZQ_ERR_ARG, "zq_moe_forward: expert table belongs to another context");
     if (m == 0 || top_k == 0) return set_error(err, ZQ_ERR_SHAPE, "zq_moe_forward: empty routing (rows=%zu top_k=%zu)", m, top_k);
+    {
+        cudaError_t stale = cudaGetLastError();  // an error some earlier call of this thread left behind is not this call's
+        if (stale != cudaSuccess) return set_error(err, ZQ_ERR_CUDA, "zq_moe_forward: the CUDA runtime already held an error on entry: %s", cudaGetErrorString(stale));
+    }
     const bool has_shared = shared_gate || shared_up || shared_down;
     if (has_shared && !(shared_gate && shared_up && shared_down)) return set_error(err, ZQ_ERR_ARG, "zq_moe_forward: shared expert needs gate, up and down");
     const size_t E = experts->num_experts, H = experts->hidden, I = experts->inter, routes = m * top_k;
     if (has_shared && (shared_gate->cols != H || shared_down->rows != H || shared_down->cols != shared_gate->rows)) return set_error(err, ZQ_ERR_SHAPE, "zq_moe_forward: shared expert shapes do not match hidden=%zu", H);
+
+    // ---- decode-sized batch: everything stays on the device
+    if (!ctx->force_moe_per_expert && moe_grouped_supported(experts, m, top_k) && routes <= 16 * E) {
+        int rc = ensure_moe_ws(ctx, moe_grouped_ws_bytes(experts, m, top_k, has_shared), err);
+        if (rc) return rc;
+        float *d_out = nullptr, *d_token_w = nullptr, *d_shared = nullptr;
+        uint32_t *d_token_slots = nullptr;
+        rc = moe_grouped_forward(ctx, experts, dev_x, x_dtype, m, dev_ids, dev_weights, top_k, reinterpret_cast<uint8_t *>(ctx->moe_ws), &d_out, &d_token_slots, &d_token_w, &d_shared, has_shared, err);
+        if (rc) return rc;
+        if (has_shared) {
+            rc = zq_gated_mlp(ctx, shared_gate, shared_up, shared_down, dev_x, x_dtype, m, d_shared, ZQ_F32, nullptr, err);
+            if (rc) return rc;
+        }
+        combine_kernel<<<grid_for(ctx, m * H, 256), 256, 0, ctx->stream>>>(d_out, d_token_slots, d_token_w, (int)top_k, d_shared, dev_residual, dev_y, y_dtype, m, (int)H);
+        ctx->launches++;
+        ZQ_CUDA_CHECK(cudaGetLastError(), err);
+        return ZQ_OK;
+    }
 
     // ---- routing back to the host, token-major stable grouping (src/moe/routing.rs:136-156)
     std::vector<uint32_t> ids(routes);

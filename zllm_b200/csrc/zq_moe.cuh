@@ -1,0 +1,24 @@
+// Resident expert table of a MoE layer and the entry points of the grouped decode path (zq_moe_grouped.cu).
+#pragma once
+#include <vector>
+
+#include "zq_common.cuh"
+
+struct zq_moe_experts {
+    zq_ctx *ctx = nullptr;
+    size_t num_experts = 0, hidden = 0, inter = 0;
+    std::vector<const zq_weight *> gate, up, down;
+    // grouped decode path: the experts' tensor maps as device arrays (gate/up: 64-row boxes, down: 128-row boxes);
+    // null when the experts do not all share one gate/up type and one down type
+    CUtensorMap *d_gate_maps = nullptr, *d_up_maps = nullptr, *d_down_maps = nullptr;
+    uint32_t gate_type = 0, down_type = 0;
+};
+
+namespace zq {
+
+bool moe_grouped_supported(const zq_moe_experts *t, size_t m, size_t top_k);
+size_t moe_grouped_ws_bytes(const zq_moe_experts *t, size_t m, size_t top_k, bool has_shared);
+int moe_grouped_forward(zq_ctx *ctx, const zq_moe_experts *t, const void *dev_x, int x_dtype, size_t m, const uint32_t *dev_ids, const float *dev_weights, size_t top_k, uint8_t *ws, float **routed_out,
+                        uint32_t **token_slots_out, float **token_w_out, float **shared_buf, bool has_shared, zq_error *err);
+
+}  // namespace zq
