@@ -91,6 +91,29 @@ def test_moe_forward_matches_cpu_path(tensor_type, m, with_shared, moe_path):
     assert H.max_rel_error(got, want) <= BOUND
 
 
+def test_shared_expert_of_another_width_takes_its_own_launches():
+    """A shared expert shaped like the routed ones rides along in the grouped launches; any other shape runs as a
+    separate gated MLP (src/moe/topk_moe.rs:84-104) and is added in the combine."""
+    from zllm_b200.backend import MoeExperts, moe_forward, moe_route
+
+    n_exp, top_k, hidden, inter, shared_inter, m = 8, 2, 512, 256, 128, 5
+    gates, ups, downs = _experts(H.Q4_K, n_exp, hidden, inter, seed=500)
+    rng = np.random.default_rng(55)
+    x = rng.standard_normal((m, hidden)).astype(np.float32)
+    router = (rng.standard_normal((n_exp, hidden)) / np.sqrt(hidden)).astype(np.float32)
+    c = ctx()
+    table = MoeExperts(c, [c.prepare_weight(H.Q4_K, g, inter, hidden) for g in gates], [c.prepare_weight(H.Q4_K, u, inter, hidden) for u in ups], [c.prepare_weight(H.Q4_K, d, hidden, inter) for d in downs])
+    sg, su = H.random_weight(H.Q8_0, shared_inter, hidden, seed=910), H.random_weight(H.Q8_0, shared_inter, hidden, seed=911)
+    sd = H.random_weight(H.Q8_0, hidden, shared_inter, seed=912, std=0.05)
+    shared_dev = (c.prepare_weight(H.Q8_0, sg, shared_inter, hidden), c.prepare_weight(H.Q8_0, su, shared_inter, hidden), c.prepare_weight(H.Q8_0, sd, hidden, shared_inter))
+    xd = dev(x)
+    ids, w = moe_route(c, xd, dev(router), top_k, 1.0, True)
+    got = host(moe_forward(c, table, xd, ids, w, shared=shared_dev))
+    want = orc.moe_forward([(H.Q4_K, g, inter, hidden) for g in gates], [(H.Q4_K, u, inter, hidden) for u in ups], [(H.Q4_K, d, hidden, inter) for d in downs], x, ids.cpu().numpy().astype(np.uint32), w.cpu().numpy(),
+                           shared=[(H.Q8_0, sg, shared_inter, hidden), (H.Q8_0, su, shared_inter, hidden), (H.Q8_0, sd, hidden, shared_inter)], residual=None)
+    assert H.max_rel_error(got, want) <= BOUND
+
+
 def test_moe_forward_rejects_bad_expert_ids():
     from zllm_b200 import ffi
     from zllm_b200.backend import MoeExperts, moe_forward

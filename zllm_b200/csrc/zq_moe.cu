@@ -26,25 +26,68 @@ namespace zq {
 constexpr int kRouterTokens = 4;     // tokens per CTA
 constexpr int kRouterThreads = 256;
 
+// Softmax top-k of one token from its logits in shared memory (the logits are consumed): repeated arg-max with ties
+// to the lower expert id; one warp per token.
+__device__ __forceinline__ void router_select(float *l, int lane, int num_experts, int top_k, float scaling, int normalize_selected, uint32_t *ids_out, float *weights_out) {
+    float maximum = -INFINITY;
+    for (int e = lane; e < num_experts; e += 32) maximum = fmaxf(maximum, l[e]);
+    for (int o = 16; o > 0; o >>= 1) maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, o));
+    float denom_all = 0.f;
+    if (!normalize_selected) {
+        for (int e = lane; e < num_experts; e += 32) denom_all += expf(l[e] - maximum);
+        for (int o = 16; o > 0; o >>= 1) denom_all += __shfl_xor_sync(0xffffffffu, denom_all, o);
+    }
+    float sel_logit = 0.f, denom_sel = 0.f;  // lane j keeps the j-th selected logit (top_k <= 32)
+    uint32_t sel_id = 0;
+    for (int slot = 0; slot < top_k; ++slot) {
+        float best = -INFINITY;
+        int best_e = 0x7fffffff;
+        for (int e = lane; e < num_experts; e += 32) {
+            float v = l[e];
+            if (v > best || (v == best && e < best_e)) { best = v; best_e = e; }
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (ov > best || (ov == best && oe < best_e)) { best = ov; best_e = oe; }
+        }
+        if (lane == slot) { sel_logit = best; sel_id = (uint32_t)best_e; }
+        if (lane == 0) l[best_e] = -INFINITY;
+        __syncwarp();
+        denom_sel += expf(best - maximum);
+    }
+    const float denom = normalize_selected ? denom_sel : denom_all;
+    if (lane < top_k) {
+        ids_out[lane] = sel_id;
+        weights_out[lane] = expf(sel_logit - maximum) / denom * scaling;
+    }
+}
+
 // logits[t, e] = x[t] . router[e] (+ bias[e]) in f32, then softmax top-k per token.
-// One CTA per 4 tokens; each warp owns experts e = warp, warp + 8, ...; lanes stride the hidden dimension.
+// One CTA per 4 tokens and per block of `experts_per_cta` experts; each warp owns experts warp, warp + 8, ... of the
+// block; lanes stride the hidden dimension.  With one expert block per token block the CTA selects right away;
+// with several (few tokens: the expert blocks are what fills the machine) the logits go to `logits_g` and
+// router_select_kernel finishes.
 __global__ void __launch_bounds__(kRouterThreads) router_topk_kernel(const void *__restrict__ x, int x_dtype, int m, int hidden, const float *__restrict__ router, const float *__restrict__ bias, int num_experts, int top_k,
-                                                                      float scaling, int normalize_selected, uint32_t *__restrict__ ids, float *__restrict__ weights) {
+                                                                      float scaling, int normalize_selected, uint32_t *__restrict__ ids, float *__restrict__ weights, int experts_per_cta, float *__restrict__ logits_g) {
     extern __shared__ float rsm[];
     float *xs = rsm;                                 // [kRouterTokens][hidden]
     float *logits = rsm + (size_t)kRouterTokens * hidden;  // [kRouterTokens][num_experts]
     const int tok0 = blockIdx.x * kRouterTokens;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e_begin = blockIdx.y * experts_per_cta;
+    const int e_end = e_begin + experts_per_cta < num_experts ? e_begin + experts_per_cta : num_experts;
     for (int i = threadIdx.x; i < kRouterTokens * hidden; i += kRouterThreads) {
         int t = i / hidden, c = i - t * hidden;
         xs[i] = (tok0 + t < m) ? load_as_f32(x, x_dtype, (size_t)(tok0 + t) * hidden + c) : 0.f;
     }
     __syncthreads();
-    for (int e = warp; e < num_experts; e += kRouterThreads / 32) {
+    for (int e = e_begin + warp; e < e_end; e += kRouterThreads / 32) {
         const float *w = router + (size_t)e * hidden;
         float acc[kRouterTokens];
 #pragma unroll
         for (int t = 0; t < kRouterTokens; ++t) acc[t] = 0.f;
+#pragma unroll 8
         for (int c = lane; c < hidden; c += 32) {
             const float wv = w[c];
 #pragma unroll
@@ -54,47 +97,33 @@ __global__ void __launch_bounds__(kRouterThreads) router_topk_kernel(const void 
         for (int t = 0; t < kRouterTokens; ++t) {
             float v = acc[t];
             for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-            if (lane == 0) logits[t * num_experts + e] = v + (bias ? bias[e] : 0.f);
+            if (lane == 0) {
+                v += bias ? bias[e] : 0.f;
+                if (logits_g) {
+                    if (tok0 + t < m) logits_g[(size_t)(tok0 + t) * num_experts + e] = v;
+                } else {
+                    logits[t * num_experts + e] = v;
+                }
+            }
         }
     }
+    if (logits_g) return;
     __syncthreads();
-    // top-k: warp t handles token t; repeated arg-max with ties to the lower expert id
-    if (warp < kRouterTokens && tok0 + warp < m) {
-        float *l = logits + warp * num_experts;
-        float maximum = -INFINITY;
-        for (int e = lane; e < num_experts; e += 32) maximum = fmaxf(maximum, l[e]);
-        for (int o = 16; o > 0; o >>= 1) maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, o));
-        float denom_all = 0.f;
-        if (!normalize_selected) {
-            for (int e = lane; e < num_experts; e += 32) denom_all += expf(l[e] - maximum);
-            for (int o = 16; o > 0; o >>= 1) denom_all += __shfl_xor_sync(0xffffffffu, denom_all, o);
-        }
-        float sel_logit = 0.f, denom_sel = 0.f;  // lane j keeps the j-th selected logit (top_k <= 32)
-        uint32_t sel_id = 0;
-        for (int slot = 0; slot < top_k; ++slot) {
-            float best = -INFINITY;
-            int best_e = 0x7fffffff;
-            for (int e = lane; e < num_experts; e += 32) {
-                float v = l[e];
-                if (v > best || (v == best && e < best_e)) { best = v; best_e = e; }
-            }
-            for (int o = 16; o > 0; o >>= 1) {
-                float ov = __shfl_xor_sync(0xffffffffu, best, o);
-                int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-                if (ov > best || (ov == best && oe < best_e)) { best = ov; best_e = oe; }
-            }
-            if (lane == slot) { sel_logit = best; sel_id = (uint32_t)best_e; }
-            if (lane == 0) l[best_e] = -INFINITY;
-            __syncwarp();
-            denom_sel += expf(best - maximum);
-        }
-        const float denom = normalize_selected ? denom_sel : denom_all;
-        if (lane < top_k) {
-            const size_t o = (size_t)(tok0 + warp) * top_k + lane;
-            ids[o] = sel_id;
-            weights[o] = expf(sel_logit - maximum) / denom * scaling;
-        }
-    }
+    if (warp < kRouterTokens && tok0 + warp < m)
+        router_select(logits + warp * num_experts, lane, num_experts, top_k, scaling, normalize_selected, ids + (size_t)(tok0 + warp) * top_k, weights + (size_t)(tok0 + warp) * top_k);
+}
+
+// Second half of the split router: one warp per token, logits from global memory.
+__global__ void __launch_bounds__(kRouterThreads) router_select_kernel(const float *__restrict__ logits_g, int m, int num_experts, int top_k, float scaling, int normalize_selected, uint32_t *__restrict__ ids,
+                                                                        float *__restrict__ weights) {
+    extern __shared__ float rsm[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tok = blockIdx.x * (kRouterThreads / 32) + warp;
+    if (tok >= m) return;
+    float *l = rsm + warp * num_experts;
+    for (int e = lane; e < num_experts; e += 32) l[e] = logits_g[(size_t)tok * num_experts + e];
+    __syncwarp();
+    router_select(l, lane, num_experts, top_k, scaling, normalize_selected, ids + (size_t)tok * top_k, weights + (size_t)tok * top_k);
 }
 
 __global__ void gather_rows_kernel(const void *__restrict__ x, int dtype, const uint32_t *__restrict__ tokens, size_t n_rows, int hidden, void *__restrict__ out) {
@@ -161,8 +190,30 @@ int zq_moe_route_softmax_topk(zq_ctx *ctx, const void *dev_x, int x_dtype, size_
         ZQ_CUDA_CHECK(cudaFuncSetAttribute(router_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), err);
         configured[ctx->device & 63] = true;
     }
-    unsigned grid = (unsigned)((m + kRouterTokens - 1) / kRouterTokens);
-    router_topk_kernel<<<grid, kRouterThreads, smem, ctx->stream>>>(dev_x, x_dtype, (int)m, (int)hidden, dev_router_f32, dev_bias_f32, (int)num_experts, (int)top_k, scaling_factor, normalize_selected, dev_ids, dev_weights);
+    const unsigned grid = (unsigned)((m + kRouterTokens - 1) / kRouterTokens);
+    // few tokens: split the experts over CTAs too, so that the router matrix is read by the whole machine
+    size_t blocks_y = 1, per_cta = num_experts;
+    if (grid < (unsigned)ctx->sm_count) {
+        blocks_y = (2 * (size_t)ctx->sm_count + grid - 1) / grid;
+        per_cta = ((num_experts + blocks_y - 1) / blocks_y + 7) & ~size_t(7);  // whole rounds of the 8 warps
+        blocks_y = (num_experts + per_cta - 1) / per_cta;
+    }
+    if (blocks_y > 1) {
+        int rc = ensure_moe_ws(ctx, m * num_experts * sizeof(float), err);  // the logits; consumed before anything else uses the buffer
+        if (rc) return rc;
+        float *logits_g = reinterpret_cast<float *>(ctx->moe_ws);
+        router_topk_kernel<<<dim3(grid, (unsigned)blocks_y), kRouterThreads, smem, ctx->stream>>>(dev_x, x_dtype, (int)m, (int)hidden, dev_router_f32, dev_bias_f32, (int)num_experts, (int)top_k, scaling_factor, normalize_selected,
+                                                                                                   dev_ids, dev_weights, (int)per_cta, logits_g);
+        ctx->launches++;
+        ZQ_CUDA_CHECK(cudaGetLastError(), err);
+        const unsigned sel_grid = (unsigned)((m + kRouterThreads / 32 - 1) / (kRouterThreads / 32));
+        router_select_kernel<<<sel_grid, kRouterThreads, (kRouterThreads / 32) * num_experts * sizeof(float), ctx->stream>>>(logits_g, (int)m, (int)num_experts, (int)top_k, scaling_factor, normalize_selected, dev_ids, dev_weights);
+        ctx->launches++;
+        ZQ_CUDA_CHECK(cudaGetLastError(), err);
+        return ZQ_OK;
+    }
+    router_topk_kernel<<<grid, kRouterThreads, smem, ctx->stream>>>(dev_x, x_dtype, (int)m, (int)hidden, dev_router_f32, dev_bias_f32, (int)num_experts, (int)top_k, scaling_factor, normalize_selected, dev_ids, dev_weights,
+                                                                    (int)num_experts, nullptr);
     ctx->launches++;
     ZQ_CUDA_CHECK(cudaGetLastError(), err);
     return ZQ_OK;
@@ -247,9 +298,12 @@ int zq_moe_forward(zq_ctx *ctx, const zq_moe_experts *experts, const zq_weight *
         if (rc) return rc;
         float *d_out = nullptr, *d_token_w = nullptr, *d_shared = nullptr;
         uint32_t *d_token_slots = nullptr;
-        rc = moe_grouped_forward(ctx, experts, dev_x, x_dtype, m, dev_ids, dev_weights, top_k, reinterpret_cast<uint8_t *>(ctx->moe_ws), &d_out, &d_token_slots, &d_token_w, &d_shared, has_shared, err);
+        // a shared expert shaped like the routed ones is one more entry of the work list (one row per token)
+        const bool rides = has_shared && moe_shared_rides_along(experts, shared_gate, shared_up, shared_down);
+        rc = moe_grouped_forward(ctx, experts, rides ? shared_gate : nullptr, rides ? shared_up : nullptr, rides ? shared_down : nullptr, dev_x, x_dtype, m, dev_ids, dev_weights, top_k,
+                                 reinterpret_cast<uint8_t *>(ctx->moe_ws), &d_out, &d_token_slots, &d_token_w, &d_shared, has_shared, err);
         if (rc) return rc;
-        if (has_shared) {
+        if (has_shared && !rides) {
             rc = zq_gated_mlp(ctx, shared_gate, shared_up, shared_down, dev_x, x_dtype, m, d_shared, ZQ_F32, nullptr, err);
             if (rc) return rc;
         }

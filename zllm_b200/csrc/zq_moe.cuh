@@ -18,7 +18,8 @@ namespace zq {
 
 bool moe_grouped_supported(const zq_moe_experts *t, size_t m, size_t top_k);
 size_t moe_grouped_ws_bytes(const zq_moe_experts *t, size_t m, size_t top_k, bool has_shared);
-int moe_grouped_forward(zq_ctx *ctx, const zq_moe_experts *t, const void *dev_x, int x_dtype, size_t m, const uint32_t *dev_ids, const float *dev_weights, size_t top_k, uint8_t *ws, float **routed_out,
-                        uint32_t **token_slots_out, float **token_w_out, float **shared_buf, bool has_shared, zq_error *err);
+bool moe_shared_rides_along(const zq_moe_experts *t, const zq_weight *sg, const zq_weight *su, const zq_weight *sd);
+int moe_grouped_forward(zq_ctx *ctx, const zq_moe_experts *t, const zq_weight *shared_gate, const zq_weight *shared_up, const zq_weight *shared_down, const void *dev_x, int x_dtype, size_t m, const uint32_t *dev_ids,
+                        const float *dev_weights, size_t top_k, uint8_t *ws, float **routed_out, uint32_t **token_slots_out, float **token_w_out, float **shared_buf, bool has_shared, zq_error *err);
 
 }  // namespace zq

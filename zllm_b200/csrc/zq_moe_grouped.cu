@@ -11,6 +11,8 @@
 //                          stage carries the weights of one (tile, 2 units) and the records of those units
 // Arithmetic per expert is that of zq_gemv_i8.cu (16-bit integer activations, exact integer weights), the combine
 // is the one of zq_moe.cu; an expert that received more than 8 rows is walked in passes of 8.
+#include <cstring>
+
 #include "zq_i8.cuh"
 #include "zq_moe.cuh"
 
@@ -28,11 +30,12 @@ __host__ __device__ constexpr int grouped_stages(uint32_t type) { return type ==
 //   offsets[e]        first slot of expert e (slots of an expert are in token order)
 //   slot_token[s]     token whose row sits in slot s;  slot_expert[s] its expert
 //   token_slots/w     per token, its top_k slots and weights in ascending expert order
-//   passes[p]         {expert, m0 | rows << 16, first slot of the expert, rows of the expert}
+//   passes[p]         {expert, m0 | rows << 16, first slot of the expert, rows of the expert}; a shared expert that
+//                     rides along is expert E with one row per token in slots routes .. routes + m - 1
 // ---------------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kPlanThreads) moe_plan_kernel(const uint32_t *__restrict__ ids, const float *__restrict__ wts, int m, int top_k, int E, uint32_t *__restrict__ offsets, uint32_t *__restrict__ slot_token,
                                                                  uint32_t *__restrict__ slot_expert, uint32_t *__restrict__ token_slots, float *__restrict__ token_w, uint4 *__restrict__ passes, uint32_t *__restrict__ n_pass,
-                                                                 uint32_t *status) {
+                                                                 int shared_rows, uint32_t *status) {
     extern __shared__ uint32_t plan_smem[];
     const int routes = m * top_k;
     uint32_t *s_cnt = plan_smem;            // [E]
@@ -53,21 +56,51 @@ __global__ void __launch_bounds__(kPlanThreads) moe_plan_kernel(const uint32_t *
         atomicAdd(&s_cnt[id], 1u);
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-        uint32_t acc = 0, np = 0;
-        for (int e = 0; e < E; ++e) {
-            const uint32_t c = s_cnt[e];
-            s_off[e] = acc;
-            offsets[e] = acc;
-            for (uint32_t m0 = 0; m0 < c; m0 += kPassRows) {
-                const uint32_t mc = c - m0 < (uint32_t)kPassRows ? c - m0 : (uint32_t)kPassRows;
-                passes[np++] = make_uint4((uint32_t)e, m0 | (mc << 16), acc, c);
+    {
+        // exclusive prefix sums over the experts (E <= 1024 = one thread each): slot offsets and pass offsets
+        __shared__ uint32_t warp_tot[2][32];
+        const int e = threadIdx.x, lane = e & 31, wid = e >> 5;
+        const uint32_t c = e < E ? s_cnt[e] : 0u;
+        const uint32_t np_e = (c + kPassRows - 1) / kPassRows;
+        uint32_t sc = c, sp = np_e;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const uint32_t a = __shfl_up_sync(0xffffffffu, sc, d), b = __shfl_up_sync(0xffffffffu, sp, d);
+            if (lane >= d) {
+                sc += a;
+                sp += b;
             }
-            acc += c;
         }
-        s_off[E] = acc;
-        offsets[E] = acc;
-        *n_pass = np;
+        if (lane == 31) {
+            warp_tot[0][wid] = sc;
+            warp_tot[1][wid] = sp;
+        }
+        __syncthreads();
+        uint32_t base_c = 0, base_p = 0;
+        for (int w = 0; w < wid; ++w) {
+            base_c += warp_tot[0][w];
+            base_p += warp_tot[1][w];
+        }
+        const uint32_t first = base_c + sc - c, pfirst = base_p + sp - np_e;
+        if (e < E) {
+            s_off[e] = first;
+            offsets[e] = first;
+            for (uint32_t j = 0; j < np_e; ++j) {
+                const uint32_t m0 = j * kPassRows, mc = c - m0 < (uint32_t)kPassRows ? c - m0 : (uint32_t)kPassRows;
+                passes[pfirst + j] = make_uint4((uint32_t)e, m0 | (mc << 16), first, c);
+            }
+        }
+        if (e == kPlanThreads - 1) {  // the last thread holds the totals
+            s_off[E] = base_c + sc;
+            offsets[E] = base_c + sc;
+            // the shared expert, when it rides along: id E, every token one row, slots right behind the routed ones
+            uint32_t np = base_p + sp;
+            for (uint32_t m0 = 0; m0 < (uint32_t)shared_rows; m0 += kPassRows) {
+                const uint32_t mc = (uint32_t)shared_rows - m0 < (uint32_t)kPassRows ? (uint32_t)shared_rows - m0 : (uint32_t)kPassRows;
+                passes[np++] = make_uint4((uint32_t)E, m0 | (mc << 16), base_c + sc, (uint32_t)shared_rows);
+            }
+            *n_pass = np;
+        }
     }
     __syncthreads();
     // token-major stable slots: the thread of expert e walks the routes in order
@@ -106,20 +139,30 @@ __global__ void __launch_bounds__(kPlanThreads) moe_plan_kernel(const uint32_t *
 
 // Records of every routed row: one warp per (slot, unit).  Record index of (expert e, unit u, local row j) is
 // offsets[e] * units + u * count_e + j, so the rows of one pass of one unit are contiguous.
-// row_of_slot: source row per slot (token of the slot), or null when the source is already in slot order.
+// row_of_slot: source row per routed slot (token of the slot), or null when the source is already in slot order.
 template <uint32_t TYPE>
 __global__ void __launch_bounds__(256) moe_quantize_kernel(const void *__restrict__ src, int src_dtype, const uint32_t *__restrict__ row_of_slot, const uint32_t *__restrict__ slot_expert,
-                                                           const uint32_t *__restrict__ offsets, int routes, int cols, int units, uint8_t *__restrict__ out) {
+                                                           const uint32_t *__restrict__ offsets, int routes, int shared_rows, int shared_id, int cols, int units, uint8_t *__restrict__ out) {
     pdl_launch_dependents();
     pdl_wait_prior_grid();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int task = blockIdx.x * 8 + warp;
-    if (task >= routes * units) return;  // warp-uniform
+    if (task >= (routes + shared_rows) * units) return;  // warp-uniform
     const int slot = task / units, unit = task - slot * units;
-    const uint32_t e = slot_expert[slot];
-    const uint32_t first = offsets[e], cnt = offsets[e + 1] - first;
+    uint32_t first, cnt;
+    size_t row;
+    if (slot < routes) {
+        const uint32_t e = slot_expert[slot];
+        first = offsets[e];
+        cnt = offsets[e + 1] - first;
+        row = row_of_slot ? row_of_slot[slot] : (uint32_t)slot;
+    } else {  // shared expert: slot routes + t holds token t
+        (void)shared_id;
+        first = (uint32_t)routes;
+        cnt = (uint32_t)shared_rows;
+        row = row_of_slot ? (size_t)(slot - routes) : (size_t)slot;
+    }
     const size_t rec = (size_t)first * units + (size_t)unit * cnt + ((uint32_t)slot - first);
-    const size_t row = row_of_slot ? row_of_slot[slot] : (uint32_t)slot;
     const int k0 = unit * kUnitWeights + 8 * lane;
     float v[8];
     load_act8(src, src_dtype, row * cols + k0, k0 < cols, v);
@@ -141,10 +184,12 @@ struct GroupedArgs {
     int units, chunks, chunk_words;
     int tiles;                  // row tiles per expert
     int n_out;                  // output features per expert (rows of gate, or of down)
+    int shared_id;              // expert id that means "the shared expert" (its maps are below), or -1
+    CUtensorMap shared_a, shared_b;
 };
 
 template <uint32_t TYPE, bool GATED>
-__global__ void __launch_bounds__(kI8Threads, 1) moe_grouped_kernel(const GroupedArgs ga) {
+__global__ void __launch_bounds__(kI8Threads, 1) moe_grouped_kernel(const __grid_constant__ GroupedArgs ga) {
     constexpr int UB = Fmt<TYPE>::unit_bytes;
     constexpr int PITCH = kChunkUnits * UB;
     constexpr int STAGE_W = kTileRows * PITCH;
@@ -193,11 +238,14 @@ __global__ void __launch_bounds__(kI8Threads, 1) moe_grouped_kernel(const Groupe
         if (nu > kChunkUnits) nu = kChunkUnits;
         uint8_t *dst = ws + (size_t)stage * STRIDE;
         mbar_expect_tx(&full[stage], (uint32_t)(STAGE_W + nu * mc * kRec));
+        const bool sh = (int)e == ga.shared_id;
+        const CUtensorMap *ma = sh ? &ga.shared_a : &ga.maps_a[e];
         if (GATED) {
-            tma_load_2d(dst, &ga.maps_a[e], &full[stage], chunk * ga.chunk_words, tile * out_rows);
-            tma_load_2d(dst + STAGE_W / 2, &ga.maps_b[e], &full[stage], chunk * ga.chunk_words, tile * out_rows);
+            const CUtensorMap *mb = sh ? &ga.shared_b : &ga.maps_b[e];
+            tma_load_2d(dst, ma, &full[stage], chunk * ga.chunk_words, tile * out_rows);
+            tma_load_2d(dst + STAGE_W / 2, mb, &full[stage], chunk * ga.chunk_words, tile * out_rows);
         } else {
-            tma_load_2d(dst, &ga.maps_a[e], &full[stage], chunk * ga.chunk_words, tile * out_rows);
+            tma_load_2d(dst, ma, &full[stage], chunk * ga.chunk_words, tile * out_rows);
         }
         for (int u = 0; u < nu; ++u) {
             const size_t rec = (size_t)first * ga.units + (size_t)(chunk * kChunkUnits + u) * cnt + m0;
@@ -305,9 +353,10 @@ __global__ void __launch_bounds__(kI8Threads, 1) moe_grouped_kernel(const Groupe
 }
 
 template <uint32_t TYPE>
-static int launch_quantize(zq_ctx *ctx, const void *src, int src_dtype, const uint32_t *row_of_slot, const uint32_t *slot_expert, const uint32_t *offsets, size_t routes, size_t cols, size_t units, uint8_t *out, zq_error *err) {
+static int launch_quantize(zq_ctx *ctx, const void *src, int src_dtype, const uint32_t *row_of_slot, const uint32_t *slot_expert, const uint32_t *offsets, size_t routes, size_t shared_rows, int shared_id, size_t cols, size_t units,
+                           uint8_t *out, zq_error *err) {
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)((routes * units + 7) / 8));
+    cfg.gridDim = dim3((unsigned)(((routes + shared_rows) * units + 7) / 8));
     cfg.blockDim = dim3(256);
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[1];
@@ -315,7 +364,7 @@ static int launch_quantize(zq_ctx *ctx, const void *src, int src_dtype, const ui
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = ctx->disable_pdl ? 0 : 1;
-    ZQ_CUDA_CHECK(cudaLaunchKernelEx(&cfg, moe_quantize_kernel<TYPE>, src, src_dtype, row_of_slot, slot_expert, offsets, (int)routes, (int)cols, (int)units, out), err);
+    ZQ_CUDA_CHECK(cudaLaunchKernelEx(&cfg, moe_quantize_kernel<TYPE>, src, src_dtype, row_of_slot, slot_expert, offsets, (int)routes, (int)shared_rows, shared_id, (int)cols, (int)units, out), err);
     ZQ_CUDA_CHECK(cudaGetLastError(), err);
     ctx->launches++;
     return ZQ_OK;
@@ -360,16 +409,28 @@ bool moe_grouped_supported(const zq_moe_experts *t, size_t m, size_t top_k) {
 size_t moe_grouped_ws_bytes(const zq_moe_experts *t, size_t m, size_t top_k, bool has_shared) {
     auto al = [](size_t v) { return (v + 255) & ~size_t(255); };
     const size_t routes = m * top_k, E = t->num_experts, H = t->hidden, I = t->inter;
+    const size_t rows = routes + (has_shared ? m : 0);  // a shared expert may ride along as m more rows, or use its own buffer
     const size_t units_h = (H + kUnitWeights - 1) / kUnitWeights, units_i = (I + kUnitWeights - 1) / kUnitWeights;
-    return al((E + 1) * 4) + 4 * al(routes * 4) + al((E + routes) * 16) + al(256) + al(routes * units_h * kRec) + al(routes * I * 4) + al(routes * units_i * kRec) + al(routes * H * 4) + (has_shared ? al(m * H * 4) : 0);
+    return al((E + 1) * 4) + 4 * al(routes * 4) + al((E + rows) * 16) + al(256) + al(rows * units_h * kRec) + al(rows * I * 4) + al(rows * units_i * kRec) + al(rows * H * 4) + (has_shared ? al(m * H * 4) : 0);
+}
+
+// The shared expert can ride along in the grouped launches when it looks like one more routed expert.
+bool moe_shared_rides_along(const zq_moe_experts *t, const zq_weight *sg, const zq_weight *su, const zq_weight *sd) {
+    return sg && su && sd && sg->type == t->gate_type && su->type == t->gate_type && sd->type == t->down_type && sg->rows == t->inter && su->rows == t->inter && sg->cols == t->hidden && su->cols == t->hidden &&
+           sd->rows == t->hidden && sd->cols == t->inter;
 }
 
 // Routed experts of a layer for a decode-sized batch; `ws` holds moe_grouped_ws_bytes().  Leaves the per-slot expert
 // outputs [routes, H] and the per-token combine tables in the workspace and reports where.
-int moe_grouped_forward(zq_ctx *ctx, const zq_moe_experts *t, const void *dev_x, int x_dtype, size_t m, const uint32_t *dev_ids, const float *dev_weights, size_t top_k, uint8_t *ws, float **routed_out,
-                        uint32_t **token_slots_out, float **token_w_out, float **shared_buf, bool has_shared, zq_error *err) {
+// `shared_*`: a shared expert that rides along (moe_shared_rides_along), or null; its output rows then follow the routed
+// ones and *shared_buf points at them, otherwise *shared_buf is a separate [m, H] buffer for the caller to fill.
+int moe_grouped_forward(zq_ctx *ctx, const zq_moe_experts *t, const zq_weight *shared_gate, const zq_weight *shared_up, const zq_weight *shared_down, const void *dev_x, int x_dtype, size_t m, const uint32_t *dev_ids,
+                        const float *dev_weights, size_t top_k, uint8_t *ws, float **routed_out, uint32_t **token_slots_out, float **token_w_out, float **shared_buf, bool has_shared, zq_error *err) {
     auto al = [](size_t v) { return (v + 255) & ~size_t(255); };
     const size_t routes = m * top_k, E = t->num_experts, H = t->hidden, I = t->inter;
+    const bool rides = shared_gate != nullptr;
+    const size_t srows = rides ? m : 0, rows = routes + (has_shared ? m : 0);
+    const int shared_id = rides ? (int)E : -1;
     const size_t units_h = (H + kUnitWeights - 1) / kUnitWeights, units_i = (I + kUnitWeights - 1) / kUnitWeights;
     size_t o = 0;
     uint32_t *d_offsets = reinterpret_cast<uint32_t *>(ws + o); o += al((E + 1) * 4);
@@ -377,13 +438,13 @@ int moe_grouped_forward(zq_ctx *ctx, const zq_moe_experts *t, const void *dev_x,
     uint32_t *d_slot_expert = reinterpret_cast<uint32_t *>(ws + o); o += al(routes * 4);
     uint32_t *d_token_slots = reinterpret_cast<uint32_t *>(ws + o); o += al(routes * 4);
     float *d_token_w = reinterpret_cast<float *>(ws + o); o += al(routes * 4);
-    uint4 *d_passes = reinterpret_cast<uint4 *>(ws + o); o += al((E + routes) * 16);
+    uint4 *d_passes = reinterpret_cast<uint4 *>(ws + o); o += al((E + rows) * 16);
     uint32_t *d_npass = reinterpret_cast<uint32_t *>(ws + o); o += al(256);
-    uint8_t *d_xq1 = ws + o; o += al(routes * units_h * kRec);
-    float *d_act = reinterpret_cast<float *>(ws + o); o += al(routes * I * 4);
-    uint8_t *d_xq2 = ws + o; o += al(routes * units_i * kRec);
-    float *d_out = reinterpret_cast<float *>(ws + o); o += al(routes * H * 4);
-    *shared_buf = has_shared ? reinterpret_cast<float *>(ws + o) : nullptr;
+    uint8_t *d_xq1 = ws + o; o += al(rows * units_h * kRec);
+    float *d_act = reinterpret_cast<float *>(ws + o); o += al(rows * I * 4);
+    uint8_t *d_xq2 = ws + o; o += al(rows * units_i * kRec);
+    float *d_out = reinterpret_cast<float *>(ws + o); o += al(rows * H * 4);
+    *shared_buf = rides ? d_out + routes * H : (has_shared ? reinterpret_cast<float *>(ws + o) : nullptr);
     *routed_out = d_out;
     *token_slots_out = d_token_slots;
     *token_w_out = d_token_w;
@@ -395,16 +456,16 @@ int moe_grouped_forward(zq_ctx *ctx, const zq_moe_experts *t, const void *dev_x,
             configured[ctx->device & 63] = true;
         }
         const size_t smem = (E * 2 + 1 + routes * 2) * 4;
-        moe_plan_kernel<<<1, kPlanThreads, smem, ctx->stream>>>(dev_ids, dev_weights, (int)m, (int)top_k, (int)E, d_offsets, d_slot_token, d_slot_expert, d_token_slots, d_token_w, d_passes, d_npass, ctx->status_dev);
+        moe_plan_kernel<<<1, kPlanThreads, smem, ctx->stream>>>(dev_ids, dev_weights, (int)m, (int)top_k, (int)E, d_offsets, d_slot_token, d_slot_expert, d_token_slots, d_token_w, d_passes, d_npass, (int)srows, ctx->status_dev);
         ctx->launches++;
         ZQ_CUDA_CHECK(cudaGetLastError(), err);
     }
     int rc;
     // ---- gate/up + SiLU
     switch (t->gate_type) {
-    case ZQ_Q4_K: rc = launch_quantize<ZQ_Q4_K>(ctx, dev_x, x_dtype, d_slot_token, d_slot_expert, d_offsets, routes, H, units_h, d_xq1, err); break;
-    case ZQ_Q4_0: rc = launch_quantize<ZQ_Q4_0>(ctx, dev_x, x_dtype, d_slot_token, d_slot_expert, d_offsets, routes, H, units_h, d_xq1, err); break;
-    default: rc = launch_quantize<ZQ_Q8_0>(ctx, dev_x, x_dtype, d_slot_token, d_slot_expert, d_offsets, routes, H, units_h, d_xq1, err); break;
+    case ZQ_Q4_K: rc = launch_quantize<ZQ_Q4_K>(ctx, dev_x, x_dtype, d_slot_token, d_slot_expert, d_offsets, routes, srows, shared_id, H, units_h, d_xq1, err); break;
+    case ZQ_Q4_0: rc = launch_quantize<ZQ_Q4_0>(ctx, dev_x, x_dtype, d_slot_token, d_slot_expert, d_offsets, routes, srows, shared_id, H, units_h, d_xq1, err); break;
+    default: rc = launch_quantize<ZQ_Q8_0>(ctx, dev_x, x_dtype, d_slot_token, d_slot_expert, d_offsets, routes, srows, shared_id, H, units_h, d_xq1, err); break;
     }
     if (rc) return rc;
     GroupedArgs ga;
@@ -420,6 +481,14 @@ int moe_grouped_forward(zq_ctx *ctx, const zq_moe_experts *t, const void *dev_x,
     ga.chunk_words = kChunkUnits * format_info(t->gate_type).unit_bytes / 4;
     ga.tiles = (int)((I + kTileRows / 2 - 1) / (kTileRows / 2));
     ga.n_out = (int)I;
+    ga.shared_id = shared_id;
+    if (rides) {
+        ga.shared_a = shared_gate->gemv_map_half;
+        ga.shared_b = shared_up->gemv_map_half;
+    } else {
+        memset(&ga.shared_a, 0, sizeof(CUtensorMap));
+        memset(&ga.shared_b, 0, sizeof(CUtensorMap));
+    }
     switch (t->gate_type) {
     case ZQ_Q4_K: rc = launch_grouped<ZQ_Q4_K, true>(ctx, ga, err); break;
     case ZQ_Q4_0: rc = launch_grouped<ZQ_Q4_0, true>(ctx, ga, err); break;
@@ -428,9 +497,9 @@ int moe_grouped_forward(zq_ctx *ctx, const zq_moe_experts *t, const void *dev_x,
     if (rc) return rc;
     // ---- down
     switch (t->down_type) {
-    case ZQ_Q4_K: rc = launch_quantize<ZQ_Q4_K>(ctx, d_act, ZQ_F32, nullptr, d_slot_expert, d_offsets, routes, I, units_i, d_xq2, err); break;
-    case ZQ_Q4_0: rc = launch_quantize<ZQ_Q4_0>(ctx, d_act, ZQ_F32, nullptr, d_slot_expert, d_offsets, routes, I, units_i, d_xq2, err); break;
-    default: rc = launch_quantize<ZQ_Q8_0>(ctx, d_act, ZQ_F32, nullptr, d_slot_expert, d_offsets, routes, I, units_i, d_xq2, err); break;
+    case ZQ_Q4_K: rc = launch_quantize<ZQ_Q4_K>(ctx, d_act, ZQ_F32, nullptr, d_slot_expert, d_offsets, routes, srows, shared_id, I, units_i, d_xq2, err); break;
+    case ZQ_Q4_0: rc = launch_quantize<ZQ_Q4_0>(ctx, d_act, ZQ_F32, nullptr, d_slot_expert, d_offsets, routes, srows, shared_id, I, units_i, d_xq2, err); break;
+    default: rc = launch_quantize<ZQ_Q8_0>(ctx, d_act, ZQ_F32, nullptr, d_slot_expert, d_offsets, routes, srows, shared_id, I, units_i, d_xq2, err); break;
     }
     if (rc) return rc;
     ga.maps_a = t->d_down_maps;
@@ -442,6 +511,10 @@ int moe_grouped_forward(zq_ctx *ctx, const zq_moe_experts *t, const void *dev_x,
     ga.chunk_words = kChunkUnits * format_info(t->down_type).unit_bytes / 4;
     ga.tiles = (int)((H + kTileRows - 1) / kTileRows);
     ga.n_out = (int)H;
+    if (rides) {
+        ga.shared_a = shared_down->gemv_map;
+        ga.shared_b = shared_down->gemv_map;
+    }
     switch (t->down_type) {
     case ZQ_Q4_K: rc = launch_grouped<ZQ_Q4_K, false>(ctx, ga, err); break;
     case ZQ_Q4_0: rc = launch_grouped<ZQ_Q4_0, false>(ctx, ga, err); break;
