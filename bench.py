@@ -135,6 +135,11 @@ def run_ours(args):
         print(json.dumps({"only_prefill": m, "launches": ctx.launch_count}))
         return
 
+    if args.only_moe:
+        out = bench_moe(ctx, device, args, world, rank, only=args.only_moe)
+        print(json.dumps({"only_moe": args.only_moe, "moe": out, "launches": ctx.launch_count}))
+        return
+
     # ---- synthetic inputs: N(0, 0.02) weights quantised on the device, N(0, 1) activations, seed 0
     gen = torch.Generator(device=device)
     cases = []  # (fmt_name, fmt, k, n, mode, weight, k_local, n_local)
@@ -404,7 +409,7 @@ def bench_prefill(ctx, device, args):
     return out
 
 
-def bench_moe(ctx, device, args, world, rank):
+def bench_moe(ctx, device, args, world, rank, only=None):
     """configs[4]: 256 experts, top-8, hidden 7168, expert FFN 2048 (Q4_K), one shared expert, softmax top-k router,
     bf16 activations; 64 tokens (decode) and 8192 tokens (prefill).  With N ranks the experts are expert-parallel
     (256/N per rank), tokens data-parallel (total fixed), routed rows cross ranks with one all-to-all each way."""
@@ -435,6 +440,8 @@ def bench_moe(ctx, device, args, world, rank):
     expert_bytes = 3 * int(I * H * BPW)
     out = {"experts": E, "top_k": K, "hidden": H, "intermediate": I, "weights": "Q4_K", "parallelism": f"ep{world}" if world > 1 else "single", "router": "softmax top-k, renormalised over the selected experts"}
     for name, m_total in (("decode_m64", 64), ("prefill_m8192", 8192)):
+        if only and only != name:
+            continue
         m = m_total // world
         gen.manual_seed(8200 + m_total)
         x_all = torch.randn((m_total, H), generator=gen, device=device, dtype=torch.float32).to(torch.bfloat16)
@@ -560,6 +567,7 @@ def main():
     ap.add_argument("--f16-gemv", action="store_true", help="decode on the f16 warp-MMA kernels instead of the integer-MMA kernel (A/B aid)")
     ap.add_argument("--stack-layers", type=int, default=64, help="layers of the prefill GEMM stack (configs[2] names 64)")
     ap.add_argument("--only-prefill", type=int, default=0, help="profiling aid: run only a few prefill GEMMs (Q4_K 5120->17408) at this token count and exit")
+    ap.add_argument("--only-moe", default=None, choices=["decode_m64", "prefill_m8192"], help="profiling aid: run only this MoE case and exit")
     ap.add_argument("--only", default=None, help="restrict the sweep to one case, e.g. q4_k:5120x17408:1 (format:KxN:batch); for profiling")
     args = ap.parse_args()
     if args.impl == "reference":
