@@ -77,9 +77,42 @@ __global__ void __launch_bounds__(kRouterThreads) router_topk_kernel(const void 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int e_begin = blockIdx.y * experts_per_cta;
     const int e_end = e_begin + experts_per_cta < num_experts ? e_begin + experts_per_cta : num_experts;
-    for (int i = threadIdx.x; i < kRouterTokens * hidden; i += kRouterThreads) {
-        int t = i / hidden, c = i - t * hidden;
-        xs[i] = (tok0 + t < m) ? load_as_f32(x, x_dtype, (size_t)(tok0 + t) * hidden + c) : 0.f;
+    if ((hidden & 7) == 0) {  // 8 columns per thread and step: 16- or 32-byte loads, no index division
+        for (int t = 0; t < kRouterTokens; ++t) {
+            const bool live = tok0 + t < m;
+            for (int c = threadIdx.x * 8; c < hidden; c += kRouterThreads * 8) {
+                float v[8];
+                const size_t o = (size_t)(tok0 + t) * hidden + c;
+                if (!live) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) v[j] = 0.f;
+                } else if (x_dtype == ZQ_F32) {
+                    const float4 f0 = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(x) + o), f1 = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(x) + o + 4);
+                    v[0] = f0.x; v[1] = f0.y; v[2] = f0.z; v[3] = f0.w; v[4] = f1.x; v[5] = f1.y; v[6] = f1.z; v[7] = f1.w;
+                } else {
+                    const uint4 raw = *reinterpret_cast<const uint4 *>(reinterpret_cast<const uint16_t *>(x) + o);
+                    const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        if (x_dtype == ZQ_F16) {
+                            const float2 f = __half22float2(u32_as_h2(rw[j]));
+                            v[2 * j] = f.x; v[2 * j + 1] = f.y;
+                        } else {
+                            v[2 * j] = __uint_as_float(rw[j] << 16);
+                            v[2 * j + 1] = __uint_as_float(rw[j] & 0xFFFF0000u);
+                        }
+                    }
+                }
+                float4 *dst = reinterpret_cast<float4 *>(xs + t * hidden + c);
+                dst[0] = make_float4(v[0], v[1], v[2], v[3]);
+                dst[1] = make_float4(v[4], v[5], v[6], v[7]);
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < kRouterTokens * hidden; i += kRouterThreads) {
+            int t = i / hidden, c = i - t * hidden;
+            xs[i] = (tok0 + t < m) ? load_as_f32(x, x_dtype, (size_t)(tok0 + t) * hidden + c) : 0.f;
+        }
     }
     __syncthreads();
     for (int e = e_begin + warp; e < e_end; e += kRouterThreads / 32) {
