@@ -187,42 +187,58 @@ def run_ours(args):
 
     from zllm_b200 import ffi
 
-    def launch(m, case):
+    def launch(m, case, collective=True):
         name, fmt, k, n, mode, w, (c0, c1), (r0, r1) = case
         x = x_local[(m, k, c0, c1)]
         y = outs[(m, name, k, n)]
         ffi.call("zq_linear", ctx.handle, w.handle, C.c_void_p(x.data_ptr()), ffi.F32, m, C.c_void_p(y.data_ptr()), ffi.F32, None)
-        if mode == "row":
+        if mode == "row" and collective:
             dist.all_reduce(y)
 
-    # One CUDA graph per (batch, format) block of launches: replaying graphs keeps the host out of the timed
-    # region (a Python/ctypes launch costs more than a 5 us kernel).  Events between graph launches bracket the
-    # Q4_K batch-1 and batch-4 blocks (the headline kernel) inside the timed region.
+    # CUDA graphs keep the host out of the timed region (a Python/ctypes launch costs more than a 5 us kernel).
+    # A block is one (batch, format) group of launches; it is cut into segments that end at every K-split matrix,
+    # because that matrix's all-reduce is launched from the host right after its segment: collectives are never
+    # captured.  With one GPU a block is one segment.  Events around the Q4_K batch-1 and batch-4 blocks (the
+    # headline kernel) are recorded inside the timed region.
     blocks = []
     for m in BATCHES:
         for fmt, name in FORMATS:
             members = [(mm, case) for mm, case in plan if mm == m and case[1] == fmt]
             if members:
                 blocks.append((m, fmt, members))
+    segments = []  # per block: list of (members, tensor to all-reduce after the segment or None)
+    for m, fmt, members in blocks:
+        segs, cur = [], []
+        for mm, case in members:
+            cur.append((mm, case))
+            if case[4] == "row":
+                segs.append((cur, outs[(mm, case[0], case[2], case[3])]))
+                cur = []
+        if cur:
+            segs.append((cur, None))
+        segments.append(segs)
     for m, fmt, members in blocks:  # eager pass: sizes every internal buffer before capture
         for mm, case in members:
             launch(mm, case)
     torch.cuda.synchronize()
-    graphs = []
+    graphs = []  # per block: one graph per segment
     launches_per_graph = []
-    if not args.no_graph and world == 1:  # collectives are launched from the host, never captured
+    if not args.no_graph:
         side = torch.cuda.Stream(device=device)
         try:
-            for m, fmt, members in blocks:
-                g = torch.cuda.CUDAGraph()
-                n0 = ctx.launch_count
-                with torch.cuda.graph(g, stream=side):
-                    ctx.set_stream(torch.cuda.current_stream(device).cuda_stream)
-                    for mm, case in members:
-                        launch(mm, case)
-                graphs.append(g)
-                launches_per_graph.append(ctx.launch_count - n0)
-        except Exception as exc:  # e.g. a collective that cannot be captured: fall back to host launches
+            for segs in segments:
+                gs = []
+                for seg_members, _ in segs:
+                    g = torch.cuda.CUDAGraph()
+                    n0 = ctx.launch_count
+                    with torch.cuda.graph(g, stream=side):
+                        ctx.set_stream(torch.cuda.current_stream(device).cuda_stream)
+                        for mm, case in seg_members:
+                            launch(mm, case, collective=False)
+                    gs.append(g)
+                    launches_per_graph.append(ctx.launch_count - n0)
+                graphs.append(gs)
+        except Exception as exc:
             graphs = []
             sys.stderr.write(f"bench: graph capture failed ({exc}); launching from the host\n")
         ctx.set_stream(torch.cuda.current_stream(device).cuda_stream)
@@ -234,7 +250,10 @@ def run_ours(args):
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
             if graphs:
-                graphs[bi].replay()
+                for g, (_, reduce_me) in zip(graphs[bi], segments[bi]):
+                    g.replay()
+                    if reduce_me is not None:
+                        dist.all_reduce(reduce_me)
             else:
                 for mm, case in members:
                     launch(mm, case)
