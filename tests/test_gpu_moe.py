@@ -91,6 +91,35 @@ def test_moe_forward_matches_cpu_path(tensor_type, m, with_shared, moe_path):
     assert H.max_rel_error(got, want) <= BOUND
 
 
+@pytest.mark.parametrize("tensor_type", [H.Q4_K, H.Q8_0])
+@pytest.mark.parametrize("m", [150, 700])
+def test_moe_prefill_runs_grouped_tensor_core_gemms(tensor_type, m, moe_path):
+    """Prefill-sized batches (>= 32 routed rows per expert): one grouped GEMM per projection over all experts, against
+    the same oracle; the per-expert path (one pair of GEMM calls per expert) must agree too.  Expert 3 gets no tokens.
+
+    Tolerance: each tensor-core GEMM meets the 2e-3 max bound on its own (tests/test_gpu_gemm.py).  The MoE layer
+    chains two of them (gate/up -> SiLU -> down, the intermediate passing through f16 as the second GEMM's operand)
+    and adds top-k results, so the WORST of ~10^5 outputs lands near 3e-3 while the relative L2 error stays below
+    5e-4; the test holds the composite to 4e-3 max and 1e-3 L2."""
+    from zllm_b200.backend import MoeExperts, moe_forward
+
+    n_exp, top_k, hidden, inter = 4, 2, 512, 768
+    gates, ups, downs = _experts(tensor_type, n_exp, hidden, inter, seed=700)
+    rng = np.random.default_rng(70 + m)
+    x = rng.standard_normal((m, hidden)).astype(np.float32)
+    ids_np = np.stack([rng.permutation(3)[:top_k] for _ in range(m)]).astype(np.uint32)  # experts 0..2 only
+    w_np = rng.random((m, top_k)).astype(np.float32)
+    w_np /= w_np.sum(axis=1, keepdims=True)
+    c = ctx()
+    table = MoeExperts(c, [c.prepare_weight(tensor_type, g, inter, hidden) for g in gates], [c.prepare_weight(tensor_type, u, inter, hidden) for u in ups],
+                       [c.prepare_weight(tensor_type, d, hidden, inter) for d in downs])
+    ids = torch.from_numpy(ids_np.astype(np.int32)).cuda()
+    got = host(moe_forward(c, table, dev(x), ids, dev(w_np)))
+    want = orc.moe_forward([(tensor_type, g, inter, hidden) for g in gates], [(tensor_type, u, inter, hidden) for u in ups], [(tensor_type, d, hidden, inter) for d in downs], x, ids_np, w_np)
+    assert H.max_rel_error(got, want) <= 2 * BOUND
+    assert float(np.linalg.norm(got - want) / np.linalg.norm(want)) <= 1e-3
+
+
 def test_shared_expert_of_another_width_takes_its_own_launches():
     """A shared expert shaped like the routed ones rides along in the grouped launches; any other shape runs as a
     separate gated MLP (src/moe/topk_moe.rs:84-104) and is added in the combine."""

@@ -264,6 +264,8 @@ struct zq_weight {
 namespace zq {
 int ensure_workspace(zq_ctx *ctx, size_t bytes, zq_error *err);
 int ensure_xq(zq_ctx *ctx, size_t bytes, zq_error *err);
+int launch_to_f16(zq_ctx *ctx, const void *x, int x_dtype, __half *out, size_t n, zq_error *err);
+int launch_gemm_grouped(zq_ctx *ctx, const __half *w, const __half *w2, size_t mats, size_t rows, size_t k, const __half *x, size_t x_rows, const int4 *items, int n_items, void *y, int y_dtype, zq_error *err);
 int ensure_scratch_mid(zq_ctx *ctx, size_t bytes, zq_error *err);
 int make_weight_map(const zq_weight *w, int box_words, int box_rows, CUtensorMap *out, zq_error *err);
 

@@ -35,6 +35,11 @@ struct GemmParams {
     int m;       // tokens
     int n_out;   // weight rows
     int k;       // input columns
+    // Grouped form (MoE prefill): the work list replaces the tile grid.  Item = {weight matrix z of the 3-D weight
+    // operand, first row of the tile, first token row, end of the matrix's token rows}; tokens are rows of one
+    // activation operand shared by all matrices, outputs are rows of y with n_out columns.
+    const int4 *items;
+    int n_items;
 };
 
 // ---- tcgen05 wrappers -------------------------------------------------------------------------------------------
@@ -124,8 +129,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k_blocks = (p.k + kBK - 1) / kBK;
     const int n_row_tiles = (p.n_out + kBM - 1) / kBM, n_tok_tiles = (p.m + kBN - 1) / kBN;
-    const int total_tiles = n_row_tiles * n_tok_tiles;
-    auto tile_coords = [&](int tile, int &row0, int &tok0) {
+    const bool grouped = p.items != nullptr;
+    const int total_tiles = grouped ? p.n_items : n_row_tiles * n_tok_tiles;
+    auto tile_coords = [&](int tile, int &row0, int &tok0, int &tok_end, int &z) {
+        if (grouped) {
+            const int4 it = p.items[tile];
+            z = it.x;
+            row0 = it.y;
+            tok0 = it.z;
+            tok_end = it.w;
+            return;
+        }
+        z = 0;
+        tok_end = p.m;
         const int per_group = kTokGroup * n_row_tiles;
         const int group = tile / per_group, in_group = tile - group * per_group;
         const int group_toks = (n_tok_tiles - group * kTokGroup) < kTokGroup ? (n_tok_tiles - group * kTokGroup) : kTokGroup;
@@ -162,15 +178,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
         if (lane == 0) {
             long long kg = 0;  // k-block counter over all tiles of this CTA: ring position
             for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-                int row0, tok0;
-                tile_coords(tile, row0, tok0);
+                int row0, tok0, tok_end, z;
+                tile_coords(tile, row0, tok0, tok_end, z);
                 for (int kb = 0; kb < k_blocks; ++kb, ++kg) {
                     const int s = (int)(kg % STAGES);
                     if (kg >= STAGES && !wait_flag(&empty[s], (uint32_t)((kg / STAGES) - 1) & 1, &s_abort, p.status, kStatusMmaTimeout)) break;
                     uint8_t *st = smem + (size_t)s * S::stage_bytes;
                     mbar_expect_tx(&full[s], S::stage_bytes);
-                    tma_load_2d(st, &map_w, &full[s], kb * kBK, row0);
-                    if (GATED) tma_load_2d(st + S::a_bytes, &map_w2, &full[s], kb * kBK, row0);
+                    if (grouped) {
+                        tma_load_3d(st, &map_w, &full[s], kb * kBK, row0, z);
+                        if (GATED) tma_load_3d(st + S::a_bytes, &map_w2, &full[s], kb * kBK, row0, z);
+                    } else {
+                        tma_load_2d(st, &map_w, &full[s], kb * kBK, row0);
+                        if (GATED) tma_load_2d(st + S::a_bytes, &map_w2, &full[s], kb * kBK, row0);
+                    }
                     tma_load_2d(st + (GATED ? 2 : 1) * S::a_bytes, &map_x, &full[s], kb * kBK, tok0);
                 }
                 if (*(volatile int *)&s_abort) break;
@@ -216,8 +237,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
         const int q = warp & 3;
         int iter = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++iter) {
-            int row0, tok0;
-            tile_coords(tile, row0, tok0);
+            int row0, tok0, tok_end, z;
+            tile_coords(tile, row0, tok0, tok_end, z);
             const int b = iter % ACC;
             const int row = row0 + q * 32 + lane;
             const bool ok = wait_flag(&acc_full[b], (uint32_t)(iter / ACC) & 1, &s_abort, p.status, kStatusMmaTimeout);
@@ -225,7 +246,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
             if (ok) {
                 const uint32_t lane_base = tmem_base + (uint32_t)b * ACC_COLS + ((uint32_t)(q * 32) << 16);
                 for (int c0 = 0; c0 < kBN; c0 += 16) {
-                    if (tok0 + c0 >= p.m) break;  // warp-uniform
+                    if (tok0 + c0 >= tok_end) break;  // warp-uniform
                     uint32_t v[16], u[16];
                     tmem_ld16(lane_base + c0, v);
                     if (GATED) tmem_ld16(lane_base + kBN + c0, u);
@@ -234,7 +255,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
                             const int tok = tok0 + c0 + j;
-                            if (tok < p.m) {
+                            if (tok < tok_end) {
                                 float val = __uint_as_float(v[j]);
                                 if (GATED) {
                                     const float up = __uint_as_float(u[j]);
@@ -320,8 +341,75 @@ int launch_gemm(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const vo
     p.m = (int)m;
     p.n_out = (int)n;
     p.k = (int)k;
+    p.items = nullptr;
+    p.n_items = 0;
     const size_t total_tiles = ((n + kBM - 1) / kBM) * ((m + kBN - 1) / kBN);
     dim3 grid((unsigned)(total_tiles < (size_t)ctx->sm_count ? total_tiles : (size_t)ctx->sm_count));
+    static bool configured[2][64] = {};
+    if (gated) {
+        if (!configured[1][ctx->device & 63]) {
+            ZQ_CUDA_CHECK(cudaFuncSetAttribute(gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<true>::total), err);
+            configured[1][ctx->device & 63] = true;
+        }
+        gemm_kernel<true><<<grid, kGemmThreads, GemmSmem<true>::total, ctx->stream>>>(map_w, map_w2, map_x, p);
+    } else {
+        if (!configured[0][ctx->device & 63]) {
+            ZQ_CUDA_CHECK(cudaFuncSetAttribute(gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<false>::total), err);
+            configured[0][ctx->device & 63] = true;
+        }
+        gemm_kernel<false><<<grid, kGemmThreads, GemmSmem<false>::total, ctx->stream>>>(map_w, map_w2, map_x, p);
+    }
+    ctx->launches++;
+    ZQ_CUDA_CHECK(cudaGetLastError(), err);
+    return ZQ_OK;
+}
+
+static int make_f16_map3(const void *base, size_t mats, size_t rows, size_t cols, CUtensorMap *out, zq_error *err) {
+    EncodeTiledFn encode = get_encode_tiled(err);
+    if (!encode) return ZQ_ERR_CUDA;
+    cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)mats};
+    cuuint64_t strides[2] = {(cuuint64_t)cols * 2, (cuuint64_t)rows * cols * 2};
+    cuuint32_t box[3] = {(cuuint32_t)kBK, (cuuint32_t)kBM, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return set_error(err, ZQ_ERR_CUDA, "cuTensorMapEncodeTiled (f16 operand %zux%zux%zu) failed with code %d", mats, rows, cols, (int)r);
+    return ZQ_OK;
+}
+
+int launch_to_f16(zq_ctx *ctx, const void *x, int x_dtype, __half *out, size_t n, zq_error *err) {
+    size_t blocks = (n / 4 + 255) / 256;
+    if (blocks > (size_t)ctx->sm_count * 32) blocks = (size_t)ctx->sm_count * 32;
+    if (blocks == 0) blocks = 1;
+    to_f16_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(x, x_dtype, out, n);
+    ctx->launches++;
+    ZQ_CUDA_CHECK(cudaGetLastError(), err);
+    return ZQ_OK;
+}
+
+// Grouped GEMM (MoE prefill): `mats` f16 weight matrices [rows, k] stacked in one buffer (and a second stack for the
+// gated form), one f16 activation operand [x_rows, k] whose row ranges belong to the matrices, a device work list of
+// {matrix, first row, first token row, end token row}.  y[token row, rows] in y_dtype; gated: silu(w x) * (w2 x).
+int launch_gemm_grouped(zq_ctx *ctx, const __half *w, const __half *w2, size_t mats, size_t rows, size_t k, const __half *x, size_t x_rows, const int4 *items, int n_items, void *y, int y_dtype, zq_error *err) {
+    if (n_items <= 0) return ZQ_OK;
+    if (k % 8) return set_error(err, ZQ_ERR_SHAPE, "grouped GEMM needs columns aligned to 8, got %zu", k);
+    const bool gated = w2 != nullptr;
+    CUtensorMap map_w, map_w2, map_x;
+    int rc = make_f16_map3(w, mats, rows, k, &map_w, err);
+    if (!rc) rc = make_f16_map3(gated ? w2 : w, mats, rows, k, &map_w2, err);
+    if (!rc) rc = make_f16_map(x, x_rows, k, kBN, &map_x, err);
+    if (rc) return rc;
+    GemmParams p;
+    p.y = y;
+    p.residual = nullptr;
+    p.status = ctx->status_dev;
+    p.y_dtype = y_dtype;
+    p.m = (int)x_rows;
+    p.n_out = (int)rows;
+    p.k = (int)k;
+    p.items = items;
+    p.n_items = n_items;
+    dim3 grid((unsigned)(n_items < ctx->sm_count ? n_items : ctx->sm_count));
     static bool configured[2][64] = {};
     if (gated) {
         if (!configured[1][ctx->device & 63]) {

@@ -410,6 +410,74 @@ int zq_moe_forward(zq_ctx *ctx, const zq_moe_experts *experts, const zq_weight *
     ZQ_CUDA_CHECK(cudaGetLastError(), err);
 
     // ---- experts, ascending id (src/moe/routing.rs:180-213: gather rows, expert batch, weighted scatter)
+    const bool grouped_gemm = !ctx->force_moe_per_expert && routes >= 32 * E && H % 8 == 0 && I % 8 == 0;
+    if (grouped_gemm) {
+        // Prefill: one grouped tensor-core GEMM per projection and chunk of experts instead of two launches per
+        // expert (an expert's own GEMM has 16-56 tiles for 148 SMs).  The chunk's packed weights are dequantised to
+        // f16 stacks [chunk][rows][K] in the workspace; the work list holds one item per (expert, token tile, row
+        // tile); tokens are the gathered slot rows, so outputs land in slot order as the combine expects.
+        const size_t per_expert = 3 * I * H * sizeof(__half);
+        size_t chunk = (size_t(3) << 30) / per_expert;  // ~3 GB of f16 operands at a time
+        if (chunk < 1) chunk = 1;
+        if (chunk > E) chunk = E;
+        auto al2 = [](size_t v) { return (v + 1023) & ~size_t(1023); };
+        const size_t w_stack = al2(chunk * I * H * sizeof(__half));
+        const size_t x16_bytes = al2(routes * H * sizeof(__half)), act16_bytes = al2(routes * I * sizeof(__half));
+        std::vector<int4> items;
+        struct ChunkPlan { size_t e0, e1; int gated_first, gated_n, down_first, down_n; };
+        std::vector<ChunkPlan> plans;
+        const int rt_i = (int)((I + 127) / 128), rt_h = (int)((H + 127) / 128);
+        for (size_t e0 = 0; e0 < E; e0 += chunk) {
+            ChunkPlan cp;
+            cp.e0 = e0;
+            cp.e1 = e0 + chunk < E ? e0 + chunk : E;
+            cp.gated_first = (int)items.size();
+            for (size_t e = cp.e0; e < cp.e1; ++e) {
+                const int first = (int)offsets[e], end = (int)offsets[e + 1];
+                for (int t0 = first; t0 < end; t0 += 256)
+                    for (int rt = 0; rt < rt_i; ++rt) items.push_back(make_int4((int)(e - e0), rt * 128, t0, end));
+            }
+            cp.gated_n = (int)items.size() - cp.gated_first;
+            cp.down_first = (int)items.size();
+            for (size_t e = cp.e0; e < cp.e1; ++e) {
+                const int first = (int)offsets[e], end = (int)offsets[e + 1];
+                for (int t0 = first; t0 < end; t0 += 256)
+                    for (int rt = 0; rt < rt_h; ++rt) items.push_back(make_int4((int)(e - e0), rt * 128, t0, end));
+            }
+            cp.down_n = (int)items.size() - cp.down_first;
+            plans.push_back(cp);
+        }
+        const size_t items_bytes = al2(items.size() * sizeof(int4));
+        rc = ensure_workspace(ctx, 3 * w_stack + x16_bytes + act16_bytes + items_bytes, err);
+        if (rc) return rc;
+        uint8_t *wsb = reinterpret_cast<uint8_t *>(ctx->workspace);
+        __half *wg16 = reinterpret_cast<__half *>(wsb), *wu16 = reinterpret_cast<__half *>(wsb + w_stack), *wd16 = reinterpret_cast<__half *>(wsb + 2 * w_stack);
+        __half *x16 = reinterpret_cast<__half *>(wsb + 3 * w_stack), *act16 = reinterpret_cast<__half *>(wsb + 3 * w_stack + x16_bytes);
+        int4 *d_items = reinterpret_cast<int4 *>(wsb + 3 * w_stack + x16_bytes + act16_bytes);
+        ZQ_CUDA_CHECK(cudaMemcpyAsync(d_items, items.data(), items.size() * sizeof(int4), cudaMemcpyHostToDevice, ctx->stream), err);
+        ZQ_CUDA_CHECK(cudaStreamSynchronize(ctx->stream), err);  // the host vector goes out of scope at return
+        const __half *xin = reinterpret_cast<const __half *>(d_xs);
+        if (x_dtype != ZQ_F16) {
+            rc = launch_to_f16(ctx, d_xs, x_dtype, x16, routes * H, err);
+            if (rc) return rc;
+            xin = x16;
+        }
+        for (const ChunkPlan &cp : plans) {
+            if (cp.gated_n == 0) continue;
+            for (size_t e = cp.e0; e < cp.e1; ++e) {
+                if (offsets[e + 1] == offsets[e]) continue;
+                const size_t z = e - cp.e0;
+                rc = launch_dequantize_f16(ctx, experts->gate[e], wg16 + z * I * H, err);
+                if (!rc) rc = launch_dequantize_f16(ctx, experts->up[e], wu16 + z * I * H, err);
+                if (!rc) rc = launch_dequantize_f16(ctx, experts->down[e], wd16 + z * H * I, err);
+                if (rc) return rc;
+            }
+            rc = launch_gemm_grouped(ctx, wg16, wu16, cp.e1 - cp.e0, I, H, xin, routes, d_items + cp.gated_first, cp.gated_n, act16, ZQ_F16, err);
+            if (rc) return rc;
+            rc = launch_gemm_grouped(ctx, wd16, nullptr, cp.e1 - cp.e0, H, I, act16, routes, d_items + cp.down_first, cp.down_n, d_out, ZQ_F32, err);
+            if (rc) return rc;
+        }
+    } else {
     for (size_t e = 0; e < E; ++e) {
         const size_t first = offsets[e], count = offsets[e + 1] - offsets[e];
         if (!count) continue;
@@ -417,6 +485,7 @@ int zq_moe_forward(zq_ctx *ctx, const zq_moe_experts *experts, const zq_weight *
         if (rc) return rc;
         rc = zq_linear(ctx, experts->down[e], d_act + first * I, ZQ_F32, count, d_out + first * H, ZQ_F32, nullptr, err);
         if (rc) return rc;
+    }
     }
     if (has_shared) {
         rc = zq_gated_mlp(ctx, shared_gate, shared_up, shared_down, dev_x, x_dtype, m, d_shared, ZQ_F32, nullptr, err);
