@@ -18,7 +18,7 @@ def _experts(tensor_type, n, hidden, inter, seed):
     return gates, ups, downs
 
 
-@pytest.mark.parametrize("m,experts,top_k,hidden", [(1, 8, 2, 512), (5, 16, 4, 256), (64, 256, 8, 512), (33, 12, 3, 1024)])
+@pytest.mark.parametrize("m,experts,top_k,hidden", [(1, 8, 2, 512), (5, 16, 4, 256), (64, 256, 8, 512), (33, 12, 3, 1024), (300, 64, 6, 1024), (1000, 12, 2, 256)])
 @pytest.mark.parametrize("normalize", [True, False])
 def test_router_matches_cpu_softmax_topk(m, experts, top_k, hidden, normalize):
     """src/moe/routing.rs:25-39 through the device router (src/kernel/cuda/routing.rs:15-62)."""

@@ -113,16 +113,28 @@ __global__ void dequantize_kernel(uint32_t type, const uint8_t *__restrict__ res
     }
 }
 
-// All rows -> f16 [rows, cols], one thread per 8 consecutive elements (one 16-byte store): the operand pass of the
-// prefill GEMM.  Each value is the reference's f32 value (same operation order as decode_unit_element) rounded once.
-__global__ void dequantize_f16_kernel(uint32_t type, const uint8_t *__restrict__ resident, size_t row_pitch, int unit_bytes, size_t rows, size_t cols, __half *__restrict__ out) {
-    const size_t oct_per_row = cols / 8;
-    const size_t total = rows * oct_per_row;
-    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
-        const size_t row = idx / oct_per_row;
-        const size_t k0 = (idx - row * oct_per_row) * 8;
-        const uint8_t *unit = resident + row * row_pitch + (k0 / kUnitWeights) * unit_bytes;
-        const int i0 = (int)(k0 % kUnitWeights);
+// Packed rows -> f16 [rows, cols]: the operand pass of the prefill GEMM.  Each value is the reference's f32 value
+// (same operation order as decode_unit_element) rounded once.  Up to kDequantBatch matrices of one type and shape
+// per launch (MoE prefill dequantises the experts of a chunk together).  One warp per 256-weight unit, 8 consecutive elements per lane: the
+// unit's packed bytes are read once with coalesced loads, the 512 output bytes are one coalesced store, and the only
+// index division is one per warp.
+constexpr int kDequantBatch = 96;
+struct DequantBatch {
+    const uint8_t *src[kDequantBatch];
+    __half *dst[kDequantBatch];
+};
+
+__global__ void __launch_bounds__(256) dequantize_f16_batch_kernel(const __grid_constant__ DequantBatch batch, uint32_t type, size_t row_pitch, int unit_bytes, int rows, int cols, int units_per_row) {
+    const uint8_t *resident = batch.src[blockIdx.y];
+    __half *out = batch.dst[blockIdx.y];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int total_units = rows * units_per_row;
+    for (int u = blockIdx.x * 8 + warp; u < total_units; u += gridDim.x * 8) {
+        const int row = u / units_per_row, ur = u - row * units_per_row;
+        const int k0 = ur * kUnitWeights + 8 * lane;
+        if (k0 >= cols) continue;  // padded tail of the last unit (cols is a multiple of 32, so all 8 or none)
+        const uint8_t *unit = resident + (size_t)row * row_pitch + (size_t)ur * unit_bytes;
+        const int i0 = 8 * lane;
         float v[8];
         if (type == ZQ_Q4_K) {
             const uint4 hdr = *reinterpret_cast<const uint4 *>(unit);
@@ -156,22 +168,39 @@ __global__ void dequantize_f16_kernel(uint32_t type, const uint8_t *__restrict__
         packed.y = h2_as_u32(__floats2half2_rn(v[2], v[3]));
         packed.z = h2_as_u32(__floats2half2_rn(v[4], v[5]));
         packed.w = h2_as_u32(__floats2half2_rn(v[6], v[7]));
-        *reinterpret_cast<uint4 *>(out + row * cols + k0) = packed;
+        *reinterpret_cast<uint4 *>(out + (size_t)row * cols + k0) = packed;
     }
 }
 
-int launch_dequantize_f16(zq_ctx *ctx, const zq_weight *w, __half *out, zq_error *err) {
-    if (w->cols % 8) return set_error(err, ZQ_ERR_SHAPE, "f16 operand pass needs columns aligned to 8, got %zu", w->cols);
-    const size_t total = w->rows * (w->cols / 8);
-    if (total == 0) return ZQ_OK;
-    const int threads = 256;
-    size_t blocks = (total + threads - 1) / threads;
-    if (blocks > (size_t)ctx->sm_count * 32) blocks = (size_t)ctx->sm_count * 32;
-    const FormatInfo f = format_info(w->type);
-    dequantize_f16_kernel<<<(unsigned)blocks, threads, 0, ctx->stream>>>(w->type, w->data, w->row_pitch, f.unit_bytes, w->rows, w->cols, out);
-    ctx->launches++;
-    ZQ_CUDA_CHECK(cudaGetLastError(), err);
+// weights[i] -> outs[i], all of one type and shape.
+int launch_dequantize_f16_batch(zq_ctx *ctx, const zq_weight *const *weights, __half *const *outs, size_t count, zq_error *err) {
+    for (size_t first = 0; first < count; first += kDequantBatch) {
+        const size_t n = count - first < (size_t)kDequantBatch ? count - first : (size_t)kDequantBatch;
+        const zq_weight *w0 = weights[first];
+        if (w0->cols % 8) return set_error(err, ZQ_ERR_SHAPE, "f16 operand pass needs columns aligned to 8, got %zu", w0->cols);
+        DequantBatch batch;
+        for (size_t i = 0; i < n; ++i) {
+            const zq_weight *w = weights[first + i];
+            if (w->type != w0->type || w->rows != w0->rows || w->cols != w0->cols) return set_error(err, ZQ_ERR_SHAPE, "batched dequantisation needs matrices of one type and shape");
+            batch.src[i] = w->data;
+            batch.dst[i] = outs[first + i];
+        }
+        const FormatInfo f = format_info(w0->type);
+        const size_t units = w0->rows * w0->units_per_row;
+        size_t bx = (units + 7) / 8;
+        const size_t cap = ((size_t)ctx->sm_count * 64 + n - 1) / n;  // enough blocks in total to fill the machine a few times over
+        if (bx > cap) bx = cap;
+        if (bx == 0) bx = 1;
+        dequantize_f16_batch_kernel<<<dim3((unsigned)bx, (unsigned)n), 256, 0, ctx->stream>>>(batch, w0->type, w0->row_pitch, f.unit_bytes, (int)w0->rows, (int)w0->cols, (int)w0->units_per_row);
+        ctx->launches++;
+        ZQ_CUDA_CHECK(cudaGetLastError(), err);
+    }
     return ZQ_OK;
+}
+
+int launch_dequantize_f16(zq_ctx *ctx, const zq_weight *w, __half *out, zq_error *err) {
+    if (w->rows == 0 || w->cols == 0) return ZQ_OK;
+    return launch_dequantize_f16_batch(ctx, &w, &out, 1, err);
 }
 
 int launch_dequantize(zq_ctx *ctx, const zq_weight *w, const uint32_t *row_ids, size_t n_rows, void *out, int out_dtype, zq_error *err) {

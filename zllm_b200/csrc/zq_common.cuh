@@ -264,6 +264,7 @@ struct zq_weight {
 namespace zq {
 int ensure_workspace(zq_ctx *ctx, size_t bytes, zq_error *err);
 int ensure_xq(zq_ctx *ctx, size_t bytes, zq_error *err);
+int launch_gemm_f16(zq_ctx *ctx, const __half *w, size_t rows, size_t k, const __half *x, size_t m, void *y, int y_dtype, zq_error *err);
 int launch_to_f16(zq_ctx *ctx, const void *x, int x_dtype, __half *out, size_t n, zq_error *err);
 int launch_gemm_grouped(zq_ctx *ctx, const __half *w, const __half *w2, size_t mats, size_t rows, size_t k, const __half *x, size_t x_rows, const int4 *items, int n_items, void *y, int y_dtype, zq_error *err);
 int ensure_scratch_mid(zq_ctx *ctx, size_t bytes, zq_error *err);
@@ -273,6 +274,7 @@ int make_weight_map(const zq_weight *w, int box_words, int box_rows, CUtensorMap
 int launch_repack(zq_ctx *ctx, uint32_t type, const uint8_t *gguf, uint8_t *resident, size_t rows, size_t cols, zq_error *err);
 int launch_dequantize(zq_ctx *ctx, const zq_weight *w, const uint32_t *row_ids, size_t n_rows, void *out, int out_dtype, zq_error *err);
 int launch_dequantize_f16(zq_ctx *ctx, const zq_weight *w, __half *out, zq_error *err);
+int launch_dequantize_f16_batch(zq_ctx *ctx, const zq_weight *const *weights, __half *const *outs, size_t count, zq_error *err);
 int launch_quantize(zq_ctx *ctx, uint32_t type, const float *values, size_t rows, size_t cols, void *out, zq_error *err);
 int launch_gemv(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const void *x, int x_dtype, size_t m, void *y, int y_dtype, const void *residual, zq_error *err);
 int launch_gemv_noalloc(zq_ctx *ctx, const zq_weight *w, const void *x, int x_dtype, size_t m, void *y, int y_dtype, zq_error *err);

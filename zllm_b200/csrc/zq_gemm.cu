@@ -200,12 +200,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
     } else if (warp == 1) {
         // ------------------------------------------------ MMA issuer
         if (lane == 0) {
-            // instruction descriptor: f32 accumulator, f16 A and B, both K-major, N = 256, M = 128
-            const uint32_t idesc = (1u << 4) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
             long long kg = 0;
             int iter = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++iter) {
+                // instruction descriptor: f32 accumulator, f16 A and B, both K-major, M = 128, N = the tile's token
+                // count rounded up to 16 (a ragged last tile of a matrix does not pay for 256 columns)
+                int row0, tok0, tok_end, z;
+                tile_coords(tile, row0, tok0, tok_end, z);
+                int n_eff = tok_end - tok0;
+                n_eff = n_eff >= kBN ? kBN : ((n_eff + 15) & ~15);
+                if (n_eff < 16) n_eff = 16;
+                const uint32_t idesc = (1u << 4) | ((uint32_t)(n_eff >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
                 const int b = iter % ACC;
                 if (iter >= ACC) ok = wait_flag(&acc_empty[b], (uint32_t)((iter / ACC) - 1) & 1, &s_abort, p.status, kStatusMmaTimeout);
                 if (!ok) break;
@@ -424,6 +430,36 @@ int launch_gemm_grouped(zq_ctx *ctx, const __half *w, const __half *w2, size_t m
         }
         gemm_kernel<false><<<grid, kGemmThreads, GemmSmem<false>::total, ctx->stream>>>(map_w, map_w2, map_x, p);
     }
+    ctx->launches++;
+    ZQ_CUDA_CHECK(cudaGetLastError(), err);
+    return ZQ_OK;
+}
+
+// Plain f16 x f16 GEMM on raw operands: y[m, rows] = x[m, k] w[rows, k]^T, f32 accumulation (router logits).
+int launch_gemm_f16(zq_ctx *ctx, const __half *w, size_t rows, size_t k, const __half *x, size_t m, void *y, int y_dtype, zq_error *err) {
+    if (k % 8) return set_error(err, ZQ_ERR_SHAPE, "f16 GEMM needs columns aligned to 8, got %zu", k);
+    CUtensorMap map_w, map_x;
+    int rc = make_f16_map(w, rows, k, kBM, &map_w, err);
+    if (!rc) rc = make_f16_map(x, m, k, kBN, &map_x, err);
+    if (rc) return rc;
+    GemmParams p;
+    p.y = y;
+    p.residual = nullptr;
+    p.status = ctx->status_dev;
+    p.y_dtype = y_dtype;
+    p.m = (int)m;
+    p.n_out = (int)rows;
+    p.k = (int)k;
+    p.items = nullptr;
+    p.n_items = 0;
+    const size_t total_tiles = ((rows + kBM - 1) / kBM) * ((m + kBN - 1) / kBN);
+    dim3 grid((unsigned)(total_tiles < (size_t)ctx->sm_count ? total_tiles : (size_t)ctx->sm_count));
+    static bool configured[64] = {};
+    if (!configured[ctx->device & 63]) {
+        ZQ_CUDA_CHECK(cudaFuncSetAttribute(gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<false>::total), err);
+        configured[ctx->device & 63] = true;
+    }
+    gemm_kernel<false><<<grid, kGemmThreads, GemmSmem<false>::total, ctx->stream>>>(map_w, map_w, map_x, p);
     ctx->launches++;
     ZQ_CUDA_CHECK(cudaGetLastError(), err);
     return ZQ_OK;

@@ -146,15 +146,33 @@ __global__ void __launch_bounds__(kRouterThreads) router_topk_kernel(const void 
         router_select(logits + warp * num_experts, lane, num_experts, top_k, scaling, normalize_selected, ids + (size_t)(tok0 + warp) * top_k, weights + (size_t)(tok0 + warp) * top_k);
 }
 
+// Router logits on the tensor cores for prefill-sized batches.  f16 operands alone would move logits by ~1e-3 and
+// flip top-k choices, so both operands are split into two f16 limbs (v = hi + lo, 22 bits) and the three products
+// that matter ride in ONE GEMM over a 3x longer K: x -> [hi | hi | lo], w -> [hi | lo | hi]; the products of f16
+// numbers are exact in the f32 accumulator, the dropped lo*lo term is 2^-22 of a product.
+__global__ void split_f16_kernel(const void *__restrict__ src, int dtype, size_t rows, int cols, int pattern, __half *__restrict__ dst) {
+    const size_t total = rows * (size_t)cols;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / cols;
+        const int c = (int)(i - r * cols);
+        const float v = load_as_f32(src, dtype, i);
+        const __half hi = __float2half_rn(v), lo = __float2half_rn(v - __half2float(hi));
+        __half *d = dst + r * 3 * (size_t)cols + c;
+        d[0] = hi;
+        d[cols] = pattern == 0 ? hi : lo;
+        d[2 * (size_t)cols] = pattern == 0 ? lo : hi;
+    }
+}
+
 // Second half of the split router: one warp per token, logits from global memory.
-__global__ void __launch_bounds__(kRouterThreads) router_select_kernel(const float *__restrict__ logits_g, int m, int num_experts, int top_k, float scaling, int normalize_selected, uint32_t *__restrict__ ids,
-                                                                        float *__restrict__ weights) {
+__global__ void __launch_bounds__(kRouterThreads) router_select_kernel(const float *__restrict__ logits_g, const float *__restrict__ bias, int m, int num_experts, int top_k, float scaling, int normalize_selected,
+                                                                        uint32_t *__restrict__ ids, float *__restrict__ weights) {
     extern __shared__ float rsm[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tok = blockIdx.x * (kRouterThreads / 32) + warp;
     if (tok >= m) return;
     float *l = rsm + warp * num_experts;
-    for (int e = lane; e < num_experts; e += 32) l[e] = logits_g[(size_t)tok * num_experts + e];
+    for (int e = lane; e < num_experts; e += 32) l[e] = logits_g[(size_t)tok * num_experts + e] + (bias ? bias[e] : 0.f);
     __syncwarp();
     router_select(l, lane, num_experts, top_k, scaling, normalize_selected, ids + (size_t)tok * top_k, weights + (size_t)tok * top_k);
 }
@@ -231,6 +249,27 @@ int zq_moe_route_softmax_topk(zq_ctx *ctx, const void *dev_x, int x_dtype, size_
         per_cta = ((num_experts + blocks_y - 1) / blocks_y + 7) & ~size_t(7);  // whole rounds of the 8 warps
         blocks_y = (num_experts + per_cta - 1) / per_cta;
     }
+    if (m >= 256 && hidden % 8 == 0) {
+        auto al = [](size_t v) { return (v + 255) & ~size_t(255); };
+        const size_t xb = al(m * 3 * hidden * sizeof(__half)), wb = al(num_experts * 3 * hidden * sizeof(__half));
+        int rc = ensure_moe_ws(ctx, xb + wb + al(m * num_experts * sizeof(float)), err);
+        if (rc) return rc;
+        uint8_t *ws = reinterpret_cast<uint8_t *>(ctx->moe_ws);
+        __half *x3 = reinterpret_cast<__half *>(ws), *w3 = reinterpret_cast<__half *>(ws + xb);
+        float *logits_g = reinterpret_cast<float *>(ws + xb + wb);
+        split_f16_kernel<<<grid_for(ctx, m * hidden, 256), 256, 0, ctx->stream>>>(dev_x, x_dtype, m, (int)hidden, 0, x3);
+        split_f16_kernel<<<grid_for(ctx, num_experts * hidden, 256), 256, 0, ctx->stream>>>(dev_router_f32, ZQ_F32, num_experts, (int)hidden, 1, w3);
+        ctx->launches += 2;
+        ZQ_CUDA_CHECK(cudaGetLastError(), err);
+        rc = launch_gemm_f16(ctx, w3, num_experts, 3 * hidden, x3, m, logits_g, ZQ_F32, err);
+        if (rc) return rc;
+        const unsigned sel_grid = (unsigned)((m + kRouterThreads / 32 - 1) / (kRouterThreads / 32));
+        router_select_kernel<<<sel_grid, kRouterThreads, (kRouterThreads / 32) * num_experts * sizeof(float), ctx->stream>>>(logits_g, dev_bias_f32, (int)m, (int)num_experts, (int)top_k, scaling_factor, normalize_selected, dev_ids,
+                                                                                                                            dev_weights);
+        ctx->launches++;
+        ZQ_CUDA_CHECK(cudaGetLastError(), err);
+        return ZQ_OK;
+    }
     if (blocks_y > 1) {
         int rc = ensure_moe_ws(ctx, m * num_experts * sizeof(float), err);  // the logits; consumed before anything else uses the buffer
         if (rc) return rc;
@@ -240,7 +279,7 @@ int zq_moe_route_softmax_topk(zq_ctx *ctx, const void *dev_x, int x_dtype, size_
         ctx->launches++;
         ZQ_CUDA_CHECK(cudaGetLastError(), err);
         const unsigned sel_grid = (unsigned)((m + kRouterThreads / 32 - 1) / (kRouterThreads / 32));
-        router_select_kernel<<<sel_grid, kRouterThreads, (kRouterThreads / 32) * num_experts * sizeof(float), ctx->stream>>>(logits_g, (int)m, (int)num_experts, (int)top_k, scaling_factor, normalize_selected, dev_ids, dev_weights);
+        router_select_kernel<<<sel_grid, kRouterThreads, (kRouterThreads / 32) * num_experts * sizeof(float), ctx->stream>>>(logits_g, nullptr, (int)m, (int)num_experts, (int)top_k, scaling_factor, normalize_selected, dev_ids, dev_weights);
         ctx->launches++;
         ZQ_CUDA_CHECK(cudaGetLastError(), err);
         return ZQ_OK;
@@ -464,13 +503,33 @@ int zq_moe_forward(zq_ctx *ctx, const zq_moe_experts *experts, const zq_weight *
         }
         for (const ChunkPlan &cp : plans) {
             if (cp.gated_n == 0) continue;
+            std::vector<const zq_weight *> wl_gu, wl_d;
+            std::vector<__half *> ol_gu, ol_d;
             for (size_t e = cp.e0; e < cp.e1; ++e) {
                 if (offsets[e + 1] == offsets[e]) continue;
                 const size_t z = e - cp.e0;
-                rc = launch_dequantize_f16(ctx, experts->gate[e], wg16 + z * I * H, err);
-                if (!rc) rc = launch_dequantize_f16(ctx, experts->up[e], wu16 + z * I * H, err);
-                if (!rc) rc = launch_dequantize_f16(ctx, experts->down[e], wd16 + z * H * I, err);
+                wl_gu.push_back(experts->gate[e]); ol_gu.push_back(wg16 + z * I * H);
+                wl_gu.push_back(experts->up[e]); ol_gu.push_back(wu16 + z * I * H);
+                wl_d.push_back(experts->down[e]); ol_d.push_back(wd16 + z * H * I);
+            }
+            // gate and up share shape but may differ in type from expert to expert only if the table was built so;
+            // the batched pass wants one type per launch, so fall back to single launches when they differ
+            bool uniform = true;
+            for (const zq_weight *w : wl_gu) uniform = uniform && w->type == wl_gu[0]->type;
+            for (const zq_weight *w : wl_d) uniform = uniform && w->type == wl_d[0]->type;
+            if (uniform) {
+                rc = launch_dequantize_f16_batch(ctx, wl_gu.data(), ol_gu.data(), wl_gu.size(), err);
+                if (!rc) rc = launch_dequantize_f16_batch(ctx, wl_d.data(), ol_d.data(), wl_d.size(), err);
                 if (rc) return rc;
+            } else {
+                for (size_t i = 0; i < wl_gu.size(); ++i) {
+                    rc = launch_dequantize_f16(ctx, wl_gu[i], ol_gu[i], err);
+                    if (rc) return rc;
+                }
+                for (size_t i = 0; i < wl_d.size(); ++i) {
+                    rc = launch_dequantize_f16(ctx, wl_d[i], ol_d[i], err);
+                    if (rc) return rc;
+                }
             }
             rc = launch_gemm_grouped(ctx, wg16, wu16, cp.e1 - cp.e0, I, H, xin, routes, d_items + cp.gated_first, cp.gated_n, act16, ZQ_F16, err);
             if (rc) return rc;
