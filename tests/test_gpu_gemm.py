@@ -16,6 +16,28 @@ pytestmark = pytest.mark.gpu
 BOUND = 2e-3
 
 
+@pytest.fixture(autouse=True, params=["fused", "operand_pass"])
+def gemm_variant(request):
+    """Q4_K runs on the kernel that dequantises inside the GEMM (default) and on the separate f16 operand pass + plain
+    GEMM (what the other formats use); both must produce the same bits, so every case runs on both."""
+    ctx().set_option("disable_fused_gemm", 1 if request.param == "operand_pass" else 0)
+    yield request.param
+    ctx().set_option("disable_fused_gemm", 0)
+
+
+def test_fused_and_operand_pass_kernels_agree_bit_for_bit(gemm_variant):
+    if gemm_variant != "fused":
+        pytest.skip("compares both variants in one go")
+    rows, cols, m = 300, 1024, 530
+    data = H.random_weight(H.Q4_K, rows, cols, seed=77)
+    x = dev(np.random.default_rng(78).standard_normal((m, cols)).astype(np.float32), torch.bfloat16)
+    w = ctx().prepare_weight(H.Q4_K, data, rows, cols)
+    a = host(ctx().linear(x, w, out_dtype=torch.float32)).copy()
+    ctx().set_option("disable_fused_gemm", 1)
+    b = host(ctx().linear(x, w, out_dtype=torch.float32))
+    assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
 @pytest.mark.parametrize("tensor_type", [H.Q4_K, H.Q4_0, H.Q8_0, H.IQ4_NL])
 @pytest.mark.parametrize("m,rows,cols", [(17, 200, 1024), (64, 128, 256), (300, 384, 2048), (512, 130, 512)])
 def test_prefill_linear_matches_cpu_matmul(tensor_type, m, rows, cols):

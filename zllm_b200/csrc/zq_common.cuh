@@ -242,6 +242,7 @@ struct zq_ctx {
     int enable_tcgen05_gemv = 0;
     int force_f16_gemv = 0;  // skip the integer-MMA decode kernel (tests of the f16 kernels)
     int disable_pdl = 0;     // launch decode kernels without programmatic dependent launch
+    int disable_fused_gemm = 0;    // Q4_K prefill: separate f16 operand pass + plain GEMM instead of the fused kernel
     int force_moe_per_expert = 0;  // MoE forward: always the host-grouped per-expert path (tests)
     std::atomic<uint64_t> launches{0};
     std::mutex mutex;
@@ -264,6 +265,7 @@ struct zq_weight {
 namespace zq {
 int ensure_workspace(zq_ctx *ctx, size_t bytes, zq_error *err);
 int ensure_xq(zq_ctx *ctx, size_t bytes, zq_error *err);
+int launch_gemm_fused_grouped(zq_ctx *ctx, const CUtensorMap *w_maps, const CUtensorMap *w2_maps, size_t rows, size_t k, const __half *x, size_t x_rows, const int4 *items, int n_items, void *y, int y_dtype, zq_error *err);
 int launch_gemm_f16(zq_ctx *ctx, const __half *w, size_t rows, size_t k, const __half *x, size_t m, void *y, int y_dtype, zq_error *err);
 int launch_to_f16(zq_ctx *ctx, const void *x, int x_dtype, __half *out, size_t n, zq_error *err);
 int launch_gemm_grouped(zq_ctx *ctx, const __half *w, const __half *w2, size_t mats, size_t rows, size_t k, const __half *x, size_t x_rows, const int4 *items, int n_items, void *y, int y_dtype, zq_error *err);

@@ -40,6 +40,8 @@ struct GemmParams {
     // activation operand shared by all matrices, outputs are rows of y with n_out columns.
     const int4 *items;
     int n_items;
+    // fused Q4_K kernel, grouped form: per-matrix tensor maps of the packed weights (device table indexed by z)
+    const CUtensorMap *w_maps, *w2_maps;
 };
 
 // ---- tcgen05 wrappers -------------------------------------------------------------------------------------------
@@ -285,6 +287,306 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
     if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Fused form for Q4_K: the packed weight tile is dequantised inside the kernel, straight into the swizzled shared-
+// memory operand the tensor core reads, so the weight crosses HBM once (0.56 bytes per weight instead of the
+// 0.56 + 2 + 2 of a separate f16 operand pass).  Same tile walk, MMA issue and epilogue as gemm_kernel; what differs is
+// the A side of the ring:
+//   warp 0        TMA: one packed box per 256 K columns (128 rows x 144 bytes) into a 2-deep ring, and the
+//                 activation k-blocks (256 tokens x 64 K, 128-byte swizzle) into the main ring
+//   warps 6..13   dequantisers: thread = (row, half of the 64-column k-block) = one 32-weight scale group; reads the
+//                 group's 16 packed bytes and the row's scales from the packed box, forms the reference's f32 value
+//                 d*sc*q - dmin*m (same operation order as the codec), rounds once to f16 and stores its four
+//                 16-byte chunks at their 128-byte-swizzle positions (chunk c of row r sits at c ^ (r & 7)), then
+//                 fence.proxy.async and one arrival per warp on the stage's a_full barrier
+//   warp 1        waits for a_full and b_full of a stage, issues the four K=16 MMAs, commits the stage's `empty`
+// The operand bits are exactly those the separate pass would have written, so results are identical.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int kFusedDqWarps = 8;
+constexpr int kFusedThreads = (6 + kFusedDqWarps) * 32;
+constexpr int kQ4kUnitBytes = 144;
+
+template <bool GATED> struct FusedSmem {
+    static constexpr int stages = GATED ? 2 : 3;
+    static constexpr int pstages = 2;
+    static constexpr int acc_bufs = GATED ? 1 : 2;
+    static constexpr int a_bytes = kBM * kBK * 2;
+    static constexpr int b_bytes = kBN * kBK * 2;
+    static constexpr int p_bytes = kBM * kQ4kUnitBytes;  // one packed box
+    static constexpr int stage_bytes = (GATED ? 2 : 1) * a_bytes + b_bytes;
+    static constexpr int pstage_bytes = (GATED ? 2 : 1) * p_bytes;
+    static constexpr int off_p = stages * stage_bytes;
+    static constexpr int off_bar = off_p + pstages * pstage_bytes;
+    static constexpr int total = off_bar + 512 + 1024;
+};
+
+// One scale group (32 weights) of one row of a packed Q4_K box -> 32 f16 in the swizzled A tile.
+// Integer -> float without the conversion unit: byte q under the exponent of 2^23 is the float 2^23 + q, and
+// subtracting 2^23 is exact, so d*sc*q - dmin*m comes out with the codec's own two roundings.
+__device__ __forceinline__ float nib_to_float(uint32_t masked, int byte) {
+    uint32_t r;
+    switch (byte) {
+    case 0: asm("prmt.b32 %0, %1, %2, 0x7540;" : "=r"(r) : "r"(masked), "r"(0x4B000000u)); break;
+    case 1: asm("prmt.b32 %0, %1, %2, 0x7541;" : "=r"(r) : "r"(masked), "r"(0x4B000000u)); break;
+    case 2: asm("prmt.b32 %0, %1, %2, 0x7542;" : "=r"(r) : "r"(masked), "r"(0x4B000000u)); break;
+    default: asm("prmt.b32 %0, %1, %2, 0x7543;" : "=r"(r) : "r"(masked), "r"(0x4B000000u)); break;
+    }
+    return __fadd_rn(__uint_as_float(r), -8388608.0f);
+}
+
+__device__ __forceinline__ void dequant_group_to_sw128(const uint8_t *unit, int pair, int half, uint8_t *a_tile, int row) {
+    const uint4 hdr = *reinterpret_cast<const uint4 *>(unit);
+    const __half2 dd = u32_as_h2(hdr.x);
+    const float d = __low2float(dd), dmin = __high2float(dd);
+    // 6-bit scale and min of group g = 2 pair + half (src/weight/codec/ggml.rs:471-473), from the 12 packed bytes
+    const int g = 2 * pair + half;
+    uint32_t sc, mn;
+    if (pair < 2) {
+        sc = (hdr.y >> (8 * g)) & 63u;
+        mn = (hdr.z >> (8 * g)) & 63u;
+    } else {
+        const int j = 8 * (g - 4);
+        sc = ((hdr.w >> j) & 0x0Fu) | (((hdr.y >> (j + 6)) & 3u) << 4);
+        mn = ((hdr.w >> (j + 4)) & 0x0Fu) | (((hdr.z >> (j + 6)) & 3u) << 4);
+    }
+    const float dsc = __fmul_rn(d, (float)sc), dm = __fmul_rn(dmin, (float)mn);
+    const uint4 q0 = *reinterpret_cast<const uint4 *>(unit + 16 + pair * 32), q1 = *reinterpret_cast<const uint4 *>(unit + 16 + pair * 32 + 16);
+    const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+    const int shift = half * 4;
+    uint8_t *row_base = a_tile + (row >> 3) * 1024 + (row & 7) * 128;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {  // chunk = 8 consecutive K = 2 packed words
+        uint32_t h[4];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const uint32_t m = (qw[2 * c + j] >> shift) & 0x0F0F0F0Fu;
+            const float v0 = __fsub_rn(__fmul_rn(dsc, nib_to_float(m, 0)), dm), v1 = __fsub_rn(__fmul_rn(dsc, nib_to_float(m, 1)), dm);
+            const float v2 = __fsub_rn(__fmul_rn(dsc, nib_to_float(m, 2)), dm), v3 = __fsub_rn(__fmul_rn(dsc, nib_to_float(m, 3)), dm);
+            h[2 * j] = h2_as_u32(__floats2half2_rn(v0, v1));
+            h[2 * j + 1] = h2_as_u32(__floats2half2_rn(v2, v3));
+        }
+        const int chunk = half * 4 + c;
+        *reinterpret_cast<uint4 *>(row_base + ((chunk ^ (row & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+    }
+}
+
+template <bool GATED>
+__global__ void __launch_bounds__(kFusedThreads, 1) gemm_q4k_fused_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2, const __grid_constant__ CUtensorMap map_x, const GemmParams p) {
+    using S = FusedSmem<GATED>;
+    constexpr int STAGES = S::stages;
+    constexpr int PST = S::pstages;
+    constexpr int ACC = S::acc_bufs;
+    constexpr uint32_t ACC_COLS = GATED ? 512 : 256;
+    constexpr uint32_t TMEM_COLS = 512;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t *a_full = reinterpret_cast<uint64_t *>(smem + S::off_bar);
+    uint64_t *b_full = a_full + STAGES;
+    uint64_t *empty = b_full + STAGES;
+    uint64_t *p_full = empty + STAGES;
+    uint64_t *p_empty = p_full + PST;
+    uint64_t *acc_full = p_empty + PST;
+    uint64_t *acc_empty = acc_full + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
+    __shared__ int s_abort;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_sb = p.k / kUnitWeights;  // Q4_K: K is a multiple of 256
+    const int n_row_tiles = (p.n_out + kBM - 1) / kBM, n_tok_tiles = (p.m + kBN - 1) / kBN;
+    const bool grouped = p.items != nullptr;
+    const int total_tiles = grouped ? p.n_items : n_row_tiles * n_tok_tiles;
+    auto tile_coords = [&](int tile, int &row0, int &tok0, int &tok_end, int &z) {
+        if (grouped) {
+            const int4 it = p.items[tile];
+            z = it.x;
+            row0 = it.y;
+            tok0 = it.z;
+            tok_end = it.w;
+            return;
+        }
+        z = 0;
+        tok_end = p.m;
+        const int per_group = kTokGroup * n_row_tiles;
+        const int group = tile / per_group, in_group = tile - group * per_group;
+        const int group_toks = (n_tok_tiles - group * kTokGroup) < kTokGroup ? (n_tok_tiles - group * kTokGroup) : kTokGroup;
+        row0 = (in_group / group_toks) * kBM;
+        tok0 = (group * kTokGroup + in_group % group_toks) * kBN;
+    };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&a_full[s], kFusedDqWarps);
+            mbar_init(&b_full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int s = 0; s < PST; ++s) {
+            mbar_init(&p_full[s], 1);
+            mbar_init(&p_empty[s], kFusedDqWarps);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 4);
+        }
+        fence_mbar_init();
+        s_abort = 0;
+        tma_prefetch_desc(&map_w);
+        tma_prefetch_desc(&map_x);
+        if (GATED) tma_prefetch_desc(&map_w2);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
+
+    if (warp == 0) {
+        // ------------------------------------------------ TMA producer: packed boxes and activation k-blocks
+        if (lane == 0) {
+            long long kg = 0, pq = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                int row0, tok0, tok_end, z;
+                tile_coords(tile, row0, tok0, tok_end, z);
+                const CUtensorMap *mw = grouped ? &p.w_maps[z] : &map_w;
+                const CUtensorMap *mw2 = grouped ? (GATED ? &p.w2_maps[z] : mw) : &map_w2;
+                for (int sb = 0; sb < n_sb && ok; ++sb, ++pq) {
+                    const int ps = (int)(pq % PST);
+                    if (pq >= PST) ok = wait_flag(&p_empty[ps], (uint32_t)((pq / PST) - 1) & 1, &s_abort, p.status, kStatusMmaTimeout);
+                    if (!ok) break;
+                    uint8_t *pst = smem + S::off_p + (size_t)ps * S::pstage_bytes;
+                    mbar_expect_tx(&p_full[ps], S::pstage_bytes);
+                    tma_load_2d(pst, mw, &p_full[ps], sb * (kQ4kUnitBytes / 4), row0);
+                    if (GATED) tma_load_2d(pst + S::p_bytes, mw2, &p_full[ps], sb * (kQ4kUnitBytes / 4), row0);
+                    for (int kb = 0; kb < kUnitWeights / kBK && ok; ++kb, ++kg) {
+                        const int s = (int)(kg % STAGES);
+                        if (kg >= STAGES) ok = wait_flag(&empty[s], (uint32_t)((kg / STAGES) - 1) & 1, &s_abort, p.status, kStatusMmaTimeout);
+                        if (!ok) break;
+                        uint8_t *st = smem + (size_t)s * S::stage_bytes;
+                        mbar_expect_tx(&b_full[s], S::b_bytes);
+                        tma_load_2d(st + (GATED ? 2 : 1) * S::a_bytes, &map_x, &b_full[s], sb * kUnitWeights + kb * kBK, tok0);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            long long kg = 0;
+            int iter = 0;
+            bool ok = true;
+            const int k_blocks = n_sb * (kUnitWeights / kBK);
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++iter) {
+                int row0, tok0, tok_end, z;
+                tile_coords(tile, row0, tok0, tok_end, z);
+                int n_eff = tok_end - tok0;
+                n_eff = n_eff >= kBN ? kBN : ((n_eff + 15) & ~15);
+                if (n_eff < 16) n_eff = 16;
+                const uint32_t idesc = (1u << 4) | ((uint32_t)(n_eff >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+                const int b = iter % ACC;
+                if (iter >= ACC) ok = wait_flag(&acc_empty[b], (uint32_t)((iter / ACC) - 1) & 1, &s_abort, p.status, kStatusMmaTimeout);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t acc_addr = tmem_base + (uint32_t)b * ACC_COLS;
+                for (int kb = 0; kb < k_blocks && ok; ++kb, ++kg) {
+                    const int s = (int)(kg % STAGES);
+                    ok = wait_flag(&b_full[s], (uint32_t)(kg / STAGES) & 1, &s_abort, p.status, kStatusTmaTimeout);
+                    if (ok) ok = wait_flag(&a_full[s], (uint32_t)(kg / STAGES) & 1, &s_abort, p.status, kStatusMmaTimeout);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t st = smem_u32(smem + (size_t)s * S::stage_bytes);
+                    const uint64_t da = make_sw128_desc(st);
+                    const uint64_t da2 = make_sw128_desc(st + S::a_bytes);
+                    const uint64_t db = make_sw128_desc(st + (GATED ? 2 : 1) * S::a_bytes);
+#pragma unroll
+                    for (int k = 0; k < kBK / 16; ++k) {
+                        const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
+                        umma_f16_ss(acc_addr, da + 2 * k, db + 2 * k, idesc, acc);
+                        if (GATED) umma_f16_ss(acc_addr + kBN, da2 + 2 * k, db + 2 * k, idesc, acc);
+                    }
+                    tc_commit(&empty[s]);
+                }
+                tc_commit(&acc_full[b]);
+            }
+        }
+    } else if (warp < 6) {
+        // ------------------------------------------------ epilogue: warp q of 4 owns TMEM lanes 32q..32q+31
+        const int q = warp & 3;
+        int iter = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++iter) {
+            int row0, tok0, tok_end, z;
+            tile_coords(tile, row0, tok0, tok_end, z);
+            const int b = iter % ACC;
+            const int row = row0 + q * 32 + lane;
+            const bool ok = wait_flag(&acc_full[b], (uint32_t)(iter / ACC) & 1, &s_abort, p.status, kStatusMmaTimeout);
+            tc_fence_after();
+            if (ok) {
+                const uint32_t lane_base = tmem_base + (uint32_t)b * ACC_COLS + ((uint32_t)(q * 32) << 16);
+                for (int c0 = 0; c0 < kBN; c0 += 16) {
+                    if (tok0 + c0 >= tok_end) break;  // warp-uniform
+                    uint32_t v[16], u[16];
+                    tmem_ld16(lane_base + c0, v);
+                    if (GATED) tmem_ld16(lane_base + kBN + c0, u);
+                    tmem_ld_wait();
+                    if (row < p.n_out) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int tok = tok0 + c0 + j;
+                            if (tok < tok_end) {
+                                float val = __uint_as_float(v[j]);
+                                if (GATED) {
+                                    const float up = __uint_as_float(u[j]);
+                                    val = (val / (1.0f + expf(-val))) * up;  // src/kernel/cpu/ggml_quant.rs:352
+                                }
+                                const size_t o = (size_t)tok * p.n_out + row;
+                                if (p.residual) val += load_as_f32(p.residual, p.y_dtype, o);
+                                store_from_f32(p.y, p.y_dtype, o, val);
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[b]);
+        }
+    } else {
+        // ------------------------------------------------ dequantisers: thread = (row, half of the k-block)
+        const int t = threadIdx.x - 6 * 32;
+        const int row = t & (kBM - 1), half = t >> 7;
+        long long kg = 0, pq = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (int sb = 0; sb < n_sb && ok; ++sb, ++pq) {
+                const int ps = (int)(pq % PST);
+                ok = wait_flag(&p_full[ps], (uint32_t)(pq / PST) & 1, &s_abort, p.status, kStatusTmaTimeout);
+                if (!ok) break;
+                const uint8_t *pst = smem + S::off_p + (size_t)ps * S::pstage_bytes;
+#pragma unroll
+                for (int kb = 0; kb < kUnitWeights / kBK; ++kb, ++kg) {
+                    if (!ok) break;
+                    const int s = (int)(kg % STAGES);
+                    if (kg >= STAGES) ok = wait_flag(&empty[s], (uint32_t)((kg / STAGES) - 1) & 1, &s_abort, p.status, kStatusMmaTimeout);
+                    if (!ok) break;
+                    uint8_t *st = smem + (size_t)s * S::stage_bytes;
+                    dequant_group_to_sw128(pst + (size_t)row * kQ4kUnitBytes, kb, half, st, row);
+                    if (GATED) dequant_group_to_sw128(pst + S::p_bytes + (size_t)row * kQ4kUnitBytes, kb, half, st + S::a_bytes, row);
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the tensor core
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&a_full[s]);
+                }
+                __syncwarp();
+                if (lane == 0 && ok) mbar_arrive(&p_empty[ps]);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
 // activations of any supported dtype -> f16 [m, k]
 __global__ void to_f16_kernel(const void *__restrict__ x, int x_dtype, __half *__restrict__ out, size_t n) {
     for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += (size_t)gridDim.x * blockDim.x * 4) {
@@ -312,6 +614,51 @@ int launch_gemm(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const vo
     const bool gated = w_up != nullptr;
     const size_t n = w->rows, k = w->cols;
     if (k % 8) return set_error(err, ZQ_ERR_SHAPE, "prefill GEMM needs columns aligned to 8, got %zu", k);
+    const bool fused = !ctx->disable_fused_gemm && w->type == ZQ_Q4_K && (!gated || w_up->type == ZQ_Q4_K) && k % kUnitWeights == 0;
+    if (fused) {
+        // Q4_K: dequantisation fused into the kernel; the workspace only holds the f16 copy of the activations
+        const size_t xb = (m * k * 2 + 255) & ~size_t(255);
+        const __half *xin = reinterpret_cast<const __half *>(x);
+        if (x_dtype != ZQ_F16) {
+            int rc = ensure_workspace(ctx, xb, err);
+            if (rc) return rc;
+            rc = launch_to_f16(ctx, x, x_dtype, reinterpret_cast<__half *>(ctx->workspace), m * k, err);
+            if (rc) return rc;
+            xin = reinterpret_cast<const __half *>(ctx->workspace);
+        }
+        CUtensorMap map_x;
+        int rc = make_f16_map(xin, m, k, kBN, &map_x, err);
+        if (rc) return rc;
+        GemmParams p;
+        p.y = y;
+        p.residual = residual;
+        p.status = ctx->status_dev;
+        p.y_dtype = y_dtype;
+        p.m = (int)m;
+        p.n_out = (int)n;
+        p.k = (int)k;
+        p.items = nullptr;
+        p.n_items = 0;
+        const size_t total_tiles = ((n + kBM - 1) / kBM) * ((m + kBN - 1) / kBN);
+        dim3 grid((unsigned)(total_tiles < (size_t)ctx->sm_count ? total_tiles : (size_t)ctx->sm_count));
+        static bool configured[2][64] = {};
+        if (gated) {
+            if (!configured[1][ctx->device & 63]) {
+                ZQ_CUDA_CHECK(cudaFuncSetAttribute(gemm_q4k_fused_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, FusedSmem<true>::total), err);
+                configured[1][ctx->device & 63] = true;
+            }
+            gemm_q4k_fused_kernel<true><<<grid, kFusedThreads, FusedSmem<true>::total, ctx->stream>>>(w->qmv_map, w_up->qmv_map, map_x, p);
+        } else {
+            if (!configured[0][ctx->device & 63]) {
+                ZQ_CUDA_CHECK(cudaFuncSetAttribute(gemm_q4k_fused_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, FusedSmem<false>::total), err);
+                configured[0][ctx->device & 63] = true;
+            }
+            gemm_q4k_fused_kernel<false><<<grid, kFusedThreads, FusedSmem<false>::total, ctx->stream>>>(w->qmv_map, w->qmv_map, map_x, p);
+        }
+        ctx->launches++;
+        ZQ_CUDA_CHECK(cudaGetLastError(), err);
+        return ZQ_OK;
+    }
     const size_t w_bytes = (n * k * 2 + 255) & ~size_t(255);
     const size_t x_bytes = (m * k * 2 + 255) & ~size_t(255);
     int rc = ensure_workspace(ctx, (gated ? 2 : 1) * w_bytes + x_bytes, err);
@@ -349,6 +696,7 @@ int launch_gemm(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const vo
     p.k = (int)k;
     p.items = nullptr;
     p.n_items = 0;
+    p.w_maps = p.w2_maps = nullptr;
     const size_t total_tiles = ((n + kBM - 1) / kBM) * ((m + kBN - 1) / kBN);
     dim3 grid((unsigned)(total_tiles < (size_t)ctx->sm_count ? total_tiles : (size_t)ctx->sm_count));
     static bool configured[2][64] = {};
@@ -415,6 +763,7 @@ int launch_gemm_grouped(zq_ctx *ctx, const __half *w, const __half *w2, size_t m
     p.k = (int)k;
     p.items = items;
     p.n_items = n_items;
+    p.w_maps = p.w2_maps = nullptr;
     dim3 grid((unsigned)(n_items < ctx->sm_count ? n_items : ctx->sm_count));
     static bool configured[2][64] = {};
     if (gated) {
@@ -452,6 +801,7 @@ int launch_gemm_f16(zq_ctx *ctx, const __half *w, size_t rows, size_t k, const _
     p.k = (int)k;
     p.items = nullptr;
     p.n_items = 0;
+    p.w_maps = p.w2_maps = nullptr;
     const size_t total_tiles = ((rows + kBM - 1) / kBM) * ((m + kBN - 1) / kBN);
     dim3 grid((unsigned)(total_tiles < (size_t)ctx->sm_count ? total_tiles : (size_t)ctx->sm_count));
     static bool configured[64] = {};
@@ -460,6 +810,47 @@ int launch_gemm_f16(zq_ctx *ctx, const __half *w, size_t rows, size_t k, const _
         configured[ctx->device & 63] = true;
     }
     gemm_kernel<false><<<grid, kGemmThreads, GemmSmem<false>::total, ctx->stream>>>(map_w, map_w, map_x, p);
+    ctx->launches++;
+    ZQ_CUDA_CHECK(cudaGetLastError(), err);
+    return ZQ_OK;
+}
+
+// Grouped fused form (MoE prefill, Q4_K experts): no f16 copy of the weights at all.  `w_maps` / `w2_maps`: device
+// tables of the experts' packed-weight tensor maps (one unit x 128 rows boxes), indexed by the work items' z.
+int launch_gemm_fused_grouped(zq_ctx *ctx, const CUtensorMap *w_maps, const CUtensorMap *w2_maps, size_t rows, size_t k, const __half *x, size_t x_rows, const int4 *items, int n_items, void *y, int y_dtype, zq_error *err) {
+    if (n_items <= 0) return ZQ_OK;
+    if (k % kUnitWeights) return set_error(err, ZQ_ERR_SHAPE, "fused Q4_K GEMM needs columns aligned to 256, got %zu", k);
+    const bool gated = w2_maps != nullptr;
+    CUtensorMap map_x;
+    int rc = make_f16_map(x, x_rows, k, kBN, &map_x, err);
+    if (rc) return rc;
+    GemmParams p;
+    p.y = y;
+    p.residual = nullptr;
+    p.status = ctx->status_dev;
+    p.y_dtype = y_dtype;
+    p.m = (int)x_rows;
+    p.n_out = (int)rows;
+    p.k = (int)k;
+    p.items = items;
+    p.n_items = n_items;
+    p.w_maps = w_maps;
+    p.w2_maps = w2_maps;
+    dim3 grid((unsigned)(n_items < ctx->sm_count ? n_items : ctx->sm_count));
+    static bool configured[2][64] = {};
+    if (gated) {
+        if (!configured[1][ctx->device & 63]) {
+            ZQ_CUDA_CHECK(cudaFuncSetAttribute(gemm_q4k_fused_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, FusedSmem<true>::total), err);
+            configured[1][ctx->device & 63] = true;
+        }
+        gemm_q4k_fused_kernel<true><<<grid, kFusedThreads, FusedSmem<true>::total, ctx->stream>>>(map_x, map_x, map_x, p);
+    } else {
+        if (!configured[0][ctx->device & 63]) {
+            ZQ_CUDA_CHECK(cudaFuncSetAttribute(gemm_q4k_fused_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, FusedSmem<false>::total), err);
+            configured[0][ctx->device & 63] = true;
+        }
+        gemm_q4k_fused_kernel<false><<<grid, kFusedThreads, FusedSmem<false>::total, ctx->stream>>>(map_x, map_x, map_x, p);
+    }
     ctx->launches++;
     ZQ_CUDA_CHECK(cudaGetLastError(), err);
     return ZQ_OK;

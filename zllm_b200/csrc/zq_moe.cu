@@ -320,19 +320,28 @@ int zq_moe_experts_create(zq_ctx *ctx, const zq_weight *const *gate, const zq_we
     t->down_type = down[0]->type;
     for (size_t e = 0; e < num_experts; ++e) uniform = uniform && gate[e]->type == t->gate_type && down[e]->type == t->down_type;
     if (uniform) {
-        std::vector<CUtensorMap> hg(num_experts), hu(num_experts), hd(num_experts);
+        std::vector<CUtensorMap> hg(num_experts), hu(num_experts), hd(num_experts), qg(num_experts), qu(num_experts), qd(num_experts);
         for (size_t e = 0; e < num_experts; ++e) {
             hg[e] = gate[e]->gemv_map_half;
             hu[e] = up[e]->gemv_map_half;
             hd[e] = down[e]->gemv_map;
+            qg[e] = gate[e]->qmv_map;
+            qu[e] = up[e]->qmv_map;
+            qd[e] = down[e]->qmv_map;
         }
         const size_t bytes = num_experts * sizeof(CUtensorMap);
         cudaError_t ce = cudaMalloc(&t->d_gate_maps, bytes);
         if (ce == cudaSuccess) ce = cudaMalloc(&t->d_up_maps, bytes);
         if (ce == cudaSuccess) ce = cudaMalloc(&t->d_down_maps, bytes);
+        if (ce == cudaSuccess) ce = cudaMalloc(&t->d_gate_qmaps, bytes);
+        if (ce == cudaSuccess) ce = cudaMalloc(&t->d_up_qmaps, bytes);
+        if (ce == cudaSuccess) ce = cudaMalloc(&t->d_down_qmaps, bytes);
         if (ce == cudaSuccess) ce = cudaMemcpy(t->d_gate_maps, hg.data(), bytes, cudaMemcpyHostToDevice);
         if (ce == cudaSuccess) ce = cudaMemcpy(t->d_up_maps, hu.data(), bytes, cudaMemcpyHostToDevice);
         if (ce == cudaSuccess) ce = cudaMemcpy(t->d_down_maps, hd.data(), bytes, cudaMemcpyHostToDevice);
+        if (ce == cudaSuccess) ce = cudaMemcpy(t->d_gate_qmaps, qg.data(), bytes, cudaMemcpyHostToDevice);
+        if (ce == cudaSuccess) ce = cudaMemcpy(t->d_up_qmaps, qu.data(), bytes, cudaMemcpyHostToDevice);
+        if (ce == cudaSuccess) ce = cudaMemcpy(t->d_down_qmaps, qd.data(), bytes, cudaMemcpyHostToDevice);
         if (ce != cudaSuccess) {
             zq_moe_experts_destroy(t);
             return set_error(err, ZQ_ERR_CUDA, "zq_moe_experts_create: tensor-map table: %s", cudaGetErrorString(ce));
@@ -347,6 +356,9 @@ void zq_moe_experts_destroy(zq_moe_experts *experts) {
     if (experts->d_gate_maps) cudaFree(experts->d_gate_maps);
     if (experts->d_up_maps) cudaFree(experts->d_up_maps);
     if (experts->d_down_maps) cudaFree(experts->d_down_maps);
+    if (experts->d_gate_qmaps) cudaFree(experts->d_gate_qmaps);
+    if (experts->d_up_qmaps) cudaFree(experts->d_up_qmaps);
+    if (experts->d_down_qmaps) cudaFree(experts->d_down_qmaps);
     delete experts;
 }
 
@@ -450,7 +462,46 @@ int zq_moe_forward(zq_ctx *ctx, const zq_moe_experts *experts, const zq_weight *
 
     // ---- experts, ascending id (src/moe/routing.rs:180-213: gather rows, expert batch, weighted scatter)
     const bool grouped_gemm = !ctx->force_moe_per_expert && routes >= 32 * E && H % 8 == 0 && I % 8 == 0;
-    if (grouped_gemm) {
+    const bool fused_gemm = grouped_gemm && !ctx->disable_fused_gemm && experts->d_gate_qmaps && experts->gate_type == ZQ_Q4_K && experts->down_type == ZQ_Q4_K && H % kUnitWeights == 0 && I % kUnitWeights == 0;
+    if (fused_gemm) {
+        // Prefill, Q4_K experts: two launches for the whole layer.  The fused tensor-core GEMM dequantises the packed
+        // tiles of whichever expert a work item names (per-expert tensor maps in a device table), so there is no f16
+        // copy of any expert.  Work list: one item per (expert, 256-token tile, 128-row tile); tokens are the gathered
+        // slot rows, so outputs land in slot order as the combine expects.
+        auto al2 = [](size_t v) { return (v + 1023) & ~size_t(1023); };
+        std::vector<int4> items;
+        const int rt_i = (int)((I + 127) / 128), rt_h = (int)((H + 127) / 128);
+        for (size_t e = 0; e < E; ++e) {
+            const int first = (int)offsets[e], end = (int)offsets[e + 1];
+            for (int t0 = first; t0 < end; t0 += 256)
+                for (int rt = 0; rt < rt_i; ++rt) items.push_back(make_int4((int)e, rt * 128, t0, end));
+        }
+        const int n_gated = (int)items.size();
+        for (size_t e = 0; e < E; ++e) {
+            const int first = (int)offsets[e], end = (int)offsets[e + 1];
+            for (int t0 = first; t0 < end; t0 += 256)
+                for (int rt = 0; rt < rt_h; ++rt) items.push_back(make_int4((int)e, rt * 128, t0, end));
+        }
+        const int n_down = (int)items.size() - n_gated;
+        const size_t x16_bytes = al2(routes * H * sizeof(__half)), act16_bytes = al2(routes * I * sizeof(__half)), items_bytes = al2(items.size() * sizeof(int4));
+        rc = ensure_workspace(ctx, x16_bytes + act16_bytes + items_bytes, err);
+        if (rc) return rc;
+        uint8_t *wsb = reinterpret_cast<uint8_t *>(ctx->workspace);
+        __half *x16 = reinterpret_cast<__half *>(wsb), *act16 = reinterpret_cast<__half *>(wsb + x16_bytes);
+        int4 *d_items = reinterpret_cast<int4 *>(wsb + x16_bytes + act16_bytes);
+        ZQ_CUDA_CHECK(cudaMemcpyAsync(d_items, items.data(), items.size() * sizeof(int4), cudaMemcpyHostToDevice, ctx->stream), err);
+        ZQ_CUDA_CHECK(cudaStreamSynchronize(ctx->stream), err);  // the host vector goes out of scope at return
+        const __half *xin = reinterpret_cast<const __half *>(d_xs);
+        if (x_dtype != ZQ_F16) {
+            rc = launch_to_f16(ctx, d_xs, x_dtype, x16, routes * H, err);
+            if (rc) return rc;
+            xin = x16;
+        }
+        rc = launch_gemm_fused_grouped(ctx, experts->d_gate_qmaps, experts->d_up_qmaps, I, H, xin, routes, d_items, n_gated, act16, ZQ_F16, err);
+        if (rc) return rc;
+        rc = launch_gemm_fused_grouped(ctx, experts->d_down_qmaps, nullptr, H, I, act16, routes, d_items + n_gated, n_down, d_out, ZQ_F32, err);
+        if (rc) return rc;
+    } else if (grouped_gemm) {
         // Prefill: one grouped tensor-core GEMM per projection and chunk of experts instead of two launches per
         // expert (an expert's own GEMM has 16-56 tiles for 148 SMs).  The chunk's packed weights are dequantised to
         // f16 stacks [chunk][rows][K] in the workspace; the work list holds one item per (expert, token tile, row

@@ -11,6 +11,8 @@ struct zq_moe_experts {
     // grouped decode path: the experts' tensor maps as device arrays (gate/up: 64-row boxes, down: 128-row boxes);
     // null when the experts do not all share one gate/up type and one down type
     CUtensorMap *d_gate_maps = nullptr, *d_up_maps = nullptr, *d_down_maps = nullptr;
+    // fused prefill GEMM: one-unit boxes of the same tensors
+    CUtensorMap *d_gate_qmaps = nullptr, *d_up_qmaps = nullptr, *d_down_qmaps = nullptr;
     uint32_t gate_type = 0, down_type = 0;
 };
 
