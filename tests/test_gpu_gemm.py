@@ -21,8 +21,10 @@ def gemm_variant(request):
     """Q4_K runs on the kernel that dequantises inside the GEMM (default) and on the separate f16 operand pass + plain
     GEMM (what the other formats use); both must produce the same bits, so every case runs on both."""
     ctx().set_option("disable_fused_gemm", 1 if request.param == "operand_pass" else 0)
+    ctx().set_option("force_fused_gemm", 1 if request.param == "fused" else 0)
     yield request.param
     ctx().set_option("disable_fused_gemm", 0)
+    ctx().set_option("force_fused_gemm", 0)
 
 
 def test_fused_and_operand_pass_kernels_agree_bit_for_bit(gemm_variant):
@@ -33,6 +35,7 @@ def test_fused_and_operand_pass_kernels_agree_bit_for_bit(gemm_variant):
     x = dev(np.random.default_rng(78).standard_normal((m, cols)).astype(np.float32), torch.bfloat16)
     w = ctx().prepare_weight(H.Q4_K, data, rows, cols)
     a = host(ctx().linear(x, w, out_dtype=torch.float32)).copy()
+    ctx().set_option("force_fused_gemm", 0)
     ctx().set_option("disable_fused_gemm", 1)
     b = host(ctx().linear(x, w, out_dtype=torch.float32))
     assert np.array_equal(a.view(np.uint32), b.view(np.uint32))

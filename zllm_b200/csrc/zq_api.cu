@@ -196,6 +196,10 @@ int zq_ctx_set_option(zq_ctx *ctx, const char *key, int value, zq_error *err) {
         ctx->force_staged_gemv = value;
         return ZQ_OK;
     }
+    if (!strcmp(key, "force_fused_gemm")) {
+        ctx->force_fused_gemm = value;
+        return ZQ_OK;
+    }
     if (!strcmp(key, "disable_fused_gemm")) {
         ctx->disable_fused_gemm = value;
         return ZQ_OK;

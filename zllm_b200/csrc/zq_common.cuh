@@ -242,6 +242,7 @@ struct zq_ctx {
     int enable_tcgen05_gemv = 0;
     int force_f16_gemv = 0;  // skip the integer-MMA decode kernel (tests of the f16 kernels)
     int disable_pdl = 0;     // launch decode kernels without programmatic dependent launch
+    int force_fused_gemm = 0;      // Q4_K prefill: the fused kernel for every token count (tests)
     int disable_fused_gemm = 0;    // Q4_K prefill: separate f16 operand pass + plain GEMM instead of the fused kernel
     int force_moe_per_expert = 0;  // MoE forward: always the host-grouped per-expert path (tests)
     std::atomic<uint64_t> launches{0};

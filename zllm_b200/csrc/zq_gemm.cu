@@ -96,6 +96,20 @@ __device__ __forceinline__ bool wait_flag(uint64_t *bar, uint32_t parity, volati
     return false;
 }
 
+// Same, for roles that share a scheduler with working warps: a failed poll is followed by a short sleep, so that
+// the waiting warp does not take issue slots from the warps that are dequantising (a bare poll loop re-issues every
+// few tens of nanoseconds).
+__device__ __forceinline__ bool wait_flag_backoff(uint64_t *bar, uint32_t parity, volatile int *abort_flag, uint32_t *status, uint32_t code, unsigned sleep_ns) {
+    for (uint32_t i = 0; i < (1u << 22); ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        __nanosleep(sleep_ns);
+    }
+    *abort_flag = 1;
+    atomicMax(status, code);
+    return false;
+}
+
 template <bool GATED> struct GemmSmem {
     static constexpr int stages = GATED ? 3 : 4;
     static constexpr int acc_bufs = GATED ? 1 : 2;  // 256-column accumulators that fit the 512 TMEM columns
@@ -520,7 +534,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) gemm_q4k_fused_kernel(const 
             tile_coords(tile, row0, tok0, tok_end, z);
             const int b = iter % ACC;
             const int row = row0 + q * 32 + lane;
-            const bool ok = wait_flag(&acc_full[b], (uint32_t)(iter / ACC) & 1, &s_abort, p.status, kStatusMmaTimeout);
+            const bool ok = wait_flag_backoff(&acc_full[b], (uint32_t)(iter / ACC) & 1, &s_abort, p.status, kStatusMmaTimeout, 400);
             tc_fence_after();
             if (ok) {
                 const uint32_t lane_base = tmem_base + (uint32_t)b * ACC_COLS + ((uint32_t)(q * 32) << 16);
@@ -561,14 +575,14 @@ __global__ void __launch_bounds__(kFusedThreads, 1) gemm_q4k_fused_kernel(const 
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
             for (int sb = 0; sb < n_sb && ok; ++sb, ++pq) {
                 const int ps = (int)(pq % PST);
-                ok = wait_flag(&p_full[ps], (uint32_t)(pq / PST) & 1, &s_abort, p.status, kStatusTmaTimeout);
+                ok = wait_flag_backoff(&p_full[ps], (uint32_t)(pq / PST) & 1, &s_abort, p.status, kStatusTmaTimeout, 60);
                 if (!ok) break;
                 const uint8_t *pst = smem + S::off_p + (size_t)ps * S::pstage_bytes;
 #pragma unroll
                 for (int kb = 0; kb < kUnitWeights / kBK; ++kb, ++kg) {
                     if (!ok) break;
                     const int s = (int)(kg % STAGES);
-                    if (kg >= STAGES) ok = wait_flag(&empty[s], (uint32_t)((kg / STAGES) - 1) & 1, &s_abort, p.status, kStatusMmaTimeout);
+                    if (kg >= STAGES) ok = wait_flag_backoff(&empty[s], (uint32_t)((kg / STAGES) - 1) & 1, &s_abort, p.status, kStatusMmaTimeout, 60);
                     if (!ok) break;
                     uint8_t *st = smem + (size_t)s * S::stage_bytes;
                     dequant_group_to_sw128(pst + (size_t)row * kQ4kUnitBytes, kb, half, st, row);
@@ -614,7 +628,10 @@ int launch_gemm(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const vo
     const bool gated = w_up != nullptr;
     const size_t n = w->rows, k = w->cols;
     if (k % 8) return set_error(err, ZQ_ERR_SHAPE, "prefill GEMM needs columns aligned to 8, got %zu", k);
-    const bool fused = !ctx->disable_fused_gemm && w->type == ZQ_Q4_K && (!gated || w_up->type == ZQ_Q4_K) && k % kUnitWeights == 0;
+    // The fused kernel saves the operand pass (one read of the packed weight, one write and one read of its f16 form),
+    // which dominates for few tokens; with many tokens the pass is amortised and the plain kernel, whose shared-memory
+    // traffic per k-block is lower (no operand stores by threads), runs the tensor core at a higher duty.
+    const bool fused = !ctx->disable_fused_gemm && (ctx->force_fused_gemm || m <= 384) && w->type == ZQ_Q4_K && (!gated || w_up->type == ZQ_Q4_K) && k % kUnitWeights == 0;
     if (fused) {
         // Q4_K: dequantisation fused into the kernel; the workspace only holds the f16 copy of the activations
         const size_t xb = (m * k * 2 + 255) & ~size_t(255);
