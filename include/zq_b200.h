@@ -103,6 +103,14 @@ int zq_linear_noalloc(zq_ctx *ctx, const zq_weight *w, const void *dev_x, int x_
  * backend that keeps activations on the host between operators calls (CpuTensor in, CpuTensor out). */
 int zq_linear_host(zq_ctx *ctx, const zq_weight *w, const void *host_x, int x_dtype, size_t m, void *host_y, int y_dtype, zq_error *err);
 
+/* Backend::begin_batch / finish_batch (src/backend/mod.rs:307-323; the reference's Vulkan backend defers its command
+ * submission the same way, src/backend/vulkan/mod.rs:194-215).  Between the two calls zq_linear_host only ENQUEUES its
+ * copy in, its kernels and its copy out; zq_batch_finish waits once for everything enqueued and then fills the
+ * callers' output buffers, which must stay valid and must not be read until then.  Input buffers may be reused as soon
+ * as their zq_linear_host call returns. */
+int zq_batch_begin(zq_ctx *ctx, zq_error *err);
+int zq_batch_finish(zq_ctx *ctx, zq_error *err);
+
 /* ---- MoE: kernel::cuda::routing (src/kernel/cuda/routing.rs:167-210) and the expert entry points
  * (src/kernel/cuda/linear.rs:1735-1819; src/backend/cuda/expert.rs:572-918). ---- */
 /* moe_route_softmax_topk_device_f32: logits = x router^T (+ bias), softmax top-k with ties to the lower expert id.

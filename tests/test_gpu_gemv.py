@@ -214,3 +214,22 @@ def test_linear_host_copies_in_and_out():
     y = np.zeros((2, rows), dtype=np.float32)
     ctx().linear_host(x, w, y)
     _check(y, orc.linear(H.Q8_0, data, rows, cols, x))
+
+
+def test_batch_bracket_defers_host_results_to_finish():
+    """Backend::begin_batch / finish_batch (src/backend/mod.rs:307-323): host-buffer calls inside the bracket are only
+    enqueued; after finish_batch every output buffer holds its result."""
+    rows, cols = 300, 768
+    datas = [H.random_weight(t, rows, cols, seed=95 + i) for i, t in enumerate((H.Q8_0, H.Q4_K, H.Q4_0))]
+    ws = [ctx().prepare_weight(t, d, rows, cols) for t, d in zip((H.Q8_0, H.Q4_K, H.Q4_0), datas)]
+    xs = [np.random.default_rng(96 + i).standard_normal((m, cols)).astype(np.float32) for i, m in enumerate((1, 3, 9))]
+    ys = [np.zeros((x.shape[0], rows), dtype=np.float32) for x in xs]
+    ctx().begin_batch()
+    for x, w, y in zip(xs, ws, ys):
+        ctx().linear_host(x, w, y)
+    ctx().finish_batch()
+    for t, d, x, y in zip((H.Q8_0, H.Q4_K, H.Q4_0), datas, xs, ys):
+        _check(y, orc.linear(t, d, rows, cols, x), tight=1e-3 if x.shape[0] > 8 else TIGHT)
+    from zllm_b200 import ffi
+    with pytest.raises(ffi.ZqFailure):
+        ctx().finish_batch()  # no bracket open

@@ -201,6 +201,14 @@ class B200Context:
     def gated_mlp_add_residual(self, x, gate, up, down, residual, out_dtype=None):
         return self.gated_mlp(x, gate, up, down, out_dtype=out_dtype or residual.dtype, residual=residual)
 
+    def begin_batch(self):
+        """Backend::begin_batch: host-buffer calls until finish_batch are enqueued, not waited for."""
+        ffi.call("zq_batch_begin", self.handle)
+
+    def finish_batch(self):
+        """Backend::finish_batch: waits once for everything enqueued since begin_batch and fills the output buffers."""
+        ffi.call("zq_batch_finish", self.handle)
+
     def linear_host(self, x_host, w: Weight, y_host):
         """Host-buffer linear: numpy arrays in and out, copies inside the call."""
         import numpy as np

@@ -159,6 +159,10 @@ void zq_ctx_destroy(zq_ctx *ctx) {
     if (ctx->status_host) cudaFreeHost(ctx->status_host);
     if (ctx->pinned) cudaFreeHost(ctx->pinned);
     if (ctx->host_io_dev) cudaFree(ctx->host_io_dev);
+    for (auto &c : ctx->io_chunks) {
+        cudaFreeHost(c.pinned);
+        cudaFree(c.dev);
+    }
     if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
     delete ctx;
 }
@@ -369,6 +373,66 @@ int zq_linear_noalloc(zq_ctx *ctx, const zq_weight *w, const void *dev_x, int x_
     return launch_gemv_noalloc(ctx, w, dev_x, x_dtype, m, dev_y, y_dtype, err);
 }
 
+// True when a host pointer is page-locked memory the GPU can copy from / to directly (cudaHostAlloc,
+// cudaHostRegister, a pinned tensor of the host framework): such buffers need no staging copy.
+static bool is_pinned_host(const void *p) {
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+        cudaGetLastError();  // older runtimes report pageable memory as an error: not pinned, and not an error of ours
+        return false;
+    }
+    return a.type == cudaMemoryTypeHost;
+}
+
+// Staging memory of a batch bracket: a (pinned, device) pair of `bytes` bytes, 256-byte aligned, valid until the
+// bracket's finish.  Chunks are kept for the next bracket; a new one is allocated only when the existing ones are full.
+static int batch_io_alloc(zq_ctx *ctx, size_t bytes, uint8_t **pinned, uint8_t **dev, zq_error *err) {
+    bytes = (bytes + 255) & ~size_t(255);
+    for (auto &c : ctx->io_chunks) {
+        if (c.bytes - c.used >= bytes) {
+            *pinned = c.pinned + c.used;
+            *dev = c.dev + c.used;
+            c.used += bytes;
+            return ZQ_OK;
+        }
+    }
+    zq_ctx::IoChunk c;
+    c.bytes = bytes > (size_t(8) << 20) ? bytes : (size_t(8) << 20);
+    c.used = bytes;
+    void *p = nullptr, *d = nullptr;
+    ZQ_CUDA_CHECK(cudaHostAlloc(&p, c.bytes, cudaHostAllocDefault), err);
+    cudaError_t e = cudaMalloc(&d, c.bytes);
+    if (e != cudaSuccess) {
+        cudaFreeHost(p);
+        return set_error(err, ZQ_ERR_CUDA, "batch staging: cudaMalloc of %zu bytes failed: %s", c.bytes, cudaGetErrorString(e));
+    }
+    c.pinned = reinterpret_cast<uint8_t *>(p);
+    c.dev = reinterpret_cast<uint8_t *>(d);
+    ctx->io_chunks.push_back(c);
+    *pinned = c.pinned;
+    *dev = c.dev;
+    return ZQ_OK;
+}
+
+int zq_batch_begin(zq_ctx *ctx, zq_error *err) {
+    if (!ctx) return set_error(err, ZQ_ERR_ARG, "zq_batch_begin: null context");
+    if (ctx->batch_active) return set_error(err, ZQ_ERR_ARG, "zq_batch_begin: a batch is already open");
+    ctx->batch_active = true;
+    return ZQ_OK;
+}
+
+int zq_batch_finish(zq_ctx *ctx, zq_error *err) {
+    if (!ctx) return set_error(err, ZQ_ERR_ARG, "zq_batch_finish: null context");
+    if (!ctx->batch_active) return set_error(err, ZQ_ERR_ARG, "zq_batch_finish: no batch is open");
+    ctx->batch_active = false;
+    int rc = zq_ctx_sync(ctx, err);
+    if (!rc)
+        for (const auto &o : ctx->pending_out) memcpy(o.host, o.pinned, o.bytes);
+    ctx->pending_out.clear();
+    for (auto &c : ctx->io_chunks) c.used = 0;
+    return rc;
+}
+
 int zq_linear_host(zq_ctx *ctx, const zq_weight *w, const void *host_x, int x_dtype, size_t m, void *host_y, int y_dtype, zq_error *err) {
     if (!ctx || !w || !host_x || !host_y) return set_error(err, ZQ_ERR_ARG, "zq_linear_host: null argument");
     int rc = check_dtype(x_dtype, "linear input", err);
@@ -376,6 +440,25 @@ int zq_linear_host(zq_ctx *ctx, const zq_weight *w, const void *host_x, int x_dt
     if (rc) return rc;
     size_t xb = m * w->cols * dtype_size(x_dtype), yb = m * w->rows * dtype_size(y_dtype);
     size_t xb_al = (xb + 255) & ~size_t(255);
+    const bool x_pinned = is_pinned_host(host_x), y_pinned = is_pinned_host(host_y);
+    if (ctx->batch_active) {
+        // inside a bracket: copy in, run and copy out are only enqueued; the bracket's finish waits once for all of them
+        // and hands the results to the callers' buffers.  Page-locked caller buffers are copied from / to directly.
+        uint8_t *px, *dx;
+        rc = batch_io_alloc(ctx, xb_al + yb, &px, &dx, err);
+        if (rc) return rc;
+        const void *src = host_x;
+        if (!x_pinned) {
+            memcpy(px, host_x, xb);
+            src = px;
+        }
+        ZQ_CUDA_CHECK(cudaMemcpyAsync(dx, src, xb, cudaMemcpyHostToDevice, ctx->stream), err);
+        rc = zq_linear(ctx, w, dx, x_dtype, m, dx + xb_al, y_dtype, nullptr, err);
+        if (rc) return rc;
+        ZQ_CUDA_CHECK(cudaMemcpyAsync(y_pinned ? host_y : px + xb_al, dx + xb_al, yb, cudaMemcpyDeviceToHost, ctx->stream), err);
+        if (!y_pinned) ctx->pending_out.push_back({host_y, px + xb_al, yb});
+        return ZQ_OK;
+    }
     if (ctx->host_io_bytes < xb_al + yb) {
         ZQ_CUDA_CHECK(cudaStreamSynchronize(ctx->stream), err);
         if (ctx->host_io_dev) cudaFree(ctx->host_io_dev);
@@ -389,14 +472,18 @@ int zq_linear_host(zq_ctx *ctx, const zq_weight *w, const void *host_x, int x_dt
     }
     uint8_t *dx = reinterpret_cast<uint8_t *>(ctx->host_io_dev), *dy = dx + xb_al;
     uint8_t *px = reinterpret_cast<uint8_t *>(ctx->pinned), *py = px + xb_al;
-    memcpy(px, host_x, xb);
-    ZQ_CUDA_CHECK(cudaMemcpyAsync(dx, px, xb, cudaMemcpyHostToDevice, ctx->stream), err);
+    const void *src = host_x;
+    if (!x_pinned) {
+        memcpy(px, host_x, xb);
+        src = px;
+    }
+    ZQ_CUDA_CHECK(cudaMemcpyAsync(dx, src, xb, cudaMemcpyHostToDevice, ctx->stream), err);
     rc = zq_linear(ctx, w, dx, x_dtype, m, dy, y_dtype, nullptr, err);
     if (rc) return rc;
-    ZQ_CUDA_CHECK(cudaMemcpyAsync(py, dy, yb, cudaMemcpyDeviceToHost, ctx->stream), err);
+    ZQ_CUDA_CHECK(cudaMemcpyAsync(y_pinned ? host_y : py, dy, yb, cudaMemcpyDeviceToHost, ctx->stream), err);
     rc = zq_ctx_sync(ctx, err);
     if (rc) return rc;
-    memcpy(host_y, py, yb);
+    if (!y_pinned) memcpy(host_y, py, yb);
     return ZQ_OK;
 }
 

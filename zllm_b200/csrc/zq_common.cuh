@@ -234,6 +234,13 @@ struct zq_ctx {
     size_t pinned_bytes = 0;
     void *host_io_dev = nullptr;
     size_t host_io_bytes = 0;
+    // Batch bracket (zq_batch_begin / zq_batch_finish): host-buffer calls inside it stage through these chunks and
+    // defer their copy-out to the finish.
+    struct IoChunk { uint8_t *pinned; uint8_t *dev; size_t bytes, used; };
+    struct PendingOut { void *host; const uint8_t *pinned; size_t bytes; };
+    std::vector<IoChunk> io_chunks;
+    std::vector<PendingOut> pending_out;
+    bool batch_active = false;
     // Diagnostics: 1 = always use the per-item activation staging GEMV (the variant for activations too large to
     // stay resident in shared memory), so that tests can cover it at small sizes.
     int force_staged_gemv = 0;

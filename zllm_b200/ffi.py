@@ -55,6 +55,8 @@ PROTOTYPES = {
     "zq_gated_mlp": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _sz, _vp, _i, _vp, _err]),
     "zq_linear_noalloc": (_i, [_vp, _vp, _vp, _i, _sz, _vp, _i, _err]),
     "zq_linear_host": (_i, [_vp, _vp, _vp, _i, _sz, _vp, _i, _err]),
+    "zq_batch_begin": (_i, [_vp, _err]),
+    "zq_batch_finish": (_i, [_vp, _err]),
     "zq_moe_route_softmax_topk": (_i, [_vp, _vp, _i, _sz, _sz, _vp, _vp, _sz, _sz, _f, _i, _vp, _vp, _err]),
     "zq_moe_experts_create": (_i, [_vp, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), _sz, C.POINTER(_vp), _err]),
     "zq_moe_experts_destroy": (None, [_vp]),
