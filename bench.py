@@ -123,6 +123,8 @@ def run_ours(args):
         ctx.set_option("force_f16_gemv", 1)
     if args.fused_gemm:
         ctx.set_option("force_fused_gemm", 1)
+    if args.narrow_tiles:
+        ctx.set_option("narrow_gemv_tiles", 1)
     device = torch.device("cuda", local_rank)
     hbm_peak, _, peak_kind = read_peaks()
     if args.only_prefill:
@@ -599,6 +601,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying CUDA graphs")
     ap.add_argument("--no-clocks", action="store_true", help="do not sample clocks with nvidia-smi")
     ap.add_argument("--no-pdl", action="store_true", help="launch decode kernels without programmatic dependent launch (A/B aid)")
+    ap.add_argument("--narrow-tiles", action="store_true", help="integer-MMA decode, up to 4 rows: 64-row tiles, two CTAs per SM (A/B aid)")
     ap.add_argument("--fused-gemm", action="store_true", help="Q4_K prefill on the kernel that dequantises inside the GEMM at every token count (A/B aid)")
     ap.add_argument("--f16-gemv", action="store_true", help="decode on the f16 warp-MMA kernels instead of the integer-MMA kernel (A/B aid)")
     ap.add_argument("--stack-layers", type=int, default=64, help="layers of the prefill GEMM stack (configs[2] names 64)")

@@ -18,19 +18,22 @@ pytestmark = pytest.mark.gpu
 _VARIANT = {"name": "i8"}
 
 
-@pytest.fixture(autouse=True, params=["i8", "tcgen05", "resident", "staged"])
+@pytest.fixture(autouse=True, params=["i8", "i8_narrow", "tcgen05", "resident", "staged"])
 def gemv_variant(request):
-    """Every case runs on all decode kernels: the integer-MMA kernel (the default; 16-bit integer activations), the
+    """Every case runs on all decode kernels: the integer-MMA kernel (the default; 16-bit integer activations;
+    "i8_narrow" runs up to 4 rows of a plain projection as 64-row tiles, two CTAs per SM), the
     tcgen05 kernel (Q4_K, opt-in), the f16 warp-MMA kernel with activations resident in shared memory, and the f16
     warp-MMA kernel with per-item activation staging."""
     ctx().set_option("enable_tcgen05_gemv", 1 if request.param == "tcgen05" else 0)
     ctx().set_option("force_staged_gemv", 1 if request.param == "staged" else 0)
     ctx().set_option("force_f16_gemv", 1 if request.param in ("resident", "tcgen05") else 0)
-    _VARIANT["name"] = request.param
+    ctx().set_option("narrow_gemv_tiles", 1 if request.param == "i8_narrow" else 0)
+    _VARIANT["name"] = "i8" if request.param == "i8_narrow" else request.param
     yield request.param
     ctx().set_option("force_staged_gemv", 0)
     ctx().set_option("enable_tcgen05_gemv", 0)
     ctx().set_option("force_f16_gemv", 0)
+    ctx().set_option("narrow_gemv_tiles", 0)
     _VARIANT["name"] = "i8"
 
 

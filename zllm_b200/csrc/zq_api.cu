@@ -200,6 +200,10 @@ int zq_ctx_set_option(zq_ctx *ctx, const char *key, int value, zq_error *err) {
         ctx->force_staged_gemv = value;
         return ZQ_OK;
     }
+    if (!strcmp(key, "narrow_gemv_tiles")) {
+        ctx->narrow_gemv_tiles = value;
+        return ZQ_OK;
+    }
     if (!strcmp(key, "force_fused_gemm")) {
         ctx->force_fused_gemm = value;
         return ZQ_OK;

@@ -248,6 +248,7 @@ struct zq_ctx {
     // parity-clean but, as measured, not yet faster than the warp-MMA path.
     int enable_tcgen05_gemv = 0;
     int force_f16_gemv = 0;  // skip the integer-MMA decode kernel (tests of the f16 kernels)
+    int narrow_gemv_tiles = 0;  // integer-MMA decode, up to 4 rows: 64-row tiles, two CTAs per SM (measured slower; off)
     int disable_pdl = 0;     // launch decode kernels without programmatic dependent launch
     int force_fused_gemm = 0;      // Q4_K prefill: the fused kernel for every token count (tests)
     int disable_fused_gemm = 0;    // Q4_K prefill: separate f16 operand pass + plain GEMM instead of the fused kernel

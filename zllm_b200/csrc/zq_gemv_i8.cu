@@ -56,11 +56,18 @@ __global__ void __launch_bounds__(256) quantize_acts_kernel(const void *x, int x
     if (lane == 0) *reinterpret_cast<float *>(dst + kRecScale) = o.scale;
 }
 
-template <uint32_t TYPE, int NT, bool GATED>
-__global__ void __launch_bounds__(kI8Threads, 1) gemv_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemvParams p, const I8Args ia) {
+// ROWS = weight rows per CTA: 128 (512 threads, one CTA per SM) or 64 (256 threads, two CTAs per SM).  The small
+// form was built for the launch-to-launch hand-over: with two CTAs per SM, a CTA of the NEXT kernel (programmatic
+// dependent launch) moves in as soon as ONE of the current kernel's CTAs leaves, and streams its first weights while
+// the other is still working.  Measured on the decode sweep it loses 3 % to the large form (every CTA repeats the
+// per-CTA work for half the rows), so it is kept behind the context option narrow_gemv_tiles.
+template <uint32_t TYPE, int NT, bool GATED, int ROWS>
+__global__ void __launch_bounds__(ROWS * 4, ROWS == 128 ? 1 : 2) gemv_i8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemvParams p, const I8Args ia) {
+    constexpr int THREADS = ROWS * 4, WARPS = THREADS / 32, SUBTILES = ROWS / 16;
+    static_assert(ROWS == 128 || (ROWS == 64 && !GATED), "64-row tiles: plain projections only");
     constexpr int UB = Fmt<TYPE>::unit_bytes;
     constexpr int PITCH = kChunkUnits * UB;
-    constexpr int STAGE_W = kTileRows * PITCH;
+    constexpr int STAGE_W = ROWS * PITCH;
     // More than 4 activation rows: the records would crowd the ring out of shared memory, and quantising them in every
     // CTA would cost more than the matrix; a small kernel quantises them once into global memory and every ring stage
     // brings the records of its two units along with the weights.
@@ -75,7 +82,7 @@ __global__ void __launch_bounds__(kI8Threads, 1) gemv_i8_kernel(const __grid_con
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int STAGES = ia.stages;
-    const int rows_per_tile = GATED ? kTileRows / 2 : kTileRows;
+    const int rows_per_tile = GATED ? ROWS / 2 : ROWS;
     const int split = ia.split, tshare = ia.tshare;
     const bool clustered = split * tshare > 1;
     const int my_tile = blockIdx.x / split, my_rank = blockIdx.x % split;
@@ -89,7 +96,7 @@ __global__ void __launch_bounds__(kI8Threads, 1) gemv_i8_kernel(const __grid_con
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], kI8Threads / 32);
+            mbar_init(&empty[s], WARPS);
         }
         fence_mbar_init();
         tma_prefetch_desc(&map_a);
@@ -133,7 +140,7 @@ __global__ void __launch_bounds__(kI8Threads, 1) gemv_i8_kernel(const __grid_con
     pdl_launch_dependents();
 
     const int g = lane >> 2, t = lane & 3;
-    const int rs = warp & 7, ul = warp >> 3;
+    const int rs = warp & (SUBTILES - 1), ul = warp / SUBTILES;
 
     int slice_units = chunk_end * kChunkUnits;
     if (slice_units > ia.units_total) slice_units = ia.units_total;
@@ -154,7 +161,7 @@ __global__ void __launch_bounds__(kI8Threads, 1) gemv_i8_kernel(const __grid_con
         // each record goes to all CTAs of the cluster that work on this K slice.  Records of activation rows past m
         // do not exist: lanes whose MMA column has no row read some existing record instead, and whatever they
         // compute only reaches accumulator columns no one reads.
-        constexpr int kBatch = 4, kWarps = kI8Threads / 32;
+        constexpr int kBatch = 4, kWarps = WARPS;
         uint32_t peer_x[8];
 #pragma unroll
         for (int q = 0; q < 8; ++q) peer_x[q] = (clustered && q < tshare) ? i8_mapa(x_base, (uint32_t)(q * split + my_rank)) : x_base;
@@ -234,7 +241,7 @@ __global__ void __launch_bounds__(kI8Threads, 1) gemv_i8_kernel(const __grid_con
             {
                 // refill: the stage consumed one iteration ago takes the item STAGES-1 ahead; a different warp each time
                 const int nxt = it + STAGES - 1;
-                if (nxt < n_items && warp == (it & 15) && lane == 0) {
+                if (nxt < n_items && warp == (it & (WARPS - 1)) && lane == 0) {
                     const int nstage = stage == 0 ? STAGES - 1 : stage - 1;
                     if (it >= 1) i8_wait_or_abort(&empty[nstage], stage == 0 ? phase ^ 1u : phase, &s_abort, p.status);
                     if (!*(volatile int *)&s_abort) {  // never start a copy nobody will wait for
@@ -277,8 +284,8 @@ __global__ void __launch_bounds__(kI8Threads, 1) gemv_i8_kernel(const __grid_con
         constexpr int RS = NT * 4;  // activation rows a tile row can hold
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-            red[(ul * RS + nt * 4 + t) * kTileRows + r0] = yacc[nt][0];  // [unit half][activation row][tile row]
-            red[(ul * RS + nt * 4 + t) * kTileRows + r0 + 8] = yacc[nt][1];
+            red[(ul * RS + nt * 4 + t) * ROWS + r0] = yacc[nt][0];  // [unit half][activation row][tile row]
+            red[(ul * RS + nt * 4 + t) * ROWS + r0 + 8] = yacc[nt][1];
         }
         if (split > 1) {
             i8_cluster_arrive();
@@ -287,9 +294,9 @@ __global__ void __launch_bounds__(kI8Threads, 1) gemv_i8_kernel(const __grid_con
             __syncthreads();
         }
         if (my_rank == 0) {
-            constexpr int out_rows = GATED ? kTileRows / 2 : kTileRows;
+            constexpr int out_rows = GATED ? ROWS / 2 : ROWS;
             auto total_of = [&](int rr, int tok) -> float {
-                const float *a = &red[tok * kTileRows + rr], *b = &red[(RS + tok) * kTileRows + rr];
+                const float *a = &red[tok * ROWS + rr], *b = &red[(RS + tok) * ROWS + rr];
                 float v = *a + *b;
                 for (int r = 1; r < split; ++r) {
                     const uint32_t peer = (uint32_t)(tile_local * split + r);
@@ -297,7 +304,7 @@ __global__ void __launch_bounds__(kI8Threads, 1) gemv_i8_kernel(const __grid_con
                 }
                 return v;
             };
-            for (int i = tid; i < out_rows * M; i += kI8Threads) {
+            for (int i = tid; i < out_rows * M; i += THREADS) {
                 const int row = i & (out_rows - 1), tok = i / out_rows;
                 const int n = my_tile * out_rows + row;
                 if (n >= p.n_out) continue;
@@ -322,7 +329,7 @@ __global__ void __launch_bounds__(kI8Threads, 1) gemv_i8_kernel(const __grid_con
 
 // How many clusters of a configuration can be resident at once (cached: the query is a host-side driver call).
 template <class Kernel>
-static int max_active_clusters(Kernel kernel, int device, int cluster, int smem_bytes, int grid) {
+static int max_active_clusters(Kernel kernel, int device, int cluster, int smem_bytes, int grid, int threads) {
     static std::mutex mu;
     static std::map<std::tuple<const void *, int, int, int>, int> cache;
     const auto key = std::make_tuple((const void *)kernel, device, cluster, smem_bytes);
@@ -331,7 +338,7 @@ static int max_active_clusters(Kernel kernel, int device, int cluster, int smem_
     if (it != cache.end()) return it->second;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(grid - grid % cluster));
-    cfg.blockDim = dim3(kI8Threads);
+    cfg.blockDim = dim3((unsigned)threads);
     cfg.dynamicSmemBytes = (size_t)smem_bytes;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -351,14 +358,16 @@ static int max_active_clusters(Kernel kernel, int device, int cluster, int smem_
 
 // Shared-memory plan: K slices per tile, ring depth and offsets; false when fewer than two ring stages fit beside
 // the quantised activation slice.
-template <uint32_t TYPE, int NT>
+template <uint32_t TYPE, int NT, int ROWS>
 static bool plan_i8(int m, int units_total, int tiles, int chunks, int sm_count, I8Args &ia, int &total_bytes) {
-    constexpr int STAGE_W = kTileRows * kChunkUnits * Fmt<TYPE>::unit_bytes;
-    const int max_smem = 232448 - 256;  // 227 KB opt-in limit minus static shared and alignment slack
-    const int red_bytes = 2 * kTileRows * NT * 4 * 4;
+    constexpr int STAGE_W = ROWS * kChunkUnits * Fmt<TYPE>::unit_bytes;
+    // 227 KB opt-in limit minus static shared and alignment slack; the 64-row form must leave room for a second CTA
+    const int max_smem = ROWS == 128 ? 232448 - 256 : 112 * 1024;
+    const int red_bytes = 2 * ROWS * NT * 4 * 4;
+    const int slots = sm_count * (ROWS == 128 ? 1 : 2);
     // K slices per tile: as many as fill the SMs (any count up to 8, not only powers of two); more than that, i.e.
     // more CTAs than SMs, only when the activation slice would otherwise leave no room for the ring
-    int split = sm_count / (tiles > 0 ? tiles : 1);
+    int split = slots / (tiles > 0 ? tiles : 1);
     if (split > 8) split = 8;
     if (split > chunks) split = chunks;
     if (split < 1) split = 1;
@@ -395,16 +404,19 @@ static bool plan_i8(int m, int units_total, int tiles, int chunks, int sm_count,
     return true;
 }
 
-template <uint32_t TYPE, int NT, bool GATED>
+template <uint32_t TYPE, int NT, bool GATED, int ROWS>
 static int launch_i8_one(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const GemvParams &p, bool &taken, zq_error *err) {
     I8Args ia;
     int total = 0;
-    taken = plan_i8<TYPE, NT>(p.m, (int)w->units_per_row, p.tiles, p.chunks, ctx->sm_count, ia, total);
+    const int rows_per_tile = GATED ? ROWS / 2 : ROWS;
+    const int tiles = (p.n_out + rows_per_tile - 1) / rows_per_tile;
+    taken = plan_i8<TYPE, NT, ROWS>(p.m, (int)w->units_per_row, tiles, p.chunks, ctx->sm_count, ia, total);
+    if (ROWS == 64 && taken && ia.stages < 3) taken = false;  // too little ring for the small form: the caller tries the large one
     if (!taken) return ZQ_OK;
-    auto kernel = gemv_i8_kernel<TYPE, NT, GATED>;
+    auto kernel = gemv_i8_kernel<TYPE, NT, GATED, ROWS>;
     static bool configured[64] = {};
     if (!configured[ctx->device & 63]) {
-        ZQ_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 256), err);
+        ZQ_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ROWS == 128 ? 232448 - 256 : 112 * 1024 + 512), err);
         configured[ctx->device & 63] = true;
     }
     if (NT > 1) {
@@ -427,24 +439,24 @@ static int launch_i8_one(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up,
     }
     // Tiles per cluster that share the activation staging: the largest divisor of the tile count that keeps the
     // cluster within 8 CTAs and still lets as many CTAs run at once as unshared clusters would.
-    const int grid = p.tiles * ia.split;
+    const int grid = tiles * ia.split;
     if (NT == 1 && p.m * (int)w->units_per_row >= 32) {  // a handful of records is quicker done by every CTA for itself
-        const int base_active = max_active_clusters(kernel, ctx->device, ia.split, total, grid) * ia.split;
+        const int base_active = max_active_clusters(kernel, ctx->device, ia.split, total, grid, ROWS * 4) * ia.split;
         const int want = grid < base_active ? grid : base_active;
         for (int ts = 8 / ia.split; ts > 1; --ts) {
-            if (p.tiles % ts) continue;
+            if (tiles % ts) continue;
             const int c = ia.split * ts;
-            if (max_active_clusters(kernel, ctx->device, c, total, grid) * c >= want) {
+            if (max_active_clusters(kernel, ctx->device, c, total, grid, ROWS * 4) * c >= want) {
                 ia.tshare = ts;
                 break;
             }
         }
     }
-    const CUtensorMap &ma = GATED ? w->gemv_map_half : w->gemv_map;
-    const CUtensorMap &mb = GATED ? w_up->gemv_map_half : w->gemv_map;
+    const CUtensorMap &ma = (GATED || ROWS == 64) ? w->gemv_map_half : w->gemv_map;  // 64-row boxes
+    const CUtensorMap &mb = GATED ? w_up->gemv_map_half : ma;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(kI8Threads);
+    cfg.blockDim = dim3((unsigned)(ROWS * 4));
     cfg.dynamicSmemBytes = (size_t)total;
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[2];
@@ -464,9 +476,16 @@ static int launch_i8_one(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up,
 template <uint32_t TYPE>
 static int launch_i8_type(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const GemvParams &p, bool &taken, zq_error *err) {
     const bool gated = w_up != nullptr;
-    if (p.m <= 4) return gated ? launch_i8_one<TYPE, 1, true>(ctx, w, w_up, p, taken, err) : launch_i8_one<TYPE, 1, false>(ctx, w, w_up, p, taken, err);
-    if (p.m <= 8) return gated ? launch_i8_one<TYPE, 2, true>(ctx, w, w_up, p, taken, err) : launch_i8_one<TYPE, 2, false>(ctx, w, w_up, p, taken, err);
-    return gated ? launch_i8_one<TYPE, 4, true>(ctx, w, w_up, p, taken, err) : launch_i8_one<TYPE, 4, false>(ctx, w, w_up, p, taken, err);
+    if (p.m <= 4) {
+        if (gated) return launch_i8_one<TYPE, 1, true, 128>(ctx, w, w_up, p, taken, err);
+        if (ctx->narrow_gemv_tiles) {  // opt-in: two 64-row CTAs per SM, so that the next kernel overlaps this one's tail
+            int rc = launch_i8_one<TYPE, 1, false, 64>(ctx, w, w_up, p, taken, err);
+            if (rc || taken) return rc;
+        }
+        return launch_i8_one<TYPE, 1, false, 128>(ctx, w, w_up, p, taken, err);
+    }
+    if (p.m <= 8) return gated ? launch_i8_one<TYPE, 2, true, 128>(ctx, w, w_up, p, taken, err) : launch_i8_one<TYPE, 2, false, 128>(ctx, w, w_up, p, taken, err);
+    return gated ? launch_i8_one<TYPE, 4, true, 128>(ctx, w, w_up, p, taken, err) : launch_i8_one<TYPE, 4, false, 128>(ctx, w, w_up, p, taken, err);
 }
 
 // Tries the integer-MMA kernel for one pass of up to 16 activation rows; `taken` tells whether it was launched
