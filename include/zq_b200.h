@@ -45,7 +45,7 @@ int zq_ctx_use_own_stream(zq_ctx *ctx, zq_error *err);
 int zq_ctx_sync(zq_ctx *ctx, zq_error *err);
 /* Diagnostic switches (the counterpart of the reference's ZLLM_CUDA_* environment switches, kept per context).
  * Known keys (0/1): "force_staged_gemv", "force_f16_gemv" (decode on the f16 kernels instead of the integer-MMA kernel),
- * "enable_tcgen05_gemv" (Q4_K decode on the tcgen05 kernel), "disable_pdl" (decode kernels without programmatic dependent launch), "force_moe_per_expert" (MoE forward always on the host-grouped path), "narrow_gemv_tiles" (decode, up to 4 rows: 64-row tiles, two CTAs per SM), "disable_fused_gemm" / "force_fused_gemm" (Q4_K prefill never / always on the kernel that dequantises inside the GEMM; default: up to 384 tokens and MoE prefill). */
+ * "enable_tcgen05_gemv" (Q4_K decode on the tcgen05 kernel), "disable_pdl" (decode kernels without programmatic dependent launch), "force_moe_per_expert" (MoE forward always on the host-grouped path), "narrow_gemv_tiles" (decode, up to 4 rows: 64-row tiles, two CTAs per SM), "disable_fused_gemm" / "force_fused_gemm" (Q4_K prefill never / always on the kernel that dequantises inside the GEMM; default: up to 1024 tokens and MoE prefill). */
 int zq_ctx_set_option(zq_ctx *ctx, const char *key, int value, zq_error *err);
 int zq_ctx_sm_count(const zq_ctx *ctx);
 /* Number of kernels this library has launched on the context since creation (bench accounting). */

@@ -113,8 +113,8 @@ __global__ void dequantize_kernel(uint32_t type, const uint8_t *__restrict__ res
     }
 }
 
-// Packed rows -> f16 [rows, cols]: the operand pass of the prefill GEMM.  Each value is the reference's f32 value
-// (same operation order as decode_unit_element) rounded once.  Up to kDequantBatch matrices of one type and shape
+// Packed rows -> f16 [rows, cols]: the operand pass of the prefill GEMM.  Each value is the weight's f32 value rounded
+// once (Q4_K: through one fused multiply-add, i.e. at least as close to the exact value as the codec's two-step form).  Up to kDequantBatch matrices of one type and shape
 // per launch (MoE prefill dequantises the experts of a chunk together).  One warp per 256-weight unit, 8 consecutive elements per lane: the
 // unit's packed bytes are read once with coalesced loads, the 512 output bytes are one coalesced store, and the only
 // index division is one per warp.
@@ -150,14 +150,15 @@ __global__ void __launch_bounds__(256) dequantize_f16_batch_kernel(const __grid_
                 sc = (scales[g + 4] & 0x0f) | ((scales[g - 4] >> 6) << 4);
                 mn = (scales[g + 4] >> 4) | ((scales[g] >> 6) << 4);
             }
-            const float dsc = __fmul_rn(d, (float)sc), dm = __fmul_rn(dmin, (float)mn);
+            // operand value: fma(d*sc, q, -(dmin*m)), one rounding (the fused GEMM kernel forms the same bits)
+            const float dsc = __fmul_rn(d, (float)sc), ndm = -__fmul_rn(dmin, (float)mn);
             const uint2 qw = *reinterpret_cast<const uint2 *>(unit + 16 + (g >> 1) * 32 + j0);
             const int shift = (g & 1) * 4;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 const uint32_t word = j < 4 ? qw.x : qw.y;
                 const int q = (word >> (8 * (j & 3) + shift)) & 0x0f;
-                v[j] = __fsub_rn(__fmul_rn(dsc, (float)q), dm);
+                v[j] = fmaf(dsc, (float)q, ndm);
             }
         } else {
 #pragma unroll

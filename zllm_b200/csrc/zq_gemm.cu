@@ -309,20 +309,22 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
 //   warp 0        TMA: one packed box per 256 K columns (128 rows x 144 bytes) into a 2-deep ring, and the
 //                 activation k-blocks (256 tokens x 64 K, 128-byte swizzle) into the main ring
 //   warps 6..13   dequantisers: thread = (row, half of the 64-column k-block) = one 32-weight scale group; reads the
-//                 group's 16 packed bytes and the row's scales from the packed box, forms the reference's f32 value
-//                 d*sc*q - dmin*m (same operation order as the codec), rounds once to f16 and stores its four
+//                 group's packed bytes and (once per super-block) the row's scales from the packed box, forms
+//                 fma(d*sc, q, -dmin*m) in f32, rounds once to f16 and stores its four
 //                 16-byte chunks at their 128-byte-swizzle positions (chunk c of row r sits at c ^ (r & 7)), then
 //                 fence.proxy.async and one arrival per warp on the stage's a_full barrier
 //   warp 1        waits for a_full and b_full of a stage, issues the four K=16 MMAs, commits the stage's `empty`
-// The operand bits are exactly those the separate pass would have written, so results are identical.
+// The operand bits are exactly those the separate operand pass writes (same formula), so both paths give identical
+// results.  A last warp issues the packed boxes on a ring of its own.
 // ---------------------------------------------------------------------------------------------------------------
-constexpr int kFusedDqWarps = 8;
-constexpr int kFusedThreads = (6 + kFusedDqWarps) * 32;
+constexpr int kFusedDqWarps = 8;   // thread = (row, half of the k-block) = one 32-weight scale group
+constexpr int kFusedThreads = (7 + kFusedDqWarps) * 32;  // + TMA (activations), MMA, 4 epilogue, TMA (packed boxes)
+constexpr int kFusedPackedWarp = 6 + kFusedDqWarps;
 constexpr int kQ4kUnitBytes = 144;
 
 template <bool GATED> struct FusedSmem {
     static constexpr int stages = GATED ? 2 : 3;
-    static constexpr int pstages = 2;
+    static constexpr int pstages = GATED ? 2 : 3;
     static constexpr int acc_bufs = GATED ? 1 : 2;
     static constexpr int a_bytes = kBM * kBK * 2;
     static constexpr int b_bytes = kBN * kBK * 2;
@@ -348,14 +350,16 @@ __device__ __forceinline__ float nib_to_float(uint32_t masked, int byte) {
     return __fadd_rn(__uint_as_float(r), -8388608.0f);
 }
 
-__device__ __forceinline__ void dequant_group_to_sw128(const uint8_t *unit, int pair, int half, uint8_t *a_tile, int row) {
-    const uint4 hdr = *reinterpret_cast<const uint4 *>(unit);
+// The f16 operand value of a Q4_K weight, as both GEMM paths form it: fma(d*sc, q, -(dmin*m)) in f32 (one rounding,
+// slightly closer to the exact value than the codec's multiply-then-subtract), rounded once to f16.
+__device__ __forceinline__ uint32_t q4k_pair_f16(float dsc, float ndm, float qa, float qb) { return h2_as_u32(__floats2half2_rn(fmaf(dsc, qa, ndm), fmaf(dsc, qb, ndm))); }
+
+// The 8 (d*sc, -dmin*m) pairs of one super-block header (src/weight/codec/ggml.rs:471-473).
+__device__ __forceinline__ void q4k_group_scales(const uint4 &hdr, int g, float &dsc, float &ndm) {
     const __half2 dd = u32_as_h2(hdr.x);
     const float d = __low2float(dd), dmin = __high2float(dd);
-    // 6-bit scale and min of group g = 2 pair + half (src/weight/codec/ggml.rs:471-473), from the 12 packed bytes
-    const int g = 2 * pair + half;
     uint32_t sc, mn;
-    if (pair < 2) {
+    if (g < 4) {
         sc = (hdr.y >> (8 * g)) & 63u;
         mn = (hdr.z >> (8 * g)) & 63u;
     } else {
@@ -363,7 +367,13 @@ __device__ __forceinline__ void dequant_group_to_sw128(const uint8_t *unit, int 
         sc = ((hdr.w >> j) & 0x0Fu) | (((hdr.y >> (j + 6)) & 3u) << 4);
         mn = ((hdr.w >> (j + 4)) & 0x0Fu) | (((hdr.z >> (j + 6)) & 3u) << 4);
     }
-    const float dsc = __fmul_rn(d, (float)sc), dm = __fmul_rn(dmin, (float)mn);
+    dsc = __fmul_rn(d, (float)sc);
+    ndm = -__fmul_rn(dmin, (float)mn);
+}
+
+// One scale group (32 weights: low or high nibbles of the pair's 32 quant bytes) of one row of a packed Q4_K box ->
+// 32 f16 in the swizzled A tile (the four 16-byte chunks 4 half .. 4 half + 3 of row `row`).
+__device__ __forceinline__ void dequant_group_to_sw128(const uint8_t *unit, int pair, int half, float dsc, float ndm, uint8_t *a_tile, int row) {
     const uint4 q0 = *reinterpret_cast<const uint4 *>(unit + 16 + pair * 32), q1 = *reinterpret_cast<const uint4 *>(unit + 16 + pair * 32 + 16);
     const uint32_t qw[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
     const int shift = half * 4;
@@ -374,10 +384,8 @@ __device__ __forceinline__ void dequant_group_to_sw128(const uint8_t *unit, int 
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
             const uint32_t m = (qw[2 * c + j] >> shift) & 0x0F0F0F0Fu;
-            const float v0 = __fsub_rn(__fmul_rn(dsc, nib_to_float(m, 0)), dm), v1 = __fsub_rn(__fmul_rn(dsc, nib_to_float(m, 1)), dm);
-            const float v2 = __fsub_rn(__fmul_rn(dsc, nib_to_float(m, 2)), dm), v3 = __fsub_rn(__fmul_rn(dsc, nib_to_float(m, 3)), dm);
-            h[2 * j] = h2_as_u32(__floats2half2_rn(v0, v1));
-            h[2 * j + 1] = h2_as_u32(__floats2half2_rn(v2, v3));
+            h[2 * j] = q4k_pair_f16(dsc, ndm, nib_to_float(m, 0), nib_to_float(m, 1));
+            h[2 * j + 1] = q4k_pair_f16(dsc, ndm, nib_to_float(m, 2), nib_to_float(m, 3));
         }
         const int chunk = half * 4 + c;
         *reinterpret_cast<uint4 *>(row_base + ((chunk ^ (row & 7)) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
@@ -457,9 +465,28 @@ __global__ void __launch_bounds__(kFusedThreads, 1) gemm_q4k_fused_kernel(const 
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
 
     if (warp == 0) {
-        // ------------------------------------------------ TMA producer: packed boxes and activation k-blocks
+        // ------------------------------------------------ TMA producer: activation k-blocks
         if (lane == 0) {
-            long long kg = 0, pq = 0;
+            long long kg = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                int row0, tok0, tok_end, z;
+                tile_coords(tile, row0, tok0, tok_end, z);
+                for (int kb = 0; kb < n_sb * (kUnitWeights / kBK) && ok; ++kb, ++kg) {
+                    const int s = (int)(kg % STAGES);
+                    if (kg >= STAGES) ok = wait_flag(&empty[s], (uint32_t)((kg / STAGES) - 1) & 1, &s_abort, p.status, kStatusMmaTimeout);
+                    if (!ok) break;
+                    uint8_t *st = smem + (size_t)s * S::stage_bytes;
+                    mbar_expect_tx(&b_full[s], S::b_bytes);
+                    tma_load_2d(st + (GATED ? 2 : 1) * S::a_bytes, &map_x, &b_full[s], kb * kBK, tok0);
+                }
+            }
+        }
+    } else if (warp == kFusedPackedWarp) {
+        // ------------------------------------------------ TMA producer: packed boxes, a ring of their own, so that a box
+        // is requested as soon as the dequantisers free its slot, not when the activation ring gets round to it
+        if (lane == 0) {
+            long long pq = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 int row0, tok0, tok_end, z;
@@ -468,20 +495,12 @@ __global__ void __launch_bounds__(kFusedThreads, 1) gemm_q4k_fused_kernel(const 
                 const CUtensorMap *mw2 = grouped ? (GATED ? &p.w2_maps[z] : mw) : &map_w2;
                 for (int sb = 0; sb < n_sb && ok; ++sb, ++pq) {
                     const int ps = (int)(pq % PST);
-                    if (pq >= PST) ok = wait_flag(&p_empty[ps], (uint32_t)((pq / PST) - 1) & 1, &s_abort, p.status, kStatusMmaTimeout);
+                    if (pq >= PST) ok = wait_flag_backoff(&p_empty[ps], (uint32_t)((pq / PST) - 1) & 1, &s_abort, p.status, kStatusMmaTimeout, 100);
                     if (!ok) break;
                     uint8_t *pst = smem + S::off_p + (size_t)ps * S::pstage_bytes;
                     mbar_expect_tx(&p_full[ps], S::pstage_bytes);
                     tma_load_2d(pst, mw, &p_full[ps], sb * (kQ4kUnitBytes / 4), row0);
                     if (GATED) tma_load_2d(pst + S::p_bytes, mw2, &p_full[ps], sb * (kQ4kUnitBytes / 4), row0);
-                    for (int kb = 0; kb < kUnitWeights / kBK && ok; ++kb, ++kg) {
-                        const int s = (int)(kg % STAGES);
-                        if (kg >= STAGES) ok = wait_flag(&empty[s], (uint32_t)((kg / STAGES) - 1) & 1, &s_abort, p.status, kStatusMmaTimeout);
-                        if (!ok) break;
-                        uint8_t *st = smem + (size_t)s * S::stage_bytes;
-                        mbar_expect_tx(&b_full[s], S::b_bytes);
-                        tma_load_2d(st + (GATED ? 2 : 1) * S::a_bytes, &map_x, &b_full[s], sb * kUnitWeights + kb * kBK, tok0);
-                    }
                 }
             }
         }
@@ -577,7 +596,20 @@ __global__ void __launch_bounds__(kFusedThreads, 1) gemm_q4k_fused_kernel(const 
                 const int ps = (int)(pq % PST);
                 ok = wait_flag_backoff(&p_full[ps], (uint32_t)(pq / PST) & 1, &s_abort, p.status, kStatusTmaTimeout, 60);
                 if (!ok) break;
-                const uint8_t *pst = smem + S::off_p + (size_t)ps * S::pstage_bytes;
+                const uint8_t *u0 = smem + S::off_p + (size_t)ps * S::pstage_bytes + (size_t)row * kQ4kUnitBytes;
+                const uint8_t *u1 = u0 + S::p_bytes;
+                // the four groups this thread will meet in this super-block: 2 kb + half
+                float dsc0[4], ndm0[4], dsc1[4], ndm1[4];
+                {
+                    const uint4 hdr = *reinterpret_cast<const uint4 *>(u0);
+#pragma unroll
+                    for (int kb = 0; kb < 4; ++kb) q4k_group_scales(hdr, 2 * kb + half, dsc0[kb], ndm0[kb]);
+                }
+                if (GATED) {
+                    const uint4 hdr = *reinterpret_cast<const uint4 *>(u1);
+#pragma unroll
+                    for (int kb = 0; kb < 4; ++kb) q4k_group_scales(hdr, 2 * kb + half, dsc1[kb], ndm1[kb]);
+                }
 #pragma unroll
                 for (int kb = 0; kb < kUnitWeights / kBK; ++kb, ++kg) {
                     if (!ok) break;
@@ -585,8 +617,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) gemm_q4k_fused_kernel(const 
                     if (kg >= STAGES) ok = wait_flag_backoff(&empty[s], (uint32_t)((kg / STAGES) - 1) & 1, &s_abort, p.status, kStatusMmaTimeout, 60);
                     if (!ok) break;
                     uint8_t *st = smem + (size_t)s * S::stage_bytes;
-                    dequant_group_to_sw128(pst + (size_t)row * kQ4kUnitBytes, kb, half, st, row);
-                    if (GATED) dequant_group_to_sw128(pst + S::p_bytes + (size_t)row * kQ4kUnitBytes, kb, half, st + S::a_bytes, row);
+                    dequant_group_to_sw128(u0, kb, half, dsc0[kb], ndm0[kb], st, row);
+                    if (GATED) dequant_group_to_sw128(u1, kb, half, dsc1[kb], ndm1[kb], st + S::a_bytes, row);
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the tensor core
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&a_full[s]);
@@ -631,7 +663,7 @@ int launch_gemm(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const vo
     // The fused kernel saves the operand pass (one read of the packed weight, one write and one read of its f16 form),
     // which dominates for few tokens; with many tokens the pass is amortised and the plain kernel, whose shared-memory
     // traffic per k-block is lower (no operand stores by threads), runs the tensor core at a higher duty.
-    const bool fused = !ctx->disable_fused_gemm && (ctx->force_fused_gemm || m <= 384) && w->type == ZQ_Q4_K && (!gated || w_up->type == ZQ_Q4_K) && k % kUnitWeights == 0;
+    const bool fused = !ctx->disable_fused_gemm && (ctx->force_fused_gemm || m <= 1024) && w->type == ZQ_Q4_K && (!gated || w_up->type == ZQ_Q4_K) && k % kUnitWeights == 0;
     if (fused) {
         // Q4_K: dequantisation fused into the kernel; the workspace only holds the f16 copy of the activations
         const size_t xb = (m * k * 2 + 255) & ~size_t(255);
