@@ -95,6 +95,8 @@ def quantize(tensor_type: int, values: np.ndarray) -> np.ndarray:
 
 
 def random_weight(tensor_type: int, rows: int, cols: int, seed: int, std: float = 0.02) -> np.ndarray:
+    if tensor_type in (Q5_K, Q6_K):
+        return random_kquant_weight(tensor_type, rows, cols, seed)
     rng = np.random.default_rng(seed)
     return quantize(tensor_type, rng.standard_normal((rows, cols), dtype=np.float32) * np.float32(std))
 
@@ -110,6 +112,22 @@ def random_bytes_weight(tensor_type: int, rows: int, cols: int, seed: int) -> np
     for s in range(n_scales):
         bits = rng.integers(0, 0x7C00, size=blocks, dtype=np.uint16) | (rng.integers(0, 2, size=blocks, dtype=np.uint16) << 15)
         out[:, off + 2 * s:off + 2 * s + 2] = bits.view(np.uint8).reshape(-1, 2)
+    return out.reshape(-1)
+
+
+def random_kquant_weight(tensor_type: int, rows: int, cols: int, seed: int) -> np.ndarray:
+    """Q5_K / Q6_K input generator (the reference has no encoder for them): uniformly random payload and scale-code
+    bytes under small positive f16 super-block scales, so that every code occurs and the values stay in the range of
+    real tensors."""
+    rng = np.random.default_rng(seed)
+    e, b = orc.BLOCK[tensor_type]
+    blocks = rows * cols // e
+    out = rng.integers(0, 256, size=(blocks, b), dtype=np.uint8)
+    n_scales = 2 if tensor_type in (Q4_K, Q5_K) else 1
+    off = 208 if tensor_type == Q6_K else 0
+    for s in range(n_scales):
+        d = rng.uniform(2.0e-4, 6.0e-4, size=blocks).astype(np.float16)
+        out[:, off + 2 * s:off + 2 * s + 2] = d.view(np.uint8).reshape(-1, 2)
     return out.reshape(-1)
 
 

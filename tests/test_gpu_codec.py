@@ -8,7 +8,7 @@ from tests import helpers as H
 from tests.gpu_util import ctx, dev, host
 
 pytestmark = pytest.mark.gpu
-TYPES = [H.Q4_0, H.Q8_0, H.Q4_K, H.IQ4_NL]
+TYPES = [H.Q4_0, H.Q8_0, H.Q4_K, H.Q5_K, H.Q6_K, H.IQ4_NL]
 
 
 def _bits(a):
@@ -63,8 +63,9 @@ def test_f16_edge_scales(tensor_type):
     data = rng.integers(0, 256, size=(n * per_row, b), dtype=np.uint8)
     for i, bits in enumerate(H.F16_EDGE_SCALES):
         for j in range(per_row):
-            data[i * per_row + j, 0:2] = np.frombuffer(np.uint16(bits).tobytes(), dtype=np.uint8)
-            if tensor_type == H.Q4_K:
+            off = 208 if tensor_type == H.Q6_K else 0
+            data[i * per_row + j, off:off + 2] = np.frombuffer(np.uint16(bits).tobytes(), dtype=np.uint8)
+            if tensor_type in (H.Q4_K, H.Q5_K):
                 data[i * per_row + j, 2:4] = np.frombuffer(np.uint16(H.F16_EDGE_SCALES[(i + 3) % n]).tobytes(), dtype=np.uint8)
     data = data.reshape(-1)
     w = ctx().prepare_weight(tensor_type, data, n, 256)
@@ -93,9 +94,19 @@ def test_reference_known_answers_through_the_device_path():
     q4[16] = 2
     out = host(ctx().dequantize(ctx().prepare_weight(H.Q4_K, q4, 1, 256)))[0]
     assert out[0] == 2.0
+    q5 = np.zeros(176, dtype=np.uint8)  # src/weight/codec/ggml.rs:577-604, Q5_K and Q6_K cases
+    q5[:2] = [0x00, 0x3C]
+    q5[4] = 1
+    q5[16] = 1
+    q5[48] = 2
+    assert host(ctx().dequantize(ctx().prepare_weight(H.Q5_K, q5, 1, 256)))[0][0] == 18.0
+    q6 = np.zeros(210, dtype=np.uint8)
+    q6[192] = 1
+    q6[208:] = [0x00, 0x3C]
+    assert host(ctx().dequantize(ctx().prepare_weight(H.Q6_K, q6, 1, 256)))[0][0] == -32.0
 
 
-@pytest.mark.parametrize("tensor_type", [H.Q8_0, H.IQ4_NL, H.Q4_K])
+@pytest.mark.parametrize("tensor_type", [H.Q8_0, H.IQ4_NL, H.Q4_K, H.Q5_K, H.Q6_K])
 def test_gather_rows_equals_f16_of_dequant(tensor_type):
     """src/kernel/cuda/linear.rs:2156-2173: gathered rows == f16(dequant) exactly."""
     rows, cols = 50, 512

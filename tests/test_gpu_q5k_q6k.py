@@ -1,0 +1,101 @@
+"""Q5_K and Q6_K linear layers (src/weight/codec/ggml.rs:425-469; the reference's CUDA kernels for them:
+src/kernel/cuda/linear.rs:1167-1234, 1967-2101) against the CPU oracle, through the C ABI.
+
+These two types have no decode kernel of their own yet: every batch size runs the f16 operand pass and the
+tensor-core GEMM, so one activation row is held to the same 2e-3 bound as a prefill batch.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as orc
+from tests import helpers as H
+from tests.gpu_util import ctx, dev, host
+
+pytestmark = pytest.mark.gpu
+BOUND = 2e-3
+TYPES = [H.Q5_K, H.Q6_K]
+
+
+@pytest.mark.parametrize("tensor_type", TYPES)
+@pytest.mark.parametrize("m,rows,cols", [(1, 200, 1024), (4, 128, 256), (16, 384, 2048), (40, 130, 512), (300, 256, 1536)])
+def test_linear_matches_cpu_path(tensor_type, m, rows, cols):
+    data = H.random_weight(tensor_type, rows, cols, seed=5 * m + rows)
+    x = dev(np.random.default_rng(m).standard_normal((m, cols)).astype(np.float32), torch.bfloat16)
+    w = ctx().prepare_weight(tensor_type, data, rows, cols)
+    got = host(ctx().linear(x, w, out_dtype=torch.float32))
+    want = orc.linear(tensor_type, data, rows, cols, x.float().cpu().numpy())
+    assert H.max_rel_error(got, want) <= BOUND
+
+
+@pytest.mark.parametrize("tensor_type", TYPES)
+def test_reference_generator_case(tensor_type):
+    """The reference's deterministic blocks and inputs (src/kernel/cpu/ggml_quant.rs:370-414, 432), one row of
+    activations, with the reference's device gate 0.05 + 0.002*|e| as an outer bound."""
+    rows, cols = 3, 256
+    packed = H.reference_packed_blocks(tensor_type, rows)
+    idx = np.arange(cols, dtype=np.int64)
+    x = (((idx * 17 % 101).astype(np.float32) - 50.0) / 64.0).reshape(1, cols)
+    w = ctx().prepare_weight(tensor_type, packed, rows, cols)
+    got = host(ctx().linear(dev(x, torch.float16), w, out_dtype=torch.float32))
+    want = orc.linear(tensor_type, packed, rows, cols, x)
+    assert np.all(np.abs(got - want) <= 0.05 + 0.002 * np.abs(want))
+    assert H.max_rel_error(got, want) <= BOUND
+
+
+@pytest.mark.parametrize("tensor_type", TYPES)
+@pytest.mark.parametrize("m", [2, 48])
+def test_linear_add_and_gated(tensor_type, m):
+    rows, cols = 256, 512
+    gate, up = H.random_weight(tensor_type, rows, cols, seed=21), H.random_weight(tensor_type, rows, cols, seed=22)
+    x = dev(np.random.default_rng(23).standard_normal((m, cols)).astype(np.float32), torch.bfloat16)
+    r = dev(np.random.default_rng(24).standard_normal((m, rows)).astype(np.float32), torch.float32)
+    wg, wu = ctx().prepare_weight(tensor_type, gate, rows, cols), ctx().prepare_weight(tensor_type, up, rows, cols)
+    xf = x.float().cpu().numpy()
+    got = host(ctx().linear_add(x, wg, r))
+    want = orc.linear(tensor_type, gate, rows, cols, xf) + r.cpu().numpy()
+    assert H.max_rel_error(got, want) <= BOUND
+    got = host(ctx().gated_linear(x, wg, wu, out_dtype=torch.float32))
+    want = orc.gated_linear(tensor_type, gate, up, rows, cols, xf)
+    assert H.max_rel_error(got, want) <= 2 * BOUND  # two f16-operand products multiplied: each factor is within BOUND
+
+
+def test_no_decode_entry_and_no_encoder_for_these_types():
+    from zllm_b200 import ffi
+
+    data = H.random_weight(H.Q6_K, 128, 256, seed=1)
+    w = ctx().prepare_weight(H.Q6_K, data, 128, 256)
+    x = dev(np.ones((1, 256), dtype=np.float32), torch.float32)
+    y = torch.empty((1, 128), dtype=torch.float32, device=x.device)
+    with pytest.raises(ffi.ZqFailure):
+        ffi.call("zq_linear_noalloc", ctx().handle, w.handle, C.c_void_p(x.data_ptr()), ffi.F32, 1, C.c_void_p(y.data_ptr()), ffi.F32)
+    with pytest.raises(ffi.ZqFailure):
+        ctx().quantize(H.Q5_K, dev(np.zeros((1, 256), dtype=np.float32), torch.float32))
+
+
+@pytest.mark.parametrize("down_type", TYPES)
+@pytest.mark.parametrize("m", [3, 48, 400])
+def test_moe_experts_with_k_quant_down_projection(down_type, m):
+    """Q4_K gate/up with a Q5_K or Q6_K down projection, the mix the reference's CUDA experts accept
+    (src/backend/cuda/expert.rs:462-473), against the oracle's moe_forward.  The down projection runs on f16
+    operands behind the f16-rounded activated intermediate, hence the composite bound of the MoE prefill test."""
+    from zllm_b200.backend import MoeExperts, moe_forward
+
+    n_exp, top_k, hidden, inter = 8, 2, 512, 256
+    rng = np.random.default_rng(40 + m)
+    gates = [H.random_weight(H.Q4_K, inter, hidden, seed=300 + 3 * e) for e in range(n_exp)]
+    ups = [H.random_weight(H.Q4_K, inter, hidden, seed=301 + 3 * e) for e in range(n_exp)]
+    downs = [H.random_weight(down_type, hidden, inter, seed=302 + 3 * e) for e in range(n_exp)]
+    x = rng.standard_normal((m, hidden)).astype(np.float32)
+    ids_np = np.stack([rng.permutation(n_exp)[:top_k] for _ in range(m)]).astype(np.uint32)
+    w_np = rng.random((m, top_k)).astype(np.float32)
+    w_np /= w_np.sum(axis=1, keepdims=True)
+    c = ctx()
+    table = MoeExperts(c, [c.prepare_weight(H.Q4_K, g, inter, hidden) for g in gates], [c.prepare_weight(H.Q4_K, u, inter, hidden) for u in ups],
+                       [c.prepare_weight(down_type, d, hidden, inter) for d in downs])
+    got = host(moe_forward(c, table, dev(x), torch.from_numpy(ids_np.astype(np.int32)).cuda(), dev(w_np)))
+    want = orc.moe_forward([(H.Q4_K, g, inter, hidden) for g in gates], [(H.Q4_K, u, inter, hidden) for u in ups], [(down_type, d, hidden, inter) for d in downs], x, ids_np, w_np)
+    assert H.max_rel_error(got, want) <= 2 * BOUND
+    assert float(np.linalg.norm(got - want) / np.linalg.norm(want)) <= 1e-3

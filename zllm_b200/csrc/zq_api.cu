@@ -86,7 +86,7 @@ static int check_dtype(int dtype, const char *what, zq_error *err) {
 static int prepare_common(zq_ctx *ctx, uint32_t type, size_t nbytes, size_t rows, size_t cols, zq_weight **out, zq_error *err) {
     if (!ctx || !out) return set_error(err, ZQ_ERR_ARG, "weight prepare: null context or output");
     FormatInfo f = format_info(type);
-    if (!f.ggml_type) return set_error(err, ZQ_ERR_UNSUPPORTED, "GGUF tensor type %u is not supported (supported: 2, 8, 12, 20)", type);
+    if (!f.ggml_type) return set_error(err, ZQ_ERR_UNSUPPORTED, "GGUF tensor type %u is not supported (supported: 2, 8, 12, 13, 14, 20)", type);
     if (rows == 0 || cols == 0 || cols % f.block_elems) return set_error(err, ZQ_ERR_SHAPE, "GGUF type %u weight [%zu, %zu]: columns must be a positive multiple of %d", type, rows, cols, f.block_elems);
     size_t expected = rows * (cols / f.block_elems) * f.block_bytes;
     if (nbytes != expected) return set_error(err, ZQ_ERR_SHAPE, "GGUF type %u weight [%zu, %zu]: %zu bytes given, %zu expected", type, rows, cols, nbytes, expected);
@@ -104,6 +104,7 @@ static int prepare_common(zq_ctx *ctx, uint32_t type, size_t nbytes, size_t rows
 }
 
 static int finish_prepare(zq_ctx *ctx, zq_weight *w, zq_error *err) {
+    if (is_operand_pass_only(w->type)) return ZQ_OK;  // no decode kernel reads these through TMA (Q6_K blocks are not even 4-byte multiples)
     FormatInfo f = format_info(w->type);
     int rc = make_weight_map(w, 2 * f.unit_bytes / 4, 128, &w->gemv_map, err);
     if (!rc) rc = make_weight_map(w, 2 * f.unit_bytes / 4, 64, &w->gemv_map_half, err);
@@ -245,7 +246,7 @@ int zq_weight_prepare_device(zq_ctx *ctx, uint32_t ggml_type, const void *dev_by
         delete w;
         return set_error(err, ZQ_ERR_CUDA, "cudaMalloc of %zu resident bytes failed: %s", resident, cudaGetErrorString(e));
     }
-    if (ggml_type == ZQ_Q4_K) {
+    if (ggml_type == ZQ_Q4_K || is_operand_pass_only(ggml_type)) {  // resident layout = GGUF layout
         e = cudaMemcpyAsync(w->data, dev_bytes, nbytes, cudaMemcpyDeviceToDevice, ctx->stream);
         if (e != cudaSuccess) rc = set_error(err, ZQ_ERR_CUDA, "copy of packed weight failed: %s", cudaGetErrorString(e));
     } else {
@@ -312,7 +313,7 @@ int zq_gather_rows(zq_ctx *ctx, const zq_weight *w, const uint32_t *dev_row_ids,
 int zq_quantize(zq_ctx *ctx, uint32_t ggml_type, const float *dev_values, size_t rows, size_t cols, void *dev_gguf_bytes, size_t nbytes, zq_error *err) {
     if (!ctx || !dev_values || !dev_gguf_bytes) return set_error(err, ZQ_ERR_ARG, "zq_quantize: null argument");
     FormatInfo f = format_info(ggml_type);
-    if (!f.ggml_type) return set_error(err, ZQ_ERR_UNSUPPORTED, "zq_quantize: GGUF tensor type %u is not supported", ggml_type);
+    if (!f.ggml_type || is_operand_pass_only(ggml_type)) return set_error(err, ZQ_ERR_UNSUPPORTED, "zq_quantize: no encoder for GGUF tensor type %u", ggml_type);
     if (cols % f.block_elems) return set_error(err, ZQ_ERR_SHAPE, "zq_quantize: columns %zu not aligned to block %d", cols, f.block_elems);
     size_t expected = rows * (cols / f.block_elems) * f.block_bytes;
     if (nbytes != expected) return set_error(err, ZQ_ERR_SHAPE, "zq_quantize: output holds %zu bytes, %zu expected", nbytes, expected);
@@ -333,7 +334,7 @@ static int check_linear(zq_ctx *ctx, const zq_weight *w, const void *x, int x_dt
 int zq_linear(zq_ctx *ctx, const zq_weight *w, const void *dev_x, int x_dtype, size_t m, void *dev_y, int y_dtype, const void *dev_residual, zq_error *err) {
     int rc = check_linear(ctx, w, dev_x, x_dtype, m, dev_y, y_dtype, err);
     if (rc) return rc;
-    if (m <= 16) return launch_gemv(ctx, w, nullptr, dev_x, x_dtype, m, dev_y, y_dtype, dev_residual, err);
+    if (m <= 16 && !is_operand_pass_only(w->type)) return launch_gemv(ctx, w, nullptr, dev_x, x_dtype, m, dev_y, y_dtype, dev_residual, err);
     return launch_gemm(ctx, w, nullptr, dev_x, x_dtype, m, dev_y, y_dtype, dev_residual, err);
 }
 
@@ -354,7 +355,7 @@ int zq_gated_silu(zq_ctx *ctx, const zq_weight *gate, const zq_weight *up, const
     if (rc) return rc;
     if (!up || up->ctx != ctx) return set_error(err, ZQ_ERR_ARG, "gated linear: bad up weight");
     if (gate->rows != up->rows || gate->cols != up->cols || gate->type != up->type) return set_error(err, ZQ_ERR_SHAPE, "gated linear: gate [%zu, %zu] type %u and up [%zu, %zu] type %u differ", gate->rows, gate->cols, gate->type, up->rows, up->cols, up->type);
-    if (m <= 16) return launch_gemv(ctx, gate, up, dev_x, x_dtype, m, dev_y, y_dtype, nullptr, err);
+    if (m <= 16 && !is_operand_pass_only(gate->type)) return launch_gemv(ctx, gate, up, dev_x, x_dtype, m, dev_y, y_dtype, nullptr, err);
     return launch_gemm(ctx, gate, up, dev_x, x_dtype, m, dev_y, y_dtype, nullptr, err);
 }
 
@@ -374,6 +375,7 @@ int zq_gated_mlp(zq_ctx *ctx, const zq_weight *gate, const zq_weight *up, const 
 int zq_linear_noalloc(zq_ctx *ctx, const zq_weight *w, const void *dev_x, int x_dtype, size_t m, void *dev_y, int y_dtype, zq_error *err) {
     int rc = check_linear(ctx, w, dev_x, x_dtype, m, dev_y, y_dtype, err);
     if (rc) return rc;
+    if (is_operand_pass_only(w->type)) return set_error(err, ZQ_ERR_UNSUPPORTED, "zq_linear_noalloc: GGUF type %u has no decode kernel (its layers need the operand workspace)", w->type);
     return launch_gemv_noalloc(ctx, w, dev_x, x_dtype, m, dev_y, y_dtype, err);
 }
 

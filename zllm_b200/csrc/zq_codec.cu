@@ -60,6 +60,32 @@ int launch_repack(zq_ctx *ctx, uint32_t type, const uint8_t *gguf, uint8_t *resi
 // Decode element `i` (0..255) of a resident unit.  Every product below is exactly representable in f32, so the
 // only rounding is the reference's final subtraction; __fmul_rn/__fsub_rn keep the compiler from contracting.
 __device__ __forceinline__ float decode_unit_element(uint32_t type, const uint8_t *unit, int i) {
+    if (type == ZQ_Q5_K) {  // src/weight/codec/ggml.rs:425-444: d, dmin, 12 scale bytes, 32 high-bit bytes, 128 low-nibble bytes
+        const __half *hd = reinterpret_cast<const __half *>(unit);
+        const float d = __half2float(hd[0]), dmin = __half2float(hd[1]);
+        const uint8_t *scales = unit + 4;
+        const int g = i >> 5, j = i & 31;
+        int sc, mn;
+        if (g < 4) {
+            sc = scales[g] & 0x3f;
+            mn = scales[g + 4] & 0x3f;
+        } else {
+            sc = (scales[g + 4] & 0x0f) | ((scales[g - 4] >> 6) << 4);
+            mn = (scales[g + 4] >> 4) | ((scales[g] >> 6) << 4);
+        }
+        const uint8_t packed = unit[48 + (g >> 1) * 32 + j];
+        const int quant = ((g & 1) ? (packed >> 4) : (packed & 0x0f)) + (((unit[16 + j] >> g) & 1) << 4);
+        return __fsub_rn(__fmul_rn(__fmul_rn(d, (float)sc), (float)quant), __fmul_rn(dmin, (float)mn));
+    }
+    if (type == ZQ_Q6_K) {  // src/weight/codec/ggml.rs:446-469: 128 low-nibble bytes, 64 high-bit bytes, 16 i8 scales, d
+        const float d = __half2float(*reinterpret_cast<const __half *>(unit + 208));
+        const int half = i >> 7, quarter = (i >> 5) & 3, index = i & 31;
+        const uint8_t lo = unit[half * 64 + index + ((quarter & 1) ? 32 : 0)];
+        const uint8_t hv = unit[128 + half * 32 + index];
+        const int q = (int)(((quarter & 2) ? (lo >> 4) : (lo & 0x0f)) | (((hv >> (2 * quarter)) & 3) << 4)) - 32;
+        const int8_t scale = (int8_t)unit[192 + half * 8 + (index >> 4) + 2 * quarter];
+        return __fmul_rn(__fmul_rn(d, (float)scale), (float)q);
+    }
     uint8_t q = unit[unit_quant_offset(type, i)];
     if (type == ZQ_Q4_K) {
         const __half *hd = reinterpret_cast<const __half *>(unit);

@@ -51,9 +51,15 @@ __host__ __device__ inline FormatInfo format_info(uint32_t t) {
     case ZQ_IQ4_NL: return {ZQ_IQ4_NL, 32, 18, 144};
     case ZQ_Q8_0: return {ZQ_Q8_0, 32, 34, 272};
     case ZQ_Q4_K: return {ZQ_Q4_K, 256, 144, 144};
+    case ZQ_Q5_K: return {ZQ_Q5_K, 256, 176, 176};
+    case ZQ_Q6_K: return {ZQ_Q6_K, 256, 210, 210};
     default: return {0, 0, 0, 0};
     }
 }
+
+// Q5_K and Q6_K (src/weight/codec/ggml.rs:425-469): resident in their GGUF layout, dequantised bit-exactly, and
+// multiplied through the f16 operand pass + tensor-core GEMM at every batch size (no decode kernel of their own yet).
+__host__ __device__ inline bool is_operand_pass_only(uint32_t type) { return type == ZQ_Q5_K || type == ZQ_Q6_K; }
 
 // Byte offset, inside a resident unit, of the quant byte that holds element `i` (0..255) of the unit.
 __host__ __device__ inline int unit_quant_offset(uint32_t type, int i) {

@@ -11,9 +11,9 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "lib", "libzq_b200.so")
 
-Q4_0, Q8_0, Q4_K, IQ4_NL = 2, 8, 12, 20
+Q4_0, Q8_0, Q4_K, Q5_K, Q6_K, IQ4_NL = 2, 8, 12, 13, 14, 20
 F32, F16, BF16 = 0, 1, 2
-BLOCK = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), IQ4_NL: (32, 18)}
+BLOCK = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210), IQ4_NL: (32, 18)}
 
 
 class ZqError(C.Structure):
