@@ -542,14 +542,23 @@ def cpu_baseline_sample():
     orc, work, xs = _cpu_sweep(batches)
     orc.set_threads(0)
     cores = orc.threads()
+    def one_pass():
+        done = 0
+        for m in batches:
+            for fmt, k, n, data in work:
+                orc.linear(fmt, data, n, k, xs[k][:m])
+                done += algorithmic_bytes(k, n, m)
+        return done
+
+    one_pass()  # untimed: page in the weights, start the worker threads
     t0 = time.perf_counter()
-    total = 0
-    for m in batches:
-        for fmt, k, n, data in work:
-            orc.linear(fmt, data, n, k, xs[k][:m])
-            total += algorithmic_bytes(k, n, m)
+    total, passes = 0, 0
+    while passes < 3 or time.perf_counter() - t0 < 10.0:  # about 10 s of CPU work
+        total += one_pass()
+        passes += 1
     dt = time.perf_counter() - t0
-    return {"value": round(total / dt / 1e9, 3), "unit": "GB/s", "cores": cores, "kind": "port", "sample": "batch 1 and 4 of all 10 matrices, one pass", "seconds": round(dt, 2)}
+    return {"value": round(total / dt / 1e9, 3), "unit": "GB/s", "cores": cores, "kind": "port", "sample": f"batch 1 and 4 of all 10 matrices, {passes} passes after one warm-up pass",
+            "seconds": round(dt, 2)}
 
 
 def run_reference(args):

@@ -166,4 +166,4 @@ def test_prepare_weight_rejects_wrong_sizes():
     with pytest.raises(ffi.ZqFailure):
         ctx().prepare_weight(H.Q4_K, np.zeros(144, dtype=np.uint8), 1, 255)
     with pytest.raises(ffi.ZqFailure):
-        ctx().prepare_weight(13, np.zeros(176, dtype=np.uint8), 1, 256)
+        ctx().prepare_weight(10, np.zeros(84, dtype=np.uint8), 1, 256)  # Q2_K: not a type of this path
