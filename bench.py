@@ -355,6 +355,8 @@ def run_ours(args):
         torch.cuda.empty_cache()
         if world == 1 and args.extras in ("all", "prefill"):
             extras["prefill_gemm"] = bench_prefill(ctx, device, args)
+        if world == 1 and args.extras in ("all", "prefill"):
+            extras["kquant_decode"] = bench_kquant_decode(ctx, device)
         if args.extras in ("all", "moe"):
             extras["moe"] = bench_moe(ctx, device, args, world, rank)
     if rank != 0:
@@ -391,6 +393,42 @@ def _time_ms(fn, reps):
     e1.record()
     torch.cuda.synchronize()
     return e0.elapsed_time(e1) / reps
+
+
+def bench_kquant_decode(ctx, device):
+    """Q5_K and Q6_K, one activation row, 5120 -> 17408 (the CUDA-core decode kernel of these two types): four distinct
+    weights (245 / 292 MB, larger than L2) used in turn; GB/s of GGUF bytes."""
+    import numpy as np
+    import torch
+
+    from zllm_b200 import Q5_K, Q6_K
+    from zllm_b200.ffi import BLOCK
+
+    k, n = 5120, 17408
+    out = {"shape": "5120->17408, 1 row, f32 in/out", "unit": "GB/s"}
+    x = torch.randn((1, k), device=device, dtype=torch.float32)
+    for fmt, name in ((Q5_K, "q5_k"), (Q6_K, "q6_k")):
+        e, b = BLOCK[fmt]
+        scale = torch.from_numpy(np.frombuffer(np.float16(3e-4).tobytes(), dtype=np.uint8).copy()).to(device)
+        weights = []
+        for i in range(4):
+            packed = torch.randint(0, 256, (n * k // e, b), device=device, dtype=torch.uint8)
+            off = 208 if fmt == Q6_K else 0
+            packed[:, off:off + 2] = scale
+            if fmt == Q5_K:
+                packed[:, 2:4] = scale
+            weights.append(ctx.prepare_weight(fmt, packed.reshape(-1), n, k))
+            del packed
+
+        def sweep():
+            for w in weights:
+                ctx.linear(x, w)
+
+        sweep()
+        ms = _time_ms(sweep, 5) / len(weights)
+        out[name] = {"us_per_launch": round(ms * 1e3, 2), "gbs": round(n * k // e * b / ms / 1e6, 1)}
+        del weights
+    return out
 
 
 def bench_prefill(ctx, device, args):

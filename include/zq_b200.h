@@ -31,9 +31,9 @@ typedef struct zq_moe_experts zq_moe_experts;
 typedef struct zq_error { char message[512]; } zq_error;
 
 /* GGUF tensor type ids (src/weight/container/gguf.rs:112-151).  Q5_K and Q6_K (src/weight/codec/ggml.rs:425-469;
- * reference CUDA kernels src/kernel/cuda/linear.rs:1167-1234, 1967-2101) dequantise bit-exactly and run every linear
- * call, one activation row included, through the f16 operand pass and the tensor-core GEMM: they have no decode
- * kernel, no encoder (zq_quantize) and no allocation-free entry yet. */
+ * reference CUDA kernels src/kernel/cuda/linear.rs:1167-1234, 1967-2101) dequantise bit-exactly; zq_linear with up to
+ * 8 activation rows runs a CUDA-core decode kernel on the packed bytes, more rows and gated pairs the f16 operand pass
+ * and the tensor-core GEMM.  They have no encoder (zq_quantize) and no allocation-free entry. */
 enum { ZQ_Q4_0 = 2, ZQ_Q8_0 = 8, ZQ_Q4_K = 12, ZQ_Q5_K = 13, ZQ_Q6_K = 14, ZQ_IQ4_NL = 20 };
 enum { ZQ_F32 = 0, ZQ_F16 = 1, ZQ_BF16 = 2 };
 enum { ZQ_OK = 0, ZQ_ERR_SHAPE = 1, ZQ_ERR_UNSUPPORTED = 2, ZQ_ERR_CUDA = 3, ZQ_ERR_ARG = 4, ZQ_ERR_DEVICE_STATUS = 5, ZQ_ERR_DIST = 6 };

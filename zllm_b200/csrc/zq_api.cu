@@ -334,6 +334,7 @@ static int check_linear(zq_ctx *ctx, const zq_weight *w, const void *x, int x_dt
 int zq_linear(zq_ctx *ctx, const zq_weight *w, const void *dev_x, int x_dtype, size_t m, void *dev_y, int y_dtype, const void *dev_residual, zq_error *err) {
     int rc = check_linear(ctx, w, dev_x, x_dtype, m, dev_y, y_dtype, err);
     if (rc) return rc;
+    if (is_operand_pass_only(w->type) && m <= 8) return launch_gemv_kq(ctx, w, dev_x, x_dtype, m, dev_y, y_dtype, dev_residual, err);
     if (m <= 16 && !is_operand_pass_only(w->type)) return launch_gemv(ctx, w, nullptr, dev_x, x_dtype, m, dev_y, y_dtype, dev_residual, err);
     return launch_gemm(ctx, w, nullptr, dev_x, x_dtype, m, dev_y, y_dtype, dev_residual, err);
 }

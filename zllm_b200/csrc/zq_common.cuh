@@ -57,8 +57,9 @@ __host__ __device__ inline FormatInfo format_info(uint32_t t) {
     }
 }
 
-// Q5_K and Q6_K (src/weight/codec/ggml.rs:425-469): resident in their GGUF layout, dequantised bit-exactly, and
-// multiplied through the f16 operand pass + tensor-core GEMM at every batch size (no decode kernel of their own yet).
+// Q5_K and Q6_K (src/weight/codec/ggml.rs:425-469): resident in their GGUF layout, dequantised bit-exactly; plain
+// projections of up to 8 activation rows run a CUDA-core decode kernel (zq_gemv_kq.cu), everything else (more rows,
+// gated pairs) the f16 operand pass + tensor-core GEMM.  No integer-MMA kernel, tensor maps or encoder for them.
 __host__ __device__ inline bool is_operand_pass_only(uint32_t type) { return type == ZQ_Q5_K || type == ZQ_Q6_K; }
 
 // Byte offset, inside a resident unit, of the quant byte that holds element `i` (0..255) of the unit.
@@ -294,6 +295,7 @@ int launch_dequantize_f16(zq_ctx *ctx, const zq_weight *w, __half *out, zq_error
 int launch_dequantize_f16_batch(zq_ctx *ctx, const zq_weight *const *weights, __half *const *outs, size_t count, zq_error *err);
 int launch_quantize(zq_ctx *ctx, uint32_t type, const float *values, size_t rows, size_t cols, void *out, zq_error *err);
 int launch_gemv(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const void *x, int x_dtype, size_t m, void *y, int y_dtype, const void *residual, zq_error *err);
+int launch_gemv_kq(zq_ctx *ctx, const zq_weight *w, const void *x, int x_dtype, size_t m, void *y, int y_dtype, const void *residual, zq_error *err);
 int launch_gemv_noalloc(zq_ctx *ctx, const zq_weight *w, const void *x, int x_dtype, size_t m, void *y, int y_dtype, zq_error *err);
 int launch_gemm(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const void *x, int x_dtype, size_t m, void *y, int y_dtype, const void *residual, zq_error *err);
 }  // namespace zq
