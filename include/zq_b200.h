@@ -85,6 +85,12 @@ int zq_quantize(zq_ctx *ctx, uint32_t ggml_type, const float *dev_values, size_t
 int zq_linear(zq_ctx *ctx, const zq_weight *w, const void *dev_x, int x_dtype, size_t m, void *dev_y, int y_dtype, const void *dev_residual, zq_error *err);
 /* Backend::dual_linear / triple_linear (src/backend/mod.rs:444-451): up to 3 weights share one input. */
 int zq_linear_multi(zq_ctx *ctx, const zq_weight *const *w, size_t n_weights, const void *dev_x, int x_dtype, size_t m, void *const *dev_y, int y_dtype, zq_error *err);
+/* Backend::rmsnorm_linear / rmsnorm_dual_linear (src/backend/mod.rs:455-464): RMSNorm of every input row
+ * (src/kernel/cpu/rmsnorm.rs:7-41: x * 1/sqrt(mean(x^2) + eps) * (norm_weight + weight_offset); offset 0 = plain,
+ * 1 = the "Gemma" form), then 1 to 3 linear layers on the normalised rows.  `dev_norm_weight`: f32 [cols].  The
+ * normalised rows stay in a context buffer (f32); the projections start under the normalisation kernel. */
+int zq_rmsnorm_linear(zq_ctx *ctx, const zq_weight *const *w, size_t n_weights, const void *dev_x, int x_dtype, size_t m, const float *dev_norm_weight, float eps, float weight_offset, void *const *dev_y,
+                      int y_dtype, zq_error *err);
 /* gated_linear_q4_k_silu_f16 / gated_linear_q4_0_silu_f16 (src/kernel/cuda/linear.rs:1683, 1916) behind
  * Backend::gated_linear (src/backend/mod.rs:467): y = silu(gate x) * (up x). */
 int zq_gated_silu(zq_ctx *ctx, const zq_weight *gate, const zq_weight *up, const void *dev_x, int x_dtype, size_t m, void *dev_y, int y_dtype, zq_error *err);

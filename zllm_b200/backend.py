@@ -172,6 +172,28 @@ class B200Context:
         ffi.call("zq_linear_multi", self.handle, wa, len(weights), _ptr(x), _dt(x), m, ya, _DTYPES[out_dtype])
         return ys
 
+    def rmsnorm_linear_multi(self, x: torch.Tensor, norm_weight: torch.Tensor, eps: float, weights: Sequence[Weight], out_dtype=None, weight_offset: float = 0.0):
+        """RMSNorm of every row, then the projections (``Backend::rmsnorm_linear`` / ``rmsnorm_dual_linear``,
+        src/backend/mod.rs:455-464); ``weight_offset`` 1.0 is the Gemma form of the norm."""
+        x = x.contiguous()
+        m = self._rows(x, weights[0].cols)
+        norm_weight = norm_weight.contiguous().float()
+        if norm_weight.numel() != weights[0].cols:
+            raise ffi.ZqFailure(1, f"norm weight has {norm_weight.numel()} elements, input width is {weights[0].cols}")
+        out_dtype = out_dtype or x.dtype
+        ys = [torch.empty((m, w.rows), dtype=out_dtype, device=x.device) for w in weights]
+        wa = (C.c_void_p * len(weights))(*[w.handle for w in weights])
+        ya = (C.c_void_p * len(weights))(*[y.data_ptr() for y in ys])
+        ffi.call("zq_rmsnorm_linear", self.handle, wa, len(weights), _ptr(x), _dt(x), m, _ptr(norm_weight), float(eps), float(weight_offset), ya, _DTYPES[out_dtype])
+        return ys
+
+    def rmsnorm_linear(self, x, norm_weight, eps: float, w: Weight, out_dtype=None, weight_offset: float = 0.0):
+        return self.rmsnorm_linear_multi(x, norm_weight, eps, [w], out_dtype, weight_offset)[0]
+
+    def rmsnorm_dual_linear(self, x, norm_weight, eps: float, first: Weight, second: Weight, out_dtype=None, weight_offset: float = 0.0):
+        a, b = self.rmsnorm_linear_multi(x, norm_weight, eps, [first, second], out_dtype, weight_offset)
+        return a, b
+
     def dual_linear(self, x, first: Weight, second: Weight, out_dtype=None):
         a, b = self.linear_multi(x, [first, second], out_dtype)
         return a, b

@@ -78,6 +78,18 @@ int ensure_scratch_mid(zq_ctx *ctx, size_t bytes, zq_error *err) {
     return ZQ_OK;
 }
 
+int ensure_scratch_norm(zq_ctx *ctx, size_t bytes, zq_error *err) {
+    if (bytes <= ctx->norm_bytes) return ZQ_OK;
+    ZQ_CUDA_CHECK(cudaStreamSynchronize(ctx->stream), err);
+    if (ctx->norm) cudaFree(ctx->norm);
+    ctx->norm = nullptr;
+    ctx->norm_bytes = 0;
+    size_t rounded = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+    ZQ_CUDA_CHECK(cudaMalloc(&ctx->norm, rounded), err);
+    ctx->norm_bytes = rounded;
+    return ZQ_OK;
+}
+
 static int check_dtype(int dtype, const char *what, zq_error *err) {
     if (dtype != ZQ_F32 && dtype != ZQ_F16 && dtype != ZQ_BF16) return set_error(err, ZQ_ERR_ARG, "%s: unknown dtype %d", what, dtype);
     return ZQ_OK;
@@ -155,6 +167,7 @@ void zq_ctx_destroy(zq_ctx *ctx) {
     if (ctx->gemv_counters) cudaFree(ctx->gemv_counters);
     if (ctx->workspace) cudaFree(ctx->workspace);
     if (ctx->mid) cudaFree(ctx->mid);
+    if (ctx->norm) cudaFree(ctx->norm);
     if (ctx->xq) cudaFree(ctx->xq);
     if (ctx->moe_ws) cudaFree(ctx->moe_ws);
     if (ctx->status_host) cudaFreeHost(ctx->status_host);
@@ -349,6 +362,25 @@ int zq_linear_multi(zq_ctx *ctx, const zq_weight *const *w, size_t n_weights, co
         if (rc) return rc;
     }
     return ZQ_OK;
+}
+
+int zq_rmsnorm_linear(zq_ctx *ctx, const zq_weight *const *w, size_t n_weights, const void *dev_x, int x_dtype, size_t m, const float *dev_norm_weight, float eps, float weight_offset, void *const *dev_y,
+                      int y_dtype, zq_error *err) {
+    if (!ctx || !w || !dev_y || !dev_x || !dev_norm_weight || n_weights == 0 || n_weights > 3) return set_error(err, ZQ_ERR_ARG, "zq_rmsnorm_linear: null argument, or not 1 to 3 weights");
+    for (size_t i = 0; i < n_weights; ++i) {
+        if (!w[i] || !dev_y[i] || w[i]->ctx != ctx) return set_error(err, ZQ_ERR_ARG, "zq_rmsnorm_linear: weight %zu is null or belongs to another context", i);
+        if (w[i]->cols != w[0]->cols) return set_error(err, ZQ_ERR_SHAPE, "zq_rmsnorm_linear: weights must share the input width");
+    }
+    int rc = check_dtype(x_dtype, "rmsnorm input", err);
+    if (rc) return rc;
+    if (m == 0) return set_error(err, ZQ_ERR_SHAPE, "zq_rmsnorm_linear: input has no rows");
+    if (!(eps >= 0.0f)) return set_error(err, ZQ_ERR_ARG, "zq_rmsnorm_linear: eps must be non-negative");
+    const size_t cols = w[0]->cols;
+    rc = ensure_scratch_norm(ctx, m * cols * sizeof(float), err);
+    if (rc) return rc;
+    rc = launch_rmsnorm(ctx, dev_x, x_dtype, m, cols, dev_norm_weight, eps, weight_offset, reinterpret_cast<float *>(ctx->norm), err);
+    for (size_t i = 0; i < n_weights && !rc; ++i) rc = zq_linear(ctx, w[i], ctx->norm, ZQ_F32, m, dev_y[i], y_dtype, nullptr, err);
+    return rc;
 }
 
 int zq_gated_silu(zq_ctx *ctx, const zq_weight *gate, const zq_weight *up, const void *dev_x, int x_dtype, size_t m, void *dev_y, int y_dtype, zq_error *err) {

@@ -233,6 +233,8 @@ struct zq_ctx {
     // Activated intermediate [m, I] of gated_mlp (grows on demand).
     void *mid = nullptr;
     size_t mid_bytes = 0;
+    void *norm = nullptr;  // normalised activations of zq_rmsnorm_linear (f32)
+    size_t norm_bytes = 0;
     // Device status word (mapped pinned host memory so the host can read it without a copy).
     uint32_t *status_host = nullptr;
     uint32_t *status_dev = nullptr;
@@ -286,6 +288,8 @@ int launch_gemm_f16(zq_ctx *ctx, const __half *w, size_t rows, size_t k, const _
 int launch_to_f16(zq_ctx *ctx, const void *x, int x_dtype, __half *out, size_t n, zq_error *err);
 int launch_gemm_grouped(zq_ctx *ctx, const __half *w, const __half *w2, size_t mats, size_t rows, size_t k, const __half *x, size_t x_rows, const int4 *items, int n_items, void *y, int y_dtype, zq_error *err);
 int ensure_scratch_mid(zq_ctx *ctx, size_t bytes, zq_error *err);
+int ensure_scratch_norm(zq_ctx *ctx, size_t bytes, zq_error *err);
+int launch_rmsnorm(zq_ctx *ctx, const void *x, int x_dtype, size_t m, size_t cols, const float *weight, float eps, float weight_offset, float *out, zq_error *err);
 int make_weight_map(const zq_weight *w, int box_words, int box_rows, CUtensorMap *out, zq_error *err);
 
 // Launchers implemented in the .cu files.
