@@ -4,14 +4,13 @@
 // weight instead of dequantising the whole matrix to f16 first.
 //
 // One warp per weight row, f32 arithmetic on the CUDA cores.  A lane owns one 32-bit word of a super-block's low
-// quant bytes: 4 consecutive positions of two scale groups (low nibbles, high nibbles) = 8 weights, decoded exactly
-// as the codec decodes them ((d*sc)*q - dmin*m, (d*scale)*q), then multiplied into up to 4 activation rows at a
-// time; the 32 lanes read a super-block's 128 low bytes as one coalesced line.  Q6_K blocks are 210 bytes, so their
+// quant bytes: 4 consecutive positions of two scale groups (low nibbles, high nibbles) = 8 weights, whose integer
+// codes are multiplied into up to 4 activation rows at a time and scaled once per group (the codec's value
+// (d*sc)*q - dmin*m resp. (d*scale)*q, with the scale factored out of the 4-element sum); the 32 lanes read a super-block's 128 low bytes as one coalesced line.  Q6_K blocks are 210 bytes, so their
 // fields are only 2-byte aligned and are read as 16-bit loads.  Activations come through the read-only cache (a
 // row of K floats is shared by all warps of the SM).  Sums are combined by warp shuffles; no shared memory, no
-// scratch.  This is the plain form: no TMA ring, no tensor cores, scalar unpacking of every byte — a first decode path
-// for these two types, about twice as fast as dequantising the matrix to f16 for a one-row call, and far from the
-// HBM roofline (see the measurement at the kernel).
+// scratch.  This is the plain form: no TMA ring, no tensor cores — a first decode path for these two types (see the
+// measurements at the kernel).
 #include "zq_common.cuh"
 
 namespace zq {
@@ -32,69 +31,118 @@ __device__ __forceinline__ void kq_load_act4(const void *x, int dtype, size_t in
     }
 }
 
-// The 8 weights of lane `lane` in super-block `unit`: w[0..3] at column offset c0 .. c0+3, w[4..7] at c1 .. c1+3.
+// Byte j of `codes` (0..255) as a float, minus `bias`: the byte is placed under the exponent of 2^23, where it is
+// the integer 2^23 + byte exactly, and the subtraction is exact; no integer -> float conversion instruction.
+template <int J>
+__device__ __forceinline__ float kq_byte_to_float(uint32_t codes, float bias_plus_2p23) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(codes), "r"(0x4B000000u), "n"(0x7540 + J));
+    return __fsub_rn(__uint_as_float(r), bias_plus_2p23);
+}
+
+// What lane `lane` holds of super-block `unit`: two groups of 4 integer codes (as floats, Q6_K already minus 32) at
+// column offsets c0 .. c0+3 and c1 .. c1+3, and per group the factors of  weight = a * code - b.
+struct KqLane {
+    float q0[4], q1[4];
+    float a0, b0, a1, b1;
+    int c0, c1;
+};
+
+// The words a lane reads of one super-block.
+struct KqRaw {
+    uint32_t lo, hi;      // 4 low-quant bytes, the 4 high-bit bytes that go with them
+    uint32_t s0, s1, s2;  // Q5_K: the 12 scale bytes; Q6_K: s0 = the two i8 scales (low-nibble group, high-nibble group)
+    uint32_t dd;          // Q5_K: d | dmin << 16; Q6_K: d
+};
+
 template <uint32_t TYPE>
-__device__ __forceinline__ void kq_lane_weights(const uint8_t *unit, int lane, float (&w)[8], int &c0, int &c1) {
+__device__ __forceinline__ KqRaw kq_lane_load(const uint8_t *unit, int lane) {
+    KqRaw r;
     if constexpr (TYPE == ZQ_Q5_K) {
         // d, dmin, 12 scale bytes, 32 high-bit bytes at 16, 128 low-nibble bytes at 48; 176-byte blocks: words are aligned
-        const uint32_t dd = *reinterpret_cast<const uint32_t *>(unit);
-        const float d = __half2float(__ushort_as_half((unsigned short)(dd & 0xFFFFu))), dmin = __half2float(__ushort_as_half((unsigned short)(dd >> 16)));
-        const uint8_t *scales = unit + 4;
+        const uint32_t *u32 = reinterpret_cast<const uint32_t *>(unit);
+        r.dd = u32[0];
+        r.s0 = u32[1];
+        r.s1 = u32[2];
+        r.s2 = u32[3];
         const int pair = lane >> 3, j = (lane & 7) * 4;
-        const uint32_t lo = *reinterpret_cast<const uint32_t *>(unit + 48 + pair * 32 + j);
-        const uint32_t hb = *reinterpret_cast<const uint32_t *>(unit + 16 + j);
+        r.lo = u32[(48 + pair * 32 + j) >> 2];
+        r.hi = u32[(16 + j) >> 2];
+    } else {
+        // 128 low-nibble bytes, 64 high-bit bytes at 128, 16 i8 scales at 192, d at 208; 210-byte blocks: 16-bit loads
+        const uint16_t *u16 = reinterpret_cast<const uint16_t *>(unit);
+        const int half = lane >> 4, o = (lane & 15) * 4;  // byte offset inside the half's 64 low bytes
+        const int index = o & 31, odd = o >> 5;           // positions index..index+3; odd: quarters 1 and 3, else 0 and 2
+        const int lw = (half * 64 + o) >> 1, hw = (128 + half * 32 + index) >> 1;
+        r.lo = (uint32_t)u16[lw] | ((uint32_t)u16[lw + 1] << 16);
+        r.hi = (uint32_t)u16[hw] | ((uint32_t)u16[hw + 1] << 16);
+        const uint8_t *scales = unit + 192 + half * 8 + (index >> 4);
+        r.s0 = (uint32_t)scales[2 * odd] | ((uint32_t)scales[2 * (odd + 2)] << 8);
+        r.s1 = r.s2 = 0;
+        r.dd = u16[104];
+    }
+    return r;
+}
+
+template <uint32_t TYPE>
+__device__ __forceinline__ KqLane kq_lane_unpack(const KqRaw &r, int lane) {
+    KqLane L;
+    uint32_t code0, code1;  // four codes each, one per byte
+    float bias;
+    if constexpr (TYPE == ZQ_Q5_K) {
+        const float d = __half2float(__ushort_as_half((unsigned short)(r.dd & 0xFFFFu))), dmin = __half2float(__ushort_as_half((unsigned short)(r.dd >> 16)));
+        const int pair = lane >> 3, j = (lane & 7) * 4;
+        // scale bytes 0..3 in s0, 4..7 in s1, 8..11 in s2 (src/weight/codec/ggml.rs:471-477)
         float dsc[2], dmn[2];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int g = 2 * pair + h;
-            int sc, mn;
+            uint32_t sc, mn;
             if (g < 4) {
-                sc = scales[g] & 0x3f;
-                mn = scales[g + 4] & 0x3f;
+                sc = (r.s0 >> (8 * g)) & 0x3Fu;
+                mn = (r.s1 >> (8 * g)) & 0x3Fu;
             } else {
-                sc = (scales[g + 4] & 0x0f) | ((scales[g - 4] >> 6) << 4);
-                mn = (scales[g + 4] >> 4) | ((scales[g] >> 6) << 4);
+                const int t = 8 * (g - 4);
+                sc = ((r.s2 >> t) & 0x0Fu) | (((r.s0 >> (t + 6)) & 3u) << 4);
+                mn = ((r.s2 >> (t + 4)) & 0x0Fu) | (((r.s1 >> (t + 6)) & 3u) << 4);
             }
             dsc[h] = __fmul_rn(d, (float)sc);
             dmn[h] = __fmul_rn(dmin, (float)mn);
         }
-#pragma unroll
-        for (int b = 0; b < 4; ++b) {
-            const uint32_t byte = (lo >> (8 * b)) & 0xFFu, high = (hb >> (8 * b)) & 0xFFu;
-            const int q0 = (int)(byte & 0x0Fu) + (int)(((high >> (2 * pair)) & 1u) << 4);
-            const int q1 = (int)(byte >> 4) + (int)(((high >> (2 * pair + 1)) & 1u) << 4);
-            w[b] = __fsub_rn(__fmul_rn(dsc[0], (float)q0), dmn[0]);
-            w[4 + b] = __fsub_rn(__fmul_rn(dsc[1], (float)q1), dmn[1]);
-        }
-        c0 = (2 * pair) * 32 + j;
-        c1 = c0 + 32;
+        code0 = (r.lo & 0x0F0F0F0Fu) | (((r.hi >> (2 * pair)) & 0x01010101u) << 4);
+        code1 = ((r.lo >> 4) & 0x0F0F0F0Fu) | (((r.hi >> (2 * pair + 1)) & 0x01010101u) << 4);
+        bias = 8388608.0f;
+        L.a0 = dsc[0]; L.b0 = dmn[0]; L.a1 = dsc[1]; L.b1 = dmn[1];
+        L.c0 = (2 * pair) * 32 + j;
+        L.c1 = L.c0 + 32;
     } else {
-        // 128 low-nibble bytes, 64 high-bit bytes at 128, 16 i8 scales at 192, d at 208; 210-byte blocks: 16-bit loads
-        const uint16_t *u16 = reinterpret_cast<const uint16_t *>(unit);
-        const float d = __half2float(__ushort_as_half(u16[104]));
-        const int half = lane >> 4, o = (lane & 15) * 4;       // byte offset inside the half's 64 low bytes
-        const int index = o & 31, odd = o >> 5;                // positions index..index+3; odd: quarters 1 and 3, else 0 and 2
-        const uint32_t lo = (uint32_t)u16[(half * 64 + o) >> 1] | ((uint32_t)u16[((half * 64 + o) >> 1) + 1] << 16);
-        const uint32_t hv = (uint32_t)u16[(128 + half * 32 + index) >> 1] | ((uint32_t)u16[((128 + half * 32 + index) >> 1) + 1] << 16);
-        const int8_t *scales = reinterpret_cast<const int8_t *>(unit + 192) + half * 8 + (index >> 4);
-        const float ds0 = __fmul_rn(d, (float)scales[2 * odd]), ds1 = __fmul_rn(d, (float)scales[2 * (odd + 2)]);
-#pragma unroll
-        for (int b = 0; b < 4; ++b) {
-            const uint32_t byte = (lo >> (8 * b)) & 0xFFu, high = (hv >> (8 * b)) & 0xFFu;
-            const int q0 = (int)((byte & 0x0Fu) | (((high >> (2 * odd)) & 3u) << 4)) - 32;
-            const int q1 = (int)((byte >> 4) | (((high >> (2 * odd + 4)) & 3u) << 4)) - 32;
-            w[b] = __fmul_rn(ds0, (float)q0);
-            w[4 + b] = __fmul_rn(ds1, (float)q1);
-        }
-        c0 = half * 128 + odd * 32 + index;
-        c1 = c0 + 64;
+        const float d = __half2float(__ushort_as_half((unsigned short)r.dd));
+        const int half = lane >> 4, o = (lane & 15) * 4;
+        const int index = o & 31, odd = o >> 5;
+        L.a0 = __fmul_rn(d, (float)(int8_t)(r.s0 & 0xFFu));
+        L.a1 = __fmul_rn(d, (float)(int8_t)((r.s0 >> 8) & 0xFFu));
+        L.b0 = L.b1 = 0.f;
+        code0 = (r.lo & 0x0F0F0F0Fu) | (((r.hi >> (2 * odd)) & 0x03030303u) << 4);
+        code1 = ((r.lo >> 4) & 0x0F0F0F0Fu) | (((r.hi >> (2 * odd + 4)) & 0x03030303u) << 4);
+        bias = 8388608.0f + 32.0f;  // codes are stored plus 32
+        L.c0 = half * 128 + odd * 32 + index;
+        L.c1 = L.c0 + 64;
     }
+    L.q0[0] = kq_byte_to_float<0>(code0, bias); L.q0[1] = kq_byte_to_float<1>(code0, bias);
+    L.q0[2] = kq_byte_to_float<2>(code0, bias); L.q0[3] = kq_byte_to_float<3>(code0, bias);
+    L.q1[0] = kq_byte_to_float<0>(code1, bias); L.q1[1] = kq_byte_to_float<1>(code1, bias);
+    L.q1[2] = kq_byte_to_float<2>(code1, bias); L.q1[3] = kq_byte_to_float<3>(code1, bias);
+    return L;
 }
 
-// Measured on 5120 -> 17408, one activation row: Q6_K 62.6 us (1.17 TB/s of packed bytes), Q5_K 74.0 us (0.83 TB/s).
-// Variants measured and not kept: the loads of 4 super-blocks issued (through the read-only path) before the first is
-// decoded (1.04 / 0.65 TB/s), and 4 rows per warp with the loads of 2 super-blocks each (0.90 / 0.58) — registers cost
-// more than bytes in flight win; the kernel is bound by the scalar unpacking.
+// Measured on 5120 -> 17408, one activation row.  Every byte unpacked by scalar shifts and integer -> float
+// conversions: Q6_K 62.6 us (1.17 TB/s of packed bytes), Q5_K 74.0 us (0.83 TB/s).  The form below (four codes
+// assembled at a time with word-wide masks, turned into floats by a byte permute, a group's scale applied once to
+// a * sum(code * x) - b * sum(x)): 56.4 us (1.30 TB/s) and 64.5 us (0.95 TB/s).  Issuing loads ahead — one super-block
+// (62.5 / 72.5 us), four super-blocks (70 / 94 us), four rows per warp (81 / 106 us) — made it slower each time:
+// the extra registers cost resident warps, and a warp holds only ~210 bytes in flight per load round, so the kernel
+// sits at about a sixth of the HBM roofline until it stages whole rows through shared memory the way the Q4_K
+// kernels do.
 template <uint32_t TYPE, int M>
 __global__ void __launch_bounds__(256) gemv_kq_kernel(const uint8_t *__restrict__ data, size_t row_pitch, int units_per_row, int unit_bytes, int n_out, int cols, const void *__restrict__ x, int x_dtype,
                                                       void *__restrict__ y, int y_dtype, const void *__restrict__ residual) {
@@ -105,19 +153,25 @@ __global__ void __launch_bounds__(256) gemv_kq_kernel(const uint8_t *__restrict_
 #pragma unroll
         for (int m = 0; m < M; ++m) acc[m] = 0.f;
         for (int u = 0; u < units_per_row; ++u) {
-            float w[8];
-            int c0, c1;
-            kq_lane_weights<TYPE>(wrow + (size_t)u * unit_bytes, lane, w, c0, c1);
+            const KqLane L = kq_lane_unpack<TYPE>(kq_lane_load<TYPE>(wrow + (size_t)u * unit_bytes, lane), lane);
             const size_t k0 = (size_t)u * kUnitWeights;
 #pragma unroll
             for (int m = 0; m < M; ++m) {
                 float a[4], b[4];
-                kq_load_act4(x, x_dtype, (size_t)m * cols + k0 + c0, a);
-                kq_load_act4(x, x_dtype, (size_t)m * cols + k0 + c1, b);
+                kq_load_act4(x, x_dtype, (size_t)m * cols + k0 + L.c0, a);
+                kq_load_act4(x, x_dtype, (size_t)m * cols + k0 + L.c1, b);
+                float t0 = 0.f, t1 = 0.f;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) acc[m] = fmaf(w[j], a[j], acc[m]);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) acc[m] = fmaf(w[4 + j], b[j], acc[m]);
+                for (int j = 0; j < 4; ++j) {
+                    t0 = fmaf(L.q0[j], a[j], t0);
+                    t1 = fmaf(L.q1[j], b[j], t1);
+                }
+                acc[m] = fmaf(L.a0, t0, acc[m]);
+                acc[m] = fmaf(L.a1, t1, acc[m]);
+                if constexpr (TYPE == ZQ_Q5_K) {
+                    acc[m] = fmaf(-L.b0, (a[0] + a[1]) + (a[2] + a[3]), acc[m]);
+                    acc[m] = fmaf(-L.b1, (b[0] + b[1]) + (b[2] + b[3]), acc[m]);
+                }
             }
         }
 #pragma unroll
