@@ -139,6 +139,10 @@ def run_ours(args):
         print(json.dumps({"only_prefill": m, "launches": ctx.launch_count}))
         return
 
+    if args.only_kquant:
+        print(json.dumps({"only_kquant": bench_kquant_decode(ctx, device), "launches": ctx.launch_count}))
+        return
+
     if args.only_moe:
         out = bench_moe(ctx, device, args, world, rank, only=args.only_moe)
         print(json.dumps({"only_moe": args.only_moe, "moe": out, "launches": ctx.launch_count}))
@@ -653,6 +657,7 @@ def main():
     ap.add_argument("--f16-gemv", action="store_true", help="decode on the f16 warp-MMA kernels instead of the integer-MMA kernel (A/B aid)")
     ap.add_argument("--stack-layers", type=int, default=64, help="layers of the prefill GEMM stack (configs[2] names 64)")
     ap.add_argument("--only-prefill", type=int, default=0, help="profiling aid: run only a few prefill GEMMs (Q4_K 5120->17408) at this token count and exit")
+    ap.add_argument("--only-kquant", action="store_true", help="profiling aid: run only the Q5_K / Q6_K one-row decode measurement and exit")
     ap.add_argument("--only-moe", default=None, choices=["decode_m64", "prefill_m8192"], help="profiling aid: run only this MoE case and exit")
     ap.add_argument("--only", default=None, help="restrict the sweep to one case, e.g. q4_k:5120x17408:1 (format:KxN:batch); for profiling")
     args = ap.parse_args()
