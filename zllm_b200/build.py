@@ -4,6 +4,7 @@ from __future__ import annotations
 import os
 import subprocess
 import sys
+from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
@@ -34,17 +35,23 @@ def build(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(OUT_DIR, exist_ok=True)
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
     headers.append(os.path.join(os.path.dirname(HERE), "include", "zq_b200.h"))
-    objects = []
+    objects = [os.path.join(OUT_DIR, src.replace(".cu", ".o")) for src in SOURCES]
     logs = []
-    for src in SOURCES:
+
+    def compile_one(src: str):
         path = os.path.join(CSRC, src)
         obj = os.path.join(OUT_DIR, src.replace(".cu", ".o"))
-        objects.append(obj)
-        if force or _stale(obj, [path] + headers):
-            r = subprocess.run([_nvcc(), *NVCC_FLAGS, "-c", path, "-o", obj], capture_output=True, text=True)
-            logs.append(r.stderr)
-            if r.returncode != 0:
-                sys.stderr.write(r.stdout + r.stderr)
+        if not (force or _stale(obj, [path] + headers)):
+            return src, 0, ""
+        r = subprocess.run([_nvcc(), *NVCC_FLAGS, "-c", path, "-o", obj], capture_output=True, text=True)
+        return src, r.returncode, r.stdout + r.stderr
+
+    # the translation units are independent: compile them side by side
+    with ThreadPoolExecutor(max_workers=min(len(SOURCES), os.cpu_count() or 4)) as pool:
+        for src, code, log in pool.map(compile_one, SOURCES):
+            logs.append(log)
+            if code != 0:
+                sys.stderr.write(log)
                 raise RuntimeError(f"nvcc failed on {src}")
     if force or _stale(LIB, objects):
         r = subprocess.run([_nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "--cudart", "static", "-o", LIB, *objects, "-lpthread", "-ldl"], capture_output=True, text=True)

@@ -90,6 +90,15 @@ int ensure_scratch_norm(zq_ctx *ctx, size_t bytes, zq_error *err) {
     return ZQ_OK;
 }
 
+// Every entry point that allocates or launches makes the context's device current first: a host that drives several
+// GPUs from one thread (one context each) must never get memory or a launch on the wrong device.
+int use_device(zq_ctx *ctx, zq_error *err) {
+    int current = -1;
+    if (cudaGetDevice(&current) == cudaSuccess && current == ctx->device) return ZQ_OK;
+    ZQ_CUDA_CHECK(cudaSetDevice(ctx->device), err);
+    return ZQ_OK;
+}
+
 static int check_dtype(int dtype, const char *what, zq_error *err) {
     if (dtype != ZQ_F32 && dtype != ZQ_F16 && dtype != ZQ_BF16) return set_error(err, ZQ_ERR_ARG, "%s: unknown dtype %d", what, dtype);
     return ZQ_OK;
@@ -129,6 +138,21 @@ static int finish_prepare(zq_ctx *ctx, zq_weight *w, zq_error *err) {
 
 using namespace zq;
 
+static int ctx_allocate(zq_ctx *ctx, zq_error *err) {
+    ZQ_CUDA_CHECK(cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking), err);
+    ctx->stream = ctx->own_stream;
+    ctx->gemv_partials_floats = (size_t)ctx->sm_count * 2 * 128 * 16;  // two partial-tile slots (128 rows x 16 activation rows) per CTA
+    ZQ_CUDA_CHECK(cudaMalloc(&ctx->gemv_partials, ctx->gemv_partials_floats * sizeof(float)), err);
+    ctx->gemv_counters_n = 1 << 16;
+    ZQ_CUDA_CHECK(cudaMalloc(&ctx->gemv_counters, ctx->gemv_counters_n * sizeof(uint32_t)), err);
+    ZQ_CUDA_CHECK(cudaMemset(ctx->gemv_counters, 0, ctx->gemv_counters_n * sizeof(uint32_t)), err);
+    ZQ_CUDA_CHECK(cudaHostAlloc(reinterpret_cast<void **>(&ctx->status_host), sizeof(uint32_t), cudaHostAllocMapped), err);
+    *ctx->status_host = 0;
+    ZQ_CUDA_CHECK(cudaHostGetDevicePointer(reinterpret_cast<void **>(&ctx->status_dev), ctx->status_host, 0), err);
+    ZQ_CUDA_CHECK(cudaDeviceSynchronize(), err);
+    return ZQ_OK;
+}
+
 extern "C" {
 
 int zq_ctx_create(int device, zq_ctx **out, zq_error *err) {
@@ -144,17 +168,11 @@ int zq_ctx_create(int device, zq_ctx **out, zq_error *err) {
     zq_ctx *ctx = new zq_ctx();
     ctx->device = device;
     ctx->sm_count = prop.multiProcessorCount;
-    ZQ_CUDA_CHECK(cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking), err);
-    ctx->stream = ctx->own_stream;
-    ctx->gemv_partials_floats = (size_t)ctx->sm_count * 2 * 128 * 16;  // two partial-tile slots (128 rows x 16 activation rows) per CTA
-    ZQ_CUDA_CHECK(cudaMalloc(&ctx->gemv_partials, ctx->gemv_partials_floats * sizeof(float)), err);
-    ctx->gemv_counters_n = 1 << 16;
-    ZQ_CUDA_CHECK(cudaMalloc(&ctx->gemv_counters, ctx->gemv_counters_n * sizeof(uint32_t)), err);
-    ZQ_CUDA_CHECK(cudaMemset(ctx->gemv_counters, 0, ctx->gemv_counters_n * sizeof(uint32_t)), err);
-    ZQ_CUDA_CHECK(cudaHostAlloc(reinterpret_cast<void **>(&ctx->status_host), sizeof(uint32_t), cudaHostAllocMapped), err);
-    *ctx->status_host = 0;
-    ZQ_CUDA_CHECK(cudaHostGetDevicePointer(reinterpret_cast<void **>(&ctx->status_dev), ctx->status_host, 0), err);
-    ZQ_CUDA_CHECK(cudaDeviceSynchronize(), err);
+    int rc = ctx_allocate(ctx, err);
+    if (rc) {
+        zq_ctx_destroy(ctx);  // frees whatever part of the state exists
+        return rc;
+    }
     *out = ctx;
     return ZQ_OK;
 }
@@ -162,7 +180,7 @@ int zq_ctx_create(int device, zq_ctx **out, zq_error *err) {
 void zq_ctx_destroy(zq_ctx *ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
-    cudaStreamSynchronize(ctx->stream);
+    if (ctx->own_stream || ctx->stream) cudaStreamSynchronize(ctx->stream);
     if (ctx->gemv_partials) cudaFree(ctx->gemv_partials);
     if (ctx->gemv_counters) cudaFree(ctx->gemv_counters);
     if (ctx->workspace) cudaFree(ctx->workspace);
@@ -252,6 +270,7 @@ int zq_weight_prepare_device(zq_ctx *ctx, uint32_t ggml_type, const void *dev_by
     if (!dev_bytes) return set_error(err, ZQ_ERR_ARG, "weight prepare: null bytes");
     zq_weight *w = nullptr;
     int rc = prepare_common(ctx, ggml_type, nbytes, rows, cols, &w, err);
+    if (!rc && (rc = use_device(ctx, err))) delete w;
     if (rc) return rc;
     size_t resident = w->rows * w->row_pitch;
     cudaError_t e = cudaMalloc(reinterpret_cast<void **>(&w->data), resident);
@@ -312,6 +331,7 @@ size_t zq_weight_gguf_bytes(const zq_weight *w) { return w ? w->gguf_bytes : 0; 
 
 int zq_dequantize_f32(zq_ctx *ctx, const zq_weight *w, float *dev_out, zq_error *err) {
     if (!ctx || !w || !dev_out) return set_error(err, ZQ_ERR_ARG, "zq_dequantize_f32: null argument");
+    if (int rc = use_device(ctx, err)) return rc;
     return launch_dequantize(ctx, w, nullptr, w->rows, dev_out, ZQ_F32, err);
 }
 
@@ -319,6 +339,7 @@ int zq_gather_rows(zq_ctx *ctx, const zq_weight *w, const uint32_t *dev_row_ids,
     if (!ctx || !w || !dev_out) return set_error(err, ZQ_ERR_ARG, "zq_gather_rows: null argument");
     int rc = check_dtype(out_dtype, "zq_gather_rows", err);
     if (rc) return rc;
+    if ((rc = use_device(ctx, err))) return rc;
     if (!dev_row_ids && n_rows > w->rows) return set_error(err, ZQ_ERR_SHAPE, "zq_gather_rows: %zu rows requested from a weight with %zu rows", n_rows, w->rows);
     return launch_dequantize(ctx, w, dev_row_ids, n_rows, dev_out, out_dtype, err);
 }
@@ -330,6 +351,7 @@ int zq_quantize(zq_ctx *ctx, uint32_t ggml_type, const float *dev_values, size_t
     if (cols % f.block_elems) return set_error(err, ZQ_ERR_SHAPE, "zq_quantize: columns %zu not aligned to block %d", cols, f.block_elems);
     size_t expected = rows * (cols / f.block_elems) * f.block_bytes;
     if (nbytes != expected) return set_error(err, ZQ_ERR_SHAPE, "zq_quantize: output holds %zu bytes, %zu expected", nbytes, expected);
+    if (int rc = use_device(ctx, err)) return rc;
     return launch_quantize(ctx, ggml_type, dev_values, rows, cols, dev_gguf_bytes, err);
 }
 
@@ -341,7 +363,7 @@ static int check_linear(zq_ctx *ctx, const zq_weight *w, const void *x, int x_dt
     if (rc) return rc;
     if (m == 0) return set_error(err, ZQ_ERR_SHAPE, "linear: input has no rows");
     if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(y) & 15)) return set_error(err, ZQ_ERR_ARG, "linear: device buffers must be 16-byte aligned");
-    return ZQ_OK;
+    return use_device(ctx, err);
 }
 
 int zq_linear(zq_ctx *ctx, const zq_weight *w, const void *dev_x, int x_dtype, size_t m, void *dev_y, int y_dtype, const void *dev_residual, zq_error *err) {
@@ -393,7 +415,7 @@ int zq_gated_silu(zq_ctx *ctx, const zq_weight *gate, const zq_weight *up, const
 }
 
 int zq_gated_mlp(zq_ctx *ctx, const zq_weight *gate, const zq_weight *up, const zq_weight *down, const void *dev_x, int x_dtype, size_t m, void *dev_y, int y_dtype, const void *dev_residual, zq_error *err) {
-    if (!down || !gate) return set_error(err, ZQ_ERR_ARG, "gated mlp: null weight");
+    if (!ctx || !down || !gate || !up) return set_error(err, ZQ_ERR_ARG, "gated mlp: null context or weight");
     if (down->cols != gate->rows) return set_error(err, ZQ_ERR_SHAPE, "gated mlp: down expects %zu inputs, gate produces %zu", down->cols, gate->rows);
     // the activated intermediate [m, I] lives in the context workspace as f32 (decode) or in the input dtype (prefill)
     int mid_dtype = m <= 16 ? ZQ_F32 : (x_dtype == ZQ_F32 ? ZQ_F32 : x_dtype);
@@ -485,16 +507,29 @@ int zq_linear_host(zq_ctx *ctx, const zq_weight *w, const void *host_x, int x_dt
         // and hands the results to the callers' buffers.  Page-locked caller buffers are copied from / to directly.
         uint8_t *px, *dx;
         rc = batch_io_alloc(ctx, xb_al + yb, &px, &dx, err);
-        if (rc) return rc;
-        const void *src = host_x;
-        if (!x_pinned) {
-            memcpy(px, host_x, xb);
-            src = px;
+        if (!rc) {
+            const void *src = host_x;
+            if (!x_pinned) {
+                memcpy(px, host_x, xb);
+                src = px;
+            }
+            cudaError_t ce = cudaMemcpyAsync(dx, src, xb, cudaMemcpyHostToDevice, ctx->stream);
+            if (ce != cudaSuccess) rc = set_error(err, ZQ_ERR_CUDA, "zq_linear_host: copy in failed: %s", cudaGetErrorString(ce));
         }
-        ZQ_CUDA_CHECK(cudaMemcpyAsync(dx, src, xb, cudaMemcpyHostToDevice, ctx->stream), err);
-        rc = zq_linear(ctx, w, dx, x_dtype, m, dx + xb_al, y_dtype, nullptr, err);
-        if (rc) return rc;
-        ZQ_CUDA_CHECK(cudaMemcpyAsync(y_pinned ? host_y : px + xb_al, dx + xb_al, yb, cudaMemcpyDeviceToHost, ctx->stream), err);
+        if (!rc) rc = zq_linear(ctx, w, dx, x_dtype, m, dx + xb_al, y_dtype, nullptr, err);
+        if (!rc) {
+            cudaError_t ce = cudaMemcpyAsync(y_pinned ? host_y : px + xb_al, dx + xb_al, yb, cudaMemcpyDeviceToHost, ctx->stream);
+            if (ce != cudaSuccess) rc = set_error(err, ZQ_ERR_CUDA, "zq_linear_host: copy out failed: %s", cudaGetErrorString(ce));
+        }
+        if (rc) {
+            // a failed call closes the bracket: what was enqueued is waited for and dropped (no output buffer of the
+            // bracket is filled), so that no caller pointer outlives the error
+            cudaStreamSynchronize(ctx->stream);
+            ctx->pending_out.clear();
+            for (auto &c : ctx->io_chunks) c.used = 0;
+            ctx->batch_active = false;
+            return rc;
+        }
         if (!y_pinned) ctx->pending_out.push_back({host_y, px + xb_al, yb});
         return ZQ_OK;
     }

@@ -281,6 +281,7 @@ struct zq_weight {
 };
 
 namespace zq {
+int use_device(zq_ctx *ctx, zq_error *err);
 int ensure_workspace(zq_ctx *ctx, size_t bytes, zq_error *err);
 int ensure_xq(zq_ctx *ctx, size_t bytes, zq_error *err);
 int launch_gemm_fused_grouped(zq_ctx *ctx, const CUtensorMap *w_maps, const CUtensorMap *w2_maps, size_t rows, size_t k, const __half *x, size_t x_rows, const int4 *items, int n_items, void *y, int y_dtype, zq_error *err);

@@ -28,7 +28,9 @@ constexpr int kRouterThreads = 256;
 
 // Softmax top-k of one token from its logits in shared memory (the logits are consumed): repeated arg-max with ties
 // to the lower expert id; one warp per token.
-__device__ __forceinline__ void router_select(float *l, int lane, int num_experts, int top_k, float scaling, int normalize_selected, uint32_t *ids_out, float *weights_out) {
+// A row whose logits are all NaN (NaN in the activations, the router matrix or the bias) has no arg-max: such a slot
+// takes expert id `slot` (always a valid id), the status word records it, and the weights come out NaN.
+__device__ __forceinline__ void router_select(float *l, int lane, int num_experts, int top_k, float scaling, int normalize_selected, uint32_t *ids_out, float *weights_out, uint32_t *status) {
     float maximum = -INFINITY;
     for (int e = lane; e < num_experts; e += 32) maximum = fmaxf(maximum, l[e]);
     for (int o = 16; o > 0; o >>= 1) maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, o));
@@ -51,6 +53,10 @@ __device__ __forceinline__ void router_select(float *l, int lane, int num_expert
             int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
             if (ov > best || (ov == best && oe < best_e)) { best = ov; best_e = oe; }
         }
+        if (best_e < 0 || best_e >= num_experts) {  // warp-uniform: no comparable logit left in the row
+            best_e = slot;
+            if (lane == 0) atomicMax(status, (uint32_t)kStatusBadIndex);
+        }
         if (lane == slot) { sel_logit = best; sel_id = (uint32_t)best_e; }
         if (lane == 0) l[best_e] = -INFINITY;
         __syncwarp();
@@ -69,7 +75,7 @@ __device__ __forceinline__ void router_select(float *l, int lane, int num_expert
 // with several (few tokens: the expert blocks are what fills the machine) the logits go to `logits_g` and
 // router_select_kernel finishes.
 __global__ void __launch_bounds__(kRouterThreads) router_topk_kernel(const void *__restrict__ x, int x_dtype, int m, int hidden, const float *__restrict__ router, const float *__restrict__ bias, int num_experts, int top_k,
-                                                                      float scaling, int normalize_selected, uint32_t *__restrict__ ids, float *__restrict__ weights, int experts_per_cta, float *__restrict__ logits_g) {
+                                                                      float scaling, int normalize_selected, uint32_t *__restrict__ ids, float *__restrict__ weights, int experts_per_cta, float *__restrict__ logits_g, uint32_t *status) {
     extern __shared__ float rsm[];
     float *xs = rsm;                                 // [kRouterTokens][hidden]
     float *logits = rsm + (size_t)kRouterTokens * hidden;  // [kRouterTokens][num_experts]
@@ -143,7 +149,7 @@ __global__ void __launch_bounds__(kRouterThreads) router_topk_kernel(const void 
     if (logits_g) return;
     __syncthreads();
     if (warp < kRouterTokens && tok0 + warp < m)
-        router_select(logits + warp * num_experts, lane, num_experts, top_k, scaling, normalize_selected, ids + (size_t)(tok0 + warp) * top_k, weights + (size_t)(tok0 + warp) * top_k);
+        router_select(logits + warp * num_experts, lane, num_experts, top_k, scaling, normalize_selected, ids + (size_t)(tok0 + warp) * top_k, weights + (size_t)(tok0 + warp) * top_k, status);
 }
 
 // Router logits on the tensor cores for prefill-sized batches.  f16 operands alone would move logits by ~1e-3 and
@@ -166,7 +172,7 @@ __global__ void split_f16_kernel(const void *__restrict__ src, int dtype, size_t
 
 // Second half of the split router: one warp per token, logits from global memory.
 __global__ void __launch_bounds__(kRouterThreads) router_select_kernel(const float *__restrict__ logits_g, const float *__restrict__ bias, int m, int num_experts, int top_k, float scaling, int normalize_selected,
-                                                                        uint32_t *__restrict__ ids, float *__restrict__ weights) {
+                                                                        uint32_t *__restrict__ ids, float *__restrict__ weights, uint32_t *status) {
     extern __shared__ float rsm[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tok = blockIdx.x * (kRouterThreads / 32) + warp;
@@ -174,7 +180,7 @@ __global__ void __launch_bounds__(kRouterThreads) router_select_kernel(const flo
     float *l = rsm + warp * num_experts;
     for (int e = lane; e < num_experts; e += 32) l[e] = logits_g[(size_t)tok * num_experts + e] + (bias ? bias[e] : 0.f);
     __syncwarp();
-    router_select(l, lane, num_experts, top_k, scaling, normalize_selected, ids + (size_t)tok * top_k, weights + (size_t)tok * top_k);
+    router_select(l, lane, num_experts, top_k, scaling, normalize_selected, ids + (size_t)tok * top_k, weights + (size_t)tok * top_k, status);
 }
 
 __global__ void gather_rows_kernel(const void *__restrict__ x, int dtype, const uint32_t *__restrict__ tokens, size_t n_rows, int hidden, void *__restrict__ out) {
@@ -234,6 +240,11 @@ int zq_moe_route_softmax_topk(zq_ctx *ctx, const void *dev_x, int x_dtype, size_
     if (num_experts == 0 || num_experts > 1024 || top_k == 0 || top_k > num_experts || top_k > 32) return set_error(err, ZQ_ERR_SHAPE, "softmax router: experts=%zu top_k=%zu outside the supported range (experts <= 1024, top_k <= 32)", num_experts, top_k);
     if (!(scaling_factor == scaling_factor) || scaling_factor > 3.0e38f || scaling_factor < -3.0e38f) return set_error(err, ZQ_ERR_ARG, "softmax router: scaling factor is not finite");
     if (m == 0 || hidden == 0) return set_error(err, ZQ_ERR_SHAPE, "softmax router: empty input");
+    if (x_dtype != ZQ_F32 && x_dtype != ZQ_F16 && x_dtype != ZQ_BF16) return set_error(err, ZQ_ERR_ARG, "softmax router: unknown input dtype %d", x_dtype);
+    // the kernels read x and the router matrix with 16-byte loads whenever hidden is a multiple of 8
+    if ((reinterpret_cast<uintptr_t>(dev_x) & 15) || (reinterpret_cast<uintptr_t>(dev_router_f32) & 15)) return set_error(err, ZQ_ERR_ARG, "softmax router: x and the router matrix must be 16-byte aligned");
+    if ((reinterpret_cast<uintptr_t>(dev_ids) & 3) || (reinterpret_cast<uintptr_t>(dev_weights) & 3) || (reinterpret_cast<uintptr_t>(dev_bias_f32) & 3)) return set_error(err, ZQ_ERR_ARG, "softmax router: ids, weights and bias must be 4-byte aligned");
+    if (int rc = use_device(ctx, err)) return rc;
     size_t smem = ((size_t)kRouterTokens * hidden + (size_t)kRouterTokens * num_experts) * sizeof(float);
     if (smem > 200 * 1024) return set_error(err, ZQ_ERR_UNSUPPORTED, "softmax router: hidden=%zu does not fit the router kernel's shared memory", hidden);
     static bool configured[64] = {};
@@ -265,7 +276,7 @@ int zq_moe_route_softmax_topk(zq_ctx *ctx, const void *dev_x, int x_dtype, size_
         if (rc) return rc;
         const unsigned sel_grid = (unsigned)((m + kRouterThreads / 32 - 1) / (kRouterThreads / 32));
         router_select_kernel<<<sel_grid, kRouterThreads, (kRouterThreads / 32) * num_experts * sizeof(float), ctx->stream>>>(logits_g, dev_bias_f32, (int)m, (int)num_experts, (int)top_k, scaling_factor, normalize_selected, dev_ids,
-                                                                                                                            dev_weights);
+                                                                                                                            dev_weights, ctx->status_dev);
         ctx->launches++;
         ZQ_CUDA_CHECK(cudaGetLastError(), err);
         return ZQ_OK;
@@ -275,17 +286,17 @@ int zq_moe_route_softmax_topk(zq_ctx *ctx, const void *dev_x, int x_dtype, size_
         if (rc) return rc;
         float *logits_g = reinterpret_cast<float *>(ctx->moe_ws);
         router_topk_kernel<<<dim3(grid, (unsigned)blocks_y), kRouterThreads, smem, ctx->stream>>>(dev_x, x_dtype, (int)m, (int)hidden, dev_router_f32, dev_bias_f32, (int)num_experts, (int)top_k, scaling_factor, normalize_selected,
-                                                                                                   dev_ids, dev_weights, (int)per_cta, logits_g);
+                                                                                                   dev_ids, dev_weights, (int)per_cta, logits_g, ctx->status_dev);
         ctx->launches++;
         ZQ_CUDA_CHECK(cudaGetLastError(), err);
         const unsigned sel_grid = (unsigned)((m + kRouterThreads / 32 - 1) / (kRouterThreads / 32));
-        router_select_kernel<<<sel_grid, kRouterThreads, (kRouterThreads / 32) * num_experts * sizeof(float), ctx->stream>>>(logits_g, nullptr, (int)m, (int)num_experts, (int)top_k, scaling_factor, normalize_selected, dev_ids, dev_weights);
+        router_select_kernel<<<sel_grid, kRouterThreads, (kRouterThreads / 32) * num_experts * sizeof(float), ctx->stream>>>(logits_g, nullptr, (int)m, (int)num_experts, (int)top_k, scaling_factor, normalize_selected, dev_ids, dev_weights, ctx->status_dev);
         ctx->launches++;
         ZQ_CUDA_CHECK(cudaGetLastError(), err);
         return ZQ_OK;
     }
     router_topk_kernel<<<grid, kRouterThreads, smem, ctx->stream>>>(dev_x, x_dtype, (int)m, (int)hidden, dev_router_f32, dev_bias_f32, (int)num_experts, (int)top_k, scaling_factor, normalize_selected, dev_ids, dev_weights,
-                                                                    (int)num_experts, nullptr);
+                                                                    (int)num_experts, nullptr, ctx->status_dev);
     ctx->launches++;
     ZQ_CUDA_CHECK(cudaGetLastError(), err);
     return ZQ_OK;
@@ -367,6 +378,13 @@ int zq_moe_forward(zq_ctx *ctx, const zq_moe_experts *experts, const zq_weight *
     if (!ctx || !experts || !dev_x || !dev_ids || !dev_weights || !dev_y) return set_error(err, ZQ_ERR_ARG, "zq_moe_forward: null argument");
     if (experts->ctx != ctx) return set_error(err, ZQ_ERR_ARG, "zq_moe_forward: expert table belongs to another context");
     if (m == 0 || top_k == 0) return set_error(err, ZQ_ERR_SHAPE, "zq_moe_forward: empty routing (rows=%zu top_k=%zu)", m, top_k);
+    if (x_dtype != ZQ_F32 && x_dtype != ZQ_F16 && x_dtype != ZQ_BF16) return set_error(err, ZQ_ERR_ARG, "zq_moe_forward: unknown input dtype %d", x_dtype);
+    if (y_dtype != ZQ_F32 && y_dtype != ZQ_F16 && y_dtype != ZQ_BF16) return set_error(err, ZQ_ERR_ARG, "zq_moe_forward: unknown output dtype %d", y_dtype);
+    // rows are gathered and stored with 16-byte accesses
+    if ((reinterpret_cast<uintptr_t>(dev_x) & 15) || (reinterpret_cast<uintptr_t>(dev_y) & 15) || (reinterpret_cast<uintptr_t>(dev_residual) & 15)) return set_error(err, ZQ_ERR_ARG, "zq_moe_forward: x, y and residual must be 16-byte aligned");
+    if ((reinterpret_cast<uintptr_t>(dev_ids) & 3) || (reinterpret_cast<uintptr_t>(dev_weights) & 3)) return set_error(err, ZQ_ERR_ARG, "zq_moe_forward: ids and weights must be 4-byte aligned");
+    if (experts->hidden % 32 || experts->inter % 32) return set_error(err, ZQ_ERR_SHAPE, "zq_moe_forward: hidden=%zu and intermediate=%zu must be multiples of 32", experts->hidden, experts->inter);
+    if (int rc = use_device(ctx, err)) return rc;
     {
         cudaError_t stale = cudaGetLastError();  // an error some earlier call of this thread left behind is not this call's
         if (stale != cudaSuccess) return set_error(err, ZQ_ERR_CUDA, "zq_moe_forward: the CUDA runtime already held an error on entry: %s", cudaGetErrorString(stale));
