@@ -182,6 +182,11 @@ def run_ours(args):
         plan = [(m, c) for m, c in plan if c[0] == oname and c[2] == ok and c[3] == on and m == int(om)]
         if not plan:
             raise SystemExit(f"--only {args.only}: no such case")
+    if args.only_block:
+        oname, om = args.only_block.split(":")
+        plan = [(m, c) for m, c in plan if c[0] == oname and m == int(om)]
+        if not plan:
+            raise SystemExit(f"--only-block {args.only_block}: no such block")
     outs = {}
     for m, case in plan:
         name, fmt, k, n, mode, w, (c0, c1), (r0, r1) = case
@@ -203,49 +208,58 @@ def run_ours(args):
         if mode == "row" and collective:
             dist.all_reduce(y)
 
-    # CUDA graphs keep the host out of the timed region (a Python/ctypes launch costs more than a 5 us kernel).
-    # A block is one (batch, format) group of launches; it is cut into segments that end at every K-split matrix,
-    # because that matrix's all-reduce is launched from the host right after its segment: collectives are never
-    # captured.  With one GPU a block is one segment.  Events around the Q4_K batch-1 and batch-4 blocks (the
-    # headline kernel) are recorded inside the timed region.
+    # A block is one (batch, format) group: five distinct matrices, 175 MB of packed weights.  By default a block is ONE
+    # zq_linear_batch call (the work-list decode kernel: one record pass + one persistent launch for the five
+    # matrices); --per-call issues one zq_linear per matrix instead.  No matrix appears twice in a block, and the
+    # blocks in between stream 175-350 MB of other weights, so no launch finds its weights in L2.
+    # CUDA graphs keep the host out of the timed region (a Python/ctypes call costs more than a 5 us kernel).
+    # Collectives are never captured: with several GPUs the all-reduces of a block's K-split matrices are launched
+    # from the host right after the block's graph.  Events around the Q4_K batch-1 and batch-4 blocks (the headline
+    # kernel) are recorded inside the timed region.
     blocks = []
     for m in BATCHES:
         for fmt, name in FORMATS:
             members = [(mm, case) for mm, case in plan if mm == m and case[1] == fmt]
             if members:
                 blocks.append((m, fmt, members))
-    segments = []  # per block: list of (members, tensor to all-reduce after the segment or None)
+    job_arrays = []
     for m, fmt, members in blocks:
-        segs, cur = [], []
-        for mm, case in members:
-            cur.append((mm, case))
-            if case[4] == "row":
-                segs.append((cur, outs[(mm, case[0], case[2], case[3])]))
-                cur = []
-        if cur:
-            segs.append((cur, None))
-        segments.append(segs)
-    for m, fmt, members in blocks:  # eager pass: sizes every internal buffer before capture
-        for mm, case in members:
-            launch(mm, case)
+        arr = (ffi.ZqLinearJob * len(members))()
+        for i, (mm, case) in enumerate(members):
+            name, _, k, n, mode, w, (c0, c1), (r0, r1) = case
+            arr[i].w = w.handle.value
+            arr[i].w_up = None
+            arr[i].dev_x = x_local[(mm, k, c0, c1)].data_ptr()
+            arr[i].m = mm
+            arr[i].dev_y = outs[(mm, name, k, n)].data_ptr()
+            arr[i].dev_residual = None
+        job_arrays.append(arr)
+    reduce_after = [[outs[(mm, case[0], case[2], case[3])] for mm, case in members if case[4] == "row"] for _, _, members in blocks]
+
+    def launch_block(bi):
+        m, fmt, members = blocks[bi]
+        if args.per_call:
+            for mm, case in members:
+                launch(mm, case, collective=False)
+        else:
+            ffi.call("zq_linear_batch", ctx.handle, job_arrays[bi], len(members), ffi.F32, ffi.F32)
+
+    for bi in range(len(blocks)):  # eager pass: sizes every internal buffer before capture
+        launch_block(bi)
     torch.cuda.synchronize()
-    graphs = []  # per block: one graph per segment
+    graphs = []  # one graph per block
     launches_per_graph = []
     if not args.no_graph:
         side = torch.cuda.Stream(device=device)
         try:
-            for segs in segments:
-                gs = []
-                for seg_members, _ in segs:
-                    g = torch.cuda.CUDAGraph()
-                    n0 = ctx.launch_count
-                    with torch.cuda.graph(g, stream=side):
-                        ctx.set_stream(torch.cuda.current_stream(device).cuda_stream)
-                        for mm, case in seg_members:
-                            launch(mm, case, collective=False)
-                    gs.append(g)
-                    launches_per_graph.append(ctx.launch_count - n0)
-                graphs.append(gs)
+            for bi in range(len(blocks)):
+                g = torch.cuda.CUDAGraph()
+                n0 = ctx.launch_count
+                with torch.cuda.graph(g, stream=side):
+                    ctx.set_stream(torch.cuda.current_stream(device).cuda_stream)
+                    launch_block(bi)
+                graphs.append(g)
+                launches_per_graph.append(ctx.launch_count - n0)
         except Exception as exc:
             graphs = []
             sys.stderr.write(f"bench: graph capture failed ({exc}); launching from the host\n")
@@ -258,20 +272,20 @@ def run_ours(args):
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
             if graphs:
-                for g, (_, reduce_me) in zip(graphs[bi], segments[bi]):
-                    g.replay()
-                    if reduce_me is not None:
-                        dist.all_reduce(reduce_me)
+                graphs[bi].replay()
             else:
-                for mm, case in members:
-                    launch(mm, case)
+                launch_block(bi)
+            if world > 1:
+                for y in reduce_after[bi]:
+                    dist.all_reduce(y)
             if mark:
                 e1.record()
                 events.append((e0, e1))
 
     step_bytes = sum(algorithmic_bytes(case[2], case[3], m) for m, case in plan)
     q4k_kernel_bytes = sum(algorithmic_bytes(case[2], case[3], m) for m, case in plan if case[1] == Q4_K and m <= 4)
-    q4k_kernel_launches = sum(1 for m, case in plan if case[1] == Q4_K and m <= 4)
+    # launches of the roofline kernel per step: one per Q4_K batch-1/-4 block (work list), or one per matrix (--per-call)
+    q4k_kernel_launches = sum(1 for m, case in plan if case[1] == Q4_K and m <= 4) if args.per_call else sum(1 for m, fmt, _ in blocks if fmt == Q4_K and m <= 4)
 
     def barrier():
         if world > 1:
@@ -376,7 +390,7 @@ def run_ours(args):
         "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": hbm_peak, "unit": "GB/s", "frac": round(achieved / hbm_peak, 4),
                      # ncu, 5120x17408 batch-1 launch: dram read+write = 50.21 MB for 50.23 MB algorithmic; scaled by bytes
                      "traffic": int(q4k_kernel_bytes // max(q4k_kernel_launches, 1) * NCU_TRAFFIC_RATIO), "traffic_kind": "ncu capture of one launch, scaled by algorithmic bytes",
-                     "kernel": "zq::gemv_i8_kernel<Q4_K, 1 column tile> (batch 1 and 4)", "peak_kind": peak_kind, "launches": q4k_kernel_launches * args.steps,
+                     "kernel": "zq::gemv_i8_kernel<Q4_K, 1 column tile> (batch 1 and 4, one launch per matrix)" if args.per_call else "zq::gemv_wl_kernel<Q4_K, 1 column tile> (batch 1 and 4; one launch per block of five matrices, timed together with its record pass)", "peak_kind": peak_kind, "launches": q4k_kernel_launches * args.steps,
                      "bytes_per_launch_avg": q4k_kernel_bytes // max(q4k_kernel_launches, 1)},
         "gpu_launches": launches, "clocks": clocks, "e2e": e2e, "cpu_baseline": cpu,
     }
@@ -649,6 +663,7 @@ def main():
     ap.add_argument("--watchdog", type=int, default=480, help="multi-GPU runs: seconds after which a stuck run dumps tracebacks and exits")
     ap.add_argument("--no-extras", action="store_true", help="skip the prefill-GEMM and MoE side measurements")
     ap.add_argument("--extras", default="all", choices=["all", "prefill", "moe"], help="which side measurements to run")
+    ap.add_argument("--per-call", action="store_true", help="one zq_linear call (and launch) per matrix instead of one zq_linear_batch call per block (A/B aid)")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying CUDA graphs")
     ap.add_argument("--no-clocks", action="store_true", help="do not sample clocks with nvidia-smi")
     ap.add_argument("--no-pdl", action="store_true", help="launch decode kernels without programmatic dependent launch (A/B aid)")
@@ -659,6 +674,7 @@ def main():
     ap.add_argument("--only-prefill", type=int, default=0, help="profiling aid: run only a few prefill GEMMs (Q4_K 5120->17408) at this token count and exit")
     ap.add_argument("--only-kquant", action="store_true", help="profiling aid: run only the Q5_K / Q6_K one-row decode measurement and exit")
     ap.add_argument("--only-moe", default=None, choices=["decode_m64", "prefill_m8192"], help="profiling aid: run only this MoE case and exit")
+    ap.add_argument("--only-block", default=None, help="restrict the sweep to one block of five matrices, e.g. q4_k:1 (format:batch); for profiling")
     ap.add_argument("--only", default=None, help="restrict the sweep to one case, e.g. q4_k:5120x17408:1 (format:KxN:batch); for profiling")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -49,7 +49,7 @@ int zq_ctx_use_own_stream(zq_ctx *ctx, zq_error *err);
 int zq_ctx_sync(zq_ctx *ctx, zq_error *err);
 /* Diagnostic switches (the counterpart of the reference's ZLLM_CUDA_* environment switches, kept per context).
  * Known keys (0/1): "force_staged_gemv", "force_f16_gemv" (decode on the f16 kernels instead of the integer-MMA kernel),
- * "enable_tcgen05_gemv" (Q4_K decode on the tcgen05 kernel), "disable_pdl" (decode kernels without programmatic dependent launch), "force_moe_per_expert" (MoE forward always on the host-grouped path), "narrow_gemv_tiles" (decode, up to 4 rows: 64-row tiles, two CTAs per SM), "disable_fused_gemm" / "force_fused_gemm" (Q4_K prefill never / always on the kernel that dequantises inside the GEMM; default: up to 1024 tokens and MoE prefill). */
+ * "enable_tcgen05_gemv" (Q4_K decode on the tcgen05 kernel), "disable_pdl" (decode kernels without programmatic dependent launch), "disable_worklist" (zq_linear_batch and the multi-weight entries launch one kernel per job), "force_moe_per_expert" (MoE forward always on the host-grouped path), "narrow_gemv_tiles" (decode, up to 4 rows: 64-row tiles, two CTAs per SM), "disable_fused_gemm" / "force_fused_gemm" (Q4_K prefill never / always on the kernel that dequantises inside the GEMM; default: up to 1024 tokens and MoE prefill). */
 int zq_ctx_set_option(zq_ctx *ctx, const char *key, int value, zq_error *err);
 int zq_ctx_sm_count(const zq_ctx *ctx);
 /* Number of kernels this library has launched on the context since creation (bench accounting). */
@@ -61,6 +61,7 @@ uint64_t zq_ctx_launch_count(const zq_ctx *ctx);
 int zq_weight_prepare(zq_ctx *ctx, uint32_t ggml_type, const void *host_bytes, size_t nbytes, size_t rows, size_t cols, zq_weight **out, zq_error *err);
 /* Same, from GGUF-layout bytes already on the device (expert tensors sliced on device, synthetic inputs). */
 int zq_weight_prepare_device(zq_ctx *ctx, uint32_t ggml_type, const void *dev_bytes, size_t nbytes, size_t rows, size_t cols, zq_weight **out, zq_error *err);
+/* Release every weight (and expert table) of a context before zq_ctx_destroy: releasing waits on the context's stream. */
 void zq_weight_release(zq_weight *w);
 size_t zq_weight_rows(const zq_weight *w);
 size_t zq_weight_cols(const zq_weight *w);
@@ -85,6 +86,24 @@ int zq_quantize(zq_ctx *ctx, uint32_t ggml_type, const float *dev_values, size_t
 int zq_linear(zq_ctx *ctx, const zq_weight *w, const void *dev_x, int x_dtype, size_t m, void *dev_y, int y_dtype, const void *dev_residual, zq_error *err);
 /* Backend::dual_linear / triple_linear (src/backend/mod.rs:444-451): up to 3 weights share one input. */
 int zq_linear_multi(zq_ctx *ctx, const zq_weight *const *w, size_t n_weights, const void *dev_x, int x_dtype, size_t m, void *const *dev_y, int y_dtype, zq_error *err);
+/* A list of INDEPENDENT decode projections in as few launches as possible (no job may read another job's output).
+ * It generalises Backend::dual_linear / triple_linear (src/backend/mod.rs:444-451) and the Metal backend's two-weight
+ * decode launch gguf_dual_gemv_q4k_f16 (src/kernel/metal/gguf/mod.rs:1787-1824) to any number of weights and inputs:
+ * the projections of a decode step that are ready together (q, k, v; gate and up; the layers of several sequences)
+ * stream through one persistent kernel whose TMA ring never drains between matrices.  Per job: y = W x (+ residual),
+ * or y = silu(gate x) * (up x) when `w_up` is given (then `w` is the gate; no residual).  Jobs of Q4_K / Q4_0 / Q8_0
+ * weights with up to 16 rows share launches (one per weight type, row-count class 1-4 / 5-8 / 9-16 and plain / gated);
+ * every other job runs as its own zq_linear / zq_gated_silu call.  All jobs share x_dtype and y_dtype.  Results do not
+ * depend on how the jobs are grouped beyond f32 rounding of the split-tile sums, and are the same from run to run. */
+typedef struct zq_linear_job {
+    const zq_weight *w;        /* the weight, or the gate of a gated pair */
+    const zq_weight *w_up;     /* NULL, or the up weight of a gated pair */
+    const void *dev_x;         /* [m, cols] */
+    size_t m;
+    void *dev_y;               /* [m, rows] */
+    const void *dev_residual;  /* NULL, or [m, rows] in y_dtype */
+} zq_linear_job;
+int zq_linear_batch(zq_ctx *ctx, const zq_linear_job *jobs, size_t n_jobs, int x_dtype, int y_dtype, zq_error *err);
 /* Backend::rmsnorm_linear / rmsnorm_dual_linear (src/backend/mod.rs:455-464): RMSNorm of every input row
  * (src/kernel/cpu/rmsnorm.rs:7-41: x * 1/sqrt(mean(x^2) + eps) * (norm_weight + weight_offset); offset 0 = plain,
  * 1 = the "Gemma" form), then 1 to 3 linear layers on the normalised rows.  `dev_norm_weight`: f32 [cols].  The

@@ -162,6 +162,37 @@ class B200Context:
     def linear_add(self, x: torch.Tensor, w: Weight, residual: torch.Tensor, out_dtype=None) -> torch.Tensor:
         return self.linear(x, w, out_dtype=out_dtype or residual.dtype, residual=residual)
 
+    def linear_batch(self, jobs, out_dtype=None):
+        """Independent decode projections in as few launches as possible (``zq_linear_batch``).
+
+        ``jobs`` is a list of ``(x, weight)``, ``(x, weight, residual)`` or ``(x, gate, up, "gated")`` tuples; all inputs
+        share one dtype.  Returns the list of outputs."""
+        arr = (ffi.ZqLinearJob * len(jobs))()
+        ys, keep = [], []
+        x_dt = None
+        for i, job in enumerate(jobs):
+            x = job[0].contiguous()
+            gated = len(job) == 4 and job[3] == "gated"
+            w = job[1]
+            m = self._rows(x, w.cols)
+            x_dt = x_dt or x.dtype
+            if x.dtype != x_dt:
+                raise TypeError("linear_batch: all inputs must share one dtype")
+            od = out_dtype or x.dtype
+            y = torch.empty((m, w.rows), dtype=od, device=x.device)
+            residual = job[2].contiguous() if (len(job) == 3 and job[2] is not None) else None
+            arr[i].w = w.handle.value
+            arr[i].w_up = job[2].handle.value if gated else None
+            arr[i].dev_x = x.data_ptr()
+            arr[i].m = m
+            arr[i].dev_y = y.data_ptr()
+            arr[i].dev_residual = residual.data_ptr() if residual is not None else None
+            ys.append(y)
+            keep.append((x, residual))
+        if jobs:
+            ffi.call("zq_linear_batch", self.handle, arr, len(jobs), _DTYPES[x_dt], _DTYPES[out_dtype or x_dt])
+        return ys
+
     def linear_multi(self, x: torch.Tensor, weights: Sequence[Weight], out_dtype=None):
         x = x.contiguous()
         m = self._rows(x, weights[0].cols)

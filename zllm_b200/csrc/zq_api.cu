@@ -1,5 +1,6 @@
 // C-ABI entry points, context and resident-weight management of the zq_b200 library.
 #include "zq_common.cuh"
+#include "zq_wl.cuh"
 
 namespace zq {
 
@@ -130,8 +131,14 @@ static int finish_prepare(zq_ctx *ctx, zq_weight *w, zq_error *err) {
     int rc = make_weight_map(w, 2 * f.unit_bytes / 4, 128, &w->gemv_map, err);
     if (!rc) rc = make_weight_map(w, 2 * f.unit_bytes / 4, 64, &w->gemv_map_half, err);
     if (!rc) rc = make_weight_map(w, f.unit_bytes / 4, 128, &w->qmv_map, err);
-    (void)ctx;
-    return rc;
+    if (rc) return rc;
+    // device copies, in the tail of the weight's own allocation (see resident_alloc_bytes)
+    const size_t tail = (w->rows * w->row_pitch + 255) & ~size_t(255);
+    CUtensorMap host_maps[3] = {w->gemv_map, w->gemv_map_half, w->qmv_map};
+    ZQ_CUDA_CHECK(cudaMemcpyAsync(w->data + tail, host_maps, sizeof(host_maps), cudaMemcpyHostToDevice, ctx->stream), err);
+    ZQ_CUDA_CHECK(cudaStreamSynchronize(ctx->stream), err);  // host_maps is a stack array
+    w->d_maps = reinterpret_cast<CUtensorMap *>(w->data + tail);
+    return ZQ_OK;
 }
 
 }  // namespace zq
@@ -248,6 +255,10 @@ int zq_ctx_set_option(zq_ctx *ctx, const char *key, int value, zq_error *err) {
         ctx->force_moe_per_expert = value;
         return ZQ_OK;
     }
+    if (!strcmp(key, "disable_worklist")) {
+        ctx->disable_worklist = value;
+        return ZQ_OK;
+    }
     if (!strcmp(key, "disable_pdl")) {
         ctx->disable_pdl = value;
         return ZQ_OK;
@@ -272,7 +283,8 @@ int zq_weight_prepare_device(zq_ctx *ctx, uint32_t ggml_type, const void *dev_by
     int rc = prepare_common(ctx, ggml_type, nbytes, rows, cols, &w, err);
     if (!rc && (rc = use_device(ctx, err))) delete w;
     if (rc) return rc;
-    size_t resident = w->rows * w->row_pitch;
+    // resident bytes, then (256-byte aligned) room for the device copies of three tensor maps
+    size_t resident = ((w->rows * w->row_pitch + 255) & ~size_t(255)) + 3 * sizeof(CUtensorMap);
     cudaError_t e = cudaMalloc(reinterpret_cast<void **>(&w->data), resident);
     if (e != cudaSuccess) {
         delete w;
@@ -374,16 +386,47 @@ int zq_linear(zq_ctx *ctx, const zq_weight *w, const void *dev_x, int x_dtype, s
     return launch_gemm(ctx, w, nullptr, dev_x, x_dtype, m, dev_y, y_dtype, dev_residual, err);
 }
 
+// One job of a batch through the single-job entry points (the route for whatever the work-list kernel does not take).
+static int run_job_alone(zq_ctx *ctx, const zq_linear_job &j, int x_dtype, int y_dtype, zq_error *err) {
+    if (j.w_up) return zq_gated_silu(ctx, j.w, j.w_up, j.dev_x, x_dtype, j.m, j.dev_y, y_dtype, err);
+    return zq_linear(ctx, j.w, j.dev_x, x_dtype, j.m, j.dev_y, y_dtype, j.dev_residual, err);
+}
+
+int zq_linear_batch(zq_ctx *ctx, const zq_linear_job *jobs, size_t n_jobs, int x_dtype, int y_dtype, zq_error *err) {
+    if (!ctx || (!jobs && n_jobs)) return set_error(err, ZQ_ERR_ARG, "zq_linear_batch: null argument");
+    // validate everything before anything is enqueued: a bad job must not leave half a batch running
+    for (size_t i = 0; i < n_jobs; ++i) {
+        const zq_linear_job &j = jobs[i];
+        int rc = check_linear(ctx, j.w, j.dev_x, x_dtype, j.m, j.dev_y, y_dtype, err);
+        if (rc) return rc;
+        if (j.w_up) {
+            if (j.w_up->ctx != ctx) return set_error(err, ZQ_ERR_ARG, "zq_linear_batch: job %zu: up weight belongs to another context", i);
+            if (j.w->rows != j.w_up->rows || j.w->cols != j.w_up->cols || j.w->type != j.w_up->type) return set_error(err, ZQ_ERR_SHAPE, "zq_linear_batch: job %zu: gate and up differ in shape or type", i);
+            if (j.dev_residual) return set_error(err, ZQ_ERR_ARG, "zq_linear_batch: job %zu: a gated job takes no residual", i);
+        }
+        if (reinterpret_cast<uintptr_t>(j.dev_residual) & 15) return set_error(err, ZQ_ERR_ARG, "zq_linear_batch: job %zu: residual must be 16-byte aligned", i);
+    }
+    std::vector<WlHostJob> listed;
+    std::vector<size_t> alone;
+    for (size_t i = 0; i < n_jobs; ++i) {
+        const zq_linear_job &j = jobs[i];
+        WlHostJob h = {j.w, j.w_up, j.dev_x, j.m, j.dev_y, j.dev_residual};
+        if (!ctx->disable_worklist && gemv_wl_supported(ctx, h)) listed.push_back(h);
+        else alone.push_back(i);
+    }
+    int rc = launch_gemv_wl(ctx, listed.data(), listed.size(), x_dtype, y_dtype, err);
+    for (size_t k = 0; k < alone.size() && !rc; ++k) rc = run_job_alone(ctx, jobs[alone[k]], x_dtype, y_dtype, err);
+    return rc;
+}
+
 int zq_linear_multi(zq_ctx *ctx, const zq_weight *const *w, size_t n_weights, const void *dev_x, int x_dtype, size_t m, void *const *dev_y, int y_dtype, zq_error *err) {
     if (!w || !dev_y || n_weights == 0 || n_weights > 3) return set_error(err, ZQ_ERR_ARG, "zq_linear_multi: 1 to 3 weights expected");
+    zq_linear_job jobs[3];
     for (size_t i = 0; i < n_weights; ++i) {
         if (!w[i] || w[i]->cols != w[0]->cols) return set_error(err, ZQ_ERR_SHAPE, "zq_linear_multi: weights must share the input width");
+        jobs[i] = {w[i], nullptr, dev_x, m, dev_y[i], nullptr};
     }
-    for (size_t i = 0; i < n_weights; ++i) {
-        int rc = zq_linear(ctx, w[i], dev_x, x_dtype, m, dev_y[i], y_dtype, nullptr, err);
-        if (rc) return rc;
-    }
-    return ZQ_OK;
+    return zq_linear_batch(ctx, jobs, n_weights, x_dtype, y_dtype, err);  // one launch: the input is quantised once
 }
 
 int zq_rmsnorm_linear(zq_ctx *ctx, const zq_weight *const *w, size_t n_weights, const void *dev_x, int x_dtype, size_t m, const float *dev_norm_weight, float eps, float weight_offset, void *const *dev_y,
@@ -397,12 +440,15 @@ int zq_rmsnorm_linear(zq_ctx *ctx, const zq_weight *const *w, size_t n_weights, 
     if (rc) return rc;
     if (m == 0) return set_error(err, ZQ_ERR_SHAPE, "zq_rmsnorm_linear: input has no rows");
     if (!(eps >= 0.0f)) return set_error(err, ZQ_ERR_ARG, "zq_rmsnorm_linear: eps must be non-negative");
+    if ((rc = use_device(ctx, err))) return rc;
     const size_t cols = w[0]->cols;
     rc = ensure_scratch_norm(ctx, m * cols * sizeof(float), err);
     if (rc) return rc;
     rc = launch_rmsnorm(ctx, dev_x, x_dtype, m, cols, dev_norm_weight, eps, weight_offset, reinterpret_cast<float *>(ctx->norm), err);
-    for (size_t i = 0; i < n_weights && !rc; ++i) rc = zq_linear(ctx, w[i], ctx->norm, ZQ_F32, m, dev_y[i], y_dtype, nullptr, err);
-    return rc;
+    if (rc) return rc;
+    zq_linear_job jobs[3];
+    for (size_t i = 0; i < n_weights; ++i) jobs[i] = {w[i], nullptr, ctx->norm, m, dev_y[i], nullptr};
+    return zq_linear_batch(ctx, jobs, n_weights, ZQ_F32, y_dtype, err);
 }
 
 int zq_gated_silu(zq_ctx *ctx, const zq_weight *gate, const zq_weight *up, const void *dev_x, int x_dtype, size_t m, void *dev_y, int y_dtype, zq_error *err) {

@@ -259,6 +259,7 @@ struct zq_ctx {
     int force_f16_gemv = 0;  // skip the integer-MMA decode kernel (tests of the f16 kernels)
     int narrow_gemv_tiles = 0;  // integer-MMA decode, up to 4 rows: 64-row tiles, two CTAs per SM (measured slower; off)
     int disable_pdl = 0;     // launch decode kernels without programmatic dependent launch
+    int disable_worklist = 0;  // zq_linear_batch and the multi-weight entries: one launch per job instead of the work-list kernel
     int force_fused_gemm = 0;      // Q4_K prefill: the fused kernel for every token count (tests)
     int disable_fused_gemm = 0;    // Q4_K prefill: separate f16 operand pass + plain GEMM instead of the fused kernel
     int force_moe_per_expert = 0;  // MoE forward: always the host-grouped per-expert path (tests)
@@ -278,6 +279,9 @@ struct zq_weight {
     CUtensorMap gemv_map;        // u32 tensor [rows, row_pitch/4], box = (chunk words, 128 rows): decode GEMV
     CUtensorMap qmv_map;         // same tensor, box of one unit x 128 rows: tcgen05 decode kernel
     CUtensorMap gemv_map_half;   // same tensor, box of 64 rows: gated GEMV (gate and up halves of one stage)
+    // Device copies {gemv_map, gemv_map_half, qmv_map} behind the resident bytes (same allocation), for kernels that
+    // pick their weight from a table at run time; null for the types no decode kernel reads through TMA.
+    CUtensorMap *d_maps = nullptr;
 };
 
 namespace zq {

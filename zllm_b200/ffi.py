@@ -28,6 +28,14 @@ class ZqFailure(RuntimeError):
 
 
 _vp, _sz, _u32, _i, _f = C.c_void_p, C.c_size_t, C.c_uint32, C.c_int, C.c_float
+
+
+class ZqLinearJob(C.Structure):
+    """``zq_linear_job``: one projection of a ``zq_linear_batch`` call."""
+
+    _fields_ = [("w", C.c_void_p), ("w_up", C.c_void_p), ("dev_x", C.c_void_p), ("m", C.c_size_t), ("dev_y", C.c_void_p), ("dev_residual", C.c_void_p)]
+
+
 _err = C.POINTER(ZqError)
 
 PROTOTYPES = {
@@ -50,6 +58,7 @@ PROTOTYPES = {
     "zq_gather_rows": (_i, [_vp, _vp, _vp, _sz, _vp, _i, _err]),
     "zq_quantize": (_i, [_vp, _u32, _vp, _sz, _sz, _vp, _sz, _err]),
     "zq_linear": (_i, [_vp, _vp, _vp, _i, _sz, _vp, _i, _vp, _err]),
+    "zq_linear_batch": (_i, [_vp, C.POINTER(ZqLinearJob), _sz, _i, _i, _err]),
     "zq_linear_multi": (_i, [_vp, C.POINTER(_vp), _sz, _vp, _i, _sz, C.POINTER(_vp), _i, _err]),
     "zq_rmsnorm_linear": (_i, [_vp, C.POINTER(_vp), _sz, _vp, _i, _sz, _vp, C.c_float, C.c_float, C.POINTER(_vp), _i, _err]),
     "zq_gated_silu": (_i, [_vp, _vp, _vp, _vp, _i, _sz, _vp, _i, _err]),
