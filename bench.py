@@ -267,7 +267,7 @@ def run_ours(args):
 
     def step(events=None):
         for bi, (m, fmt, members) in enumerate(blocks):
-            mark = events is not None and fmt == Q4_K and m <= 4
+            mark = events is not None
             if mark:
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
@@ -280,7 +280,7 @@ def run_ours(args):
                     dist.all_reduce(y)
             if mark:
                 e1.record()
-                events.append((e0, e1))
+                events.append((bi, e0, e1))
 
     step_bytes = sum(algorithmic_bytes(case[2], case[3], m) for m, case in plan)
     q4k_kernel_bytes = sum(algorithmic_bytes(case[2], case[3], m) for m, case in plan if case[1] == Q4_K and m <= 4)
@@ -309,7 +309,14 @@ def run_ours(args):
     barrier()
     ctx.sync()
     elapsed_ms = t0.elapsed_time(t1)
-    kernel_ms = sum(a.elapsed_time(b) for a, b in events)
+    block_ms = [0.0] * len(blocks)
+    for bi, a, b in events:
+        block_ms[bi] += a.elapsed_time(b)
+    kernel_ms = sum(t for t, (m, fmt, _) in zip(block_ms, blocks) if fmt == Q4_K and m <= 4)
+    # every block of the step on its own (this rank's CUDA events inside the timed region)
+    blocks_report = [{"batch": m, "format": "q4_k" if fmt == Q4_K else "q4_0", "us": round(t / max(args.steps, 1) * 1e3, 2),
+                      "gbs": round(sum(algorithmic_bytes(c[2], c[3], mm) for mm, c in members) / (t / max(args.steps, 1) * 1e-3) / 1e9 / max(world, 1), 1) if t > 0 else None}
+                     for t, (m, fmt, members) in zip(block_ms, blocks)]
     launches = ctx.launch_count - launches_before
     if graphs:  # replayed launches do not pass through the library's counter: count what each graph captured
         launches = sum(launches_per_graph) * args.steps
@@ -393,6 +400,7 @@ def run_ours(args):
                      "kernel": "zq::gemv_i8_kernel<Q4_K, 1 column tile> (batch 1 and 4, one launch per matrix)" if args.per_call else "zq::gemv_wl_kernel<Q4_K, 1 column tile> (batch 1 and 4; one launch per block of five matrices, timed together with its record pass)", "peak_kind": peak_kind, "launches": q4k_kernel_launches * args.steps,
                      "bytes_per_launch_avg": q4k_kernel_bytes // max(q4k_kernel_launches, 1)},
         "gpu_launches": launches, "clocks": clocks, "e2e": e2e, "cpu_baseline": cpu,
+        "blocks": blocks_report,
     }
     line.update(extras)
     print(json.dumps(line))

@@ -106,13 +106,15 @@ template <uint32_t TYPE, int NT> struct WlSmem {
 };
 
 constexpr int kWlConsumers = kI8Threads;        // 16 consumer warps: 8 row sub-tiles x 2 units
-constexpr int kWlThreads = kWlConsumers + 32;   // + one producer warp
+constexpr int kWlThreads = kWlConsumers + 64;   // + the producer warp and the finisher warp
 // Named barriers (0 is left to __syncthreads, which this kernel never uses: the producer warp runs its own loop).
 constexpr int kBarQuad = 1;    // 1..4: the four warps that hold gate and up sums of the same 16 output rows (gated tiles)
 constexpr int kBarPair = 5;    // 5..12: the two warps (unit halves) of one row sub-tile
-constexpr int kBarAll = 13;    // the 16 consumer warps (tiles cut by a range boundary)
+constexpr int kBarFix = 13;    // 13, 14: the 16 consumer warps hand a cut tile's partial sums to the finisher warp (first / second cut piece)
+constexpr int kBarAll = 15;    // the 16 consumer warps among themselves (9..16 activation rows: they finish cut tiles on their own)
 
 __device__ __forceinline__ void named_bar_sync(int id, int threads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory"); }
+__device__ __forceinline__ void named_bar_arrive(int id, int threads) { asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory"); }
 
 // CTA that owns ring item q when Q items are cut into G ranges [floor(c Q / G), floor((c + 1) Q / G)).
 __device__ __forceinline__ int wl_owner(long long q, long long G, long long Q) { return (int)(((q + 1) * G - 1) / Q); }
@@ -149,6 +151,9 @@ __global__ void __launch_bounds__(kWlThreads, 1) gemv_wl_kernel(const __grid_con
     uint64_t *empty = full + 8;
     __shared__ uint32_t s_abort;
     __shared__ int s_nseg, s_last, s_c0, s_cl;
+    // Up to 8 activation rows a cut tile's partial sums are a few KB and one warp adds them up beside the consumers; with
+    // 9..16 rows that warp would need longer than the consumers themselves, so they do it together (and wait for it).
+    constexpr bool kAsyncFix = NT < 4;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const long long G = gridDim.x, Q = a.q_total;
@@ -182,6 +187,25 @@ __global__ void __launch_bounds__(kWlThreads, 1) gemv_wl_kernel(const __grid_con
             }
         }
         if (q < q1) atomicMax(a.status, (uint32_t)kStatusBadIndex);  // the host sizes launches so that this never happens
+        // Cut tiles first: a piece of a tile that a range boundary cuts (only the first and the last piece of a range can
+        // be one) is finished by whichever contributor arrives last, so every CTA does its cut pieces at the start and
+        // the hand-over completes under the streaming of the whole tiles instead of at the very end of the kernel.
+        if (n >= 2) {
+            const int4 last = segs[n - 1];
+            const bool last_cut = !((last.z & 0xFFFF) == 0 && (last.z >> 16) == a.jobs[last.x].chunks);
+            const int4 first = segs[0];
+            const bool first_cut = !((first.z & 0xFFFF) == 0 && (first.z >> 16) == a.jobs[first.x].chunks);
+            if (last_cut) {
+                const int pos = first_cut ? 1 : 0;
+                for (int k = n - 1; k > pos; --k) segs[k] = segs[k - 1];
+                segs[pos] = last;
+                int item = 0;
+                for (int k = 0; k < n; ++k) {
+                    segs[k].w = item;
+                    item += (segs[k].z >> 16) - (segs[k].z & 0xFFFF);
+                }
+            }
+        }
         s_nseg = n;
     }
     __syncthreads();  // the only CTA-wide barrier: before the roles part
@@ -190,6 +214,77 @@ __global__ void __launch_bounds__(kWlThreads, 1) gemv_wl_kernel(const __grid_con
     const int total_items = last_item < n_items ? last_item : n_items;
     const uint32_t abort_addr = smem_u32(&s_abort);
 
+    if (warp == kWlConsumers / 32 + 1) {
+        // ------------------------------------------------------------------------------------------ finisher warp
+        // Completes the tiles this CTA shares with its neighbours, off the consumers' path: waits until the consumers
+        // have stored a cut piece's partial sums, publishes them (fence + arrival count) and, if this CTA was the last
+        // contributor, adds all partials in CTA order and stores the tile.
+        pdl_launch_dependents();
+        if (!kAsyncFix) return;
+        pdl_wait_prior_grid();  // outputs and the fix-up scratch belong to earlier kernels until they complete
+        constexpr int G4 = 4 * NT;  // float4 groups per lane: 128 rows x (4 NT) activation rows / 4 / 32 lanes
+        for (int k = 0; k < 2 && k < nseg; ++k) {
+            const int4 sg = segs[k];
+            const WlJob &jb = a.jobs[sg.x];
+            const int tile = sg.y, cb = sg.z & 0xFFFF, ce = sg.z >> 16, M = jb.m;
+            if (cb == 0 && ce == jb.chunks) break;  // cut pieces come first
+            named_bar_sync(kBarFix + k, kWlConsumers + 32);  // the consumers have stored this piece's partial sums
+            int last = 0, c0 = 0, cl = 0;
+            if (lane == 0) {
+                __threadfence();
+                const long long ts = (long long)jb.q_begin + (long long)tile * jb.chunks;
+                c0 = wl_owner(ts, G, Q);
+                cl = wl_owner(ts + jb.chunks - 1, G, Q);
+                last = atomicAdd(&a.counters[c0], 1u) == (uint32_t)(cl - c0);
+            }
+            last = __shfl_sync(0xffffffffu, last, 0);
+            c0 = __shfl_sync(0xffffffffu, c0, 0);
+            cl = __shfl_sync(0xffffffffu, cl, 0);
+            if (!last) continue;
+            __threadfence();
+            // A slot is [activation row][128 tile rows] f32.  Lane L owns tile rows 4L..4L+3 (one float4) of every
+            // activation row; up to 8 activation rows are summed at a time so that a contributor costs one round trip.
+            constexpr int GB = G4 < 8 ? G4 : 8;
+            for (int qb = 0; qb < G4 && qb < M; qb += GB) {
+                float4 acc[GB];
+#pragma unroll
+                for (int i = 0; i < GB; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int c = c0; c <= cl; ++c) {
+                    const float4 *ps = reinterpret_cast<const float4 *>(a.partials + (size_t)(2 * c + (c == c0 ? 1 : 0)) * kSlotFloats);
+                    float4 got[GB];
+#pragma unroll
+                    for (int i = 0; i < GB; ++i) got[i] = qb + i < M ? __ldcg(ps + lane + 32 * (qb + i)) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int i = 0; i < GB; ++i) {
+                        acc[i].x += got[i].x; acc[i].y += got[i].y; acc[i].z += got[i].z; acc[i].w += got[i].w;
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < GB; ++i) {
+                    const int tok = qb + i;
+                    if (tok >= M) break;  // warp-uniform
+                    const float vv[4] = {acc[i].x, acc[i].y, acc[i].z, acc[i].w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int row = 4 * lane + e;  // row inside the 128-row slot
+                        float v = vv[e];
+                        if (GATED) {
+                            const float up = __shfl_down_sync(0xffffffffu, v, 16);  // lanes 16..31 hold rows 64..127: the up sums
+                            if (row >= out_rows) continue;
+                            v = (v / (1.0f + expf(-v))) * up;
+                        }
+                        const int n = tile * out_rows + row;
+                        if (n >= jb.n_out) continue;
+                        const size_t o = (size_t)tok * jb.n_out + n;
+                        if (jb.residual) v += load_as_f32(jb.residual, a.y_dtype, o);
+                        store_from_f32(jb.y, a.y_dtype, o, v);
+                    }
+                }
+            }
+            if (lane == 0) a.counters[c0] = 0;  // ready for the next launch
+        }
+        return;
+    }
     if (warp == kWlConsumers / 32) {
         // ------------------------------------------------------------------------------------------ producer warp
         if (lane == 0) {
@@ -261,7 +356,7 @@ __global__ void __launch_bounds__(kWlThreads, 1) gemv_wl_kernel(const __grid_con
 
     float yacc[NT][2];
     uint32_t moff[NT], soff[NT];
-    int si = -1, seg_end = 0, chunk = 0, units = 0, M = 1, buf = 0;
+    int si = -1, seg_end = 0, chunk = 0, units = 0, M = 1, buf = 0, cut_k = 0;
     uint32_t rec_unit = 0;  // byte offset of this warp's unit inside a stage's records
     int stage = 0;
     uint32_t phase = 0;
@@ -358,33 +453,38 @@ __global__ void __launch_bounds__(kWlThreads, 1) gemv_wl_kernel(const __grid_con
                         }
                     }
                 }
-                __threadfence();
-                named_bar_sync(kBarAll, kWlConsumers);
-                if (tid == 0) {
-                    const long long ts = (long long)jb.q_begin + (long long)tile * jb.chunks;
-                    const int c0 = wl_owner(ts, G, Q), cl = wl_owner(ts + jb.chunks - 1, G, Q);
-                    const uint32_t old = atomicAdd(&a.counters[c0], 1u);
-                    s_last = old == (uint32_t)(cl - c0);
-                    s_c0 = c0;
-                    s_cl = cl;
-                }
-                named_bar_sync(kBarAll, kWlConsumers);
-                if (s_last) {  // every contributor has arrived: add the partials in CTA order
+                if constexpr (kAsyncFix) {
+                    named_bar_arrive(kBarFix + cut_k, kWlConsumers + 32);  // over to the finisher warp; this warp goes on
+                    ++cut_k;
+                } else {
                     __threadfence();
-                    const int c0 = s_c0, cl = s_cl;
-                    for (int i = tid; i < out_rows * M; i += kWlConsumers) {
-                        const int row = i & (out_rows - 1), tok = i / out_rows;
-                        float v = 0.f, vup = 0.f;
-                        for (int c = c0; c <= cl; ++c) {
-                            const float *ps = a.partials + (size_t)(2 * c + (c == c0 ? 1 : 0)) * kSlotFloats + tok * kTileRows;
-                            v += __ldcg(ps + row);
-                            if (GATED) vup += __ldcg(ps + out_rows + row);
-                        }
-                        finish(row, tok, v, vup);
+                    named_bar_sync(kBarAll, kWlConsumers);
+                    if (tid == 0) {
+                        const long long ts = (long long)jb.q_begin + (long long)tile * jb.chunks;
+                        const int c0 = wl_owner(ts, G, Q), cl = wl_owner(ts + jb.chunks - 1, G, Q);
+                        const uint32_t old = atomicAdd(&a.counters[c0], 1u);
+                        s_last = old == (uint32_t)(cl - c0);
+                        s_c0 = c0;
+                        s_cl = cl;
                     }
-                    if (tid == 0) a.counters[c0] = 0;  // ready for the next launch
+                    named_bar_sync(kBarAll, kWlConsumers);
+                    if (s_last) {  // every contributor has arrived: add the partials in CTA order
+                        __threadfence();
+                        const int c0 = s_c0, cl = s_cl;
+                        for (int i = tid; i < out_rows * M; i += kWlConsumers) {
+                            const int row = i & (out_rows - 1), tok = i / out_rows;
+                            float v = 0.f, vup = 0.f;
+                            for (int c = c0; c <= cl; ++c) {
+                                const float *ps = a.partials + (size_t)(2 * c + (c == c0 ? 1 : 0)) * kSlotFloats + tok * kTileRows;
+                                v += __ldcg(ps + row);
+                                if (GATED) vup += __ldcg(ps + out_rows + row);
+                            }
+                            finish(row, tok, v, vup);
+                        }
+                        if (tid == 0) a.counters[c0] = 0;  // ready for the next launch
+                    }
+                    named_bar_sync(kBarAll, kWlConsumers);  // s_last may be rewritten by the next cut tile only after everyone read it
                 }
-                named_bar_sync(kBarAll, kWlConsumers);  // s_last may be rewritten by the next cut tile only after everyone read it
             }
         }
     }
