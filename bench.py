@@ -117,6 +117,8 @@ def run_ours(args):
         faulthandler.dump_traceback_later(args.watchdog, exit=True)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), timeout=datetime.timedelta(seconds=120))
     ctx = B200Context(local_rank)
+    if world > 1 and not args.nccl_reduce:
+        ctx.dist_init(slot_bytes=4 << 20)  # peer group of the node: exchange buffers mapped over CUDA IPC
     if args.no_pdl:
         ctx.set_option("disable_pdl", 1)
     if args.f16_gemv:
@@ -204,8 +206,11 @@ def run_ours(args):
         name, fmt, k, n, mode, w, (c0, c1), (r0, r1) = case
         x = x_local[(m, k, c0, c1)]
         y = outs[(m, name, k, n)]
+        if mode == "row" and world > 1 and not args.nccl_reduce:
+            ffi.call("zq_linear_row_parallel", ctx.handle, w.handle, C.c_void_p(x.data_ptr()), ffi.F32, m, C.c_void_p(y.data_ptr()), ffi.F32, None)
+            return
         ffi.call("zq_linear", ctx.handle, w.handle, C.c_void_p(x.data_ptr()), ffi.F32, m, C.c_void_p(y.data_ptr()), ffi.F32, None)
-        if mode == "row" and collective:
+        if mode == "row" and collective and world > 1:
             dist.all_reduce(y)
 
     # A block is one (batch, format) group: five distinct matrices, 175 MB of packed weights.  By default a block is ONE
@@ -233,8 +238,11 @@ def run_ours(args):
             arr[i].m = mm
             arr[i].dev_y = outs[(mm, name, k, n)].data_ptr()
             arr[i].dev_residual = None
+            # K-split matrices: the partial results of the ranks are summed by the library's own peer-store reduce kernel
+            arr[i].flags = ffi.JOB_ROW_PARALLEL if (mode == "row" and world > 1 and not args.nccl_reduce) else 0
         job_arrays.append(arr)
-    reduce_after = [[outs[(mm, case[0], case[2], case[3])] for mm, case in members if case[4] == "row"] for _, _, members in blocks]
+    # --nccl-reduce (A/B aid): the partials are summed by a host-launched NCCL all-reduce after the block instead
+    reduce_after = [[outs[(mm, case[0], case[2], case[3])] for mm, case in members if case[4] == "row" and args.nccl_reduce] for _, _, members in blocks]
 
     def launch_block(bi):
         m, fmt, members = blocks[bi]
@@ -373,6 +381,10 @@ def run_ours(args):
             "per_call_wait": {"value": round(step_bytes / t_call / 1e9, 2), "ms_per_step": round(t_call * 1e3, 3), "api": "zq_linear_host waiting inside every call"},
         }
 
+    parity = None
+    if world > 1 and not args.nccl_reduce:
+        parity = {"tp_row_split_max_rel_error": tp_parity(ctx, device, world, rank), "bound": 2e-3,
+                  "what": "Q4_K 1024x4096, 4 rows: K-split over the ranks + peer-store reduce, against the same weight as one matrix on one GPU"}
     # free the sweep's weights before the larger side measurements
     extras = {}
     if not args.no_extras:
@@ -400,12 +412,46 @@ def run_ours(args):
                      "kernel": "zq::gemv_i8_kernel<Q4_K, 1 column tile> (batch 1 and 4, one launch per matrix)" if args.per_call else "zq::gemv_wl_kernel<Q4_K, 1 column tile> (batch 1 and 4; one launch per block of five matrices, timed together with its record pass)", "peak_kind": peak_kind, "launches": q4k_kernel_launches * args.steps,
                      "bytes_per_launch_avg": q4k_kernel_bytes // max(q4k_kernel_launches, 1)},
         "gpu_launches": launches, "clocks": clocks, "e2e": e2e, "cpu_baseline": cpu,
-        "blocks": blocks_report,
+        "blocks": blocks_report, "parity": parity,
     }
     line.update(extras)
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def tp_parity(ctx, device, world, rank):
+    """Correctness of the multi-GPU path on the hardware it runs on, outside any timed region: one K-split matrix
+    (Q4_K, 1024 x 4096, 4 rows; every rank quantises its 256-aligned column slice, the blocks being independent the
+    slices concatenate to the full quantised weight) through the row-parallel entry, against the SAME weight as one
+    matrix on this GPU.  Returns max_i |a_i - e_i| / max(|e_i|, rms(e)), the largest over the ranks."""
+    import torch
+    import torch.distributed as dist
+
+    from zllm_b200.dist import shard_plan
+
+    n, k, m = 1024, 4096, 4
+    gen = torch.Generator(device=device)
+    gen.manual_seed(4242)
+    full = torch.randn((n, k), generator=gen, device=device, dtype=torch.float32) * 0.02
+    x = torch.randn((m, k), generator=gen, device=device, dtype=torch.float32)
+    units = k // 256
+    base, extra = divmod(units, world)
+    lo = rank * base + min(rank, extra)
+    hi = lo + base + (1 if rank < extra else 0)
+    c0, c1 = lo * 256, hi * 256
+    w_local = ctx.prepare_weight(Q4_K, ctx.quantize(Q4_K, full[:, c0:c1].contiguous()), n, c1 - c0)
+    w_full = ctx.prepare_weight(Q4_K, ctx.quantize(Q4_K, full), n, k)
+    got = ctx.linear_row_parallel(x[:, c0:c1].contiguous(), w_local)
+    want = ctx.linear(x, w_full)
+    ctx.sync()
+    rms = want.double().pow(2).mean().sqrt()
+    err = ((got.double() - want.double()).abs() / torch.maximum(want.double().abs(), rms)).max()
+    t = torch.tensor([float(err)], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    w_local.release()
+    w_full.release()
+    return float(t[0])
 
 
 def _time_ms(fn, reps):
@@ -671,6 +717,7 @@ def main():
     ap.add_argument("--watchdog", type=int, default=480, help="multi-GPU runs: seconds after which a stuck run dumps tracebacks and exits")
     ap.add_argument("--no-extras", action="store_true", help="skip the prefill-GEMM and MoE side measurements")
     ap.add_argument("--extras", default="all", choices=["all", "prefill", "moe"], help="which side measurements to run")
+    ap.add_argument("--nccl-reduce", action="store_true", help="several GPUs: sum the K-split partials with a host-launched NCCL all-reduce instead of the library's peer-store reduce (A/B aid)")
     ap.add_argument("--per-call", action="store_true", help="one zq_linear call (and launch) per matrix instead of one zq_linear_batch call per block (A/B aid)")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying CUDA graphs")
     ap.add_argument("--no-clocks", action="store_true", help="do not sample clocks with nvidia-smi")

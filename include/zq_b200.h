@@ -95,6 +95,7 @@ int zq_linear_multi(zq_ctx *ctx, const zq_weight *const *w, size_t n_weights, co
  * weights with up to 16 rows share launches (one per weight type, row-count class 1-4 / 5-8 / 9-16 and plain / gated);
  * every other job runs as its own zq_linear / zq_gated_silu call.  All jobs share x_dtype and y_dtype.  Results do not
  * depend on how the jobs are grouped beyond f32 rounding of the split-tile sums, and are the same from run to run. */
+enum { ZQ_JOB_ROW_PARALLEL = 1 };  /* zq_linear_job.flags: sum this job's result over the ranks of the peer group (zq_dist_init) */
 typedef struct zq_linear_job {
     const zq_weight *w;        /* the weight, or the gate of a gated pair */
     const zq_weight *w_up;     /* NULL, or the up weight of a gated pair */
@@ -102,8 +103,34 @@ typedef struct zq_linear_job {
     size_t m;
     void *dev_y;               /* [m, rows] */
     const void *dev_residual;  /* NULL, or [m, rows] in y_dtype */
+    uint32_t flags;            /* 0, or ZQ_JOB_ROW_PARALLEL (plain jobs only) */
 } zq_linear_job;
 int zq_linear_batch(zq_ctx *ctx, const zq_linear_job *jobs, size_t n_jobs, int x_dtype, int y_dtype, zq_error *err);
+/* ---- tensor parallelism over the GPUs of one node (one process and one context per GPU).
+ * Column split (output rows divided over the ranks) needs nothing from this library: every rank prepares its rows as a
+ * weight of its own.  Row split (input columns divided on 256-column boundaries, the rule of the reference's two-GPU
+ * operator pair, src/backend/rocm/expert.rs:182-207) leaves every rank with a partial result; the ranks' partials are
+ * exchanged and added (src/backend/rocm/expert.rs:1394-1409; the fused join of
+ * src/kernel/rocm/hip/peer_copy/source.hip:64-81) by ONE kernel per call that stores them into every peer's exchange
+ * buffer over NVLink (plain 8-byte stores of {value, epoch} into memory mapped with CUDA IPC), polls the peers' words with
+ * a bounded wait and adds in rank order: no host-launched collective, so a whole decode step stays one CUDA graph.  A wait that runs
+ * out sets the device status word (zq_ctx_sync reports it) and the kernel returns; nothing hangs.
+ *   zq_dist_export  allocates this rank's exchange buffer (`slot_bytes` = 8 bytes per f32 partial result of the largest
+ *                   call, the same on every rank) and writes ZQ_DIST_HANDLE_BYTES bytes to hand to the other ranks;
+ *   zq_dist_init    takes the blobs of all ranks in rank order (exchanged by the host: a channel, a file, MPI, NCCL ...).
+ * Every rank must issue the same sequence of row-parallel calls with the same shapes. */
+#define ZQ_DIST_HANDLE_BYTES 80
+int zq_dist_export(zq_ctx *ctx, size_t slot_bytes, void *out_handle, zq_error *err);
+int zq_dist_init(zq_ctx *ctx, int rank, int world, const void *all_handles, zq_error *err);
+int zq_dist_set_wait_ms(zq_ctx *ctx, unsigned milliseconds, zq_error *err);
+int zq_dist_rank(const zq_ctx *ctx);
+int zq_dist_world(const zq_ctx *ctx);
+void zq_dist_shutdown(zq_ctx *ctx);
+/* y = sum over ranks of (W_rank x_rank) (+ residual): this rank's column slice of the weight against its slice of the
+ * input, any number of rows (decode kernel up to 16 rows, tensor-core GEMM above).  Same as a one-job zq_linear_batch
+ * with ZQ_JOB_ROW_PARALLEL.  Without a peer group (or a group of one) it is zq_linear. */
+int zq_linear_row_parallel(zq_ctx *ctx, const zq_weight *w, const void *dev_x, int x_dtype, size_t m, void *dev_y, int y_dtype, const void *dev_residual, zq_error *err);
+
 /* Backend::rmsnorm_linear / rmsnorm_dual_linear (src/backend/mod.rs:455-464): RMSNorm of every input row
  * (src/kernel/cpu/rmsnorm.rs:7-41: x * 1/sqrt(mean(x^2) + eps) * (norm_weight + weight_offset); offset 0 = plain,
  * 1 = the "Gemma" form), then 1 to 3 linear layers on the normalised rows.  `dev_norm_weight`: f32 [cols].  The

@@ -1,0 +1,236 @@
+"""GPU parity at the sizes the benchmark configurations name, through the C ABI, against the CPU oracle.
+
+The oracle cannot run a 17408 x 5120 x 16384 product in test time, so at these sizes it is evaluated on a seeded
+subsample: a block of weight rows (their packed bytes are a contiguous slice of the weight) against a block of tokens,
+about 2 000 (row, token) pairs per case, with the oracle's own matmul.  Weights are quantised on the device (the Q4_K
+encoder is bit-identical to the reference's, tests/test_gpu_codec.py) and the same bytes go to the oracle.
+
+Tolerance: max_i |a_i - e_i| / max(|e_i|, rms(e)) <= 2e-3 per quantised matmul (fp32 accumulation); rms is that of the
+compared block.  The MoE layer chains two matmuls per expert: the chain is checked matmul by matmul (the oracle's down
+projection is fed the device's own activated intermediate), and end to end against 4e-3.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as orc
+from tests import helpers as H
+from tests.gpu_util import ctx, host
+
+pytestmark = pytest.mark.gpu
+BOUND = 2e-3
+
+
+def _device_weight(rows, cols, seed, std=0.02):
+    """Q4_K weight quantised on the device; returns (weight handle, packed bytes on the host)."""
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(seed)
+    full = torch.randn((rows, cols), generator=gen, device="cuda", dtype=torch.float32) * std
+    packed = ctx().quantize(H.Q4_K, full)
+    del full
+    w = ctx().prepare_weight(H.Q4_K, packed, rows, cols)
+    return w, packed.cpu().numpy()
+
+
+def _sample_check(got, packed, rows, cols, x_f32, row_blocks, tok_blocks, bound=BOUND):
+    """got: [m, rows] device result (f32, host); packed: GGUF bytes of the whole weight."""
+    row_bytes = orc.row_bytes(H.Q4_K, cols)
+    worst = 0.0
+    for (r0, nr), (t0, nt) in zip(row_blocks, tok_blocks):
+        sub = packed[r0 * row_bytes:(r0 + nr) * row_bytes]
+        want = orc.linear(H.Q4_K, sub, nr, cols, np.ascontiguousarray(x_f32[t0:t0 + nt]))
+        worst = max(worst, H.max_rel_error(got[t0:t0 + nt, r0:r0 + nr], want))
+    assert worst <= bound, f"max relative error {worst} on the sampled blocks"
+
+
+@pytest.mark.parametrize("variant", ["fused", "operand_pass"])
+@pytest.mark.parametrize("rows,cols,m", [(17408, 5120, 4096), (5120, 17408, 4096), (17408, 5120, 16384)])
+def test_prefill_gemm_at_benchmark_size(variant, rows, cols, m):
+    """configs[2]: Q4_K 5120 -> 17408 and 17408 -> 5120, bf16 activations, 4 096 and 16 384 tokens: the persistent tile
+    scheduler over all SMs, K = 17408 through the stage ring, ragged nothing; both GEMM kernels."""
+    if variant == "operand_pass" and m == 16384:
+        pytest.skip("one 16 384-token case is enough; the operand-pass kernel runs the 4 096-token cases")
+    c = ctx()
+    c.set_option("disable_fused_gemm", 1 if variant == "operand_pass" else 0)
+    c.set_option("force_fused_gemm", 1 if variant == "fused" else 0)
+    try:
+        w, packed = _device_weight(rows, cols, seed=rows + m)
+        gen = torch.Generator(device="cuda")
+        gen.manual_seed(m)
+        x = torch.randn((m, cols), generator=gen, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+        y = host(c.linear(x, w, out_dtype=torch.float32))
+        x_f32 = x.float().cpu().numpy()
+        rng = np.random.default_rng(rows ^ m)
+        # 8 blocks of 16 rows x 16 tokens = 2 048 pairs, including the last rows and the last tokens
+        row_blocks = [(int(rng.integers(0, rows - 16)), 16) for _ in range(7)] + [(rows - 16, 16)]
+        tok_blocks = [(int(rng.integers(0, m - 16)), 16) for _ in range(7)] + [(m - 16, 16)]
+        _sample_check(y, packed, rows, cols, x_f32, row_blocks, tok_blocks)
+        w.release()
+    finally:
+        c.set_option("disable_fused_gemm", 0)
+        c.set_option("force_fused_gemm", 0)
+        torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("m", [1024, 1025])
+def test_prefill_gemm_around_the_kernel_switch(m):
+    """Up to 1 024 tokens Q4_K prefill takes the fused kernel, above it the operand pass: both sides of the switch."""
+    rows, cols = 5120, 2048
+    w, packed = _device_weight(rows, cols, seed=m)
+    x = torch.randn((m, cols), device="cuda", dtype=torch.float32).to(torch.bfloat16)
+    y = host(ctx().linear(x, w, out_dtype=torch.float32))
+    _sample_check(y, packed, rows, cols, x.float().cpu().numpy(), [(0, 32), (rows - 32, 32)], [(0, 32), (m - 32, 32)])
+    w.release()
+
+
+def _random_experts(n, hidden, inter, seed):
+    """Random packed Q4_K experts generated on the device (uniform codes under small positive f16 super-block scales: the
+    value range of real tensors, every code occurs); returns lists of (handle, host bytes) for gate, up, down."""
+    c = ctx()
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(seed)
+    out = []
+    for rows, cols in ((inter, hidden), (inter, hidden), (hidden, inter)):
+        blocks = rows * cols // 256
+        mats = []
+        for e in range(n):
+            packed = torch.randint(0, 256, (blocks, 144), generator=gen, device="cuda", dtype=torch.uint8)
+            d = (torch.rand((blocks, 2), generator=gen, device="cuda") * 2.0e-4 + 2.0e-4).to(torch.float16)
+            packed[:, 0:4] = d.view(torch.uint8).reshape(blocks, 4)
+            flat = packed.reshape(-1)
+            mats.append((c.prepare_weight(H.Q4_K, flat, rows, cols), flat))
+        out.append(mats)
+    return out
+
+
+def test_moe_layer_at_benchmark_size():
+    """configs[4]: 256 experts, top-8, hidden 7168, expert FFN 2048, Q4_K, one shared expert, softmax top-k router, bf16
+    activations.  64 tokens (the device-grouped decode path) are checked in full; of 8 192 tokens (host-grouped routes,
+    two grouped tensor-core launches) a seeded subsample of tokens is checked, the oracle running only the experts those
+    tokens hit."""
+    from zllm_b200.backend import MoeExperts, moe_forward, moe_route
+
+    E, K, Hd, I = 256, 8, 7168, 2048
+    c = ctx()
+    gates, ups, downs = _random_experts(E + 1, Hd, I, seed=9)  # the last one is the shared expert
+    table = MoeExperts(c, [g[0] for g in gates[:E]], [u[0] for u in ups[:E]], [d[0] for d in downs[:E]])
+    shared = (gates[E][0], ups[E][0], downs[E][0])
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(10)
+    router = torch.randn((E, Hd), generator=gen, device="cuda", dtype=torch.float32) / (Hd ** 0.5)
+    host_cache = {}
+
+    def host_mat(lst, e):
+        key = (id(lst), e)
+        if key not in host_cache:
+            host_cache[key] = lst[e][1].cpu().numpy()
+        return host_cache[key]
+
+    def oracle_rows(x_rows, ids_rows, w_rows):
+        """The oracle's MoE forward for a few tokens: only the experts they hit are brought to the host; the other
+        entries of the expert lists are never touched because no route names them."""
+        hit = sorted(set(int(e) for e in ids_rows.reshape(-1)))
+        remap = {e: i for i, e in enumerate(hit)}
+        g = [(H.Q4_K, host_mat(gates, e), I, Hd) for e in hit]
+        u = [(H.Q4_K, host_mat(ups, e), I, Hd) for e in hit]
+        d = [(H.Q4_K, host_mat(downs, e), Hd, I) for e in hit]
+        local_ids = np.vectorize(remap.get)(ids_rows).astype(np.uint32)
+        sh = ((H.Q4_K, host_mat(gates, E), I, Hd), (H.Q4_K, host_mat(ups, E), I, Hd), (H.Q4_K, host_mat(downs, E), Hd, I))
+        return orc.moe_forward(g, u, d, x_rows, local_ids, w_rows, shared=sh)
+
+    for m, check in ((64, list(range(0, 64, 8))), (8192, [0, 1234, 4095, 8191])):
+        x = torch.randn((m, Hd), generator=gen, device="cuda", dtype=torch.float32).to(torch.bfloat16)
+        ids, wts = moe_route(c, x, router, K, 1.0, True)
+        y = moe_forward(c, table, x, ids, wts, shared=shared, out_dtype=torch.float32)
+        c.sync()
+        ids_np, w_np = ids.cpu().numpy().astype(np.uint32), wts.cpu().numpy()
+        x_np = x.float().cpu().numpy()
+        # router parity on every token: ids exact, weights to 2e-5
+        want_ids, want_w = orc.moe_route_softmax(x_np, router.cpu().numpy(), K, 1.0, True)
+        # From 256 tokens the logits come from the tensor cores (two f16 limbs per operand, 22 bits): of 8 192 x 256 logits
+        # a few pairs lie closer together than that resolution and may swap places; everywhere else ids are exact.
+        same = (ids_np == want_ids).all(axis=1)
+        assert same.all() if m == 64 else same.mean() >= 0.998, f"{m} tokens: {int((~same).sum())} tokens route differently"
+        np.testing.assert_allclose(w_np[same], want_w[same], rtol=2e-5, atol=1e-7)
+        check = [t for t in check if same[t]]
+        got = y.cpu().numpy()[check]
+        want = oracle_rows(x_np[check], ids_np[check], w_np[check])
+        err = H.max_rel_error(got, want)
+        # decode path: 16-bit integer activations, f32 intermediate; prefill path: f16 operands on both matmuls of the chain
+        assert err <= (BOUND if m == 64 else 2 * BOUND), f"{m} tokens: max relative error {err}"
+    del table
+    for lst in (gates, ups, downs):
+        for w, _ in lst:
+            w.release()
+    torch.cuda.empty_cache()
+
+
+def test_gated_mlp_chain_meets_the_bound_matmul_by_matmul():
+    """The 2e-3 bound is per quantised matmul.  gate/up + SiLU and down at an expert's shape (7168 -> 2048 -> 7168), 300
+    tokens on the tensor-core path: the activated intermediate against the oracle's gated matmul, and the down projection
+    against the oracle's matmul fed with the DEVICE's intermediate."""
+    c = ctx()
+    Hd, I, m = 7168, 2048, 300
+    (wg, pg), (wu, pu), (wd, pd) = [_device_weight(r, k, seed=s, std=sd) for r, k, s, sd in ((I, Hd, 1, 0.02), (I, Hd, 2, 0.02), (Hd, I, 3, 0.05))]
+    x = torch.randn((m, Hd), device="cuda", dtype=torch.float32).to(torch.bfloat16)
+    mid = c.gated_linear(x, wg, wu, out_dtype=torch.float16)  # what the chain hands to the down projection
+    y = c.linear(mid, wd, out_dtype=torch.float32)
+    c.sync()
+    toks = [0, 7, 150, 299]
+    x_np = x.float().cpu().numpy()[toks]
+    want_mid = orc.gated_linear(H.Q4_K, pg, pu, I, Hd, x_np)
+    err_mid = H.max_rel_error(mid.float().cpu().numpy()[toks], want_mid)
+    assert err_mid <= 2 * BOUND, f"activated intermediate: {err_mid}"  # a product of two matmul results, each within the bound
+    want_y = orc.linear(H.Q4_K, pd, Hd, I, mid.float().cpu().numpy()[toks])
+    err_y = H.max_rel_error(y.cpu().numpy()[toks], want_y)
+    assert err_y <= BOUND, f"down projection on the device's intermediate: {err_y}"
+    for w in (wg, wu, wd):
+        w.release()
+
+
+@pytest.mark.parametrize("normalize", [True, False])
+def test_router_with_bias_matches_cpu_path(normalize):
+    """kernel::cuda::routing adds a bias to the logits before the softmax (src/kernel/cuda/routing.rs:30); the CPU
+    routing takes logits, so the oracle gets x router^T + bias.  Small batch (one kernel), split experts and the
+    tensor-core logits of large batches."""
+    from zllm_b200.backend import moe_route
+
+    for m, experts, top_k, hidden in ((3, 16, 4, 256), (64, 256, 8, 512), (300, 64, 6, 1024)):
+        rng = np.random.default_rng(m)
+        x = rng.standard_normal((m, hidden)).astype(np.float32)
+        router = (rng.standard_normal((experts, hidden)) / np.sqrt(hidden)).astype(np.float32)
+        bias = rng.standard_normal(experts).astype(np.float32)
+        ids, w = moe_route(ctx(), torch.from_numpy(x).cuda(), torch.from_numpy(router).cuda(), top_k, 1.25, normalize, bias=torch.from_numpy(bias).cuda())
+        ctx().sync()
+        logits = (x.astype(np.float64) @ router.astype(np.float64).T + bias).astype(np.float32)
+        rows = [orc.route_softmax_logits(logits[t], top_k, 1.25, normalize) for t in range(m)]
+        want_ids, want_w = np.stack([r[0] for r in rows]), np.stack([r[1] for r in rows])
+        got_ids = ids.cpu().numpy().astype(np.uint32)
+        # a bias-shifted near-tie may order differently in f32 and f64 logits: compare where the logit gap is clear
+        order = np.sort(logits, axis=1)[:, ::-1]
+        clear = np.all(np.abs(np.diff(order[:, :top_k + 1], axis=1)) > 1e-5, axis=1)
+        assert clear.mean() > 0.9
+        assert np.array_equal(got_ids[clear], np.asarray(want_ids).reshape(m, top_k)[clear])
+        np.testing.assert_allclose(w.cpu().numpy()[clear], np.asarray(want_w).reshape(m, top_k)[clear], rtol=1e-4, atol=1e-6)
+
+
+def test_router_row_of_nans_is_reported_not_faulted():
+    """A token whose activations are NaN has no arg-max: the router writes valid expert ids, NaN weights, and the status
+    word reports it; nothing is read or written out of range."""
+    from zllm_b200 import ffi
+    from zllm_b200.backend import moe_route
+
+    m, experts, top_k, hidden = 4, 32, 4, 256
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal((m, hidden)).astype(np.float32)
+    x[2, :] = np.nan
+    router = (rng.standard_normal((experts, hidden)) / 16).astype(np.float32)
+    ids, w = moe_route(ctx(), torch.from_numpy(x).cuda(), torch.from_numpy(router).cuda(), top_k, 1.0, True)
+    with pytest.raises(ffi.ZqFailure) as info:
+        ctx().sync()
+    assert info.value.code == 5
+    got = ids.cpu().numpy()
+    assert got.min() >= 0 and got.max() < experts
+    want_ids, _ = orc.moe_route_softmax(x[[0, 1, 3]], router, top_k, 1.0, True)
+    assert np.array_equal(got[[0, 1, 3]].astype(np.uint32), want_ids)
+    ctx().sync()  # the status was reported once; the context goes on

@@ -165,8 +165,9 @@ class B200Context:
     def linear_batch(self, jobs, out_dtype=None):
         """Independent decode projections in as few launches as possible (``zq_linear_batch``).
 
-        ``jobs`` is a list of ``(x, weight)``, ``(x, weight, residual)`` or ``(x, gate, up, "gated")`` tuples; all inputs
-        share one dtype.  Returns the list of outputs."""
+        ``jobs`` is a list of ``(x, weight)``, ``(x, weight, residual)``, ``(x, gate, up, "gated")`` or
+        ``(x, weight, residual_or_None, "row")`` tuples (the last form is a row-parallel job: its result is summed over the
+        ranks of the peer group); all inputs share one dtype.  Returns the list of outputs."""
         arr = (ffi.ZqLinearJob * len(jobs))()
         ys, keep = [], []
         x_dt = None
@@ -180,18 +181,47 @@ class B200Context:
                 raise TypeError("linear_batch: all inputs must share one dtype")
             od = out_dtype or x.dtype
             y = torch.empty((m, w.rows), dtype=od, device=x.device)
-            residual = job[2].contiguous() if (len(job) == 3 and job[2] is not None) else None
+            row = len(job) == 4 and job[3] == "row"
+            residual = job[2].contiguous() if ((len(job) == 3 or row) and job[2] is not None) else None
             arr[i].w = w.handle.value
             arr[i].w_up = job[2].handle.value if gated else None
             arr[i].dev_x = x.data_ptr()
             arr[i].m = m
             arr[i].dev_y = y.data_ptr()
             arr[i].dev_residual = residual.data_ptr() if residual is not None else None
+            arr[i].flags = ffi.JOB_ROW_PARALLEL if row else 0
             ys.append(y)
             keep.append((x, residual))
         if jobs:
             ffi.call("zq_linear_batch", self.handle, arr, len(jobs), _DTYPES[x_dt], _DTYPES[out_dtype or x_dt])
         return ys
+
+    def linear_row_parallel(self, x: torch.Tensor, w: Weight, out_dtype=None, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """This rank's column slice of a weight against its slice of the input; the ranks' partial results are summed
+        (``zq_linear_row_parallel``)."""
+        x = x.contiguous()
+        m = self._rows(x, w.cols)
+        out_dtype = out_dtype or x.dtype
+        y = torch.empty((m, w.rows), dtype=out_dtype, device=x.device)
+        if residual is not None:
+            residual = residual.contiguous()
+        ffi.call("zq_linear_row_parallel", self.handle, w.handle, _ptr(x), _dt(x), m, _ptr(y), _DTYPES[out_dtype], _ptr(residual))
+        return y
+
+    def dist_init(self, slot_bytes: int = 4 << 20, group=None):
+        """Joins the peer group of the node: allocates this rank's exchange buffer, exchanges the handles of all ranks
+        through ``torch.distributed`` (any transport would do: the library only sees the bytes) and maps the peers."""
+        import torch.distributed as dist
+
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        blob = (C.c_uint8 * ffi.DIST_HANDLE_BYTES)()
+        ffi.call("zq_dist_export", self.handle, int(slot_bytes), blob)
+        mine = torch.tensor(list(blob), dtype=torch.uint8, device=self.device if dist.get_backend(group) == "nccl" else "cpu")
+        gathered = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(gathered, mine, group=group)
+        flat = bytes(torch.cat(gathered).cpu().tolist())
+        buf = (C.c_uint8 * len(flat)).from_buffer_copy(flat)
+        ffi.call("zq_dist_init", self.handle, rank, world, buf)
 
     def linear_multi(self, x: torch.Tensor, weights: Sequence[Weight], out_dtype=None):
         x = x.contiguous()

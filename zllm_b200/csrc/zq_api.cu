@@ -1,5 +1,6 @@
 // C-ABI entry points, context and resident-weight management of the zq_b200 library.
 #include "zq_common.cuh"
+#include "zq_dist.cuh"
 #include "zq_wl.cuh"
 
 namespace zq {
@@ -186,6 +187,7 @@ int zq_ctx_create(int device, zq_ctx **out, zq_error *err) {
 
 void zq_ctx_destroy(zq_ctx *ctx) {
     if (!ctx) return;
+    zq_dist_shutdown(ctx);
     cudaSetDevice(ctx->device);
     if (ctx->own_stream || ctx->stream) cudaStreamSynchronize(ctx->stream);
     if (ctx->gemv_partials) cudaFree(ctx->gemv_partials);
@@ -227,7 +229,8 @@ int zq_ctx_sync(zq_ctx *ctx, zq_error *err) {
         const char *what = status == kStatusTmaTimeout ? "a TMA copy did not complete within its wait limit"
                          : status == kStatusMmaTimeout ? "a tensor-core pipeline wait ran out"
                          : status == kStatusTmemAlloc ? "tensor memory could not be allocated"
-                         : status == kStatusBadIndex ? "an index argument was out of range (the access was skipped)" : "unknown device status";
+                         : status == kStatusBadIndex ? "an index argument was out of range (the access was skipped)"
+                         : status == kStatusPeerTimeout ? "a peer rank's partial result did not arrive within the wait limit" : "unknown device status";
         return set_error(err, ZQ_ERR_DEVICE_STATUS, "device status %u: %s", status, what);
     }
     return ZQ_OK;
@@ -394,29 +397,62 @@ static int run_job_alone(zq_ctx *ctx, const zq_linear_job &j, int x_dtype, int y
 
 int zq_linear_batch(zq_ctx *ctx, const zq_linear_job *jobs, size_t n_jobs, int x_dtype, int y_dtype, zq_error *err) {
     if (!ctx || (!jobs && n_jobs)) return set_error(err, ZQ_ERR_ARG, "zq_linear_batch: null argument");
+    const bool grouped = ctx->dist && ctx->dist->world > 1;  // row-parallel jobs are summed over the peer group
     // validate everything before anything is enqueued: a bad job must not leave half a batch running
+    size_t rp_floats = 0, rp_jobs = 0;
     for (size_t i = 0; i < n_jobs; ++i) {
         const zq_linear_job &j = jobs[i];
         int rc = check_linear(ctx, j.w, j.dev_x, x_dtype, j.m, j.dev_y, y_dtype, err);
         if (rc) return rc;
+        if (j.flags & ~(uint32_t)ZQ_JOB_ROW_PARALLEL) return set_error(err, ZQ_ERR_ARG, "zq_linear_batch: job %zu: unknown flag bits 0x%x", i, j.flags);
         if (j.w_up) {
             if (j.w_up->ctx != ctx) return set_error(err, ZQ_ERR_ARG, "zq_linear_batch: job %zu: up weight belongs to another context", i);
             if (j.w->rows != j.w_up->rows || j.w->cols != j.w_up->cols || j.w->type != j.w_up->type) return set_error(err, ZQ_ERR_SHAPE, "zq_linear_batch: job %zu: gate and up differ in shape or type", i);
             if (j.dev_residual) return set_error(err, ZQ_ERR_ARG, "zq_linear_batch: job %zu: a gated job takes no residual", i);
+            if (j.flags & ZQ_JOB_ROW_PARALLEL) return set_error(err, ZQ_ERR_ARG, "zq_linear_batch: job %zu: a gated job cannot be row-parallel (the activation is not linear)", i);
         }
         if (reinterpret_cast<uintptr_t>(j.dev_residual) & 15) return set_error(err, ZQ_ERR_ARG, "zq_linear_batch: job %zu: residual must be 16-byte aligned", i);
+        if (grouped && (j.flags & ZQ_JOB_ROW_PARALLEL)) {
+            rp_floats += (j.m * j.w->rows + 3) & ~size_t(3);
+            ++rp_jobs;
+        }
     }
+    if (rp_jobs > (size_t)kDistMaxJobs) return set_error(err, ZQ_ERR_DIST, "zq_linear_batch: %zu row-parallel jobs in one call, at most %d", rp_jobs, kDistMaxJobs);
+    // the exchange slot carries 8 bytes per f32 partial (value + epoch)
+    if (rp_jobs && rp_floats * 8 > ctx->dist->slot_bytes) return set_error(err, ZQ_ERR_DIST, "zq_linear_batch: the row-parallel jobs need %zu bytes of exchange slot, it holds %zu (zq_dist_export)", rp_floats * 8, ctx->dist->slot_bytes);
     std::vector<WlHostJob> listed;
-    std::vector<size_t> alone;
+    std::vector<zq_linear_job> alone;
+    std::vector<int> alone_y_dtype;
+    std::vector<DistReduceJob> reduce;
+    size_t staged = 0;
     for (size_t i = 0; i < n_jobs; ++i) {
-        const zq_linear_job &j = jobs[i];
-        WlHostJob h = {j.w, j.w_up, j.dev_x, j.m, j.dev_y, j.dev_residual};
-        if (!ctx->disable_worklist && gemv_wl_supported(ctx, h)) listed.push_back(h);
-        else alone.push_back(i);
+        zq_linear_job j = jobs[i];
+        int jy = -1;
+        if (grouped && (j.flags & ZQ_JOB_ROW_PARALLEL)) {
+            // the partial result goes to the staging vector as f32; the reduce kernel adds the peers' partials and the residual
+            reduce.push_back({j.dev_y, j.dev_residual, j.m * j.w->rows});
+            j.dev_y = ctx->dist->staging + staged * sizeof(float);
+            j.dev_residual = nullptr;
+            staged += (j.m * j.w->rows + 3) & ~size_t(3);
+            jy = ZQ_F32;
+        }
+        WlHostJob h = {j.w, j.w_up, j.dev_x, j.m, j.dev_y, j.dev_residual, jy};
+        if (!ctx->disable_worklist && gemv_wl_supported(ctx, h)) {
+            listed.push_back(h);
+        } else {
+            alone.push_back(j);
+            alone_y_dtype.push_back(jy >= 0 ? jy : y_dtype);
+        }
     }
     int rc = launch_gemv_wl(ctx, listed.data(), listed.size(), x_dtype, y_dtype, err);
-    for (size_t k = 0; k < alone.size() && !rc; ++k) rc = run_job_alone(ctx, jobs[alone[k]], x_dtype, y_dtype, err);
+    for (size_t k = 0; k < alone.size() && !rc; ++k) rc = run_job_alone(ctx, alone[k], x_dtype, alone_y_dtype[k], err);
+    if (!rc && !reduce.empty()) rc = launch_tp_allreduce(ctx, reduce.data(), reduce.size(), y_dtype, err);
     return rc;
+}
+
+int zq_linear_row_parallel(zq_ctx *ctx, const zq_weight *w, const void *dev_x, int x_dtype, size_t m, void *dev_y, int y_dtype, const void *dev_residual, zq_error *err) {
+    zq_linear_job job = {w, nullptr, dev_x, m, dev_y, dev_residual, ZQ_JOB_ROW_PARALLEL};
+    return zq_linear_batch(ctx, &job, 1, x_dtype, y_dtype, err);
 }
 
 int zq_linear_multi(zq_ctx *ctx, const zq_weight *const *w, size_t n_weights, const void *dev_x, int x_dtype, size_t m, void *const *dev_y, int y_dtype, zq_error *err) {
@@ -424,7 +460,7 @@ int zq_linear_multi(zq_ctx *ctx, const zq_weight *const *w, size_t n_weights, co
     zq_linear_job jobs[3];
     for (size_t i = 0; i < n_weights; ++i) {
         if (!w[i] || w[i]->cols != w[0]->cols) return set_error(err, ZQ_ERR_SHAPE, "zq_linear_multi: weights must share the input width");
-        jobs[i] = {w[i], nullptr, dev_x, m, dev_y[i], nullptr};
+        jobs[i] = {w[i], nullptr, dev_x, m, dev_y[i], nullptr, 0};
     }
     return zq_linear_batch(ctx, jobs, n_weights, x_dtype, y_dtype, err);  // one launch: the input is quantised once
 }
@@ -447,7 +483,7 @@ int zq_rmsnorm_linear(zq_ctx *ctx, const zq_weight *const *w, size_t n_weights, 
     rc = launch_rmsnorm(ctx, dev_x, x_dtype, m, cols, dev_norm_weight, eps, weight_offset, reinterpret_cast<float *>(ctx->norm), err);
     if (rc) return rc;
     zq_linear_job jobs[3];
-    for (size_t i = 0; i < n_weights; ++i) jobs[i] = {w[i], nullptr, ctx->norm, m, dev_y[i], nullptr};
+    for (size_t i = 0; i < n_weights; ++i) jobs[i] = {w[i], nullptr, ctx->norm, m, dev_y[i], nullptr, 0};
     return zq_linear_batch(ctx, jobs, n_weights, ZQ_F32, y_dtype, err);
 }
 

@@ -83,7 +83,7 @@ __device__ __constant__ const int8_t kIq4nlValues[16] = {-127, -104, -83, -65, -
 // Device status word: kernels never trap or spin forever.  A bounded wait that runs out records a code here
 // and the kernel returns; zq_ctx_sync reports it.
 // ---------------------------------------------------------------------------------------------------------------
-enum DeviceStatus : uint32_t { kStatusOk = 0, kStatusTmaTimeout = 1, kStatusMmaTimeout = 2, kStatusTmemAlloc = 3, kStatusBadIndex = 4 };
+enum DeviceStatus : uint32_t { kStatusOk = 0, kStatusTmaTimeout = 1, kStatusMmaTimeout = 2, kStatusTmemAlloc = 3, kStatusBadIndex = 4, kStatusPeerTimeout = 5 };
 
 // ---------------------------------------------------------------------------------------------------------------
 // PTX wrappers.
@@ -210,8 +210,11 @@ EncodeTiledFn get_encode_tiled(zq_error *err);
 
 }  // namespace zq
 
+struct zq_dist_state;
+
 struct zq_ctx {
     int device = 0;
+    zq_dist_state *dist = nullptr;  // peer group of the node (zq_dist_export / zq_dist_init), or null
     int sm_count = 0;
     cudaStream_t own_stream = nullptr;
     cudaStream_t stream = nullptr;

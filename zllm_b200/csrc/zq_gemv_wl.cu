@@ -39,6 +39,8 @@ struct WlJob {
     int chunks;                // ring items per tile = ceil(units / 2)
     int tiles;                 // row tiles
     int q_begin;               // first ring item of the job in the launch's (job, tile, chunk) order
+    int y_dtype;               // output (and residual) dtype of this job
+    int pad;
 };
 
 struct WlArgs {
@@ -114,6 +116,9 @@ constexpr int kBarFix = 13;    // 13, 14: the 16 consumer warps hand a cut tile'
 constexpr int kBarAll = 15;    // the 16 consumer warps among themselves (9..16 activation rows: they finish cut tiles on their own)
 
 __device__ __forceinline__ void named_bar_sync(int id, int threads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory"); }
+// Release / acquire fence at GPU scope: orders this thread's (and, after a CTA barrier, its CTA's) earlier accesses before
+// its later ones; lighter than the sequentially consistent fence __threadfence() stands for.
+__device__ __forceinline__ void fence_acq_rel_gpu() { asm volatile("fence.acq_rel.gpu;" ::: "memory"); }
 __device__ __forceinline__ void named_bar_arrive(int id, int threads) { asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory"); }
 
 // CTA that owns ring item q when Q items are cut into G ranges [floor(c Q / G), floor((c + 1) Q / G)).
@@ -161,6 +166,11 @@ __global__ void __launch_bounds__(kWlThreads, 1) gemv_wl_kernel(const __grid_con
     const int q0 = (int)(bid * Q / G), q1 = (int)((bid + 1) * Q / G);
     const int n_items = q1 - q0;
 
+    // the tensor maps live in global memory: fetch them into the descriptor cache while thread 0 lays out the range
+    if (tid >= 32 && tid < 32 + a.n_jobs) {
+        tma_prefetch_desc(a.jobs[tid - 32].map_a);
+        if (GATED) tma_prefetch_desc(a.jobs[tid - 32].map_b);
+    }
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&full[s], 1);
@@ -231,7 +241,7 @@ __global__ void __launch_bounds__(kWlThreads, 1) gemv_wl_kernel(const __grid_con
             named_bar_sync(kBarFix + k, kWlConsumers + 32);  // the consumers have stored this piece's partial sums
             int last = 0, c0 = 0, cl = 0;
             if (lane == 0) {
-                __threadfence();
+                fence_acq_rel_gpu();
                 const long long ts = (long long)jb.q_begin + (long long)tile * jb.chunks;
                 c0 = wl_owner(ts, G, Q);
                 cl = wl_owner(ts + jb.chunks - 1, G, Q);
@@ -241,7 +251,7 @@ __global__ void __launch_bounds__(kWlThreads, 1) gemv_wl_kernel(const __grid_con
             c0 = __shfl_sync(0xffffffffu, c0, 0);
             cl = __shfl_sync(0xffffffffu, cl, 0);
             if (!last) continue;
-            __threadfence();
+            fence_acq_rel_gpu();
             // A slot is [activation row][128 tile rows] f32.  Lane L owns tile rows 4L..4L+3 (one float4) of every
             // activation row; up to 8 activation rows are summed at a time so that a contributor costs one round trip.
             constexpr int GB = G4 < 8 ? G4 : 8;
@@ -276,8 +286,8 @@ __global__ void __launch_bounds__(kWlThreads, 1) gemv_wl_kernel(const __grid_con
                         const int n = tile * out_rows + row;
                         if (n >= jb.n_out) continue;
                         const size_t o = (size_t)tok * jb.n_out + n;
-                        if (jb.residual) v += load_as_f32(jb.residual, a.y_dtype, o);
-                        store_from_f32(jb.y, a.y_dtype, o, v);
+                        if (jb.residual) v += load_as_f32(jb.residual, jb.y_dtype, o);
+                        store_from_f32(jb.y, jb.y_dtype, o, v);
                     }
                 }
             }
@@ -425,8 +435,8 @@ __global__ void __launch_bounds__(kWlThreads, 1) gemv_wl_kernel(const __grid_con
                 if (n >= jb.n_out || tok >= M) return;
                 if (GATED) v = (v / (1.0f + expf(-v))) * vup;
                 const size_t o = (size_t)tok * jb.n_out + n;
-                if (jb.residual) v += load_as_f32(jb.residual, a.y_dtype, o);
-                store_from_f32(jb.y, a.y_dtype, o, v);
+                if (jb.residual) v += load_as_f32(jb.residual, jb.y_dtype, o);
+                store_from_f32(jb.y, jb.y_dtype, o, v);
             };
             if (whole) {
                 if (owner) {
@@ -655,6 +665,8 @@ int launch_gemv_wl(zq_ctx *ctx, const WlHostJob *jobs, size_t n_jobs, int x_dtyp
             d.chunks = (int)chunks;
             d.tiles = (int)tiles;
             d.q_begin = wa.q_total;
+            d.y_dtype = j.y_dtype >= 0 ? j.y_dtype : y_dtype;
+            d.pad = 0;
             wa.q_total += (int)(tiles * chunks);
             if ((int)chunks < min_chunks) min_chunks = (int)chunks;
         }

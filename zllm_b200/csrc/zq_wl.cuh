@@ -15,6 +15,7 @@ struct WlHostJob {
     size_t m;               // 1..16
     void *y;                // [m, rows]
     const void *residual;   // [m, rows] in the output dtype, or null
+    int y_dtype;            // output dtype of this job, or -1 for the call's
 };
 
 // True when the job can ride in a work-list launch (Q4_K / Q4_0 / Q8_0, up to 16 activation rows).

@@ -13,6 +13,8 @@ LIB_PATH = os.path.join(_HERE, "lib", "libzq_b200.so")
 
 Q4_0, Q8_0, Q4_K, Q5_K, Q6_K, IQ4_NL = 2, 8, 12, 13, 14, 20
 F32, F16, BF16 = 0, 1, 2
+JOB_ROW_PARALLEL = 1
+DIST_HANDLE_BYTES = 80
 BLOCK = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210), IQ4_NL: (32, 18)}
 
 
@@ -33,7 +35,7 @@ _vp, _sz, _u32, _i, _f = C.c_void_p, C.c_size_t, C.c_uint32, C.c_int, C.c_float
 class ZqLinearJob(C.Structure):
     """``zq_linear_job``: one projection of a ``zq_linear_batch`` call."""
 
-    _fields_ = [("w", C.c_void_p), ("w_up", C.c_void_p), ("dev_x", C.c_void_p), ("m", C.c_size_t), ("dev_y", C.c_void_p), ("dev_residual", C.c_void_p)]
+    _fields_ = [("w", C.c_void_p), ("w_up", C.c_void_p), ("dev_x", C.c_void_p), ("m", C.c_size_t), ("dev_y", C.c_void_p), ("dev_residual", C.c_void_p), ("flags", C.c_uint32)]
 
 
 _err = C.POINTER(ZqError)
@@ -59,6 +61,13 @@ PROTOTYPES = {
     "zq_quantize": (_i, [_vp, _u32, _vp, _sz, _sz, _vp, _sz, _err]),
     "zq_linear": (_i, [_vp, _vp, _vp, _i, _sz, _vp, _i, _vp, _err]),
     "zq_linear_batch": (_i, [_vp, C.POINTER(ZqLinearJob), _sz, _i, _i, _err]),
+    "zq_linear_row_parallel": (_i, [_vp, _vp, _vp, _i, _sz, _vp, _i, _vp, _err]),
+    "zq_dist_export": (_i, [_vp, _sz, _vp, _err]),
+    "zq_dist_init": (_i, [_vp, _i, _i, _vp, _err]),
+    "zq_dist_set_wait_ms": (_i, [_vp, C.c_uint, _err]),
+    "zq_dist_rank": (_i, [_vp]),
+    "zq_dist_world": (_i, [_vp]),
+    "zq_dist_shutdown": (None, [_vp]),
     "zq_linear_multi": (_i, [_vp, C.POINTER(_vp), _sz, _vp, _i, _sz, C.POINTER(_vp), _i, _err]),
     "zq_rmsnorm_linear": (_i, [_vp, C.POINTER(_vp), _sz, _vp, _i, _sz, _vp, C.c_float, C.c_float, C.POINTER(_vp), _i, _err]),
     "zq_gated_silu": (_i, [_vp, _vp, _vp, _vp, _i, _sz, _vp, _i, _err]),
