@@ -383,8 +383,9 @@ def run_ours(args):
 
     parity = None
     if world > 1 and not args.nccl_reduce:
-        parity = {"tp_row_split_max_rel_error": tp_parity(ctx, device, world, rank), "bound": 2e-3,
-                  "what": "Q4_K 1024x4096, 4 rows: K-split over the ranks + peer-store reduce, against the same weight as one matrix on one GPU"}
+        parity = {"tp_row_split_max_rel_error": tp_parity(ctx, device, world, rank), "ep_moe_max_rel_error": ep_parity(device, world, rank, local_rank), "bound": 2e-3,
+                  "what": "TP: Q4_K 1024x4096, 4 rows, K-split over the ranks + peer-store reduce; "
+                          "EP: 16 experts over the ranks, 64 tokens; both against float64 references on the bit-exact dequantised weights"}
     # free the sweep's weights before the larger side measurements
     extras = {}
     if not args.no_extras:
@@ -423,8 +424,8 @@ def run_ours(args):
 def tp_parity(ctx, device, world, rank):
     """Correctness of the multi-GPU path on the hardware it runs on, outside any timed region: one K-split matrix
     (Q4_K, 1024 x 4096, 4 rows; every rank quantises its 256-aligned column slice, the blocks being independent the
-    slices concatenate to the full quantised weight) through the row-parallel entry, against the SAME weight as one
-    matrix on this GPU.  Returns max_i |a_i - e_i| / max(|e_i|, rms(e)), the largest over the ranks."""
+    slices concatenate to the full quantised weight) through the row-parallel entry, against a float64 product with
+    the library's (bit-exact) dequantisation of the SAME weight as one matrix.  Returns max_i |a_i - e_i| / max(|e_i|, rms(e)), the largest over the ranks."""
     import torch
     import torch.distributed as dist
 
@@ -443,7 +444,7 @@ def tp_parity(ctx, device, world, rank):
     w_local = ctx.prepare_weight(Q4_K, ctx.quantize(Q4_K, full[:, c0:c1].contiguous()), n, c1 - c0)
     w_full = ctx.prepare_weight(Q4_K, ctx.quantize(Q4_K, full), n, k)
     got = ctx.linear_row_parallel(x[:, c0:c1].contiguous(), w_local)
-    want = ctx.linear(x, w_full)
+    want = x.double() @ ctx.dequantize(w_full).double().T  # float64 product with the exact dequantised values
     ctx.sync()
     rms = want.double().pow(2).mean().sqrt()
     err = ((got.double() - want.double()).abs() / torch.maximum(want.double().abs(), rms)).max()
@@ -451,6 +452,67 @@ def tp_parity(ctx, device, world, rank):
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     w_local.release()
     w_full.release()
+    return float(t[0])
+
+
+def ep_parity(device, world, rank, local_rank):
+    """Correctness of the expert-parallel MoE forward on the hardware it runs on, outside any timed region: 16 experts
+    (Q4_K, hidden 512, FFN 256, top-4, one shared expert) over the ranks, 64 tokens data-parallel, against the same
+    layer in float64 on the library's (bit-exact) dequantised weights, for this rank's tokens.  Largest error over the
+    ranks."""
+    import torch
+    import torch.distributed as dist
+
+    from zllm_b200.backend import B200Context, MoeExperts, moe_forward, moe_forward_ep, moe_route
+    from zllm_b200.dist import expert_range
+
+    E, K, H, I, M = 16, 4, 512, 256, 64
+    c = B200Context(local_rank)
+    c.dist_init(slot_bytes=1 << 20)
+    c.moe_ep_init(M // world, H, K, E, dtype=torch.bfloat16)
+    gen = torch.Generator(device=device)
+
+    def make(rows, cols, seed):
+        gen.manual_seed(seed)
+        full = torch.randn((rows, cols), generator=gen, device=device, dtype=torch.float32) * 0.03
+        return c.prepare_weight(Q4_K, c.quantize(Q4_K, full), rows, cols)
+
+    gates = [make(I, H, 100 + 3 * e) for e in range(E + 1)]
+    ups = [make(I, H, 101 + 3 * e) for e in range(E + 1)]
+    downs = [make(H, I, 102 + 3 * e) for e in range(E + 1)]
+    lo, hi = expert_range(E, world, rank)
+    local_table = MoeExperts(c, gates[lo:hi], ups[lo:hi], downs[lo:hi])
+    shared = (gates[E], ups[E], downs[E])
+    gen.manual_seed(55)
+    x_all = torch.randn((M, H), generator=gen, device=device, dtype=torch.float32).to(torch.bfloat16)
+    router = torch.randn((E, H), generator=gen, device=device, dtype=torch.float32) / (H ** 0.5)
+    per = M // world
+    x = x_all[rank * per:(rank + 1) * per].contiguous()
+    ids, w = moe_route(c, x, router, K, 1.0, True)
+    got = moe_forward_ep(c, local_table, x, ids, w, shared=shared, out_dtype=torch.float32)
+    c.sync()
+    # float64 reference from the library's (bit-exact) dequantised values
+    dq = lambda lst: [c.dequantize(wgt).double() for wgt in lst]
+    Wg, Wu, Wd = dq(gates), dq(ups), dq(downs)
+    xd = x.double()
+
+    def expert(e, rows):
+        g, u = rows @ Wg[e].T, rows @ Wu[e].T
+        return (g / (1.0 + torch.exp(-g)) * u) @ Wd[e].T
+
+    want = expert(E, xd)
+    for t in range(per):
+        for j in range(K):
+            want[t] += float(w[t, j]) * expert(int(ids[t, j]), xd[t:t + 1])[0]
+    rms = want.double().pow(2).mean().sqrt()
+    err = ((got.double() - want.double()).abs() / torch.maximum(want.double().abs(), rms)).max()
+    t = torch.tensor([float(err)], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dist.barrier()
+    del local_table
+    for wgt in gates + ups + downs:
+        wgt.release()
+    c.close()
     return float(t[0])
 
 
@@ -563,7 +625,7 @@ def bench_moe(ctx, device, args, world, rank, only=None):
     import torch
     import torch.distributed as dist
 
-    from zllm_b200.backend import MoeExperts, moe_forward, moe_route
+    from zllm_b200.backend import MoeExperts, moe_forward, moe_forward_ep, moe_route
     from zllm_b200.dist import expert_parallel_forward, expert_range
 
     E, K, H, I = 256, 8, 7168, 2048
@@ -585,7 +647,10 @@ def bench_moe(ctx, device, args, world, rank, only=None):
     gen.manual_seed(8100)
     router = torch.randn((E, H), generator=gen, device=device, dtype=torch.float32) / (H ** 0.5)
     expert_bytes = 3 * int(I * H * BPW)
-    out = {"experts": E, "top_k": K, "hidden": H, "intermediate": I, "weights": "Q4_K", "parallelism": f"ep{world}" if world > 1 else "single", "router": "softmax top-k, renormalised over the selected experts"}
+    native_ep = world > 1 and not args.nccl_reduce
+    if native_ep:
+        ctx.moe_ep_init(8192 // world, H, K, E, dtype=torch.bfloat16)  # exchange buffers for the larger of the two batches
+    out = {"experts": E, "top_k": K, "hidden": H, "intermediate": I, "weights": "Q4_K", "parallelism": f"ep{world}" if world > 1 else "single", "exchange": ("peer-memory stores (zq_moe_forward_ep)" if native_ep else "NCCL all-to-all from the host") if world > 1 else None, "router": "softmax top-k, renormalised over the selected experts"}
     for name, m_total in (("decode_m64", 64), ("prefill_m8192", 8192)):
         if only and only != name:
             continue
@@ -602,6 +667,8 @@ def bench_moe(ctx, device, args, world, rank, only=None):
             ids, w = moe_route(ctx, x, router, K, 1.0, True)
             if world == 1:
                 return moe_forward(ctx, table, x, ids, w, shared=shared, out_dtype=torch.bfloat16), ids
+            if native_ep:  # dispatch, experts and combine inside the library, over peer memory
+                return moe_forward_ep(ctx, table, x, ids, w, shared=shared, out_dtype=torch.bfloat16), ids
             routed = expert_parallel_forward(x, ids, w, E, run_local)
             sh = ctx.gated_mlp(x, *shared, out_dtype=torch.float32)
             return (routed + sh).to(torch.bfloat16), ids

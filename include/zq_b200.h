@@ -183,7 +183,27 @@ void zq_moe_experts_destroy(zq_moe_experts *experts);
  * decode_routed_experts (src/backend/mod.rs:1921-1960, 2012-2024).
  * y[m, hidden] = residual + shared(x) + sum_k w_k * expert_k(x), contributions added in ascending expert id per
  * token (src/backend/cpu/moe.rs:107-141).  shared_* may be NULL. */
+#define ZQ_MOE_NO_ROUTE 0xFFFFFFFFu /* an expert id that means "no route in this place": no expert runs, nothing is added */
 int zq_moe_forward(zq_ctx *ctx, const zq_moe_experts *experts, const zq_weight *shared_gate, const zq_weight *shared_up, const zq_weight *shared_down, const void *dev_x, int x_dtype, size_t m, const uint32_t *dev_ids, const float *dev_weights, size_t top_k, void *dev_y, int y_dtype, const void *dev_residual, zq_error *err);
+
+/* ---- expert parallelism over the GPUs of one node.  The reference keeps every expert on (or cached by) one device
+ * (src/backend/cuda/expert.rs:284-570) and has no counterpart; the arithmetic of an expert and the ascending-expert order
+ * of a token's sum are its own (src/kernel/cpu/moe.rs:122-138, src/backend/cpu/moe.rs:107-141).  Rank r of the peer group
+ * owns the contiguous block of experts [r E / W, (r + 1) E / W) (the first E % W ranks hold one more) and passes a table of
+ * exactly those; tokens stay with the rank that brings them, with GLOBAL expert ids.  Each token travels once per owner
+ * rank it routes to (not once per route), its routes on that rank are weighted and summed there, one f32 row per (token,
+ * rank) comes back, and the token's rank adds shared expert, residual and the returned rows in ascending rank order.
+ * Transport: plain stores into peer memory mapped with CUDA IPC, {count, epoch} flags, bounded waits that set the
+ * status word and go on (zq_ctx_sync reports them).  Needs zq_dist_init first; every rank makes the same calls.
+ *   zq_moe_ep_export   allocates the exchange buffers for up to `max_tokens_per_rank` tokens per rank and call, writes
+ *                      ZQ_DIST_HANDLE_BYTES bytes for the other ranks;  zq_moe_ep_init maps the peers' buffers. */
+int zq_moe_ep_export(zq_ctx *ctx, size_t max_tokens_per_rank, size_t hidden, size_t top_k, size_t num_experts_total, int x_dtype, void *out_handle, zq_error *err);
+int zq_moe_ep_init(zq_ctx *ctx, const void *all_handles, zq_error *err);
+void zq_moe_ep_shutdown(zq_ctx *ctx);
+/* `m` = this rank's tokens; `m_cap` = the largest m of any rank in this call (the same value on every rank, at most the
+ * allocated bound; 0 = every rank passes the same m). */
+int zq_moe_forward_ep(zq_ctx *ctx, const zq_moe_experts *local_experts, const zq_weight *shared_gate, const zq_weight *shared_up, const zq_weight *shared_down, const void *dev_x, int x_dtype, size_t m, size_t m_cap,
+                      const uint32_t *dev_ids, const float *dev_weights, size_t top_k, void *dev_y, int y_dtype, const void *dev_residual, zq_error *err);
 
 #ifdef __cplusplus
 }

@@ -80,6 +80,77 @@ def test_missing_peer_runs_into_the_wait_limit_and_the_context_survives():
     c.close()
 
 
+EP = dict(experts=16, top_k=4, hidden=512, inter=256)
+
+
+def _ep_inputs(m_total):
+    """Experts, router outputs and tokens of the expert-parallel cases, the same on every rank (seeded)."""
+    E, K, Hd, I = EP["experts"], EP["top_k"], EP["hidden"], EP["inter"]
+    gates = [H.random_weight(H.Q4_K, I, Hd, seed=900 + 3 * e) for e in range(E + 1)]
+    ups = [H.random_weight(H.Q4_K, I, Hd, seed=901 + 3 * e) for e in range(E + 1)]
+    downs = [H.random_weight(H.Q4_K, Hd, I, seed=902 + 3 * e, std=0.05) for e in range(E + 1)]
+    rng = np.random.default_rng(m_total)
+    x = rng.standard_normal((m_total, Hd)).astype(np.float32)
+    ids = np.stack([rng.permutation(E)[:K] for _ in range(m_total)]).astype(np.uint32)
+    w = rng.random((m_total, K)).astype(np.float32)
+    w /= w.sum(axis=1, keepdims=True)
+    res = rng.standard_normal((m_total, Hd)).astype(np.float32)
+    return gates, ups, downs, x, ids, w, res
+
+
+def _ep_run(c, rank, world, m_total):
+    """This rank's share of an expert-parallel forward; returns its output rows."""
+    from zllm_b200.backend import MoeExperts, moe_forward_ep
+
+    E, K, Hd, I = EP["experts"], EP["top_k"], EP["hidden"], EP["inter"]
+    gates, ups, downs, x, ids, w, res = _ep_inputs(m_total)
+    base, extra = divmod(E, world)
+    lo = rank * base + min(rank, extra)
+    hi = lo + base + (1 if rank < extra else 0)
+    table = MoeExperts(c, [c.prepare_weight(H.Q4_K, gates[e], I, Hd) for e in range(lo, hi)], [c.prepare_weight(H.Q4_K, ups[e], I, Hd) for e in range(lo, hi)],
+                       [c.prepare_weight(H.Q4_K, downs[e], Hd, I) for e in range(lo, hi)])
+    shared = (c.prepare_weight(H.Q4_K, gates[E], I, Hd), c.prepare_weight(H.Q4_K, ups[E], I, Hd), c.prepare_weight(H.Q4_K, downs[E], Hd, I))
+    per = m_total // world
+    t0, t1 = rank * per, (rank + 1) * per
+    xs = torch.from_numpy(x[t0:t1]).cuda().to(torch.bfloat16)
+    out = []
+    for _ in range(2):  # twice: the buffers are reused call after call
+        y = moe_forward_ep(c, table, xs, torch.from_numpy(ids[t0:t1].astype(np.int32)).cuda(), torch.from_numpy(w[t0:t1]).cuda(), shared=shared,
+                           residual=torch.from_numpy(res[t0:t1]).cuda(), out_dtype=torch.float32)
+        c.sync()
+        out.append(y.cpu().numpy())
+    assert np.array_equal(out[0].view(np.uint32), out[1].view(np.uint32)), "a repeated call differs"
+    return out[0]
+
+
+def _ep_oracle(m_total):
+    from oracle import oracle as orc
+
+    E, K, Hd, I = EP["experts"], EP["top_k"], EP["hidden"], EP["inter"]
+    gates, ups, downs, x, ids, w, res = _ep_inputs(m_total)
+    x16 = torch.from_numpy(x).to(torch.bfloat16).float().numpy()  # what the device consumes
+    sh = ((H.Q4_K, gates[E], I, Hd), (H.Q4_K, ups[E], I, Hd), (H.Q4_K, downs[E], Hd, I))
+    return orc.moe_forward([(H.Q4_K, g, I, Hd) for g in gates[:E]], [(H.Q4_K, u, I, Hd) for u in ups[:E]], [(H.Q4_K, d, Hd, I) for d in downs[:E]], x16, ids, w, shared=sh, residual=res)
+
+
+def test_expert_parallel_group_of_one_matches_the_oracle():
+    """One rank owns every expert: rows are 'sent' to the rank itself through the same buffers and kernels."""
+    from zllm_b200 import ffi
+    from zllm_b200.backend import B200Context
+
+    c = B200Context(0)
+    blob = (C.c_uint8 * ffi.DIST_HANDLE_BYTES)()
+    ffi.call("zq_dist_export", c.handle, 1 << 20, blob)
+    ffi.call("zq_dist_init", c.handle, 0, 1, blob)
+    eb = (C.c_uint8 * ffi.DIST_HANDLE_BYTES)()
+    ffi.call("zq_moe_ep_export", c.handle, 320, EP["hidden"], EP["top_k"], EP["experts"], ffi.BF16, eb)
+    ffi.call("zq_moe_ep_init", c.handle, eb)
+    for m_total, bound in ((8, BOUND), (320, 2 * BOUND)):  # device-grouped decode path / host-grouped tensor-core path
+        got = _ep_run(c, 0, 1, m_total)
+        assert H.max_rel_error(got, _ep_oracle(m_total)) <= bound
+    c.close()
+
+
 def _rank_main(rank, world, port, out_dir):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world), NCCL_NVLS_ENABLE="0")
     import torch.distributed as dist
@@ -132,6 +203,10 @@ def _rank_main(rank, world, port, out_dir):
     results["graph_col"] = ys[0].cpu().numpy()
     results["graph_row"] = ys[1].cpu().numpy()
     results["graph_row2"] = ys[2].cpu().numpy()
+    # expert parallelism: 16 experts over the ranks, a decode-sized and a prefill-sized batch
+    c.moe_ep_init(40 * 8 // world, EP["hidden"], EP["top_k"], EP["experts"], dtype=torch.bfloat16)
+    for m_total in (8, 320):
+        results[f"ep{m_total}"] = _ep_run(c, rank, world, m_total)
     np.savez(os.path.join(out_dir, f"rank{rank}.npz"), **results)
     dist.barrier()
     w_row.release()
@@ -175,6 +250,9 @@ def test_row_parallel_on_all_gpus_matches_the_oracle_on_the_full_weight(tmp_path
             assert H.max_rel_error(got, want) <= (3e-4 if m <= 16 else BOUND), (ci, r)
             assert np.array_equal(got.view(np.uint32), outs[0][f"case{ci}"].view(np.uint32)), "ranks disagree"
             assert np.array_equal(got.view(np.uint32), outs[r][f"case{ci}_again"].view(np.uint32)), "a repeated call differs"
+    for m_total, bound in ((8, BOUND), (320, 2 * BOUND)):
+        got = np.concatenate([outs[r][f"ep{m_total}"] for r in range(world)])
+        assert H.max_rel_error(got, _ep_oracle(m_total)) <= bound, f"expert-parallel forward, {m_total} tokens"
     rows, cols, m = 512, 2048, 2
     full = (np.random.default_rng(7).standard_normal((rows, cols)) * 0.02).astype(np.float32)
     x = np.random.default_rng(8).standard_normal((m, cols)).astype(np.float32)

@@ -216,12 +216,23 @@ class B200Context:
         world, rank = dist.get_world_size(group), dist.get_rank(group)
         blob = (C.c_uint8 * ffi.DIST_HANDLE_BYTES)()
         ffi.call("zq_dist_export", self.handle, int(slot_bytes), blob)
+        ffi.call("zq_dist_init", self.handle, rank, world, self._exchange_blobs(blob, group))
+
+    def _exchange_blobs(self, blob, group=None):
+        import torch.distributed as dist
+
+        world = dist.get_world_size(group)
         mine = torch.tensor(list(blob), dtype=torch.uint8, device=self.device if dist.get_backend(group) == "nccl" else "cpu")
         gathered = [torch.empty_like(mine) for _ in range(world)]
         dist.all_gather(gathered, mine, group=group)
         flat = bytes(torch.cat(gathered).cpu().tolist())
-        buf = (C.c_uint8 * len(flat)).from_buffer_copy(flat)
-        ffi.call("zq_dist_init", self.handle, rank, world, buf)
+        return (C.c_uint8 * len(flat)).from_buffer_copy(flat)
+
+    def moe_ep_init(self, max_tokens_per_rank: int, hidden: int, top_k: int, num_experts_total: int, dtype=torch.bfloat16, group=None):
+        """Expert-parallel exchange buffers of this rank (after ``dist_init``): allocate, exchange handles, map the peers."""
+        blob = (C.c_uint8 * ffi.DIST_HANDLE_BYTES)()
+        ffi.call("zq_moe_ep_export", self.handle, int(max_tokens_per_rank), int(hidden), int(top_k), int(num_experts_total), _DTYPES[dtype], blob)
+        ffi.call("zq_moe_ep_init", self.handle, self._exchange_blobs(blob, group))
 
     def linear_multi(self, x: torch.Tensor, weights: Sequence[Weight], out_dtype=None):
         x = x.contiguous()
@@ -335,6 +346,25 @@ def moe_route(ctx: B200Context, x: torch.Tensor, router: torch.Tensor, top_k: in
     w = torch.empty((m, top_k), dtype=torch.float32, device=x.device)
     ffi.call("zq_moe_route_softmax_topk", ctx.handle, _ptr(x), _dt(x), m, hidden, _ptr(router), _ptr(bias), experts, top_k, float(scaling_factor), int(normalize_selected), _ptr(ids), _ptr(w))
     return ids, w
+
+
+def moe_forward_ep(ctx: B200Context, local_experts: MoeExperts, x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, shared=None, residual: Optional[torch.Tensor] = None, out_dtype=None,
+                   max_tokens_any_rank: int = 0) -> torch.Tensor:
+    """Expert-parallel routed experts (``zq_moe_forward_ep``): ``local_experts`` are this rank's block of the experts,
+    ``ids`` are global expert ids of this rank's own tokens; ``max_tokens_any_rank`` is the largest token count of any
+    rank in this call (0: all ranks bring as many tokens as this one)."""
+    x = x.contiguous()
+    m, hidden = x.shape
+    out_dtype = out_dtype or x.dtype
+    y = torch.empty((m, hidden), dtype=out_dtype, device=x.device)
+    ids = ids.contiguous()
+    weights = weights.contiguous().float()
+    top_k = ids.numel() // m
+    sg, su, sd = (w.handle for w in shared) if shared is not None else (None, None, None)
+    if residual is not None:
+        residual = residual.contiguous()
+    ffi.call("zq_moe_forward_ep", ctx.handle, local_experts.handle, sg, su, sd, _ptr(x), _dt(x), m, int(max_tokens_any_rank), _ptr(ids), _ptr(weights), top_k, _ptr(y), _DTYPES[out_dtype], _ptr(residual))
+    return y
 
 
 def moe_forward(ctx: B200Context, experts: MoeExperts, x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, shared=None, residual: Optional[torch.Tensor] = None, out_dtype=None) -> torch.Tensor:

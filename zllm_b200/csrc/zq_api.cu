@@ -187,6 +187,7 @@ int zq_ctx_create(int device, zq_ctx **out, zq_error *err) {
 
 void zq_ctx_destroy(zq_ctx *ctx) {
     if (!ctx) return;
+    zq_moe_ep_shutdown(ctx);
     zq_dist_shutdown(ctx);
     cudaSetDevice(ctx->device);
     if (ctx->own_stream || ctx->stream) cudaStreamSynchronize(ctx->stream);
@@ -499,8 +500,10 @@ int zq_gated_silu(zq_ctx *ctx, const zq_weight *gate, const zq_weight *up, const
 int zq_gated_mlp(zq_ctx *ctx, const zq_weight *gate, const zq_weight *up, const zq_weight *down, const void *dev_x, int x_dtype, size_t m, void *dev_y, int y_dtype, const void *dev_residual, zq_error *err) {
     if (!ctx || !down || !gate || !up) return set_error(err, ZQ_ERR_ARG, "gated mlp: null context or weight");
     if (down->cols != gate->rows) return set_error(err, ZQ_ERR_SHAPE, "gated mlp: down expects %zu inputs, gate produces %zu", down->cols, gate->rows);
-    // the activated intermediate [m, I] lives in the context workspace as f32 (decode) or in the input dtype (prefill)
-    int mid_dtype = m <= 16 ? ZQ_F32 : (x_dtype == ZQ_F32 ? ZQ_F32 : x_dtype);
+    // the activated intermediate [m, I] lives in the context workspace: f32 for the decode kernels; f16 for the tensor-core
+    // GEMM, whose operands are f16 anyway (a bf16 or f32 intermediate would be rounded to f16 by the next GEMM's operand
+    // pass, a bf16 one after losing three more bits first)
+    int mid_dtype = m <= 16 ? ZQ_F32 : ZQ_F16;
     size_t mid_bytes = m * gate->rows * dtype_size(mid_dtype);
     int rc = ensure_scratch_mid(ctx, mid_bytes, err);
     if (rc) return rc;

@@ -211,10 +211,12 @@ EncodeTiledFn get_encode_tiled(zq_error *err);
 }  // namespace zq
 
 struct zq_dist_state;
+struct zq_ep_state;
 
 struct zq_ctx {
     int device = 0;
     zq_dist_state *dist = nullptr;  // peer group of the node (zq_dist_export / zq_dist_init), or null
+    zq_ep_state *ep = nullptr;      // expert-parallel exchange buffers (zq_moe_ep_export / zq_moe_ep_init), or null
     int sm_count = 0;
     cudaStream_t own_stream = nullptr;
     cudaStream_t stream = nullptr;

@@ -202,7 +202,11 @@ __global__ void combine_kernel(const float *__restrict__ routed, const uint32_t 
         size_t t = i / hidden;
         int c = (int)(i - t * hidden);
         float acc = 0.f;
-        for (int j = 0; j < top_k; ++j) acc = __fadd_rn(acc, __fmul_rn(routed[(size_t)slots[t * top_k + j] * hidden + c], w[t * top_k + j]));
+        for (int j = 0; j < top_k; ++j) {
+            const float wj = w[t * top_k + j];
+            if (wj == 0.f) continue;  // an absent route (ZQ_MOE_NO_ROUTE) has no slot: nothing is read for it
+            acc = __fadd_rn(acc, __fmul_rn(routed[(size_t)slots[t * top_k + j] * hidden + c], wj));
+        }
         if (shared) acc = __fadd_rn(acc, shared[i]);
         if (residual) acc = __fadd_rn(acc, load_as_f32(residual, y_dtype, i));
         store_from_f32(y, y_dtype, i, acc);
@@ -423,6 +427,7 @@ int zq_moe_forward(zq_ctx *ctx, const zq_moe_experts *experts, const zq_weight *
     ZQ_CUDA_CHECK(cudaStreamSynchronize(ctx->stream), err);
     std::vector<uint32_t> offsets(E + 1, 0);
     for (size_t r = 0; r < routes; ++r) {
+        if (ids[r] == ZQ_MOE_NO_ROUTE) continue;  // an absent route: no expert runs for it, its weight counts as 0
         if (ids[r] >= E) return set_error(err, ZQ_ERR_SHAPE, "router returned expert %u, table holds %zu", ids[r], E);
         offsets[ids[r] + 1]++;
     }
@@ -436,6 +441,12 @@ int zq_moe_forward(zq_ctx *ctx, const zq_moe_experts *experts, const zq_weight *
     for (size_t t = 0; t < m; ++t) {
         for (size_t j = 0; j < top_k; ++j) {
             uint32_t e = ids[t * top_k + j];
+            if (e == ZQ_MOE_NO_ROUTE) {  // sorts behind every real expert; slot 0 is never read for a zero weight
+                order[j] = {e, (uint32_t)j};
+                token_slots[t * top_k + j] = 0;
+                wts[t * top_k + j] = 0.f;
+                continue;
+            }
             uint32_t slot = cursor[e]++;
             slot_token[slot] = (uint32_t)t;
             order[j] = {e, (uint32_t)j};

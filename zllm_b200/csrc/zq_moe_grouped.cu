@@ -48,6 +48,11 @@ __global__ void __launch_bounds__(kPlanThreads) moe_plan_kernel(const uint32_t *
     __syncthreads();
     for (int r = threadIdx.x; r < routes; r += kPlanThreads) {
         uint32_t id = ids[r];
+        if (id == ZQ_MOE_NO_ROUTE) {  // an absent route: no slot, no expert work, weight 0 in the combine
+            s_ids[r] = (uint32_t)E;
+            s_slot[r] = 0;
+            continue;
+        }
         if (id >= (uint32_t)E) {  // never index out of the table: record it and park the route on the last expert
             atomicMax(status, (uint32_t)kStatusBadIndex);
             id = (uint32_t)E - 1;
@@ -97,7 +102,7 @@ __global__ void __launch_bounds__(kPlanThreads) moe_plan_kernel(const uint32_t *
             uint32_t np = base_p + sp;
             for (uint32_t m0 = 0; m0 < (uint32_t)shared_rows; m0 += kPassRows) {
                 const uint32_t mc = (uint32_t)shared_rows - m0 < (uint32_t)kPassRows ? (uint32_t)shared_rows - m0 : (uint32_t)kPassRows;
-                passes[np++] = make_uint4((uint32_t)E, m0 | (mc << 16), base_c + sc, (uint32_t)shared_rows);
+                passes[np++] = make_uint4((uint32_t)E, m0 | (mc << 16), (uint32_t)routes, (uint32_t)shared_rows);  // behind ALL route places, absent ones included
             }
             *n_pass = np;
         }
@@ -122,7 +127,7 @@ __global__ void __launch_bounds__(kPlanThreads) moe_plan_kernel(const uint32_t *
         float kw[64];
         for (int j = 0; j < top_k; ++j) {
             const uint32_t e = s_ids[t * top_k + j], s = s_slot[t * top_k + j];
-            const float w = wts[t * top_k + j];
+            const float w = e == (uint32_t)E ? 0.f : wts[t * top_k + j];
             int i = j;
             while (i > 0 && ke[i - 1] > e) {
                 ke[i] = ke[i - 1]; ks[i] = ks[i - 1]; kw[i] = kw[i - 1];
@@ -142,7 +147,7 @@ __global__ void __launch_bounds__(kPlanThreads) moe_plan_kernel(const uint32_t *
 // row_of_slot: source row per routed slot (token of the slot), or null when the source is already in slot order.
 template <uint32_t TYPE>
 __global__ void __launch_bounds__(256) moe_quantize_kernel(const void *__restrict__ src, int src_dtype, const uint32_t *__restrict__ row_of_slot, const uint32_t *__restrict__ slot_expert,
-                                                           const uint32_t *__restrict__ offsets, int routes, int shared_rows, int shared_id, int cols, int units, uint8_t *__restrict__ out) {
+                                                           const uint32_t *__restrict__ offsets, int routes, int shared_rows, int shared_id, int num_experts, int cols, int units, uint8_t *__restrict__ out) {
     pdl_launch_dependents();
     pdl_wait_prior_grid();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -152,6 +157,7 @@ __global__ void __launch_bounds__(256) moe_quantize_kernel(const void *__restric
     uint32_t first, cnt;
     size_t row;
     if (slot < routes) {
+        if ((uint32_t)slot >= offsets[num_experts]) return;  // absent routes take no slot: nothing lives behind the last expert's rows
         const uint32_t e = slot_expert[slot];
         first = offsets[e];
         cnt = offsets[e + 1] - first;
@@ -353,8 +359,8 @@ __global__ void __launch_bounds__(kI8Threads, 1) moe_grouped_kernel(const __grid
 }
 
 template <uint32_t TYPE>
-static int launch_quantize(zq_ctx *ctx, const void *src, int src_dtype, const uint32_t *row_of_slot, const uint32_t *slot_expert, const uint32_t *offsets, size_t routes, size_t shared_rows, int shared_id, size_t cols, size_t units,
-                           uint8_t *out, zq_error *err) {
+static int launch_quantize(zq_ctx *ctx, const void *src, int src_dtype, const uint32_t *row_of_slot, const uint32_t *slot_expert, const uint32_t *offsets, size_t routes, size_t shared_rows, int shared_id, int num_experts,
+                           size_t cols, size_t units, uint8_t *out, zq_error *err) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(((routes + shared_rows) * units + 7) / 8));
     cfg.blockDim = dim3(256);
@@ -364,7 +370,7 @@ static int launch_quantize(zq_ctx *ctx, const void *src, int src_dtype, const ui
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = ctx->disable_pdl ? 0 : 1;
-    ZQ_CUDA_CHECK(cudaLaunchKernelEx(&cfg, moe_quantize_kernel<TYPE>, src, src_dtype, row_of_slot, slot_expert, offsets, (int)routes, (int)shared_rows, shared_id, (int)cols, (int)units, out), err);
+    ZQ_CUDA_CHECK(cudaLaunchKernelEx(&cfg, moe_quantize_kernel<TYPE>, src, src_dtype, row_of_slot, slot_expert, offsets, (int)routes, (int)shared_rows, shared_id, num_experts, (int)cols, (int)units, out), err);
     ZQ_CUDA_CHECK(cudaGetLastError(), err);
     ctx->launches++;
     return ZQ_OK;
@@ -463,9 +469,9 @@ int moe_grouped_forward(zq_ctx *ctx, const zq_moe_experts *t, const zq_weight *s
     int rc;
     // ---- gate/up + SiLU
     switch (t->gate_type) {
-    case ZQ_Q4_K: rc = launch_quantize<ZQ_Q4_K>(ctx, dev_x, x_dtype, d_slot_token, d_slot_expert, d_offsets, routes, srows, shared_id, H, units_h, d_xq1, err); break;
-    case ZQ_Q4_0: rc = launch_quantize<ZQ_Q4_0>(ctx, dev_x, x_dtype, d_slot_token, d_slot_expert, d_offsets, routes, srows, shared_id, H, units_h, d_xq1, err); break;
-    default: rc = launch_quantize<ZQ_Q8_0>(ctx, dev_x, x_dtype, d_slot_token, d_slot_expert, d_offsets, routes, srows, shared_id, H, units_h, d_xq1, err); break;
+    case ZQ_Q4_K: rc = launch_quantize<ZQ_Q4_K>(ctx, dev_x, x_dtype, d_slot_token, d_slot_expert, d_offsets, routes, srows, shared_id, (int)E, H, units_h, d_xq1, err); break;
+    case ZQ_Q4_0: rc = launch_quantize<ZQ_Q4_0>(ctx, dev_x, x_dtype, d_slot_token, d_slot_expert, d_offsets, routes, srows, shared_id, (int)E, H, units_h, d_xq1, err); break;
+    default: rc = launch_quantize<ZQ_Q8_0>(ctx, dev_x, x_dtype, d_slot_token, d_slot_expert, d_offsets, routes, srows, shared_id, (int)E, H, units_h, d_xq1, err); break;
     }
     if (rc) return rc;
     GroupedArgs ga;
@@ -497,9 +503,9 @@ int moe_grouped_forward(zq_ctx *ctx, const zq_moe_experts *t, const zq_weight *s
     if (rc) return rc;
     // ---- down
     switch (t->down_type) {
-    case ZQ_Q4_K: rc = launch_quantize<ZQ_Q4_K>(ctx, d_act, ZQ_F32, nullptr, d_slot_expert, d_offsets, routes, srows, shared_id, I, units_i, d_xq2, err); break;
-    case ZQ_Q4_0: rc = launch_quantize<ZQ_Q4_0>(ctx, d_act, ZQ_F32, nullptr, d_slot_expert, d_offsets, routes, srows, shared_id, I, units_i, d_xq2, err); break;
-    default: rc = launch_quantize<ZQ_Q8_0>(ctx, d_act, ZQ_F32, nullptr, d_slot_expert, d_offsets, routes, srows, shared_id, I, units_i, d_xq2, err); break;
+    case ZQ_Q4_K: rc = launch_quantize<ZQ_Q4_K>(ctx, d_act, ZQ_F32, nullptr, d_slot_expert, d_offsets, routes, srows, shared_id, (int)E, I, units_i, d_xq2, err); break;
+    case ZQ_Q4_0: rc = launch_quantize<ZQ_Q4_0>(ctx, d_act, ZQ_F32, nullptr, d_slot_expert, d_offsets, routes, srows, shared_id, (int)E, I, units_i, d_xq2, err); break;
+    default: rc = launch_quantize<ZQ_Q8_0>(ctx, d_act, ZQ_F32, nullptr, d_slot_expert, d_offsets, routes, srows, shared_id, (int)E, I, units_i, d_xq2, err); break;
     }
     if (rc) return rc;
     ga.maps_a = t->d_down_maps;

@@ -79,6 +79,10 @@ PROTOTYPES = {
     "zq_moe_route_softmax_topk": (_i, [_vp, _vp, _i, _sz, _sz, _vp, _vp, _sz, _sz, _f, _i, _vp, _vp, _err]),
     "zq_moe_experts_create": (_i, [_vp, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), _sz, C.POINTER(_vp), _err]),
     "zq_moe_experts_destroy": (None, [_vp]),
+    "zq_moe_ep_export": (_i, [_vp, _sz, _sz, _sz, _sz, _i, _vp, _err]),
+    "zq_moe_ep_init": (_i, [_vp, _vp, _err]),
+    "zq_moe_ep_shutdown": (None, [_vp]),
+    "zq_moe_forward_ep": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _sz, _sz, _vp, _vp, _sz, _vp, _i, _vp, _err]),
     "zq_moe_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _sz, _vp, _vp, _sz, _vp, _i, _vp, _err]),
 }
 
