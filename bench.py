@@ -33,7 +33,9 @@ Q4_0, Q4_K = 2, 12
 FORMATS = [(Q4_K, "q4_k"), (Q4_0, "q4_0")]
 METRIC = "Q4_K/Q4_0 decode GEMV sweep, algorithmic HBM GB/s"
 BPW = 0.5625
-NCU_TRAFFIC_RATIO = 50.21 / 50.23  # measured DRAM bytes over algorithmic bytes of the captured launch (profiles/)
+# DRAM bytes (read + write) over algorithmic bytes of one captured launch of the roofline kernel (ncu, the Q4_K batch-1
+# block of five matrices: 177.65 MB read + 4.29 MB written for 175.28 MB algorithmic)
+NCU_TRAFFIC_RATIO = (177.65 + 4.29) / 175.28
 
 
 def algorithmic_bytes(k: int, n: int, m: int) -> int:
@@ -62,7 +64,7 @@ class ClockSampler:
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except Exception:
             self.proc = None
             return
@@ -95,7 +97,8 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(name)
         sm.sort()
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(smax) if smax else None, "samples": len(sm), "reasons": sorted(reasons)}
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(smax) if smax else None, "samples": len(sm), "reasons": sorted(reasons),
+                "window": "every 20 ms from before ~0.25 s of untimed steps of the same work, through the warm-up, to the end of the timed steps"}
 
 
 def run_ours(args):
@@ -300,12 +303,21 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
-        step()
-    barrier()
+    # The timed region of a default run lasts a few milliseconds, less than one period of the clock sampler, so the
+    # sampler runs from here on: through ~0.25 s of untimed steps of the very same work (not counted as warm-up steps),
+    # the warm-up steps and the timed steps.
     sampler = ClockSampler(local_rank)
     if rank == 0 and not args.no_clocks:
         sampler.start()
+    if not args.no_clocks:
+        settle = time.perf_counter()
+        while time.perf_counter() - settle < 0.25:
+            for _ in range(20):
+                step()
+            torch.cuda.synchronize()
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
     launches_before = ctx.launch_count
     events = []
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -395,6 +407,12 @@ def run_ours(args):
             extras["prefill_gemm"] = bench_prefill(ctx, device, args)
         if world == 1 and args.extras in ("all", "prefill"):
             extras["kquant_decode"] = bench_kquant_decode(ctx, device)
+        if world == 1 and args.extras in ("all", "configs"):
+            sustained = hbm_peak
+            peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+            sustained_tf = float(json.load(open(peaks_path)).get("bf16_tflops_sustained", 1387.8)) if os.path.exists(peaks_path) else 1400.0
+            extras["config0_minicpm5_decode_step"] = bench_config0(ctx, device, hbm_peak)
+            extras["config3_iq4nl_q8_0"] = bench_config3(ctx, device, hbm_peak, sustained_tf)
         if args.extras in ("all", "moe"):
             extras["moe"] = bench_moe(ctx, device, args, world, rank)
     if rank != 0:
@@ -527,6 +545,182 @@ def _time_ms(fn, reps):
     e1.record()
     torch.cuda.synchronize()
     return e0.elapsed_time(e1) / reps
+
+
+def _graph_time_us(ctx, device, fn, reps=20):
+    """Average time of one fn() call: captured once in a CUDA graph (after an eager pass that sizes the library's
+    buffers), replayed `reps` times between CUDA events."""
+    import torch
+
+    fn()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream(device=device)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side):
+        ctx.set_stream(torch.cuda.current_stream(device).cuda_stream)
+        fn()
+    ctx.set_stream(torch.cuda.current_stream(device).cuda_stream)
+    for _ in range(3):
+        g.replay()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(reps):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps * 1e3
+
+
+def bench_config0(ctx, device, hbm_peak):
+    """configs[0]: the decode step of a 1B-class dense decoder (MiniCPM5-1B Q4_K_M shape): hidden 1536, q/o 1536 -> 1536,
+    k/v 1536 -> 512, gate/up 1536 -> 3840, down 3840 -> 1536, Q4_K from N(0, 0.02), one f32 N(0, 1) row, seed 0; LM head
+    Q8_0 with a synthetic vocabulary of 32 768 rows (the reference reads the vocabulary from the model file).  24
+    layers of distinct weights (326 MB: larger than L2) are walked in turn.  Reported: latency of every projection on
+    its own (one zq_linear per call), and of the layer's linear work as the fused operators issue it: RMSNorm + q/k/v
+    (zq_rmsnorm_linear, one decode launch), o + residual, RMSNorm + gate/up + SiLU and down + residual (zq_gated_mlp).
+    Attention itself is not part of this path and is left out."""
+    import ctypes as C
+
+    import torch
+
+    from zllm_b200 import ffi
+
+    hidden, kv, ffn, layers, vocab = 1536, 512, 3840, 24, 32768
+    shapes = {"q": (hidden, hidden), "k": (kv, hidden), "v": (kv, hidden), "o": (hidden, hidden), "gate": (ffn, hidden), "up": (ffn, hidden), "down": (hidden, ffn)}
+    gen = torch.Generator(device=device)
+    weights = []
+    for l in range(layers):
+        layer = {}
+        for i, (name, (rows, cols)) in enumerate(shapes.items()):
+            gen.manual_seed(l * 16 + i)
+            full = torch.randn((rows, cols), generator=gen, device=device, dtype=torch.float32) * 0.02
+            layer[name] = ctx.prepare_weight(Q4_K, ctx.quantize(Q4_K, full), rows, cols)
+        weights.append(layer)
+    gen.manual_seed(999)
+    head_full = torch.randn((vocab, hidden), generator=gen, device=device, dtype=torch.float32) * 0.02
+    head = ctx.prepare_weight(8, ctx.quantize(8, head_full), vocab, hidden)
+    del head_full
+    gen.manual_seed(0)
+    x = torch.randn((1, hidden), generator=gen, device=device, dtype=torch.float32)
+    xf = torch.randn((1, ffn), generator=gen, device=device, dtype=torch.float32)
+    norm_w = torch.ones(hidden, device=device, dtype=torch.float32)
+    out = {"layers_walked": layers, "unit": "us", "weights": "Q4_K (N(0, 0.02) through the reference's encoder), LM head Q8_0 x 32768 rows (synthetic vocabulary)"}
+    per = {}
+    for name, (rows, cols) in shapes.items():
+        src = xf if cols == ffn else x
+        y = torch.empty((1, rows), device=device, dtype=torch.float32)
+
+        def each(name=name, src=src, y=y, rows=rows):
+            for l in range(layers):
+                ffi.call("zq_linear", ctx.handle, weights[l][name].handle, C.c_void_p(src.data_ptr()), ffi.F32, 1, C.c_void_p(y.data_ptr()), ffi.F32, None)
+
+        us = _graph_time_us(ctx, device, each) / layers
+        nbytes = int(rows * cols * BPW) + cols * 4 + rows * 4
+        per[name] = {"us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1)}
+    out["per_projection"] = per
+    yq, yk, yv = (torch.empty((1, r), device=device, dtype=torch.float32) for r in (hidden, kv, kv))
+    yo, ymlp = torch.empty((1, hidden), device=device, dtype=torch.float32), torch.empty((1, hidden), device=device, dtype=torch.float32)
+    y3 = (C.c_void_p * 3)(yq.data_ptr(), yk.data_ptr(), yv.data_ptr())
+
+    def step():
+        for l in range(layers):
+            w = weights[l]
+            w3 = (C.c_void_p * 3)(w["q"].handle, w["k"].handle, w["v"].handle)
+            ffi.call("zq_rmsnorm_linear", ctx.handle, w3, 3, C.c_void_p(x.data_ptr()), ffi.F32, 1, C.c_void_p(norm_w.data_ptr()), C.c_float(1e-6), C.c_float(0.0), y3, ffi.F32)
+            ffi.call("zq_linear", ctx.handle, w["o"].handle, C.c_void_p(yq.data_ptr()), ffi.F32, 1, C.c_void_p(yo.data_ptr()), ffi.F32, C.c_void_p(x.data_ptr()))
+            ffi.call("zq_gated_mlp", ctx.handle, w["gate"].handle, w["up"].handle, w["down"].handle, C.c_void_p(yo.data_ptr()), ffi.F32, 1, C.c_void_p(ymlp.data_ptr()), ffi.F32, C.c_void_p(yo.data_ptr()))
+
+    n0 = ctx.launch_count
+    step()
+    launches = (ctx.launch_count - n0) // layers
+    us_layer = _graph_time_us(ctx, device, step) / layers
+    layer_bytes = sum(int(r * c * BPW) for r, c in shapes.values())
+    out["fused_layer"] = {"us": round(us_layer, 2), "launches": launches, "weight_bytes": layer_bytes, "gbs": round(layer_bytes / us_layer / 1e3, 1),
+                          "roofline": {"bound": "hbm", "achieved": round(layer_bytes / us_layer / 1e3, 1), "peak": hbm_peak, "unit": "GB/s", "frac": round(layer_bytes / us_layer / 1e3 / hbm_peak, 4),
+                                       "note": "13.6 MB per layer stream in 2 us at peak: the layer is bound by its launches, not by bandwidth"}}
+    yh = torch.empty((1, vocab), device=device, dtype=torch.float32)
+    us_head = _graph_time_us(ctx, device, lambda: ffi.call("zq_linear", ctx.handle, head.handle, C.c_void_p(x.data_ptr()), ffi.F32, 1, C.c_void_p(yh.data_ptr()), ffi.F32, None))
+    head_bytes = int(vocab * hidden * 1.0625)
+    out["lm_head_q8_0"] = {"us": round(us_head, 2), "gbs": round(head_bytes / us_head / 1e3, 1), "note": "53 MB: fits in L2 when replayed back to back"}
+    for layer in weights:
+        for w in layer.values():
+            w.release()
+    head.release()
+    torch.cuda.empty_cache()
+    return out
+
+
+def bench_config3(ctx, device, hbm_peak, sustained_tflops):
+    """configs[3]: mixed formats: IQ4_NL for the FFN (gate/up 3840 -> 15360, down 15360 -> 3840), Q8_0 for the attention
+    projections (q, k, v, o taken as 3840 -> 3840: the head geometry is not given).  Decode with one f32 row (four
+    layers of distinct weights, 650 MB, walked in turn) and prefill with 4 096 bf16 tokens (one layer)."""
+    import ctypes as C
+
+    import torch
+
+    from zllm_b200 import ffi
+
+    IQ4_NL, Q8_0 = 20, 8
+    hidden, ffn, layers = 3840, 15360, 4
+    shapes = [("q", Q8_0, hidden, hidden), ("k", Q8_0, hidden, hidden), ("v", Q8_0, hidden, hidden), ("o", Q8_0, hidden, hidden), ("gate", IQ4_NL, ffn, hidden), ("up", IQ4_NL, ffn, hidden), ("down", IQ4_NL, hidden, ffn)]
+    bpw = {Q8_0: 1.0625, IQ4_NL: 0.5625}
+    gen = torch.Generator(device=device)
+    weights = []
+    for l in range(layers):
+        layer = {}
+        for i, (name, fmt, rows, cols) in enumerate(shapes):
+            gen.manual_seed(7000 + l * 16 + i)
+            full = torch.randn((rows, cols), generator=gen, device=device, dtype=torch.float32) * 0.02
+            layer[name] = ctx.prepare_weight(fmt, ctx.quantize(fmt, full), rows, cols)
+            del full
+        weights.append(layer)
+    gen.manual_seed(1)
+    x = torch.randn((1, hidden), generator=gen, device=device, dtype=torch.float32)
+    xf = torch.randn((1, ffn), generator=gen, device=device, dtype=torch.float32)
+    out = {"formats": "attention q/k/v/o Q8_0 3840->3840 (assumed geometry), FFN IQ4_NL 3840->15360 / 15360->3840"}
+    dec, total_us, total_bytes = {}, 0.0, 0
+    for name, fmt, rows, cols in shapes:
+        src = xf if cols == ffn else x
+        y = torch.empty((1, rows), device=device, dtype=torch.float32)
+
+        def each(name=name, src=src, y=y):
+            for l in range(layers):
+                ffi.call("zq_linear", ctx.handle, weights[l][name].handle, C.c_void_p(src.data_ptr()), ffi.F32, 1, C.c_void_p(y.data_ptr()), ffi.F32, None)
+
+        us = _graph_time_us(ctx, device, each) / layers
+        nbytes = int(rows * cols * bpw[fmt]) + cols * 4 + rows * 4
+        dec[name] = {"us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1)}
+        total_us += us
+        total_bytes += nbytes
+    dec["all_seven"] = {"us": round(total_us, 2), "gbs": round(total_bytes / total_us / 1e3, 1)}
+    dec["roofline"] = {"bound": "hbm", "achieved": round(total_bytes / total_us / 1e3, 1), "peak": hbm_peak, "unit": "GB/s", "frac": round(total_bytes / total_us / 1e3 / hbm_peak, 4),
+                       "kernels": "Q8_0: integer-MMA decode kernel; IQ4_NL: f16 warp-MMA decode kernel (codebook lookup per weight)"}
+    out["decode_m1"] = dec
+    m = 4096
+    xb = torch.randn((m, hidden), generator=gen, device=device, dtype=torch.float32).to(torch.bfloat16)
+    xfb = torch.randn((m, ffn), generator=gen, device=device, dtype=torch.float32).to(torch.bfloat16)
+    pre, total_ms, total_flop = {}, 0.0, 0.0
+    for name, fmt, rows, cols in shapes:
+        src = xfb if cols == ffn else xb
+        y = torch.empty((m, rows), device=device, dtype=torch.bfloat16)
+        fn = lambda name=name, src=src, y=y: ffi.call("zq_linear", ctx.handle, weights[0][name].handle, C.c_void_p(src.data_ptr()), ffi.BF16, m, C.c_void_p(y.data_ptr()), ffi.BF16, None)
+        fn()
+        ms = _time_ms(fn, 3)
+        flop = 2.0 * m * rows * cols
+        pre[name] = {"ms": round(ms, 3), "tflops": round(flop / ms / 1e9, 1)}
+        total_ms += ms
+        total_flop += flop
+        del y
+    pre["all_seven"] = {"ms": round(total_ms, 3), "tflops": round(total_flop / total_ms / 1e9, 1)}
+    pre["roofline"] = {"bound": "tensor", "achieved": round(total_flop / total_ms / 1e9, 1), "peak": sustained_tflops, "unit": "TFLOP/s", "frac": round(total_flop / total_ms / 1e9 / sustained_tflops, 4),
+                       "kernels": "f16 operand pass (dequantise to the workspace) + tcgen05 GEMM: these block-32 formats have no fused prefill kernel"}
+    out["prefill_m4096"] = pre
+    for layer in weights:
+        for w in layer.values():
+            w.release()
+    torch.cuda.empty_cache()
+    return out
 
 
 def bench_kquant_decode(ctx, device):
@@ -755,10 +949,14 @@ def run_reference(args):
                 orc.linear(fmt, data, n, k, xs[k][:m])
 
     step_bytes = sum(algorithmic_bytes(k, n, m) for m in BATCHES for _, k, n, _ in work)
-    warm = min(args.warmup, 1)
+    # --steps and --warmup are honoured as given; only a run that would pass four minutes is cut short (and says so in
+    # "steps"): a full sweep step takes ~0.2 s on 16 cores
+    warm = max(args.warmup, 0)
+    t_first = time.perf_counter()
     for _ in range(warm):
         step()
-    steps = max(1, min(args.steps, 3))
+    est = (time.perf_counter() - t_first) / warm if warm else 0.2
+    steps = max(1, min(args.steps, int(240.0 / max(est, 1e-3))))
     t0 = time.perf_counter()
     for _ in range(steps):
         step()
@@ -783,7 +981,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--watchdog", type=int, default=480, help="multi-GPU runs: seconds after which a stuck run dumps tracebacks and exits")
     ap.add_argument("--no-extras", action="store_true", help="skip the prefill-GEMM and MoE side measurements")
-    ap.add_argument("--extras", default="all", choices=["all", "prefill", "moe"], help="which side measurements to run")
+    ap.add_argument("--extras", default="all", choices=["all", "prefill", "moe", "configs"], help="which side measurements to run")
     ap.add_argument("--nccl-reduce", action="store_true", help="several GPUs: sum the K-split partials with a host-launched NCCL all-reduce instead of the library's peer-store reduce (A/B aid)")
     ap.add_argument("--per-call", action="store_true", help="one zq_linear call (and launch) per matrix instead of one zq_linear_batch call per block (A/B aid)")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from the host instead of replaying CUDA graphs")

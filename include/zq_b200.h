@@ -137,6 +137,15 @@ int zq_linear_row_parallel(zq_ctx *ctx, const zq_weight *w, const void *dev_x, i
  * normalised rows stay in a context buffer (f32); the projections start under the normalisation kernel. */
 int zq_rmsnorm_linear(zq_ctx *ctx, const zq_weight *const *w, size_t n_weights, const void *dev_x, int x_dtype, size_t m, const float *dev_norm_weight, float eps, float weight_offset, void *const *dev_y,
                       int y_dtype, zq_error *err);
+/* Backend::rope / rope_prefix / rope_prefix_qk (src/backend/mod.rs:545-583): rotary position embedding of the q and k
+ * projection outputs, in place, one launch for both (their head counts may differ).  Arithmetic and parameter errors are
+ * those of attention::rope::apply_f32 (src/attention/rope.rs:120-165); f32 rows are bit-identical to the CPU path.
+ * q: [rows, q_heads * head_dim]; k: [rows, k_heads * head_dim] or NULL; row r uses table row `position + r` of the f32
+ * tables cos / sin [table_len / (rotary_dim / 2), rotary_dim / 2] on the device. */
+enum { ZQ_ROPE_SPLIT_HALF = 0, ZQ_ROPE_INTERLEAVED = 1 };  /* RotaryLayout */
+enum { ZQ_ROPE_PREFIX = 0, ZQ_ROPE_SUFFIX = 1 };           /* RotaryPlacement: rope_prefix / rope */
+int zq_rope_qk(zq_ctx *ctx, void *dev_q, size_t q_heads, void *dev_k, size_t k_heads, int dtype, size_t rows, size_t head_dim, size_t rotary_dim, int layout, int placement, size_t position,
+               const float *dev_cos, const float *dev_sin, size_t table_len, zq_error *err);
 /* gated_linear_q4_k_silu_f16 / gated_linear_q4_0_silu_f16 (src/kernel/cuda/linear.rs:1683, 1916) behind
  * Backend::gated_linear (src/backend/mod.rs:467): y = silu(gate x) * (up x). */
 int zq_gated_silu(zq_ctx *ctx, const zq_weight *gate, const zq_weight *up, const void *dev_x, int x_dtype, size_t m, void *dev_y, int y_dtype, zq_error *err);

@@ -170,6 +170,18 @@ def silu_mul(gate, up) -> np.ndarray:
     return out
 
 
+def rope(data, head_count, rotary_dim, position, cos, sin, layout=0, placement=0) -> np.ndarray:
+    """attention::rope::apply_f32 (src/attention/rope.rs:120-165) on ``data`` [rows, columns]; returns a new array.
+    layout 0 = split-half, 1 = interleaved; placement 0 = prefix, 1 = suffix."""
+    out = np.array(data, dtype=np.float32, order="C", copy=True)
+    rows, columns = out.shape
+    cos, sin = _f32(cos).reshape(-1), _f32(sin).reshape(-1)
+    if cos.size != sin.size:
+        raise OracleError("rope: cos and sin tables differ in length")
+    _check(lib().zqo_rope(_p(out), C.c_size_t(rows), C.c_size_t(columns), C.c_size_t(head_count), C.c_size_t(rotary_dim), C.c_size_t(position), _p(cos), _p(sin), C.c_size_t(cos.size), C.c_int(layout), C.c_int(placement)), "rope")
+    return out
+
+
 def route_softmax_logits(logits, top_k, scaling_factor=1.0, normalize_selected=True):
     logits = _f32(logits).reshape(-1)
     ids = np.zeros(top_k, dtype=np.uint32)

@@ -769,3 +769,38 @@ int zqo_moe_forward(const zqo_matrix *gates, const zqo_matrix *ups, const zqo_ma
     free(offsets); free(tokens); free(rweights);
     return rc;
 }
+
+/* ------------------------------------------------------------------ RoPE on projection outputs */
+
+/* attention::rope::apply_f32 (src/attention/rope.rs:120-165), the arithmetic behind Backend::rope / rope_prefix /
+ * rope_prefix_qk (src/backend/mod.rs:545-583; CPU: src/backend/cpu/context.rs:590-625, whose 8-lane fast path keeps the
+ * same mul / sub / add order).  layout 0 = SplitHalf (pair p = elements p and half + p), 1 = Interleaved (2p, 2p + 1);
+ * placement 0 = Prefix (the head's first rotary_dim elements), 1 = Suffix (its last).  In place.
+ * Returns 0, or 1 for the parameter errors the reference reports. */
+int zqo_rope(float *data, size_t rows, size_t columns, size_t head_count, size_t rotary_dim, size_t position, const float *cos_table, const float *sin_table, size_t table_len, int layout, int placement) {
+    if (head_count == 0 || rotary_dim == 0 || rotary_dim % 2 || columns % head_count) return 1;
+    const size_t head_dim = columns / head_count;
+    if (rotary_dim > head_dim) return 1;
+    const size_t half = rotary_dim / 2;
+    if ((position + rows) * half > table_len) return 1;
+    float *source = (float *)malloc(rotary_dim * sizeof(float));
+    for (size_t row = 0; row < rows; ++row) {
+        const float *cos_row = cos_table + (position + row) * half, *sin_row = sin_table + (position + row) * half;
+        for (size_t head = 0; head < head_count; ++head) {
+            const size_t head_start = row * columns + head * head_dim;
+            const size_t start = placement == 0 ? head_start : head_start + head_dim - rotary_dim;
+            memcpy(source, data + start, rotary_dim * sizeof(float));
+            for (size_t pair = 0; pair < half; ++pair) {
+                const size_t ri = layout == 0 ? pair : pair * 2, ii = layout == 0 ? half + pair : pair * 2 + 1;
+                const float real = source[ri], imaginary = source[ii];
+                /* separate roundings, as the reference's scalar code (this file is built with -ffp-contract=off) */
+                volatile float a = real * cos_row[pair], b = imaginary * sin_row[pair];
+                volatile float c = imaginary * cos_row[pair], d = real * sin_row[pair];
+                data[start + ri] = a - b;
+                data[start + ii] = c + d;
+            }
+        }
+    }
+    free(source);
+    return 0;
+}

@@ -274,6 +274,21 @@ class B200Context:
         a, b, c = self.linear_multi(x, [first, second, third], out_dtype)
         return a, b, c
 
+    def rope_prefix_qk(self, query: torch.Tensor, key: Optional[torch.Tensor], num_heads: int, num_kv_heads: int, rotary_dim: int, position: int, cos: torch.Tensor, sin: torch.Tensor,
+                       interleaved: bool = False, suffix: bool = False):
+        """``Backend::rope_prefix_qk`` (src/backend/mod.rs:567; ``suffix=True`` is ``rope``): rotates q and k in place,
+        one launch; ``cos`` / ``sin`` are f32 device tables [positions, rotary_dim / 2]."""
+        rows = query.shape[0] if query.dim() > 1 else 1
+        head_dim = query.numel() // rows // num_heads
+        if key is not None and (key.dtype != query.dtype or key.numel() != rows * num_kv_heads * head_dim):
+            raise ffi.ZqFailure(1, "rope: key shape or dtype does not match the query's")
+        cos, sin = cos.contiguous().float(), sin.contiguous().float()
+        if cos.numel() != sin.numel():
+            raise ffi.ZqFailure(1, f"rope: cos and sin tables differ in length ({cos.numel()} / {sin.numel()})")
+        ffi.call("zq_rope_qk", self.handle, _ptr(query), num_heads, _ptr(key), num_kv_heads if key is not None else 0, _dt(query), rows, head_dim, rotary_dim, int(interleaved), int(suffix), position,
+                 _ptr(cos), _ptr(sin), cos.numel())
+        return query, key
+
     def gated_linear(self, x: torch.Tensor, gate: Weight, up: Weight, out_dtype=None) -> torch.Tensor:
         x = x.contiguous()
         m = self._rows(x, gate.cols)

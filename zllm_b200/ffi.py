@@ -70,6 +70,7 @@ PROTOTYPES = {
     "zq_dist_shutdown": (None, [_vp]),
     "zq_linear_multi": (_i, [_vp, C.POINTER(_vp), _sz, _vp, _i, _sz, C.POINTER(_vp), _i, _err]),
     "zq_rmsnorm_linear": (_i, [_vp, C.POINTER(_vp), _sz, _vp, _i, _sz, _vp, C.c_float, C.c_float, C.POINTER(_vp), _i, _err]),
+    "zq_rope_qk": (_i, [_vp, _vp, _sz, _vp, _sz, _i, _sz, _sz, _sz, _i, _i, _sz, _vp, _vp, _sz, _err]),
     "zq_gated_silu": (_i, [_vp, _vp, _vp, _vp, _i, _sz, _vp, _i, _err]),
     "zq_gated_mlp": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _sz, _vp, _i, _vp, _err]),
     "zq_linear_noalloc": (_i, [_vp, _vp, _vp, _i, _sz, _vp, _i, _err]),
