@@ -33,8 +33,11 @@ typedef struct zq_error { char message[512]; } zq_error;
 /* GGUF tensor type ids (src/weight/container/gguf.rs:112-151).  Q5_K and Q6_K (src/weight/codec/ggml.rs:425-469;
  * reference CUDA kernels src/kernel/cuda/linear.rs:1167-1234, 1967-2101) dequantise bit-exactly; zq_linear with up to
  * 8 activation rows runs a CUDA-core decode kernel on the packed bytes, more rows and gated pairs the f16 operand pass
- * and the tensor-core GEMM.  They have no encoder (zq_quantize) and no allocation-free entry. */
-enum { ZQ_Q4_0 = 2, ZQ_Q8_0 = 8, ZQ_Q4_K = 12, ZQ_Q5_K = 13, ZQ_Q6_K = 14, ZQ_IQ4_NL = 20 };
+ * and the tensor-core GEMM.  They have no encoder (zq_quantize) and no allocation-free entry.  Q5_0 / Q5_1 (types 6, 7,
+ * which the reference CUDA backend accepts, src/backend/cuda/mod.rs:62-72), Q3_K (11) and IQ4_XS (23)
+ * (src/weight/codec/ggml.rs:111-130, 384-406, 246-261) dequantise bit-exactly too and run every projection through the
+ * operand pass and the GEMM.  The codebook-grid types (IQ2_*, IQ3_*) are not taken. */
+enum { ZQ_Q4_0 = 2, ZQ_Q5_0 = 6, ZQ_Q5_1 = 7, ZQ_Q8_0 = 8, ZQ_Q3_K = 11, ZQ_Q4_K = 12, ZQ_Q5_K = 13, ZQ_Q6_K = 14, ZQ_IQ4_NL = 20, ZQ_IQ4_XS = 23 };
 enum { ZQ_F32 = 0, ZQ_F16 = 1, ZQ_BF16 = 2 };
 enum { ZQ_OK = 0, ZQ_ERR_SHAPE = 1, ZQ_ERR_UNSUPPORTED = 2, ZQ_ERR_CUDA = 3, ZQ_ERR_ARG = 4, ZQ_ERR_DEVICE_STATUS = 5, ZQ_ERR_DIST = 6 };
 
@@ -183,6 +186,14 @@ int zq_batch_finish(zq_ctx *ctx, zq_error *err);
 /* moe_route_softmax_topk_device_f32: logits = x router^T (+ bias), softmax top-k with ties to the lower expert id.
  * router_f32 [num_experts, hidden] on the device; bias may be NULL.  Writes ids [m, top_k] and weights [m, top_k]. */
 int zq_moe_route_softmax_topk(zq_ctx *ctx, const void *dev_x, int x_dtype, size_t m, size_t hidden, const float *dev_router_f32, const float *dev_bias_f32, size_t num_experts, size_t top_k, float scaling_factor, int normalize_selected, uint32_t *dev_ids, float *dev_weights, zq_error *err);
+/* The same call with the router family of src/moe/routing.rs as a parameter.  ZQ_ROUTE_SOFTMAX is the call above.
+ * ZQ_ROUTE_SIGMOID_BIAS (route_sigmoid_bias_logits, :74) and ZQ_ROUTE_SQRT_SOFTPLUS_BIAS (route_sqrt_softplus_bias_logits,
+ * :79) follow route_bias_corrected_logits (:45-67): raw score sigmoid(logit) or sqrt(softplus(logit)); the bias only takes
+ * part in choosing the top-k (raw + bias, ties to the lower id); the chosen experts' raw scores are normalised to sum 1
+ * and multiplied by scaling_factor (`normalize_selected` is ignored; a NULL bias counts as zero). */
+enum { ZQ_ROUTE_SOFTMAX = 0, ZQ_ROUTE_SIGMOID_BIAS = 1, ZQ_ROUTE_SQRT_SOFTPLUS_BIAS = 2 };
+int zq_moe_route_topk(zq_ctx *ctx, int scoring, const void *dev_x, int x_dtype, size_t m, size_t hidden, const float *dev_router_f32, const float *dev_bias_f32, size_t num_experts, size_t top_k, float scaling_factor,
+                      int normalize_selected, uint32_t *dev_ids, float *dev_weights, zq_error *err);
 /* The resident expert table that replaces CudaMoeState's LRU/arena cache (src/backend/cuda/expert.rs:284-570)
  * when every expert fits in HBM.  gate/up: [intermediate, hidden]; down: [hidden, intermediate].  The table
  * borrows the weights; release them after zq_moe_experts_destroy. */

@@ -18,7 +18,8 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "build", "libzq_oracle.so")
 
 Q4_0, Q8_0, Q4_K, Q5_K, Q6_K, IQ4_NL = 2, 8, 12, 13, 14, 20
-BLOCK = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210), IQ4_NL: (32, 18)}
+Q5_0, Q5_1, Q3_K, IQ4_XS = 6, 7, 11, 23
+BLOCK = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210), IQ4_NL: (32, 18), Q5_0: (32, 22), Q5_1: (32, 24), Q3_K: (256, 110), IQ4_XS: (256, 136)}
 KVALUES_IQ4NL = np.array([-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113], dtype=np.int8)
 
 
@@ -187,6 +188,25 @@ def route_softmax_logits(logits, top_k, scaling_factor=1.0, normalize_selected=T
     ids = np.zeros(top_k, dtype=np.uint32)
     w = np.zeros(top_k, dtype=np.float32)
     _check(lib().zqo_route_softmax_logits(_p(logits), C.c_size_t(logits.size), C.c_size_t(top_k), C.c_float(scaling_factor), C.c_int(int(normalize_selected)), _p(ids), _p(w)), "route_softmax_logits")
+    return ids, w
+
+
+def router_logits(x_row, router) -> np.ndarray:
+    """kernel::cpu::moe::router_logits (src/kernel/cpu/moe.rs:38-55) for one token."""
+    x_row, router = _f32(x_row).reshape(-1), _f32(router)
+    out = np.zeros(router.shape[0], dtype=np.float32)
+    lib().zqo_router_logits(_p(x_row), _p(router), C.c_size_t(x_row.size), C.c_size_t(router.shape[0]), _p(out))
+    return out
+
+
+def route_bias_corrected_logits(logits, bias, top_k, scaling_factor=1.0, kind=1):
+    """route_sigmoid_bias_logits (kind 1) / route_sqrt_softplus_bias_logits (kind 2), src/moe/routing.rs:43-81, one row."""
+    logits, bias = _f32(logits).reshape(-1), _f32(bias).reshape(-1)
+    if logits.size != bias.size:
+        raise OracleError("router: logits and bias differ in length")
+    ids = np.zeros(top_k, dtype=np.uint32)
+    w = np.zeros(top_k, dtype=np.float32)
+    _check(lib().zqo_route_bias_corrected_logits(_p(logits), _p(bias), C.c_size_t(logits.size), C.c_size_t(top_k), C.c_float(scaling_factor), C.c_int(kind), _p(ids), _p(w)), "route_bias_corrected_logits")
     return ids, w
 
 

@@ -55,11 +55,15 @@ int zqo_block_layout(uint32_t tensor_type, size_t *elements, size_t *bytes) {
     case 0: *elements = 1; *bytes = 4; return 0;
     case 1: *elements = 1; *bytes = 2; return 0;
     case 2: *elements = 32; *bytes = 18; return 0;
+    case 6: *elements = 32; *bytes = 22; return 0;
+    case 7: *elements = 32; *bytes = 24; return 0;
     case 8: *elements = 32; *bytes = 34; return 0;
+    case 11: *elements = QK_K; *bytes = 110; return 0;
     case 12: *elements = QK_K; *bytes = 144; return 0;
     case 13: *elements = QK_K; *bytes = 176; return 0;
     case 14: *elements = QK_K; *bytes = 210; return 0;
     case 20: *elements = 32; *bytes = 18; return 0;
+    case 23: *elements = QK_K; *bytes = 136; return 0;
     default: return -1;
     }
 }
@@ -176,6 +180,70 @@ static void decode_q6_k(const uint8_t *block, float *output) {
 }
 
 /* src/weight/codec/ggml.rs:73-100 (decode_block) */
+/* src/weight/codec/ggml.rs:111-119 (Q5_0: f16 scale, 32 high bits, 16 nibble bytes; value = d * (q5 - 16)) */
+static void decode_q5_0(const uint8_t *block, float *output) {
+    const float scale = read_f16(block, 0);
+    uint32_t high;
+    memcpy(&high, block + 2, 4);
+    for (int index = 0; index < 32; ++index) {
+        const uint8_t packed = block[6 + index % 16];
+        const uint32_t low = index < 16 ? (uint32_t)(packed & 15) : (uint32_t)(packed >> 4);
+        output[index] = scale * (float)((int32_t)(low | (((high >> index) & 1u) << 4)) - 16);
+    }
+}
+
+/* src/weight/codec/ggml.rs:121-130 (Q5_1: f16 scale, f16 minimum, 32 high bits, 16 nibble bytes; value = d * q5 + m) */
+static void decode_q5_1(const uint8_t *block, float *output) {
+    const float scale = read_f16(block, 0), minimum = read_f16(block, 2);
+    uint32_t high;
+    memcpy(&high, block + 4, 4);
+    for (int index = 0; index < 16; ++index) {
+        const uint8_t low = block[8 + index];
+        volatile float a = scale * (float)((uint32_t)(low & 15) | (((high >> index) & 1u) << 4));
+        volatile float b = scale * (float)((uint32_t)(low >> 4) | (((high >> (index + 16)) & 1u) << 4));
+        output[index] = a + minimum;
+        output[index + 16] = b + minimum;
+    }
+}
+
+/* src/weight/codec/ggml.rs:246-261 (IQ4_XS: f16 d, 16 high scale bits, 4 low scale bytes, 128 nibble bytes; each block of
+ * 32 has a 6-bit scale ls, value = d * (ls - 32) * codebook[nibble]) */
+static void decode_iq4_xs(const uint8_t *block, float *output) {
+    const float d = read_f16(block, 0);
+    const uint16_t scales_h = (uint16_t)(block[2] | (block[3] << 8));
+    const uint8_t *scales_l = block + 4, *quants = block + 8;
+    for (int ib = 0; ib < 8; ++ib) {
+        const int ls = ((scales_l[ib / 2] >> (4 * (ib % 2))) & 0x0f) | (((scales_h >> (2 * ib)) & 0x03) << 4);
+        const float dl = d * ((float)ls - 32.0f);
+        for (int j = 0; j < 16; ++j) {
+            const uint8_t q = quants[ib * 16 + j];
+            output[ib * 32 + j] = dl * (float)KVALUES_IQ4NL[q & 0x0f];
+            output[ib * 32 + j + 16] = dl * (float)KVALUES_IQ4NL[q >> 4];
+        }
+    }
+}
+
+/* src/weight/codec/ggml.rs:384-406 (Q3_K: 32 high-bit mask bytes, 64 two-bit bytes, 12 scale bytes, f16 d; 16 groups of
+ * 16 with a 6-bit scale - 32; value = d * scale * (q2 - (high bit clear ? 4 : 0)), multiplied left to right) */
+static void decode_q3_k(const uint8_t *block, float *output) {
+    const uint8_t *hmask = block, *quants = block + 32, *scales = block + 96;
+    const float d = read_f16(block, 108);
+    for (int group = 0; group < 16; ++group) {
+        const uint8_t low = group < 8 ? (uint8_t)(scales[group] & 0x0f) : (uint8_t)(scales[group - 8] >> 4);
+        const uint8_t high = (uint8_t)((scales[8 + group % 4] >> (2 * (group / 4))) & 0x03);
+        const int scale = (int)(low | (high << 4)) - 32;
+        const int half = group / 8, pair = group % 8;
+        const int source = half * 32 + (pair % 2) * 16, mask_source = (pair % 2) * 16, shift = 2 * (pair / 2);
+        const uint8_t mask = (uint8_t)(1u << (group / 2));
+        for (int index = 0; index < 16; ++index) {
+            const int low_bits = (quants[source + index] >> shift) & 0x03;
+            const int quant = low_bits - ((hmask[mask_source + index] & mask) == 0 ? 4 : 0);
+            volatile float ds = d * (float)scale;
+            output[group * 16 + index] = ds * (float)quant;
+        }
+    }
+}
+
 int zqo_decode_block(uint32_t tensor_type, const uint8_t *bytes, size_t nbytes, float *output, size_t noutput) {
     size_t elements, block_bytes;
     if (zqo_block_layout(tensor_type, &elements, &block_bytes)) return -1;
@@ -184,11 +252,15 @@ int zqo_decode_block(uint32_t tensor_type, const uint8_t *bytes, size_t nbytes, 
     case 0: memcpy(output, bytes, 4); return 0;
     case 1: output[0] = read_f16(bytes, 0); return 0;
     case 2: decode_q4_0(bytes, output); return 0;
+    case 6: decode_q5_0(bytes, output); return 0;
+    case 7: decode_q5_1(bytes, output); return 0;
     case 8: decode_q8_0(bytes, output); return 0;
+    case 11: decode_q3_k(bytes, output); return 0;
     case 12: decode_q4_k(bytes, output); return 0;
     case 13: decode_q5_k(bytes, output); return 0;
     case 14: decode_q6_k(bytes, output); return 0;
     case 20: decode_iq4_nl(bytes, output); return 0;
+    case 23: decode_iq4_xs(bytes, output); return 0;
     default: return -1;
     }
 }
@@ -803,4 +875,43 @@ int zqo_rope(float *data, size_t rows, size_t columns, size_t head_count, size_t
     }
     free(source);
     return 0;
+}
+
+/* ------------------------------------------------------------------ bias-corrected routers */
+
+/* route_bias_corrected_logits (src/moe/routing.rs:45-67) behind route_sigmoid_bias_logits (:74, kind 1) and
+ * route_sqrt_softplus_bias_logits (:79, kind 2; sqrt_softplus_score :70-73): every expert has a raw score; raw + bias ranks
+ * the experts (descending, ties to the lower id); the top_k raw scores are normalised to sum 1 and scaled.
+ * Returns 0, or 1 for the parameter / mass errors the reference reports. */
+static float raw_router_score(float logit, int kind) {
+    if (kind == 1) return 1.0f / (1.0f + expf(-logit));
+    const float softplus = logit > 0.0f ? logit + log1pf(expf(-logit)) : log1pf(expf(logit));
+    return sqrtf(softplus);
+}
+
+int zqo_route_bias_corrected_logits(const float *logits, const float *bias, size_t num_experts, size_t top_k, float scaling_factor, int kind, uint32_t *experts, float *weights) {
+    if (num_experts == 0 || top_k == 0 || top_k > num_experts || !isfinite(scaling_factor) || (kind != 1 && kind != 2)) return 1;
+    float *raw = (float *)malloc(num_experts * sizeof(float));
+    float *corrected = (float *)malloc(num_experts * sizeof(float));
+    char *taken = (char *)calloc(num_experts, 1);
+    for (size_t e = 0; e < num_experts; ++e) {
+        raw[e] = raw_router_score(logits[e], kind);
+        corrected[e] = raw[e] + bias[e];
+    }
+    float sum_raw = 0.0f;
+    for (size_t slot = 0; slot < top_k; ++slot) {  /* repeated arg-max = a stable descending sort's first top_k entries */
+        size_t best = num_experts;
+        for (size_t e = 0; e < num_experts; ++e) {
+            if (taken[e]) continue;
+            if (best == num_experts || corrected[e] > corrected[best]) best = e;
+        }
+        taken[best] = 1;
+        experts[slot] = (uint32_t)best;
+        sum_raw += raw[best];
+    }
+    int rc = 0;
+    if (!isfinite(sum_raw) || sum_raw <= 0.0f) rc = 1;
+    for (size_t slot = 0; slot < top_k && !rc; ++slot) weights[slot] = raw[experts[slot]] / sum_raw * scaling_factor;
+    free(raw); free(corrected); free(taken);
+    return rc;
 }

@@ -7,6 +7,9 @@ import numpy as np
 from oracle import oracle as orc
 
 Q4_0, Q8_0, Q4_K, Q5_K, Q6_K, IQ4_NL = orc.Q4_0, orc.Q8_0, orc.Q4_K, orc.Q5_K, orc.Q6_K, orc.IQ4_NL
+Q5_0, Q5_1, Q3_K, IQ4_XS = orc.Q5_0, orc.Q5_1, orc.Q3_K, orc.IQ4_XS
+# byte offsets of the f16 scale fields of a block, per type
+SCALE_OFFSETS = {Q4_0: (0,), Q8_0: (0,), IQ4_NL: (0,), Q4_K: (0, 2), Q5_K: (0, 2), Q6_K: (208,), Q5_0: (0,), Q5_1: (0, 2), Q3_K: (108,), IQ4_XS: (0,)}
 F16_EDGE_SCALES = [0x0000, 0x0001, 0x03FF, 0x0400, 0x0401, 0x13FF, 0x17FF, 0x8401]
 
 
@@ -95,7 +98,7 @@ def quantize(tensor_type: int, values: np.ndarray) -> np.ndarray:
 
 
 def random_weight(tensor_type: int, rows: int, cols: int, seed: int, std: float = 0.02) -> np.ndarray:
-    if tensor_type in (Q5_K, Q6_K):
+    if tensor_type in (Q5_K, Q6_K, Q5_0, Q5_1, Q3_K, IQ4_XS):
         return random_kquant_weight(tensor_type, rows, cols, seed)
     rng = np.random.default_rng(seed)
     return quantize(tensor_type, rng.standard_normal((rows, cols), dtype=np.float32) * np.float32(std))
@@ -107,11 +110,9 @@ def random_bytes_weight(tensor_type: int, rows: int, cols: int, seed: int) -> np
     e, b = orc.BLOCK[tensor_type]
     blocks = rows * cols // e
     out = rng.integers(0, 256, size=(blocks, b), dtype=np.uint8)
-    n_scales = 2 if tensor_type in (Q4_K, Q5_K) else 1
-    off = 208 if tensor_type == Q6_K else 0
-    for s in range(n_scales):
+    for off in SCALE_OFFSETS[tensor_type]:
         bits = rng.integers(0, 0x7C00, size=blocks, dtype=np.uint16) | (rng.integers(0, 2, size=blocks, dtype=np.uint16) << 15)
-        out[:, off + 2 * s:off + 2 * s + 2] = bits.view(np.uint8).reshape(-1, 2)
+        out[:, off:off + 2] = bits.view(np.uint8).reshape(-1, 2)
     return out.reshape(-1)
 
 
@@ -123,11 +124,11 @@ def random_kquant_weight(tensor_type: int, rows: int, cols: int, seed: int) -> n
     e, b = orc.BLOCK[tensor_type]
     blocks = rows * cols // e
     out = rng.integers(0, 256, size=(blocks, b), dtype=np.uint8)
-    n_scales = 2 if tensor_type in (Q4_K, Q5_K) else 1
-    off = 208 if tensor_type == Q6_K else 0
-    for s in range(n_scales):
-        d = rng.uniform(2.0e-4, 6.0e-4, size=blocks).astype(np.float16)
-        out[:, off + 2 * s:off + 2 * s + 2] = d.view(np.uint8).reshape(-1, 2)
+    # super-block scales of K-quants multiply 6-bit sub-scales; block-32 scales multiply the codes directly
+    lo, hi = ((2.0e-4, 6.0e-4) if tensor_type in (Q5_K, Q6_K, Q3_K, IQ4_XS) else (2.0e-3, 6.0e-3))
+    for off in SCALE_OFFSETS[tensor_type]:
+        d = rng.uniform(lo, hi, size=blocks).astype(np.float16)
+        out[:, off:off + 2] = d.view(np.uint8).reshape(-1, 2)
     return out.reshape(-1)
 
 

@@ -214,6 +214,30 @@ def test_router_with_bias_matches_cpu_path(normalize):
         np.testing.assert_allclose(w.cpu().numpy()[clear], np.asarray(want_w).reshape(m, top_k)[clear], rtol=1e-4, atol=1e-6)
 
 
+@pytest.mark.parametrize("kind", [1, 2])
+def test_bias_corrected_routers_match_cpu_path(kind):
+    """route_sigmoid_bias_logits / route_sqrt_softplus_bias_logits (src/moe/routing.rs:43-81): the bias chooses, the raw
+    scores weigh.  Small batch, split experts, and the tensor-core logits of large batches."""
+    from zllm_b200.backend import moe_route
+
+    for m, experts, top_k, hidden in ((3, 16, 4, 256), (64, 256, 8, 512), (300, 64, 6, 1024)):
+        rng = np.random.default_rng(m + kind)
+        x = rng.standard_normal((m, hidden)).astype(np.float32)
+        router = (rng.standard_normal((experts, hidden)) / np.sqrt(hidden)).astype(np.float32)
+        bias = (0.3 * rng.standard_normal(experts)).astype(np.float32)
+        ids, w = moe_route(ctx(), torch.from_numpy(x).cuda(), torch.from_numpy(router).cuda(), top_k, 2.5, True, bias=torch.from_numpy(bias).cuda(), scoring=kind)
+        ctx().sync()
+        got_ids, got_w = ids.cpu().numpy().astype(np.uint32), w.cpu().numpy()
+        agree = 0
+        for t in range(m):
+            want_ids, want_w = orc.route_bias_corrected_logits(orc.router_logits(x[t], router), bias, top_k, 2.5, kind=kind)
+            if np.array_equal(got_ids[t], want_ids):  # a near-tie of two corrected scores may order differently in the two f32 sums
+                agree += 1
+                np.testing.assert_allclose(got_w[t], want_w, rtol=2e-5, atol=1e-7)
+                assert abs(float(got_w[t].sum()) - 2.5) < 1e-4
+        assert agree >= 0.98 * m
+
+
 def test_router_row_of_nans_is_reported_not_faulted():
     """A token whose activations are NaN has no arg-max: the router writes valid expert ids, NaN weights, and the status
     word reports it; nothing is read or written out of range."""

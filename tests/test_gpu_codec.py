@@ -8,7 +8,7 @@ from tests import helpers as H
 from tests.gpu_util import ctx, dev, host
 
 pytestmark = pytest.mark.gpu
-TYPES = [H.Q4_0, H.Q8_0, H.Q4_K, H.Q5_K, H.Q6_K, H.IQ4_NL]
+TYPES = [H.Q4_0, H.Q8_0, H.Q4_K, H.Q5_K, H.Q6_K, H.IQ4_NL, H.Q5_0, H.Q5_1, H.Q3_K, H.IQ4_XS]
 
 
 def _bits(a):
@@ -25,7 +25,7 @@ def test_dequantize_is_bit_exact_on_random_bytes(tensor_type, rows, cols):
     assert np.array_equal(_bits(got), _bits(want))
 
 
-@pytest.mark.parametrize("tensor_type", [H.Q4_0, H.Q8_0, H.IQ4_NL])
+@pytest.mark.parametrize("tensor_type", [H.Q4_0, H.Q8_0, H.IQ4_NL, H.Q5_0, H.Q5_1])
 @pytest.mark.parametrize("cols", [32, 1056, 2560])
 def test_dequantize_handles_rows_that_are_not_whole_units(tensor_type, cols):
     """Column counts of the reference's Q8_0 test (src/kernel/cuda/linear.rs:2209-2230): 32-aligned, not 256-aligned."""
@@ -63,10 +63,10 @@ def test_f16_edge_scales(tensor_type):
     data = rng.integers(0, 256, size=(n * per_row, b), dtype=np.uint8)
     for i, bits in enumerate(H.F16_EDGE_SCALES):
         for j in range(per_row):
-            off = 208 if tensor_type == H.Q6_K else 0
-            data[i * per_row + j, off:off + 2] = np.frombuffer(np.uint16(bits).tobytes(), dtype=np.uint8)
-            if tensor_type in (H.Q4_K, H.Q5_K):
-                data[i * per_row + j, 2:4] = np.frombuffer(np.uint16(H.F16_EDGE_SCALES[(i + 3) % n]).tobytes(), dtype=np.uint8)
+            offs = H.SCALE_OFFSETS[tensor_type]
+            data[i * per_row + j, offs[0]:offs[0] + 2] = np.frombuffer(np.uint16(bits).tobytes(), dtype=np.uint8)
+            if len(offs) > 1:
+                data[i * per_row + j, offs[1]:offs[1] + 2] = np.frombuffer(np.uint16(H.F16_EDGE_SCALES[(i + 3) % n]).tobytes(), dtype=np.uint8)
     data = data.reshape(-1)
     w = ctx().prepare_weight(tensor_type, data, n, 256)
     got = host(ctx().dequantize(w))
@@ -106,7 +106,52 @@ def test_reference_known_answers_through_the_device_path():
     assert host(ctx().dequantize(ctx().prepare_weight(H.Q6_K, q6, 1, 256)))[0][0] == -32.0
 
 
-@pytest.mark.parametrize("tensor_type", [H.Q8_0, H.IQ4_NL, H.Q4_K, H.Q5_K, H.Q6_K])
+def test_reference_known_answers_of_the_operand_pass_types():
+    """src/weight/codec/ggml.rs:483-511, 578-585, 616-625 (Q5_0, Q5_1, Q3_K, IQ4_XS) decoded by the CUDA kernels."""
+    b = np.zeros((1, 22), dtype=np.uint8)
+    b[0, :2] = np.frombuffer(H.f16_bytes(0.5), dtype=np.uint8)
+    b[0, 2:6] = np.frombuffer(np.uint32(0xFFFF0000).tobytes(), dtype=np.uint8)
+    for i in range(16):
+        b[0, 6 + i] = i | ((15 - i) << 4)
+    out = host(ctx().dequantize(ctx().prepare_weight(H.Q5_0, b.reshape(-1), 1, 32)))[0]
+    assert all(out[i] == (i - 16.0) * 0.5 and out[16 + i] == (15 - i) * 0.5 for i in range(16))
+    b = np.zeros((1, 24), dtype=np.uint8)
+    b[0, :2] = np.frombuffer(H.f16_bytes(0.25), dtype=np.uint8)
+    b[0, 2:4] = np.frombuffer(H.f16_bytes(-3.0), dtype=np.uint8)
+    b[0, 4:8] = np.frombuffer(np.uint32(0xFFFF0000).tobytes(), dtype=np.uint8)
+    for i in range(16):
+        b[0, 8 + i] = i | (i << 4)
+    out = host(ctx().dequantize(ctx().prepare_weight(H.Q5_1, b.reshape(-1), 1, 32)))[0]
+    assert all(out[i] == i * 0.25 - 3.0 for i in range(32))
+    q3 = np.zeros(110, dtype=np.uint8)
+    q3[0], q3[32], q3[96], q3[104] = 1, 3, 1, 2
+    q3[108:] = [0x00, 0x3C]
+    assert host(ctx().dequantize(ctx().prepare_weight(H.Q3_K, q3, 1, 256)))[0][0] == 3.0
+    xs = np.zeros(136, dtype=np.uint8)
+    xs[:2] = [0x00, 0x3C]
+    xs[2:4] = [2, 0]
+    xs[4] = 1
+    xs[8] = 0xF0
+    out = host(ctx().dequantize(ctx().prepare_weight(H.IQ4_XS, xs, 1, 256)))[0]
+    assert out[0] == -127.0 and out[16] == 113.0
+
+
+@pytest.mark.parametrize("tensor_type", [H.Q5_0, H.Q5_1, H.Q3_K, H.IQ4_XS])
+@pytest.mark.parametrize("m", [1, 5, 40])
+def test_operand_pass_types_run_the_linear_layer(tensor_type, m):
+    """Q5_0, Q5_1, Q3_K and IQ4_XS have no decode kernel: every projection is the f16 operand pass and the tensor-core GEMM
+    (2e-3 against the CPU path, which decodes each block and takes an f32 dot product)."""
+    rows, cols = 192, 1024
+    data = H.random_weight(tensor_type, rows, cols, seed=40 + m)
+    x = np.random.default_rng(m).standard_normal((m, cols)).astype(np.float32)
+    xb = dev(x, torch.bfloat16)
+    w = ctx().prepare_weight(tensor_type, data, rows, cols)
+    got = host(ctx().linear(xb, w, out_dtype=torch.float32))
+    want = orc.linear(tensor_type, data, rows, cols, xb.float().cpu().numpy())
+    assert H.max_rel_error(got, want) <= 2e-3
+
+
+@pytest.mark.parametrize("tensor_type", [H.Q8_0, H.IQ4_NL, H.Q4_K, H.Q5_K, H.Q6_K, H.Q5_0, H.IQ4_XS])
 def test_gather_rows_equals_f16_of_dequant(tensor_type):
     """src/kernel/cuda/linear.rs:2156-2173: gathered rows == f16(dequant) exactly."""
     rows, cols = 50, 512

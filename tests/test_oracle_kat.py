@@ -273,3 +273,65 @@ def test_q4_k_encode_roundtrip_error_is_bounded():
     back = orc.dequantize(12, packed, v.size)
     step = (v.reshape(-1, 32).max(axis=1) - np.minimum(v.reshape(-1, 32).min(axis=1), 0)).max() / 15
     assert np.max(np.abs(back - v)) <= step
+
+
+def test_q5_0_preserves_signed_fifth_bit():
+    """src/weight/codec/ggml.rs:483-496"""
+    block = np.zeros(22, dtype=np.uint8)
+    block[:2] = np.frombuffer(np.float16(0.5).tobytes(), dtype=np.uint8)
+    block[2:6] = np.frombuffer(np.uint32(0xFFFF0000).tobytes(), dtype=np.uint8)
+    for i in range(16):
+        block[6 + i] = i | ((15 - i) << 4)
+    out = orc.dequantize(6, block, 32)
+    for i in range(16):
+        assert out[i] == (i - 16.0) * 0.5
+        assert out[16 + i] == (15 - i) * 0.5
+
+
+def test_q5_1_preserves_unsigned_fifth_bit_and_minimum():
+    """src/weight/codec/ggml.rs:498-511"""
+    block = np.zeros(24, dtype=np.uint8)
+    block[:2] = np.frombuffer(np.float16(0.25).tobytes(), dtype=np.uint8)
+    block[2:4] = np.frombuffer(np.float16(-3.0).tobytes(), dtype=np.uint8)
+    block[4:8] = np.frombuffer(np.uint32(0xFFFF0000).tobytes(), dtype=np.uint8)
+    for i in range(16):
+        block[8 + i] = i | (i << 4)
+    out = orc.dequantize(7, block, 32)
+    for i, v in enumerate(out):
+        assert v == i * 0.25 - 3.0
+
+
+def test_decodes_q3_k_block_layout():
+    """src/weight/codec/ggml.rs:578-585"""
+    q3 = np.zeros(110, dtype=np.uint8)
+    q3[0], q3[32], q3[96], q3[104] = 1, 3, 1, 2
+    q3[108:] = [0x00, 0x3C]
+    assert orc.dequantize(11, q3, 256)[0] == 3.0
+
+
+def test_decodes_iq4_xs_non_zero():
+    """src/weight/codec/ggml.rs:616-625"""
+    block = np.zeros(136, dtype=np.uint8)
+    block[:2] = [0x00, 0x3C]
+    block[2:4] = [2, 0]
+    block[4] = 1
+    block[8] = 0xF0
+    out = orc.dequantize(23, block, 256)
+    assert out[0] == -127.0 and out[16] == 113.0
+
+
+def test_sigmoid_bias_uses_bias_for_selection_and_raw_for_weights():
+    """src/moe/routing.rs:234-256"""
+    ids, w = orc.route_bias_corrected_logits([0.0, 1.0, -1.0], [1.0, 0.0, 0.0], 2, 2.0, kind=1)
+    assert list(ids) == [0, 1]
+    raw = [0.5, 1.0 / (1.0 + np.exp(-1.0))]
+    np.testing.assert_allclose(w, [2.0 * raw[0] / sum(raw), 2.0 * raw[1] / sum(raw)], rtol=1e-6)
+    assert abs(float(w.sum()) - 2.0) < 1e-6
+
+
+def test_sqrt_softplus_bias_separates_selection_from_weight():
+    """src/moe/routing.rs:258-264"""
+    ids, w = orc.route_bias_corrected_logits([0.0, 2.0, 1.0], [2.0, 0.0, 0.0], 2, 1.5, kind=2)
+    assert list(ids) == [0, 1]
+    assert abs(float(w.sum()) - 1.5) < 1e-6
+    assert w[1] > w[0]

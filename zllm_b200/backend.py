@@ -351,15 +351,16 @@ class MoeExperts:
             pass
 
 
-def moe_route(ctx: B200Context, x: torch.Tensor, router: torch.Tensor, top_k: int, scaling_factor: float = 1.0, normalize_selected: bool = True, bias: Optional[torch.Tensor] = None):
-    """``moe_route_softmax_topk_device_f32`` (src/kernel/cuda/routing.rs:167): returns ``(ids [m, k] int32, weights [m, k] f32)`` on the device."""
+def moe_route(ctx: B200Context, x: torch.Tensor, router: torch.Tensor, top_k: int, scaling_factor: float = 1.0, normalize_selected: bool = True, bias: Optional[torch.Tensor] = None, scoring: int = ffi.ROUTE_SOFTMAX):
+    """``moe_route_softmax_topk_device_f32`` (src/kernel/cuda/routing.rs:167) and, with ``scoring``, the bias-corrected
+    routers of src/moe/routing.rs:43-81: returns ``(ids [m, k] int32, weights [m, k] f32)`` on the device."""
     x = x.contiguous()
     router = router.contiguous().float()
     m, hidden = x.shape
     experts = router.shape[0]
     ids = torch.empty((m, top_k), dtype=torch.int32, device=x.device)
     w = torch.empty((m, top_k), dtype=torch.float32, device=x.device)
-    ffi.call("zq_moe_route_softmax_topk", ctx.handle, _ptr(x), _dt(x), m, hidden, _ptr(router), _ptr(bias), experts, top_k, float(scaling_factor), int(normalize_selected), _ptr(ids), _ptr(w))
+    ffi.call("zq_moe_route_topk", ctx.handle, int(scoring), _ptr(x), _dt(x), m, hidden, _ptr(router), _ptr(bias), experts, top_k, float(scaling_factor), int(normalize_selected), _ptr(ids), _ptr(w))
     return ids, w
 
 

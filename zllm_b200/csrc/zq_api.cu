@@ -109,7 +109,7 @@ static int check_dtype(int dtype, const char *what, zq_error *err) {
 static int prepare_common(zq_ctx *ctx, uint32_t type, size_t nbytes, size_t rows, size_t cols, zq_weight **out, zq_error *err) {
     if (!ctx || !out) return set_error(err, ZQ_ERR_ARG, "weight prepare: null context or output");
     FormatInfo f = format_info(type);
-    if (!f.ggml_type) return set_error(err, ZQ_ERR_UNSUPPORTED, "GGUF tensor type %u is not supported (supported: 2, 8, 12, 13, 14, 20)", type);
+    if (!f.ggml_type) return set_error(err, ZQ_ERR_UNSUPPORTED, "GGUF tensor type %u is not supported (supported: 2, 6, 7, 8, 11, 12, 13, 14, 20, 23)", type);
     if (rows == 0 || cols == 0 || cols % f.block_elems) return set_error(err, ZQ_ERR_SHAPE, "GGUF type %u weight [%zu, %zu]: columns must be a positive multiple of %d", type, rows, cols, f.block_elems);
     size_t expected = rows * (cols / f.block_elems) * f.block_bytes;
     if (nbytes != expected) return set_error(err, ZQ_ERR_SHAPE, "GGUF type %u weight [%zu, %zu]: %zu bytes given, %zu expected", type, rows, cols, nbytes, expected);
@@ -121,6 +121,8 @@ static int prepare_common(zq_ctx *ctx, uint32_t type, size_t nbytes, size_t rows
     w->cols = cols;
     w->units_per_row = (cols + kUnitWeights - 1) / kUnitWeights;
     w->row_pitch = w->units_per_row * f.unit_bytes;
+    // block-32 types kept in GGUF order: a row is exactly its blocks (a last unit may be short; nothing reads past the columns)
+    if (type == ZQ_Q5_0 || type == ZQ_Q5_1) w->row_pitch = (cols / f.block_elems) * f.block_bytes;
     w->gguf_bytes = nbytes;
     *out = w;
     return ZQ_OK;
@@ -385,7 +387,7 @@ static int check_linear(zq_ctx *ctx, const zq_weight *w, const void *x, int x_dt
 int zq_linear(zq_ctx *ctx, const zq_weight *w, const void *dev_x, int x_dtype, size_t m, void *dev_y, int y_dtype, const void *dev_residual, zq_error *err) {
     int rc = check_linear(ctx, w, dev_x, x_dtype, m, dev_y, y_dtype, err);
     if (rc) return rc;
-    if (is_operand_pass_only(w->type) && m <= 8) return launch_gemv_kq(ctx, w, dev_x, x_dtype, m, dev_y, y_dtype, dev_residual, err);
+    if (has_kq_decode(w->type) && m <= 8) return launch_gemv_kq(ctx, w, dev_x, x_dtype, m, dev_y, y_dtype, dev_residual, err);
     if (m <= 16 && !is_operand_pass_only(w->type)) return launch_gemv(ctx, w, nullptr, dev_x, x_dtype, m, dev_y, y_dtype, dev_residual, err);
     return launch_gemm(ctx, w, nullptr, dev_x, x_dtype, m, dev_y, y_dtype, dev_residual, err);
 }

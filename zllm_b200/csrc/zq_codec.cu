@@ -86,6 +86,38 @@ __device__ __forceinline__ float decode_unit_element(uint32_t type, const uint8_
         const int8_t scale = (int8_t)unit[192 + half * 8 + (index >> 4) + 2 * quarter];
         return __fmul_rn(__fmul_rn(d, (float)scale), (float)q);
     }
+    if (type == ZQ_Q5_0 || type == ZQ_Q5_1) {  // src/weight/codec/ggml.rs:111-130; the unit is 8 GGUF blocks in file order
+        const int e = i & 31;
+        const uint8_t *block = unit + (i >> 5) * (type == ZQ_Q5_0 ? 22 : 24);
+        const float d = __half2float(*reinterpret_cast<const __half *>(block));
+        const int hoff = type == ZQ_Q5_0 ? 2 : 4;
+        const uint32_t high = (uint32_t)block[hoff] | ((uint32_t)block[hoff + 1] << 8) | ((uint32_t)block[hoff + 2] << 16) | ((uint32_t)block[hoff + 3] << 24);
+        const uint8_t packed = block[hoff + 4 + (e & 15)];
+        const int q5 = (int)((e < 16 ? (packed & 15) : (packed >> 4)) | (((high >> e) & 1u) << 4));
+        if (type == ZQ_Q5_0) return __fmul_rn(d, (float)(q5 - 16));
+        return __fadd_rn(__fmul_rn(d, (float)q5), __half2float(*reinterpret_cast<const __half *>(block + 2)));
+    }
+    if (type == ZQ_IQ4_XS) {  // src/weight/codec/ggml.rs:246-261
+        const float d = __half2float(*reinterpret_cast<const __half *>(unit));
+        const uint32_t scales_h = (uint32_t)unit[2] | ((uint32_t)unit[3] << 8);
+        const int ib = i >> 5, j = i & 31;
+        const int ls = (int)(((unit[4 + ib / 2] >> (4 * (ib & 1))) & 0x0f) | (((scales_h >> (2 * ib)) & 3u) << 4));
+        const float dl = __fmul_rn(d, __fsub_rn((float)ls, 32.0f));
+        const uint8_t qb = unit[8 + ib * 16 + (j & 15)];
+        return __fmul_rn(dl, (float)kIq4nlValues[j < 16 ? (qb & 0x0f) : (qb >> 4)]);
+    }
+    if (type == ZQ_Q3_K) {  // src/weight/codec/ggml.rs:384-406
+        const uint8_t *hmask = unit, *quants = unit + 32, *scales = unit + 96;
+        const float d = __half2float(*reinterpret_cast<const __half *>(unit + 108));
+        const int group = i >> 4, index = i & 15;
+        const int low = group < 8 ? (scales[group] & 0x0f) : (scales[group - 8] >> 4);
+        const int high = (scales[8 + (group & 3)] >> (2 * (group >> 2))) & 3;
+        const int scale = (low | (high << 4)) - 32;
+        const int half = group >> 3, pair = group & 7;
+        const int low_bits = (quants[half * 32 + (pair & 1) * 16 + index] >> (2 * (pair >> 1))) & 3;
+        const int quant = low_bits - ((hmask[(pair & 1) * 16 + index] & (1u << (group >> 1))) ? 0 : 4);
+        return __fmul_rn(__fmul_rn(d, (float)scale), (float)quant);
+    }
     uint8_t q = unit[unit_quant_offset(type, i)];
     if (type == ZQ_Q4_K) {
         const __half *hd = reinterpret_cast<const __half *>(unit);

@@ -53,6 +53,10 @@ __host__ __device__ inline FormatInfo format_info(uint32_t t) {
     case ZQ_Q4_K: return {ZQ_Q4_K, 256, 144, 144};
     case ZQ_Q5_K: return {ZQ_Q5_K, 256, 176, 176};
     case ZQ_Q6_K: return {ZQ_Q6_K, 256, 210, 210};
+    case ZQ_Q5_0: return {ZQ_Q5_0, 32, 22, 176};   // unit = 8 consecutive GGUF blocks
+    case ZQ_Q5_1: return {ZQ_Q5_1, 32, 24, 192};
+    case ZQ_Q3_K: return {ZQ_Q3_K, 256, 110, 110};
+    case ZQ_IQ4_XS: return {ZQ_IQ4_XS, 256, 136, 136};
     default: return {0, 0, 0, 0};
     }
 }
@@ -60,7 +64,11 @@ __host__ __device__ inline FormatInfo format_info(uint32_t t) {
 // Q5_K and Q6_K (src/weight/codec/ggml.rs:425-469): resident in their GGUF layout, dequantised bit-exactly; plain
 // projections of up to 8 activation rows run a CUDA-core decode kernel (zq_gemv_kq.cu), everything else (more rows,
 // gated pairs) the f16 operand pass + tensor-core GEMM.  No integer-MMA kernel, tensor maps or encoder for them.
-__host__ __device__ inline bool is_operand_pass_only(uint32_t type) { return type == ZQ_Q5_K || type == ZQ_Q6_K; }
+__host__ __device__ inline bool is_operand_pass_only(uint32_t type) { return type == ZQ_Q5_K || type == ZQ_Q6_K || type == ZQ_Q5_0 || type == ZQ_Q5_1 || type == ZQ_Q3_K || type == ZQ_IQ4_XS; }
+// Of those, the two with a decode kernel of their own (zq_gemv_kq.cu).  Q5_0, Q5_1, Q3_K and IQ4_XS
+// (src/weight/codec/ggml.rs:111-130, 246-261, 384-406) are resident in GGUF layout, dequantise bit-exactly, and run every
+// projection through the f16 operand pass and the tensor-core GEMM.
+__host__ __device__ inline bool has_kq_decode(uint32_t type) { return type == ZQ_Q5_K || type == ZQ_Q6_K; }
 
 // Byte offset, inside a resident unit, of the quant byte that holds element `i` (0..255) of the unit.
 __host__ __device__ inline int unit_quant_offset(uint32_t type, int i) {

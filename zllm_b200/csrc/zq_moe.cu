@@ -28,9 +28,57 @@ constexpr int kRouterThreads = 256;
 
 // Softmax top-k of one token from its logits in shared memory (the logits are consumed): repeated arg-max with ties
 // to the lower expert id; one warp per token.
+// Raw score of the bias-corrected routers (src/moe/routing.rs:43-81): sigmoid, or sqrt(softplus) in its stable form.
+__device__ __forceinline__ float router_raw_score(float logit, int scoring) {
+    if (scoring == ZQ_ROUTE_SIGMOID_BIAS) return 1.0f / (1.0f + expf(-logit));
+    const float softplus = logit > 0.0f ? logit + log1pf(expf(-logit)) : log1pf(expf(logit));
+    return sqrtf(softplus);
+}
+
+// Bias-corrected top-k (route_bias_corrected_logits, src/moe/routing.rs:45-67): every expert has a raw score; the bias
+// takes part in the SELECTION only (raw + bias, descending, ties to the lower id); the selected experts' raw scores are
+// normalised to sum 1 and scaled.  `l` holds the logits (left untouched); one warp per token; each lane owns experts
+// lane, lane + 32, ... and remembers the ones already taken in a bit mask (num_experts <= 1024).
+__device__ __forceinline__ void router_select_bias(const float *l, const float *bias, int scoring, int lane, int num_experts, int top_k, float scaling, uint32_t *ids_out, float *weights_out, uint32_t *status) {
+    uint32_t taken = 0;
+    float sel_raw = 0.f, sum_raw = 0.f;
+    uint32_t sel_id = 0;
+    for (int slot = 0; slot < top_k; ++slot) {
+        float best = -INFINITY;
+        int best_e = 0x7fffffff;
+        for (int e = lane, i = 0; e < num_experts; e += 32, ++i) {
+            if ((taken >> i) & 1u) continue;
+            const float v = router_raw_score(l[e], scoring) + (bias ? bias[e] : 0.f);
+            if (v > best || (v == best && e < best_e)) { best = v; best_e = e; }
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (ov > best || (ov == best && oe < best_e)) { best = ov; best_e = oe; }
+        }
+        if (best_e < 0 || best_e >= num_experts) {  // warp-uniform: nothing comparable left (NaN scores): a valid id, and a report
+            best_e = slot;
+            if (lane == 0) atomicMax(status, (uint32_t)kStatusBadIndex);
+        }
+        if ((best_e & 31) == lane) taken |= 1u << (best_e >> 5);
+        const float raw = router_raw_score(l[best_e], scoring);
+        if (lane == slot) { sel_raw = raw; sel_id = (uint32_t)best_e; }
+        sum_raw += raw;
+    }
+    if (lane < top_k) {
+        ids_out[lane] = sel_id;
+        weights_out[lane] = sel_raw / sum_raw * scaling;
+    }
+}
+
 // A row whose logits are all NaN (NaN in the activations, the router matrix or the bias) has no arg-max: such a slot
 // takes expert id `slot` (always a valid id), the status word records it, and the weights come out NaN.
-__device__ __forceinline__ void router_select(float *l, int lane, int num_experts, int top_k, float scaling, int normalize_selected, uint32_t *ids_out, float *weights_out, uint32_t *status) {
+__device__ __forceinline__ void router_select(float *l, int lane, int num_experts, int top_k, float scaling, int normalize_selected, uint32_t *ids_out, float *weights_out, uint32_t *status, int scoring = ZQ_ROUTE_SOFTMAX,
+                                              const float *bias = nullptr) {
+    if (scoring != ZQ_ROUTE_SOFTMAX) {
+        router_select_bias(l, bias, scoring, lane, num_experts, top_k, scaling, ids_out, weights_out, status);
+        return;
+    }
     float maximum = -INFINITY;
     for (int e = lane; e < num_experts; e += 32) maximum = fmaxf(maximum, l[e]);
     for (int o = 16; o > 0; o >>= 1) maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, o));
@@ -75,7 +123,7 @@ __device__ __forceinline__ void router_select(float *l, int lane, int num_expert
 // with several (few tokens: the expert blocks are what fills the machine) the logits go to `logits_g` and
 // router_select_kernel finishes.
 __global__ void __launch_bounds__(kRouterThreads) router_topk_kernel(const void *__restrict__ x, int x_dtype, int m, int hidden, const float *__restrict__ router, const float *__restrict__ bias, int num_experts, int top_k,
-                                                                      float scaling, int normalize_selected, uint32_t *__restrict__ ids, float *__restrict__ weights, int experts_per_cta, float *__restrict__ logits_g, uint32_t *status) {
+                                                                      float scaling, int normalize_selected, uint32_t *__restrict__ ids, float *__restrict__ weights, int experts_per_cta, float *__restrict__ logits_g, uint32_t *status, int scoring) {
     extern __shared__ float rsm[];
     float *xs = rsm;                                 // [kRouterTokens][hidden]
     float *logits = rsm + (size_t)kRouterTokens * hidden;  // [kRouterTokens][num_experts]
@@ -137,7 +185,7 @@ __global__ void __launch_bounds__(kRouterThreads) router_topk_kernel(const void 
             float v = acc[t];
             for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
             if (lane == 0) {
-                v += bias ? bias[e] : 0.f;
+                if (scoring == ZQ_ROUTE_SOFTMAX) v += bias ? bias[e] : 0.f;  // the other routers use the bias for the selection only
                 if (logits_g) {
                     if (tok0 + t < m) logits_g[(size_t)(tok0 + t) * num_experts + e] = v;
                 } else {
@@ -149,7 +197,7 @@ __global__ void __launch_bounds__(kRouterThreads) router_topk_kernel(const void 
     if (logits_g) return;
     __syncthreads();
     if (warp < kRouterTokens && tok0 + warp < m)
-        router_select(logits + warp * num_experts, lane, num_experts, top_k, scaling, normalize_selected, ids + (size_t)(tok0 + warp) * top_k, weights + (size_t)(tok0 + warp) * top_k, status);
+        router_select(logits + warp * num_experts, lane, num_experts, top_k, scaling, normalize_selected, ids + (size_t)(tok0 + warp) * top_k, weights + (size_t)(tok0 + warp) * top_k, status, scoring, bias);
 }
 
 // Router logits on the tensor cores for prefill-sized batches.  f16 operands alone would move logits by ~1e-3 and
@@ -172,15 +220,15 @@ __global__ void split_f16_kernel(const void *__restrict__ src, int dtype, size_t
 
 // Second half of the split router: one warp per token, logits from global memory.
 __global__ void __launch_bounds__(kRouterThreads) router_select_kernel(const float *__restrict__ logits_g, const float *__restrict__ bias, int m, int num_experts, int top_k, float scaling, int normalize_selected,
-                                                                        uint32_t *__restrict__ ids, float *__restrict__ weights, uint32_t *status) {
+                                                                        uint32_t *__restrict__ ids, float *__restrict__ weights, uint32_t *status, int scoring) {
     extern __shared__ float rsm[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tok = blockIdx.x * (kRouterThreads / 32) + warp;
     if (tok >= m) return;
     float *l = rsm + warp * num_experts;
-    for (int e = lane; e < num_experts; e += 32) l[e] = logits_g[(size_t)tok * num_experts + e] + (bias ? bias[e] : 0.f);
+    for (int e = lane; e < num_experts; e += 32) l[e] = logits_g[(size_t)tok * num_experts + e] + ((bias && scoring == ZQ_ROUTE_SOFTMAX) ? bias[e] : 0.f);
     __syncwarp();
-    router_select(l, lane, num_experts, top_k, scaling, normalize_selected, ids + (size_t)tok * top_k, weights + (size_t)tok * top_k, status);
+    router_select(l, lane, num_experts, top_k, scaling, normalize_selected, ids + (size_t)tok * top_k, weights + (size_t)tok * top_k, status, scoring, bias);
 }
 
 __global__ void gather_rows_kernel(const void *__restrict__ x, int dtype, const uint32_t *__restrict__ tokens, size_t n_rows, int hidden, void *__restrict__ out) {
@@ -239,7 +287,13 @@ extern "C" {
 
 int zq_moe_route_softmax_topk(zq_ctx *ctx, const void *dev_x, int x_dtype, size_t m, size_t hidden, const float *dev_router_f32, const float *dev_bias_f32, size_t num_experts, size_t top_k, float scaling_factor, int normalize_selected,
                               uint32_t *dev_ids, float *dev_weights, zq_error *err) {
-    if (!ctx || !dev_x || !dev_router_f32 || !dev_ids || !dev_weights) return set_error(err, ZQ_ERR_ARG, "zq_moe_route_softmax_topk: null argument");
+    return zq_moe_route_topk(ctx, ZQ_ROUTE_SOFTMAX, dev_x, x_dtype, m, hidden, dev_router_f32, dev_bias_f32, num_experts, top_k, scaling_factor, normalize_selected, dev_ids, dev_weights, err);
+}
+
+int zq_moe_route_topk(zq_ctx *ctx, int scoring, const void *dev_x, int x_dtype, size_t m, size_t hidden, const float *dev_router_f32, const float *dev_bias_f32, size_t num_experts, size_t top_k, float scaling_factor,
+                      int normalize_selected, uint32_t *dev_ids, float *dev_weights, zq_error *err) {
+    if (!ctx || !dev_x || !dev_router_f32 || !dev_ids || !dev_weights) return set_error(err, ZQ_ERR_ARG, "zq_moe_route_topk: null argument");
+    if (scoring != ZQ_ROUTE_SOFTMAX && scoring != ZQ_ROUTE_SIGMOID_BIAS && scoring != ZQ_ROUTE_SQRT_SOFTPLUS_BIAS) return set_error(err, ZQ_ERR_ARG, "zq_moe_route_topk: unknown scoring %d", scoring);
     // same limits as the reference's device router (src/kernel/cuda/routing.rs:177): experts <= 1024, 0 < top_k <= experts
     if (num_experts == 0 || num_experts > 1024 || top_k == 0 || top_k > num_experts || top_k > 32) return set_error(err, ZQ_ERR_SHAPE, "softmax router: experts=%zu top_k=%zu outside the supported range (experts <= 1024, top_k <= 32)", num_experts, top_k);
     if (!(scaling_factor == scaling_factor) || scaling_factor > 3.0e38f || scaling_factor < -3.0e38f) return set_error(err, ZQ_ERR_ARG, "softmax router: scaling factor is not finite");
@@ -280,7 +334,7 @@ int zq_moe_route_softmax_topk(zq_ctx *ctx, const void *dev_x, int x_dtype, size_
         if (rc) return rc;
         const unsigned sel_grid = (unsigned)((m + kRouterThreads / 32 - 1) / (kRouterThreads / 32));
         router_select_kernel<<<sel_grid, kRouterThreads, (kRouterThreads / 32) * num_experts * sizeof(float), ctx->stream>>>(logits_g, dev_bias_f32, (int)m, (int)num_experts, (int)top_k, scaling_factor, normalize_selected, dev_ids,
-                                                                                                                            dev_weights, ctx->status_dev);
+                                                                                                                            dev_weights, ctx->status_dev, scoring);
         ctx->launches++;
         ZQ_CUDA_CHECK(cudaGetLastError(), err);
         return ZQ_OK;
@@ -290,17 +344,17 @@ int zq_moe_route_softmax_topk(zq_ctx *ctx, const void *dev_x, int x_dtype, size_
         if (rc) return rc;
         float *logits_g = reinterpret_cast<float *>(ctx->moe_ws);
         router_topk_kernel<<<dim3(grid, (unsigned)blocks_y), kRouterThreads, smem, ctx->stream>>>(dev_x, x_dtype, (int)m, (int)hidden, dev_router_f32, dev_bias_f32, (int)num_experts, (int)top_k, scaling_factor, normalize_selected,
-                                                                                                   dev_ids, dev_weights, (int)per_cta, logits_g, ctx->status_dev);
+                                                                                                   dev_ids, dev_weights, (int)per_cta, logits_g, ctx->status_dev, scoring);
         ctx->launches++;
         ZQ_CUDA_CHECK(cudaGetLastError(), err);
         const unsigned sel_grid = (unsigned)((m + kRouterThreads / 32 - 1) / (kRouterThreads / 32));
-        router_select_kernel<<<sel_grid, kRouterThreads, (kRouterThreads / 32) * num_experts * sizeof(float), ctx->stream>>>(logits_g, nullptr, (int)m, (int)num_experts, (int)top_k, scaling_factor, normalize_selected, dev_ids, dev_weights, ctx->status_dev);
+        router_select_kernel<<<sel_grid, kRouterThreads, (kRouterThreads / 32) * num_experts * sizeof(float), ctx->stream>>>(logits_g, scoring == ZQ_ROUTE_SOFTMAX ? nullptr : dev_bias_f32, (int)m, (int)num_experts, (int)top_k, scaling_factor, normalize_selected, dev_ids, dev_weights, ctx->status_dev, scoring);
         ctx->launches++;
         ZQ_CUDA_CHECK(cudaGetLastError(), err);
         return ZQ_OK;
     }
     router_topk_kernel<<<grid, kRouterThreads, smem, ctx->stream>>>(dev_x, x_dtype, (int)m, (int)hidden, dev_router_f32, dev_bias_f32, (int)num_experts, (int)top_k, scaling_factor, normalize_selected, dev_ids, dev_weights,
-                                                                    (int)num_experts, nullptr, ctx->status_dev);
+                                                                    (int)num_experts, nullptr, ctx->status_dev, scoring);
     ctx->launches++;
     ZQ_CUDA_CHECK(cudaGetLastError(), err);
     return ZQ_OK;

@@ -12,10 +12,12 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "lib", "libzq_b200.so")
 
 Q4_0, Q8_0, Q4_K, Q5_K, Q6_K, IQ4_NL = 2, 8, 12, 13, 14, 20
+Q5_0, Q5_1, Q3_K, IQ4_XS = 6, 7, 11, 23
 F32, F16, BF16 = 0, 1, 2
 JOB_ROW_PARALLEL = 1
+ROUTE_SOFTMAX, ROUTE_SIGMOID_BIAS, ROUTE_SQRT_SOFTPLUS_BIAS = 0, 1, 2
 DIST_HANDLE_BYTES = 80
-BLOCK = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210), IQ4_NL: (32, 18)}
+BLOCK = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210), IQ4_NL: (32, 18), Q5_0: (32, 22), Q5_1: (32, 24), Q3_K: (256, 110), IQ4_XS: (256, 136)}
 
 
 class ZqError(C.Structure):
@@ -78,6 +80,7 @@ PROTOTYPES = {
     "zq_batch_begin": (_i, [_vp, _err]),
     "zq_batch_finish": (_i, [_vp, _err]),
     "zq_moe_route_softmax_topk": (_i, [_vp, _vp, _i, _sz, _sz, _vp, _vp, _sz, _sz, _f, _i, _vp, _vp, _err]),
+    "zq_moe_route_topk": (_i, [_vp, _i, _vp, _i, _sz, _sz, _vp, _vp, _sz, _sz, _f, _i, _vp, _vp, _err]),
     "zq_moe_experts_create": (_i, [_vp, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), _sz, C.POINTER(_vp), _err]),
     "zq_moe_experts_destroy": (None, [_vp]),
     "zq_moe_ep_export": (_i, [_vp, _sz, _sz, _sz, _sz, _i, _vp, _err]),
