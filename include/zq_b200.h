@@ -206,6 +206,31 @@ void zq_moe_experts_destroy(zq_moe_experts *experts);
 #define ZQ_MOE_NO_ROUTE 0xFFFFFFFFu /* an expert id that means "no route in this place": no expert runs, nothing is added */
 int zq_moe_forward(zq_ctx *ctx, const zq_moe_experts *experts, const zq_weight *shared_gate, const zq_weight *shared_up, const zq_weight *shared_down, const void *dev_x, int x_dtype, size_t m, const uint32_t *dev_ids, const float *dev_weights, size_t top_k, void *dev_y, int y_dtype, const void *dev_residual, zq_error *err);
 
+/* ---- GGUF container: GgufReader (src/weight/container/gguf.rs:332-566).  open / parse_shard (:364-412, :663-725): GGUF
+ * v3 header, metadata, tensor directory, data offset from general.alignment, every tensor inside its file, split files
+ * "<prefix>-00001-of-0000N.gguf" opened together (:727-750).  Metadata scalars and strings can be read; arrays only
+ * report their length.  Errors (not a GGUF file, another version, unknown type, a tensor beyond the file, duplicate
+ * names, split counts that do not add up) come back as codes with a message. */
+typedef struct zq_gguf zq_gguf;
+int zq_gguf_open(const char *path, zq_gguf **out, zq_error *err);
+void zq_gguf_close(zq_gguf *file);
+size_t zq_gguf_tensor_count(const zq_gguf *file);
+int zq_gguf_tensor_name(const zq_gguf *file, size_t index, char *out, size_t capacity, zq_error *err);
+/* dims4: the GGUF dimension order (a matrix is [columns, rows]; an expert tensor [columns, rows, count]), padded with 1. */
+int zq_gguf_tensor_info(const zq_gguf *file, const char *name, uint32_t *type, uint32_t *n_dims, uint64_t *dims4, uint64_t *nbytes, zq_error *err);
+int zq_gguf_metadata_u64(const zq_gguf *file, const char *key, uint64_t *out, zq_error *err);
+int zq_gguf_metadata_f64(const zq_gguf *file, const char *key, double *out, zq_error *err);
+int zq_gguf_metadata_str(const zq_gguf *file, const char *key, char *out, size_t capacity, zq_error *err);
+/* read_matrix (:506-514) / read_matrix_slice (:516-534) + prepare_weight: the tensor's bytes go from the file to a resident
+ * weight.  The slice form takes matrix `index` of a [columns, rows, count] tensor: one expert of an expert tensor. */
+int zq_gguf_load_matrix(zq_ctx *ctx, const zq_gguf *file, const char *name, zq_weight **out, zq_error *err);
+int zq_gguf_load_matrix_slice(zq_ctx *ctx, const zq_gguf *file, const char *name, size_t index, zq_weight **out, zq_error *err);
+/* embedding_rows (:618-629) is zq_gather_rows on the loaded embedding matrix.  The LM head of a greedy decode step:
+ * logits = head x (any row count) and the arg-max of every row on the device (ties to the lower token id, NaN never
+ * chosen), so the logits do not travel to the host; zq_argmax_rows is the second half on its own. */
+int zq_argmax_rows(zq_ctx *ctx, const void *dev_x, int dtype, size_t rows, size_t cols, uint32_t *dev_ids, zq_error *err);
+int zq_lm_head_argmax(zq_ctx *ctx, const zq_weight *head, const void *dev_x, int x_dtype, size_t m, uint32_t *dev_ids, zq_error *err);
+
 /* ---- expert parallelism over the GPUs of one node.  The reference keeps every expert on (or cached by) one device
  * (src/backend/cuda/expert.rs:284-570) and has no counterpart; the arithmetic of an expert and the ascending-expert order
  * of a token's sum are its own (src/kernel/cpu/moe.rs:122-138, src/backend/cpu/moe.rs:107-141).  Rank r of the peer group

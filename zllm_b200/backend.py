@@ -328,6 +328,76 @@ class B200Context:
         return y_host
 
 
+class GgufFile:
+    """``GgufReader`` (src/weight/container/gguf.rs:332-566): header, metadata and tensor directory of a GGUF v3 file (or
+    of a set of standard split files); matrices and expert slices go straight to resident weights."""
+
+    def __init__(self, path: str):
+        handle = C.c_void_p()
+        ffi.call("zq_gguf_open", str(path).encode(), C.byref(handle))
+        self.handle = handle
+
+    def close(self):
+        if self.handle:
+            ffi.load().zq_gguf_close(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def tensor_names(self):
+        out = []
+        buf = C.create_string_buffer(512)
+        for i in range(ffi.load().zq_gguf_tensor_count(self.handle)):
+            ffi.call("zq_gguf_tensor_name", self.handle, i, buf, len(buf))
+            out.append(buf.value.decode())
+        return out
+
+    def tensor_info(self, name: str):
+        """``(type, dims in GGUF order, bytes)``"""
+        t, nd, nb = C.c_uint32(), C.c_uint32(), C.c_uint64()
+        dims = (C.c_uint64 * 4)()
+        ffi.call("zq_gguf_tensor_info", self.handle, name.encode(), C.byref(t), C.byref(nd), dims, C.byref(nb))
+        return t.value, [int(dims[i]) for i in range(nd.value)], int(nb.value)
+
+    def metadata_u64(self, key: str) -> int:
+        v = C.c_uint64()
+        ffi.call("zq_gguf_metadata_u64", self.handle, key.encode(), C.byref(v))
+        return int(v.value)
+
+    def metadata_f64(self, key: str) -> float:
+        v = C.c_double()
+        ffi.call("zq_gguf_metadata_f64", self.handle, key.encode(), C.byref(v))
+        return float(v.value)
+
+    def metadata_str(self, key: str) -> str:
+        buf = C.create_string_buffer(4096)
+        ffi.call("zq_gguf_metadata_str", self.handle, key.encode(), buf, len(buf))
+        return buf.value.decode()
+
+    def load_matrix(self, ctx: "B200Context", name: str) -> Weight:
+        out = C.c_void_p()
+        ffi.call("zq_gguf_load_matrix", ctx.handle, self.handle, name.encode(), C.byref(out))
+        return Weight(ctx, out)
+
+    def load_matrix_slice(self, ctx: "B200Context", name: str, index: int) -> Weight:
+        out = C.c_void_p()
+        ffi.call("zq_gguf_load_matrix_slice", ctx.handle, self.handle, name.encode(), int(index), C.byref(out))
+        return Weight(ctx, out)
+
+
+def lm_head_argmax(ctx: B200Context, head: Weight, x: torch.Tensor) -> torch.Tensor:
+    """Greedy token ids of an LM-head projection, computed on the device (``zq_lm_head_argmax``)."""
+    x = x.contiguous()
+    m = x.numel() // head.cols
+    ids = torch.empty(m, dtype=torch.int32, device=x.device)
+    ffi.call("zq_lm_head_argmax", ctx.handle, head.handle, _ptr(x), _dt(x), m, _ptr(ids))
+    return ids
+
+
 class MoeExperts:
     """Resident expert table (replaces ``CudaMoeState``'s cache when every expert fits in HBM,
     src/backend/cuda/expert.rs:284-570).  Keeps the weights alive for as long as the table."""

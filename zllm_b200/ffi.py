@@ -83,6 +83,18 @@ PROTOTYPES = {
     "zq_moe_route_topk": (_i, [_vp, _i, _vp, _i, _sz, _sz, _vp, _vp, _sz, _sz, _f, _i, _vp, _vp, _err]),
     "zq_moe_experts_create": (_i, [_vp, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), _sz, C.POINTER(_vp), _err]),
     "zq_moe_experts_destroy": (None, [_vp]),
+    "zq_gguf_open": (_i, [C.c_char_p, C.POINTER(_vp), _err]),
+    "zq_gguf_close": (None, [_vp]),
+    "zq_gguf_tensor_count": (_sz, [_vp]),
+    "zq_gguf_tensor_name": (_i, [_vp, _sz, C.c_char_p, _sz, _err]),
+    "zq_gguf_tensor_info": (_i, [_vp, C.c_char_p, C.POINTER(_u32), C.POINTER(_u32), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), _err]),
+    "zq_gguf_metadata_u64": (_i, [_vp, C.c_char_p, C.POINTER(C.c_uint64), _err]),
+    "zq_gguf_metadata_f64": (_i, [_vp, C.c_char_p, C.POINTER(C.c_double), _err]),
+    "zq_gguf_metadata_str": (_i, [_vp, C.c_char_p, C.c_char_p, _sz, _err]),
+    "zq_gguf_load_matrix": (_i, [_vp, _vp, C.c_char_p, C.POINTER(_vp), _err]),
+    "zq_gguf_load_matrix_slice": (_i, [_vp, _vp, C.c_char_p, _sz, C.POINTER(_vp), _err]),
+    "zq_argmax_rows": (_i, [_vp, _vp, _i, _sz, _sz, _vp, _err]),
+    "zq_lm_head_argmax": (_i, [_vp, _vp, _vp, _i, _sz, _vp, _err]),
     "zq_moe_ep_export": (_i, [_vp, _sz, _sz, _sz, _sz, _i, _vp, _err]),
     "zq_moe_ep_init": (_i, [_vp, _vp, _err]),
     "zq_moe_ep_shutdown": (None, [_vp]),
