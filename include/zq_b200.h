@@ -161,8 +161,10 @@ int zq_gated_mlp(zq_ctx *ctx, const zq_weight *gate, const zq_weight *up, const 
  * scratch (partial tiles and arrival counters of the split-tile fix-up) lives in a fixed device array inside the
  * library, about 2.6 MB per GPU, held from library load until process exit.  Limits: at most 8 activation rows per
  * call, weights of at most 524 288 rows, devices of at most 160 SMs; anything beyond is rejected with an error.
- * The first call on a device looks up the array's device address (no allocation) and should be made before any
- * stream capture.  All calls on a device share the array: calls that overlap on the GPU (two streams, two contexts)
+ * The first call on a device looks up the array's device address (no allocation).  Results equal zq_linear's bit
+ * for bit for 1..4 rows; 5..8 rows of Q4_K / Q4_0 / Q8_0 run on the f16-limb kernel rather than zq_linear's
+ * integer-MMA one (whose activation workspace may have to grow) and agree to f32 rounding.  All calls on a device
+ * share the array: calls that overlap on the GPU (two streams, two contexts)
  * race; calls ordered on one stream do not.  Inputs, outputs and the prepared weight are the caller's, as for
  * zq_linear. */
 int zq_linear_noalloc(zq_ctx *ctx, const zq_weight *w, const void *dev_x, int x_dtype, size_t m, void *dev_y, int y_dtype, zq_error *err);
@@ -194,6 +196,15 @@ int zq_moe_route_softmax_topk(zq_ctx *ctx, const void *dev_x, int x_dtype, size_
 enum { ZQ_ROUTE_SOFTMAX = 0, ZQ_ROUTE_SIGMOID_BIAS = 1, ZQ_ROUTE_SQRT_SOFTPLUS_BIAS = 2 };
 int zq_moe_route_topk(zq_ctx *ctx, int scoring, const void *dev_x, int x_dtype, size_t m, size_t hidden, const float *dev_router_f32, const float *dev_bias_f32, size_t num_experts, size_t top_k, float scaling_factor,
                       int normalize_selected, uint32_t *dev_ids, float *dev_weights, zq_error *err);
+/* The gather / scatter halves of the MoE trait on their own, for callers that orchestrate experts themselves
+ * (Backend::moe_gather_rows / moe_scatter_add_rows, src/backend/mod.rs:1657-1662; kernels gather_rows_f16 and
+ * scatter_add_rows_f32, src/kernel/cuda/routing.rs:112-125; prefill_expert_batch callers, src/moe/prefill.rs:291-327):
+ *   gather       out[i] = x[row_ids[i]]                          (rows in x's dtype; a row must be a multiple of 16 bytes)
+ *   scatter-add  out_f32[row_ids[i]] += weights[i] * rows[i]     (weights may be NULL = 1; the accumulator is f32
+ *                [out_rows, hidden], zeroed by the caller = moe_zeros; atomic adds as in the reference)
+ * Row ids out of range are skipped and reported by zq_ctx_sync. */
+int zq_moe_gather_rows(zq_ctx *ctx, const void *dev_x, int dtype, size_t x_rows, size_t hidden, const uint32_t *dev_row_ids, size_t n_rows, void *dev_out, zq_error *err);
+int zq_moe_scatter_add_rows(zq_ctx *ctx, const void *dev_rows, int dtype, const uint32_t *dev_row_ids, const float *dev_weights, size_t n_rows, size_t hidden, float *dev_out_f32, size_t out_rows, zq_error *err);
 /* The resident expert table that replaces CudaMoeState's LRU/arena cache (src/backend/cuda/expert.rs:284-570)
  * when every expert fits in HBM.  gate/up: [intermediate, hidden]; down: [hidden, intermediate].  The table
  * borrows the weights; release them after zq_moe_experts_destroy. */

@@ -166,3 +166,36 @@ def test_moe_forward_rejects_bad_expert_ids():
     with pytest.raises(ffi.ZqFailure):
         c.sync()
     c.sync()  # reported once, then clear
+
+
+def test_gather_and_scatter_add_rows_on_their_own():
+    """Backend::moe_gather_rows / moe_scatter_add_rows (src/backend/mod.rs:1657-1662) as exported entries: an expert's
+    tokens are gathered, its outputs are added into an f32 accumulator with their route weights
+    (src/moe/routing.rs:180-213), row ids out of range are skipped and reported."""
+    from zllm_b200 import ffi
+    from zllm_b200.backend import moe_gather_rows, moe_scatter_add_rows
+
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((20, 64)).astype(np.float32)
+    ids = np.array([19, 0, 7, 3], dtype=np.int32)
+    for dtype in (torch.float32, torch.float16, torch.bfloat16):
+        xd = torch.from_numpy(x).cuda().to(dtype)
+        got = moe_gather_rows(ctx(), xd, torch.from_numpy(ids))
+        ctx().sync()
+        assert torch.equal(got.cpu(), xd.cpu()[ids.astype(np.int64)])
+    acc = torch.zeros((20, 64), dtype=torch.float32, device="cuda")
+    rows = rng.standard_normal((4, 64)).astype(np.float32)
+    w = rng.random(4).astype(np.float32)
+    moe_scatter_add_rows(ctx(), acc, torch.from_numpy(rows).cuda().to(torch.float16), torch.from_numpy(ids), torch.from_numpy(w).cuda())
+    moe_scatter_add_rows(ctx(), acc, torch.from_numpy(rows).cuda().to(torch.float16), torch.from_numpy(ids), torch.from_numpy(w).cuda())
+    ctx().sync()
+    want = np.zeros((20, 64), dtype=np.float32)
+    r16 = rows.astype(np.float16).astype(np.float32)
+    for _ in range(2):
+        for i, t in enumerate(ids):
+            want[t] += r16[i] * w[i]
+    np.testing.assert_allclose(acc.cpu().numpy(), want, rtol=1e-6, atol=1e-7)
+    moe_scatter_add_rows(ctx(), acc, torch.from_numpy(rows).cuda(), torch.tensor([0, 1, 2, 99], dtype=torch.int32), None)
+    with pytest.raises(ffi.ZqFailure):
+        ctx().sync()
+    ctx().sync()

@@ -46,6 +46,40 @@ def test_noalloc_matches_regular_linear_on_consecutive_calls(tensor_type, rows, 
     assert np.array_equal(got2.view(np.uint32), want2.view(np.uint32))
 
 
+@pytest.mark.parametrize("m", [1, 4, 5, 8])
+@pytest.mark.parametrize("tensor_type", [H.Q4_K, H.Q8_0, H.IQ4_NL])
+def test_noalloc_with_default_options(tensor_type, m):
+    """The kernels a caller gets without any option set: equal to zq_linear bit for bit for 1..4 rows (and for every
+    row count of IQ4_NL, which both entries run on the f16-limb kernel), within f32 rounding for 5..8 rows of the
+    integer-MMA types; against the CPU oracle at the decode path's bound; and the device's free memory does not move."""
+    from oracle import oracle as O
+
+    rows, cols = 384, 4096
+    data = H.random_weight(tensor_type, rows, cols, seed=11 * m)
+    w = ctx().prepare_weight(tensor_type, data, rows, cols)
+    x_host = np.random.default_rng(m).standard_normal((m, cols)).astype(np.float32)
+    x = dev(x_host)
+    want = host(ctx().linear(x, w)).copy()
+    _noalloc(x, w, m)  # the first call on a device resolves the scratch address
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    got1 = _noalloc(x, w, m)
+    got2 = _noalloc(x, w, m)
+    torch.cuda.synchronize()
+    # torch.empty for the two outputs is served from torch's cache or not; the library itself must take nothing:
+    # the outputs are 2 * m * rows * 4 bytes, far below one allocator segment, so allow exactly torch's segment
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_before - free_after <= 2 * (2 << 20)
+    got1, got2 = host(got1), host(got2)
+    assert np.array_equal(got1.view(np.uint32), got2.view(np.uint32))
+    if m <= 4 or tensor_type == H.IQ4_NL:
+        assert np.array_equal(got1.view(np.uint32), want.view(np.uint32))
+    else:
+        assert H.max_rel_error(got1, want) <= 2e-5
+    ref = O.linear(tensor_type, data, rows, cols, x_host)
+    assert H.max_rel_error(got1, ref) <= 3e-4  # the decode path's own bound (16-bit activation slices), inside the 2e-3 contract
+
+
 def test_noalloc_rejects_sizes_beyond_its_limits():
     from zllm_b200 import ffi
 

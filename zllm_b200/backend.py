@@ -434,6 +434,27 @@ def moe_route(ctx: B200Context, x: torch.Tensor, router: torch.Tensor, top_k: in
     return ids, w
 
 
+def moe_gather_rows(ctx: B200Context, x: torch.Tensor, row_ids: torch.Tensor) -> torch.Tensor:
+    """``Backend::moe_gather_rows`` (src/backend/mod.rs:1657): ``out[i] = x[row_ids[i]]``."""
+    x = x.contiguous()
+    row_ids = row_ids.to(device=x.device, dtype=torch.int32).contiguous()
+    out = torch.empty((row_ids.numel(), x.shape[1]), dtype=x.dtype, device=x.device)
+    ffi.call("zq_moe_gather_rows", ctx.handle, _ptr(x), _dt(x), x.shape[0], x.shape[1], _ptr(row_ids), row_ids.numel(), _ptr(out))
+    return out
+
+
+def moe_scatter_add_rows(ctx: B200Context, accumulator: torch.Tensor, rows: torch.Tensor, row_ids: torch.Tensor, weights: Optional[torch.Tensor]) -> torch.Tensor:
+    """``Backend::moe_scatter_add_rows`` (src/backend/mod.rs:1661): ``accumulator[row_ids[i]] += weights[i] * rows[i]`` (f32 accumulator, in place)."""
+    rows = rows.contiguous()
+    row_ids = row_ids.to(device=rows.device, dtype=torch.int32).contiguous()
+    if weights is not None:
+        weights = weights.contiguous().float()
+    if accumulator.dtype != torch.float32 or not accumulator.is_contiguous():
+        raise TypeError("the MoE accumulator is a contiguous f32 tensor")
+    ffi.call("zq_moe_scatter_add_rows", ctx.handle, _ptr(rows), _dt(rows), _ptr(row_ids), _ptr(weights), rows.shape[0], rows.shape[1], _ptr(accumulator), accumulator.shape[0])
+    return accumulator
+
+
 def moe_forward_ep(ctx: B200Context, local_experts: MoeExperts, x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, shared=None, residual: Optional[torch.Tensor] = None, out_dtype=None,
                    max_tokens_any_rank: int = 0) -> torch.Tensor:
     """Expert-parallel routed experts (``zq_moe_forward_ep``): ``local_experts`` are this rank's block of the experts,

@@ -471,13 +471,19 @@ int launch_gemv_noalloc(zq_ctx *ctx, const zq_weight *w, const void *x, int x_dt
     ZQ_CUDA_CHECK(cudaMemsetAsync(scratch->counters, 0, (size_t)p.tiles * sizeof(uint32_t), ctx->stream), err);
     long long total = (long long)p.tiles * p.chunks;
     int grid = (int)(total < ctx->sm_count ? total : ctx->sm_count);
+    if (p.tiles <= ctx->sm_count && p.tiles * 100 >= ctx->sm_count * 85) grid = p.tiles;  // launch_gemv's whole-tile rule: same grid, same summation order
     if (grid <= 0) return ZQ_OK;
+    // Kernel choice and grid follow launch_gemv, so 1..4 rows (and every row count of a type or option that
+    // zq_linear also runs on the f16-limb kernels) agree with zq_linear bit for bit.  The one difference: zq_linear
+    // runs 5..8 rows of Q4_K / Q4_0 / Q8_0 on the integer-MMA kernel, which reads activation records from a
+    // workspace the context may have to grow; here those rows take the f16-limb kernel, and agree with zq_linear to
+    // f32 rounding (a few 1e-6 relative to the largest output) instead.
     bool taken = false;
-    if (ctx->enable_tcgen05_gemv && !ctx->force_staged_gemv) {  // same kernel choice as zq_linear, so results agree bit for bit
+    if (ctx->enable_tcgen05_gemv && !ctx->force_staged_gemv) {
         rc = launch_qmv(ctx, w, p, taken, err);
         if (rc || taken) return rc;
     }
-    if (!ctx->force_staged_gemv && !ctx->force_f16_gemv && m <= 4) {  // beyond 4 rows that kernel wants a device buffer it may have to allocate
+    if (!ctx->force_staged_gemv && !ctx->force_f16_gemv && m <= 4) {
         rc = launch_gemv_i8(ctx, w, nullptr, p, taken, err);
         if (rc || taken) return rc;
     }

@@ -261,6 +261,37 @@ __global__ void combine_kernel(const float *__restrict__ routed, const uint32_t 
     }
 }
 
+// out[rows[i]] += weights[i] * in[i]: scatter_add_rows_f32 (src/kernel/cuda/routing.rs:112-125).  Atomic adds, like the
+// reference's: the rows of one call are distinct targets in every use the runtime makes of it (the tokens of one expert),
+// so the sum each target receives per call is a single addition and the result does not depend on scheduling.
+__global__ void scatter_add_rows_kernel(const void *__restrict__ in, int dtype, const uint32_t *__restrict__ rows, const float *__restrict__ w, size_t n, int hidden, size_t out_rows, float *__restrict__ out, uint32_t *status) {
+    const size_t total = n * (size_t)hidden;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / hidden;
+        const uint32_t target = rows[r];
+        if (target >= out_rows) {  // never write out of range: record it and skip
+            atomicMax(status, (uint32_t)kStatusBadIndex);
+            continue;
+        }
+        atomicAdd(out + (size_t)target * hidden + (i - r * hidden), load_as_f32(in, dtype, i) * (w ? w[r] : 1.0f));
+    }
+}
+
+__global__ void gather_rows_checked_kernel(const void *__restrict__ x, int dtype, const uint32_t *__restrict__ tokens, size_t n_rows, size_t x_rows, int hidden, void *__restrict__ out, uint32_t *status) {
+    const size_t esz = dtype_size(dtype);
+    const size_t row_bytes = (size_t)hidden * esz, vec_per_row = row_bytes / 16, total = n_rows * vec_per_row;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / vec_per_row, v = i - r * vec_per_row;
+        const uint32_t src = tokens[r];
+        if (src >= x_rows) {
+            atomicMax(status, (uint32_t)kStatusBadIndex);
+            reinterpret_cast<uint4 *>(out)[i] = make_uint4(0, 0, 0, 0);
+            continue;
+        }
+        reinterpret_cast<uint4 *>(out)[i] = reinterpret_cast<const uint4 *>(reinterpret_cast<const uint8_t *>(x) + (size_t)src * row_bytes)[v];
+    }
+}
+
 static unsigned grid_for(zq_ctx *ctx, size_t total, int threads) {
     size_t blocks = (total + threads - 1) / threads;
     size_t cap = (size_t)ctx->sm_count * 32;
@@ -355,6 +386,29 @@ int zq_moe_route_topk(zq_ctx *ctx, int scoring, const void *dev_x, int x_dtype, 
     }
     router_topk_kernel<<<grid, kRouterThreads, smem, ctx->stream>>>(dev_x, x_dtype, (int)m, (int)hidden, dev_router_f32, dev_bias_f32, (int)num_experts, (int)top_k, scaling_factor, normalize_selected, dev_ids, dev_weights,
                                                                     (int)num_experts, nullptr, ctx->status_dev, scoring);
+    ctx->launches++;
+    ZQ_CUDA_CHECK(cudaGetLastError(), err);
+    return ZQ_OK;
+}
+
+int zq_moe_gather_rows(zq_ctx *ctx, const void *dev_x, int dtype, size_t x_rows, size_t hidden, const uint32_t *dev_row_ids, size_t n_rows, void *dev_out, zq_error *err) {
+    if (!ctx || !dev_x || !dev_row_ids || !dev_out) return set_error(err, ZQ_ERR_ARG, "zq_moe_gather_rows: null argument");
+    if (dtype != ZQ_F32 && dtype != ZQ_F16 && dtype != ZQ_BF16) return set_error(err, ZQ_ERR_ARG, "zq_moe_gather_rows: unknown dtype %d", dtype);
+    if (n_rows == 0 || hidden == 0 || (hidden * dtype_size(dtype)) % 16) return set_error(err, ZQ_ERR_SHAPE, "zq_moe_gather_rows: rows=%zu hidden=%zu (a row must be a multiple of 16 bytes)", n_rows, hidden);
+    if ((reinterpret_cast<uintptr_t>(dev_x) & 15) || (reinterpret_cast<uintptr_t>(dev_out) & 15)) return set_error(err, ZQ_ERR_ARG, "zq_moe_gather_rows: buffers must be 16-byte aligned");
+    if (int rc = use_device(ctx, err)) return rc;
+    gather_rows_checked_kernel<<<grid_for(ctx, n_rows * (hidden * dtype_size(dtype) / 16), 256), 256, 0, ctx->stream>>>(dev_x, dtype, dev_row_ids, n_rows, x_rows, (int)hidden, dev_out, ctx->status_dev);
+    ctx->launches++;
+    ZQ_CUDA_CHECK(cudaGetLastError(), err);
+    return ZQ_OK;
+}
+
+int zq_moe_scatter_add_rows(zq_ctx *ctx, const void *dev_rows, int dtype, const uint32_t *dev_row_ids, const float *dev_weights, size_t n_rows, size_t hidden, float *dev_out_f32, size_t out_rows, zq_error *err) {
+    if (!ctx || !dev_rows || !dev_row_ids || !dev_out_f32) return set_error(err, ZQ_ERR_ARG, "zq_moe_scatter_add_rows: null argument");
+    if (dtype != ZQ_F32 && dtype != ZQ_F16 && dtype != ZQ_BF16) return set_error(err, ZQ_ERR_ARG, "zq_moe_scatter_add_rows: unknown dtype %d", dtype);
+    if (n_rows == 0 || hidden == 0 || out_rows == 0 || hidden > (size_t)INT32_MAX) return set_error(err, ZQ_ERR_SHAPE, "zq_moe_scatter_add_rows: rows=%zu hidden=%zu targets=%zu", n_rows, hidden, out_rows);
+    if (int rc = use_device(ctx, err)) return rc;
+    scatter_add_rows_kernel<<<grid_for(ctx, n_rows * hidden, 256), 256, 0, ctx->stream>>>(dev_rows, dtype, dev_row_ids, dev_weights, n_rows, (int)hidden, out_rows, dev_out_f32, ctx->status_dev);
     ctx->launches++;
     ZQ_CUDA_CHECK(cudaGetLastError(), err);
     return ZQ_OK;

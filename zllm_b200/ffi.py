@@ -81,6 +81,8 @@ PROTOTYPES = {
     "zq_batch_finish": (_i, [_vp, _err]),
     "zq_moe_route_softmax_topk": (_i, [_vp, _vp, _i, _sz, _sz, _vp, _vp, _sz, _sz, _f, _i, _vp, _vp, _err]),
     "zq_moe_route_topk": (_i, [_vp, _i, _vp, _i, _sz, _sz, _vp, _vp, _sz, _sz, _f, _i, _vp, _vp, _err]),
+    "zq_moe_gather_rows": (_i, [_vp, _vp, _i, _sz, _sz, _vp, _sz, _vp, _err]),
+    "zq_moe_scatter_add_rows": (_i, [_vp, _vp, _i, _vp, _vp, _sz, _sz, _vp, _sz, _err]),
     "zq_moe_experts_create": (_i, [_vp, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), _sz, C.POINTER(_vp), _err]),
     "zq_moe_experts_destroy": (None, [_vp]),
     "zq_gguf_open": (_i, [C.c_char_p, C.POINTER(_vp), _err]),
