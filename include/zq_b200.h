@@ -52,7 +52,7 @@ int zq_ctx_use_own_stream(zq_ctx *ctx, zq_error *err);
 int zq_ctx_sync(zq_ctx *ctx, zq_error *err);
 /* Diagnostic switches (the counterpart of the reference's ZLLM_CUDA_* environment switches, kept per context).
  * Known keys (0/1): "force_staged_gemv", "force_f16_gemv" (decode on the f16 kernels instead of the integer-MMA kernel),
- * "enable_tcgen05_gemv" (Q4_K decode on the tcgen05 kernel), "disable_pdl" (decode kernels without programmatic dependent launch), "disable_worklist" (zq_linear_batch and the multi-weight entries launch one kernel per job), "force_moe_per_expert" (MoE forward always on the host-grouped path), "narrow_gemv_tiles" (decode, up to 4 rows: 64-row tiles, two CTAs per SM), "disable_fused_gemm" / "force_fused_gemm" (Q4_K prefill never / always on the kernel that dequantises inside the GEMM; default: up to 1024 tokens and MoE prefill). */
+ * "enable_tcgen05_gemv" (Q4_K decode on the tcgen05 kernel), "disable_pdl" (decode kernels without programmatic dependent launch), "disable_worklist" (zq_linear_batch and the multi-weight entries launch one kernel per job), "force_moe_per_expert" (MoE forward always on the host-grouped path), "force_moe_host_grouping" (MoE prefill: routes grouped on the host instead of on the device), "narrow_gemv_tiles" (decode, up to 4 rows: 64-row tiles, two CTAs per SM), "disable_fused_gemm" / "force_fused_gemm" (Q4_K prefill never / always on the kernel that dequantises inside the GEMM; default: up to 1024 tokens and MoE prefill). */
 int zq_ctx_set_option(zq_ctx *ctx, const char *key, int value, zq_error *err);
 int zq_ctx_sm_count(const zq_ctx *ctx);
 /* Number of kernels this library has launched on the context since creation (bench accounting). */
@@ -162,8 +162,9 @@ int zq_gated_mlp(zq_ctx *ctx, const zq_weight *gate, const zq_weight *up, const 
  * library, about 2.6 MB per GPU, held from library load until process exit.  Limits: at most 8 activation rows per
  * call, weights of at most 524 288 rows, devices of at most 160 SMs; anything beyond is rejected with an error.
  * The first call on a device looks up the array's device address (no allocation).  Results equal zq_linear's bit
- * for bit for 1..4 rows; 5..8 rows of Q4_K / Q4_0 / Q8_0 run on the f16-limb kernel rather than zq_linear's
- * integer-MMA one (whose activation workspace may have to grow) and agree to f32 rounding.  All calls on a device
+ * for bit for 1..4 rows; 5..8 rows of Q4_K / Q4_0 / Q8_0 / IQ4_NL run on the f16-limb kernel rather than zq_linear's
+ * integer-MMA one (whose activation workspace may have to grow) and agree within that kernel's activation rounding
+ * (16-bit integers per 256-column slice: a few 1e-5 of the largest output).  All calls on a device
  * share the array: calls that overlap on the GPU (two streams, two contexts)
  * race; calls ordered on one stream do not.  Inputs, outputs and the prepared weight are the caller's, as for
  * zq_linear. */

@@ -120,6 +120,48 @@ def test_moe_prefill_runs_grouped_tensor_core_gemms(tensor_type, m, moe_path):
     assert float(np.linalg.norm(got - want) / np.linalg.norm(want)) <= 1e-3
 
 
+def test_moe_prefill_grouping_on_the_device_equals_grouping_on_the_host():
+    """Prefill with Q4_K experts groups the routes on the device (a stable counting sort over chunks of tokens) and
+    hands the grouped GEMMs their work lists without a host round trip.  Slots, combine order and work lists are
+    those of the host grouping (src/moe/routing.rs:136-156), so the two give the same bits: several chunks, an
+    expert without tokens, an expert with several 256-token tiles, absent routes, a shared expert and a residual."""
+    from zllm_b200 import ffi
+    from zllm_b200.backend import MoeExperts, moe_forward
+
+    n_exp, top_k, hidden, inter, m = 6, 3, 512, 256, 1300
+    gates, ups, downs = _experts(H.Q4_K, n_exp, hidden, inter, seed=820)
+    rng = np.random.default_rng(82)
+    x = rng.standard_normal((m, hidden)).astype(np.float32)
+    # expert 4 never chosen, expert 0 on most tokens
+    ids_np = np.stack([np.concatenate(([0], rng.permutation([1, 2, 3, 5])[:top_k - 1])) if rng.random() < 0.8 else rng.permutation([1, 2, 3, 5])[:top_k] for _ in range(m)]).astype(np.uint32)
+    w_np = rng.random((m, top_k)).astype(np.float32)
+    absent = rng.random((m, top_k)) < 0.15
+    ids_np[absent] = ffi.MOE_NO_ROUTE
+    resid = rng.standard_normal((m, hidden)).astype(np.float32)
+    c = ctx()
+    table = MoeExperts(c, [c.prepare_weight(H.Q4_K, g, inter, hidden) for g in gates], [c.prepare_weight(H.Q4_K, u, inter, hidden) for u in ups], [c.prepare_weight(H.Q4_K, d, hidden, inter) for d in downs])
+    sh = _experts(H.Q4_K, 1, hidden, inter, seed=990)
+    shared = (c.prepare_weight(H.Q4_K, sh[0][0], inter, hidden), c.prepare_weight(H.Q4_K, sh[1][0], inter, hidden), c.prepare_weight(H.Q4_K, sh[2][0], hidden, inter))
+    ids = torch.from_numpy(ids_np.view(np.int32)).cuda()
+    xd, wd, rd = dev(x), dev(w_np), dev(resid)
+    on_device = host(moe_forward(c, table, xd, ids, wd, shared=shared, residual=rd)).copy()
+    again = host(moe_forward(c, table, xd, ids, wd, shared=shared, residual=rd)).copy()
+    c.set_option("force_moe_host_grouping", 1)
+    try:
+        on_host = host(moe_forward(c, table, xd, ids, wd, shared=shared, residual=rd)).copy()
+    finally:
+        c.set_option("force_moe_host_grouping", 0)
+    assert np.array_equal(on_device.view(np.uint32), again.view(np.uint32))
+    assert np.array_equal(on_device.view(np.uint32), on_host.view(np.uint32))
+    # and against the oracle (absent routes carry weight 0 there)
+    ids_o, w_o = ids_np.copy(), w_np.copy()
+    w_o[absent] = 0.0
+    ids_o[absent] = 4
+    want = orc.moe_forward([(H.Q4_K, g, inter, hidden) for g in gates], [(H.Q4_K, u, inter, hidden) for u in ups], [(H.Q4_K, d, hidden, inter) for d in downs], x, ids_o, w_o,
+                           shared=[(H.Q4_K, sh[0][0], inter, hidden), (H.Q4_K, sh[1][0], inter, hidden), (H.Q4_K, sh[2][0], hidden, inter)], residual=resid)
+    assert H.max_rel_error(on_device, want) <= 2 * BOUND
+
+
 def test_shared_expert_of_another_width_takes_its_own_launches():
     """A shared expert shaped like the routed ones rides along in the grouped launches; any other shape runs as a
     separate gated MLP (src/moe/topk_moe.rs:84-104) and is added in the combine."""

@@ -49,9 +49,9 @@ def test_noalloc_matches_regular_linear_on_consecutive_calls(tensor_type, rows, 
 @pytest.mark.parametrize("m", [1, 4, 5, 8])
 @pytest.mark.parametrize("tensor_type", [H.Q4_K, H.Q8_0, H.IQ4_NL])
 def test_noalloc_with_default_options(tensor_type, m):
-    """The kernels a caller gets without any option set: equal to zq_linear bit for bit for 1..4 rows (and for every
-    row count of IQ4_NL, which both entries run on the f16-limb kernel), within f32 rounding for 5..8 rows of the
-    integer-MMA types; against the CPU oracle at the decode path's bound; and the device's free memory does not move."""
+    """The kernels a caller gets without any option set: equal to zq_linear bit for bit for 1..4 rows, within the
+    integer-MMA kernel's activation rounding for 5..8 rows (which zq_linear runs on that kernel and this entry on the
+    f16-limb one); against the CPU oracle at the decode path's bound; and the device's free memory does not move."""
     from oracle import oracle as O
 
     rows, cols = 384, 4096
@@ -72,10 +72,10 @@ def test_noalloc_with_default_options(tensor_type, m):
     assert free_before - free_after <= 2 * (2 << 20)
     got1, got2 = host(got1), host(got2)
     assert np.array_equal(got1.view(np.uint32), got2.view(np.uint32))
-    if m <= 4 or tensor_type == H.IQ4_NL:
+    if m <= 4:
         assert np.array_equal(got1.view(np.uint32), want.view(np.uint32))
     else:
-        assert H.max_rel_error(got1, want) <= 2e-5
+        assert H.max_rel_error(got1, want) <= 3e-4
     ref = O.linear(tensor_type, data, rows, cols, x_host)
     assert H.max_rel_error(got1, ref) <= 3e-4  # the decode path's own bound (16-bit activation slices), inside the 2e-3 contract
 

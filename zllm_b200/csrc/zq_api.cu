@@ -261,6 +261,10 @@ int zq_ctx_set_option(zq_ctx *ctx, const char *key, int value, zq_error *err) {
         ctx->force_moe_per_expert = value;
         return ZQ_OK;
     }
+    if (!strcmp(key, "force_moe_host_grouping")) {
+        ctx->force_moe_host_grouping = value;
+        return ZQ_OK;
+    }
     if (!strcmp(key, "disable_worklist")) {
         ctx->disable_worklist = value;
         return ZQ_OK;

@@ -276,6 +276,7 @@ struct zq_ctx {
     int force_fused_gemm = 0;      // Q4_K prefill: the fused kernel for every token count (tests)
     int disable_fused_gemm = 0;    // Q4_K prefill: separate f16 operand pass + plain GEMM instead of the fused kernel
     int force_moe_per_expert = 0;  // MoE forward: always the host-grouped per-expert path (tests)
+    int force_moe_host_grouping = 0;  // MoE prefill: group the routes on the host instead of on the device (tests, A/B)
     std::atomic<uint64_t> launches{0};
     std::mutex mutex;
 };
@@ -301,7 +302,7 @@ namespace zq {
 int use_device(zq_ctx *ctx, zq_error *err);
 int ensure_workspace(zq_ctx *ctx, size_t bytes, zq_error *err);
 int ensure_xq(zq_ctx *ctx, size_t bytes, zq_error *err);
-int launch_gemm_fused_grouped(zq_ctx *ctx, const CUtensorMap *w_maps, const CUtensorMap *w2_maps, size_t rows, size_t k, const __half *x, size_t x_rows, const int4 *items, int n_items, void *y, int y_dtype, zq_error *err);
+int launch_gemm_fused_grouped(zq_ctx *ctx, const CUtensorMap *w_maps, const CUtensorMap *w2_maps, size_t rows, size_t k, const __half *x, size_t x_rows, const int4 *items, int n_items, const int *n_items_dev, void *y, int y_dtype, zq_error *err);
 int launch_gemm_f16(zq_ctx *ctx, const __half *w, size_t rows, size_t k, const __half *x, size_t m, void *y, int y_dtype, zq_error *err);
 int launch_to_f16(zq_ctx *ctx, const void *x, int x_dtype, __half *out, size_t n, zq_error *err);
 int launch_gemm_grouped(zq_ctx *ctx, const __half *w, const __half *w2, size_t mats, size_t rows, size_t k, const __half *x, size_t x_rows, const int4 *items, int n_items, void *y, int y_dtype, zq_error *err);

@@ -40,6 +40,7 @@ struct GemmParams {
     // activation operand shared by all matrices, outputs are rows of y with n_out columns.
     const int4 *items;
     int n_items;
+    const int *n_items_dev;  // when set, the item count is read from device memory (a plan kernel wrote it); n_items is then its upper bound
     // fused Q4_K kernel, grouped form: per-matrix tensor maps of the packed weights (device table indexed by z)
     const CUtensorMap *w_maps, *w2_maps;
 };
@@ -146,7 +147,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const __grid_cons
     const int k_blocks = (p.k + kBK - 1) / kBK;
     const int n_row_tiles = (p.n_out + kBM - 1) / kBM, n_tok_tiles = (p.m + kBN - 1) / kBN;
     const bool grouped = p.items != nullptr;
-    const int total_tiles = grouped ? p.n_items : n_row_tiles * n_tok_tiles;
+    const int total_tiles = grouped ? (p.n_items_dev ? *p.n_items_dev : p.n_items) : n_row_tiles * n_tok_tiles;
     auto tile_coords = [&](int tile, int &row0, int &tok0, int &tok_end, int &z) {
         if (grouped) {
             const int4 it = p.items[tile];
@@ -416,7 +417,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) gemm_q4k_fused_kernel(const 
     const int n_sb = p.k / kUnitWeights;  // Q4_K: K is a multiple of 256
     const int n_row_tiles = (p.n_out + kBM - 1) / kBM, n_tok_tiles = (p.m + kBN - 1) / kBN;
     const bool grouped = p.items != nullptr;
-    const int total_tiles = grouped ? p.n_items : n_row_tiles * n_tok_tiles;
+    const int total_tiles = grouped ? (p.n_items_dev ? *p.n_items_dev : p.n_items) : n_row_tiles * n_tok_tiles;
     auto tile_coords = [&](int tile, int &row0, int &tok0, int &tok_end, int &z) {
         if (grouped) {
             const int4 it = p.items[tile];
@@ -688,6 +689,7 @@ int launch_gemm(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const vo
         p.k = (int)k;
         p.items = nullptr;
         p.n_items = 0;
+        p.n_items_dev = nullptr;
         const size_t total_tiles = ((n + kBM - 1) / kBM) * ((m + kBN - 1) / kBN);
         dim3 grid((unsigned)(total_tiles < (size_t)ctx->sm_count ? total_tiles : (size_t)ctx->sm_count));
         static bool configured[2][64] = {};
@@ -745,6 +747,7 @@ int launch_gemm(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const vo
     p.k = (int)k;
     p.items = nullptr;
     p.n_items = 0;
+    p.n_items_dev = nullptr;
     p.w_maps = p.w2_maps = nullptr;
     const size_t total_tiles = ((n + kBM - 1) / kBM) * ((m + kBN - 1) / kBN);
     dim3 grid((unsigned)(total_tiles < (size_t)ctx->sm_count ? total_tiles : (size_t)ctx->sm_count));
@@ -812,6 +815,7 @@ int launch_gemm_grouped(zq_ctx *ctx, const __half *w, const __half *w2, size_t m
     p.k = (int)k;
     p.items = items;
     p.n_items = n_items;
+    p.n_items_dev = nullptr;
     p.w_maps = p.w2_maps = nullptr;
     dim3 grid((unsigned)(n_items < ctx->sm_count ? n_items : ctx->sm_count));
     static bool configured[2][64] = {};
@@ -850,6 +854,7 @@ int launch_gemm_f16(zq_ctx *ctx, const __half *w, size_t rows, size_t k, const _
     p.k = (int)k;
     p.items = nullptr;
     p.n_items = 0;
+    p.n_items_dev = nullptr;
     p.w_maps = p.w2_maps = nullptr;
     const size_t total_tiles = ((rows + kBM - 1) / kBM) * ((m + kBN - 1) / kBN);
     dim3 grid((unsigned)(total_tiles < (size_t)ctx->sm_count ? total_tiles : (size_t)ctx->sm_count));
@@ -866,7 +871,8 @@ int launch_gemm_f16(zq_ctx *ctx, const __half *w, size_t rows, size_t k, const _
 
 // Grouped fused form (MoE prefill, Q4_K experts): no f16 copy of the weights at all.  `w_maps` / `w2_maps`: device
 // tables of the experts' packed-weight tensor maps (one unit x 128 rows boxes), indexed by the work items' z.
-int launch_gemm_fused_grouped(zq_ctx *ctx, const CUtensorMap *w_maps, const CUtensorMap *w2_maps, size_t rows, size_t k, const __half *x, size_t x_rows, const int4 *items, int n_items, void *y, int y_dtype, zq_error *err) {
+int launch_gemm_fused_grouped(zq_ctx *ctx, const CUtensorMap *w_maps, const CUtensorMap *w2_maps, size_t rows, size_t k, const __half *x, size_t x_rows, const int4 *items, int n_items, const int *n_items_dev, void *y, int y_dtype,
+                              zq_error *err) {
     if (n_items <= 0) return ZQ_OK;
     if (k % kUnitWeights) return set_error(err, ZQ_ERR_SHAPE, "fused Q4_K GEMM needs columns aligned to 256, got %zu", k);
     const bool gated = w2_maps != nullptr;
@@ -883,6 +889,7 @@ int launch_gemm_fused_grouped(zq_ctx *ctx, const CUtensorMap *w_maps, const CUte
     p.k = (int)k;
     p.items = items;
     p.n_items = n_items;
+    p.n_items_dev = n_items_dev;
     p.w_maps = w_maps;
     p.w2_maps = w2_maps;
     dim3 grid((unsigned)(n_items < ctx->sm_count ? n_items : ctx->sm_count));

@@ -475,9 +475,9 @@ int launch_gemv_noalloc(zq_ctx *ctx, const zq_weight *w, const void *x, int x_dt
     if (grid <= 0) return ZQ_OK;
     // Kernel choice and grid follow launch_gemv, so 1..4 rows (and every row count of a type or option that
     // zq_linear also runs on the f16-limb kernels) agree with zq_linear bit for bit.  The one difference: zq_linear
-    // runs 5..8 rows of Q4_K / Q4_0 / Q8_0 on the integer-MMA kernel, which reads activation records from a
-    // workspace the context may have to grow; here those rows take the f16-limb kernel, and agree with zq_linear to
-    // f32 rounding (a few 1e-6 relative to the largest output) instead.
+    // runs 5..8 rows on the integer-MMA kernel, which reads activation records from a workspace the context may
+    // have to grow; here those rows take the f16-limb kernel, and agree with zq_linear within the integer kernel's
+    // activation rounding (16-bit integers per 256-column slice) instead.
     bool taken = false;
     if (ctx->enable_tcgen05_gemv && !ctx->force_staged_gemv) {
         rc = launch_qmv(ctx, w, p, taken, err);

@@ -15,6 +15,7 @@
 //          the min term is one f16 MMA per unit on the exact integer sums S_G = 1024 a + r (a and r exact in f16).
 //   Q4_0   y += s_x * d_b/16 * [sum 16 (q - 8) x_q]     (operand bytes (16 q) ^ 0x80 read as s8)
 //   Q8_0   y += s_x * d_b * [sum q x_q]
+//   IQ4_NL y += s_x * d_b * [sum K[q] x_q]               (codebook bytes looked up with PRMT, zq_i8.cuh)
 // Everything up to the final scale is exact integer arithmetic; the result differs from the f32 reference only by
 // the 2^-16 activation resolution and f32 rounding of the per-unit terms.
 //
@@ -489,14 +490,14 @@ static int launch_i8_type(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up
 }
 
 // Tries the integer-MMA kernel for one pass of up to 16 activation rows; `taken` tells whether it was launched
-// (IQ4_NL, whose codebook values would need a table lookup per weight, and slices that do not fit stay on the
-// f16 kernels).
+// (slices that do not fit stay on the f16 kernels).
 int launch_gemv_i8(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const GemvParams &p, bool &taken, zq_error *err) {
     taken = false;
     if (p.m < 1 || p.m > kMaxGemvRows) return ZQ_OK;
     switch (w->type) {
     case ZQ_Q4_K: return launch_i8_type<ZQ_Q4_K>(ctx, w, w_up, p, taken, err);
     case ZQ_Q4_0: return launch_i8_type<ZQ_Q4_0>(ctx, w, w_up, p, taken, err);
+    case ZQ_IQ4_NL: return launch_i8_type<ZQ_IQ4_NL>(ctx, w, w_up, p, taken, err);
     case ZQ_Q8_0: return launch_i8_type<ZQ_Q8_0>(ctx, w, w_up, p, taken, err);
     default: return ZQ_OK;
     }

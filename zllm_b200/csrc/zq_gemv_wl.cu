@@ -548,7 +548,7 @@ static int launch_wl_type(zq_ctx *ctx, const WlArgs &wa, int nt, bool gated, zq_
     return gated ? launch_wl_one<TYPE, 4, true>(ctx, wa, err) : launch_wl_one<TYPE, 4, false>(ctx, wa, err);
 }
 
-static bool wl_type_ok(uint32_t t) { return t == ZQ_Q4_K || t == ZQ_Q4_0 || t == ZQ_Q8_0; }
+static bool wl_type_ok(uint32_t t) { return t == ZQ_Q4_K || t == ZQ_Q4_0 || t == ZQ_Q8_0 || t == ZQ_IQ4_NL; }
 
 bool gemv_wl_supported(const zq_ctx *ctx, const WlHostJob &j) {
     if (!j.w || !j.w->d_maps || !wl_type_ok(j.w->type) || j.m < 1 || j.m > (size_t)kMaxGemvRows) return false;
@@ -635,6 +635,7 @@ int launch_gemv_wl(zq_ctx *ctx, const WlHostJob *jobs, size_t n_jobs, int x_dtyp
             switch (type) {
             case ZQ_Q4_K: r = launch_wl_type<ZQ_Q4_K>(ctx, wa, nt, gated, err); break;
             case ZQ_Q4_0: r = launch_wl_type<ZQ_Q4_0>(ctx, wa, nt, gated, err); break;
+            case ZQ_IQ4_NL: r = launch_wl_type<ZQ_IQ4_NL>(ctx, wa, nt, gated, err); break;
             default: r = launch_wl_type<ZQ_Q8_0>(ctx, wa, nt, gated, err); break;
             }
             wa.n_jobs = 0;

@@ -198,12 +198,37 @@ __device__ __forceinline__ void consume_q4k_i8(uint32_t wq0, uint32_t wq1, int t
     }
 }
 
-// One block-32 unit (8 blocks of 32 weights) of the thread's two fragment rows: Q4_0 or Q8_0.
+// IQ4_NL: the 8 codebook values (src/weight/codec/ggml.rs:4) of one packed word as two s8x4 operands, `lo` for the four
+// low nibbles and `hi` for the four high nibbles.  PRMT is the table lookup: its selector's low 16 bits are four
+// nibbles, each picking one of 8 table bytes by its low three bits, so the low half-word looks up [lo0, hi0, lo1, hi1]
+// in both halves of the table; the nibble's top bit (spread to a byte mask by PRMT's sign-replicate mode) picks between
+// the halves; two more PRMTs put the low-nibble and the high-nibble results into words of their own.
+__device__ __forceinline__ uint32_t prmt_b32(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+__device__ __forceinline__ uint32_t lop3_select(uint32_t mask, uint32_t on, uint32_t off) {  // (mask & on) | (~mask & off)
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0xCA;" : "=r"(r) : "r"(mask), "r"(on), "r"(off));
+    return r;
+}
+__device__ __forceinline__ void iq4nl_lookup(uint32_t w, uint32_t &lo, uint32_t &hi) {
+    constexpr uint32_t T0 = 0xBFAD9881u, T1 = 0xF6EADDCFu, T2 = 0x26190D01u, T3 = 0x71594535u;  // -127 .. 113 as s8
+    const uint32_t ws = w & 0x77777777u, w4 = w << 4;
+    const uint32_t x = lop3_select(prmt_b32(w4, w, 0xD9C8u), prmt_b32(T2, T3, ws), prmt_b32(T0, T1, ws));
+    const uint32_t ws2 = ws >> 16;
+    const uint32_t y = lop3_select(prmt_b32(w4, w, 0xFBEAu), prmt_b32(T2, T3, ws2), prmt_b32(T0, T1, ws2));
+    lo = prmt_b32(x, y, 0x6420u);
+    hi = prmt_b32(x, y, 0x7531u);
+}
+
+// One block-32 unit (8 blocks of 32 weights) of the thread's two fragment rows: Q4_0, IQ4_NL or Q8_0.
 template <uint32_t TYPE, int NT>
 __device__ __forceinline__ void consume_b32_i8(uint32_t wq0, uint32_t wq1, int t, const uint32_t (&rec)[NT], const uint32_t (&srec)[NT], uint32_t xoff, float (&yacc)[NT][2]) {
     constexpr int H = TYPE == ZQ_Q8_0 ? 4 : 2;     // 16-byte pieces per lane
     constexpr int BPP = TYPE == ZQ_Q8_0 ? 2 : 4;   // blocks per piece
-    constexpr float kPre = TYPE == ZQ_Q8_0 ? 1.f : 0.0625f;
+    constexpr float kPre = TYPE == ZQ_Q4_0 ? 0.0625f : 1.f;
     const uint4 hdr0 = lds128(wq0), hdr1 = lds128(wq1);
     uint4 pc0[H], pc1[H];
 #pragma unroll
@@ -230,6 +255,9 @@ __device__ __forceinline__ void consume_b32_i8(uint32_t wq0, uint32_t wq1, int t
             uint32_t a0, a1, a2, a3;
             if constexpr (TYPE == ZQ_Q8_0) {
                 a0 = q0[2 * bb]; a1 = q1[2 * bb]; a2 = q0[2 * bb + 1]; a3 = q1[2 * bb + 1];
+            } else if constexpr (TYPE == ZQ_IQ4_NL) {
+                iq4nl_lookup(q0[bb], a0, a2);
+                iq4nl_lookup(q1[bb], a1, a3);
             } else {  // 16 (q - 8) as s8: low nibbles moved up, high nibbles in place
                 a0 = lop3_and_xor(q0[bb] << 4, 0xF0F0F0F0u, 0x80808080u);
                 a1 = lop3_and_xor(q1[bb] << 4, 0xF0F0F0F0u, 0x80808080u);

@@ -292,6 +292,159 @@ __global__ void gather_rows_checked_kernel(const void *__restrict__ x, int dtype
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Prefill grouping on the device (src/moe/routing.rs:136-156: token-major stable grouping; per-token combine order
+// ascending expert id, src/backend/cpu/moe.rs:107-141).  A stable counting sort over chunks of whole tokens:
+//   count   per chunk, how many routes go to each expert
+//   scan    one CTA, thread per expert: the chunk's first slot inside each expert's range, the experts' ranges, and
+//           the two work lists of the grouped GEMMs (one item per expert, 256-token tile, 128-row tile) with their counts
+//   place   per chunk: slot of every route (the thread of an expert walks the chunk's routes in order), the
+//           slot -> token table, and each token's slots and weights in combine order
+// Nothing returns to the host: the GEMM kernels read their item counts from device memory.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int kGroupThreads = 1024;
+
+__global__ void __launch_bounds__(kGroupThreads) moe_prefill_count_kernel(const uint32_t *__restrict__ ids, int m, int top_k, int E, int tokens_per_chunk, uint32_t *__restrict__ hist, uint32_t *status) {
+    extern __shared__ uint32_t grp_smem[];
+    uint32_t *s_cnt = grp_smem;
+    for (int e = threadIdx.x; e < E; e += kGroupThreads) s_cnt[e] = 0;
+    __syncthreads();
+    const int t0 = blockIdx.x * tokens_per_chunk, t1 = min(m, t0 + tokens_per_chunk);
+    const int r0 = t0 * top_k, nr = (t1 - t0) * top_k;
+    for (int r = threadIdx.x; r < nr; r += kGroupThreads) {
+        uint32_t id = ids[r0 + r];
+        if (id == ZQ_MOE_NO_ROUTE) continue;
+        if (id >= (uint32_t)E) {  // never index out of the table: record it and park the route on the last expert
+            atomicMax(status, (uint32_t)kStatusBadIndex);
+            id = (uint32_t)E - 1;
+        }
+        atomicAdd(&s_cnt[id], 1u);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += kGroupThreads) hist[(size_t)blockIdx.x * E + e] = s_cnt[e];
+}
+
+// counts: [0] items of the gated launch, [1] items of the down launch, [2] routed rows in all
+__global__ void __launch_bounds__(kGroupThreads) moe_prefill_scan_kernel(uint32_t *__restrict__ hist, int chunks, int E, uint32_t *__restrict__ offsets, int rt_gated, int rt_down, int4 *__restrict__ items_gated,
+                                                                         int4 *__restrict__ items_down, int *__restrict__ counts) {
+    __shared__ uint32_t warp_tot[2][32];
+    const int e = threadIdx.x, lane = e & 31, wid = e >> 5;
+    uint32_t c = 0;
+    if (e < E)
+        for (int b = 0; b < chunks; ++b) {  // exclusive prefix over the chunks: where chunk b's routes start inside expert e's range
+            const uint32_t v = hist[(size_t)b * E + e];
+            hist[(size_t)b * E + e] = c;
+            c += v;
+        }
+    const uint32_t nt = (c + 255u) / 256u;  // 256-token tiles of this expert
+    uint32_t sc = c, st = nt;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const uint32_t a = __shfl_up_sync(0xffffffffu, sc, d), b = __shfl_up_sync(0xffffffffu, st, d);
+        if (lane >= d) {
+            sc += a;
+            st += b;
+        }
+    }
+    if (lane == 31) {
+        warp_tot[0][wid] = sc;
+        warp_tot[1][wid] = st;
+    }
+    __syncthreads();
+    uint32_t base_c = 0, base_t = 0;
+    for (int w = 0; w < wid; ++w) {
+        base_c += warp_tot[0][w];
+        base_t += warp_tot[1][w];
+    }
+    const uint32_t first = base_c + sc - c, tfirst = base_t + st - nt;
+    if (e < E) {
+        offsets[e] = first;
+        for (uint32_t tt = 0; tt < nt; ++tt) {
+            const int t0 = (int)(first + tt * 256u), end = (int)(first + c);
+            for (int rt = 0; rt < rt_gated; ++rt) items_gated[(size_t)(tfirst + tt) * rt_gated + rt] = make_int4(e, rt * 128, t0, end);
+            for (int rt = 0; rt < rt_down; ++rt) items_down[(size_t)(tfirst + tt) * rt_down + rt] = make_int4(e, rt * 128, t0, end);
+        }
+    }
+    if (e == kGroupThreads - 1) {  // the last thread holds the totals
+        offsets[E] = base_c + sc;
+        const uint32_t tiles = base_t + st;
+        counts[0] = (int)(tiles * (uint32_t)rt_gated);
+        counts[1] = (int)(tiles * (uint32_t)rt_down);
+        counts[2] = (int)(base_c + sc);
+    }
+}
+
+__global__ void __launch_bounds__(kGroupThreads) moe_prefill_place_kernel(const uint32_t *__restrict__ ids, const float *__restrict__ wts, int m, int top_k, int E, int tokens_per_chunk, const uint32_t *__restrict__ hist,
+                                                                          const uint32_t *__restrict__ offsets, uint32_t *__restrict__ slot_token, uint32_t *__restrict__ token_slots, float *__restrict__ token_w) {
+    extern __shared__ uint32_t grp_smem[];
+    const int cap = tokens_per_chunk * top_k;
+    uint32_t *s_ids = grp_smem;         // [cap]
+    uint32_t *s_slot = s_ids + cap;     // [cap]
+    uint32_t *s_cnt = s_slot + cap;     // [E]
+    for (int e = threadIdx.x; e < E; e += kGroupThreads) s_cnt[e] = 0;
+    __syncthreads();
+    const int t0 = blockIdx.x * tokens_per_chunk, t1 = min(m, t0 + tokens_per_chunk);
+    const int r0 = t0 * top_k, nr = (t1 - t0) * top_k;
+    for (int r = threadIdx.x; r < nr; r += kGroupThreads) {
+        uint32_t id = ids[r0 + r];
+        s_slot[r] = 0;
+        if (id == ZQ_MOE_NO_ROUTE) {  // an absent route: no slot, weight 0 in the combine
+            s_ids[r] = (uint32_t)E;
+            continue;
+        }
+        if (id >= (uint32_t)E) id = (uint32_t)E - 1;  // reported by the count kernel
+        s_ids[r] = id;
+        atomicAdd(&s_cnt[id], 1u);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += kGroupThreads) {
+        if (s_cnt[e] == 0) continue;
+        uint32_t slot = offsets[e] + hist[(size_t)blockIdx.x * E + e];
+        for (int r = 0; r < nr; ++r) {
+            if (s_ids[r] == (uint32_t)e) {
+                slot_token[slot] = (uint32_t)((r0 + r) / top_k);
+                s_slot[r] = slot++;
+            }
+        }
+    }
+    __syncthreads();
+    for (int t = threadIdx.x; t < t1 - t0; t += kGroupThreads) {
+        uint32_t ke[64], ks[64];
+        float kw[64];
+        for (int j = 0; j < top_k; ++j) {
+            const uint32_t e = s_ids[t * top_k + j], s = s_slot[t * top_k + j];
+            const float w = e == (uint32_t)E ? 0.f : wts[r0 + t * top_k + j];
+            int i = j;
+            while (i > 0 && ke[i - 1] > e) {
+                ke[i] = ke[i - 1]; ks[i] = ks[i - 1]; kw[i] = kw[i - 1];
+                --i;
+            }
+            ke[i] = e; ks[i] = s; kw[i] = w;
+        }
+        for (int j = 0; j < top_k; ++j) {
+            token_slots[(size_t)(t0 + t) * top_k + j] = ks[j];
+            token_w[(size_t)(t0 + t) * top_k + j] = kw[j];
+        }
+    }
+}
+
+// out16[s] = f16(x[slot_token[s]]) for the slots that exist (their number is on the device); 8 elements per thread
+__global__ void gather_rows_f16_kernel(const void *__restrict__ x, int dtype, const uint32_t *__restrict__ slot_token, const int *__restrict__ n_rows_dev, int hidden, __half *__restrict__ out) {
+    const size_t vec_per_row = (size_t)hidden / 8, total = (size_t)*n_rows_dev * vec_per_row;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / vec_per_row, v = i - r * vec_per_row;
+        const size_t src = (size_t)slot_token[r] * hidden + v * 8;
+        __align__(16) __half h[8];
+        if (dtype == ZQ_F16) {
+            *reinterpret_cast<uint4 *>(h) = *reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(x) + src);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(load_as_f32(x, dtype, src + j));
+        }
+        reinterpret_cast<uint4 *>(out)[i] = *reinterpret_cast<const uint4 *>(h);
+    }
+}
+
 static unsigned grid_for(zq_ctx *ctx, size_t total, int threads) {
     size_t blocks = (total + threads - 1) / threads;
     size_t cap = (size_t)ctx->sm_count * 32;
@@ -309,6 +462,62 @@ static int ensure_moe_ws(zq_ctx *ctx, size_t bytes, zq_error *err) {
     size_t rounded = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
     ZQ_CUDA_CHECK(cudaMalloc(&ctx->moe_ws, rounded), err);
     ctx->moe_ws_bytes = rounded;
+    return ZQ_OK;
+}
+
+// MoE prefill with Q4_K experts, everything on the device: grouping (three small kernels), one gather that also
+// converts to f16, the two grouped fused GEMMs (their item counts read from device memory), shared expert, combine.
+static int moe_prefill_device(zq_ctx *ctx, const zq_moe_experts *experts, const zq_weight *shared_gate, const zq_weight *shared_up, const zq_weight *shared_down, const void *dev_x, int x_dtype, size_t m, const uint32_t *dev_ids,
+                              const float *dev_weights, size_t top_k, void *dev_y, int y_dtype, const void *dev_residual, zq_error *err) {
+    const size_t E = experts->num_experts, H = experts->hidden, I = experts->inter, routes = m * top_k;
+    const bool has_shared = shared_gate != nullptr;
+    const int tokens_per_chunk = (int)(kGroupThreads / top_k > 0 ? kGroupThreads / top_k : 1);
+    const int chunks = (int)((m + tokens_per_chunk - 1) / tokens_per_chunk);
+    const int rt_i = (int)((I + 127) / 128), rt_h = (int)((H + 127) / 128);
+    const size_t max_tiles = routes / 256 + E;  // sum over experts of ceil(count / 256)
+    auto al = [](size_t v) { return (v + 255) & ~size_t(255); };
+    // tables and f32 results
+    const size_t o_hist = 0, o_offsets = o_hist + al((size_t)chunks * E * 4), o_counts = o_offsets + al((E + 1) * 4), o_slot_token = o_counts + al(16), o_token_slots = o_slot_token + al(routes * 4);
+    const size_t o_token_w = o_token_slots + al(routes * 4), o_out = o_token_w + al(routes * 4), o_shared = o_out + al(routes * H * 4), total = o_shared + (has_shared ? al(m * H * 4) : 0);
+    int rc = ensure_moe_ws(ctx, total, err);
+    if (rc) return rc;
+    uint8_t *ws = reinterpret_cast<uint8_t *>(ctx->moe_ws);
+    uint32_t *d_hist = reinterpret_cast<uint32_t *>(ws + o_hist), *d_offsets = reinterpret_cast<uint32_t *>(ws + o_offsets), *d_slot_token = reinterpret_cast<uint32_t *>(ws + o_slot_token);
+    uint32_t *d_token_slots = reinterpret_cast<uint32_t *>(ws + o_token_slots);
+    int *d_counts = reinterpret_cast<int *>(ws + o_counts);
+    float *d_token_w = reinterpret_cast<float *>(ws + o_token_w), *d_out = reinterpret_cast<float *>(ws + o_out), *d_shared = has_shared ? reinterpret_cast<float *>(ws + o_shared) : nullptr;
+    // f16 operands and work lists
+    auto al2 = [](size_t v) { return (v + 1023) & ~size_t(1023); };
+    const size_t x16_bytes = al2(routes * H * sizeof(__half)), act16_bytes = al2(routes * I * sizeof(__half)), items_g_bytes = al2(max_tiles * rt_i * sizeof(int4)), items_d_bytes = al2(max_tiles * rt_h * sizeof(int4));
+    rc = ensure_workspace(ctx, x16_bytes + act16_bytes + items_g_bytes + items_d_bytes, err);
+    if (rc) return rc;
+    uint8_t *wsb = reinterpret_cast<uint8_t *>(ctx->workspace);
+    __half *x16 = reinterpret_cast<__half *>(wsb), *act16 = reinterpret_cast<__half *>(wsb + x16_bytes);
+    int4 *d_items_g = reinterpret_cast<int4 *>(wsb + x16_bytes + act16_bytes), *d_items_d = reinterpret_cast<int4 *>(wsb + x16_bytes + act16_bytes + items_g_bytes);
+
+    static bool configured[64] = {};
+    const size_t place_smem = ((size_t)tokens_per_chunk * top_k * 2 + E) * 4;
+    if (!configured[ctx->device & 63]) {
+        ZQ_CUDA_CHECK(cudaFuncSetAttribute(moe_prefill_place_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024), err);
+        configured[ctx->device & 63] = true;
+    }
+    moe_prefill_count_kernel<<<chunks, kGroupThreads, E * 4, ctx->stream>>>(dev_ids, (int)m, (int)top_k, (int)E, tokens_per_chunk, d_hist, ctx->status_dev);
+    moe_prefill_scan_kernel<<<1, kGroupThreads, 0, ctx->stream>>>(d_hist, chunks, (int)E, d_offsets, rt_i, rt_h, d_items_g, d_items_d, d_counts);
+    moe_prefill_place_kernel<<<chunks, kGroupThreads, place_smem, ctx->stream>>>(dev_ids, dev_weights, (int)m, (int)top_k, (int)E, tokens_per_chunk, d_hist, d_offsets, d_slot_token, d_token_slots, d_token_w);
+    gather_rows_f16_kernel<<<grid_for(ctx, routes * (H / 8), 256), 256, 0, ctx->stream>>>(dev_x, x_dtype, d_slot_token, d_counts + 2, (int)H, x16);
+    ctx->launches += 4;
+    ZQ_CUDA_CHECK(cudaGetLastError(), err);
+    rc = launch_gemm_fused_grouped(ctx, experts->d_gate_qmaps, experts->d_up_qmaps, I, H, x16, routes, d_items_g, (int)(max_tiles * rt_i), d_counts, act16, ZQ_F16, err);
+    if (rc) return rc;
+    rc = launch_gemm_fused_grouped(ctx, experts->d_down_qmaps, nullptr, H, I, act16, routes, d_items_d, (int)(max_tiles * rt_h), d_counts + 1, d_out, ZQ_F32, err);
+    if (rc) return rc;
+    if (has_shared) {
+        rc = zq_gated_mlp(ctx, shared_gate, shared_up, shared_down, dev_x, x_dtype, m, d_shared, ZQ_F32, nullptr, err);
+        if (rc) return rc;
+    }
+    combine_kernel<<<grid_for(ctx, m * H, 256), 256, 0, ctx->stream>>>(d_out, d_token_slots, d_token_w, (int)top_k, d_shared, dev_residual, dev_y, y_dtype, m, (int)H);
+    ctx->launches++;
+    ZQ_CUDA_CHECK(cudaGetLastError(), err);
     return ZQ_OK;
 }
 
@@ -527,6 +736,11 @@ int zq_moe_forward(zq_ctx *ctx, const zq_moe_experts *experts, const zq_weight *
         return ZQ_OK;
     }
 
+    // ---- prefill with Q4_K experts: grouping, gather and the two grouped GEMMs stay on the device
+    if (!ctx->force_moe_per_expert && !ctx->force_moe_host_grouping && !ctx->disable_fused_gemm && routes >= 32 * E && E <= (size_t)kGroupThreads && top_k <= 64 && experts->d_gate_qmaps &&
+        experts->gate_type == ZQ_Q4_K && experts->down_type == ZQ_Q4_K && H % kUnitWeights == 0 && I % kUnitWeights == 0)
+        return moe_prefill_device(ctx, experts, shared_gate, shared_up, shared_down, dev_x, x_dtype, m, dev_ids, dev_weights, top_k, dev_y, y_dtype, dev_residual, err);
+
     // ---- routing back to the host, token-major stable grouping (src/moe/routing.rs:136-156)
     std::vector<uint32_t> ids(routes);
     std::vector<float> wts(routes);
@@ -634,9 +848,9 @@ int zq_moe_forward(zq_ctx *ctx, const zq_moe_experts *experts, const zq_weight *
             if (rc) return rc;
             xin = x16;
         }
-        rc = launch_gemm_fused_grouped(ctx, experts->d_gate_qmaps, experts->d_up_qmaps, I, H, xin, routes, d_items, n_gated, act16, ZQ_F16, err);
+        rc = launch_gemm_fused_grouped(ctx, experts->d_gate_qmaps, experts->d_up_qmaps, I, H, xin, routes, d_items, n_gated, nullptr, act16, ZQ_F16, err);
         if (rc) return rc;
-        rc = launch_gemm_fused_grouped(ctx, experts->d_down_qmaps, nullptr, H, I, act16, routes, d_items + n_gated, n_down, d_out, ZQ_F32, err);
+        rc = launch_gemm_fused_grouped(ctx, experts->d_down_qmaps, nullptr, H, I, act16, routes, d_items + n_gated, n_down, nullptr, d_out, ZQ_F32, err);
         if (rc) return rc;
     } else if (grouped_gemm) {
         // Prefill: one grouped tensor-core GEMM per projection and chunk of experts instead of two launches per

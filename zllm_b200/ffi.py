@@ -16,6 +16,7 @@ Q5_0, Q5_1, Q3_K, IQ4_XS = 6, 7, 11, 23
 F32, F16, BF16 = 0, 1, 2
 JOB_ROW_PARALLEL = 1
 ROUTE_SOFTMAX, ROUTE_SIGMOID_BIAS, ROUTE_SQRT_SOFTPLUS_BIAS = 0, 1, 2
+MOE_NO_ROUTE = 0xFFFFFFFF  # ZQ_MOE_NO_ROUTE: an expert id that means "no route in this place"
 DIST_HANDLE_BYTES = 80
 BLOCK = {Q4_0: (32, 18), Q8_0: (32, 34), Q4_K: (256, 144), Q5_K: (256, 176), Q6_K: (256, 210), IQ4_NL: (32, 18), Q5_0: (32, 22), Q5_1: (32, 24), Q3_K: (256, 110), IQ4_XS: (256, 136)}
 
