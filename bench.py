@@ -386,10 +386,10 @@ def run_ours(args):
             return (time.perf_counter() - h0) / n
 
         t_call, t_batch = time_host(False), time_host(True)
-        e2e = {
+        e2e = {  # h2d: an input shared by several matrices of the bracket travels once
             "value": round(step_bytes / t_batch / 1e9, 2), "unit": "GB/s",
-            "h2d_bytes_per_step": sum(m * case[2] * 4 for m, case in plan), "d2h_bytes_per_step": sum(m * case[3] * 4 for m, case in plan),
-            "ms_per_step": round(t_batch * 1e3, 3), "api": "zq_batch_begin, zq_linear_host per matrix (H2D from pinned host memory, kernels, D2H to pinned host memory: enqueued), zq_batch_finish (one wait)",
+            "h2d_bytes_per_step": sum(m * k * 4 for m, k in {(m, case[2]) for m, case in plan}), "d2h_bytes_per_step": sum(m * case[3] * 4 for m, case in plan),
+            "ms_per_step": round(t_batch * 1e3, 3), "api": "zq_batch_begin, zq_linear_host per matrix (H2D from pinned host memory starts, the layer is recorded), zq_batch_finish (the recorded layers as work-list launches, D2H to pinned host memory, one wait)",
             "per_call_wait": {"value": round(step_bytes / t_call / 1e9, 2), "ms_per_step": round(t_call * 1e3, 3), "api": "zq_linear_host waiting inside every call"},
         }
 
@@ -803,6 +803,26 @@ def bench_prefill(ctx, device, args):
         flops = layers * 2 * 2.0 * m * k * n
         out[f"m{m}"] = {"ms_per_stack": round(ms, 3), "tflops": round(flops / ms / 1e9, 1)}
         del x, h0, h, y
+    # end to end through the host-buffer entry: one up-projection at 4 096 tokens, bf16 rows in page-locked host memory in
+    # and out (the copies cross PCIe inside the timed region)
+    if not args.no_e2e:
+        m = 4096
+        hx = torch.randn((m, k), dtype=torch.float32).to(torch.bfloat16).pin_memory()
+        hy = torch.empty((m, n), dtype=torch.bfloat16).pin_memory()
+
+        def host_call():
+            ffi.call("zq_linear_host", ctx.handle, ups[0].handle, C.c_void_p(hx.data_ptr()), ffi.BF16, m, C.c_void_p(hy.data_ptr()), ffi.BF16)
+
+        host_call()
+        t0 = time.perf_counter()
+        for _ in range(5):
+            host_call()
+        dt = (time.perf_counter() - t0) / 5
+        out["e2e"] = {"value": round(2.0 * m * k * n / dt / 1e12, 1), "unit": "TFLOP/s", "ms": round(dt * 1e3, 3), "h2d_bytes_per_step": m * k * 2, "d2h_bytes_per_step": m * n * 2,
+                      "api": "zq_linear_host, Q4_K 5120->17408 at 4096 tokens, bf16 in / out in page-locked host memory (waits inside the call)"}
+        del hx, hy
+    if not args.no_cpu:
+        out["cpu_baseline"] = cpu_prefill_sample()
     best = out["m16384"]["tflops"]
     out["roofline"] = {"bound": "tensor", "achieved": best, "peak": sustained, "unit": "TFLOP/s", "frac": round(best / sustained, 4), "peak_kind": kind + " (sustained bf16)", "kernel": "zq::gemm_kernel (tcgen05, M=16384, incl. operand dequantisation)"}
     out["gpu_launches"] = ctx.launch_count - launches0
@@ -881,9 +901,91 @@ def bench_moe(ctx, device, args, world, rank, only=None):
         if m_total == 64:
             entry["distinct_experts_hit_rank0"] = distinct
             entry["weight_gbs_rank0"] = round((distinct + 1) * expert_bytes / ms / 1e6, 1)
+        if world == 1 and not args.no_e2e:
+            # end to end through the public API: token rows from page-locked host memory, router, experts, result rows back
+            hx = x.cpu().pin_memory()
+            hy = torch.empty((m, H), dtype=torch.bfloat16).pin_memory()
+
+            def host_forward():
+                xd = hx.to(device, non_blocking=True)
+                ids_d, w_d = moe_route(ctx, xd, router, K, 1.0, True)
+                yd = moe_forward(ctx, table, xd, ids_d, w_d, shared=shared, out_dtype=torch.bfloat16)
+                ctx.sync()
+                hy.copy_(yd, non_blocking=True)
+                torch.cuda.synchronize()
+
+            host_forward()
+            t0 = time.perf_counter()
+            for _ in range(3):
+                host_forward()
+            dt = (time.perf_counter() - t0) / 3
+            entry["e2e"] = {"value": round(flops / dt / 1e12, 2), "unit": "TFLOP/s", "ms": round(dt * 1e3, 3), "h2d_bytes_per_step": m * H * 2, "d2h_bytes_per_step": m * H * 2,
+                            "api": "moe_route + moe_forward (zq_moe_route_softmax_topk, zq_moe_forward) on rows copied from / to page-locked host memory inside the timed region"}
+            del hx, hy
         out[name] = entry
         del x_all, x, y
+    if world == 1 and rank == 0 and not args.no_cpu:
+        out["cpu_baseline"] = cpu_moe_sample()
     return out
+
+
+def _random_q4k_bytes(rng, rows, cols):
+    """Random Q4_K bytes with small finite scales: CPU time does not depend on the values."""
+    import numpy as np
+
+    data = rng.integers(0, 256, size=(rows * cols // 256, 144), dtype=np.uint8)
+    data[:, 0:2] = np.frombuffer(np.float16(0.01).tobytes(), dtype=np.uint8)
+    data[:, 2:4] = np.frombuffer(np.float16(0.01).tobytes(), dtype=np.uint8)
+    return data.reshape(-1)
+
+
+def cpu_prefill_sample():
+    """ggml_quant::matmul (src/kernel/cpu/ggml_quant.rs:280-315) on the host cores: Q4_K 5120->17408 at 16 tokens."""
+    import numpy as np
+
+    from oracle import oracle as orc
+
+    orc.set_threads(0)
+    k, n, m = 5120, 17408, 16
+    rng = np.random.default_rng(0)
+    data = _random_q4k_bytes(rng, n, k)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    orc.linear(Q4_K, data, n, k, x)  # untimed: page in, start the worker threads
+    t0 = time.perf_counter()
+    passes = 0
+    while passes < 3 or time.perf_counter() - t0 < 4.0:
+        orc.linear(Q4_K, data, n, k, x)
+        passes += 1
+    dt = time.perf_counter() - t0
+    return {"value": round(2.0 * m * n * k * passes / dt / 1e12, 4), "unit": "TFLOP/s", "cores": orc.threads(), "kind": "port", "sample": f"Q4_K 5120->17408 at {m} tokens, {passes} passes after one warm-up pass", "seconds": round(dt, 2)}
+
+
+def cpu_moe_sample():
+    """The CPU MoE path (src/kernel/cpu/moe.rs:122-138: per token, per routed expert, three matvecs) on the host cores:
+    8 experts of the configured shape, every token routed to all 8, 4 tokens."""
+    import numpy as np
+
+    from oracle import oracle as orc
+
+    orc.set_threads(0)
+    E, K, H, I, m = 8, 8, 7168, 2048, 4
+    rng = np.random.default_rng(0)
+    gates = [(Q4_K, _random_q4k_bytes(rng, I, H), I, H) for _ in range(E)]
+    ups = [(Q4_K, _random_q4k_bytes(rng, I, H), I, H) for _ in range(E)]
+    downs = [(Q4_K, _random_q4k_bytes(rng, H, I), H, I) for _ in range(E)]
+    x = rng.standard_normal((m, H)).astype(np.float32)
+    ids = np.tile(np.arange(E, dtype=np.uint32), (m, 1))
+    w = np.full((m, K), 1.0 / K, dtype=np.float32)
+    orc.moe_forward(gates, ups, downs, x, ids, w)
+    t0 = time.perf_counter()
+    passes = 0
+    while passes < 2 or time.perf_counter() - t0 < 4.0:
+        orc.moe_forward(gates, ups, downs, x, ids, w)
+        passes += 1
+    dt = time.perf_counter() - t0
+    flops = m * K * 3 * 2.0 * H * I * passes
+    return {"value": round(flops / dt / 1e12, 5), "unit": "TFLOP/s", "tokens_per_s": round(m * passes / dt, 2), "cores": orc.threads(), "kind": "port",
+            "sample": f"{E} experts of the configured shape, {m} tokens each routed to all {K}, {passes} passes after one warm-up pass", "seconds": round(dt, 2)}
 
 
 def _cpu_sweep(batches, repeat_seed=0):

@@ -175,12 +175,14 @@ int zq_linear_noalloc(zq_ctx *ctx, const zq_weight *w, const void *dev_x, int x_
 int zq_linear_host(zq_ctx *ctx, const zq_weight *w, const void *host_x, int x_dtype, size_t m, void *host_y, int y_dtype, zq_error *err);
 
 /* Backend::begin_batch / finish_batch (src/backend/mod.rs:307-323; the reference's Vulkan backend defers its command
- * submission the same way, src/backend/vulkan/mod.rs:194-215).  Between the two calls zq_linear_host only ENQUEUES its
- * copy in, its kernels and its copy out; zq_batch_finish waits once for everything enqueued and then fills the
- * callers' output buffers, which must stay valid and must not be read until then.  Pageable input buffers may be reused
+ * submission the same way, src/backend/vulkan/mod.rs:194-215).  Between the two calls zq_linear_host only starts its
+ * copy in and records the layer; zq_batch_finish runs the recorded layers as one zq_linear_batch (several matrices per
+ * kernel launch), copies the results out, waits once and then fills the callers' output buffers, which must stay valid
+ * and must not be read until then.  An error of a recorded layer is reported by the finish; any error closes the bracket.  Pageable input buffers may be reused
  * as soon as their zq_linear_host call returns (they are copied into the library's staging memory inside the call);
  * page-locked input buffers (cudaHostAlloc, cudaHostRegister, a pinned tensor) are read by the GPU's copy engine
- * directly and must stay untouched until zq_batch_finish returns. */
+ * directly and must stay untouched until zq_batch_finish returns (the same page-locked input given to several calls
+ * of one bracket is copied once). */
 int zq_batch_begin(zq_ctx *ctx, zq_error *err);
 int zq_batch_finish(zq_ctx *ctx, zq_error *err);
 

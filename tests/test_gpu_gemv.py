@@ -236,3 +236,49 @@ def test_batch_bracket_defers_host_results_to_finish():
     from zllm_b200 import ffi
     with pytest.raises(ffi.ZqFailure):
         ctx().finish_batch()  # no bracket open
+
+
+def test_batch_bracket_with_page_locked_buffers_and_a_shared_input():
+    """Page-locked caller buffers are copied from / to directly; one page-locked input given to several layers of a
+    bracket travels once; the bracket's layers run as one batch at the finish.  Also a mixed bracket (f32 and f16
+    inputs, a prefill-sized layer among the decode ones) and the same call outside a bracket."""
+    rows, cols = 384, 1024
+    types = (H.Q4_K, H.Q4_0, H.Q8_0, H.IQ4_NL)
+    datas = [H.random_weight(t, rows, cols, seed=120 + i) for i, t in enumerate(types)]
+    ws = [ctx().prepare_weight(t, d, rows, cols) for t, d in zip(types, datas)]
+    x_t = torch.from_numpy(np.random.default_rng(121).standard_normal((3, cols)).astype(np.float32)).pin_memory()
+    x16_t = x_t.to(torch.float16).pin_memory()
+    big_t = torch.from_numpy(np.random.default_rng(122).standard_normal((40, cols)).astype(np.float32)).pin_memory()
+    ys = [torch.zeros((3, rows), dtype=torch.float32).pin_memory() for _ in types]
+    y16 = torch.zeros((3, rows), dtype=torch.float32).pin_memory()
+    ybig = np.zeros((40, rows), dtype=np.float32)  # pageable output
+    ctx().begin_batch()
+    for w, y in zip(ws, ys):
+        ctx().linear_host(x_t.numpy(), w, y.numpy())
+    ctx().linear_host(x16_t.numpy(), ws[0], y16.numpy())
+    ctx().linear_host(big_t.numpy(), ws[2], ybig)
+    ctx().finish_batch()
+    for t, d, y in zip(types, datas, ys):
+        _check(y.numpy(), orc.linear(t, d, rows, cols, x_t.numpy()))
+    _check(y16.numpy(), orc.linear(types[0], datas[0], rows, cols, x16_t.float().numpy()))
+    assert H.max_rel_error(ybig, orc.linear(types[2], datas[2], rows, cols, big_t.numpy())) <= BOUND
+    y_out = torch.zeros((3, rows), dtype=torch.float32).pin_memory()
+    ctx().linear_host(x_t.numpy(), ws[1], y_out.numpy())  # outside a bracket: waits inside the call
+    _check(y_out.numpy(), orc.linear(types[1], datas[1], rows, cols, x_t.numpy()))
+
+
+def test_an_error_inside_a_bracket_closes_it():
+    from zllm_b200 import ffi
+
+    w = ctx().prepare_weight(H.Q4_K, H.random_weight(H.Q4_K, 64, 256, seed=130), 64, 256)
+    x = np.zeros((1, 256), dtype=np.float32)
+    y = np.zeros((1, 64), dtype=np.float32)
+    ctx().begin_batch()
+    ctx().linear_host(x, w, y)
+    with pytest.raises(ffi.ZqFailure):
+        ffi.call("zq_linear_host", ctx().handle, w.handle, x.ctypes.data_as(__import__("ctypes").c_void_p), 7, 1, y.ctypes.data_as(__import__("ctypes").c_void_p), ffi.F32)  # unknown dtype
+    with pytest.raises(ffi.ZqFailure):
+        ctx().finish_batch()  # the failed call closed the bracket
+    ctx().begin_batch()       # and a new one opens cleanly
+    ctx().linear_host(x, w, y)
+    ctx().finish_batch()

@@ -444,7 +444,8 @@ int zq_linear_batch(zq_ctx *ctx, const zq_linear_job *jobs, size_t n_jobs, int x
             jy = ZQ_F32;
         }
         WlHostJob h = {j.w, j.w_up, j.dev_x, j.m, j.dev_y, j.dev_residual, jy};
-        if (!ctx->disable_worklist && gemv_wl_supported(ctx, h)) {
+        // the diagnostic switches that pick a decode kernel hold for batches too: with one set, every job runs alone on it
+        if (!ctx->disable_worklist && !ctx->force_f16_gemv && !ctx->force_staged_gemv && !ctx->enable_tcgen05_gemv && gemv_wl_supported(ctx, h)) {
             listed.push_back(h);
         } else {
             alone.push_back(j);
@@ -566,6 +567,43 @@ static int batch_io_alloc(zq_ctx *ctx, size_t bytes, uint8_t **pinned, uint8_t *
     return ZQ_OK;
 }
 
+// Drops whatever an open bracket holds: waits for what was enqueued, fills no output, forgets every caller pointer.
+static void batch_abandon(zq_ctx *ctx) {
+    cudaStreamSynchronize(ctx->stream);
+    ctx->pending_out.clear();
+    ctx->pending_linear.clear();
+    ctx->pending_in.clear();
+    for (auto &c : ctx->io_chunks) c.used = 0;
+    ctx->batch_active = false;
+}
+
+// Runs the bracket's deferred layers: one zq_linear_batch call per run of layers with the same dtypes (in call order),
+// then the copies out.
+static int batch_flush(zq_ctx *ctx, zq_error *err) {
+    size_t i = 0;
+    std::vector<zq_linear_job> jobs;
+    while (i < ctx->pending_linear.size()) {
+        const int xd = ctx->pending_linear[i].x_dtype, yd = ctx->pending_linear[i].y_dtype;
+        size_t e = i;
+        jobs.clear();
+        while (e < ctx->pending_linear.size() && ctx->pending_linear[e].x_dtype == xd && ctx->pending_linear[e].y_dtype == yd) {
+            const zq_ctx::PendingLinear &p = ctx->pending_linear[e];
+            zq_linear_job j = {p.w, nullptr, p.dev_x, p.m, p.dev_y, nullptr, 0};
+            jobs.push_back(j);
+            ++e;
+        }
+        int rc = zq_linear_batch(ctx, jobs.data(), jobs.size(), xd, yd, err);
+        if (rc) return rc;
+        for (size_t k = i; k < e; ++k) {
+            const zq_ctx::PendingLinear &p = ctx->pending_linear[k];
+            ZQ_CUDA_CHECK(cudaMemcpyAsync(p.host_y_direct, p.dev_y, p.y_bytes, cudaMemcpyDeviceToHost, ctx->stream), err);
+        }
+        i = e;
+    }
+    ctx->pending_linear.clear();
+    return ZQ_OK;
+}
+
 int zq_batch_begin(zq_ctx *ctx, zq_error *err) {
     if (!ctx) return set_error(err, ZQ_ERR_ARG, "zq_batch_begin: null context");
     if (ctx->batch_active) return set_error(err, ZQ_ERR_ARG, "zq_batch_begin: a batch is already open");
@@ -576,29 +614,46 @@ int zq_batch_begin(zq_ctx *ctx, zq_error *err) {
 int zq_batch_finish(zq_ctx *ctx, zq_error *err) {
     if (!ctx) return set_error(err, ZQ_ERR_ARG, "zq_batch_finish: null context");
     if (!ctx->batch_active) return set_error(err, ZQ_ERR_ARG, "zq_batch_finish: no batch is open");
+    int rc = batch_flush(ctx, err);
+    if (!rc) rc = zq_ctx_sync(ctx, err);
+    if (rc) {
+        batch_abandon(ctx);
+        return rc;
+    }
     ctx->batch_active = false;
-    int rc = zq_ctx_sync(ctx, err);
-    if (!rc)
-        for (const auto &o : ctx->pending_out) memcpy(o.host, o.pinned, o.bytes);
+    for (const auto &o : ctx->pending_out) memcpy(o.host, o.pinned, o.bytes);
     ctx->pending_out.clear();
+    ctx->pending_in.clear();
     for (auto &c : ctx->io_chunks) c.used = 0;
-    return rc;
+    return ZQ_OK;
 }
 
 int zq_linear_host(zq_ctx *ctx, const zq_weight *w, const void *host_x, int x_dtype, size_t m, void *host_y, int y_dtype, zq_error *err) {
     if (!ctx || !w || !host_x || !host_y) return set_error(err, ZQ_ERR_ARG, "zq_linear_host: null argument");
     int rc = check_dtype(x_dtype, "linear input", err);
     if (!rc) rc = check_dtype(y_dtype, "linear output", err);
-    if (rc) return rc;
+    if (!rc && w->ctx != ctx) rc = set_error(err, ZQ_ERR_ARG, "zq_linear_host: weight belongs to another context");
+    if (!rc && m == 0) rc = set_error(err, ZQ_ERR_SHAPE, "zq_linear_host: no activation rows");
+    if (rc) {
+        if (ctx->batch_active) batch_abandon(ctx);  // a failed call closes the bracket
+        return rc;
+    }
     size_t xb = m * w->cols * dtype_size(x_dtype), yb = m * w->rows * dtype_size(y_dtype);
     size_t xb_al = (xb + 255) & ~size_t(255);
     const bool x_pinned = is_pinned_host(host_x), y_pinned = is_pinned_host(host_y);
     if (ctx->batch_active) {
-        // inside a bracket: copy in, run and copy out are only enqueued; the bracket's finish waits once for all of them
-        // and hands the results to the callers' buffers.  Page-locked caller buffers are copied from / to directly.
-        uint8_t *px, *dx;
-        rc = batch_io_alloc(ctx, xb_al + yb, &px, &dx, err);
-        if (!rc) {
+        // Inside a bracket the input starts its way to the device now and the layer itself is deferred: the finish runs
+        // the bracket's layers as one batch (work-list launches: several matrices per kernel), copies the results out
+        // and waits once.  Page-locked caller buffers are copied from / to directly; a page-locked input that an earlier
+        // call of the bracket already brought over is not copied again (it must stay unchanged until the finish).
+        const uint8_t *dev_in = nullptr;
+        if (x_pinned)
+            for (const auto &pi : ctx->pending_in)
+                if (pi.host == host_x && pi.bytes == xb) dev_in = pi.dev;
+        uint8_t *px = nullptr, *dx = nullptr;
+        rc = use_device(ctx, err);
+        if (!rc) rc = batch_io_alloc(ctx, (dev_in ? 0 : xb_al) + yb, &px, &dx, err);
+        if (!rc && !dev_in) {
             const void *src = host_x;
             if (!x_pinned) {
                 memcpy(px, host_x, xb);
@@ -606,22 +661,15 @@ int zq_linear_host(zq_ctx *ctx, const zq_weight *w, const void *host_x, int x_dt
             }
             cudaError_t ce = cudaMemcpyAsync(dx, src, xb, cudaMemcpyHostToDevice, ctx->stream);
             if (ce != cudaSuccess) rc = set_error(err, ZQ_ERR_CUDA, "zq_linear_host: copy in failed: %s", cudaGetErrorString(ce));
-        }
-        if (!rc) rc = zq_linear(ctx, w, dx, x_dtype, m, dx + xb_al, y_dtype, nullptr, err);
-        if (!rc) {
-            cudaError_t ce = cudaMemcpyAsync(y_pinned ? host_y : px + xb_al, dx + xb_al, yb, cudaMemcpyDeviceToHost, ctx->stream);
-            if (ce != cudaSuccess) rc = set_error(err, ZQ_ERR_CUDA, "zq_linear_host: copy out failed: %s", cudaGetErrorString(ce));
+            if (!rc && x_pinned) ctx->pending_in.push_back({host_x, xb, dx});
         }
         if (rc) {
-            // a failed call closes the bracket: what was enqueued is waited for and dropped (no output buffer of the
-            // bracket is filled), so that no caller pointer outlives the error
-            cudaStreamSynchronize(ctx->stream);
-            ctx->pending_out.clear();
-            for (auto &c : ctx->io_chunks) c.used = 0;
-            ctx->batch_active = false;
+            batch_abandon(ctx);
             return rc;
         }
-        if (!y_pinned) ctx->pending_out.push_back({host_y, px + xb_al, yb});
+        const size_t y_off = dev_in ? 0 : xb_al;
+        ctx->pending_linear.push_back({w, dev_in ? dev_in : dx, m, dx + y_off, y_pinned ? host_y : px + y_off, yb, x_dtype, y_dtype});
+        if (!y_pinned) ctx->pending_out.push_back({host_y, px + y_off, yb});
         return ZQ_OK;
     }
     if (ctx->host_io_bytes < xb_al + yb) {

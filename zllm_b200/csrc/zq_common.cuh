@@ -260,8 +260,14 @@ struct zq_ctx {
     // defer their copy-out to the finish.
     struct IoChunk { uint8_t *pinned; uint8_t *dev; size_t bytes, used; };
     struct PendingOut { void *host; const uint8_t *pinned; size_t bytes; };
+    // A host-buffer linear of an open bracket: its input is already on its way to `dev_x`; the layer itself runs at the
+    // bracket's finish, together with the bracket's other layers, as one zq_linear_batch call (work-list launches).
+    struct PendingLinear { const zq_weight *w; const uint8_t *dev_x; size_t m; uint8_t *dev_y; void *host_y_direct; size_t y_bytes; int x_dtype, y_dtype; };
+    struct PendingIn { const void *host; size_t bytes; const uint8_t *dev; };  // page-locked inputs already copied in this bracket
     std::vector<IoChunk> io_chunks;
     std::vector<PendingOut> pending_out;
+    std::vector<PendingLinear> pending_linear;
+    std::vector<PendingIn> pending_in;
     bool batch_active = false;
     // Diagnostics: 1 = always use the per-item activation staging GEMV (the variant for activations too large to
     // stay resident in shared memory), so that tests can cover it at small sizes.
