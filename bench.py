@@ -389,7 +389,7 @@ def run_ours(args):
         e2e = {  # h2d: an input shared by several matrices of the bracket travels once
             "value": round(step_bytes / t_batch / 1e9, 2), "unit": "GB/s",
             "h2d_bytes_per_step": sum(m * k * 4 for m, k in {(m, case[2]) for m, case in plan}), "d2h_bytes_per_step": sum(m * case[3] * 4 for m, case in plan),
-            "ms_per_step": round(t_batch * 1e3, 3), "api": "zq_batch_begin, zq_linear_host per matrix (H2D from pinned host memory starts, the layer is recorded), zq_batch_finish (the recorded layers as work-list launches, D2H to pinned host memory, one wait)",
+            "ms_per_step": round(t_batch * 1e3, 3), "api": "zq_batch_begin, zq_linear_host per matrix (H2D from pinned host memory starts, the layer is recorded), layers launched as work-list batches once a launch-worth is pending, D2H to pinned host memory; zq_batch_finish (the rest, one wait)",
             "per_call_wait": {"value": round(step_bytes / t_call / 1e9, 2), "ms_per_step": round(t_call * 1e3, 3), "api": "zq_linear_host waiting inside every call"},
         }
 

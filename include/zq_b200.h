@@ -176,9 +176,10 @@ int zq_linear_host(zq_ctx *ctx, const zq_weight *w, const void *host_x, int x_dt
 
 /* Backend::begin_batch / finish_batch (src/backend/mod.rs:307-323; the reference's Vulkan backend defers its command
  * submission the same way, src/backend/vulkan/mod.rs:194-215).  Between the two calls zq_linear_host only starts its
- * copy in and records the layer; zq_batch_finish runs the recorded layers as one zq_linear_batch (several matrices per
- * kernel launch), copies the results out, waits once and then fills the callers' output buffers, which must stay valid
- * and must not be read until then.  An error of a recorded layer is reported by the finish; any error closes the bracket.  Pageable input buffers may be reused
+ * copy in and records the layer; recorded layers run as zq_linear_batch calls (several matrices per kernel launch),
+ * as soon as a launch's worth of them is pending and the rest at zq_batch_finish, which copies the last results out,
+ * waits once and then fills the callers' output buffers; these must stay valid and must not be read until then.  An
+ * error of a recorded layer is reported by the call that launches it or by the finish; any error closes the bracket.  Pageable input buffers may be reused
  * as soon as their zq_linear_host call returns (they are copied into the library's staging memory inside the call);
  * page-locked input buffers (cudaHostAlloc, cudaHostRegister, a pinned tensor) are read by the GPU's copy engine
  * directly and must stay untouched until zq_batch_finish returns (the same page-locked input given to several calls

@@ -35,6 +35,30 @@ def test_router_matches_cpu_softmax_topk(m, experts, top_k, hidden, normalize):
     np.testing.assert_allclose(w.cpu().numpy(), want_w, rtol=2e-5, atol=1e-7)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("m,experts,top_k,hidden", [(5, 16, 4, 256), (64, 256, 8, 1024), (13, 200, 6, 7168)])
+def test_router_with_half_precision_rows(m, experts, top_k, hidden, dtype):
+    """Decode-sized batches of f16 / bf16 rows take the kernel that keeps the rows as 16-bit values in shared memory; the
+    oracle sees the same rounded rows, and a bias takes part in the softmax."""
+    from zllm_b200.backend import moe_route
+
+    rng = np.random.default_rng(3 * m + experts)
+    x = torch.from_numpy(rng.standard_normal((m, hidden)).astype(np.float32)).to(dtype)
+    router = (rng.standard_normal((experts, hidden)) / np.sqrt(hidden)).astype(np.float32)
+    bias = (0.1 * rng.standard_normal(experts)).astype(np.float32)
+    ids, w = moe_route(ctx(), x.cuda(), dev(router), top_k, 1.0, True, bias=dev(bias))
+    ctx().sync()
+    logits = (x.float().numpy().astype(np.float64) @ router.astype(np.float64).T + bias).astype(np.float32)
+    rows = [orc.route_softmax_logits(logits[t], top_k, 1.0, True) for t in range(m)]
+    want_ids, want_w = np.stack([r[0] for r in rows]).reshape(m, top_k), np.stack([r[1] for r in rows]).reshape(m, top_k)
+    # a near-tie may order differently in f32 and f64 logits: compare where the logit gap is clear
+    order = np.sort(logits, axis=1)[:, ::-1]
+    clear = np.all(np.abs(np.diff(order[:, :top_k + 1], axis=1)) > 1e-5, axis=1)
+    assert clear.mean() > 0.9
+    assert np.array_equal(ids.cpu().numpy().astype(np.uint32)[clear], want_ids[clear])
+    np.testing.assert_allclose(w.cpu().numpy()[clear], want_w[clear], rtol=1e-4, atol=1e-6)
+
+
 def test_router_breaks_ties_by_lower_expert_id():
     from zllm_b200.backend import moe_route
 

@@ -667,9 +667,32 @@ int zq_linear_host(zq_ctx *ctx, const zq_weight *w, const void *host_x, int x_dt
             batch_abandon(ctx);
             return rc;
         }
+        // The GPU should not sit idle while the host records a long bracket: what is pending goes out as soon as it is a
+        // launch's worth, i.e. when the next layer is of another kernel class (weight type, row-count class, dtypes) or
+        // when the pending weights pass ~160 MB (tens of microseconds of streaming).
+        auto row_class = [](size_t rows) { return rows <= 4 ? 1 : rows <= 8 ? 2 : rows <= 16 ? 4 : 0; };
+        if (!ctx->pending_linear.empty()) {
+            const zq_ctx::PendingLinear &last = ctx->pending_linear.back();
+            if (last.w->type != w->type || row_class(last.m) != row_class(m) || last.x_dtype != x_dtype || last.y_dtype != y_dtype) {
+                rc = batch_flush(ctx, err);
+                if (rc) {
+                    batch_abandon(ctx);
+                    return rc;
+                }
+            }
+        }
         const size_t y_off = dev_in ? 0 : xb_al;
         ctx->pending_linear.push_back({w, dev_in ? dev_in : dx, m, dx + y_off, y_pinned ? host_y : px + y_off, yb, x_dtype, y_dtype});
         if (!y_pinned) ctx->pending_out.push_back({host_y, px + y_off, yb});
+        size_t pending_bytes = 0;
+        for (const auto &p : ctx->pending_linear) pending_bytes += p.w->gguf_bytes;
+        if (pending_bytes >= (size_t(160) << 20)) {
+            rc = batch_flush(ctx, err);
+            if (rc) {
+                batch_abandon(ctx);
+                return rc;
+            }
+        }
         return ZQ_OK;
     }
     if (ctx->host_io_bytes < xb_al + yb) {

@@ -174,11 +174,24 @@ __global__ void __launch_bounds__(kRouterThreads) router_topk_kernel(const void 
         float acc[kRouterTokens];
 #pragma unroll
         for (int t = 0; t < kRouterTokens; ++t) acc[t] = 0.f;
+        if ((hidden & 127) == 0) {  // 16-byte loads of the router row, several in flight per lane
+            const float4 *w4 = reinterpret_cast<const float4 *>(w);
 #pragma unroll 8
-        for (int c = lane; c < hidden; c += 32) {
-            const float wv = w[c];
+            for (int c4 = lane; c4 < hidden / 4; c4 += 32) {
+                const float4 wv = __ldg(w4 + c4);
 #pragma unroll
-            for (int t = 0; t < kRouterTokens; ++t) acc[t] = fmaf(xs[t * hidden + c], wv, acc[t]);
+                for (int t = 0; t < kRouterTokens; ++t) {
+                    const float4 xv = reinterpret_cast<const float4 *>(xs + t * hidden)[c4];
+                    acc[t] = fmaf(xv.w, wv.w, fmaf(xv.z, wv.z, fmaf(xv.y, wv.y, fmaf(xv.x, wv.x, acc[t]))));
+                }
+            }
+        } else {
+#pragma unroll 8
+            for (int c = lane; c < hidden; c += 32) {
+                const float wv = w[c];
+#pragma unroll
+                for (int t = 0; t < kRouterTokens; ++t) acc[t] = fmaf(xs[t * hidden + c], wv, acc[t]);
+            }
         }
 #pragma unroll
         for (int t = 0; t < kRouterTokens; ++t) {
@@ -198,6 +211,57 @@ __global__ void __launch_bounds__(kRouterThreads) router_topk_kernel(const void 
     __syncthreads();
     if (warp < kRouterTokens && tok0 + warp < m)
         router_select(logits + warp * num_experts, lane, num_experts, top_k, scaling, normalize_selected, ids + (size_t)(tok0 + warp) * top_k, weights + (size_t)(tok0 + warp) * top_k, status, scoring, bias);
+}
+
+// Few tokens with f16 / bf16 activations (MoE decode): eight tokens per CTA kept as 16-bit values in shared memory
+// (half the footprint of the f32 staging above, so half as many token blocks re-read the router matrix), one expert per
+// warp and round, 16-byte loads of the router row.  Writes logits only; router_select_kernel finishes.
+constexpr int kRouter16Tokens = 8;
+__global__ void __launch_bounds__(kRouterThreads) router_logits16_kernel(const uint16_t *__restrict__ x, int x_dtype, int m, int hidden, const float *__restrict__ router, int num_experts, int experts_per_cta,
+                                                                          float *__restrict__ logits_g) {
+    extern __shared__ float rsm[];
+    uint16_t *xs = reinterpret_cast<uint16_t *>(rsm);  // [kRouter16Tokens][hidden]
+    const int tok0 = blockIdx.x * kRouter16Tokens;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int e_begin = blockIdx.y * experts_per_cta;
+    const int e_end = e_begin + experts_per_cta < num_experts ? e_begin + experts_per_cta : num_experts;
+    const int vec_per_row = hidden / 8;
+    for (int i = threadIdx.x; i < kRouter16Tokens * vec_per_row; i += kRouterThreads) {
+        const int t = i / vec_per_row, v = i - t * vec_per_row;
+        uint4 raw = make_uint4(0, 0, 0, 0);
+        if (tok0 + t < m) raw = reinterpret_cast<const uint4 *>(x + (size_t)(tok0 + t) * hidden)[v];
+        reinterpret_cast<uint4 *>(xs + (size_t)t * hidden)[v] = raw;
+    }
+    __syncthreads();
+    for (int e = e_begin + warp; e < e_end; e += kRouterThreads / 32) {
+        const float4 *w4 = reinterpret_cast<const float4 *>(router + (size_t)e * hidden);
+        float acc[kRouter16Tokens];
+#pragma unroll
+        for (int t = 0; t < kRouter16Tokens; ++t) acc[t] = 0.f;
+#pragma unroll 4
+        for (int c4 = lane; c4 < hidden / 4; c4 += 32) {
+            const float4 wv = __ldg(w4 + c4);
+#pragma unroll
+            for (int t = 0; t < kRouter16Tokens; ++t) {
+                const uint2 raw = reinterpret_cast<const uint2 *>(xs + (size_t)t * hidden)[c4];
+                float x0, x1, x2, x3;
+                if (x_dtype == ZQ_F16) {
+                    const float2 a = __half22float2(u32_as_h2(raw.x)), b = __half22float2(u32_as_h2(raw.y));
+                    x0 = a.x; x1 = a.y; x2 = b.x; x3 = b.y;
+                } else {  // bf16: the upper half of an f32
+                    x0 = __uint_as_float(raw.x << 16); x1 = __uint_as_float(raw.x & 0xFFFF0000u);
+                    x2 = __uint_as_float(raw.y << 16); x3 = __uint_as_float(raw.y & 0xFFFF0000u);
+                }
+                acc[t] = fmaf(x3, wv.w, fmaf(x2, wv.z, fmaf(x1, wv.y, fmaf(x0, wv.x, acc[t]))));
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < kRouter16Tokens; ++t) {
+            float v = acc[t];
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0 && tok0 + t < m) logits_g[(size_t)(tok0 + t) * num_experts + e] = v;
+        }
+    }
 }
 
 // Router logits on the tensor cores for prefill-sized batches.  f16 operands alone would move logits by ~1e-3 and
@@ -572,6 +636,30 @@ int zq_moe_route_topk(zq_ctx *ctx, int scoring, const void *dev_x, int x_dtype, 
         ZQ_CUDA_CHECK(cudaGetLastError(), err);
         rc = launch_gemm_f16(ctx, w3, num_experts, 3 * hidden, x3, m, logits_g, ZQ_F32, err);
         if (rc) return rc;
+        const unsigned sel_grid = (unsigned)((m + kRouterThreads / 32 - 1) / (kRouterThreads / 32));
+        router_select_kernel<<<sel_grid, kRouterThreads, (kRouterThreads / 32) * num_experts * sizeof(float), ctx->stream>>>(logits_g, dev_bias_f32, (int)m, (int)num_experts, (int)top_k, scaling_factor, normalize_selected, dev_ids,
+                                                                                                                            dev_weights, ctx->status_dev, scoring);
+        ctx->launches++;
+        ZQ_CUDA_CHECK(cudaGetLastError(), err);
+        return ZQ_OK;
+    }
+    if (blocks_y > 1 && x_dtype != ZQ_F32 && hidden % 128 == 0 && (size_t)kRouter16Tokens * hidden * 2 <= 200 * 1024) {
+        int rc = ensure_moe_ws(ctx, m * num_experts * sizeof(float), err);
+        if (rc) return rc;
+        float *logits_g = reinterpret_cast<float *>(ctx->moe_ws);
+        static bool configured16[64] = {};
+        if (!configured16[ctx->device & 63]) {
+            ZQ_CUDA_CHECK(cudaFuncSetAttribute(router_logits16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024), err);
+            configured16[ctx->device & 63] = true;
+        }
+        const size_t grid16 = (m + kRouter16Tokens - 1) / kRouter16Tokens;
+        size_t by = (2 * (size_t)ctx->sm_count + grid16 - 1) / grid16;
+        size_t per16 = ((num_experts + by - 1) / by + 7) & ~size_t(7);  // whole rounds of the 8 warps
+        by = (num_experts + per16 - 1) / per16;
+        router_logits16_kernel<<<dim3((unsigned)grid16, (unsigned)by), kRouterThreads, (size_t)kRouter16Tokens * hidden * 2, ctx->stream>>>(reinterpret_cast<const uint16_t *>(dev_x), x_dtype, (int)m, (int)hidden, dev_router_f32,
+                                                                                                                                         (int)num_experts, (int)per16, logits_g);
+        ctx->launches++;
+        ZQ_CUDA_CHECK(cudaGetLastError(), err);
         const unsigned sel_grid = (unsigned)((m + kRouterThreads / 32 - 1) / (kRouterThreads / 32));
         router_select_kernel<<<sel_grid, kRouterThreads, (kRouterThreads / 32) * num_experts * sizeof(float), ctx->stream>>>(logits_g, dev_bias_f32, (int)m, (int)num_experts, (int)top_k, scaling_factor, normalize_selected, dev_ids,
                                                                                                                             dev_weights, ctx->status_dev, scoring);
