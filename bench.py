@@ -145,7 +145,7 @@ def run_ours(args):
         return
 
     if args.only_kquant:
-        print(json.dumps({"only_kquant": bench_kquant_decode(ctx, device), "launches": ctx.launch_count}))
+        print(json.dumps({"only_kquant": bench_kquant_decode(ctx, device, read_peaks()[0]), "launches": ctx.launch_count}))
         return
 
     if args.only_moe:
@@ -406,7 +406,7 @@ def run_ours(args):
         if world == 1 and args.extras in ("all", "prefill"):
             extras["prefill_gemm"] = bench_prefill(ctx, device, args)
         if world == 1 and args.extras in ("all", "prefill"):
-            extras["kquant_decode"] = bench_kquant_decode(ctx, device)
+            extras["kquant_decode"] = bench_kquant_decode(ctx, device, hbm_peak)
         if world == 1 and args.extras in ("all", "configs"):
             sustained = hbm_peak
             peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -723,9 +723,9 @@ def bench_config3(ctx, device, hbm_peak, sustained_tflops):
     return out
 
 
-def bench_kquant_decode(ctx, device):
-    """Q5_K and Q6_K, one activation row, 5120 -> 17408 (the CUDA-core decode kernel of these two types): four distinct
-    weights (245 / 292 MB, larger than L2) used in turn; GB/s of GGUF bytes."""
+def bench_kquant_decode(ctx, device, hbm_peak=6545.9):
+    """Q5_K and Q6_K, one activation row, 5120 -> 17408 (integer-MMA decode kernel, one launch per matrix): four
+    distinct weights (245 / 292 MB, larger than L2) used in turn; GB/s of GGUF bytes."""
     import numpy as np
     import torch
 
@@ -754,8 +754,10 @@ def bench_kquant_decode(ctx, device):
 
         sweep()
         ms = _time_ms(sweep, 5) / len(weights)
-        out[name] = {"us_per_launch": round(ms * 1e3, 2), "gbs": round(n * k // e * b / ms / 1e6, 1)}
+        gbs = n * k // e * b / ms / 1e6
+        out[name] = {"us_per_launch": round(ms * 1e3, 2), "gbs": round(gbs, 1), "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": hbm_peak, "unit": "GB/s", "frac": round(gbs / hbm_peak, 4)}}
         del weights
+    out["kernel"] = "zq::gemv_i8_kernel<Q5_K / Q6_K, 1 column tile>"
     return out
 
 

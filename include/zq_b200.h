@@ -30,13 +30,14 @@ typedef struct zq_moe_experts zq_moe_experts;
 
 typedef struct zq_error { char message[512]; } zq_error;
 
-/* GGUF tensor type ids (src/weight/container/gguf.rs:112-151).  Q5_K and Q6_K (src/weight/codec/ggml.rs:425-469;
- * reference CUDA kernels src/kernel/cuda/linear.rs:1167-1234, 1967-2101) dequantise bit-exactly; zq_linear with up to
- * 8 activation rows runs a CUDA-core decode kernel on the packed bytes, more rows and gated pairs the f16 operand pass
- * and the tensor-core GEMM.  They have no encoder (zq_quantize) and no allocation-free entry.  Q5_0 / Q5_1 (types 6, 7,
- * which the reference CUDA backend accepts, src/backend/cuda/mod.rs:62-72), Q3_K (11) and IQ4_XS (23)
+/* GGUF tensor type ids (src/weight/container/gguf.rs:112-151).  Q4_K, Q4_0, Q8_0, IQ4_NL, Q5_K and Q6_K
+ * (src/weight/codec/ggml.rs:102-109, 229-244, 408-469; reference CUDA kernels src/kernel/cuda/linear.rs:139-294, 1167-1234,
+ * 1967-2101) decode (up to 16 activation rows, plain, residual and gated) on the integer-MMA kernels; all dequantise
+ * bit-exactly.  Q5_K and Q6_K have no encoder (zq_quantize) and no allocation-free entry; Q6_K is re-laid into 224-byte
+ * units at prepare time (zq_weight_gguf_bytes still reports the 210-byte packing).  Q5_0 / Q5_1 (types 6, 7, which the
+ * reference CUDA backend accepts, src/backend/cuda/mod.rs:62-72), Q3_K (11) and IQ4_XS (23)
  * (src/weight/codec/ggml.rs:111-130, 384-406, 246-261) dequantise bit-exactly too and run every projection through the
- * operand pass and the GEMM.  The codebook-grid types (IQ2_*, IQ3_*) are not taken. */
+ * f16 operand pass and the tensor-core GEMM.  The codebook-grid types (IQ2_*, IQ3_*) are not taken. */
 enum { ZQ_Q4_0 = 2, ZQ_Q5_0 = 6, ZQ_Q5_1 = 7, ZQ_Q8_0 = 8, ZQ_Q3_K = 11, ZQ_Q4_K = 12, ZQ_Q5_K = 13, ZQ_Q6_K = 14, ZQ_IQ4_NL = 20, ZQ_IQ4_XS = 23 };
 enum { ZQ_F32 = 0, ZQ_F16 = 1, ZQ_BF16 = 2 };
 enum { ZQ_OK = 0, ZQ_ERR_SHAPE = 1, ZQ_ERR_UNSUPPORTED = 2, ZQ_ERR_CUDA = 3, ZQ_ERR_ARG = 4, ZQ_ERR_DEVICE_STATUS = 5, ZQ_ERR_DIST = 6 };

@@ -10,7 +10,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(OUT_DIR, "libzq_b200.so")
-SOURCES = ["zq_api.cu", "zq_codec.cu", "zq_norm.cu", "zq_rope.cu", "zq_gemv.cu", "zq_gemv_resident.cu", "zq_gemv_i8.cu", "zq_gemv_wl.cu", "zq_dist.cu", "zq_gemv_kq.cu", "zq_qmv.cu", "zq_gemm.cu", "zq_moe.cu", "zq_moe_grouped.cu", "zq_moe_ep.cu", "zq_gguf.cu"]
+SOURCES = ["zq_api.cu", "zq_codec.cu", "zq_norm.cu", "zq_rope.cu", "zq_gemv.cu", "zq_gemv_resident.cu", "zq_gemv_i8.cu", "zq_gemv_wl.cu", "zq_dist.cu", "zq_qmv.cu", "zq_gemm.cu", "zq_moe.cu", "zq_moe_grouped.cu", "zq_moe_ep.cu", "zq_gguf.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--cudart", "static", "-Xptxas", "-v",

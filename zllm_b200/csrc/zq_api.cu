@@ -129,7 +129,7 @@ static int prepare_common(zq_ctx *ctx, uint32_t type, size_t nbytes, size_t rows
 }
 
 static int finish_prepare(zq_ctx *ctx, zq_weight *w, zq_error *err) {
-    if (is_operand_pass_only(w->type)) return ZQ_OK;  // no decode kernel reads these through TMA (Q6_K blocks are not even 4-byte multiples)
+    if (!has_i8_decode(w->type)) return ZQ_OK;  // no decode kernel reads these through TMA (Q6_K blocks are not even 4-byte multiples)
     FormatInfo f = format_info(w->type);
     int rc = make_weight_map(w, 2 * f.unit_bytes / 4, 128, &w->gemv_map, err);
     if (!rc) rc = make_weight_map(w, 2 * f.unit_bytes / 4, 64, &w->gemv_map_half, err);
@@ -300,7 +300,7 @@ int zq_weight_prepare_device(zq_ctx *ctx, uint32_t ggml_type, const void *dev_by
         delete w;
         return set_error(err, ZQ_ERR_CUDA, "cudaMalloc of %zu resident bytes failed: %s", resident, cudaGetErrorString(e));
     }
-    if (ggml_type == ZQ_Q4_K || is_operand_pass_only(ggml_type)) {  // resident layout = GGUF layout
+    if (resident_is_gguf_layout(ggml_type)) {
         e = cudaMemcpyAsync(w->data, dev_bytes, nbytes, cudaMemcpyDeviceToDevice, ctx->stream);
         if (e != cudaSuccess) rc = set_error(err, ZQ_ERR_CUDA, "copy of packed weight failed: %s", cudaGetErrorString(e));
     } else {
@@ -391,7 +391,8 @@ static int check_linear(zq_ctx *ctx, const zq_weight *w, const void *x, int x_dt
 int zq_linear(zq_ctx *ctx, const zq_weight *w, const void *dev_x, int x_dtype, size_t m, void *dev_y, int y_dtype, const void *dev_residual, zq_error *err) {
     int rc = check_linear(ctx, w, dev_x, x_dtype, m, dev_y, y_dtype, err);
     if (rc) return rc;
-    if (has_kq_decode(w->type) && m <= 8) return launch_gemv_kq(ctx, w, dev_x, x_dtype, m, dev_y, y_dtype, dev_residual, err);
+    // Q5_K, Q6_K: the integer-MMA kernel (launch_gemv falls back to the GEMM where that one does not fit)
+    if ((w->type == ZQ_Q5_K || w->type == ZQ_Q6_K) && m <= 16 && !ctx->force_f16_gemv && !ctx->force_staged_gemv) return launch_gemv(ctx, w, nullptr, dev_x, x_dtype, m, dev_y, y_dtype, dev_residual, err);
     if (m <= 16 && !is_operand_pass_only(w->type)) return launch_gemv(ctx, w, nullptr, dev_x, x_dtype, m, dev_y, y_dtype, dev_residual, err);
     return launch_gemm(ctx, w, nullptr, dev_x, x_dtype, m, dev_y, y_dtype, dev_residual, err);
 }
@@ -500,7 +501,7 @@ int zq_gated_silu(zq_ctx *ctx, const zq_weight *gate, const zq_weight *up, const
     if (rc) return rc;
     if (!up || up->ctx != ctx) return set_error(err, ZQ_ERR_ARG, "gated linear: bad up weight");
     if (gate->rows != up->rows || gate->cols != up->cols || gate->type != up->type) return set_error(err, ZQ_ERR_SHAPE, "gated linear: gate [%zu, %zu] type %u and up [%zu, %zu] type %u differ", gate->rows, gate->cols, gate->type, up->rows, up->cols, up->type);
-    if (m <= 16 && !is_operand_pass_only(gate->type)) return launch_gemv(ctx, gate, up, dev_x, x_dtype, m, dev_y, y_dtype, nullptr, err);
+    if (m <= 16 && (!is_operand_pass_only(gate->type) || ((gate->type == ZQ_Q5_K || gate->type == ZQ_Q6_K) && !ctx->force_f16_gemv && !ctx->force_staged_gemv))) return launch_gemv(ctx, gate, up, dev_x, x_dtype, m, dev_y, y_dtype, nullptr, err);
     return launch_gemm(ctx, gate, up, dev_x, x_dtype, m, dev_y, y_dtype, nullptr, err);
 }
 

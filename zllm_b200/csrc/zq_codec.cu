@@ -42,7 +42,54 @@ __global__ void repack_kernel(uint32_t type, const uint8_t *__restrict__ gguf, u
     }
 }
 
+// The 6-bit code (0..63) of column `i` of a GGUF Q6_K super-block (src/weight/codec/ggml.rs:446-469: 128 low-nibble
+// bytes, 64 high-bit bytes, 16 i8 scales, d).
+__device__ __forceinline__ int q6k_gguf_code(const uint8_t *block, int i) {
+    const int half = i >> 7, quarter = (i >> 5) & 3, index = i & 31;
+    const uint8_t lo = block[half * 64 + index + ((quarter & 1) ? 32 : 0)];
+    const uint8_t hv = block[128 + half * 32 + index];
+    return (int)(((quarter & 2) ? (lo >> 4) : (lo & 0x0f)) | (((hv >> (2 * quarter)) & 3) << 4));
+}
+
+// One thread per resident byte of the Q6_K units (layout: kQ6k* in zq_common.cuh).
+__global__ void repack_q6k_kernel(const uint8_t *__restrict__ gguf, uint8_t *__restrict__ resident, size_t rows, size_t units_per_row) {
+    const size_t total = rows * units_per_row * 224;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t unit = idx / 224;
+        const int o = (int)(idx - unit * 224);
+        const uint8_t *block = gguf + unit * 210;  // rows are whole super-blocks: unit u of the tensor is block u of the file
+        uint8_t v = 0;
+        if (o < 2) {
+            v = block[208 + o];
+        } else if (o >= kQ6kScales && o < kQ6kLow) {
+            v = block[192 + (o - kQ6kScales)];
+        } else if (o >= kQ6kLow && o < kQ6kHigh) {
+            const int r = o - kQ6kLow, t = r >> 5, G = (r >> 2) & 7, i = r & 3;
+            const int c0 = (q6k_gguf_code(block, 32 * G + 4 * t + i) - 32) & 63, c1 = (q6k_gguf_code(block, 32 * G + 16 + 4 * t + i) - 32) & 63;
+            v = (uint8_t)((c0 & 15) | ((c1 & 15) << 4));
+        } else if (o >= kQ6kHigh) {
+            const int r = o - kQ6kHigh, t = r >> 4, vv = (r >> 2) & 3, i = r & 3;
+            for (int x = 0; x < 4; ++x) {
+                const int G = 2 * vv + (x >> 1), h = x & 1;
+                const int c = (q6k_gguf_code(block, 32 * G + 16 * h + 4 * t + i) - 32) & 63;
+                v |= (uint8_t)((c >> 4) << (2 * x));
+            }
+        }
+        resident[idx] = v;
+    }
+}
+
 int launch_repack(zq_ctx *ctx, uint32_t type, const uint8_t *gguf, uint8_t *resident, size_t rows, size_t cols, zq_error *err) {
+    if (type == ZQ_Q6_K) {
+        const size_t units = cols / kUnitWeights, total_q6 = rows * units * 224;
+        if (total_q6 == 0) return ZQ_OK;
+        size_t nb = (total_q6 + 255) / 256;
+        if (nb > 65535u * 16u) nb = 65535u * 16u;
+        repack_q6k_kernel<<<(unsigned)nb, 256, 0, ctx->stream>>>(gguf, resident, rows, units);
+        ctx->launches++;
+        ZQ_CUDA_CHECK(cudaGetLastError(), err);
+        return ZQ_OK;
+    }
     FormatInfo f = format_info(type);
     size_t blocks_per_row = cols / f.block_elems;
     size_t units_per_row = (cols + kUnitWeights - 1) / kUnitWeights;
@@ -77,13 +124,14 @@ __device__ __forceinline__ float decode_unit_element(uint32_t type, const uint8_
         const int quant = ((g & 1) ? (packed >> 4) : (packed & 0x0f)) + (((unit[16 + j] >> g) & 1) << 4);
         return __fsub_rn(__fmul_rn(__fmul_rn(d, (float)sc), (float)quant), __fmul_rn(dmin, (float)mn));
     }
-    if (type == ZQ_Q6_K) {  // src/weight/codec/ggml.rs:446-469: 128 low-nibble bytes, 64 high-bit bytes, 16 i8 scales, d
-        const float d = __half2float(*reinterpret_cast<const __half *>(unit + 208));
-        const int half = i >> 7, quarter = (i >> 5) & 3, index = i & 31;
-        const uint8_t lo = unit[half * 64 + index + ((quarter & 1) ? 32 : 0)];
-        const uint8_t hv = unit[128 + half * 32 + index];
-        const int q = (int)(((quarter & 2) ? (lo >> 4) : (lo & 0x0f)) | (((hv >> (2 * quarter)) & 3) << 4)) - 32;
-        const int8_t scale = (int8_t)unit[192 + half * 8 + (index >> 4) + 2 * quarter];
+    if (type == ZQ_Q6_K) {  // src/weight/codec/ggml.rs:446-469 on the re-laid unit (kQ6k* in zq_common.cuh): (d * scale) * (q - 32)
+        const float d = __half2float(*reinterpret_cast<const __half *>(unit));
+        const int G = i >> 5, h = (i >> 4) & 1, t = (i >> 2) & 3, ii = i & 3;
+        const int lo = (unit[kQ6kLow + 32 * t + 4 * G + ii] >> (4 * h)) & 15;
+        const int hi = (unit[kQ6kHigh + 16 * t + 4 * (G >> 1) + ii] >> (2 * (2 * (G & 1) + h))) & 3;
+        const int c = lo | (hi << 4);
+        const int q = c >= 32 ? c - 64 : c;  // the stored code is (q - 32) mod 64
+        const int8_t scale = (int8_t)unit[kQ6kScales + (i >> 4)];
         return __fmul_rn(__fmul_rn(d, (float)scale), (float)q);
     }
     if (type == ZQ_Q5_0 || type == ZQ_Q5_1) {  // src/weight/codec/ggml.rs:111-130; the unit is 8 GGUF blocks in file order

@@ -52,7 +52,7 @@ __host__ __device__ inline FormatInfo format_info(uint32_t t) {
     case ZQ_Q8_0: return {ZQ_Q8_0, 32, 34, 272};
     case ZQ_Q4_K: return {ZQ_Q4_K, 256, 144, 144};
     case ZQ_Q5_K: return {ZQ_Q5_K, 256, 176, 176};
-    case ZQ_Q6_K: return {ZQ_Q6_K, 256, 210, 210};
+    case ZQ_Q6_K: return {ZQ_Q6_K, 256, 210, 224};   // re-laid: see kQ6k* below
     case ZQ_Q5_0: return {ZQ_Q5_0, 32, 22, 176};   // unit = 8 consecutive GGUF blocks
     case ZQ_Q5_1: return {ZQ_Q5_1, 32, 24, 192};
     case ZQ_Q3_K: return {ZQ_Q3_K, 256, 110, 110};
@@ -61,14 +61,30 @@ __host__ __device__ inline FormatInfo format_info(uint32_t t) {
     }
 }
 
-// Q5_K and Q6_K (src/weight/codec/ggml.rs:425-469): resident in their GGUF layout, dequantised bit-exactly; plain
-// projections of up to 8 activation rows run a CUDA-core decode kernel (zq_gemv_kq.cu), everything else (more rows,
-// gated pairs) the f16 operand pass + tensor-core GEMM.  No integer-MMA kernel, tensor maps or encoder for them.
+// Types without an unpacker in the f16 decode kernels and without an encoder.  Of these, Q5_K and Q6_K
+// (src/weight/codec/ggml.rs:425-469) decode on the integer-MMA kernels (has_i8_decode); with more than 16 rows, or with a
+// diagnostic switch that turns those kernels off, they take the f16 operand pass + tensor-core GEMM like the rest.
 __host__ __device__ inline bool is_operand_pass_only(uint32_t type) { return type == ZQ_Q5_K || type == ZQ_Q6_K || type == ZQ_Q5_0 || type == ZQ_Q5_1 || type == ZQ_Q3_K || type == ZQ_IQ4_XS; }
-// Of those, the two with a decode kernel of their own (zq_gemv_kq.cu).  Q5_0, Q5_1, Q3_K and IQ4_XS
-// (src/weight/codec/ggml.rs:111-130, 246-261, 384-406) are resident in GGUF layout, dequantise bit-exactly, and run every
-// projection through the f16 operand pass and the tensor-core GEMM.
-__host__ __device__ inline bool has_kq_decode(uint32_t type) { return type == ZQ_Q5_K || type == ZQ_Q6_K; }
+// Q5_0, Q5_1, Q3_K and IQ4_XS (src/weight/codec/ggml.rs:111-130, 246-261, 384-406) are resident in GGUF layout, dequantise
+// bit-exactly, and run every projection through the f16 operand pass and the tensor-core GEMM.
+// Q5_K is Q4_K plus one high bit per weight in a 32-byte field (176-byte super-blocks, a multiple of 16, so TMA can carry
+// its rows as they are): its decode (1..16 rows, plain and gated) also runs on the integer-MMA kernels; the f16 kernels
+// have no unpacker for it.
+__host__ __device__ inline bool has_i8_decode(uint32_t type) { return type == ZQ_Q4_K || type == ZQ_Q4_0 || type == ZQ_Q8_0 || type == ZQ_IQ4_NL || type == ZQ_Q5_K || type == ZQ_Q6_K; }
+// Types whose resident bytes are the GGUF bytes; the others are re-laid at prepare time.
+__host__ __device__ inline bool resident_is_gguf_layout(uint32_t type) { return type == ZQ_Q4_K || type == ZQ_Q5_K || type == ZQ_Q5_0 || type == ZQ_Q5_1 || type == ZQ_Q3_K || type == ZQ_IQ4_XS; }
+
+// Q6_K resident unit (224 bytes for the 210 of a GGUF super-block, so that rows are 16-byte multiples and TMA can carry
+// them): d (f16) and 14 zero bytes; the 16 i8 scales in file order; then the 6-bit codes as c = (q - 32) mod 64 (two's
+// complement), split into a low nibble and a high bit pair and ordered for the integer-MMA fragments.  Column
+// 32 G + 16 h + 4 t + i of the unit (G 0..7, h 0..1, t 0..3, i 0..3):
+//   low nibble   byte kQ6kLow  + 32 t + 4 G + i, bits [4h+3 : 4h]
+//   high bits    byte kQ6kHigh + 16 t + 4 (G / 2) + i, bits [2x+1 : 2x], x = 2 (G & 1) + h
+// so that lane-in-quad t reads its 48 bytes of a row's unit with three 16-byte loads, and a word of low nibbles masked by
+// 0x0F0F0F0F / 0xF0F0F0F0 is the operand of the first / second 16-column scale group of block G.
+constexpr int kQ6kScales = 16, kQ6kLow = 32, kQ6kHigh = 160;
+// The two formats whose records carry group sums (for the min term) and the Q4_K column order.
+__host__ __device__ constexpr bool is_kclass(uint32_t type) { return type == ZQ_Q4_K || type == ZQ_Q5_K; }
 
 // Byte offset, inside a resident unit, of the quant byte that holds element `i` (0..255) of the unit.
 __host__ __device__ inline int unit_quant_offset(uint32_t type, int i) {
@@ -324,7 +340,6 @@ int launch_dequantize_f16(zq_ctx *ctx, const zq_weight *w, __half *out, zq_error
 int launch_dequantize_f16_batch(zq_ctx *ctx, const zq_weight *const *weights, __half *const *outs, size_t count, zq_error *err);
 int launch_quantize(zq_ctx *ctx, uint32_t type, const float *values, size_t rows, size_t cols, void *out, zq_error *err);
 int launch_gemv(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const void *x, int x_dtype, size_t m, void *y, int y_dtype, const void *residual, zq_error *err);
-int launch_gemv_kq(zq_ctx *ctx, const zq_weight *w, const void *x, int x_dtype, size_t m, void *y, int y_dtype, const void *residual, zq_error *err);
 int launch_gemv_noalloc(zq_ctx *ctx, const zq_weight *w, const void *x, int x_dtype, size_t m, void *y, int y_dtype, zq_error *err);
 int launch_gemm(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const void *x, int x_dtype, size_t m, void *y, int y_dtype, const void *residual, zq_error *err);
 }  // namespace zq

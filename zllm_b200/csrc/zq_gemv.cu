@@ -363,7 +363,7 @@ int launch_gemv(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const vo
         p.y = reinterpret_cast<uint8_t *>(y) + m0 * w->rows * dtype_size(y_dtype);
         p.residual = residual ? reinterpret_cast<const uint8_t *>(residual) + m0 * w->rows * dtype_size(y_dtype) : nullptr;
         int rc;
-        if (ctx->enable_tcgen05_gemv && !ctx->force_staged_gemv && !gated) {
+        if (ctx->enable_tcgen05_gemv && !ctx->force_staged_gemv && !gated && w->type == ZQ_Q4_K) {
             bool taken = false;
             rc = launch_qmv(ctx, w, p, taken, err);
             if (rc) return rc;
@@ -386,6 +386,10 @@ int launch_gemv(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const vo
         case ZQ_Q4_0: rc = launch_type<ZQ_Q4_0>(ctx, w, w_up, p, grid, err); break;
         case ZQ_IQ4_NL: rc = launch_type<ZQ_IQ4_NL>(ctx, w, w_up, p, grid, err); break;
         case ZQ_Q8_0: rc = launch_type<ZQ_Q8_0>(ctx, w, w_up, p, grid, err); break;
+        case ZQ_Q5_K:  // only the integer-MMA kernel unpacks these; where that one did not fit: the operand pass + GEMM
+        case ZQ_Q6_K:
+            rc = launch_gemm(ctx, w, w_up, p.x, x_dtype, mm, p.y, y_dtype, p.residual, err);
+            break;
         default: return set_error(err, ZQ_ERR_UNSUPPORTED, "GEMV: unsupported GGUF type %u", w->type);
         }
         if (rc) return rc;

@@ -18,6 +18,8 @@ template <> struct Fmt<ZQ_Q4_K> { static constexpr int unit_bytes = 144; static 
 template <> struct Fmt<ZQ_Q4_0> { static constexpr int unit_bytes = 144; static constexpr int stages = 4; static constexpr bool lut = false; };
 template <> struct Fmt<ZQ_IQ4_NL> { static constexpr int unit_bytes = 144; static constexpr int stages = 3; static constexpr bool lut = true; };
 template <> struct Fmt<ZQ_Q8_0> { static constexpr int unit_bytes = 272; static constexpr int stages = 2; static constexpr bool lut = false; };
+template <> struct Fmt<ZQ_Q6_K> { static constexpr int unit_bytes = 224; static constexpr int stages = 3; static constexpr bool lut = false; };  // integer-MMA kernels only
+template <> struct Fmt<ZQ_Q5_K> { static constexpr int unit_bytes = 176; static constexpr int stages = 3; static constexpr bool lut = false; };  // integer-MMA kernels only
 
 template <uint32_t TYPE, int NT> struct GemvSmem {
     static constexpr int stages = (NT == 2 && Fmt<TYPE>::stages > 3) ? 3 : Fmt<TYPE>::stages;  // two column tiles need room

@@ -53,7 +53,7 @@ __global__ void __launch_bounds__(256) quantize_acts_kernel(const void *x, int x
     const RecLane o = quantize_record<TYPE>(v, lane);
     uint8_t *dst = out + (size_t)rec * kRec;
     *reinterpret_cast<uint4 *>(dst + o.slot) = make_uint4(o.ph0, o.ph1, o.pl0, o.pl1);
-    if (TYPE == ZQ_Q4_K && (lane & 7) == 0) *reinterpret_cast<uint2 *>(dst + kRecSums + (lane >> 3) * 8) = make_uint2(o.sw0, o.sw1);
+    if (is_kclass(TYPE) && (lane & 7) == 0) *reinterpret_cast<uint2 *>(dst + kRecSums + (lane >> 3) * 8) = make_uint2(o.sw0, o.sw1);
     if (lane == 0) *reinterpret_cast<float *>(dst + kRecScale) = o.scale;
 }
 
@@ -189,7 +189,7 @@ __global__ void __launch_bounds__(ROWS * 4, ROWS == 128 ? 1 : 2) gemv_i8_kernel(
                 if (tshare == 1) {  // plain shared-memory stores
                     uint8_t *dst = smem + ia.off_x + rec_off;
                     *reinterpret_cast<uint4 *>(dst + o.slot) = make_uint4(o.ph0, o.ph1, o.pl0, o.pl1);
-                    if (TYPE == ZQ_Q4_K && (lane & 7) == 0) *reinterpret_cast<uint2 *>(dst + kRecSums + (lane >> 3) * 8) = make_uint2(o.sw0, o.sw1);
+                    if (is_kclass(TYPE) && (lane & 7) == 0) *reinterpret_cast<uint2 *>(dst + kRecSums + (lane >> 3) * 8) = make_uint2(o.sw0, o.sw1);
                     if (lane == 0) *reinterpret_cast<float *>(dst + kRecScale) = o.scale;
                 } else {
 #pragma unroll
@@ -197,7 +197,7 @@ __global__ void __launch_bounds__(ROWS * 4, ROWS == 128 ? 1 : 2) gemv_i8_kernel(
                         if (q < tshare) {
                             const uint32_t dst = peer_x[q] + rec_off;
                             i8_st_cluster_v4(dst + o.slot, o.ph0, o.ph1, o.pl0, o.pl1);
-                            if (TYPE == ZQ_Q4_K && (lane & 7) == 0) i8_st_cluster_v2(dst + kRecSums + (lane >> 3) * 8, o.sw0, o.sw1);
+                            if (is_kclass(TYPE) && (lane & 7) == 0) i8_st_cluster_v2(dst + kRecSums + (lane >> 3) * 8, o.sw0, o.sw1);
                             if (lane == 0) i8_st_cluster_u32(dst + kRecScale, __float_as_uint(o.scale));
                         }
                     }
@@ -263,7 +263,8 @@ __global__ void __launch_bounds__(ROWS * 4, ROWS == 128 ? 1 : 2) gemv_i8_kernel(
                     rec[nt] = rb + moff[nt];
                     srec[nt] = rb + soff[nt];
                 }
-                if constexpr (TYPE == ZQ_Q4_K) consume_q4k_i8<NT>(wq0, wq1, t, rec, srec, xoff, yacc);
+                if constexpr (TYPE == ZQ_Q6_K) consume_q6k_i8<NT>(wq0, wq1, t, rec, srec, xoff, yacc);
+            else if constexpr (is_kclass(TYPE)) consume_q4k_i8<NT, TYPE == ZQ_Q5_K>(wq0, wq1, t, rec, srec, xoff, yacc);
                 else consume_b32_i8<TYPE, NT>(wq0, wq1, t, rec, srec, xoff, yacc);
             }
             __syncwarp();
@@ -496,6 +497,8 @@ int launch_gemv_i8(zq_ctx *ctx, const zq_weight *w, const zq_weight *w_up, const
     if (p.m < 1 || p.m > kMaxGemvRows) return ZQ_OK;
     switch (w->type) {
     case ZQ_Q4_K: return launch_i8_type<ZQ_Q4_K>(ctx, w, w_up, p, taken, err);
+    case ZQ_Q5_K: return launch_i8_type<ZQ_Q5_K>(ctx, w, w_up, p, taken, err);
+    case ZQ_Q6_K: return launch_i8_type<ZQ_Q6_K>(ctx, w, w_up, p, taken, err);
     case ZQ_Q4_0: return launch_i8_type<ZQ_Q4_0>(ctx, w, w_up, p, taken, err);
     case ZQ_IQ4_NL: return launch_i8_type<ZQ_IQ4_NL>(ctx, w, w_up, p, taken, err);
     case ZQ_Q8_0: return launch_i8_type<ZQ_Q8_0>(ctx, w, w_up, p, taken, err);

@@ -84,7 +84,7 @@ __global__ void __launch_bounds__(256) wl_quantize_kernel(const __grid_constant_
     const RecLane o = quantize_record<TYPE>(v, lane);
     uint8_t *dst = qa.out + (size_t)rec * kRec;
     *reinterpret_cast<uint4 *>(dst + o.slot) = make_uint4(o.ph0, o.ph1, o.pl0, o.pl1);
-    if (TYPE == ZQ_Q4_K && (lane & 7) == 0) *reinterpret_cast<uint2 *>(dst + kRecSums + (lane >> 3) * 8) = make_uint2(o.sw0, o.sw1);
+    if (is_kclass(TYPE) && (lane & 7) == 0) *reinterpret_cast<uint2 *>(dst + kRecSums + (lane >> 3) * 8) = make_uint2(o.sw0, o.sw1);
     if (lane == 0) *reinterpret_cast<float *>(dst + kRecScale) = o.scale;
 }
 
@@ -401,7 +401,8 @@ __global__ void __launch_bounds__(kWlThreads, 1) gemv_wl_kernel(const __grid_con
                 rec[nt] = rb + moff[nt];
                 srec[nt] = rb + soff[nt];
             }
-            if constexpr (TYPE == ZQ_Q4_K) consume_q4k_i8<NT>(wq0, wq1, t, rec, srec, xoff, yacc);
+            if constexpr (TYPE == ZQ_Q6_K) consume_q6k_i8<NT>(wq0, wq1, t, rec, srec, xoff, yacc);
+            else if constexpr (is_kclass(TYPE)) consume_q4k_i8<NT, TYPE == ZQ_Q5_K>(wq0, wq1, t, rec, srec, xoff, yacc);
             else consume_b32_i8<TYPE, NT>(wq0, wq1, t, rec, srec, xoff, yacc);
         }
         __syncwarp();
@@ -548,7 +549,7 @@ static int launch_wl_type(zq_ctx *ctx, const WlArgs &wa, int nt, bool gated, zq_
     return gated ? launch_wl_one<TYPE, 4, true>(ctx, wa, err) : launch_wl_one<TYPE, 4, false>(ctx, wa, err);
 }
 
-static bool wl_type_ok(uint32_t t) { return t == ZQ_Q4_K || t == ZQ_Q4_0 || t == ZQ_Q8_0 || t == ZQ_IQ4_NL; }
+static bool wl_type_ok(uint32_t t) { return t == ZQ_Q4_K || t == ZQ_Q4_0 || t == ZQ_Q8_0 || t == ZQ_IQ4_NL || t == ZQ_Q5_K || t == ZQ_Q6_K; }
 
 bool gemv_wl_supported(const zq_ctx *ctx, const WlHostJob &j) {
     if (!j.w || !j.w->d_maps || !wl_type_ok(j.w->type) || j.m < 1 || j.m > (size_t)kMaxGemvRows) return false;
@@ -569,7 +570,7 @@ int launch_gemv_wl(zq_ctx *ctx, const WlHostJob *jobs, size_t n_jobs, int x_dtyp
     size_t total_rec = 0;
     for (size_t i = 0; i < n_jobs; ++i) {
         const WlHostJob &j = jobs[i];
-        const bool q4k = j.w->type == ZQ_Q4_K;
+        const bool q4k = is_kclass(j.w->type);
         size_t s = 0;
         for (; s < srcs.size(); ++s)
             if (srcs[s].x == j.x && srcs[s].m == j.m && srcs[s].cols == j.w->cols && srcs[s].q4k == q4k) break;
@@ -634,6 +635,8 @@ int launch_gemv_wl(zq_ctx *ctx, const WlHostJob *jobs, size_t n_jobs, int x_dtyp
             int r;
             switch (type) {
             case ZQ_Q4_K: r = launch_wl_type<ZQ_Q4_K>(ctx, wa, nt, gated, err); break;
+            case ZQ_Q5_K: r = launch_wl_type<ZQ_Q5_K>(ctx, wa, nt, gated, err); break;
+            case ZQ_Q6_K: r = launch_wl_type<ZQ_Q6_K>(ctx, wa, nt, gated, err); break;
             case ZQ_Q4_0: r = launch_wl_type<ZQ_Q4_0>(ctx, wa, nt, gated, err); break;
             case ZQ_IQ4_NL: r = launch_wl_type<ZQ_IQ4_NL>(ctx, wa, nt, gated, err); break;
             default: r = launch_wl_type<ZQ_Q8_0>(ctx, wa, nt, gated, err); break;

@@ -72,6 +72,11 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
     return v;
 }
+__device__ __forceinline__ uint32_t lds_f32_bits(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
 __device__ __forceinline__ float lds_f32(uint32_t addr) {
     float v;
     asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
@@ -116,15 +121,26 @@ __device__ __forceinline__ uint32_t pack_s8x4(int a, int b, int c, int d) {
 //   wq0 / wq1  unit base of fragment rows g and g+8 (shared addresses)
 //   rec[nt]    record of the activation row this lane's B column of tile nt belongs to (row g / 2);  xoff = 16 t + 8 limb
 //   srec[nt]   record of the activation row this lane's accumulator columns belong to (row t): its slice scale
-template <int NT>
+// Q5_K (Q5 = true): the same super-block with a 32-byte field of high bits between the header and the quant bytes (bit g of
+// byte j is bit 4 of weight j of group g, src/weight/codec/ggml.rs:425-447).  The five-bit code no longer fits the
+// "16 q in place" trick of the high-nibble groups, so both groups of a pair are brought down to plain codes 0..31.
+template <int NT, bool Q5 = false>
 __device__ __forceinline__ void consume_q4k_i8(uint32_t wq0, uint32_t wq1, int t, const uint32_t (&rec)[NT], const uint32_t (&srec)[NT], uint32_t xoff, float (&yacc)[NT][2]) {
+    constexpr uint32_t QS = Q5 ? 48 : 16;  // byte offset of the quant bytes inside the unit
     const uint4 hdr0 = lds128(wq0), hdr1 = lds128(wq1);
     uint2 q0[4], q1[4];
 #pragma unroll
     for (int pr = 0; pr < 4; ++pr) {
-        q0[pr] = lds64(wq0 + 16 + 32 * pr + 8 * t);
-        q1[pr] = lds64(wq1 + 16 + 32 * pr + 8 * t);
+        q0[pr] = lds64(wq0 + QS + 32 * pr + 8 * t);
+        q1[pr] = lds64(wq1 + QS + 32 * pr + 8 * t);
     }
+    uint2 h0 = make_uint2(0, 0), h1 = make_uint2(0, 0);
+    if constexpr (Q5) {
+        h0 = lds64(wq0 + 16 + 8 * t);
+        h1 = lds64(wq1 + 16 + 8 * t);
+    }
+    // bit `g` of every byte of h, moved to bit 4
+    auto hbit = [](uint32_t h, int g) -> uint32_t { return (g <= 4 ? (h << (4 - g)) : (h >> (g - 4))) & 0x10101010u; };
     const uint32_t sc_lo0 = hdr0.y & 0x3F3F3F3Fu, sc_hi0 = (hdr0.w & 0x0F0F0F0Fu) | ((hdr0.y >> 2) & 0x30303030u);
     const uint32_t sc_lo1 = hdr1.y & 0x3F3F3F3Fu, sc_hi1 = (hdr1.w & 0x0F0F0F0Fu) | ((hdr1.y >> 2) & 0x30303030u);
     int tl[NT][4], th[NT][4];  // sum over groups of scale * MMA result: low-nibble groups, high-nibble groups
@@ -143,7 +159,10 @@ __device__ __forceinline__ void consume_q4k_i8(uint32_t wq0, uint32_t wq1, int t
         const uint32_t s0w = pr < 2 ? sc_lo0 : sc_hi0, s1w = pr < 2 ? sc_lo1 : sc_hi1;
         {
             const int s0 = (pr & 1) ? byte_of<2>(s0w) : byte_of<0>(s0w), s1 = (pr & 1) ? byte_of<2>(s1w) : byte_of<0>(s1w);
-            const uint32_t a0 = q0[pr].x & 0x0F0F0F0Fu, a1 = q1[pr].x & 0x0F0F0F0Fu, a2 = q0[pr].y & 0x0F0F0F0Fu, a3 = q1[pr].y & 0x0F0F0F0Fu;
+            uint32_t a0 = q0[pr].x & 0x0F0F0F0Fu, a1 = q1[pr].x & 0x0F0F0F0Fu, a2 = q0[pr].y & 0x0F0F0F0Fu, a3 = q1[pr].y & 0x0F0F0F0Fu;
+            if constexpr (Q5) {
+                a0 |= hbit(h0.x, 2 * pr); a1 |= hbit(h1.x, 2 * pr); a2 |= hbit(h0.y, 2 * pr); a3 |= hbit(h1.y, 2 * pr);
+            }
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
                 int d[4];
@@ -156,7 +175,13 @@ __device__ __forceinline__ void consume_q4k_i8(uint32_t wq0, uint32_t wq1, int t
         }
         {
             const int s0 = (pr & 1) ? byte_of<3>(s0w) : byte_of<1>(s0w), s1 = (pr & 1) ? byte_of<3>(s1w) : byte_of<1>(s1w);
-            const uint32_t a0 = q0[pr].x & 0xF0F0F0F0u, a1 = q1[pr].x & 0xF0F0F0F0u, a2 = q0[pr].y & 0xF0F0F0F0u, a3 = q1[pr].y & 0xF0F0F0F0u;
+            uint32_t a0, a1, a2, a3;
+            if constexpr (Q5) {  // plain codes; the factor 16 the epilogue expects of this half is put on the scale instead
+                a0 = ((q0[pr].x >> 4) & 0x0F0F0F0Fu) | hbit(h0.x, 2 * pr + 1); a1 = ((q1[pr].x >> 4) & 0x0F0F0F0Fu) | hbit(h1.x, 2 * pr + 1);
+                a2 = ((q0[pr].y >> 4) & 0x0F0F0F0Fu) | hbit(h0.y, 2 * pr + 1); a3 = ((q1[pr].y >> 4) & 0x0F0F0F0Fu) | hbit(h1.y, 2 * pr + 1);
+            } else {
+                a0 = q0[pr].x & 0xF0F0F0F0u; a1 = q1[pr].x & 0xF0F0F0F0u; a2 = q0[pr].y & 0xF0F0F0F0u; a3 = q1[pr].y & 0xF0F0F0F0u;
+            }
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
                 int d[4];
@@ -186,13 +211,15 @@ __device__ __forceinline__ void consume_q4k_i8(uint32_t wq0, uint32_t wq1, int t
         }
     }
     const __half2 dd0 = u32_as_h2(hdr0.x), dd1 = u32_as_h2(hdr1.x);
-    const float d_0 = __low2float(dd0) * 0.0625f, dm_0 = __high2float(dd0), d_1 = __low2float(dd1) * 0.0625f, dm_1 = __high2float(dd1);
+    constexpr float kHalfPre = Q5 ? 1.f : 0.0625f;  // Q4_K's high-nibble groups carry 16 q
+    constexpr int kLowShift = Q5 ? 0 : 4;
+    const float d_0 = __low2float(dd0) * kHalfPre, dm_0 = __high2float(dd0), d_1 = __low2float(dd1) * kHalfPre, dm_1 = __high2float(dd1);
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
         // columns 2t / 2t+1 of the tile are the hi / lo limb of one activation row
         const float sa = lds_f32(srec[nt] + kRecScale);
-        const float f0 = (float)((tl[nt][0] << 4) + th[nt][0]) * 256.f + (float)((tl[nt][1] << 4) + th[nt][1]);
-        const float f1 = (float)((tl[nt][2] << 4) + th[nt][2]) * 256.f + (float)((tl[nt][3] << 4) + th[nt][3]);
+        const float f0 = (float)((tl[nt][0] << kLowShift) + th[nt][0]) * 256.f + (float)((tl[nt][1] << kLowShift) + th[nt][1]);
+        const float f1 = (float)((tl[nt][2] << kLowShift) + th[nt][2]) * 256.f + (float)((tl[nt][3] << kLowShift) + th[nt][3]);
         yacc[nt][0] += sa * (d_0 * f0 - dm_0 * d2[nt][0]);
         yacc[nt][1] += sa * (d_1 * f1 - dm_1 * d2[nt][2]);
     }
@@ -221,6 +248,71 @@ __device__ __forceinline__ void iq4nl_lookup(uint32_t w, uint32_t &lo, uint32_t 
     const uint32_t y = lop3_select(prmt_b32(w4, w, 0xFBEAu), prmt_b32(T2, T3, ws2), prmt_b32(T0, T1, ws2));
     lo = prmt_b32(x, y, 0x6420u);
     hi = prmt_b32(x, y, 0x7531u);
+}
+
+// m16n8k16, s8 x s8 -> s32: one 16-weight scale group of the thread's two fragment rows (a0: row g, a1: row g + 8; k 4t..4t+3).
+__device__ __forceinline__ void imma_16816_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%7,%7,%7,%7};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(b0), "r"(0));
+}
+// sign-extended byte J of a word
+template <int J> __device__ __forceinline__ int sbyte_of(uint32_t w) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(w), "r"(0u), "n"(0x8880 + 0x1111 * J));
+    return (int)r;
+}
+
+// One Q6_K unit (re-laid, kQ6k* in zq_common.cuh) of the thread's two fragment rows.  Codes are stored as 6-bit two's
+// complement (q - 32); moved to the top six bits of a byte they are the s8 value 4 (q - 32), so no sign extension is
+// needed and the factor 4 goes onto d.  One m16n8k16 MMA per 16-column scale group; the i8 group scales multiply the s32
+// results.  Records are those of the block-32 formats (slot t of block G: columns 4t..4t+3 and 16+4t..16+4t+3).
+template <int NT>
+__device__ __forceinline__ void consume_q6k_i8(uint32_t wq0, uint32_t wq1, int t, const uint32_t (&rec)[NT], const uint32_t (&srec)[NT], uint32_t xoff, float (&yacc)[NT][2]) {
+    const uint32_t d0w = lds_f32_bits(wq0), d1w = lds_f32_bits(wq1);
+    const uint4 s0 = lds128(wq0 + kQ6kScales), s1 = lds128(wq1 + kQ6kScales);
+    const uint4 l0a = lds128(wq0 + kQ6kLow + 32 * t), l0b = lds128(wq0 + kQ6kLow + 32 * t + 16), l1a = lds128(wq1 + kQ6kLow + 32 * t), l1b = lds128(wq1 + kQ6kLow + 32 * t + 16);
+    const uint4 h0 = lds128(wq0 + kQ6kHigh + 16 * t), h1 = lds128(wq1 + kQ6kHigh + 16 * t);
+    const uint32_t lo0[8] = {l0a.x, l0a.y, l0a.z, l0a.w, l0b.x, l0b.y, l0b.z, l0b.w}, lo1[8] = {l1a.x, l1a.y, l1a.z, l1a.w, l1b.x, l1b.y, l1b.z, l1b.w};
+    const uint32_t hi0[4] = {h0.x, h0.y, h0.z, h0.w}, hi1[4] = {h1.x, h1.y, h1.z, h1.w};
+    const uint32_t sc0[4] = {s0.x, s0.y, s0.z, s0.w}, sc1[4] = {s1.x, s1.y, s1.z, s1.w};
+    int tot[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) tot[nt][j] = 0;
+#pragma unroll
+    for (int G = 0; G < 8; ++G) {
+        uint2 b[NT];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) b[nt] = lds64(rec[nt] + xoff + G * 64);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int x = 2 * (G & 1) + h;  // which bit pair of the high-bits word
+            const uint32_t n0 = h ? (lo0[G] & 0xF0F0F0F0u) >> 2 : (lo0[G] & 0x0F0F0F0Fu) << 2;
+            const uint32_t n1 = h ? (lo1[G] & 0xF0F0F0F0u) >> 2 : (lo1[G] & 0x0F0F0F0Fu) << 2;
+            const uint32_t a0 = lop3_select(0xC0C0C0C0u, hi0[G >> 1] << (6 - 2 * x), n0), a1 = lop3_select(0xC0C0C0C0u, hi1[G >> 1] << (6 - 2 * x), n1);
+            const int g16 = 2 * G + h;
+            const int k0 = (g16 & 3) == 0 ? sbyte_of<0>(sc0[g16 >> 2]) : (g16 & 3) == 1 ? sbyte_of<1>(sc0[g16 >> 2]) : (g16 & 3) == 2 ? sbyte_of<2>(sc0[g16 >> 2]) : sbyte_of<3>(sc0[g16 >> 2]);
+            const int k1 = (g16 & 3) == 0 ? sbyte_of<0>(sc1[g16 >> 2]) : (g16 & 3) == 1 ? sbyte_of<1>(sc1[g16 >> 2]) : (g16 & 3) == 2 ? sbyte_of<2>(sc1[g16 >> 2]) : sbyte_of<3>(sc1[g16 >> 2]);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                int d[4];
+                imma_16816_s8(d, a0, a1, h ? b[nt].y : b[nt].x);
+                tot[nt][0] += d[0] * k0;
+                tot[nt][1] += d[1] * k0;
+                tot[nt][2] += d[2] * k1;
+                tot[nt][3] += d[3] * k1;
+            }
+        }
+    }
+    const float d_0 = __half2float(__ushort_as_half((unsigned short)(d0w & 0xFFFFu))) * 0.25f, d_1 = __half2float(__ushort_as_half((unsigned short)(d1w & 0xFFFFu))) * 0.25f;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        const float sa = lds_f32(srec[nt] + kRecScale);
+        yacc[nt][0] += (sa * d_0) * ((float)tot[nt][0] * 256.f + (float)tot[nt][1]);
+        yacc[nt][1] += (sa * d_1) * ((float)tot[nt][2] * 256.f + (float)tot[nt][3]);
+    }
 }
 
 // One block-32 unit (8 blocks of 32 weights) of the thread's two fragment rows: Q4_0, IQ4_NL or Q8_0.
@@ -335,7 +427,7 @@ template <uint32_t TYPE> __device__ __forceinline__ RecLane quantize_record(cons
     // the lane's two quads (columns 8 lane .. +3 and +4 .. +7) as packed limbs
     o.ph0 = pack_s8x4(hi[0], hi[1], hi[2], hi[3]); o.ph1 = pack_s8x4(hi[4], hi[5], hi[6], hi[7]);
     o.pl0 = pack_s8x4(lo[0], lo[1], lo[2], lo[3]); o.pl1 = pack_s8x4(lo[4], lo[5], lo[6], lo[7]);
-    if constexpr (TYPE == ZQ_Q4_K) {
+    if constexpr (is_kclass(TYPE)) {
         o.slot = (uint32_t)lane * 16;  // group lane / 4, slot t = lane % 4: both quads are this lane's
     } else {
         // block lane / 4; the quads are (slot 2 (lane & 1) + qd, register r) with r = (lane >> 1) & 1: trade the quad of
@@ -348,7 +440,7 @@ template <uint32_t TYPE> __device__ __forceinline__ RecLane quantize_record(cons
         o.slot = (uint32_t)(4 * (lane >> 2) + 2 * (lane & 1) + r) * 16;
     }
     o.sw0 = o.sw1 = 0;
-    if constexpr (TYPE == ZQ_Q4_K) {
+    if constexpr (is_kclass(TYPE)) {
         // exact integer sum of each 32-column group: |sum| can reach 32 * 32512, beyond f16, so sum = 1024 a + r with
         // |a| <= 1016, |r| <= 512, both exact in f16; the factor 1024 rides on the min codes of the hi-limb K slots.
         // Fragment entry t' = {half2(a_2t', a_2t'+1), half2(r_2t', r_2t'+1)}.
