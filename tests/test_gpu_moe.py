@@ -144,6 +144,29 @@ def test_moe_prefill_runs_grouped_tensor_core_gemms(tensor_type, m, moe_path):
     assert float(np.linalg.norm(got - want) / np.linalg.norm(want)) <= 1e-3
 
 
+@pytest.mark.parametrize("gate_type,down_type", [(H.Q4_K, H.Q6_K), (H.Q5_K, H.Q5_K), (H.IQ4_NL, H.IQ4_NL), (H.Q6_K, H.Q4_K)])
+def test_moe_decode_with_mixed_expert_types(gate_type, down_type, moe_path):
+    """Files mix types inside an expert (a Q4_K_M file carries Q6_K down projections; the reference's CUDA experts accept
+    Q5_K / Q6_K down matrices, src/backend/cuda/expert.rs:462-473): the grouped decode launches take every type the
+    integer-MMA kernels unpack, one type for gate/up and one for down."""
+    from zllm_b200.backend import MoeExperts, moe_forward
+
+    n_exp, top_k, hidden, inter, m = 6, 2, 512, 256, 7
+    gates = [H.random_weight(gate_type, inter, hidden, seed=610 + 3 * e) for e in range(n_exp)]
+    ups = [H.random_weight(gate_type, inter, hidden, seed=611 + 3 * e) for e in range(n_exp)]
+    downs = [H.random_weight(down_type, hidden, inter, seed=612 + 3 * e, std=0.05) for e in range(n_exp)]
+    rng = np.random.default_rng(61)
+    x = rng.standard_normal((m, hidden)).astype(np.float32)
+    ids_np = np.stack([rng.permutation(n_exp)[:top_k] for _ in range(m)]).astype(np.uint32)
+    w_np = rng.random((m, top_k)).astype(np.float32)
+    c = ctx()
+    table = MoeExperts(c, [c.prepare_weight(gate_type, g, inter, hidden) for g in gates], [c.prepare_weight(gate_type, u, inter, hidden) for u in ups],
+                       [c.prepare_weight(down_type, d, hidden, inter) for d in downs])
+    got = host(moe_forward(c, table, dev(x), torch.from_numpy(ids_np.astype(np.int32)).cuda(), dev(w_np)))
+    want = orc.moe_forward([(gate_type, g, inter, hidden) for g in gates], [(gate_type, u, inter, hidden) for u in ups], [(down_type, d, hidden, inter) for d in downs], x, ids_np, w_np)
+    assert H.max_rel_error(got, want) <= BOUND
+
+
 def test_moe_prefill_grouping_on_the_device_equals_grouping_on_the_host():
     """Prefill with Q4_K experts groups the routes on the device (a stable counting sort over chunks of tokens) and
     hands the grouped GEMMs their work lists without a host round trip.  Slots, combine order and work lists are

@@ -23,7 +23,7 @@ constexpr int kPassUnitBytes = kPassRows * kRec;  // record slot of one unit ins
 constexpr int kItemCache = 512;                 // work items whose descriptors a CTA keeps in shared memory
 constexpr int kPlanThreads = 1024;
 // ring depth: the wide Q8_0 rows leave room for two stages only
-__host__ __device__ constexpr int grouped_stages(uint32_t type) { return type == ZQ_Q8_0 ? 2 : 4; }
+__host__ __device__ constexpr int grouped_stages(uint32_t type) { return type == ZQ_Q8_0 ? 2 : (type == ZQ_Q5_K || type == ZQ_Q6_K) ? 3 : 4; }
 
 // ---------------------------------------------------------------------------------------------------------------
 // Plan: one CTA.  ids/weights are the router's [m, top_k] outputs.
@@ -175,7 +175,7 @@ __global__ void __launch_bounds__(256) moe_quantize_kernel(const void *__restric
     const RecLane o = quantize_record<TYPE>(v, lane);
     uint8_t *dst = out + rec * kRec;
     *reinterpret_cast<uint4 *>(dst + o.slot) = make_uint4(o.ph0, o.ph1, o.pl0, o.pl1);
-    if (TYPE == ZQ_Q4_K && (lane & 7) == 0) *reinterpret_cast<uint2 *>(dst + kRecSums + (lane >> 3) * 8) = make_uint2(o.sw0, o.sw1);
+    if (is_kclass(TYPE) && (lane & 7) == 0) *reinterpret_cast<uint2 *>(dst + kRecSums + (lane >> 3) * 8) = make_uint2(o.sw0, o.sw1);
     if (lane == 0) *reinterpret_cast<float *>(dst + kRecScale) = o.scale;
 }
 
@@ -306,11 +306,13 @@ __global__ void __launch_bounds__(kI8Threads, 1) moe_grouped_kernel(const __grid
             const uint32_t rb = rec_first + soffs;
             if (mc <= 4) {
                 const uint32_t rec[1] = {rb + moff[0]}, srec[1] = {rb + soff[0]};
-                if constexpr (TYPE == ZQ_Q4_K) consume_q4k_i8<1>(wq0, wq1, t, rec, srec, xoff, yacc1);
+                if constexpr (TYPE == ZQ_Q6_K) consume_q6k_i8<1>(wq0, wq1, t, rec, srec, xoff, yacc1);
+                else if constexpr (is_kclass(TYPE)) consume_q4k_i8<1, TYPE == ZQ_Q5_K>(wq0, wq1, t, rec, srec, xoff, yacc1);
                 else consume_b32_i8<TYPE, 1>(wq0, wq1, t, rec, srec, xoff, yacc1);
             } else {
                 const uint32_t rec[2] = {rb + moff[0], rb + moff[1]}, srec[2] = {rb + soff[0], rb + soff[1]};
-                if constexpr (TYPE == ZQ_Q4_K) consume_q4k_i8<2>(wq0, wq1, t, rec, srec, xoff, yacc2);
+                if constexpr (TYPE == ZQ_Q6_K) consume_q6k_i8<2>(wq0, wq1, t, rec, srec, xoff, yacc2);
+                else if constexpr (is_kclass(TYPE)) consume_q4k_i8<2, TYPE == ZQ_Q5_K>(wq0, wq1, t, rec, srec, xoff, yacc2);
                 else consume_b32_i8<TYPE, 2>(wq0, wq1, t, rec, srec, xoff, yacc2);
             }
         }
@@ -405,7 +407,7 @@ static int launch_grouped(zq_ctx *ctx, const GroupedArgs &ga, zq_error *err) {
 }
 
 bool moe_grouped_supported(const zq_moe_experts *t, size_t m, size_t top_k) {
-    auto ok_type = [](uint32_t ty) { return ty == ZQ_Q4_K || ty == ZQ_Q4_0 || ty == ZQ_Q8_0; };
+    auto ok_type = [](uint32_t ty) { return has_i8_decode(ty); };
     const size_t routes = m * top_k;
     return t->d_gate_maps && ok_type(t->gate_type) && ok_type(t->down_type) && t->num_experts <= 1024 && top_k <= 64 && routes <= 8192 && (t->num_experts * 2 + 1 + routes * 2) * 4 <= 200 * 1024 &&
            t->inter % 64 == 0;
@@ -468,11 +470,9 @@ int moe_grouped_forward(zq_ctx *ctx, const zq_moe_experts *t, const zq_weight *s
     }
     int rc;
     // ---- gate/up + SiLU
-    switch (t->gate_type) {
-    case ZQ_Q4_K: rc = launch_quantize<ZQ_Q4_K>(ctx, dev_x, x_dtype, d_slot_token, d_slot_expert, d_offsets, routes, srows, shared_id, (int)E, H, units_h, d_xq1, err); break;
-    case ZQ_Q4_0: rc = launch_quantize<ZQ_Q4_0>(ctx, dev_x, x_dtype, d_slot_token, d_slot_expert, d_offsets, routes, srows, shared_id, (int)E, H, units_h, d_xq1, err); break;
-    default: rc = launch_quantize<ZQ_Q8_0>(ctx, dev_x, x_dtype, d_slot_token, d_slot_expert, d_offsets, routes, srows, shared_id, (int)E, H, units_h, d_xq1, err); break;
-    }
+    // two record formats: the K-quant column order with group sums, and the block-32 order
+    if (is_kclass(t->gate_type)) rc = launch_quantize<ZQ_Q4_K>(ctx, dev_x, x_dtype, d_slot_token, d_slot_expert, d_offsets, routes, srows, shared_id, (int)E, H, units_h, d_xq1, err);
+    else rc = launch_quantize<ZQ_Q4_0>(ctx, dev_x, x_dtype, d_slot_token, d_slot_expert, d_offsets, routes, srows, shared_id, (int)E, H, units_h, d_xq1, err);
     if (rc) return rc;
     GroupedArgs ga;
     ga.maps_a = t->d_gate_maps;
@@ -497,16 +497,16 @@ int moe_grouped_forward(zq_ctx *ctx, const zq_moe_experts *t, const zq_weight *s
     }
     switch (t->gate_type) {
     case ZQ_Q4_K: rc = launch_grouped<ZQ_Q4_K, true>(ctx, ga, err); break;
+    case ZQ_Q5_K: rc = launch_grouped<ZQ_Q5_K, true>(ctx, ga, err); break;
+    case ZQ_Q6_K: rc = launch_grouped<ZQ_Q6_K, true>(ctx, ga, err); break;
     case ZQ_Q4_0: rc = launch_grouped<ZQ_Q4_0, true>(ctx, ga, err); break;
+    case ZQ_IQ4_NL: rc = launch_grouped<ZQ_IQ4_NL, true>(ctx, ga, err); break;
     default: rc = launch_grouped<ZQ_Q8_0, true>(ctx, ga, err); break;
     }
     if (rc) return rc;
     // ---- down
-    switch (t->down_type) {
-    case ZQ_Q4_K: rc = launch_quantize<ZQ_Q4_K>(ctx, d_act, ZQ_F32, nullptr, d_slot_expert, d_offsets, routes, srows, shared_id, (int)E, I, units_i, d_xq2, err); break;
-    case ZQ_Q4_0: rc = launch_quantize<ZQ_Q4_0>(ctx, d_act, ZQ_F32, nullptr, d_slot_expert, d_offsets, routes, srows, shared_id, (int)E, I, units_i, d_xq2, err); break;
-    default: rc = launch_quantize<ZQ_Q8_0>(ctx, d_act, ZQ_F32, nullptr, d_slot_expert, d_offsets, routes, srows, shared_id, (int)E, I, units_i, d_xq2, err); break;
-    }
+    if (is_kclass(t->down_type)) rc = launch_quantize<ZQ_Q4_K>(ctx, d_act, ZQ_F32, nullptr, d_slot_expert, d_offsets, routes, srows, shared_id, (int)E, I, units_i, d_xq2, err);
+    else rc = launch_quantize<ZQ_Q4_0>(ctx, d_act, ZQ_F32, nullptr, d_slot_expert, d_offsets, routes, srows, shared_id, (int)E, I, units_i, d_xq2, err);
     if (rc) return rc;
     ga.maps_a = t->d_down_maps;
     ga.maps_b = t->d_down_maps;
@@ -523,7 +523,10 @@ int moe_grouped_forward(zq_ctx *ctx, const zq_moe_experts *t, const zq_weight *s
     }
     switch (t->down_type) {
     case ZQ_Q4_K: rc = launch_grouped<ZQ_Q4_K, false>(ctx, ga, err); break;
+    case ZQ_Q5_K: rc = launch_grouped<ZQ_Q5_K, false>(ctx, ga, err); break;
+    case ZQ_Q6_K: rc = launch_grouped<ZQ_Q6_K, false>(ctx, ga, err); break;
     case ZQ_Q4_0: rc = launch_grouped<ZQ_Q4_0, false>(ctx, ga, err); break;
+    case ZQ_IQ4_NL: rc = launch_grouped<ZQ_IQ4_NL, false>(ctx, ga, err); break;
     default: rc = launch_grouped<ZQ_Q8_0, false>(ctx, ga, err); break;
     }
     return rc;
