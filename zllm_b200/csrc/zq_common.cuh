@@ -298,6 +298,7 @@ struct zq_ctx {
     int force_fused_gemm = 0;      // Q4_K prefill: the fused kernel for every token count (tests)
     int disable_fused_gemm = 0;    // Q4_K prefill: separate f16 operand pass + plain GEMM instead of the fused kernel
     int force_moe_per_expert = 0;  // MoE forward: always the host-grouped per-expert path (tests)
+    const void *moe_row_sink = nullptr;  // zq::PeerRowSink of the expert-parallel forward while it runs its local experts, else null
     int force_moe_host_grouping = 0;  // MoE prefill: group the routes on the host instead of on the device (tests, A/B)
     std::atomic<uint64_t> launches{0};
     std::mutex mutex;

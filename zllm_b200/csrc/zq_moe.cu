@@ -238,7 +238,7 @@ __global__ void __launch_bounds__(kRouterThreads) router_logits16_kernel(const u
         float acc[kRouter16Tokens];
 #pragma unroll
         for (int t = 0; t < kRouter16Tokens; ++t) acc[t] = 0.f;
-#pragma unroll 4
+#pragma unroll 8
         for (int c4 = lane; c4 < hidden / 4; c4 += 32) {
             const float4 wv = __ldg(w4 + c4);
 #pragma unroll
@@ -282,15 +282,49 @@ __global__ void split_f16_kernel(const void *__restrict__ src, int dtype, size_t
     }
 }
 
+// The same operands cut into `chunks` slices of the (3x longer) K, slice c of all rows stored together ([chunk][rows][kc]):
+// with few tokens one GEMM over the whole K has too few tiles for the machine, so the slices become the "matrices" of a
+// grouped GEMM whose partial logits router_select_kernel adds in ascending order.
+__global__ void split_f16_chunked_kernel(const void *__restrict__ src, int dtype, size_t rows, int cols, int pattern, int kc, __half *__restrict__ dst) {
+    const size_t total = rows * (size_t)cols;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / cols;
+        const int c = (int)(i - r * cols);
+        const float v = load_as_f32(src, dtype, i);
+        const __half hi = __float2half_rn(v), lo = __float2half_rn(v - __half2float(hi));
+        const __half seg[3] = {hi, pattern == 0 ? hi : lo, pattern == 0 ? lo : hi};
+#pragma unroll
+        for (int sgm = 0; sgm < 3; ++sgm) {
+            const int g = sgm * cols + c, chunk = g / kc, kcol = g - chunk * kc;
+            dst[((size_t)chunk * rows + r) * kc + kcol] = seg[sgm];
+        }
+    }
+}
+
+// work list of that grouped GEMM: item = {slice, first expert row, first token row, end of the slice's token rows}
+__global__ void router_items_kernel(int chunks, int row_tiles, int tok_tiles, int m, int4 *__restrict__ items) {
+    const int n = chunks * row_tiles * tok_tiles;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const int c = i / (row_tiles * tok_tiles), rem = i - c * row_tiles * tok_tiles, rt = rem / tok_tiles, tt = rem - rt * tok_tiles;
+        items[i] = make_int4(c, rt * 128, c * m + tt * 256, c * m + m);
+    }
+}
+
 // Second half of the split router: one warp per token, logits from global memory.
+// `chunks` > 1: the logits arrive as that many partial sums over slices of the hidden dimension ([chunk][m][experts]) and are
+// added here in ascending order.
 __global__ void __launch_bounds__(kRouterThreads) router_select_kernel(const float *__restrict__ logits_g, const float *__restrict__ bias, int m, int num_experts, int top_k, float scaling, int normalize_selected,
-                                                                        uint32_t *__restrict__ ids, float *__restrict__ weights, uint32_t *status, int scoring) {
+                                                                        uint32_t *__restrict__ ids, float *__restrict__ weights, uint32_t *status, int scoring, int chunks = 1) {
     extern __shared__ float rsm[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tok = blockIdx.x * (kRouterThreads / 32) + warp;
     if (tok >= m) return;
     float *l = rsm + warp * num_experts;
-    for (int e = lane; e < num_experts; e += 32) l[e] = logits_g[(size_t)tok * num_experts + e] + ((bias && scoring == ZQ_ROUTE_SOFTMAX) ? bias[e] : 0.f);
+    for (int e = lane; e < num_experts; e += 32) {
+        float v = logits_g[(size_t)tok * num_experts + e];
+        for (int c = 1; c < chunks; ++c) v += logits_g[((size_t)c * m + tok) * num_experts + e];
+        l[e] = v + ((bias && scoring == ZQ_ROUTE_SOFTMAX) ? bias[e] : 0.f);
+    }
     __syncwarp();
     router_select(l, lane, num_experts, top_k, scaling, normalize_selected, ids + (size_t)tok * top_k, weights + (size_t)tok * top_k, status, scoring, bias);
 }
@@ -307,21 +341,61 @@ __global__ void gather_rows_kernel(const void *__restrict__ x, int dtype, const 
 }
 
 // y[t] = ((sum_j w[t,j] * out[slot[t,j]]) + shared[t]) + residual[t]; slots of a token are in ascending expert order.
-__global__ void combine_kernel(const float *__restrict__ routed, const uint32_t *__restrict__ slots, const float *__restrict__ w, int top_k, const float *__restrict__ shared, const void *__restrict__ residual, void *__restrict__ y,
-                               int y_dtype, size_t m, int hidden) {
-    const size_t total = m * (size_t)hidden;
+// Four columns per thread (hidden is a multiple of 32).  With a sink (expert-parallel owner side) the rows go to the source
+// ranks' return buffers instead of y.
+__global__ void __launch_bounds__(256) combine_kernel(const float *__restrict__ routed, const uint32_t *__restrict__ slots, const float *__restrict__ w, int top_k, const float *__restrict__ shared,
+                                                      const void *__restrict__ residual, void *__restrict__ y, int y_dtype, size_t m, int hidden, const PeerRowSink sink) {
+    const int hv = hidden / 4;
+    const size_t total = m * (size_t)hv;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        size_t t = i / hidden;
-        int c = (int)(i - t * hidden);
-        float acc = 0.f;
+        const size_t t = i / hv;
+        const int c = (int)(i - t * hv);
+        float *sink_row = nullptr;
+        if (sink.world) {
+            const int s = (int)(t / sink.cap), r = (int)(t - (size_t)s * sink.cap);
+            if (r >= sink.counts[s]) continue;  // nothing was sent for this place
+            sink_row = sink.base[s] + (size_t)r * hidden;
+        }
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int j = 0; j < top_k; ++j) {
             const float wj = w[t * top_k + j];
             if (wj == 0.f) continue;  // an absent route (ZQ_MOE_NO_ROUTE) has no slot: nothing is read for it
-            acc = __fadd_rn(acc, __fmul_rn(routed[(size_t)slots[t * top_k + j] * hidden + c], wj));
+            const float4 v = __ldcs(reinterpret_cast<const float4 *>(routed + (size_t)slots[t * top_k + j] * hidden) + c);
+            acc.x = __fadd_rn(acc.x, __fmul_rn(v.x, wj));
+            acc.y = __fadd_rn(acc.y, __fmul_rn(v.y, wj));
+            acc.z = __fadd_rn(acc.z, __fmul_rn(v.z, wj));
+            acc.w = __fadd_rn(acc.w, __fmul_rn(v.w, wj));
         }
-        if (shared) acc = __fadd_rn(acc, shared[i]);
-        if (residual) acc = __fadd_rn(acc, load_as_f32(residual, y_dtype, i));
-        store_from_f32(y, y_dtype, i, acc);
+        float vv[4] = {acc.x, acc.y, acc.z, acc.w};
+        const size_t o = t * (size_t)hidden + 4 * (size_t)c;
+        if (shared) {
+            const float4 sh = *reinterpret_cast<const float4 *>(shared + o);
+            vv[0] = __fadd_rn(vv[0], sh.x); vv[1] = __fadd_rn(vv[1], sh.y); vv[2] = __fadd_rn(vv[2], sh.z); vv[3] = __fadd_rn(vv[3], sh.w);
+        }
+        if (residual) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) vv[q] = __fadd_rn(vv[q], load_as_f32(residual, y_dtype, o + q));
+        }
+        if (sink_row) {
+            reinterpret_cast<float4 *>(sink_row)[c] = make_float4(vv[0], vv[1], vv[2], vv[3]);
+        } else if (y_dtype == ZQ_F32) {
+            *reinterpret_cast<float4 *>(reinterpret_cast<float *>(y) + o) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+        } else {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) store_from_f32(y, y_dtype, o + q, vv[q]);
+        }
+    }
+    if (sink.world) {  // rows first, then the flags: every CTA fences its peer stores, the last one to arrive announces them
+        __threadfence_system();
+        __syncthreads();
+        __shared__ int s_last;
+        if (threadIdx.x == 0) s_last = atomicAdd(sink.done, 1u) == gridDim.x - 1;
+        __syncthreads();
+        if (s_last) {
+            __threadfence_system();
+            if ((int)threadIdx.x < sink.world) asm volatile("st.release.sys.global.v2.u32 [%0], {%1,%2};" ::"l"(sink.flag[threadIdx.x]), "r"(0u), "r"(sink.epoch) : "memory");
+            if (threadIdx.x == 0) *sink.done = 0;
+        }
     }
 }
 
@@ -461,15 +535,18 @@ __global__ void __launch_bounds__(kGroupThreads) moe_prefill_place_kernel(const 
         atomicAdd(&s_cnt[id], 1u);
     }
     __syncthreads();
-    for (int e = threadIdx.x; e < E; e += kGroupThreads) {
-        if (s_cnt[e] == 0) continue;
-        uint32_t slot = offsets[e] + hist[(size_t)blockIdx.x * E + e];
-        for (int r = 0; r < nr; ++r) {
-            if (s_ids[r] == (uint32_t)e) {
-                slot_token[slot] = (uint32_t)((r0 + r) / top_k);
-                s_slot[r] = slot++;
-            }
-        }
+    // every route counts the earlier routes of its expert inside the chunk itself (independent compares over at most
+    // 1024 entries, instead of a serial walk per expert)
+    for (int r = threadIdx.x; r < nr; r += kGroupThreads) {
+        const uint32_t id = s_ids[r];
+        if (id == (uint32_t)E) continue;
+        uint32_t before = 0;
+        int r2 = 0;
+        for (; r2 + 4 <= r; r2 += 4) before += (s_ids[r2] == id) + (s_ids[r2 + 1] == id) + (s_ids[r2 + 2] == id) + (s_ids[r2 + 3] == id);
+        for (; r2 < r; ++r2) before += s_ids[r2] == id;
+        const uint32_t slot = offsets[id] + hist[(size_t)blockIdx.x * E + id] + before;
+        slot_token[slot] = (uint32_t)((r0 + r) / top_k);
+        s_slot[r] = slot;
     }
     __syncthreads();
     for (int t = threadIdx.x; t < t1 - t0; t += kGroupThreads) {
@@ -579,7 +656,7 @@ static int moe_prefill_device(zq_ctx *ctx, const zq_moe_experts *experts, const 
         rc = zq_gated_mlp(ctx, shared_gate, shared_up, shared_down, dev_x, x_dtype, m, d_shared, ZQ_F32, nullptr, err);
         if (rc) return rc;
     }
-    combine_kernel<<<grid_for(ctx, m * H, 256), 256, 0, ctx->stream>>>(d_out, d_token_slots, d_token_w, (int)top_k, d_shared, dev_residual, dev_y, y_dtype, m, (int)H);
+    combine_kernel<<<grid_for(ctx, m * (H / 4), 256), 256, 0, ctx->stream>>>(d_out, d_token_slots, d_token_w, (int)top_k, d_shared, dev_residual, dev_y, y_dtype, m, (int)H, ctx->moe_row_sink ? *reinterpret_cast<const PeerRowSink *>(ctx->moe_row_sink) : PeerRowSink());
     ctx->launches++;
     ZQ_CUDA_CHECK(cudaGetLastError(), err);
     return ZQ_OK;
@@ -624,21 +701,43 @@ int zq_moe_route_topk(zq_ctx *ctx, int scoring, const void *dev_x, int x_dtype, 
     }
     if (m >= 256 && hidden % 8 == 0) {
         auto al = [](size_t v) { return (v + 255) & ~size_t(255); };
-        const size_t xb = al(m * 3 * hidden * sizeof(__half)), wb = al(num_experts * 3 * hidden * sizeof(__half));
-        int rc = ensure_moe_ws(ctx, xb + wb + al(m * num_experts * sizeof(float)), err);
+        // slices of K as separate tiles while the whole-K tiles would leave most SMs idle
+        const int row_tiles = (int)((num_experts + 127) / 128), tok_tiles = (int)((m + 255) / 256);
+        int chunks = 1;
+        if (hidden % 64 == 0)
+            for (int c = 16; c >= 2; --c)
+                if ((3 * hidden / 64) % c == 0 && row_tiles * tok_tiles * c <= 2 * ctx->sm_count) {
+                    chunks = c;
+                    break;
+                }
+        const int n_items = chunks * row_tiles * tok_tiles;
+        const size_t xb = al(m * 3 * hidden * sizeof(__half)), wb = al(num_experts * 3 * hidden * sizeof(__half)), lb = al((size_t)chunks * m * num_experts * sizeof(float));
+        int rc = ensure_moe_ws(ctx, xb + wb + lb + al((size_t)n_items * sizeof(int4)), err);
         if (rc) return rc;
         uint8_t *ws = reinterpret_cast<uint8_t *>(ctx->moe_ws);
         __half *x3 = reinterpret_cast<__half *>(ws), *w3 = reinterpret_cast<__half *>(ws + xb);
         float *logits_g = reinterpret_cast<float *>(ws + xb + wb);
-        split_f16_kernel<<<grid_for(ctx, m * hidden, 256), 256, 0, ctx->stream>>>(dev_x, x_dtype, m, (int)hidden, 0, x3);
-        split_f16_kernel<<<grid_for(ctx, num_experts * hidden, 256), 256, 0, ctx->stream>>>(dev_router_f32, ZQ_F32, num_experts, (int)hidden, 1, w3);
-        ctx->launches += 2;
-        ZQ_CUDA_CHECK(cudaGetLastError(), err);
-        rc = launch_gemm_f16(ctx, w3, num_experts, 3 * hidden, x3, m, logits_g, ZQ_F32, err);
-        if (rc) return rc;
+        int4 *d_items = reinterpret_cast<int4 *>(ws + xb + wb + lb);
         const unsigned sel_grid = (unsigned)((m + kRouterThreads / 32 - 1) / (kRouterThreads / 32));
+        if (chunks > 1) {
+            const int kc = (int)(3 * hidden / chunks);
+            split_f16_chunked_kernel<<<grid_for(ctx, m * hidden, 256), 256, 0, ctx->stream>>>(dev_x, x_dtype, m, (int)hidden, 0, kc, x3);
+            split_f16_chunked_kernel<<<grid_for(ctx, num_experts * hidden, 256), 256, 0, ctx->stream>>>(dev_router_f32, ZQ_F32, num_experts, (int)hidden, 1, kc, w3);
+            router_items_kernel<<<(n_items + 255) / 256, 256, 0, ctx->stream>>>(chunks, row_tiles, tok_tiles, (int)m, d_items);
+            ctx->launches += 3;
+            ZQ_CUDA_CHECK(cudaGetLastError(), err);
+            rc = launch_gemm_grouped(ctx, w3, nullptr, (size_t)chunks, num_experts, (size_t)kc, x3, (size_t)chunks * m, d_items, n_items, logits_g, ZQ_F32, err);
+            if (rc) return rc;
+        } else {
+            split_f16_kernel<<<grid_for(ctx, m * hidden, 256), 256, 0, ctx->stream>>>(dev_x, x_dtype, m, (int)hidden, 0, x3);
+            split_f16_kernel<<<grid_for(ctx, num_experts * hidden, 256), 256, 0, ctx->stream>>>(dev_router_f32, ZQ_F32, num_experts, (int)hidden, 1, w3);
+            ctx->launches += 2;
+            ZQ_CUDA_CHECK(cudaGetLastError(), err);
+            rc = launch_gemm_f16(ctx, w3, num_experts, 3 * hidden, x3, m, logits_g, ZQ_F32, err);
+            if (rc) return rc;
+        }
         router_select_kernel<<<sel_grid, kRouterThreads, (kRouterThreads / 32) * num_experts * sizeof(float), ctx->stream>>>(logits_g, dev_bias_f32, (int)m, (int)num_experts, (int)top_k, scaling_factor, normalize_selected, dev_ids,
-                                                                                                                            dev_weights, ctx->status_dev, scoring);
+                                                                                                                            dev_weights, ctx->status_dev, scoring, chunks);
         ctx->launches++;
         ZQ_CUDA_CHECK(cudaGetLastError(), err);
         return ZQ_OK;
@@ -818,7 +917,7 @@ int zq_moe_forward(zq_ctx *ctx, const zq_moe_experts *experts, const zq_weight *
             rc = zq_gated_mlp(ctx, shared_gate, shared_up, shared_down, dev_x, x_dtype, m, d_shared, ZQ_F32, nullptr, err);
             if (rc) return rc;
         }
-        combine_kernel<<<grid_for(ctx, m * H, 256), 256, 0, ctx->stream>>>(d_out, d_token_slots, d_token_w, (int)top_k, d_shared, dev_residual, dev_y, y_dtype, m, (int)H);
+        combine_kernel<<<grid_for(ctx, m * (H / 4), 256), 256, 0, ctx->stream>>>(d_out, d_token_slots, d_token_w, (int)top_k, d_shared, dev_residual, dev_y, y_dtype, m, (int)H, ctx->moe_row_sink ? *reinterpret_cast<const PeerRowSink *>(ctx->moe_row_sink) : PeerRowSink());
         ctx->launches++;
         ZQ_CUDA_CHECK(cudaGetLastError(), err);
         return ZQ_OK;
@@ -1040,7 +1139,7 @@ int zq_moe_forward(zq_ctx *ctx, const zq_moe_experts *experts, const zq_weight *
         rc = zq_gated_mlp(ctx, shared_gate, shared_up, shared_down, dev_x, x_dtype, m, d_shared, ZQ_F32, nullptr, err);
         if (rc) return rc;
     }
-    combine_kernel<<<grid_for(ctx, m * H, 256), 256, 0, ctx->stream>>>(d_out, d_token_slots, d_token_w, (int)top_k, d_shared, dev_residual, dev_y, y_dtype, m, (int)H);
+    combine_kernel<<<grid_for(ctx, m * (H / 4), 256), 256, 0, ctx->stream>>>(d_out, d_token_slots, d_token_w, (int)top_k, d_shared, dev_residual, dev_y, y_dtype, m, (int)H, ctx->moe_row_sink ? *reinterpret_cast<const PeerRowSink *>(ctx->moe_row_sink) : PeerRowSink());
     ctx->launches++;
     ZQ_CUDA_CHECK(cudaGetLastError(), err);
     return ZQ_OK;

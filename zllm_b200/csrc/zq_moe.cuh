@@ -18,6 +18,19 @@ struct zq_moe_experts {
 
 namespace zq {
 
+// Where the combine of zq_moe_forward puts its rows when the caller is the expert-parallel forward: row r = s * cap + i
+// (row i of what source rank s sent) goes, as f32, straight into rank s's return buffer over NVLink, rows beyond the
+// count that s sent are skipped, and the last CTA to finish announces the rows to every source ({0, epoch} flags, as the
+// separate return kernel did).  Unused (world = 0) everywhere else.
+struct PeerRowSink {
+    float *base[8] = {};        // per source rank: first row of this rank's block in that rank's return buffer
+    uint2 *flag[8] = {};        // per source rank: this rank's return flag in that rank's buffer
+    const int *counts = nullptr;  // rows each source sent
+    uint32_t *done = nullptr;   // arrival counter of the CTAs (zero between uses)
+    uint32_t epoch = 0;
+    int cap = 0, world = 0;
+};
+
 bool moe_grouped_supported(const zq_moe_experts *t, size_t m, size_t top_k);
 size_t moe_grouped_ws_bytes(const zq_moe_experts *t, size_t m, size_t top_k, bool has_shared);
 bool moe_shared_rides_along(const zq_moe_experts *t, const zq_weight *sg, const zq_weight *su, const zq_weight *sd);

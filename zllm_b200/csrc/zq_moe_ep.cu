@@ -15,8 +15,8 @@
 //                 last CTA publishes {row count, epoch} to every destination
 //   ep_gate       waits (bounded) for every source's count, marks the unused rows of the dispatch buffer "no route"
 //   (experts)     zq_moe_forward on the received rows: a token's routes on this rank are weighted and summed HERE, so one
-//                 row per (token, rank) travels back
-//   ep_return     stores those rows into the sources' return buffers, publishes the epoch
+//                 row per (token, rank) travels back; the forward's combine kernel stores those rows straight into the
+//                 sources' return buffers (PeerRowSink) and its last CTA publishes the epoch
 //   ep_combine    waits (bounded) for every owner rank, then y = residual + shared + sum over ranks in ascending order
 // Every wait has a limit in nanoseconds; a wait that runs out sets the device status word and the kernel goes on, so
 // nothing hangs (zq_ctx_sync reports it).  A rank finishes a call only after every peer has sent its part of the same
@@ -196,26 +196,6 @@ __global__ void __launch_bounds__(1024) ep_gate_kernel(const EpArgs a, int *recv
             ids[i] = ZQ_MOE_NO_ROUTE;
             wts[i] = 0.f;
         }
-    }
-}
-
-// grid (chunks, world): the summed expert outputs of source s's rows back into s's return buffer.
-__global__ void __launch_bounds__(kEpThreads) ep_return_kernel(const EpArgs a, const int *recv_cnt, const float *out_rows) {
-    const int s = blockIdx.y;
-    const int n = recv_cnt[s];
-    float4 *dst = reinterpret_cast<float4 *>(a.peers[s] + a.off_ret) + ((size_t)a.rank * a.cap) * (a.hidden / 4);
-    const float4 *src = reinterpret_cast<const float4 *>(out_rows) + ((size_t)s * a.cap) * (a.hidden / 4);
-    const size_t total = (size_t)n * (a.hidden / 4);
-    for (size_t i = (size_t)blockIdx.x * kEpThreads + threadIdx.x; i < total; i += (size_t)gridDim.x * kEpThreads) dst[i] = src[i];
-    __threadfence_system();
-    __syncthreads();
-    __shared__ int s_last;
-    if (threadIdx.x == 0) s_last = atomicAdd(a.done, 1u) == gridDim.x * gridDim.y - 1;
-    __syncthreads();
-    if (s_last) {
-        __threadfence_system();
-        if (threadIdx.x < a.world) ep_st_flag(reinterpret_cast<uint2 *>(a.peers[threadIdx.x] + 2048 + 16 * a.rank), make_uint2(0u, a.epoch));
-        if (threadIdx.x == 0) *a.done = 0;
     }
 }
 
@@ -416,17 +396,29 @@ int zq_moe_forward_ep(zq_ctx *ctx, const zq_moe_experts *local_experts, const zq
     ZQ_CUDA_CHECK(cudaGetLastError(), err);
     // this rank's experts on everything it received: one output row per received row = the weighted sum of that token's
     // routes on this rank
+    // The combine of the local forward writes each summed row straight into its source rank's return buffer and its last
+    // CTA sets the return flags: no local copy of the rows, no separate return pass.
     uint8_t *local = s->exchange;
+    PeerRowSink sink;
+    for (int r = 0; r < world; ++r) {
+        sink.base[r] = reinterpret_cast<float *>(s->peers[r] + l.off_ret) + ((size_t)rank * l.cap) * l.hidden;
+        sink.flag[r] = reinterpret_cast<uint2 *>(s->peers[r] + 2048 + 16 * rank);
+    }
+    sink.counts = recv_cnt;
+    sink.done = a.done;
+    sink.epoch = a.epoch;
+    sink.cap = (int)l.cap;
+    sink.world = world;
+    ctx->moe_row_sink = &sink;
     rc = zq_moe_forward(ctx, local_experts, nullptr, nullptr, nullptr, local + l.off_rows, x_dtype, (size_t)world * l.cap, reinterpret_cast<const uint32_t *>(local + l.off_ids),
                         reinterpret_cast<const float *>(local + l.off_w), top_k, s->out_rows, ZQ_F32, nullptr, err);
+    ctx->moe_row_sink = nullptr;
     if (rc) return rc;
-    const unsigned rchunks = (unsigned)((m * l.hidden / 4 + kEpThreads * 8 - 1) / (kEpThreads * 8) < 128 ? (m * l.hidden / 4 + kEpThreads * 8 - 1) / (kEpThreads * 8) : 128);
-    ep_return_kernel<<<dim3(rchunks ? rchunks : 1, (unsigned)world), kEpThreads, 0, ctx->stream>>>(a, recv_cnt, s->out_rows);
     const size_t tot = m * l.hidden / 4;
     size_t cblocks = (tot + kEpThreads - 1) / kEpThreads;
     if (cblocks > (size_t)ctx->sm_count * 8) cblocks = (size_t)ctx->sm_count * 8;
     ep_combine_kernel<<<(unsigned)cblocks, kEpThreads, 0, ctx->stream>>>(a, has_shared ? s->shared_out : nullptr, dev_residual, dev_y, y_dtype);
-    ctx->launches += 2;
+    ctx->launches += 1;
     ZQ_CUDA_CHECK(cudaGetLastError(), err);
     return ZQ_OK;
 }

@@ -108,15 +108,33 @@ __global__ void __launch_bounds__(kPlanThreads) moe_plan_kernel(const uint32_t *
         }
     }
     __syncthreads();
-    // token-major stable slots: the thread of expert e walks the routes in order
-    for (int e = threadIdx.x; e < E; e += kPlanThreads) {
-        if (s_cnt[e] == 0) continue;
-        uint32_t slot = s_off[e];
-        for (int r = 0; r < routes; ++r) {
-            if (s_ids[r] == (uint32_t)e) {
-                slot_token[slot] = (uint32_t)(r / top_k);
-                slot_expert[slot] = (uint32_t)e;
-                s_slot[r] = slot++;
+    // token-major stable slots
+    if (routes <= 2048) {
+        // few routes (decode): every route counts the earlier routes of its expert itself: independent compares, no
+        // serial walk (a quarter of the time of the walk below at 512 routes)
+        for (int r = threadIdx.x; r < routes; r += kPlanThreads) {
+            const uint32_t id = s_ids[r];
+            if (id == (uint32_t)E) continue;
+            uint32_t before = 0;
+            int r2 = 0;
+            for (; r2 + 4 <= r; r2 += 4) before += (s_ids[r2] == id) + (s_ids[r2 + 1] == id) + (s_ids[r2 + 2] == id) + (s_ids[r2 + 3] == id);
+            for (; r2 < r; ++r2) before += s_ids[r2] == id;
+            const uint32_t slot = s_off[id] + before;
+            slot_token[slot] = (uint32_t)(r / top_k);
+            slot_expert[slot] = id;
+            s_slot[r] = slot;
+        }
+    } else {
+        // many routes: the thread of expert e walks the routes in order
+        for (int e = threadIdx.x; e < E; e += kPlanThreads) {
+            if (s_cnt[e] == 0) continue;
+            uint32_t slot = s_off[e];
+            for (int r = 0; r < routes; ++r) {
+                if (s_ids[r] == (uint32_t)e) {
+                    slot_token[slot] = (uint32_t)(r / top_k);
+                    slot_expert[slot] = (uint32_t)e;
+                    s_slot[r] = slot++;
+                }
             }
         }
     }
