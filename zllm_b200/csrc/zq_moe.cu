@@ -17,6 +17,7 @@
 // over gathered token rows.
 #include <algorithm>
 
+#include "zq_i8.cuh"
 #include "zq_moe.cuh"
 
 using namespace zq;
@@ -226,11 +227,22 @@ __global__ void __launch_bounds__(kRouterThreads) router_logits16_kernel(const u
     const int e_begin = blockIdx.y * experts_per_cta;
     const int e_end = e_begin + experts_per_cta < num_experts ? e_begin + experts_per_cta : num_experts;
     const int vec_per_row = hidden / 8;
-    for (int i = threadIdx.x; i < kRouter16Tokens * vec_per_row; i += kRouterThreads) {
-        const int t = i / vec_per_row, v = i - t * vec_per_row;
-        uint4 raw = make_uint4(0, 0, 0, 0);
-        if (tok0 + t < m) raw = reinterpret_cast<const uint4 *>(x + (size_t)(tok0 + t) * hidden)[v];
-        reinterpret_cast<uint4 *>(xs + (size_t)t * hidden)[v] = raw;
+    // the eight rows are contiguous in x: a flat copy, four 16-byte loads in flight per thread
+    const int live_vec = (m - tok0 < kRouter16Tokens ? m - tok0 : kRouter16Tokens) * vec_per_row, all_vec = kRouter16Tokens * vec_per_row;
+    const uint4 *src = reinterpret_cast<const uint4 *>(x + (size_t)tok0 * hidden);
+    uint4 *dst = reinterpret_cast<uint4 *>(xs);
+    for (int i = threadIdx.x; i < all_vec; i += 4 * kRouterThreads) {
+        uint4 raw[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int k = i + j * kRouterThreads;
+            raw[j] = k < live_vec ? __ldg(src + k) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int k = i + j * kRouterThreads;
+            if (k < all_vec) dst[k] = raw[j];
+        }
     }
     __syncthreads();
     for (int e = e_begin + warp; e < e_end; e += kRouterThreads / 32) {
@@ -238,21 +250,28 @@ __global__ void __launch_bounds__(kRouterThreads) router_logits16_kernel(const u
         float acc[kRouter16Tokens];
 #pragma unroll
         for (int t = 0; t < kRouter16Tokens; ++t) acc[t] = 0.f;
-#pragma unroll 8
-        for (int c4 = lane; c4 < hidden / 4; c4 += 32) {
-            const float4 wv = __ldg(w4 + c4);
+        const int hv = hidden / 4;
+        for (int base = lane; base < hv; base += 32 * 8) {  // eight 16-byte loads of the router row in flight, then the arithmetic
+            float4 wv[8];
 #pragma unroll
-            for (int t = 0; t < kRouter16Tokens; ++t) {
-                const uint2 raw = reinterpret_cast<const uint2 *>(xs + (size_t)t * hidden)[c4];
-                float x0, x1, x2, x3;
-                if (x_dtype == ZQ_F16) {
-                    const float2 a = __half22float2(u32_as_h2(raw.x)), b = __half22float2(u32_as_h2(raw.y));
-                    x0 = a.x; x1 = a.y; x2 = b.x; x3 = b.y;
-                } else {  // bf16: the upper half of an f32
-                    x0 = __uint_as_float(raw.x << 16); x1 = __uint_as_float(raw.x & 0xFFFF0000u);
-                    x2 = __uint_as_float(raw.y << 16); x3 = __uint_as_float(raw.y & 0xFFFF0000u);
+            for (int j = 0; j < 8; ++j) wv[j] = base + 32 * j < hv ? __ldg(w4 + base + 32 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int c4 = base + 32 * j;
+                if (c4 >= hv) break;
+#pragma unroll
+                for (int t = 0; t < kRouter16Tokens; ++t) {
+                    const uint2 raw = reinterpret_cast<const uint2 *>(xs + (size_t)t * hidden)[c4];
+                    float x0, x1, x2, x3;
+                    if (x_dtype == ZQ_F16) {
+                        const float2 a = __half22float2(u32_as_h2(raw.x)), b = __half22float2(u32_as_h2(raw.y));
+                        x0 = a.x; x1 = a.y; x2 = b.x; x3 = b.y;
+                    } else {  // bf16: the upper half of an f32
+                        x0 = __uint_as_float(raw.x << 16); x1 = __uint_as_float(raw.x & 0xFFFF0000u);
+                        x2 = __uint_as_float(raw.y << 16); x3 = __uint_as_float(raw.y & 0xFFFF0000u);
+                    }
+                    acc[t] = fmaf(x3, wv[j].w, fmaf(x2, wv[j].z, fmaf(x1, wv[j].y, fmaf(x0, wv[j].x, acc[t]))));
                 }
-                acc[t] = fmaf(x3, wv.w, fmaf(x2, wv.z, fmaf(x1, wv.y, fmaf(x0, wv.x, acc[t]))));
             }
         }
 #pragma unroll
@@ -268,35 +287,32 @@ __global__ void __launch_bounds__(kRouterThreads) router_logits16_kernel(const u
 // flip top-k choices, so both operands are split into two f16 limbs (v = hi + lo, 22 bits) and the three products
 // that matter ride in ONE GEMM over a 3x longer K: x -> [hi | hi | lo], w -> [hi | lo | hi]; the products of f16
 // numbers are exact in the f32 accumulator, the dropped lo*lo term is 2^-22 of a product.
-__global__ void split_f16_kernel(const void *__restrict__ src, int dtype, size_t rows, int cols, int pattern, __half *__restrict__ dst) {
-    const size_t total = rows * (size_t)cols;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        const size_t r = i / cols;
-        const int c = (int)(i - r * cols);
-        const float v = load_as_f32(src, dtype, i);
-        const __half hi = __float2half_rn(v), lo = __float2half_rn(v - __half2float(hi));
-        __half *d = dst + r * 3 * (size_t)cols + c;
-        d[0] = hi;
-        d[cols] = pattern == 0 ? hi : lo;
-        d[2 * (size_t)cols] = pattern == 0 ? lo : hi;
-    }
-}
-
-// The same operands cut into `chunks` slices of the (3x longer) K, slice c of all rows stored together ([chunk][rows][kc]):
+// The operands are stored cut into `chunks` slices of that K, slice c of all rows together ([chunk][rows][kc]; one slice =
+// the plain [rows][3 K] layout):
 // with few tokens one GEMM over the whole K has too few tiles for the machine, so the slices become the "matrices" of a
 // grouped GEMM whose partial logits router_select_kernel adds in ascending order.
 __global__ void split_f16_chunked_kernel(const void *__restrict__ src, int dtype, size_t rows, int cols, int pattern, int kc, __half *__restrict__ dst) {
-    const size_t total = rows * (size_t)cols;
+    // eight consecutive columns per thread (cols and kc are multiples of 8, so they never straddle a slice): one 16- or
+    // 32-byte load, three 16-byte stores
+    const int groups = cols / 8;
+    const size_t total = rows * (size_t)groups;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        const size_t r = i / cols;
-        const int c = (int)(i - r * cols);
-        const float v = load_as_f32(src, dtype, i);
-        const __half hi = __float2half_rn(v), lo = __float2half_rn(v - __half2float(hi));
-        const __half seg[3] = {hi, pattern == 0 ? hi : lo, pattern == 0 ? lo : hi};
+        const size_t r = i / groups;
+        const int c = (int)(i - r * groups) * 8;
+        float v[8];
+        load_act8(src, dtype, r * (size_t)cols + c, true, v);
+        __align__(16) __half hi[8], lo[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            hi[q] = __float2half_rn(v[q]);
+            lo[q] = __float2half_rn(v[q] - __half2float(hi[q]));
+        }
+        const uint4 vh = *reinterpret_cast<const uint4 *>(hi), vl = *reinterpret_cast<const uint4 *>(lo);
+        const uint4 seg[3] = {vh, pattern == 0 ? vh : vl, pattern == 0 ? vl : vh};
 #pragma unroll
         for (int sgm = 0; sgm < 3; ++sgm) {
             const int g = sgm * cols + c, chunk = g / kc, kcol = g - chunk * kc;
-            dst[((size_t)chunk * rows + r) * kc + kcol] = seg[sgm];
+            *reinterpret_cast<uint4 *>(dst + ((size_t)chunk * rows + r) * kc + kcol) = seg[sgm];
         }
     }
 }
@@ -721,16 +737,16 @@ int zq_moe_route_topk(zq_ctx *ctx, int scoring, const void *dev_x, int x_dtype, 
         const unsigned sel_grid = (unsigned)((m + kRouterThreads / 32 - 1) / (kRouterThreads / 32));
         if (chunks > 1) {
             const int kc = (int)(3 * hidden / chunks);
-            split_f16_chunked_kernel<<<grid_for(ctx, m * hidden, 256), 256, 0, ctx->stream>>>(dev_x, x_dtype, m, (int)hidden, 0, kc, x3);
-            split_f16_chunked_kernel<<<grid_for(ctx, num_experts * hidden, 256), 256, 0, ctx->stream>>>(dev_router_f32, ZQ_F32, num_experts, (int)hidden, 1, kc, w3);
+            split_f16_chunked_kernel<<<grid_for(ctx, m * hidden / 8, 256), 256, 0, ctx->stream>>>(dev_x, x_dtype, m, (int)hidden, 0, kc, x3);
+            split_f16_chunked_kernel<<<grid_for(ctx, num_experts * hidden / 8, 256), 256, 0, ctx->stream>>>(dev_router_f32, ZQ_F32, num_experts, (int)hidden, 1, kc, w3);
             router_items_kernel<<<(n_items + 255) / 256, 256, 0, ctx->stream>>>(chunks, row_tiles, tok_tiles, (int)m, d_items);
             ctx->launches += 3;
             ZQ_CUDA_CHECK(cudaGetLastError(), err);
             rc = launch_gemm_grouped(ctx, w3, nullptr, (size_t)chunks, num_experts, (size_t)kc, x3, (size_t)chunks * m, d_items, n_items, logits_g, ZQ_F32, err);
             if (rc) return rc;
         } else {
-            split_f16_kernel<<<grid_for(ctx, m * hidden, 256), 256, 0, ctx->stream>>>(dev_x, x_dtype, m, (int)hidden, 0, x3);
-            split_f16_kernel<<<grid_for(ctx, num_experts * hidden, 256), 256, 0, ctx->stream>>>(dev_router_f32, ZQ_F32, num_experts, (int)hidden, 1, w3);
+            split_f16_chunked_kernel<<<grid_for(ctx, m * hidden / 8, 256), 256, 0, ctx->stream>>>(dev_x, x_dtype, m, (int)hidden, 0, (int)(3 * hidden), x3);  // one slice: the plain [rows][3 K] layout
+            split_f16_chunked_kernel<<<grid_for(ctx, num_experts * hidden / 8, 256), 256, 0, ctx->stream>>>(dev_router_f32, ZQ_F32, num_experts, (int)hidden, 1, (int)(3 * hidden), w3);
             ctx->launches += 2;
             ZQ_CUDA_CHECK(cudaGetLastError(), err);
             rc = launch_gemm_f16(ctx, w3, num_experts, 3 * hidden, x3, m, logits_g, ZQ_F32, err);
