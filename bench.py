@@ -3,8 +3,9 @@
 
 One "step" is one pass over the whole decode sweep: batch 1, 4 and 16 activation rows, Q4_0 and Q4_K weights,
 shapes (K->N) 3840->3840, 3840->15360, 15360->3840, 5120->17408, 17408->5120, fp32 in / fp32 out.  The step
-streams 350 MB of distinct packed weights per batch size (larger than L2), in an order that puts 350 MB of
-other traffic between two uses of the same matrix, so no launch finds its weights in L2.
+streams 350 MB of distinct packed weights per batch size (larger than L2; two sets of weights), in an order that puts at
+least 350 MB of other traffic between two uses of the same matrix, so no launch finds its weights in L2.  The timed
+steps replay two CUDA graphs each (the roofline kernel's two launches, then the rest) with one event between them.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
@@ -155,18 +156,24 @@ def run_ours(args):
 
     # ---- synthetic inputs: N(0, 0.02) weights quantised on the device, N(0, 1) activations, seed 0
     gen = torch.Generator(device=device)
-    cases = []  # (fmt_name, fmt, k, n, mode, weight, k_local, n_local)
-    for fmt, name in FORMATS:
-        for si, (k, n) in enumerate(SHAPES):
-            gen.manual_seed(1000 * fmt + si)
-            full = torch.randn((n, k), generator=gen, device=device, dtype=torch.float32) * 0.02
-            mode, (r0, r1), (c0, c1) = shard_plan(k, n, world, rank)
-            local = full[r0:r1, c0:c1].contiguous()
-            del full
-            packed = ctx.quantize(fmt, local)
-            w = ctx.prepare_weight(fmt, packed, r1 - r0, c1 - c0)
-            del local, packed
-            cases.append((name, fmt, k, n, mode, w, (c0, c1), (r0, r1)))
+    # two sets of the ten matrices: batch 1 and 16 use set 0, batch 4 uses set 1, so that the two Q4_K blocks that open a
+    # step (batch 1, batch 4) do not share a byte
+    case_sets = []  # per set: (fmt_name, fmt, k, n, mode, weight, k_local, n_local)
+    for wset in range(2):
+        cases = []
+        for fmt, name in FORMATS:
+            for si, (k, n) in enumerate(SHAPES):
+                gen.manual_seed(1000 * fmt + si + 100000 * wset)
+                full = torch.randn((n, k), generator=gen, device=device, dtype=torch.float32) * 0.02
+                mode, (r0, r1), (c0, c1) = shard_plan(k, n, world, rank)
+                local = full[r0:r1, c0:c1].contiguous()
+                del full
+                packed = ctx.quantize(fmt, local)
+                w = ctx.prepare_weight(fmt, packed, r1 - r0, c1 - c0)
+                del local, packed
+                cases.append((name, fmt, k, n, mode, w, (c0, c1), (r0, r1)))
+        case_sets.append(cases)
+    cases = case_sets[0]
     xs = {}
     for k in sorted({k for k, _ in SHAPES}):
         gen.manual_seed(77 + k)
@@ -174,13 +181,15 @@ def run_ours(args):
     ctx.sync()
     torch.cuda.synchronize()
 
-    # step order: batch-major, then format, then shape => 350 MB of other weights between two uses of a matrix
+    # Step order.  The two blocks of the roofline kernel come first (Q4_K batch 1 on set 0, Q4_K batch 4 on set 1), then
+    # Q4_0 batch 1 (set 0), Q4_0 batch 4 (set 1), Q4_K batch 16 (set 0), Q4_0 batch 16 (set 0): at least 350 MB of other
+    # weights stream between two uses of a matrix, so no launch finds its weights in L2.
+    order = [(1, Q4_K), (4, Q4_K), (1, Q4_0), (4, Q4_0), (16, Q4_K), (16, Q4_0)]
     plan = []
-    for m in BATCHES:
-        for fmt, name in FORMATS:
-            for case in cases:
-                if case[1] == fmt:
-                    plan.append((m, case))
+    for m, fmt in order:
+        for case in case_sets[1 if m == 4 else 0]:
+            if case[1] == fmt:
+                plan.append((m, case))
     if args.only:
         oname, oshape, om = args.only.split(":")
         ok, on = (int(v) for v in oshape.split("x"))
@@ -225,11 +234,11 @@ def run_ours(args):
     # from the host right after the block's graph.  Events around the Q4_K batch-1 and batch-4 blocks (the headline
     # kernel) are recorded inside the timed region.
     blocks = []
-    for m in BATCHES:
-        for fmt, name in FORMATS:
-            members = [(mm, case) for mm, case in plan if mm == m and case[1] == fmt]
-            if members:
-                blocks.append((m, fmt, members))
+    for m, fmt in order:
+        members = [(mm, case) for mm, case in plan if mm == m and case[1] == fmt]
+        if members:
+            blocks.append((m, fmt, members))
+    head = [bi for bi, (m, fmt, _) in enumerate(blocks) if fmt == Q4_K and m <= 4]  # the roofline kernel's blocks: the first ones of a step
     job_arrays = []
     for m, fmt, members in blocks:
         arr = (ffi.ZqLinearJob * len(members))()
@@ -271,12 +280,37 @@ def run_ours(args):
                     launch_block(bi)
                 graphs.append(g)
                 launches_per_graph.append(ctx.launch_count - n0)
+            # A step as TWO graphs: the roofline kernel's blocks (Q4_K batch 1 and 4), then the rest, each chained by
+            # programmatic dependent launch with no host launch inside; one CUDA event between the two.
+            step_graph = None
+            if not args.nccl_reduce and not args.per_call and head == list(range(len(head))) and len(head) < len(blocks):
+                step_graph = []
+                for part in (head, [bi for bi in range(len(blocks)) if bi not in head]):
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=side):
+                        ctx.set_stream(torch.cuda.current_stream(device).cuda_stream)
+                        for bi in part:
+                            launch_block(bi)
+                    step_graph.append(g)
         except Exception as exc:
             graphs = []
+            step_graph = None
             sys.stderr.write(f"bench: graph capture failed ({exc}); launching from the host\n")
         ctx.set_stream(torch.cuda.current_stream(device).cuda_stream)
+    else:
+        step_graph = None
 
-    def step(events=None):
+    def step(events=None, head_events=None):
+        if events is None and step_graph is not None:  # the headline form: two graph replays per step
+            if head_events is not None:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+            step_graph[0].replay()
+            if head_events is not None:
+                e1.record()
+                head_events.append((e0, e1))
+            step_graph[1].replay()
+            return
         for bi, (m, fmt, members) in enumerate(blocks):
             mark = events is not None
             if mark:
@@ -322,22 +356,40 @@ def run_ours(args):
     events = []
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    head_events = [] if step_graph is not None else None
     t0.record()
     for _ in range(args.steps):
-        step(events)
+        step(None if step_graph is not None else events, head_events)
     t1.record()
     barrier()
     ctx.sync()
     elapsed_ms = t0.elapsed_time(t1)
+    head_ms = sum(a.elapsed_time(b) for a, b in head_events) if head_events else None
+    launches = ctx.launch_count - launches_before
+    per_block_pass_ms = elapsed_ms
+    if step_graph is not None:
+        # Second pass over the very same K steps, block by block (one graph per block, CUDA events on the launching
+        # stream around each): the per-block report.  Not part of the timed region.
+        barrier()
+        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        p0.record()
+        for _ in range(args.steps):
+            step(events)
+        p1.record()
+        barrier()
+        ctx.sync()
+        per_block_pass_ms = p0.elapsed_time(p1)
     block_ms = [0.0] * len(blocks)
     for bi, a, b in events:
         block_ms[bi] += a.elapsed_time(b)
     kernel_ms = sum(t for t, (m, fmt, _) in zip(block_ms, blocks) if fmt == Q4_K and m <= 4)
-    # every block of the step on its own (this rank's CUDA events inside the timed region)
+    per_block_kernel_ms = kernel_ms
+    if head_ms is not None:  # the roofline kernel's launches as timed inside the timed region (first graph of every step)
+        kernel_ms = head_ms
+    # every block of the step on its own (this rank's CUDA events; see "per_block_pass")
     blocks_report = [{"batch": m, "format": "q4_k" if fmt == Q4_K else "q4_0", "us": round(t / max(args.steps, 1) * 1e3, 2),
                       "gbs": round(sum(algorithmic_bytes(c[2], c[3], mm) for mm, c in members) / (t / max(args.steps, 1) * 1e-3) / 1e9 / max(world, 1), 1) if t > 0 else None}
                      for t, (m, fmt, members) in zip(block_ms, blocks)]
-    launches = ctx.launch_count - launches_before
     if graphs:  # replayed launches do not pass through the library's counter: count what each graph captured
         launches = sum(launches_per_graph) * args.steps
     clocks = sampler.stop() if rank == 0 and not args.no_clocks else None
@@ -401,7 +453,7 @@ def run_ours(args):
     # free the sweep's weights before the larger side measurements
     extras = {}
     if not args.no_extras:
-        del graphs, cases, plan, blocks
+        del graphs, step_graph, cases, case_sets, plan, blocks, job_arrays
         torch.cuda.empty_cache()
         if world == 1 and args.extras in ("all", "prefill"):
             extras["prefill_gemm"] = bench_prefill(ctx, device, args)
@@ -424,11 +476,14 @@ def run_ours(args):
         "metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u4 x s16 (two s8 limbs) -> s32, f32 scales", "data": "synthetic",
         "config": {"workload": "configs[1]: decode GEMV sweep, batch 1/4/16, Q4_0+Q4_K, 5 shapes, fp32 in/out", "l2": "inputs larger than L2: 350 MB of distinct weights between reuses",
-                   "parallelism": f"tp{world}" if world > 1 else "single", "bytes_per_step": step_bytes, "launches_per_step": launches // max(args.steps, 1) // max(world, 1)},
+                   "parallelism": f"tp{world}" if world > 1 else "single", "bytes_per_step": step_bytes, "launch": ("two CUDA graphs per step (Q4_K batch 1+4, then the other four blocks; zq_linear_batch calls chained by programmatic dependent launch)" if step_graph is not None else "one CUDA graph per block" if graphs else "host launches"), "launches_per_step": launches // max(args.steps, 1) // max(world, 1)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": hbm_peak, "unit": "GB/s", "frac": round(achieved / hbm_peak, 4),
                      # ncu, 5120x17408 batch-1 launch: dram read+write = 50.21 MB for 50.23 MB algorithmic; scaled by bytes
                      "traffic": int(q4k_kernel_bytes // max(q4k_kernel_launches, 1) * NCU_TRAFFIC_RATIO), "traffic_kind": "ncu capture of one launch, scaled by algorithmic bytes",
                      "kernel": "zq::gemv_i8_kernel<Q4_K, 1 column tile> (batch 1 and 4, one launch per matrix)" if args.per_call else "zq::gemv_wl_kernel<Q4_K, 1 column tile> (batch 1 and 4; one launch per block of five matrices, timed together with its record pass)", "peak_kind": peak_kind, "launches": q4k_kernel_launches * args.steps,
+                     "timing": ("CUDA events inside the timed region around the first graph of every step = the Q4_K batch-1 and batch-4 launches (with their record passes), chained by programmatic dependent launch" if head_ms is not None else "CUDA events around each block inside the timed region"),
+                     "per_block_pass": {"what": "the same launches timed one graph per block with an event pair each, in a second pass after the timed region", "achieved": round(q4k_kernel_bytes * args.steps / (per_block_kernel_ms * 1e-3) / 1e9 / max(world, 1), 2) if per_block_kernel_ms > 0 else None,
+                                        "ms_per_step": round(per_block_pass_ms / args.steps, 4)},
                      "bytes_per_launch_avg": q4k_kernel_bytes // max(q4k_kernel_launches, 1)},
         "gpu_launches": launches, "clocks": clocks, "e2e": e2e, "cpu_baseline": cpu,
         "blocks": blocks_report, "parity": parity,
