@@ -82,23 +82,30 @@ __global__ void __launch_bounds__(kDistThreads) tp_allreduce_kernel(const __grid
     bool gave_up = false;
     int j = 0;
     for (int i = first; i < a.total; i += stride) {
+        // all peers' words of this element are requested together (one round trip when they have already arrived), then
+        // each is waited for
+        uint2 got[kDistMaxWorld];
+#pragma unroll
+        for (int src = 0; src < kDistMaxWorld; ++src)
+            if (src < a.world && src != a.rank) got[src] = ld_relaxed_sys_v2(slot_of(local, parity, src, a.world, a.slot_bytes) + i);
         float s = 0.f;
-        for (int src = 0; src < a.world; ++src) {
+#pragma unroll
+        for (int src = 0; src < kDistMaxWorld; ++src) {
+            if (src >= a.world) break;
             float v;
             if (src == a.rank) {
                 v = a.staging[i];
             } else {
                 const uint2 *word = slot_of(local, parity, src, a.world, a.slot_bytes) + i;
-                uint2 got = ld_relaxed_sys_v2(word);
-                while (got.y != tag && !gave_up) {
+                while (got[src].y != tag && !gave_up) {
                     if (global_timer_ns() - t0 > a.wait_ns) {  // give up: report, and let the kernel finish on whatever is there
                         gave_up = true;
                         atomicMax(a.status, (uint32_t)kStatusPeerTimeout);
                         break;
                     }
-                    got = ld_relaxed_sys_v2(word);
+                    got[src] = ld_relaxed_sys_v2(word);
                 }
-                v = __uint_as_float(got.x);
+                v = __uint_as_float(got[src].x);
             }
             s += v;
         }
@@ -152,7 +159,7 @@ int launch_tp_allreduce(zq_ctx *ctx, const DistReduceJob *jobs, size_t n_jobs, i
     a.status = ctx->status_dev;
     a.wait_ns = d->wait_ns ? d->wait_ns : kDistWaitNsDefault;
     // a few elements per thread: the same CTA count on every rank is not required (threads pair up by element index)
-    int slices = (total + kDistThreads * 4 - 1) / (kDistThreads * 4);
+    int slices = (total + kDistThreads - 1) / kDistThreads;  // one element per thread while the CTAs last: every wait is one round trip
     if (slices < 1) slices = 1;
     if (slices > kDistMaxSlices) slices = kDistMaxSlices;
     cudaLaunchConfig_t cfg = {};
