@@ -187,6 +187,16 @@ int zq_linear_host(zq_ctx *ctx, const zq_weight *w, const void *host_x, int x_dt
  * of one bracket is copied once). */
 int zq_batch_begin(zq_ctx *ctx, zq_error *err);
 int zq_batch_finish(zq_ctx *ctx, zq_error *err);
+/* A whole bracket in one call: zq_batch_begin, zq_linear_host for every job in order, zq_batch_finish.  For hosts whose
+ * per-call cost is not negligible (a scripting-language binding), and for callers that already hold a layer's list of
+ * projections.  Must not be called inside an open bracket. */
+typedef struct zq_linear_host_job {
+    const zq_weight *w;
+    const void *host_x;  /* [m, cols] */
+    size_t m;
+    void *host_y;        /* [m, rows] */
+} zq_linear_host_job;
+int zq_linear_host_batch(zq_ctx *ctx, const zq_linear_host_job *jobs, size_t n_jobs, int x_dtype, int y_dtype, zq_error *err);
 
 /* ---- MoE: kernel::cuda::routing (src/kernel/cuda/routing.rs:167-210) and the expert entry points
  * (src/kernel/cuda/linear.rs:1735-1819; src/backend/cuda/expert.rs:572-918). ---- */

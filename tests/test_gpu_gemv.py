@@ -282,3 +282,19 @@ def test_an_error_inside_a_bracket_closes_it():
     ctx().begin_batch()       # and a new one opens cleanly
     ctx().linear_host(x, w, y)
     ctx().finish_batch()
+
+
+def test_host_batch_is_a_whole_bracket_in_one_call():
+    rows, cols = 384, 1024
+    types = (H.Q4_K, H.Q8_0)
+    datas = [H.random_weight(t, rows, cols, seed=140 + i) for i, t in enumerate(types)]
+    ws = [ctx().prepare_weight(t, d, rows, cols) for t, d in zip(types, datas)]
+    xs = [np.random.default_rng(141 + i).standard_normal((m, cols)).astype(np.float32) for i, m in enumerate((2, 5))]
+    ys = [np.zeros((x.shape[0], rows), dtype=np.float32) for x in xs]
+    ctx().linear_host_batch([(x, w, y) for x, w, y in zip(xs, ws, ys)])
+    for t, d, x, y in zip(types, datas, xs, ys):
+        _check(y, orc.linear(t, d, rows, cols, x))
+    from zllm_b200 import ffi
+    ctx().begin_batch()
+    with pytest.raises(ffi.ZqFailure):
+        ctx().linear_host_batch([(xs[0], ws[0], ys[0])])  # a bracket is already open (and this error closes it)

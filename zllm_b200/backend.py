@@ -328,6 +328,21 @@ class B200Context:
         return y_host
 
 
+    def linear_host_batch(self, jobs):
+        """A whole bracket in one call (``zq_linear_host_batch``): ``jobs`` is a list of ``(x_host, weight, y_host)`` numpy
+        triples sharing one input dtype and one output dtype."""
+        import numpy as np
+
+        dt = {np.dtype(np.float32): ffi.F32, np.dtype(np.float16): ffi.F16}
+        arr = (ffi.ZqLinearHostJob * len(jobs))()
+        for i, (x_host, w, y_host) in enumerate(jobs):
+            arr[i].w = w.handle.value
+            arr[i].host_x = x_host.ctypes.data
+            arr[i].m = x_host.size // w.cols
+            arr[i].host_y = y_host.ctypes.data
+        ffi.call("zq_linear_host_batch", self.handle, arr, len(jobs), dt[jobs[0][0].dtype], dt[jobs[0][2].dtype])
+
+
 class GgufFile:
     """``GgufReader`` (src/weight/container/gguf.rs:332-566): header, metadata and tensor directory of a GGUF v3 file (or
     of a set of standard split files); matrices and expert slices go straight to resident weights."""

@@ -724,4 +724,15 @@ int zq_linear_host(zq_ctx *ctx, const zq_weight *w, const void *host_x, int x_dt
     return ZQ_OK;
 }
 
+int zq_linear_host_batch(zq_ctx *ctx, const zq_linear_host_job *jobs, size_t n_jobs, int x_dtype, int y_dtype, zq_error *err) {
+    if (!ctx || (!jobs && n_jobs)) return set_error(err, ZQ_ERR_ARG, "zq_linear_host_batch: null argument");
+    int rc = zq_batch_begin(ctx, err);
+    if (rc) return rc;
+    for (size_t i = 0; i < n_jobs; ++i) {
+        rc = zq_linear_host(ctx, jobs[i].w, jobs[i].host_x, x_dtype, jobs[i].m, jobs[i].host_y, y_dtype, err);
+        if (rc) return rc;  // the failed call closed the bracket
+    }
+    return zq_batch_finish(ctx, err);
+}
+
 }  // extern "C"

@@ -41,6 +41,12 @@ class ZqLinearJob(C.Structure):
     _fields_ = [("w", C.c_void_p), ("w_up", C.c_void_p), ("dev_x", C.c_void_p), ("m", C.c_size_t), ("dev_y", C.c_void_p), ("dev_residual", C.c_void_p), ("flags", C.c_uint32)]
 
 
+class ZqLinearHostJob(C.Structure):
+    """``zq_linear_host_job``: one host-buffer projection of a ``zq_linear_host_batch`` call."""
+
+    _fields_ = [("w", C.c_void_p), ("host_x", C.c_void_p), ("m", C.c_size_t), ("host_y", C.c_void_p)]
+
+
 _err = C.POINTER(ZqError)
 
 PROTOTYPES = {
@@ -78,6 +84,7 @@ PROTOTYPES = {
     "zq_gated_mlp": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _sz, _vp, _i, _vp, _err]),
     "zq_linear_noalloc": (_i, [_vp, _vp, _vp, _i, _sz, _vp, _i, _err]),
     "zq_linear_host": (_i, [_vp, _vp, _vp, _i, _sz, _vp, _i, _err]),
+    "zq_linear_host_batch": (_i, [_vp, _vp, _sz, _i, _i, _err]),
     "zq_batch_begin": (_i, [_vp, _err]),
     "zq_batch_finish": (_i, [_vp, _err]),
     "zq_moe_route_softmax_topk": (_i, [_vp, _vp, _i, _sz, _sz, _vp, _vp, _sz, _sz, _f, _i, _vp, _vp, _err]),
