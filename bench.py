@@ -99,7 +99,7 @@ class ClockSampler:
                     reasons.add(name)
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(smax) if smax else None, "samples": len(sm), "reasons": sorted(reasons),
-                "window": "every 20 ms from before ~0.25 s of untimed steps of the same work, through the warm-up, to the end of the timed steps"}
+                "window": "every 20 ms from before ~0.25 s (several GPUs: 600) of untimed steps of the same work, through the warm-up, to the end of the timed steps"}
 
 
 def run_ours(args):
@@ -344,11 +344,19 @@ def run_ours(args):
     if rank == 0 and not args.no_clocks:
         sampler.start()
     if not args.no_clocks:
-        settle = time.perf_counter()
-        while time.perf_counter() - settle < 0.25:
-            for _ in range(20):
-                step()
-            torch.cuda.synchronize()
+        if world > 1:
+            # every rank must issue the same number of steps (the row-parallel reduces pair up across ranks), so the
+            # settle phase is a fixed count here, not a time
+            for _ in range(30):
+                for _ in range(20):
+                    step()
+                torch.cuda.synchronize()
+        else:
+            settle = time.perf_counter()
+            while time.perf_counter() - settle < 0.25:
+                for _ in range(20):
+                    step()
+                torch.cuda.synchronize()
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
