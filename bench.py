@@ -462,6 +462,8 @@ def run_ours(args):
         parity = {"tp_row_split_max_rel_error": tp_parity(ctx, device, world, rank), "ep_moe_max_rel_error": ep_parity(device, world, rank, local_rank), "bound": 2e-3,
                   "what": "TP: Q4_K 1024x4096, 4 rows, K-split over the ranks + peer-store reduce; "
                           "EP: 16 experts over the ranks, 64 tokens; both against float64 references on the bit-exact dequantised weights"}
+    launch_desc = ("two CUDA graphs per step (Q4_K batch 1+4, then the other four blocks; zq_linear_batch calls chained by programmatic dependent launch)" if step_graph is not None
+                   else "one CUDA graph per block" if graphs else "host launches")
     # free the sweep's weights before the larger side measurements
     extras = {}
     if not args.no_extras:
@@ -488,7 +490,7 @@ def run_ours(args):
         "metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u4 x s16 (two s8 limbs) -> s32, f32 scales", "data": "synthetic",
         "config": {"workload": "configs[1]: decode GEMV sweep, batch 1/4/16, Q4_0+Q4_K, 5 shapes, fp32 in/out", "l2": "inputs larger than L2: 350 MB of distinct weights between reuses",
-                   "parallelism": f"tp{world}" if world > 1 else "single", "bytes_per_step": step_bytes, "launch": ("two CUDA graphs per step (Q4_K batch 1+4, then the other four blocks; zq_linear_batch calls chained by programmatic dependent launch)" if step_graph is not None else "one CUDA graph per block" if graphs else "host launches"), "launches_per_step": launches // max(args.steps, 1) // max(world, 1)},
+                   "parallelism": f"tp{world}" if world > 1 else "single", "bytes_per_step": step_bytes, "launch": launch_desc, "launches_per_step": launches // max(args.steps, 1) // max(world, 1)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 2), "peak": hbm_peak, "unit": "GB/s", "frac": round(achieved / hbm_peak, 4),
                      # ncu, 5120x17408 batch-1 launch: dram read+write = 50.21 MB for 50.23 MB algorithmic; scaled by bytes
                      "traffic": int(q4k_kernel_bytes // max(q4k_kernel_launches, 1) * NCU_TRAFFIC_RATIO), "traffic_kind": "ncu capture of one launch, scaled by algorithmic bytes",
