@@ -459,9 +459,11 @@ def run_ours(args):
 
     parity = None
     if world > 1 and not args.nccl_reduce:
-        parity = {"tp_row_split_max_rel_error": tp_parity(ctx, device, world, rank), "ep_moe_max_rel_error": ep_parity(device, world, rank, local_rank), "bound": 2e-3,
-                  "what": "TP: Q4_K 1024x4096, 4 rows, K-split over the ranks + peer-store reduce; "
-                          "EP: 16 experts over the ranks, 64 tokens; both against float64 references on the bit-exact dequantised weights"}
+        parity = {"tp_row_split_max_rel_error": tp_parity(ctx, device, world, rank), "ep_moe_max_rel_error": ep_parity(device, world, rank, local_rank, experts_per_rank=16), "bound": 2e-3,
+                  "ep_moe_prefill_path_max_rel_error": ep_parity(device, world, rank, local_rank), "prefill_path_chain_bound": 4e-3,
+                  "what": "TP: Q4_K 1024x4096, 4 rows, K-split over the ranks + peer-store reduce; EP: 64 tokens, 16 experts per rank (owners on the decode path, as in the "
+                          "64-token case) and 16 experts in all (owners on the prefill path: two tensor-core GEMMs per expert with an f16 intermediate, each within 2e-3 of the "
+                          "CPU matmul on its own input, the chain of the two within 4e-3); all against float64 references on the bit-exact dequantised weights"}
     launch_desc = ("two CUDA graphs per step (Q4_K batch 1+4, then the other four blocks; zq_linear_batch calls chained by programmatic dependent launch)" if step_graph is not None
                    else "one CUDA graph per block" if graphs else "host launches")
     # free the sweep's weights before the larger side measurements
@@ -542,18 +544,20 @@ def tp_parity(ctx, device, world, rank):
     return float(t[0])
 
 
-def ep_parity(device, world, rank, local_rank):
-    """Correctness of the expert-parallel MoE forward on the hardware it runs on, outside any timed region: 16 experts
+def ep_parity(device, world, rank, local_rank, experts_per_rank=None):
+    """Correctness of the expert-parallel MoE forward on the hardware it runs on, outside any timed region: experts
     (Q4_K, hidden 512, FFN 256, top-4, one shared expert) over the ranks, 64 tokens data-parallel, against the same
     layer in float64 on the library's (bit-exact) dequantised weights, for this rank's tokens.  Largest error over the
-    ranks."""
+    ranks.  With 16 experts per rank the owners run the decode path (integer-MMA kernels, f32 intermediate), as the
+    64-token case of the bench does; with 16 experts in all they run the prefill path (tensor-core GEMMs, f16
+    intermediate between the two GEMMs of an expert)."""
     import torch
     import torch.distributed as dist
 
     from zllm_b200.backend import B200Context, MoeExperts, moe_forward, moe_forward_ep, moe_route
     from zllm_b200.dist import expert_range
 
-    E, K, H, I, M = 16, 4, 512, 256, 64
+    E, K, H, I, M = (experts_per_rank * world if experts_per_rank else 16), 4, 512, 256, 64
     c = B200Context(local_rank)
     c.dist_init(slot_bytes=1 << 20)
     c.moe_ep_init(M // world, H, K, E, dtype=torch.bfloat16)
