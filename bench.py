@@ -768,7 +768,7 @@ def bench_config3(ctx, device, hbm_peak, sustained_tflops):
         total_bytes += nbytes
     dec["all_seven"] = {"us": round(total_us, 2), "gbs": round(total_bytes / total_us / 1e3, 1)}
     dec["roofline"] = {"bound": "hbm", "achieved": round(total_bytes / total_us / 1e3, 1), "peak": hbm_peak, "unit": "GB/s", "frac": round(total_bytes / total_us / 1e3 / hbm_peak, 4),
-                       "kernels": "Q8_0: integer-MMA decode kernel; IQ4_NL: f16 warp-MMA decode kernel (codebook lookup per weight)"}
+                       "kernels": "integer-MMA decode kernel, one launch per matrix (IQ4_NL: codebook looked up with byte permutes)"}
     out["decode_m1"] = dec
     m = 4096
     xb = torch.randn((m, hidden), generator=gen, device=device, dtype=torch.float32).to(torch.bfloat16)

@@ -189,7 +189,7 @@ int zq_batch_begin(zq_ctx *ctx, zq_error *err);
 int zq_batch_finish(zq_ctx *ctx, zq_error *err);
 /* A whole bracket in one call: zq_batch_begin, zq_linear_host for every job in order, zq_batch_finish.  For hosts whose
  * per-call cost is not negligible (a scripting-language binding), and for callers that already hold a layer's list of
- * projections.  Must not be called inside an open bracket. */
+ * projections.  Must not be called inside an open bracket (an error that, like every error, closes that bracket). */
 typedef struct zq_linear_host_job {
     const zq_weight *w;
     const void *host_x;  /* [m, cols] */

@@ -297,4 +297,6 @@ def test_host_batch_is_a_whole_bracket_in_one_call():
     from zllm_b200 import ffi
     ctx().begin_batch()
     with pytest.raises(ffi.ZqFailure):
-        ctx().linear_host_batch([(xs[0], ws[0], ys[0])])  # a bracket is already open (and this error closes it)
+        ctx().linear_host_batch([(xs[0], ws[0], ys[0])])  # a bracket is already open; like every error this closes it
+    with pytest.raises(ffi.ZqFailure):
+        ctx().finish_batch()

@@ -726,6 +726,10 @@ int zq_linear_host(zq_ctx *ctx, const zq_weight *w, const void *host_x, int x_dt
 
 int zq_linear_host_batch(zq_ctx *ctx, const zq_linear_host_job *jobs, size_t n_jobs, int x_dtype, int y_dtype, zq_error *err) {
     if (!ctx || (!jobs && n_jobs)) return set_error(err, ZQ_ERR_ARG, "zq_linear_host_batch: null argument");
+    if (ctx->batch_active) {  // like every error inside a bracket, this one closes it
+        batch_abandon(ctx);
+        return set_error(err, ZQ_ERR_ARG, "zq_linear_host_batch: called inside an open bracket (the bracket is closed, none of its outputs is filled)");
+    }
     int rc = zq_batch_begin(ctx, err);
     if (rc) return rc;
     for (size_t i = 0; i < n_jobs; ++i) {
