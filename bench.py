@@ -35,8 +35,8 @@ FORMATS = [(Q4_K, "q4_k"), (Q4_0, "q4_0")]
 METRIC = "Q4_K/Q4_0 decode GEMV sweep, algorithmic HBM GB/s"
 BPW = 0.5625
 # DRAM bytes (read + write) over algorithmic bytes of one captured launch of the roofline kernel (ncu, the Q4_K batch-1
-# block of five matrices: 177.65 MB read + 4.29 MB written for 175.28 MB algorithmic)
-NCU_TRAFFIC_RATIO = (177.65 + 4.29) / 175.28
+# block of five matrices: 177.70 MB read + 3.91 MB written for 175.83 MB algorithmic)
+NCU_TRAFFIC_RATIO = (177.70 + 3.91) / 175.83
 
 
 def algorithmic_bytes(k: int, n: int, m: int) -> int:
