@@ -178,7 +178,8 @@ int zq_linear_host(zq_ctx *ctx, const zq_weight *w, const void *host_x, int x_dt
 /* Backend::begin_batch / finish_batch (src/backend/mod.rs:307-323; the reference's Vulkan backend defers its command
  * submission the same way, src/backend/vulkan/mod.rs:194-215).  Between the two calls zq_linear_host only starts its
  * copy in and records the layer; recorded layers run as zq_linear_batch calls (several matrices per kernel launch),
- * as soon as a launch's worth of them is pending and the rest at zq_batch_finish, which copies the last results out,
+ * as soon as a launch's worth of them is pending (inputs and results travel on copy streams of the context's own beside
+ * the layers) and the rest at zq_batch_finish, which copies the last results out,
  * waits once and then fills the callers' output buffers; these must stay valid and must not be read until then.  An
  * error of a recorded layer is reported by the call that launches it or by the finish; any error closes the bracket.  Pageable input buffers may be reused
  * as soon as their zq_linear_host call returns (they are copied into the library's staging memory inside the call);

@@ -86,7 +86,7 @@ def test_gated_jobs_match_cpu_path(tensor_type, m, rows, cols):
     x = np.random.default_rng(23).standard_normal((m, cols)).astype(np.float32)
     # a gated job and a plain job in one call
     yg, yp = ctx().linear_batch([(dev(x), wg, wu, "gated"), (dev(x), wu)])
-    _check(host(yg), orc.gated_linear(tensor_type, gate, up, rows, cols, x), tight=2 * TIGHT)  # a product of two projections: each factor within TIGHT
+    _check(host(yg), orc.gated_linear(tensor_type, gate, up, rows, cols, x), tight=1e-3)  # silu(g) * u: where u is large and silu(g) small the error of g is weighed by u against the rms of the outputs
     _check(host(yp), orc.linear(tensor_type, up, rows, cols, x))
 
 

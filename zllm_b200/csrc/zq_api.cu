@@ -207,6 +207,10 @@ void zq_ctx_destroy(zq_ctx *ctx) {
         cudaFreeHost(c.pinned);
         cudaFree(c.dev);
     }
+    if (ctx->io_in) cudaStreamDestroy(ctx->io_in);
+    if (ctx->io_out) cudaStreamDestroy(ctx->io_out);
+    if (ctx->ev_in) cudaEventDestroy(ctx->ev_in);
+    if (ctx->ev_done) cudaEventDestroy(ctx->ev_done);
     if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
     delete ctx;
 }
@@ -569,8 +573,20 @@ static int batch_io_alloc(zq_ctx *ctx, size_t bytes, uint8_t **pinned, uint8_t *
 }
 
 // Drops whatever an open bracket holds: waits for what was enqueued, fills no output, forgets every caller pointer.
+static int batch_streams(zq_ctx *ctx, zq_error *err) {
+    if (ctx->io_in) return ZQ_OK;
+    ZQ_CUDA_CHECK(cudaStreamCreateWithFlags(&ctx->io_in, cudaStreamNonBlocking), err);
+    ZQ_CUDA_CHECK(cudaStreamCreateWithFlags(&ctx->io_out, cudaStreamNonBlocking), err);
+    ZQ_CUDA_CHECK(cudaEventCreateWithFlags(&ctx->ev_in, cudaEventDisableTiming), err);
+    ZQ_CUDA_CHECK(cudaEventCreateWithFlags(&ctx->ev_done, cudaEventDisableTiming), err);
+    return ZQ_OK;
+}
+
 static void batch_abandon(zq_ctx *ctx) {
+    if (ctx->io_in) cudaStreamSynchronize(ctx->io_in);
     cudaStreamSynchronize(ctx->stream);
+    if (ctx->io_out) cudaStreamSynchronize(ctx->io_out);
+    ctx->io_out_used = false;
     ctx->pending_out.clear();
     ctx->pending_linear.clear();
     ctx->pending_in.clear();
@@ -593,12 +609,18 @@ static int batch_flush(zq_ctx *ctx, zq_error *err) {
             jobs.push_back(j);
             ++e;
         }
+        // the layers wait for the inputs copied so far; the copies out wait for the layers and run beside the next batch
+        ZQ_CUDA_CHECK(cudaEventRecord(ctx->ev_in, ctx->io_in), err);
+        ZQ_CUDA_CHECK(cudaStreamWaitEvent(ctx->stream, ctx->ev_in, 0), err);
         int rc = zq_linear_batch(ctx, jobs.data(), jobs.size(), xd, yd, err);
         if (rc) return rc;
+        ZQ_CUDA_CHECK(cudaEventRecord(ctx->ev_done, ctx->stream), err);
+        ZQ_CUDA_CHECK(cudaStreamWaitEvent(ctx->io_out, ctx->ev_done, 0), err);
         for (size_t k = i; k < e; ++k) {
             const zq_ctx::PendingLinear &p = ctx->pending_linear[k];
-            ZQ_CUDA_CHECK(cudaMemcpyAsync(p.host_y_direct, p.dev_y, p.y_bytes, cudaMemcpyDeviceToHost, ctx->stream), err);
+            ZQ_CUDA_CHECK(cudaMemcpyAsync(p.host_y_direct, p.dev_y, p.y_bytes, cudaMemcpyDeviceToHost, ctx->io_out), err);
         }
+        ctx->io_out_used = true;
         i = e;
     }
     ctx->pending_linear.clear();
@@ -617,10 +639,15 @@ int zq_batch_finish(zq_ctx *ctx, zq_error *err) {
     if (!ctx->batch_active) return set_error(err, ZQ_ERR_ARG, "zq_batch_finish: no batch is open");
     int rc = batch_flush(ctx, err);
     if (!rc) rc = zq_ctx_sync(ctx, err);
+    if (!rc && ctx->io_out_used) {
+        cudaError_t ce = cudaStreamSynchronize(ctx->io_out);
+        if (ce != cudaSuccess) rc = set_error(err, ZQ_ERR_CUDA, "zq_batch_finish: copies out failed: %s", cudaGetErrorString(ce));
+    }
     if (rc) {
         batch_abandon(ctx);
         return rc;
     }
+    ctx->io_out_used = false;
     ctx->batch_active = false;
     for (const auto &o : ctx->pending_out) memcpy(o.host, o.pinned, o.bytes);
     ctx->pending_out.clear();
@@ -653,6 +680,7 @@ int zq_linear_host(zq_ctx *ctx, const zq_weight *w, const void *host_x, int x_dt
                 if (pi.host == host_x && pi.bytes == xb) dev_in = pi.dev;
         uint8_t *px = nullptr, *dx = nullptr;
         rc = use_device(ctx, err);
+        if (!rc) rc = batch_streams(ctx, err);
         if (!rc) rc = batch_io_alloc(ctx, (dev_in ? 0 : xb_al) + yb, &px, &dx, err);
         if (!rc && !dev_in) {
             const void *src = host_x;
@@ -660,7 +688,7 @@ int zq_linear_host(zq_ctx *ctx, const zq_weight *w, const void *host_x, int x_dt
                 memcpy(px, host_x, xb);
                 src = px;
             }
-            cudaError_t ce = cudaMemcpyAsync(dx, src, xb, cudaMemcpyHostToDevice, ctx->stream);
+            cudaError_t ce = cudaMemcpyAsync(dx, src, xb, cudaMemcpyHostToDevice, ctx->io_in);
             if (ce != cudaSuccess) rc = set_error(err, ZQ_ERR_CUDA, "zq_linear_host: copy in failed: %s", cudaGetErrorString(ce));
             if (!rc && x_pinned) ctx->pending_in.push_back({host_x, xb, dx});
         }

@@ -280,6 +280,11 @@ struct zq_ctx {
     // bracket's finish, together with the bracket's other layers, as one zq_linear_batch call (work-list launches).
     struct PendingLinear { const zq_weight *w; const uint8_t *dev_x; size_t m; uint8_t *dev_y; void *host_y_direct; size_t y_bytes; int x_dtype, y_dtype; };
     struct PendingIn { const void *host; size_t bytes; const uint8_t *dev; };  // page-locked inputs already copied in this bracket
+    // Copy streams of a bracket: inputs travel on io_in and results on io_out while the compute stream runs the layers
+    // (events order a batch of layers after its inputs and the copies out after the batch); created on first use.
+    cudaStream_t io_in = nullptr, io_out = nullptr;
+    cudaEvent_t ev_in = nullptr, ev_done = nullptr;
+    bool io_out_used = false;
     std::vector<IoChunk> io_chunks;
     std::vector<PendingOut> pending_out;
     std::vector<PendingLinear> pending_linear;
