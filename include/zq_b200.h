@@ -273,7 +273,9 @@ int zq_moe_ep_export(zq_ctx *ctx, size_t max_tokens_per_rank, size_t hidden, siz
 int zq_moe_ep_init(zq_ctx *ctx, const void *all_handles, zq_error *err);
 void zq_moe_ep_shutdown(zq_ctx *ctx);
 /* `m` = this rank's tokens; `m_cap` = the largest m of any rank in this call (the same value on every rank, at most the
- * allocated bound; 0 = every rank passes the same m). */
+ * allocated bound; 0 = every rank passes the same m).  Every call advances an exchange epoch that the host passes to the
+ * kernels, so the call is issued from the host each time (a replayed CUDA graph would repeat a stale epoch), unlike the
+ * row-parallel reduce, whose epoch lives on the device. */
 int zq_moe_forward_ep(zq_ctx *ctx, const zq_moe_experts *local_experts, const zq_weight *shared_gate, const zq_weight *shared_up, const zq_weight *shared_down, const void *dev_x, int x_dtype, size_t m, size_t m_cap,
                       const uint32_t *dev_ids, const float *dev_weights, size_t top_k, void *dev_y, int y_dtype, const void *dev_residual, zq_error *err);
 
