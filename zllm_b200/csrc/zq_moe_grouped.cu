@@ -22,6 +22,7 @@ constexpr int kPassRows = 8;                    // activation rows per pass (two
 constexpr int kPassUnitBytes = kPassRows * kRec;  // record slot of one unit inside a ring stage
 constexpr int kItemCache = 512;                 // work items whose descriptors a CTA keeps in shared memory
 constexpr int kPlanThreads = 1024;
+constexpr int kGroupedThreads = kI8Threads + 32;  // 16 consumer warps and a TMA producer warp
 // ring depth: the wide Q8_0 rows leave room for two stages only
 __host__ __device__ constexpr int grouped_stages(uint32_t type) { return type == ZQ_Q8_0 ? 2 : (type == ZQ_Q5_K || type == ZQ_Q6_K) ? 3 : 4; }
 
@@ -213,7 +214,7 @@ struct GroupedArgs {
 };
 
 template <uint32_t TYPE, bool GATED>
-__global__ void __launch_bounds__(kI8Threads, 1) moe_grouped_kernel(const __grid_constant__ GroupedArgs ga) {
+__global__ void __launch_bounds__(kGroupedThreads, 1) moe_grouped_kernel(const __grid_constant__ GroupedArgs ga) {
     constexpr int UB = Fmt<TYPE>::unit_bytes;
     constexpr int PITCH = kChunkUnits * UB;
     constexpr int STAGE_W = kTileRows * PITCH;
@@ -276,9 +277,23 @@ __global__ void __launch_bounds__(kI8Threads, 1) moe_grouped_kernel(const __grid
             bulk_load_1d(dst + STAGE_W + u * kPassUnitBytes, ga.xq + rec * kRec, mc * kRec, &full[stage]);
         }
     };
-    if (tid == 0) {
-        const int pre = total_q < STAGES - 1 ? (int)total_q : STAGES - 1;
-        for (int s = 0; s < pre; ++s) issue(s, s);
+    if (warp == kI8Threads / 32) {
+        // ------------------------------------------------ producer warp: keeps the ring full; a stage is refilled as soon
+        // as all sixteen consumer warps have released it, whichever of them is late
+        if (lane == 0) {
+            int pstage = 0;
+            uint32_t pphase = 0;
+            for (long long q = 0; q < total_q; ++q) {
+                if (q >= STAGES) i8_wait_or_abort(&empty[pstage], pphase ^ 1u, &s_abort, ga.status);
+                if (*(volatile int *)&s_abort) break;  // never start a copy nobody will wait for
+                issue(q, pstage);
+                if (++pstage == STAGES) {
+                    pstage = 0;
+                    pphase ^= 1u;
+                }
+            }
+        }
+        return;
     }
 
     const int g = lane >> 2, t = lane & 3;
@@ -306,16 +321,6 @@ __global__ void __launch_bounds__(kI8Threads, 1) moe_grouped_kernel(const __grid
             }
             yacc1[0][0] = yacc1[0][1] = 0.f;
             yacc2[0][0] = yacc2[0][1] = yacc2[1][0] = yacc2[1][1] = 0.f;
-        }
-        {
-            // refill: the stage consumed one iteration ago takes the ring item STAGES-1 ahead; a different warp each time
-            const long long nxt = q + STAGES - 1;
-            if (nxt < total_q && warp == (int)(q & 15) && lane == 0) {
-                const int nstage = stage == 0 ? STAGES - 1 : stage - 1;
-                if (q >= 1) i8_wait_or_abort(&empty[nstage], stage == 0 ? phase ^ 1u : phase, &s_abort, ga.status);
-                if (!*(volatile int *)&s_abort) issue(nxt, nstage);  // never start a copy nobody will wait for
-            }
-            __syncwarp();
         }
         i8_wait_or_abort(&full[stage], phase, &s_abort, ga.status);
         if (chunk * kChunkUnits + ul < ga.units) {
@@ -353,7 +358,7 @@ __global__ void __launch_bounds__(kI8Threads, 1) moe_grouped_kernel(const __grid
                     rb_[(ul * RS + nt * 4 + t) * kTileRows + r0 + 8] = yacc2[nt][1];
                 }
             }
-            __syncthreads();  // the other buffer is written next item, and read only after that item's barrier
+            asm volatile("bar.sync 1, %0;" ::"n"(kI8Threads) : "memory");  // the consumer warps only; the other buffer is written next item, and read only after that item's barrier
             const uint4 pe = pass_of(k);
             const int tile = (bid + k * G) % ga.tiles;
             const size_t slot0 = (size_t)pe.z + (pe.y & 0xFFFFu);
@@ -410,7 +415,7 @@ static int launch_grouped(zq_ctx *ctx, const GroupedArgs &ga, zq_error *err) {
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)ctx->sm_count);
-    cfg.blockDim = dim3(kI8Threads);
+    cfg.blockDim = dim3(kGroupedThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[1];
