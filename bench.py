@@ -1173,11 +1173,36 @@ def main():
     ap.add_argument("--only-moe", default=None, choices=["decode_m64", "prefill_m8192"], help="profiling aid: run only this MoE case and exit")
     ap.add_argument("--only-block", default=None, help="restrict the sweep to one block of five matrices, e.g. q4_k:1 (format:batch); for profiling")
     ap.add_argument("--only", default=None, help="restrict the sweep to one case, e.g. q4_k:5120x17408:1 (format:KxN:batch); for profiling")
+    ap.add_argument("--timeline", action="store_true", help="profiling aid for runs on several GPUs (where ncu is not used): record rank 0's kernels with the torch profiler (CUPTI) and print the last ones, with start offsets and durations, to stderr")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.timeline:
+        run_with_timeline(args)
     else:
         run_ours(args)
+
+
+def run_with_timeline(args):
+    """The same run under the torch profiler; rank 0 prints the kernels of the library that ran last (one forward of
+    --only-moe, or the last steps of the sweep) as `+start_us duration_us name` lines on stderr.  Times under a profiler
+    are for attribution, never bench values."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        run_ours(args)
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    events = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA and "zq::" in e.name]
+    events.sort(key=lambda e: e.time_range.start)
+    tail = events[-48:]
+    if not tail:
+        sys.stderr.write("timeline: no kernels of the library were recorded\n")
+        return
+    t0 = tail[0].time_range.start
+    for e in tail:
+        sys.stderr.write(f"+{e.time_range.start - t0:10.1f} {e.time_range.end - e.time_range.start:9.1f} us  {e.name[:110]}\n")
 
 
 if __name__ == "__main__":
